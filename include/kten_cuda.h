@@ -1,0 +1,189 @@
+/* kten_cuda.h -- C ABI of libkten_cuda.so, the sm_100a compute backend for the
+ * KTen tensor library's float32 hot path (broadcast elementwise ops, axis and
+ * full reductions, and the broadcast-gradient sum-to-shape reduction).
+ *
+ * This is the surface a `backend/kten-cuda` module binds (JNI `external fun`
+ * or Java FFM downcall handles) to implement the reference's backend SPI:
+ *   ART  = kten-api/src/main/kotlin/eu/redbean/kten/api/tensor/store/AbstractRawTensor.kt
+ *   TOPS = kten-api/src/main/kotlin/eu/redbean/kten/api/tensor/operations/TensorOperations.kt
+ *   JVM  = backend/kten-jvm/src/main/kotlin/eu/redbean/kten/jvm/tensor/store/JVMRawTensor.kt
+ *   OCLM = backend/kten-opencl/src/main/kotlin/eu/redbean/kten/opencl/tensor/store/OCLMemoryObject.kt
+ *   OCLE = backend/kten-opencl/src/main/kotlin/eu/redbean/kten/opencl/tensor/platform/OCLEnvironment.kt
+ *   OCLK = backend/kten-opencl/src/main/kotlin/eu/redbean/kten/opencl/tensor/platform/kernels/OCLKernels.kt
+ * Each entry point names the reference interface it stands in for.
+ *
+ * Conventions
+ *  - Every function returns 0 (KTC_OK) or a negative KTC_E* status; the text
+ *    of the last failure on the calling thread is ktc_last_error().
+ *  - Buffers are opaque 64-bit handles to device-resident float32 storage,
+ *    reference counted (a handle starts at 1).  Shapes live on the caller's
+ *    side exactly as AbstractRawTensor keeps them on the JVM heap (ART:5-23);
+ *    calls that need them take `const int64_t*` + ndim (ndim <= KTC_MAX_DIMS).
+ *  - All compute calls enqueue on the owning device's single in-order stream
+ *    (the role of the one in-order command queue at OCLE:291-299) and return
+ *    without waiting; host reads (ktc_d2h, ktc_get) wait for that stream.
+ *  - There is no CPU fallback: without a usable CUDA device ktc_init fails.
+ */
+#ifndef KTEN_CUDA_H
+#define KTEN_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define KTC_API __attribute__((visibility("default")))
+#else
+#define KTC_API
+#endif
+
+#define KTC_MAX_DIMS 10   /* same limit as the OpenCL backend's shape arrays (OCLKernelConstant.kt:4) */
+
+typedef uint64_t ktc_buf;   /* device buffer handle; 0 is never valid */
+typedef uint64_t ktc_comm;  /* communicator handle */
+
+/* status codes */
+enum {
+    KTC_OK        = 0,
+    KTC_EINVAL    = -1,  /* bad argument / shape mismatch  -> IllegalArgumentException */
+    KTC_ESTATE    = -2,  /* released handle, not initialised -> IllegalStateException (OCLM:167-170) */
+    KTC_ENOMEM    = -3,  /* pool limit or device allocation failure */
+    KTC_ECUDA     = -4,  /* CUDA runtime error */
+    KTC_ECOMM     = -5,  /* collective library error */
+    KTC_ETIMEOUT  = -6,  /* a bounded device-side wait ran out */
+    KTC_ENOTSUP   = -7
+};
+
+/* elementwise binary ops: JVM:110-140, kernels.cl calc_by_elwise_op (kernels.cl:79-94) */
+enum { KTC_PLUS = 0, KTC_MINUS = 1, KTC_TIMES = 2, KTC_DIV = 3, KTC_POW = 4 };
+/* unary maps: JVM:122,142,144,395-399, kernels.cl tensor_mapping_op (kernels.cl:132-156) */
+enum { KTC_EXP = 0, KTC_LOG = 1, KTC_TANH = 2, KTC_SIGMOID = 3, KTC_RECIPROCAL = 4, KTC_NEG = 5 };
+/* aggregations: kten-api/.../tensor/store/AggregatingOperation.kt:3-4 */
+enum { KTC_SUM = 0, KTC_MEAN = 1, KTC_MAX = 2, KTC_MIN = 3, KTC_ARGMAX = 4, KTC_ARGMIN = 5 };
+/* compares used by Clamp.doBackward (PointwiseFunctions.kt:154-162; JVM:355-393) */
+enum { KTC_LT = 0, KTC_LTE = 1, KTC_GT = 2, KTC_GTE = 3 };
+
+/* ---- lifecycle / devices ------------------------------------------------
+ * Stands in for OCLPlatformInitializer device enumeration
+ * (OCLPlatformInitializer.kt:20-41) and the lazily created per-device
+ * environment (OCLE:20-28). */
+KTC_API int ktc_init(int* n_devices);
+KTC_API int ktc_shutdown(void);
+KTC_API int ktc_device_info(int dev, char* name, size_t name_len, int64_t* total_mem_bytes, int* sm_count);
+KTC_API const char* ktc_last_error(void);
+KTC_API const char* ktc_version(void);
+
+/* ---- storage --------------------------------------------------------------
+ * ktc_alloc: createRaw(shape) (TOPS:16; OCLM lazy cl_mem + reuse pool OCLE:98-107,191-200).
+ * ktc_retain / ktc_release: incrementRef / release (TOPS:22-28; OCLM:108-145).
+ * ktc_wrap: adopt caller-owned device memory (not pooled, never freed here).
+ * ktc_pool_limit: PlatformProvider.memoryUsageScaleHint (PlatformProvider.kt:12-40, OCLE:53-54).
+ * ktc_pool_stats: PlatformMetricsProvider.getMetrics (PlatformMetricsProvider.kt:3-6, OCLE:89-96). */
+KTC_API int ktc_alloc(int dev, int64_t n_floats, ktc_buf* out);
+KTC_API int ktc_wrap(int dev, void* device_ptr, int64_t n_floats, ktc_buf* out);
+KTC_API int ktc_retain(ktc_buf buf);
+KTC_API int ktc_release(ktc_buf buf);
+KTC_API int ktc_refcount(ktc_buf buf, int* count);
+KTC_API int ktc_buf_info(ktc_buf buf, int* dev, int64_t* n_floats, void** device_ptr);
+KTC_API int ktc_pool_stats(int dev, int64_t* live_bytes, int64_t* cached_bytes, int64_t* n_alloc_calls, int64_t* n_pool_hits);
+KTC_API int ktc_pool_trim(int dev);
+KTC_API int ktc_pool_limit(int dev, int64_t max_bytes);   /* <= 0: no limit */
+
+/* pinned host staging memory for createRaw(shape, init) uploads (TOPS:11; OCLM:209-231) */
+KTC_API int ktc_host_alloc(int64_t n_floats, float** out);
+KTC_API int ktc_host_free(float* p);
+
+/* ---- transfers -------------------------------------------------------------
+ * h2d: createRaw(shape, init) / fromCommonSerializable (TOPS:11,135; OCLM:209-231).
+ * d2h: toSerializableData, getSingleValue, item() (TOPS:133; OCLM:189-207, 357-361).
+ * d2d: copy(shallow=false) (JVM:257-262; CLBlastScopy at OCLM:242).
+ * fill: createRawFill / zerosLike / zeroOut / inplaceFill (TOPS:18-26; kernels.cl:73-76).
+ * h2d/d2h are asynchronous when `sync` is 0 (the host range must then stay
+ * valid and, for real overlap, pinned, until ktc_sync). */
+KTC_API int ktc_h2d(ktc_buf dst, int64_t dst_off, const float* src, int64_t n, int sync);
+KTC_API int ktc_d2h(float* dst, ktc_buf src, int64_t src_off, int64_t n, int sync);
+KTC_API int ktc_d2d(ktc_buf dst, int64_t dst_off, ktc_buf src, int64_t src_off, int64_t n);
+KTC_API int ktc_fill(ktc_buf buf, int64_t off, int64_t n, float value);
+KTC_API int ktc_sync(int dev);
+
+/* ---- elementwise -----------------------------------------------------------
+ * ktc_binary:         elementwiseOpOnCommonShapedTensors (JVM:75-79), kernels.cl:96-99.
+ * ktc_binary_bcast:   elementwiseOpOnTensors (JVM:81-87) WITHOUT materialising
+ *                     the broadcast operand (replaces broadcast_to_shape,
+ *                     kernels.cl:44-70, + OCLRawTensor.kt:107-114).  Shapes are
+ *                     right-aligned; a non-singleton mismatch is KTC_EINVAL
+ *                     (ShapeFunctions.kt:168-185).  `out` holds the common volume.
+ * ktc_binary_inplace: inplaceElementwiseOpOnTensors (JVM:89-97): a = a op b, equal sizes.
+ * ktc_scalar:         mapElementsCopy with a constant (JVM:112-140) and
+ *                     TensorOperations.pow(constant, raw) (TOPS:39) via scalar_first.
+ * ktc_scalar_inplace: inplaceMapElements (JVM:105-108,116,130,136).
+ * ktc_unary:          JVM:122,142,144,395-399.   ktc_clamp: JVM:409-411.
+ * ktc_compare_scalar: lt/lte/gt/gte(value) -> 1.0f / 0.0f (JVM:377-383). */
+KTC_API int ktc_binary(int op, ktc_buf out, ktc_buf a, ktc_buf b, int64_t n);
+KTC_API int ktc_binary_bcast(int op, ktc_buf out,
+                             ktc_buf a, const int64_t* a_shape, int a_ndim,
+                             ktc_buf b, const int64_t* b_shape, int b_ndim);
+KTC_API int ktc_binary_inplace(int op, ktc_buf a, ktc_buf b, int64_t n);
+KTC_API int ktc_scalar(int op, ktc_buf out, ktc_buf a, float s, int64_t n, int scalar_first);
+KTC_API int ktc_scalar_inplace(int op, ktc_buf a, float s, int64_t n);
+KTC_API int ktc_unary(int op, ktc_buf out, ktc_buf a, int64_t n);
+KTC_API int ktc_clamp(ktc_buf out, ktc_buf a, float lo, float hi, int64_t n);
+KTC_API int ktc_compare_scalar(int op, ktc_buf out, ktc_buf a, float value, int64_t n);
+
+/* broadcastTo for callers that really need the expanded tensor
+ * (Sum/Mean/Expand backward: AggregatingFunctions.kt:19-25,40-53; JVM:51-73). */
+KTC_API int ktc_broadcast_to(ktc_buf out, const int64_t* out_shape, int out_ndim,
+                             ktc_buf a, const int64_t* a_shape, int a_ndim);
+
+/* ---- reductions ------------------------------------------------------------
+ * ktc_reduce_axis: aggregateOverAxis (JVM:154-225; kernels.cl:198-260) on the
+ *   collapsed view [outer, axis_len, inner]; out holds outer*inner floats
+ *   (index results are float32, JVM:180).
+ * ktc_reduce_axis_validx: value and index in one pass (what
+ *   AggregatingFunctions.kt:83-87 asks for in its TODO).
+ * ktc_reduce_all: sum() / mean() to one float (JVM:146-152; OCLK:336-415).
+ * ktc_sum_to_shape: mayUnexpand (Utils.kt:14-41) and Expand.doBackward
+ *   (TensorFunctions.kt:262-283): out has old_shape's volume. */
+KTC_API int ktc_reduce_axis(int op, ktc_buf out, ktc_buf in, int64_t outer, int64_t axis_len, int64_t inner);
+KTC_API int ktc_reduce_axis_validx(int is_max, ktc_buf out_val, ktc_buf out_idx, ktc_buf in,
+                                   int64_t outer, int64_t axis_len, int64_t inner);
+KTC_API int ktc_reduce_all(int op, ktc_buf out, ktc_buf in, int64_t n);
+KTC_API int ktc_sum_to_shape(ktc_buf out, const int64_t* old_shape, int old_ndim,
+                             ktc_buf in, const int64_t* in_shape, int in_ndim);
+
+/* inplaceScatter along an axis with one index per [outer, inner] position:
+ * the Max/Min backward (AggregatingFunctions.kt:68-79; JVM:227-256,
+ * kernels.cl:521-546).  target is [outer, axis_len, inner]; index and src are
+ * [outer, 1, inner].  An index outside [0, axis_len) is reported as
+ * KTC_EINVAL after the stream drains (the JVM throws, JVM:236-237). */
+KTC_API int ktc_scatter_axis(ktc_buf target, ktc_buf index, ktc_buf src,
+                             int64_t outer, int64_t axis_len, int64_t inner);
+
+/* ---- multi-GPU (no counterpart in the reference, which is single-device) ----
+ * One process per GPU.  Rank 0 creates the id, every rank joins with it, and
+ * partial reductions / weight gradients are summed in place across ranks. */
+#define KTC_COMM_ID_BYTES 128
+KTC_API int ktc_comm_unique_id(unsigned char id[KTC_COMM_ID_BYTES]);
+KTC_API int ktc_comm_init_rank(int dev, int n_ranks, int rank, const unsigned char id[KTC_COMM_ID_BYTES], ktc_comm* out);
+KTC_API int ktc_allreduce_sum(ktc_comm comm, ktc_buf buf, int64_t off, int64_t n);
+KTC_API int ktc_comm_destroy(ktc_comm comm);
+
+/* ---- measurement -----------------------------------------------------------
+ * CUDA events recorded on the device's compute stream; launch counter. */
+KTC_API int ktc_timer_start(int dev);
+KTC_API int ktc_timer_stop(int dev, float* elapsed_ms);   /* waits for the stop event */
+KTC_API int64_t ktc_launch_count(void);                    /* kernels launched by this library so far */
+KTC_API int ktc_flush_l2(int dev);                         /* overwrites a scratch buffer larger than L2 */
+KTC_API int ktc_tune_set(const char* key, int value);      /* launch-shape tunables (tile sizes, CTAs per SM); also env KTC_<KEY> */
+
+/* ---- test hooks (host-side failure injection; nothing here faults a GPU) ---- */
+KTC_API int ktc_test_inject_comm_error(int n_calls);        /* next n collective calls report KTC_ECOMM */
+KTC_API int ktc_test_bounded_wait(int dev, int64_t limit_ns, int* status); /* waits on a flag nothing sets */
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KTEN_CUDA_H */

@@ -1,0 +1,125 @@
+"""ctypes binding of libkten_cuda.so (the C ABI declared in include/kten_cuda.h).
+
+The library is the product; this module only loads it and declares the
+prototypes.  There is no fallback of any kind: if the shared object is missing
+the import of the symbol table fails, and if no CUDA device is usable
+`ktc_init` fails, each with an error that says so.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libkten_cuda.so")
+
+# status codes (include/kten_cuda.h)
+KTC_OK, KTC_EINVAL, KTC_ESTATE, KTC_ENOMEM, KTC_ECUDA, KTC_ECOMM, KTC_ETIMEOUT, KTC_ENOTSUP = 0, -1, -2, -3, -4, -5, -6, -7
+# op codes
+PLUS, MINUS, TIMES, DIV, POW = range(5)
+EXP, LOG, TANH, SIGMOID, RECIPROCAL, NEG = range(6)
+SUM, MEAN, MAX, MIN, ARGMAX, ARGMIN = range(6)
+LT, LTE, GT, GTE = range(4)
+MAX_DIMS = 10
+COMM_ID_BYTES = 128
+
+i32, i64, u64, f32 = C.c_int, C.c_int64, C.c_uint64, C.c_float
+p_i32, p_i64, p_u64, p_f32 = C.POINTER(i32), C.POINTER(i64), C.POINTER(u64), C.POINTER(f32)
+
+_PROTOTYPES = {
+    "ktc_init": (i32, [p_i32]),
+    "ktc_shutdown": (i32, []),
+    "ktc_device_info": (i32, [i32, C.c_char_p, C.c_size_t, p_i64, p_i32]),
+    "ktc_last_error": (C.c_char_p, []),
+    "ktc_version": (C.c_char_p, []),
+    "ktc_alloc": (i32, [i32, i64, p_u64]),
+    "ktc_wrap": (i32, [i32, C.c_void_p, i64, p_u64]),
+    "ktc_retain": (i32, [u64]),
+    "ktc_release": (i32, [u64]),
+    "ktc_refcount": (i32, [u64, p_i32]),
+    "ktc_buf_info": (i32, [u64, p_i32, p_i64, C.POINTER(C.c_void_p)]),
+    "ktc_pool_stats": (i32, [i32, p_i64, p_i64, p_i64, p_i64]),
+    "ktc_pool_trim": (i32, [i32]),
+    "ktc_pool_limit": (i32, [i32, i64]),
+    "ktc_host_alloc": (i32, [i64, C.POINTER(p_f32)]),
+    "ktc_host_free": (i32, [p_f32]),
+    "ktc_h2d": (i32, [u64, i64, C.c_void_p, i64, i32]),
+    "ktc_d2h": (i32, [C.c_void_p, u64, i64, i64, i32]),
+    "ktc_d2d": (i32, [u64, i64, u64, i64, i64]),
+    "ktc_fill": (i32, [u64, i64, i64, f32]),
+    "ktc_sync": (i32, [i32]),
+    "ktc_binary": (i32, [i32, u64, u64, u64, i64]),
+    "ktc_binary_bcast": (i32, [i32, u64, u64, p_i64, i32, u64, p_i64, i32]),
+    "ktc_binary_inplace": (i32, [i32, u64, u64, i64]),
+    "ktc_scalar": (i32, [i32, u64, u64, f32, i64, i32]),
+    "ktc_scalar_inplace": (i32, [i32, u64, f32, i64]),
+    "ktc_unary": (i32, [i32, u64, u64, i64]),
+    "ktc_clamp": (i32, [u64, u64, f32, f32, i64]),
+    "ktc_compare_scalar": (i32, [i32, u64, u64, f32, i64]),
+    "ktc_broadcast_to": (i32, [u64, p_i64, i32, u64, p_i64, i32]),
+    "ktc_reduce_axis": (i32, [i32, u64, u64, i64, i64, i64]),
+    "ktc_reduce_axis_validx": (i32, [i32, u64, u64, u64, i64, i64, i64]),
+    "ktc_reduce_all": (i32, [i32, u64, u64, i64]),
+    "ktc_sum_to_shape": (i32, [u64, p_i64, i32, u64, p_i64, i32]),
+    "ktc_scatter_axis": (i32, [u64, u64, u64, i64, i64, i64]),
+    "ktc_comm_unique_id": (i32, [C.c_char_p]),
+    "ktc_comm_init_rank": (i32, [i32, i32, i32, C.c_char_p, p_u64]),
+    "ktc_allreduce_sum": (i32, [u64, u64, i64, i64]),
+    "ktc_comm_destroy": (i32, [u64]),
+    "ktc_timer_start": (i32, [i32]),
+    "ktc_timer_stop": (i32, [i32, p_f32]),
+    "ktc_launch_count": (i64, []),
+    "ktc_flush_l2": (i32, [i32]),
+    "ktc_tune_set": (i32, [C.c_char_p, i32]),
+    "ktc_test_inject_comm_error": (i32, [i32]),
+    "ktc_test_bounded_wait": (i32, [i32, i64, p_i32]),
+}
+
+_lib = None
+
+
+class KtenCudaError(RuntimeError):
+    """A KTC_E* status from the library; `.status` holds the code."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(f"[{status}] {message}")
+        self.status = status
+
+
+def load() -> C.CDLL:
+    """Load the shared library (once) and attach the prototypes."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m kten_b200.build` "
+            "(nvcc, sm_100a).  kten_b200 has no CPU or PyTorch fallback.")
+    lib = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL if hasattr(C, "RTLD_GLOBAL") else 0)
+    for name, (res, args) in _PROTOTYPES.items():
+        fn = getattr(lib, name)          # AttributeError if the symbol is not exported
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def check(status: int) -> None:
+    """Map a negative status to the exception the JVM backend would throw:
+    KTC_EINVAL -> ValueError (IllegalArgumentException), KTC_ESTATE ->
+    RuntimeError (IllegalStateException), KTC_ENOMEM -> MemoryError."""
+    if status == KTC_OK:
+        return
+    msg = load().ktc_last_error().decode("utf-8", "replace")
+    if status == KTC_EINVAL:
+        raise ValueError(msg)
+    if status == KTC_ENOMEM:
+        raise MemoryError(msg)
+    if status == KTC_ETIMEOUT:
+        raise TimeoutError(msg)
+    raise KtenCudaError(status, msg)
+
+
+def shape_array(shape):
+    arr = (i64 * max(len(shape), 1))(*shape)
+    return arr, len(shape)
