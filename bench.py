@@ -1,0 +1,505 @@
+#!/usr/bin/env python
+"""Benchmark of the kten float32 hot path on B200: HBM GB/s and fraction of peak for
+contiguous elementwise ops, broadcast binary ops and axis / full reductions.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W]             # this library
+    python bench.py --impl reference [--steps K] [--warmup W]        # kten-jvm's algorithm on the host cores
+
+One step is one pass over the sweep below on synthetic, seeded inputs that are
+already resident in HBM (every operand is >= 1 GiB, far larger than the 126 MB
+L2, so nothing is served from cache between iterations):
+
+  C2  contiguous, 2^28 elements ~ U(0.1, 2):   plus, times, div, pow;  exp, log, tanh, sigmoid
+  C3  broadcast, a[1024,1024,256] ~ N(0,1):    a*b, (a*b)+c, a/b   with b[1,1024,1], c[1024,1,256]
+  C4  reductions, N(0,1) rounded to 1/16:      sum, mean, max, argmax over the last axis of [65536,4096];
+                                               sum, max over the middle axis of [512,4096,128]; full sum of 2^28
+
+With N > 1 (one process per GPU, launched by torch.distributed.run) each rank
+owns one leading-dimension shard of an N-times larger batch and runs the same
+sweep on it (weak scaling); the only exchange on the path is the all-reduce of
+the full-sum partial.  The value is whole-job algorithmic bytes / max-over-ranks
+device time.
+
+The JSON line also carries: `e2e` (the same sweep through the public API with
+pinned HOST buffers, host<->device copies inside the timed region), `roofline`
+for the kernel with the largest share of the step, `per_op` GB/s, `cpu_baseline`
+(the CPU oracle in kten-jvm's structure, on a bounded sample) and the SM clocks
+sampled during the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N28 = 1 << 28
+GIB = 1 << 30
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+
+
+# ----------------------------------------------------------------------------------------------
+# workload description (shared by both arms)
+# ----------------------------------------------------------------------------------------------
+def sweep_spec():
+    """name, kernel family, algorithmic bytes (each distinct input element once at its
+    un-broadcast size + each output element once), elements the throughput is quoted on."""
+    ops = []
+    for name in ("plus", "times", "div", "pow"):
+        ops.append(dict(name=f"c2.{name}", family="map2", bytes=3 * GIB, elements=N28))
+    for name in ("exp", "log", "tanh", "sigmoid"):
+        ops.append(dict(name=f"c2.{name}", family="map1", bytes=2 * GIB, elements=N28))
+    ops.append(dict(name="c3.a*b", family="bcast", bytes=2 * GIB + 4096, elements=N28))
+    ops.append(dict(name="c3.(a*b)+c", family="bcast", bytes=2 * GIB + (1 << 20), elements=N28))
+    ops.append(dict(name="c3.a/b", family="bcast", bytes=2 * GIB + 4096, elements=N28))
+    for name in ("sum", "mean", "max", "argmax"):
+        ops.append(dict(name=f"c4.last.{name}", family="reduce_rows", bytes=GIB + 65536 * 4, elements=N28))
+    for name in ("sum", "max"):
+        ops.append(dict(name=f"c4.mid.{name}", family="reduce_cols", bytes=GIB + 512 * 128 * 4, elements=N28))
+    ops.append(dict(name="c4.full.sum", family="reduce_rows", bytes=GIB + 4, elements=N28))
+    return ops
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """nvidia-smi SM clock / throttle-reason samples while the timed region runs (read only)."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, power, reasons = [], [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(smax)), "power_w_max": float(max(power)),
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ----------------------------------------------------------------------------------------------
+# CPU side: the oracle in kten-jvm's structure, on a bounded sample
+# ----------------------------------------------------------------------------------------------
+def cpu_sample_pass(sample_log2: int, tuned: bool = False):
+    """One pass of the sweep on a 2^sample_log2-element sample with the CPU oracle:
+    broadcast operands materialised, out-of-place maps single-threaded, in-place ops and
+    axis aggregation on all host threads (what kten-jvm does).  Returns (seconds, algorithmic
+    bytes of the sample, per-op seconds)."""
+    from kten_b200 import datagen as D
+    from oracle import oracle as O
+    n = 1 << sample_log2
+    scale = n / N28
+    a, b = D.uniform(n, 1, 0.1, 2.0), D.uniform(n, 2, 0.1, 2.0)
+    rows3 = max(1, int(1024 * scale))
+    a3 = D.normal(rows3 * 1024 * 256, 3, 0.0, 1.0)
+    b3, c3 = D.uniform(1024, 4, 0.5, 2.0), D.uniform(rows3 * 256, 5, -1.0, 1.0)
+    x4 = D.normal(n, 6, 0.0, 1.0, quantum=16.0)
+    rows4, outer4 = n // 4096, max(1, n // (4096 * 128))
+    per_op, total_bytes = {}, 0.0
+    t_all = time.perf_counter()
+    for spec in sweep_spec():
+        name = spec["name"]
+        t0 = time.perf_counter()
+        if name.startswith("c2."):
+            op = name[3:]
+            if spec["family"] == "map2":
+                O.binary_same({"plus": O.PLUS, "times": O.TIMES, "div": O.DIV, "pow": O.POW}[op], a, b, tuned=tuned)
+            else:
+                O.unary({"exp": O.EXP, "log": O.LOG, "tanh": O.TANH, "sigmoid": O.SIGMOID}[op], a, tuned=tuned)
+        elif name == "c3.a*b":
+            t3, _ = O.binary(O.TIMES, a3, [rows3, 1024, 256], b3, [1, 1024, 1])
+        elif name == "c3.(a*b)+c":
+            O.binary(O.PLUS, t3, [rows3, 1024, 256], c3, [rows3, 1, 256])
+        elif name == "c3.a/b":
+            O.binary(O.DIV, a3, [rows3, 1024, 256], b3, [1, 1024, 1])
+        elif name.startswith("c4.last."):
+            O.aggregate({"sum": O.SUM, "mean": O.MEAN, "max": O.MAX, "argmax": O.ARGMAX}[name[8:]], x4, rows4, 4096, 1, mode=0)
+        elif name.startswith("c4.mid."):
+            O.aggregate({"sum": O.SUM, "max": O.MAX}[name[7:]], x4[:outer4 * 4096 * 128], outer4, 4096, 128, mode=0)
+        else:
+            O.reduce_all(O.SUM, x4, mode=0)
+        per_op[name] = time.perf_counter() - t0
+        total_bytes += spec["bytes"] * scale
+    return time.perf_counter() - t_all, total_bytes, per_op
+
+
+def run_reference_arm(args):
+    """`--impl reference`: the reference's own CPU algorithm (kten-jvm restated in C++, the
+    JVM itself cannot run here) on the host cores, same metric and config."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    from oracle import oracle as O
+    sample_log2 = args.cpu_sample_log2
+    for _ in range(args.warmup):
+        cpu_sample_pass(min(sample_log2, 20))
+    secs, nbytes = 0.0, 0.0
+    for _ in range(args.steps):
+        s, b, _ = cpu_sample_pass(sample_log2)
+        secs += s; nbytes += b
+    gbs = nbytes / secs / 1e9
+    line = {
+        "impl": "reference", "metric": "HBM GB/s (algorithmic bytes / time), broadcast elementwise + axis reduce sweep",
+        "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * secs / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "C2+C3+C4 sweep (contiguous elementwise, broadcast binary, axis/full reductions)",
+                   "sample": f"2^{sample_log2} elements per operand (1/{N28 >> sample_log2} of the full size), same shapes ratio"},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": O.num_threads(), "kind": "port",
+                         "sample": f"each step = the sweep on 2^{sample_log2}-element operands; kten-jvm structure: broadcast operands "
+                                   "materialised, out-of-place maps on one thread, in-place ops and axis aggregation on all threads"},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "kten-jvm itself needs a JDK + Kotlin toolchain that is not in this image; this is its algorithm restated in C++ "
+                "(oracle/kten_oracle.cpp), which is faster than the JVM original (no boxing, no per-element List allocation)",
+    }
+    print(json.dumps(line))
+    return 0
+
+
+# ----------------------------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------------------------
+class GpuSweep:
+    def __init__(self, device: int, rank: int, comm=None):
+        from kten_b200 import _lib as L
+        from kten_b200 import datagen as D
+        from kten_b200.tensor_operations import CUDATensorOperations
+        self.L, self.D = L, D
+        self.ops = CUDATensorOperations(device)
+        self.lib, self.dev, self.rank, self.comm = self.ops.lib, device, rank, comm
+        first = rank * N28                       # this rank's shard of the N-times larger batch
+        t0 = time.time()
+        self.h_in = [self._pinned(N28), self._pinned(N28)]
+        self.h_out = self._pinned(N28)
+        mk = self.ops.createRaw
+        # C2
+        D.uniform(N28, 1, 0.1, 2.0, first=first, out=self.h_in[0]); self.a2 = mk([N28]); self._up(self.a2, self.h_in[0])
+        D.uniform(N28, 2, 0.1, 2.0, first=first, out=self.h_in[1]); self.b2 = mk([N28]); self._up(self.b2, self.h_in[1])
+        # C3
+        D.normal(N28, 3, 0.0, 1.0, first=first, out=self.h_in[0]); self.a3 = mk([1024, 1024, 256]); self._up(self.a3, self.h_in[0])
+        self.hb3 = D.uniform(1024, 4, 0.5, 2.0); self.b3 = mk([1, 1024, 1], self.hb3)
+        self.hc3 = D.uniform(1024 * 256, 5, -1.0, 1.0, first=rank * 1024 * 256); self.c3 = mk([1024, 1, 256], self.hc3)
+        self.t3 = mk([1024, 1024, 256])
+        # C4
+        D.normal(N28, 6, 0.0, 1.0, first=first, quantum=16.0, out=self.h_in[0]); self.x4 = mk([N28]); self._up(self.x4, self.h_in[0])
+        self.out = mk([N28])
+        self.small = mk([65536])
+        self.small_host = np.empty(65536, dtype=np.float32)
+        self.ops.synchronize()
+        self.setup_s = time.time() - t0
+        self.h_state = None                       # which host data h_in currently holds
+
+    def _pinned(self, n):
+        p = C.POINTER(C.c_float)()
+        self.L.check(self.lib.ktc_host_alloc(n, C.byref(p)))
+        return np.ctypeslib.as_array(p, shape=(n,))
+
+    def _up(self, raw, host, n=None):
+        n = raw.size if n is None else n
+        self.L.check(self.lib.ktc_h2d(raw.storeReference, 0, host.ctypes.data_as(C.c_void_p), n, 0))
+        self.ops.synchronize()
+
+    # ---- one op, inputs resident in HBM --------------------------------------------------------
+    def launch(self, name):
+        L, lib = self.L, self.lib
+        ck = L.check
+        a2, b2, out = self.a2.storeReference, self.b2.storeReference, self.out.storeReference
+        if name.startswith("c2."):
+            op = name[3:]
+            if op in ("plus", "times", "div", "pow"):
+                ck(lib.ktc_binary({"plus": L.PLUS, "times": L.TIMES, "div": L.DIV, "pow": L.POW}[op], out, a2, b2, N28))
+            else:
+                ck(lib.ktc_unary({"exp": L.EXP, "log": L.LOG, "tanh": L.TANH, "sigmoid": L.SIGMOID}[op], out, a2, N28))
+        elif name.startswith("c3."):
+            s3, n3 = L.shape_array([1024, 1024, 256]); sb, nb = L.shape_array([1, 1024, 1]); sc, nc = L.shape_array([1024, 1, 256])
+            a3, b3, c3, t3 = self.a3.storeReference, self.b3.storeReference, self.c3.storeReference, self.t3.storeReference
+            if name == "c3.a*b":
+                ck(lib.ktc_binary_bcast(L.TIMES, t3, a3, s3, n3, b3, sb, nb))
+            elif name == "c3.(a*b)+c":
+                ck(lib.ktc_binary_bcast(L.PLUS, out, t3, s3, n3, c3, sc, nc))
+            else:
+                ck(lib.ktc_binary_bcast(L.DIV, out, a3, s3, n3, b3, sb, nb))
+        elif name.startswith("c4.last."):
+            ck(lib.ktc_reduce_axis({"sum": L.SUM, "mean": L.MEAN, "max": L.MAX, "argmax": L.ARGMAX}[name[8:]],
+                                   self.small.storeReference, self.x4.storeReference, 65536, 4096, 1))
+        elif name.startswith("c4.mid."):
+            ck(lib.ktc_reduce_axis({"sum": L.SUM, "max": L.MAX}[name[7:]], self.small.storeReference, self.x4.storeReference, 512, 4096, 128))
+        else:
+            ck(lib.ktc_reduce_all(L.SUM, self.small.storeReference, self.x4.storeReference, N28))
+            if self.comm is not None:            # the one exchange step of the sharded path
+                ck(lib.ktc_allreduce_sum(self.comm, self.small.storeReference, 0, 1))
+
+    # ---- one op through the public API with HOST buffers (copies inside the timed region) -------
+    def e2e_op(self, name, host_a, host_b):
+        """Returns (h2d bytes, d2h bytes).  host_a/host_b are the pinned operands."""
+        L, lib = self.L, self.lib
+        vp = lambda h: h.ctypes.data_as(C.c_void_p)
+        up = lambda raw, h, n: L.check(lib.ktc_h2d(raw.storeReference, 0, vp(h), n, 0))
+        down = lambda h, raw, n: L.check(lib.ktc_d2h(vp(h), raw.storeReference, 0, n, 0))
+        if name.startswith("c2."):
+            binary = name[3:] in ("plus", "times", "div", "pow")
+            up(self.a2, host_a, N28)
+            if binary:
+                up(self.b2, host_b, N28)
+            self.launch(name)
+            down(self.h_out, self.out, N28)
+            return (8 if binary else 4) * N28, 4 * N28
+        if name.startswith("c3."):
+            if name == "c3.(a*b)+c":
+                up(self.t3, host_a, N28); up(self.c3, self.hc3, 1024 * 256)
+                self.launch(name); down(self.h_out, self.out, N28)
+                return 4 * N28 + (1 << 20), 4 * N28
+            up(self.a3, host_a, N28); up(self.b3, self.hb3, 1024)
+            self.launch(name)
+            down(self.h_out, self.t3 if name == "c3.a*b" else self.out, N28)
+            return 4 * N28 + 4096, 4 * N28
+        up(self.x4, host_a, N28)
+        self.launch(name)
+        n_out = 1 if name == "c4.full.sum" else 65536
+        down(self.small_host, self.small, n_out)
+        return 4 * N28, 4 * n_out
+
+    def timer_start(self):
+        self.L.check(self.lib.ktc_timer_start(self.dev))
+
+    def timer_stop(self) -> float:
+        ms = C.c_float(0)
+        self.L.check(self.lib.ktc_timer_stop(self.dev, C.byref(ms)))
+        return float(ms.value)
+
+
+def init_distributed(n_gpus):
+    """(rank, world, local_rank, dist module or None).  torch.distributed is plumbing only:
+    rendezvous, the barrier and the max over ranks."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world <= 1:
+        return 0, 1, 0, None
+    import torch
+    import torch.distributed as dist
+    rank, local = int(os.environ["RANK"]), int(os.environ.get("LOCAL_RANK", os.environ["RANK"]))
+    torch.cuda.set_device(local)
+    dist.init_process_group(backend="cpu:gloo,cuda:nccl", rank=rank, world_size=world)
+    return rank, world, local, dist
+
+
+def make_comm(lib, L, dist, rank, world, local):
+    ident = C.create_string_buffer(L.COMM_ID_BYTES)
+    if rank == 0:
+        L.check(lib.ktc_comm_unique_id(ident))
+    box = [bytes(ident.raw)]
+    dist.broadcast_object_list(box, src=0)
+    comm = C.c_uint64(0)
+    L.check(lib.ktc_comm_init_rank(local, world, rank, box[0], C.byref(comm)))
+    return comm.value
+
+
+def run_gpu_arm(args):
+    rank, world, local, dist = init_distributed(args.gpus)
+    from kten_b200 import _lib as L
+    lib = L.load()
+    n = C.c_int(0)
+    L.check(lib.ktc_init(C.byref(n)))
+    comm = make_comm(lib, L, dist, rank, world, local) if dist is not None else None
+    sweep = GpuSweep(local, rank, comm)
+    spec = sweep_spec()
+    names = [s["name"] for s in spec]
+    step_bytes = float(sum(s["bytes"] for s in spec))
+
+    def barrier():
+        sweep.ops.synchronize()
+        if dist is not None:
+            dist.barrier()
+
+    def run_step():
+        for nm in names:
+            sweep.launch(nm)
+
+    for _ in range(max(args.warmup, 3)):
+        run_step()
+    barrier()
+
+    # ---- timed region: exactly K steps, device-timed on the launching stream ----------------------
+    sampler = ClockSampler(local)
+    sampler.start()
+    time.sleep(0.3)
+    launches0 = lib.ktc_launch_count()
+    barrier()
+    sweep.timer_start()
+    for _ in range(args.steps):
+        run_step()
+    step_ms_total = sweep.timer_stop()
+    barrier()
+    launches = lib.ktc_launch_count() - launches0
+
+    # ---- per-op durations, same inputs, same clocks window (events around K launches of each op) --
+    per_op = []
+    for s in spec:
+        sweep.launch(s["name"])
+        sweep.timer_start()
+        for _ in range(args.steps):
+            sweep.launch(s["name"])
+        ms = sweep.timer_stop() / args.steps
+        per_op.append(dict(name=s["name"], family=s["family"], ms=ms, gbs=s["bytes"] / ms / 1e6,
+                           gelem_s=s["elements"] / ms / 1e6))
+    clocks = sampler.stop()
+
+    # ---- end to end: host buffers, copies inside the timed region ----------------------------------
+    e2e_steps = max(1, min(args.steps, args.e2e_steps))
+    D = sweep.D
+    first = rank * N28
+    host_sets = {}
+    D.uniform(N28, 1, 0.1, 2.0, first=first, out=sweep.h_in[0]); D.uniform(N28, 2, 0.1, 2.0, first=first, out=sweep.h_in[1])
+    h2d = d2h = 0
+    barrier()
+    sweep.timer_start()
+    t_wall = time.perf_counter()
+    for _ in range(e2e_steps):
+        for nm in names:
+            bi, bo = sweep.e2e_op(nm, sweep.h_in[0], sweep.h_in[1])
+            h2d += bi; d2h += bo
+    e2e_ms = sweep.timer_stop()
+    e2e_wall = time.perf_counter() - t_wall
+    barrier()
+
+    # ---- max over ranks -----------------------------------------------------------------------------
+    if dist is not None:
+        import torch
+        t = torch.tensor([step_ms_total, e2e_ms], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        step_ms_total, e2e_ms = float(t[0]), float(t[1])
+    ms_per_step = step_ms_total / args.steps
+    value = world * step_bytes / (ms_per_step * 1e6)
+    e2e_value = world * step_bytes * e2e_steps / (e2e_ms * 1e6)
+
+    peak, peak_src = measured_peak()
+    fam_time = {}
+    for p in per_op:
+        fam_time[p["family"]] = fam_time.get(p["family"], 0.0) + p["ms"]
+    top_family = max(fam_time, key=fam_time.get)
+    fam_ops = [(p, s) for p, s in zip(per_op, spec) if p["family"] == top_family]
+    fam_bytes = sum(s["bytes"] for _, s in fam_ops) / len(fam_ops)
+    fam_ms = sum(p["ms"] for p, _ in fam_ops) / len(fam_ops)
+    achieved = fam_bytes / fam_ms / 1e6
+    kernel_names = {"map2": "k_map2_vec", "map1": "k_map1_vec", "bcast": "k_bcast3", "reduce_rows": "k_rows_block", "reduce_cols": "k_cols"}
+    traffic = load_traffic(kernel_names[top_family])
+
+    line = {
+        "metric": "HBM GB/s (algorithmic bytes / time), broadcast elementwise + axis reduce sweep",
+        "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "C2+C3+C4 sweep (contiguous elementwise, broadcast binary, axis/full reductions), one shard per GPU",
+                   "elements_per_operand": N28, "ops_per_step": len(names), "algorithmic_bytes_per_step_per_gpu": step_bytes,
+                   "l2": "inputs larger than L2 (every operand >= 1 GiB, L2 is 126 MB)", "parallelism": f"batch-sharded x{world}"},
+        "frac_of_measured_peak": value / world / peak, "frac_of_nominal_8TBs": value / world / NOMINAL_HBM_GBS,
+        "gelem_per_s": world * sum(s["elements"] for s in spec) / (ms_per_step * 1e6),
+        "gpu_launches": int(launches),
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d // e2e_steps, "d2h_bytes_per_step": d2h // e2e_steps,
+                "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps, "wall_ms_per_step": 1e3 * e2e_wall / e2e_steps,
+                "note": "pinned host operands -> ktc_h2d -> op -> ktc_d2h of the result, per op, all on the compute stream"},
+        "roofline": {"bound": "hbm", "kernel": kernel_names[top_family], "ops": [p["name"] for p, _ in fam_ops],
+                     "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
+                     "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "traffic": traffic,
+                     "algorithmic_bytes_per_launch": fam_bytes, "ms_per_launch": fam_ms,
+                     "share_of_step": fam_time[top_family] / sum(fam_time.values())},
+        "per_op": [{"name": p["name"], "ms": round(p["ms"], 4), "gbs": round(p["gbs"], 1), "frac_measured": round(p["gbs"] / peak, 3),
+                    "frac_nominal": round(p["gbs"] / NOMINAL_HBM_GBS, 3)} for p in per_op],
+        "clocks": clocks,
+        "setup_s": round(sweep.setup_s, 1),
+    }
+    if rank == 0:
+        if args.cpu_baseline:
+            secs, nbytes, _ = cpu_sample_pass(args.cpu_sample_log2)
+            from oracle import oracle as O
+            line["cpu_baseline"] = {"value": nbytes / secs / 1e9, "unit": "GB/s", "cores": O.num_threads(), "kind": "port",
+                                    "sample": f"the same sweep on 2^{args.cpu_sample_log2}-element operands ({secs:.1f} s), CPU oracle in "
+                                              "kten-jvm's structure (broadcast operands materialised, out-of-place maps single-threaded, "
+                                              "in-place ops and axis aggregation on all host threads)"}
+        print(json.dumps(line))
+    if dist is not None:
+        if comm is not None:
+            lib.ktc_comm_destroy(comm)
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def load_traffic(kernel: str):
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the
+    committed ncu summary (profiles/dram_traffic.json); None when no capture exists."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as fh:
+            return json.load(fh).get(kernel, {}).get("traffic_bytes_per_full_launch")
+    except Exception:
+        return None
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="kten_b200", choices=["kten_b200", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--cpu-sample-log2", type=int, default=None, help="log2 of the CPU sample size (default 25 for cpu_baseline, 24 for --impl reference)")
+    ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
+    args = ap.parse_args()
+    if args.cpu_sample_log2 is None:
+        args.cpu_sample_log2 = 24 if args.impl == "reference" else 25
+    if args.impl == "reference":
+        return run_reference_arm(args)
+    return run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -102,6 +102,9 @@ int pool_alloc(Device* d, int64_t n_floats, float** ptr, size_t* rounded) {
     const size_t bytes = round_bytes(n_floats);
     std::lock_guard<std::mutex> lk(d->pool_mu);
     d->n_alloc_calls++;
+    if (d->limit_bytes > 0 && d->live_bytes + (int64_t)bytes > d->limit_bytes)
+        return fail(KTC_ENOMEM, "pool limit: %lld live + %zu requested > %lld allowed",
+                    (long long)d->live_bytes, bytes, (long long)d->limit_bytes);
     auto it = d->free_lists.find(bytes);
     if (it != d->free_lists.end() && !it->second.empty()) {
         *ptr = (float*)it->second.back(); it->second.pop_back();
@@ -109,9 +112,6 @@ int pool_alloc(Device* d, int64_t n_floats, float** ptr, size_t* rounded) {
         *rounded = bytes;
         return KTC_OK;
     }
-    if (d->limit_bytes > 0 && d->live_bytes + (int64_t)bytes > d->limit_bytes)
-        return fail(KTC_ENOMEM, "pool limit: %lld live + %zu requested > %lld allowed",
-                    (long long)d->live_bytes, bytes, (long long)d->limit_bytes);
     if (d->limit_bytes > 0 && d->live_bytes + d->cached_bytes + (int64_t)bytes > d->limit_bytes) trim_locked(d);
     void* p = nullptr;
     cudaError_t e = cudaMalloc(&p, bytes);

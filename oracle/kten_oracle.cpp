@@ -362,6 +362,12 @@ KTO_API int kto_sum_to_shape(const float* in, const int64_t* in_shape, int in_n,
         std::memcpy(out, cur.data(), cur.size() * sizeof(float));
         return KTO_OK;
     }
+    bool any_reduced = lead > 0;
+    for (int i = 0; i < old_n; ++i) any_reduced |= (old_shape[i] != in_shape[lead + i]);
+    if (!any_reduced) {                                             // no sum is issued: the tensor itself comes back
+        std::memcpy(out, in, volume(in_shape, in_n) * sizeof(float));
+        return KTO_OK;
+    }
     int64_t ostride[16]; int64_t st = 1;
     for (int i = in_n - 1; i >= 0; --i) {
         int io = i - lead;
