@@ -95,6 +95,7 @@ __global__ void k_fill_scalar(float* __restrict__ out, int64_t n, float v) {
 static inline int grid_for(Device* d, int64_t items, int64_t per_block, int max_blocks_per_sm) {
     int64_t need = (items + per_block - 1) / per_block;
     int64_t cap = (int64_t)d->sm_count * max_blocks_per_sm;
+    if (max_blocks_per_sm <= 0) cap = 0x7fffffff;          // one tile per CTA, no grid-stride loop
     if (need < 1) need = 1;
     return (int)(need < cap ? need : cap);
 }
