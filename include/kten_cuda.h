@@ -154,6 +154,23 @@ KTC_API int ktc_reduce_all(int op, ktc_buf out, ktc_buf in, int64_t n);
 KTC_API int ktc_sum_to_shape(ktc_buf out, const int64_t* old_shape, int old_ndim,
                              ktc_buf in, const int64_t* in_shape, int in_ndim);
 
+/* Full sum / mean that obtains no memory, for callers that must not allocate
+ * while they run: loops whose free device memory is already committed to
+ * another allocator, latency-bound sections that cannot take the device-wide
+ * synchronisation of cudaMalloc, code running while someone else holds the
+ * allocator.  This entry point has no counterpart in the reference.
+ * Same result contract as ktc_reduce_all (op is KTC_SUM or KTC_MEAN, `out`
+ * receives one float); the per-CTA partials live in a fixed
+ * KTC_NOALLOC_SCRATCH_BYTES array inside the library image on every GPU that
+ * loads it.  n may not exceed KTC_NOALLOC_MAX_ELEMS (KTC_EINVAL otherwise).
+ * All calls on a device share that array: they are issued on the device's one
+ * compute stream and must not be made to overlap on the GPU.  The first call
+ * on a device resolves the array's device address; make it before any stream
+ * capture begins. */
+#define KTC_NOALLOC_SCRATCH_BYTES 16384
+#define KTC_NOALLOC_MAX_ELEMS ((int64_t)1 << 30)
+KTC_API int ktc_reduce_all_noalloc(int op, ktc_buf out, ktc_buf in, int64_t n);
+
 /* inplaceScatter along an axis with one index per [outer, inner] position:
  * the Max/Min backward (AggregatingFunctions.kt:68-79; JVM:227-256,
  * kernels.cl:521-546).  target is [outer, axis_len, inner]; index and src are

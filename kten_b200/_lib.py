@@ -22,6 +22,8 @@ SUM, MEAN, MAX, MIN, ARGMAX, ARGMIN = range(6)
 LT, LTE, GT, GTE = range(4)
 MAX_DIMS = 10
 COMM_ID_BYTES = 128
+NOALLOC_SCRATCH_BYTES = 16384
+NOALLOC_MAX_ELEMS = 1 << 30
 
 i32, i64, u64, f32 = C.c_int, C.c_int64, C.c_uint64, C.c_float
 p_i32, p_i64, p_u64, p_f32 = C.POINTER(i32), C.POINTER(i64), C.POINTER(u64), C.POINTER(f32)
@@ -60,6 +62,7 @@ _PROTOTYPES = {
     "ktc_reduce_axis": (i32, [i32, u64, u64, i64, i64, i64]),
     "ktc_reduce_axis_validx": (i32, [i32, u64, u64, u64, i64, i64, i64]),
     "ktc_reduce_all": (i32, [i32, u64, u64, i64]),
+    "ktc_reduce_all_noalloc": (i32, [i32, u64, u64, i64]),
     "ktc_sum_to_shape": (i32, [u64, p_i64, i32, u64, p_i64, i32]),
     "ktc_scatter_axis": (i32, [u64, u64, u64, i64, i64, i64]),
     "ktc_comm_unique_id": (i32, [C.c_char_p]),
