@@ -114,7 +114,7 @@ static int run_map1(Device* d, float* out, const float* a, int64_t n, F f) {
     if (aligned16(out) && aligned16(a) && n >= 4) {
         const int64_t n4 = n / 4;
         const int U = tune("map_unroll", 4);
-        const int bps = tune("map_blocks_per_sm", 8);
+        const int bps = tune("map_blocks_per_sm", 0);
         int launches = 1;
         if (U == 8)      k_map1_vec<8, F><<<grid_for(d, n4, threads * 8, bps), threads, 0, d->stream>>>((const float4*)a, (float4*)out, n4, f);
         else if (U == 2) k_map1_vec<2, F><<<grid_for(d, n4, threads * 2, bps), threads, 0, d->stream>>>((const float4*)a, (float4*)out, n4, f);
@@ -133,7 +133,7 @@ static int run_map2(Device* d, float* out, const float* a, const float* b, int64
     if (aligned16(out) && aligned16(a) && aligned16(b) && n >= 4) {
         const int64_t n4 = n / 4;
         const int U = tune("map_unroll", 4);
-        const int bps = tune("map_blocks_per_sm", 8);
+        const int bps = tune("map_blocks_per_sm", 0);
         int launches = 1;
         if (U == 8)      k_map2_vec<8, F><<<grid_for(d, n4, threads * 8, bps), threads, 0, d->stream>>>((const float4*)a, (const float4*)b, (float4*)out, n4, f);
         else if (U == 2) k_map2_vec<2, F><<<grid_for(d, n4, threads * 2, bps), threads, 0, d->stream>>>((const float4*)a, (const float4*)b, (float4*)out, n4, f);
@@ -231,6 +231,7 @@ struct BcastArgs {
     int cols_per_tile;       // CW, multiple of 4
     int64_t tiles_d1, tiles_d2;
     int a_stream, b_stream;  // DIRECT operand is full-size: read it with the streaming hint
+    int txc, txc_log2;       // threads across the columns of a tile (power of two <= 256)
 };
 
 template <int MODE>
@@ -286,25 +287,28 @@ __global__ void __launch_bounds__(256) k_bcast3(BcastArgs p, F f) {
         const float* bbase = (MODE_B == AM_DIRECT) ? p.b + i0 * p.bs0 + r0 * p.bs1 + c0 : nullptr;
         float* obase = p.out + (i0 * p.D1 + r0) * p.D2 + c0;
 
-        const int items = rows * cols4;
+        // thread (tx, ty): fixed column group, rows ty, ty + TYC, ... -- no per-item division
+        const int tx = threadIdx.x & (p.txc - 1), ty = threadIdx.x >> p.txc_log2;
+        const int tyc = blockDim.x >> p.txc_log2;
         constexpr int U = 4;
-        for (int it = threadIdx.x; it < items; it += blockDim.x * U) {
-            float4 va[U], vb[U];
-            int row[U], col[U];
-            #pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int k = it + u * blockDim.x;
-                if (k < items) {
-                    row[u] = k / cols4; col[u] = (k - row[u] * cols4) << 2;
-                    va[u] = load_operand<MODE_A>(sm_a, abase, p.as1, row[u], col[u], p.a_stream);
-                    vb[u] = load_operand<MODE_B>(sm_b, bbase, p.bs1, row[u], col[u], p.b_stream);
+        for (int c4 = tx; c4 < cols4; c4 += p.txc) {
+            const int col = c4 << 2;
+            for (int r = ty; r < rows; r += tyc * U) {
+                float4 va[U], vb[U];
+                #pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int row = r + u * tyc;
+                    if (row < rows) {
+                        va[u] = load_operand<MODE_A>(sm_a, abase, p.as1, row, col, p.a_stream);
+                        vb[u] = load_operand<MODE_B>(sm_b, bbase, p.bs1, row, col, p.b_stream);
+                    }
                 }
-            }
-            #pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int k = it + u * blockDim.x;
-                if (k < items)
-                    st_stream(reinterpret_cast<float4*>(obase + (int64_t)row[u] * p.D2 + col[u]), apply2(f, va[u], vb[u]));
+                #pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int row = r + u * tyc;
+                    if (row < rows)
+                        st_stream(reinterpret_cast<float4*>(obase + (int64_t)row * p.D2 + col), apply2(f, va[u], vb[u]));
+                }
             }
         }
     }
@@ -399,9 +403,12 @@ static int run_bcast(Device* d, float* out, const int64_t* oshape, int ndim, con
         p.rows_per_tile = (int)rb;
         p.tiles_d1 = (D[1] + rb - 1) / rb;
         p.tiles_d2 = (D[2] + p.cols_per_tile - 1) / p.cols_per_tile;
+        const int cw4 = p.cols_per_tile >> 2;
+        p.txc = 1; p.txc_log2 = 0;
+        while (p.txc < 256 && p.txc < cw4) { p.txc <<= 1; ++p.txc_log2; }
         const int64_t n_tiles = D[0] * p.tiles_d1 * p.tiles_d2;
-        const int bps = tune("bcast_blocks_per_sm", 8);
-        const int64_t cap = (int64_t)d->sm_count * bps;
+        const int bps = tune("bcast_blocks_per_sm", 0);             // <= 0: one tile per CTA, tiles in address order
+        const int64_t cap = bps > 0 ? (int64_t)d->sm_count * bps : 0x7fffffffLL;
         const int grid = (int)(n_tiles < cap ? n_tiles : cap);
         const int sm_stride = p.cols_per_tile > ((p.rows_per_tile + 3) & ~3) ? p.cols_per_tile : ((p.rows_per_tile + 3) & ~3);
         const size_t smem = sizeof(float) * (size_t)sm_stride *

@@ -16,6 +16,7 @@
 #include <math_constants.h>
 
 #include "../../include/kten_cuda.h"
+#include "ktc_fastmath.h"
 
 namespace ktc {
 
@@ -46,52 +47,44 @@ __device__ __forceinline__ float pow_ref(float x, float y) {
     return (float)pow((double)x, (double)y);
 }
 
-// exp(x) to well under one ulp in float arithmetic only.
-// x = n*ln2 + r with a two-part ln2 (r carried as hi + lo), exp(r) by a
-// degree-9 Taylor polynomial, and the final 1 + r + t summed with an exact
-// two-sum so that only one rounding of size ulp/2 remains.  Arguments whose
-// result would leave the normal range take the double path.
-__device__ __forceinline__ float exp_fast(float x) {
-    if (!(fabsf(x) <= 87.0f)) return exp_ref(x);          // also NaN
-    const float n = rintf(x * 1.44269504088896341f);
-    // ln2 = LN2_HI + LN2_LO, LN2_HI has 11 trailing zero bits so n*LN2_HI is exact for |n| < 2^11
-    const float LN2_HI = 0.693145751953125f;               // 0x1.62e400p-1
-    const float LN2_LO = 1.42860682030941723212e-6f;       // ln2 - LN2_HI
-    const float r_hi = fmaf(n, -LN2_HI, x);                // exact
-    const float nl = n * LN2_LO;
-    const float nl_err = fmaf(n, LN2_LO, -nl);             // exact product error
-    const float r = r_hi - nl;
-    const float r_lo = ((r_hi - r) - nl) - nl_err;         // r_hi - n*LN2_LO = r + r_lo
-    // q(r) = sum_{k=2..9} r^(k-2)/k!
-    float q = 2.7557319223985893e-6f;                      // 1/9!
-    q = fmaf(q, r, 2.4801587301587302e-5f);
-    q = fmaf(q, r, 1.9841269841269841e-4f);
-    q = fmaf(q, r, 1.3888888888888889e-3f);
-    q = fmaf(q, r, 8.3333333333333333e-3f);
-    q = fmaf(q, r, 4.1666666666666664e-2f);
-    q = fmaf(q, r, 1.6666666666666666e-1f);
-    q = fmaf(q, r, 0.5f);
-    const float t = fmaf(r * r, q, fmaf(r, r_lo, r_lo));   // r^2 q + r_lo (1 + r)
-    const float hi = 1.0f + r;
-    const float err = (1.0f - hi) + r;                     // exact: |1| >= |r|
-    const float s = hi + (err + t);
-    return s * __int_as_float(((int)n + 127) << 23);       // exact scaling, result normal
+// Fast paths (ktc_fastmath.h): float-only exp and pow, about 0.5-0.6 ulp, verified on
+// the host against the double libm; arguments outside their domain (results that
+// leave the normal range, zero / negative / non-finite operands) take the double path,
+// which also carries Math.pow's special cases.
+__device__ __forceinline__ float exp_f(float x) {
+    float r;
+    return kf_exp(x, &r) ? r : exp_ref(x);
 }
+// correctly rounded exp for the sigmoid composite: e is then bit-identical to the
+// JVM's (float)Math.exp, and the two IEEE operations that follow reproduce it exactly
+__device__ __forceinline__ float exp_cr(float x) {
+    float r;
+    return kf_exp_cr(x, &r) ? r : exp_ref(x);
+}
+__device__ __forceinline__ float pow_f(float x, float y) {
+    if (y == 0.0f) return 1.0f;
+    float r;
+    return kf_pow(x, y, &r) ? r : pow_ref(x, y);
+}
+// log and tanh: CUDA's logf (max error 1 ulp) and tanhf (2 ulp) stay within the
+// 2-ulp bar against the correctly rounded value kten-jvm returns.
+__device__ __forceinline__ float log_f(float x)  { return logf(x); }
+__device__ __forceinline__ float tanh_f(float x) { return tanhf(x); }
 
 template <int OP> struct BinOp;
 template <> struct BinOp<KTC_PLUS>  { __device__ __forceinline__ float operator()(float a, float b) const { return __fadd_rn(a, b); } };
 template <> struct BinOp<KTC_MINUS> { __device__ __forceinline__ float operator()(float a, float b) const { return __fsub_rn(a, b); } };
 template <> struct BinOp<KTC_TIMES> { __device__ __forceinline__ float operator()(float a, float b) const { return __fmul_rn(a, b); } };
 template <> struct BinOp<KTC_DIV>   { __device__ __forceinline__ float operator()(float a, float b) const { return __fdiv_rn(a, b); } };
-template <> struct BinOp<KTC_POW>   { __device__ __forceinline__ float operator()(float a, float b) const { return pow_ref(a, b); } };
+template <> struct BinOp<KTC_POW>   { __device__ __forceinline__ float operator()(float a, float b) const { return pow_f(a, b); } };
 
 template <int OP> struct UnOp;
-template <> struct UnOp<KTC_EXP>  { __device__ __forceinline__ float operator()(float x) const { return exp_ref(x); } };
-template <> struct UnOp<KTC_LOG>  { __device__ __forceinline__ float operator()(float x) const { return log_ref(x); } };
-template <> struct UnOp<KTC_TANH> { __device__ __forceinline__ float operator()(float x) const { return tanh_ref(x); } };
+template <> struct UnOp<KTC_EXP>  { __device__ __forceinline__ float operator()(float x) const { return exp_f(x); } };
+template <> struct UnOp<KTC_LOG>  { __device__ __forceinline__ float operator()(float x) const { return log_f(x); } };
+template <> struct UnOp<KTC_TANH> { __device__ __forceinline__ float operator()(float x) const { return tanh_f(x); } };
 template <> struct UnOp<KTC_SIGMOID> {
     __device__ __forceinline__ float operator()(float x) const {
-        const float e = exp_ref(__fmul_rn(-1.0f, x));
+        const float e = exp_cr(__fmul_rn(-1.0f, x));
         return __fdiv_rn(1.0f, __fadd_rn(1.0f, e));
     }
 };

@@ -1,29 +1,36 @@
-// ktc_reduce.cu -- axis reductions, full reductions, sum-to-shape, scatter (sm_100a).
+// ktc_reduce.cu -- axis reductions, full reductions, scatter (sm_100a).
 //
 // Every reduction works on the collapsed view [outer, A, inner] of a contiguous
 // float32 tensor (aggregateOverAxis, JVMRawTensor.kt:154-225).  Three read-only
-// streaming kernels cover the shapes, each usable as a single pass or as the
-// first pass of a split reduction (the axis cut into S segments, partials in
-// scratch memory, combined by a small second kernel in a fixed order, so the
-// result does not depend on scheduling and is bit-stable from run to run):
+// streaming kernels cover the shapes.  Each can run as a single pass or as the
+// first pass of a split reduction: the axis is cut into S segments, every
+// segment leaves one partial in scratch memory, and a small second kernel
+// combines the S partials of each output in a fixed order, so results do not
+// depend on scheduling and are bit-stable from run to run.
 //
-//   rows_small : inner == 1, short rows: G lanes (1..32) per row, shuffle tree
-//   rows_block : inner == 1, long rows : one CTA per (row, segment), float4 loads,
-//                several independent loads in flight per thread, block tree
-//   cols       : inner  > 1           : a CTA owns TX (x4) adjacent columns and a
-//                segment of the axis, threads stride over the axis (every
-//                warp-level load is one contiguous row piece), tree over TY
+//   rows_small : inner == 1, short rows : G lanes (1..32) per row, shuffle tree
+//   rows_warp  : inner == 1, long rows  : one WARP per (row, segment) of at most
+//                32 KB; 128-bit loads, eight independent requests in flight per
+//                lane, shuffle tree, no shared memory and no block barrier
+//   cols_warp  : inner  > 1            : one warp per (slice, segment, column tile);
+//                each lane owns up to four adjacent columns and walks the axis, every
+//                warp-level load is a contiguous row piece; no shared memory
 //
-// Accumulation.  SUM/MEAN: each thread sums at most CHUNK values in float, then
-// folds that partial into a double accumulator; all cross-thread and
+// Work items are small (tens of KB) and launched in address order, one per
+// warp / CTA, so that the set of items in flight at any time covers one
+// contiguous region of memory: DRAM sees a single forward stream instead of
+// a thousand interleaved ones.
+//
+// Accumulation.  SUM/MEAN: every batch of loads (at most 32 values per thread)
+// is added in float and folded into a double accumulator; all cross-thread and
 // cross-segment combining is done in double and narrowed once.  The result is
-// therefore within a few float ulps of the exact sum for any length, which is
-// the tolerance reductions are held to (kten-jvm's own float-sequential sum()
-// stalls at 2^24-scale totals and cannot serve as the target).  MAX/MIN follow
-// Math.max/min (NaN-propagating, -0 < +0).  ARGMAX/ARGMIN use strict compares
-// from -inf/+inf, so a NaN is never selected, ties resolve to the lowest index
-// and an all -inf (or all-NaN) row yields index 0 (JVMRawTensor.kt:166-184);
-// indices are returned as float32.
+// within a few float ulps of the exact sum for any length, which is the
+// tolerance reductions are held to (kten-jvm's own float-sequential sum() stalls
+// at 2^24-scale totals and cannot serve as the target).  MAX/MIN follow Math.max
+// / Math.min (NaN-propagating, -0 < +0: the max.NaN / min.NaN instructions).
+// ARGMAX/ARGMIN use strict compares from -inf/+inf, so a NaN is never selected,
+// ties resolve to the lowest index and an all -inf (or all-NaN) row yields index
+// 0 (JVMRawTensor.kt:166-184); indices are returned as float32.
 #include "ktc_internal.hpp"
 #include "ktc_math.cuh"
 
@@ -36,368 +43,403 @@ static inline int finish_launch(const char* what, int launches = 1) {
     return KTC_OK;
 }
 
+// Math.max / Math.min in one instruction: NaN if either operand is NaN, +0 > -0
+__device__ __forceinline__ float max_nan(float a, float b) { float r; asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b)); return r; }
+__device__ __forceinline__ float min_nan(float a, float b) { float r; asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b)); return r; }
+
 // ---- accumulators ---------------------------------------------------------------
-// One accumulator type per operation family; `Partial` is what a split first
-// pass stores per (segment, output).
+// A thread feeds its accumulator in batches: begin(); add(v, j) for at most 32
+// values in increasing j; end().  `Partial` is what a split first pass stores
+// per (segment, output).
+constexpr int kNoIndex = 0x7fffffff;
+
 struct SumAcc {
     typedef double Partial;
-    float run; int cnt; double acc;
-    static constexpr int CHUNK = 32;
-    __device__ __forceinline__ void init() { run = 0.f; cnt = 0; acc = 0.0; }
-    __device__ __forceinline__ void add(float v, int64_t) {
-        run = __fadd_rn(run, v);
-        if (++cnt == CHUNK) { acc += (double)run; run = 0.f; cnt = 0; }
-    }
-    __device__ __forceinline__ void flush() { acc += (double)run; run = 0.f; cnt = 0; }
+    float run; double acc;
+    __device__ __forceinline__ void init() { run = 0.f; acc = 0.0; }
+    __device__ __forceinline__ void begin() { run = 0.f; }
+    __device__ __forceinline__ void add(float v, int) { run = __fadd_rn(run, v); }
+    __device__ __forceinline__ void add4(float4 v, int) { run = __fadd_rn(run, __fadd_rn(__fadd_rn(v.x, v.y), __fadd_rn(v.z, v.w))); }
+    __device__ __forceinline__ void end() { acc += (double)run; run = 0.f; }
     __device__ __forceinline__ void merge_partial(double p) { acc += p; }
-    __device__ __forceinline__ void merge(SumAcc& o) { flush(); acc += o.partial(); }
-    __device__ __forceinline__ void shfl_merge(unsigned mask, int off) { flush(); acc += __shfl_xor_sync(mask, acc, off); }
-    __device__ __forceinline__ double partial() { flush(); return acc; }
+    __device__ __forceinline__ void merge(SumAcc& o) { acc += o.acc; }
+    __device__ __forceinline__ void shfl_merge(unsigned mask, int off) { acc += __shfl_xor_sync(mask, acc, off); }
+    __device__ __forceinline__ double partial() { return acc; }
 };
 
 template <bool IS_MAX> struct ExtAcc {
     typedef float Partial;
     float v;
+    __device__ __forceinline__ static float op(float a, float b) { return IS_MAX ? max_nan(a, b) : min_nan(a, b); }
     __device__ __forceinline__ void init() { v = IS_MAX ? -CUDART_INF_F : CUDART_INF_F; }
-    __device__ __forceinline__ void add(float x, int64_t) { v = IS_MAX ? jmax(v, x) : jmin(v, x); }
-    __device__ __forceinline__ void merge_partial(float p) { v = IS_MAX ? jmax(v, p) : jmin(v, p); }
-    __device__ __forceinline__ void merge(ExtAcc& o) { merge_partial(o.v); }
-    __device__ __forceinline__ void shfl_merge(unsigned mask, int off) {
-        const float o = __shfl_xor_sync(mask, v, off);
-        v = IS_MAX ? jmax(v, o) : jmin(v, o);
-    }
+    __device__ __forceinline__ void begin() {}
+    __device__ __forceinline__ void add(float x, int) { v = op(v, x); }
+    __device__ __forceinline__ void add4(float4 x, int) { v = op(v, op(op(x.x, x.y), op(x.z, x.w))); }
+    __device__ __forceinline__ void end() {}
+    __device__ __forceinline__ void merge_partial(float p) { v = op(v, p); }
+    __device__ __forceinline__ void merge(ExtAcc& o) { v = op(v, o.v); }
+    __device__ __forceinline__ void shfl_merge(unsigned mask, int off) { v = op(v, __shfl_xor_sync(mask, v, off)); }
     __device__ __forceinline__ float partial() { return v; }
 };
 
-struct ArgPair { float v; int64_t i; };
+struct ArgPair { float v; int i; };
 
 template <bool IS_MAX> struct ArgAcc {
     typedef ArgPair Partial;
-    float v; int64_t i;
-    // "no candidate yet" is (-inf / +inf, index 2^62); index 0 is substituted at the very end
-    __device__ __forceinline__ void init() { v = IS_MAX ? -CUDART_INF_F : CUDART_INF_F; i = (int64_t)1 << 62; }
-    __device__ __forceinline__ void take(float x, int64_t j) {
-        const bool better = IS_MAX ? (x > v) : (x < v);
-        if (better || (x == v && j < i)) { v = x; i = j; }
+    float v; int i;
+    // "no candidate yet" is (-inf / +inf, kNoIndex); index 0 is substituted at the very end
+    __device__ __forceinline__ void init() { v = IS_MAX ? -CUDART_INF_F : CUDART_INF_F; i = kNoIndex; }
+    __device__ __forceinline__ void begin() {}
+    // a thread sees its indices in increasing order, so the strict compare of the
+    // reference loop is enough: NaN and the initial value never win, the first of equals stays
+    __device__ __forceinline__ void add(float x, int j) { if (IS_MAX ? (x > v) : (x < v)) { v = x; i = j; } }
+    __device__ __forceinline__ void add4(float4 x, int j) { add(x.x, j); add(x.y, j + 1); add(x.z, j + 2); add(x.w, j + 3); }
+    __device__ __forceinline__ void end() {}
+    // candidates from another thread / segment: larger value wins, equal values -> lower index
+    __device__ __forceinline__ void take(float x, int j) {
+        if (j != kNoIndex && ((IS_MAX ? (x > v) : (x < v)) || (x == v && j < i))) { v = x; i = j; }
     }
-    __device__ __forceinline__ void add(float x, int64_t j) {
-        // strict compare against the running best: NaN and the initial value never win
-        const bool cand = IS_MAX ? (x > -CUDART_INF_F) : (x < CUDART_INF_F);
-        if (cand) take(x, j);
-    }
-    __device__ __forceinline__ void merge_partial(ArgPair p) { if (p.i < ((int64_t)1 << 62)) take(p.v, p.i); }
-    __device__ __forceinline__ void merge(ArgAcc& o) { merge_partial(o.partial()); }
+    __device__ __forceinline__ void merge_partial(ArgPair p) { take(p.v, p.i); }
+    __device__ __forceinline__ void merge(ArgAcc& o) { take(o.v, o.i); }
     __device__ __forceinline__ void shfl_merge(unsigned mask, int off) {
         const float ov = __shfl_xor_sync(mask, v, off);
-        const long long oi = __shfl_xor_sync(mask, (long long)i, off);
-        if (oi < ((long long)1 << 62)) take(ov, (int64_t)oi);
+        const int oi = __shfl_xor_sync(mask, i, off);
+        take(ov, oi);
     }
     __device__ __forceinline__ ArgPair partial() { ArgPair p; p.v = v; p.i = i; return p; }
 };
 
-// final store: OUT_KIND 0 = value, 1 = mean (sum / count), 2 = index, 3 = value + index
-template <int OUT_KIND, class Acc> struct Finish;
-template <> struct Finish<0, SumAcc> { static __device__ __forceinline__ void put(SumAcc& a, float* out, float*, int64_t o, int64_t) { out[o] = (float)a.partial(); } };
-template <> struct Finish<1, SumAcc> { static __device__ __forceinline__ void put(SumAcc& a, float* out, float*, int64_t o, int64_t A) { out[o] = (float)(a.partial() / (double)A); } };
-template <bool M> struct Finish<0, ExtAcc<M>> { static __device__ __forceinline__ void put(ExtAcc<M>& a, float* out, float*, int64_t o, int64_t) { out[o] = a.v; } };
-template <bool M> struct Finish<2, ArgAcc<M>> {
-    static __device__ __forceinline__ void put(ArgAcc<M>& a, float* out, float*, int64_t o, int64_t) {
-        out[o] = (a.i < ((int64_t)1 << 62)) ? (float)a.i : 0.0f;
-    }
-};
-// value + index: the value follows Math.max/min (so NaN propagates), computed by a second accumulator
+// value + index in one pass: the value follows Math.max/min (NaN propagates), the index the strict-compare rule
+struct ValIdxPair { float e; float v; int i; };
 template <bool M> struct ValIdxAcc {
-    typedef ArgPair Partial;   // unused: the fused kernel is never split
+    typedef ValIdxPair Partial;
     ExtAcc<M> e; ArgAcc<M> a;
     __device__ __forceinline__ void init() { e.init(); a.init(); }
-    __device__ __forceinline__ void add(float x, int64_t j) { e.add(x, j); a.add(x, j); }
+    __device__ __forceinline__ void begin() {}
+    __device__ __forceinline__ void add(float x, int j) { e.add(x, j); a.add(x, j); }
+    __device__ __forceinline__ void add4(float4 x, int j) { e.add4(x, j); a.add4(x, j); }
+    __device__ __forceinline__ void end() {}
     __device__ __forceinline__ void shfl_merge(unsigned mask, int off) { e.shfl_merge(mask, off); a.shfl_merge(mask, off); }
-    __device__ __forceinline__ void merge_partial(ArgPair) {}
+    __device__ __forceinline__ void merge_partial(ValIdxPair p) { e.merge_partial(p.e); a.take(p.v, p.i); }
     __device__ __forceinline__ void merge(ValIdxAcc& o) { e.merge(o.e); a.merge(o.a); }
-    __device__ __forceinline__ ArgPair partial() { return a.partial(); }
+    __device__ __forceinline__ ValIdxPair partial() { ValIdxPair p; p.e = e.v; p.v = a.v; p.i = a.i; return p; }
+};
+
+// final store: OUT_KIND 0 = value, 1 = mean (sum / count), 2 = index, 3 = value + index
+template <int OUT_KIND, class Acc> struct Finish;
+template <> struct Finish<0, SumAcc> { static __device__ __forceinline__ void put(SumAcc& a, float* out, float*, int64_t o, int64_t) { out[o] = (float)a.acc; } };
+template <> struct Finish<1, SumAcc> { static __device__ __forceinline__ void put(SumAcc& a, float* out, float*, int64_t o, int64_t A) { out[o] = (float)(a.acc / (double)A); } };
+template <bool M> struct Finish<0, ExtAcc<M>> { static __device__ __forceinline__ void put(ExtAcc<M>& a, float* out, float*, int64_t o, int64_t) { out[o] = a.v; } };
+template <bool M> struct Finish<2, ArgAcc<M>> {
+    static __device__ __forceinline__ void put(ArgAcc<M>& a, float* out, float*, int64_t o, int64_t) { out[o] = (a.i != kNoIndex) ? (float)a.i : 0.0f; }
 };
 template <bool M> struct Finish<3, ValIdxAcc<M>> {
     static __device__ __forceinline__ void put(ValIdxAcc<M>& a, float* out, float* out_idx, int64_t o, int64_t) {
         out[o] = a.e.v;
-        out_idx[o] = (a.a.i < ((int64_t)1 << 62)) ? (float)a.a.i : 0.0f;
+        out_idx[o] = (a.a.i != kNoIndex) ? (float)a.a.i : 0.0f;
     }
 };
-
-// block-level tree: every warp reduces with shuffles, warp leaders publish to
-// shared memory, warp 0 combines them in warp order.
-template <class Acc>
-__device__ __forceinline__ void block_reduce(Acc& a, Acc* sm) {
-    #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) a.shfl_merge(0xffffffffu, off);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-    __syncthreads();
-    if (lane == 0) sm[warp] = a;
-    __syncthreads();
-    if (warp == 0) {
-        Acc b; b.init();
-        if (lane < nwarps) b = sm[lane];
-        #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) b.shfl_merge(0xffffffffu, off);
-        a = b;
-    }
-}
 
 // ---- rows_small: inner == 1, G lanes per row --------------------------------------
 template <int G, int OUT_KIND, class Acc>
 __global__ void __launch_bounds__(256) k_rows_small(const float* __restrict__ in, float* __restrict__ out, float* __restrict__ out_idx,
                                                     int64_t outer, int64_t A) {
-    const int64_t gthread = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
     const int lane_in_group = threadIdx.x & (G - 1);
-    // all lanes of a warp run the same number of iterations so the shuffles stay converged
-    const int64_t rows_per_sweep = nthreads / G;
-    const int64_t sweeps = (outer + rows_per_sweep - 1) / rows_per_sweep;
-    for (int64_t s = 0; s < sweeps; ++s) {
-        const int64_t row = s * rows_per_sweep + gthread / G;
-        Acc acc; acc.init();
-        if (row < outer) {
-            const float* p = in + row * A;
-            for (int64_t j = lane_in_group; j < A; j += G) acc.add(__ldg(p + j), j);
+    const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / G;     // whole groups share a row; a warp never splits a group
+    Acc acc; acc.init();
+    if (row < outer) {
+        const float* p = in + row * A;
+        constexpr int U = 8;
+        for (int64_t j = lane_in_group; j < A; j += (int64_t)G * U) {
+            float v[U];
+            #pragma unroll
+            for (int u = 0; u < U; ++u) { const int64_t jj = j + (int64_t)u * G; if (jj < A) v[u] = __ldg(p + jj); }
+            acc.begin();
+            #pragma unroll
+            for (int u = 0; u < U; ++u) { const int64_t jj = j + (int64_t)u * G; if (jj < A) acc.add(v[u], (int)jj); }
+            acc.end();
         }
-        #pragma unroll
-        for (int off = G >> 1; off > 0; off >>= 1) acc.shfl_merge(0xffffffffu, off);
-        if (row < outer && lane_in_group == 0) Finish<OUT_KIND, Acc>::put(acc, out, out_idx, row, A);
+    }
+    #pragma unroll
+    for (int off = G >> 1; off > 0; off >>= 1) acc.shfl_merge(0xffffffffu, off);
+    if (row < outer && lane_in_group == 0) Finish<OUT_KIND, Acc>::put(acc, out, out_idx, row, A);
+}
+
+// ---- rows_warp: inner == 1, one warp per (row, segment) ------------------------------
+// Item w = row * S + seg covers in[row*A + seg*seg_len ... ) -- items are in address
+// order.  VEC = 4 needs A % 4 == 0, seg_len % 4 == 0 and a 16-byte aligned base;
+// VEC = 1 is the scalar variant.  MODE 0: final value per row (S == 1).  MODE 1: one
+// Partial per segment at part[seg * outer + row].  MODE 2 (S % 8 == 0): the eight
+// warps of a CTA hold consecutive segments of one row and leave ONE Partial, combined
+// in warp order, at part[(seg / 8) * outer + row].
+template <int VEC, int OUT_KIND, int MODE, class Acc>
+__global__ void __launch_bounds__(256) k_rows_warp(const float* __restrict__ in, float* __restrict__ out, float* __restrict__ out_idx,
+                                                   typename Acc::Partial* __restrict__ part,
+                                                   int64_t outer, int64_t A, int S, int64_t seg_len) {
+    __shared__ Acc sm[8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t item = (int64_t)blockIdx.x * 8 + warp;
+    if (MODE != 2 && item >= outer * S) return;          // whole warps leave together (MODE 2 grids are exact)
+    const int64_t row = item / S; const int seg = (int)(item - row * S);
+    const int64_t j0 = (int64_t)seg * seg_len;
+    const int64_t j1 = min(A, j0 + seg_len);
+    const float* p = in + row * A;
+    Acc acc; acc.init();
+    constexpr int U = 8;
+    if (VEC == 4) {
+        const float4* p4 = reinterpret_cast<const float4*>(p);
+        const int64_t q1 = j1 >> 2;
+        for (int64_t q = (j0 >> 2) + lane; q < q1; q += 32 * U) {
+            float4 v[U];
+            #pragma unroll
+            for (int u = 0; u < U; ++u) { const int64_t k = q + 32 * u; if (k < q1) v[u] = __ldcs(p4 + k); }
+            acc.begin();
+            #pragma unroll
+            for (int u = 0; u < U; ++u) { const int64_t k = q + 32 * u; if (k < q1) acc.add4(v[u], (int)(k << 2)); }
+            acc.end();
+        }
+    } else {
+        for (int64_t j = j0 + lane; j < j1; j += 32 * U) {
+            float v[U];
+            #pragma unroll
+            for (int u = 0; u < U; ++u) { const int64_t k = j + 32 * u; if (k < j1) v[u] = __ldg(p + k); }
+            acc.begin();
+            #pragma unroll
+            for (int u = 0; u < U; ++u) { const int64_t k = j + 32 * u; if (k < j1) acc.add(v[u], (int)k); }
+            acc.end();
+        }
+    }
+    #pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc.shfl_merge(0xffffffffu, off);
+    if (MODE == 2) {
+        if (lane == 0) sm[warp] = acc;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            Acc r = sm[0];
+            #pragma unroll
+            for (int w = 1; w < 8; ++w) { Acc other = sm[w]; r.merge(other); }
+            part[(int64_t)(seg >> 3) * outer + row] = r.partial();
+        }
+    } else if (lane == 0) {
+        if (MODE == 1) part[(int64_t)seg * outer + row] = acc.partial();
+        else Finish<OUT_KIND, Acc>::put(acc, out, out_idx, row, A);
     }
 }
 
-// ---- rows_block: inner == 1, one CTA per (row, segment) ------------------------------
-// A % 4 == 0 and 16-byte aligned rows are required for the float4 path (VEC=4);
-// VEC=1 is the scalar variant.  When S > 1 the CTA writes a Partial to
-// part[seg * outer + row] instead of the final value.
+// ---- cols: inner > 1, one warp per (o, segment, column tile) --------------------------
+// A warp owns TX*VEC adjacent columns (TX lanes, a power of two) and the rows
+// [j0, j1) of the axis; when TX < 32 the other lanes take different rows (TYW = 32/TX
+// rows at a time).  Every lane accumulates its own columns over its rows -- each
+// warp-level load is TYW contiguous row pieces -- and the TYW row groups are merged
+// with shuffles at the end: no shared memory, no barrier.  Items are ordered with the
+// column tile fastest, then the segment, then o, i.e. in address order.
 template <int VEC, int OUT_KIND, bool SPLIT, class Acc>
-__global__ void __launch_bounds__(512) k_rows_block(const float* __restrict__ in, float* __restrict__ out, float* __restrict__ out_idx,
-                                                    typename Acc::Partial* __restrict__ part,
-                                                    int64_t outer, int64_t A, int S, int64_t seg_len) {
-    __shared__ Acc sm[32];
-    const int64_t n_items = outer * S;
-    for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
-        const int64_t row = item / S; const int seg = (int)(item - row * S);
-        const int64_t j0 = (int64_t)seg * seg_len;
-        const int64_t j1 = min(A, j0 + seg_len);
-        const float* p = in + row * A;
-        Acc acc; acc.init();
-        if (VEC == 4) {
-            constexpr int U = 4;
-            const float4* p4 = reinterpret_cast<const float4*>(p);
-            const int64_t q0 = j0 >> 2, q1 = j1 >> 2;          // seg_len is a multiple of 4
-            for (int64_t q = q0 + threadIdx.x; q < q1; q += (int64_t)blockDim.x * U) {
+__global__ void __launch_bounds__(256) k_cols_warp(const float* __restrict__ in, float* __restrict__ out, float* __restrict__ out_idx,
+                                                   typename Acc::Partial* __restrict__ part,
+                                                   int64_t outer, int64_t A, int64_t inner, int S, int64_t seg_len,
+                                                   int64_t col_tiles, int TX) {
+    const int lane = threadIdx.x & 31;
+    const int64_t item = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (item >= outer * S * col_tiles) return;           // whole warps leave together
+    const int64_t ct = item % col_tiles;
+    const int64_t rest = item / col_tiles;
+    const int seg = (int)(rest % S);
+    const int64_t o = rest / S;
+    const int tx = lane & (TX - 1), tyw = lane / TX, TYW = 32 / TX;
+    const int64_t c = (ct * TX + tx) * VEC;
+    const int64_t j0 = (int64_t)seg * seg_len, j1 = min(A, j0 + seg_len);
+    Acc acc[VEC];
+    #pragma unroll
+    for (int k = 0; k < VEC; ++k) acc[k].init();
+    if (c < inner) {
+        const float* p = in + o * A * inner + c;
+        constexpr int U = 8;
+        for (int64_t j = j0 + tyw; j < j1; j += (int64_t)TYW * U) {
+            if (VEC == 4) {
                 float4 v[U];
                 #pragma unroll
-                for (int u = 0; u < U; ++u) { const int64_t k = q + (int64_t)u * blockDim.x; if (k < q1) v[u] = __ldcs(p4 + k); }
+                for (int u = 0; u < U; ++u) { const int64_t jj = j + (int64_t)u * TYW; if (jj < j1) v[u] = __ldcs(reinterpret_cast<const float4*>(p + jj * inner)); }
+                #pragma unroll
+                for (int k = 0; k < VEC; ++k) acc[k].begin();
                 #pragma unroll
                 for (int u = 0; u < U; ++u) {
-                    const int64_t k = q + (int64_t)u * blockDim.x;
-                    if (k < q1) { const int64_t j = k << 2; acc.add(v[u].x, j); acc.add(v[u].y, j + 1); acc.add(v[u].z, j + 2); acc.add(v[u].w, j + 3); }
+                    const int64_t jj = j + (int64_t)u * TYW;
+                    if (jj < j1) { acc[0].add(v[u].x, (int)jj); acc[1 % VEC].add(v[u].y, (int)jj); acc[2 % VEC].add(v[u].z, (int)jj); acc[3 % VEC].add(v[u].w, (int)jj); }
                 }
+                #pragma unroll
+                for (int k = 0; k < VEC; ++k) acc[k].end();
+            } else {
+                float v[U];
+                #pragma unroll
+                for (int u = 0; u < U; ++u) { const int64_t jj = j + (int64_t)u * TYW; if (jj < j1) v[u] = __ldg(p + jj * inner); }
+                acc[0].begin();
+                #pragma unroll
+                for (int u = 0; u < U; ++u) { const int64_t jj = j + (int64_t)u * TYW; if (jj < j1) acc[0].add(v[u], (int)jj); }
+                acc[0].end();
             }
-        } else {
-            for (int64_t j = j0 + threadIdx.x; j < j1; j += blockDim.x) acc.add(__ldg(p + j), j);
-        }
-        block_reduce(acc, sm);
-        if (threadIdx.x == 0) {
-            if (SPLIT) part[(int64_t)seg * outer + row] = acc.partial();
-            else Finish<OUT_KIND, Acc>::put(acc, out, out_idx, row, A);
         }
     }
-}
-
-// ---- cols: inner > 1 ------------------------------------------------------------
-// blockDim = (TX, TY).  A CTA owns columns [c0, c0 + TX*VEC) of one `outer`
-// slice and axis rows [j0, j1); thread (tx, ty) walks rows j0+ty, j0+ty+TY, ...
-template <int VEC, int OUT_KIND, bool SPLIT, class Acc>
-__global__ void __launch_bounds__(256) k_cols(const float* __restrict__ in, float* __restrict__ out, float* __restrict__ out_idx,
-                                              typename Acc::Partial* __restrict__ part,
-                                              int64_t outer, int64_t A, int64_t inner, int S, int64_t seg_len, int64_t col_tiles) {
-    extern __shared__ __align__(16) unsigned char sm_raw[];
-    Acc* sm = reinterpret_cast<Acc*>(sm_raw);               // [TY][TX*VEC]
-    const int TX = blockDim.x, TY = blockDim.y;
-    const int tx = threadIdx.x, ty = threadIdx.y;
-    const int64_t n_items = outer * col_tiles * S;
-    for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
-        const int seg = (int)(item % S);
-        const int64_t rest = item / S;
-        const int64_t ct = rest % col_tiles, o = rest / col_tiles;
-        const int64_t c = ct * (int64_t)TX * VEC + (int64_t)tx * VEC;
-        const int64_t j0 = (int64_t)seg * seg_len, j1 = min(A, j0 + seg_len);
-        Acc acc[VEC];
+    for (int off = TX; off < 32; off <<= 1) {            // merge the row groups (all lanes take part)
         #pragma unroll
-        for (int k = 0; k < VEC; ++k) acc[k].init();
-        if (c < inner) {
-            const float* p = in + o * A * inner + c;
-            constexpr int U = 4;
-            for (int64_t j = j0 + ty; j < j1; j += (int64_t)TY * U) {
-                if (VEC == 4) {
-                    float4 v[U];
-                    #pragma unroll
-                    for (int u = 0; u < U; ++u) { const int64_t jj = j + (int64_t)u * TY; if (jj < j1) v[u] = __ldcs(reinterpret_cast<const float4*>(p + jj * inner)); }
-                    #pragma unroll
-                    for (int u = 0; u < U; ++u) {
-                        const int64_t jj = j + (int64_t)u * TY;
-                        if (jj < j1) { acc[0].add(v[u].x, jj); acc[1 % VEC].add(v[u].y, jj); acc[2 % VEC].add(v[u].z, jj); acc[3 % VEC].add(v[u].w, jj); }
-                    }
-                } else {
-                    float v[U];
-                    #pragma unroll
-                    for (int u = 0; u < U; ++u) { const int64_t jj = j + (int64_t)u * TY; if (jj < j1) v[u] = __ldg(p + jj * inner); }
-                    #pragma unroll
-                    for (int u = 0; u < U; ++u) { const int64_t jj = j + (int64_t)u * TY; if (jj < j1) acc[0].add(v[u], jj); }
-                }
-            }
-        }
-        // tree over ty in shared memory (fixed order)
-        __syncthreads();
+        for (int k = 0; k < VEC; ++k) acc[k].shfl_merge(0xffffffffu, off);
+    }
+    if (tyw == 0 && c < inner) {
         #pragma unroll
-        for (int k = 0; k < VEC; ++k) sm[(ty * TX + tx) * VEC + k] = acc[k];
-        __syncthreads();
-        if (ty == 0 && c < inner) {
-            #pragma unroll
-            for (int k = 0; k < VEC; ++k) {
-                Acc r = sm[tx * VEC + k];
-                for (int y = 1; y < TY; ++y) {
-                    Acc other = sm[(y * TX + tx) * VEC + k];
-                    r.merge(other);
-                }
-                const int64_t oidx = o * inner + c + k;
-                if (SPLIT) part[(int64_t)seg * (outer * inner) + oidx] = r.partial();
-                else Finish<OUT_KIND, Acc>::put(r, out, out_idx, oidx, A);
-            }
+        for (int k = 0; k < VEC; ++k) {
+            const int64_t oidx = o * inner + c + k;
+            if (SPLIT) part[(int64_t)seg * (outer * inner) + oidx] = acc[k].partial();
+            else Finish<OUT_KIND, Acc>::put(acc[k], out, out_idx, oidx, A);
         }
     }
 }
 
 // ---- second pass: combine S partials per output in segment order --------------------
+// One warp per output when there are many segments, one thread per output when few
+// (coalesced across outputs).
 template <int OUT_KIND, class Acc>
-__global__ void k_combine(const typename Acc::Partial* __restrict__ part, float* __restrict__ out, float* __restrict__ out_idx,
-                          int64_t n_out, int S, int64_t A) {
-    // one warp per output; lanes stride over the segments, then a shuffle tree
-    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+__global__ void __launch_bounds__(256) k_combine_warp(const typename Acc::Partial* __restrict__ part, float* __restrict__ out,
+                                                      float* __restrict__ out_idx, int64_t n_out, int S, int64_t A) {
+    const int64_t o = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
-    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-    for (int64_t o = warp; o < n_out; o += nwarps) {
-        Acc acc; acc.init();
-        for (int s = lane; s < S; s += 32) acc.merge_partial(part[(int64_t)s * n_out + o]);
-        #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) acc.shfl_merge(0xffffffffu, off);
-        if (lane == 0) Finish<OUT_KIND, Acc>::put(acc, out, out_idx, o, A);
+    if (o >= n_out) return;
+    Acc acc; acc.init();
+    for (int s = lane; s < S; s += 32) acc.merge_partial(part[(int64_t)s * n_out + o]);
+    #pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc.shfl_merge(0xffffffffu, off);
+    if (lane == 0) Finish<OUT_KIND, Acc>::put(acc, out, out_idx, o, A);
+}
+
+template <int OUT_KIND, class Acc>
+__global__ void __launch_bounds__(256) k_combine_thread(const typename Acc::Partial* __restrict__ part, float* __restrict__ out,
+                                                        float* __restrict__ out_idx, int64_t n_out, int S, int64_t A) {
+    const int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (o >= n_out) return;
+    Acc acc; acc.init();
+    for (int s = 0; s < S; ++s) acc.merge_partial(part[(int64_t)s * n_out + o]);
+    Finish<OUT_KIND, Acc>::put(acc, out, out_idx, o, A);
+}
+
+// few outputs, many segments: one CTA per output, threads stride over the segments,
+// then shuffles inside each warp and a fixed-order pass over the warp leaders
+template <int OUT_KIND, class Acc>
+__global__ void __launch_bounds__(512) k_combine_block(const typename Acc::Partial* __restrict__ part, float* __restrict__ out,
+                                                       float* __restrict__ out_idx, int64_t n_out, int S, int64_t A) {
+    __shared__ Acc sm[16];
+    const int64_t o = blockIdx.x;
+    Acc acc; acc.init();
+    for (int s = threadIdx.x; s < S; s += blockDim.x) acc.merge_partial(part[(int64_t)s * n_out + o]);
+    #pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc.shfl_merge(0xffffffffu, off);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) sm[warp] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        Acc r = sm[0];
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w) { Acc other = sm[w]; r.merge(other); }
+        Finish<OUT_KIND, Acc>::put(r, out, out_idx, o, A);
     }
 }
 
 // ---- host side ------------------------------------------------------------------
 struct Plan {
-    int kind;          // 0 rows_small, 1 rows_block, 2 cols
+    int kind;          // 0 rows_small, 1 rows_warp, 2 cols_warp
     int G;             // rows_small lanes per row
     int vec;           // 1 or 4
-    int S;             // segments
+    int S;             // segments of the axis
+    int S_out;         // partials per output the first pass leaves (S, or S/8 with the CTA pre-combine)
     int64_t seg_len;
-    int tx, ty; int64_t col_tiles;
-    int grid;
+    int tx; int64_t col_tiles;
+    int64_t grid;
 };
 
-static Plan make_plan(Device* d, const float* in, int64_t outer, int64_t A, int64_t inner, bool allow_split) {
-    Plan p{}; p.S = 1; p.seg_len = A; p.vec = 1; p.G = 1;
-    const int64_t target_ctas = (int64_t)d->sm_count * tune("reduce_ctas_per_sm", 8);
+static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+static Plan make_plan(Device* d, const float* in, int64_t outer, int64_t A, int64_t inner, int partial_bytes) {
+    Plan p{}; p.S = 1; p.S_out = 1; p.seg_len = A; p.vec = 1; p.G = 1;
     if (inner == 1) {
         const bool vec_ok = (A % 4 == 0) && aligned16(in);
-        const int64_t small_limit = tune("reduce_rows_small_max", 512);
-        if (A <= small_limit || (A < 4096 && !vec_ok && outer >= 2048)) {
+        if (A <= tune("reduce_rows_small_max", 64)) {
             p.kind = 0;
-            int g = 1; while (g < 32 && g * 4 < A) g <<= 1;      // about four elements per lane, at most a warp
+            int g = 1; while (g < 32 && g * 4 < A) g <<= 1;      // about four elements per lane
             p.G = g;
-            const int64_t threads_needed = outer * g;
-            int64_t blocks = (threads_needed + 255) / 256;
-            const int64_t cap = (int64_t)d->sm_count * 16;
-            p.grid = (int)(blocks < cap ? (blocks < 1 ? 1 : blocks) : cap);
+            p.grid = ceil_div(outer * g, 256);
             return p;
         }
         p.kind = 1; p.vec = vec_ok ? 4 : 1;
-        if (allow_split && outer < target_ctas) {
-            int64_t S = (target_ctas + outer - 1) / outer;
-            const int64_t min_seg = 8192;                        // floats per segment worth a CTA
-            const int64_t max_S = (A + min_seg - 1) / min_seg;
-            if (S > max_S) S = max_S;
-            if (S > 1) {
-                int64_t seg = (A + S - 1) / S; seg = (seg + 3) & ~(int64_t)3;
-                p.S = (int)((A + seg - 1) / seg); p.seg_len = seg;
-            }
+        int64_t seg = tune("reduce_seg_floats", 8192);            // 32 KB per warp
+        seg = (seg + 3) & ~(int64_t)3;
+        if (A > seg + seg / 2) {
+            p.S = (int)ceil_div(A, seg); p.seg_len = seg;
+            if (p.S >= 16) {                                       // eight segments per CTA, one partial per CTA
+                p.S = (p.S + 7) & ~7;                              // (trailing segments may be empty)
+                p.S_out = p.S / 8;
+            } else p.S_out = p.S;
         }
-        const int64_t items = outer * p.S;
-        p.grid = (int)(items < target_ctas * 4 ? items : target_ctas * 4);
-        if (p.grid < 1) p.grid = 1;
+        p.grid = ceil_div(outer * p.S, 8);                        // 8 warps per CTA
         return p;
     }
     p.kind = 2;
     const bool vec_ok = (inner % 4 == 0) && aligned16(in);
     p.vec = vec_ok ? 4 : 1;
-    const int64_t lanes_needed = (inner + p.vec - 1) / p.vec;
+    const int64_t lanes_needed = ceil_div(inner, p.vec);
     int tx = 1; while (tx < 32 && tx < lanes_needed) tx <<= 1;
-    p.tx = tx; p.ty = 256 / tx;
-    if ((int64_t)p.ty > A) { int ty = 1; while (ty < A) ty <<= 1; p.ty = ty < 1 ? 1 : ty; }
-    p.col_tiles = (lanes_needed + tx - 1) / tx;
-    const int64_t base_items = outer * p.col_tiles;
-    if (allow_split && base_items < target_ctas) {
-        int64_t S = (target_ctas + base_items - 1) / base_items;
-        const int64_t min_seg = (int64_t)p.ty * 16;
-        const int64_t max_S = (A + min_seg - 1) / min_seg;
-        if (S > max_S) S = max_S;
-        if (S > 1) { const int64_t seg = (A + S - 1) / S; p.S = (int)((A + seg - 1) / seg); p.seg_len = seg; }
-    }
-    const int64_t items = base_items * p.S;
-    p.grid = (int)(items < target_ctas * 4 ? items : target_ctas * 4);
-    if (p.grid < 1) p.grid = 1;
+    p.tx = tx;
+    p.col_tiles = ceil_div(lanes_needed, tx);
+    // a warp streams about reduce_cols_item_kb; the partial traffic must stay under ~3 % of the input
+    const int64_t row_bytes = (int64_t)tx * p.vec * 4;
+    int64_t seg = tune("reduce_cols_item_kb", 64) * 1024 / row_bytes;
+    const int64_t min_seg = (int64_t)partial_bytes * 8;           // S * partial_bytes <= A * 4 / 32
+    if (seg < min_seg) seg = min_seg;
+    if (A > seg + seg / 2) { p.S = (int)ceil_div(A, seg); p.seg_len = seg; }
+    p.S_out = p.S;
+    p.grid = ceil_div(outer * p.S * p.col_tiles, 8);
     return p;
 }
 
 template <int OUT_KIND, class Acc>
-static int run_reduce(Device* d, float* out, float* out_idx, const float* in, int64_t outer, int64_t A, int64_t inner,
-                      bool allow_split) {
+static int run_reduce(Device* d, float* out, float* out_idx, const float* in, int64_t outer, int64_t A, int64_t inner) {
     const int64_t n_out = outer * inner;
     if (n_out == 0) return KTC_OK;
-    const Plan p = make_plan(d, in, outer, A, inner, allow_split);
     typedef typename Acc::Partial Partial;
+    const Plan p = make_plan(d, in, outer, A, inner, (int)sizeof(Partial));
+    if (p.grid > 0x7fffffffLL) return fail(KTC_ENOTSUP, "reduction needs %lld CTAs", (long long)p.grid);
     Scratch scratch; Partial* part = nullptr;
     if (p.S > 1) {
-        const int64_t floats = ((int64_t)sizeof(Partial) * p.S * n_out + 3) / 4;
+        const int64_t floats = ((int64_t)sizeof(Partial) * p.S_out * n_out + 3) / 4;
         KTC_TRY(scratch.get(d, floats));
         part = reinterpret_cast<Partial*>(scratch.ptr);
     }
+    const int grid = (int)(p.grid < 1 ? 1 : p.grid);
     if (p.kind == 0) {
-#define KTC_RS(GG) case GG: k_rows_small<GG, OUT_KIND, Acc><<<p.grid, 256, 0, d->stream>>>(in, out, out_idx, outer, A); break;
+#define KTC_RS(GG) case GG: k_rows_small<GG, OUT_KIND, Acc><<<grid, 256, 0, d->stream>>>(in, out, out_idx, outer, A); break;
         switch (p.G) { KTC_RS(1) KTC_RS(2) KTC_RS(4) KTC_RS(8) KTC_RS(16) KTC_RS(32) }
 #undef KTC_RS
         return finish_launch("rows_small");
     }
     if (p.kind == 1) {
-        const int threads = tune("reduce_block_threads", 256);
-        if (p.S > 1) {
-            if (p.vec == 4) k_rows_block<4, OUT_KIND, true, Acc><<<p.grid, threads, 0, d->stream>>>(in, out, out_idx, part, outer, A, p.S, p.seg_len);
-            else            k_rows_block<1, OUT_KIND, true, Acc><<<p.grid, threads, 0, d->stream>>>(in, out, out_idx, part, outer, A, p.S, p.seg_len);
-        } else {
-            if (p.vec == 4) k_rows_block<4, OUT_KIND, false, Acc><<<p.grid, threads, 0, d->stream>>>(in, out, out_idx, part, outer, A, 1, A);
-            else            k_rows_block<1, OUT_KIND, false, Acc><<<p.grid, threads, 0, d->stream>>>(in, out, out_idx, part, outer, A, 1, A);
-        }
+        const int mode = p.S == 1 ? 0 : (p.S_out == p.S ? 1 : 2);
+#define KTC_RW(V, M) k_rows_warp<V, OUT_KIND, M, Acc><<<grid, 256, 0, d->stream>>>(in, out, out_idx, part, outer, A, p.S, p.seg_len)
+        if (p.vec == 4) { if (mode == 0) KTC_RW(4, 0); else if (mode == 1) KTC_RW(4, 1); else KTC_RW(4, 2); }
+        else            { if (mode == 0) KTC_RW(1, 0); else if (mode == 1) KTC_RW(1, 1); else KTC_RW(1, 2); }
+#undef KTC_RW
     } else {
-        const dim3 block(p.tx, p.ty);
-        const size_t smem = sizeof(Acc) * (size_t)p.tx * p.ty * p.vec;
-        if (p.S > 1) {
-            if (p.vec == 4) k_cols<4, OUT_KIND, true, Acc><<<p.grid, block, smem, d->stream>>>(in, out, out_idx, part, outer, A, inner, p.S, p.seg_len, p.col_tiles);
-            else            k_cols<1, OUT_KIND, true, Acc><<<p.grid, block, smem, d->stream>>>(in, out, out_idx, part, outer, A, inner, p.S, p.seg_len, p.col_tiles);
-        } else {
-            if (p.vec == 4) k_cols<4, OUT_KIND, false, Acc><<<p.grid, block, smem, d->stream>>>(in, out, out_idx, part, outer, A, inner, 1, A, p.col_tiles);
-            else            k_cols<1, OUT_KIND, false, Acc><<<p.grid, block, smem, d->stream>>>(in, out, out_idx, part, outer, A, inner, 1, A, p.col_tiles);
-        }
+#define KTC_CW(V, SP) k_cols_warp<V, OUT_KIND, SP, Acc><<<grid, 256, 0, d->stream>>>(in, out, out_idx, part, outer, A, inner, p.S, p.seg_len, p.col_tiles, p.tx)
+        if (p.vec == 4) { if (p.S > 1) KTC_CW(4, true); else KTC_CW(4, false); }
+        else            { if (p.S > 1) KTC_CW(1, true); else KTC_CW(1, false); }
+#undef KTC_CW
     }
-    KTC_TRY(finish_launch(p.kind == 1 ? "rows_block" : "cols"));
+    KTC_TRY(finish_launch(p.kind == 1 ? "rows_warp" : "cols_warp"));
     if (p.S > 1) {
-        const int64_t warps = n_out;
-        int64_t blocks = (warps * 32 + 255) / 256;
-        const int64_t cap = (int64_t)d->sm_count * 8;
-        if (blocks > cap) blocks = cap;
-        k_combine<OUT_KIND, Acc><<<(int)blocks, 256, 0, d->stream>>>(part, out, out_idx, n_out, p.S, A);
+        const int S2 = p.S_out;
+        if (S2 >= 1024 && n_out <= 64) {
+            k_combine_block<OUT_KIND, Acc><<<(int)n_out, 512, 0, d->stream>>>(part, out, out_idx, n_out, S2, A);
+        } else if (S2 >= 64 || n_out < 4096) {
+            const int64_t blocks = ceil_div(n_out * 32, 256);
+            if (blocks > 0x7fffffffLL) return fail(KTC_ENOTSUP, "combine needs %lld CTAs", (long long)blocks);
+            k_combine_warp<OUT_KIND, Acc><<<(int)blocks, 256, 0, d->stream>>>(part, out, out_idx, n_out, S2, A);
+        } else {
+            k_combine_thread<OUT_KIND, Acc><<<(int)ceil_div(n_out, 256), 256, 0, d->stream>>>(part, out, out_idx, n_out, S2, A);
+        }
         KTC_TRY(finish_launch("combine"));
     }
     return KTC_OK;
@@ -406,15 +448,17 @@ static int run_reduce(Device* d, float* out, float* out_idx, const float* in, in
 // op: KTC_SUM..KTC_ARGMIN, or 100 / 101 for fused (value, index) of max / min
 int launch_reduce_axis(Device* d, int op, float* out, float* out_idx, const float* in,
                        int64_t outer, int64_t A, int64_t inner) {
+    if ((op == KTC_ARGMAX || op == KTC_ARGMIN || op >= 100) && A >= (int64_t)kNoIndex)
+        return fail(KTC_EINVAL, "index reductions support an axis of at most 2^31 - 2 elements (the reference indexes with Int)");
     switch (op) {
-    case KTC_SUM:    return run_reduce<0, SumAcc>(d, out, nullptr, in, outer, A, inner, true);
-    case KTC_MEAN:   return run_reduce<1, SumAcc>(d, out, nullptr, in, outer, A, inner, true);
-    case KTC_MAX:    return run_reduce<0, ExtAcc<true>>(d, out, nullptr, in, outer, A, inner, true);
-    case KTC_MIN:    return run_reduce<0, ExtAcc<false>>(d, out, nullptr, in, outer, A, inner, true);
-    case KTC_ARGMAX: return run_reduce<2, ArgAcc<true>>(d, out, nullptr, in, outer, A, inner, true);
-    case KTC_ARGMIN: return run_reduce<2, ArgAcc<false>>(d, out, nullptr, in, outer, A, inner, true);
-    case 100:        return run_reduce<3, ValIdxAcc<true>>(d, out, out_idx, in, outer, A, inner, false);
-    case 101:        return run_reduce<3, ValIdxAcc<false>>(d, out, out_idx, in, outer, A, inner, false);
+    case KTC_SUM:    return run_reduce<0, SumAcc>(d, out, nullptr, in, outer, A, inner);
+    case KTC_MEAN:   return run_reduce<1, SumAcc>(d, out, nullptr, in, outer, A, inner);
+    case KTC_MAX:    return run_reduce<0, ExtAcc<true>>(d, out, nullptr, in, outer, A, inner);
+    case KTC_MIN:    return run_reduce<0, ExtAcc<false>>(d, out, nullptr, in, outer, A, inner);
+    case KTC_ARGMAX: return run_reduce<2, ArgAcc<true>>(d, out, nullptr, in, outer, A, inner);
+    case KTC_ARGMIN: return run_reduce<2, ArgAcc<false>>(d, out, nullptr, in, outer, A, inner);
+    case 100:        return run_reduce<3, ValIdxAcc<true>>(d, out, out_idx, in, outer, A, inner);
+    case 101:        return run_reduce<3, ValIdxAcc<false>>(d, out, out_idx, in, outer, A, inner);
     }
     return fail(KTC_EINVAL, "unknown aggregating op %d", op);
 }
