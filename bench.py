@@ -80,9 +80,10 @@ def measured_peak():
 
 
 class ClockSampler:
-    """nvidia-smi SM clock / throttle-reason samples while the timed region runs (read only)."""
+    """nvidia-smi SM clock / throttle-reason samples (read only).  Sampling runs in the
+    background; `stop(t0, t1)` keeps the samples whose timestamps fall inside [t0, t1]."""
 
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
@@ -90,7 +91,7 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50",
                                           "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -101,30 +102,38 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
-    def stop(self):
+    def stop(self, t0: float, t1: float):
+        import datetime
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, smax, power, reasons = [], [], [], set()
+        sm, smax, power, reasons, total = [], [], [], set(), 0
         for ln in self.lines:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
             try:
-                sm.append(float(f[1])); smax.append(float(f[2])); power.append(float(f[3]))
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                vals = (float(f[1]), float(f[2]), float(f[3]))
             except ValueError:
                 continue
+            total += 1
+            if not (t0 - 0.02 <= ts <= t1 + 0.02):
+                continue
+            sm.append(vals[0]); smax.append(vals[1]); power.append(vals[2])
             for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
         if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(smax)), "power_w_max": float(max(power)),
-                "samples": len(sm), "reasons": sorted(reasons)}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [f"no samples inside the timed window ({total} outside)"]}
+        return {"sm_mhz": float(np.median(sm)), "sm_min_mhz": float(min(sm)), "sm_max_mhz": float(max(smax)),
+                "power_w_median": float(np.median(power)), "power_w_max": float(max(power)),
+                "samples_in_window": len(sm), "reasons": sorted(reasons)}
 
 
 # ----------------------------------------------------------------------------------------------
@@ -318,6 +327,55 @@ class GpuSweep:
         return float(ms.value)
 
 
+def run_sharded_graph(ops, lib, L, D, rank, world, comm, steps, warmup, dist):
+    """The sharded autograd configuration: x[262144,1024] ~ U(-1,1) split by rows over the ranks
+    (strong scaling: the global tensor is fixed), w[1,1024] ~ N(0,0.02), b[1024] = 0;
+    loss = sum(sigmoid(x*w + b) pow 2), backward for w and b, partials all-reduced."""
+    from kten_b200.sharded import NcclCollective, ShardedSigmoidGraph, shard_rows
+    rows, cols = 262144, 1024
+    first, count = shard_rows(rows, world, rank)
+    hx = D.uniform(count * cols, 0, -1.0, 1.0, stream=0, first=first * cols)
+    hw = D.normal(cols, 0, 0.0, 0.02, stream=1)
+    x = ops.createRaw([count, cols], hx)
+    w = ops.createRaw([1, cols], hw)
+    b = ops.createRawFill([cols], 0.0)
+    del hx
+    graph = ShardedSigmoidGraph(ops, x, w, b, NcclCollective(ops, comm) if comm is not None else None)
+    ms = C.c_float(0)
+
+    def one_step():
+        with ops.garbageCollector():
+            out = graph.step()
+            graph.release_step()
+        return out
+
+    for _ in range(max(warmup, 3)):
+        out = one_step()
+    ops.synchronize()
+    if dist is not None:
+        dist.barrier()
+    launches0 = lib.ktc_launch_count()
+    L.check(lib.ktc_timer_start(ops.device))
+    for _ in range(steps):
+        out = one_step()
+    L.check(lib.ktc_timer_stop(ops.device, C.byref(ms)))
+    launches = lib.ktc_launch_count() - launches0
+    # the loss tensor of the last step was released with its graph; gw / gb are the Variables' gradients
+    gw, gb = graph.w.gradient.toArray().reshape(-1), graph.b.gradient.toArray()
+    t = float(ms.value)
+    if dist is not None:
+        import torch
+        tt = torch.tensor([t], dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        t = float(tt[0])
+    for r in (x, w, b):
+        r.release()
+    return {"workload": "x[262144,1024] row-sharded, loss = sum(sigmoid(x*w+b) pow 2), backward + all-reduce of (loss, gw, gb)",
+            "scaling": "strong", "ms_per_step": t / steps, "gelem_per_s": rows * cols / (t / steps) / 1e6,
+            "kernel_launches_per_step": launches / steps, "rows_per_gpu": count,
+            "grad_w_abs_sum": float(np.abs(gw).sum()), "grad_b_abs_sum": float(np.abs(gb).sum())}
+
+
 def init_distributed(n_gpus):
     """(rank, world, local_rank, dist module or None).  torch.distributed is plumbing only:
     rendezvous, the barrier and the max over ranks."""
@@ -371,9 +429,10 @@ def run_gpu_arm(args):
     # ---- timed region: exactly K steps, device-timed on the launching stream ----------------------
     sampler = ClockSampler(local)
     sampler.start()
-    time.sleep(0.3)
+    time.sleep(0.5)
     launches0 = lib.ktc_launch_count()
     barrier()
+    t_window0 = time.time()
     sweep.timer_start()
     for _ in range(args.steps):
         run_step()
@@ -391,7 +450,8 @@ def run_gpu_arm(args):
         ms = sweep.timer_stop() / args.steps
         per_op.append(dict(name=s["name"], family=s["family"], ms=ms, gbs=s["bytes"] / ms / 1e6,
                            gelem_s=s["elements"] / ms / 1e6))
-    clocks = sampler.stop()
+    sweep.ops.synchronize()
+    clocks = sampler.stop(t_window0, time.time())
 
     # ---- end to end: host buffers, copies inside the timed region ----------------------------------
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
@@ -410,6 +470,14 @@ def run_gpu_arm(args):
     e2e_ms = sweep.timer_stop()
     e2e_wall = time.perf_counter() - t_wall
     barrier()
+
+    # ---- the sharded autograd graph (strong scaling over the same ranks) ---------------------------
+    sharded = None
+    if args.sharded_graph:
+        for r in (sweep.a2, sweep.b2, sweep.a3, sweep.t3, sweep.x4, sweep.out):
+            r.release()                               # hand the sweep's buffers back to the pool first
+        L.check(lib.ktc_pool_trim(local))
+        sharded = run_sharded_graph(sweep.ops, lib, L, D, rank, world, comm, max(2, min(args.steps, 5)), args.warmup, dist)
 
     # ---- max over ranks -----------------------------------------------------------------------------
     if dist is not None:
@@ -457,6 +525,8 @@ def run_gpu_arm(args):
         "clocks": clocks,
         "setup_s": round(sweep.setup_s, 1),
     }
+    if sharded is not None:
+        line["sharded_graph"] = sharded
     if rank == 0:
         if args.cpu_baseline:
             secs, nbytes, _ = cpu_sample_pass(args.cpu_sample_log2)
@@ -474,6 +544,65 @@ def run_gpu_arm(args):
     return 0
 
 
+def run_single_case(args):
+    """`--case NAME --log2n L --reps R`: launch one op of the sweep R times on 2^L-element
+    operands (same shapes ratio as the full sweep).  This is the small, self-terminating
+    workload the ncu captures under profiles/ are taken on; it prints the op's GB/s."""
+    from kten_b200 import _lib as L
+    from kten_b200 import datagen as D
+    from kten_b200.tensor_operations import CUDATensorOperations
+    ops = CUDATensorOperations(0)
+    lib = ops.lib
+    n = 1 << args.log2n
+    scale = n / N28
+    name = args.case
+    spec = {s_["name"]: s_ for s_ in sweep_spec()}[name]
+    mk = ops.createRaw
+    out = mk([n])
+    small = mk([max(1, n // 4096)])
+    if name.startswith("c2."):
+        a, b = mk([n], D.uniform(n, 1, 0.1, 2.0)), mk([n], D.uniform(n, 2, 0.1, 2.0))
+        op = name[3:]
+        if op in ("plus", "times", "div", "pow"):
+            code = {"plus": L.PLUS, "times": L.TIMES, "div": L.DIV, "pow": L.POW}[op]
+            fn = lambda: L.check(lib.ktc_binary(code, out.storeReference, a.storeReference, b.storeReference, n))
+        else:
+            code = {"exp": L.EXP, "log": L.LOG, "tanh": L.TANH, "sigmoid": L.SIGMOID}[op]
+            fn = lambda: L.check(lib.ktc_unary(code, out.storeReference, a.storeReference, n))
+    elif name.startswith("c3."):
+        rows = max(1, int(1024 * scale))
+        a = mk([rows, 1024, 256], D.normal(n, 3, 0.0, 1.0))
+        b = mk([1, 1024, 1], D.uniform(1024, 4, 0.5, 2.0))
+        c = mk([rows, 1, 256], D.uniform(rows * 256, 5, -1.0, 1.0))
+        s3, n3 = L.shape_array([rows, 1024, 256]); sb, nb = L.shape_array([1, 1024, 1]); sc, nc = L.shape_array([rows, 1, 256])
+        if name == "c3.a*b":
+            fn = lambda: L.check(lib.ktc_binary_bcast(L.TIMES, out.storeReference, a.storeReference, s3, n3, b.storeReference, sb, nb))
+        elif name == "c3.(a*b)+c":
+            fn = lambda: L.check(lib.ktc_binary_bcast(L.PLUS, out.storeReference, a.storeReference, s3, n3, c.storeReference, sc, nc))
+        else:
+            fn = lambda: L.check(lib.ktc_binary_bcast(L.DIV, out.storeReference, a.storeReference, s3, n3, b.storeReference, sb, nb))
+    else:
+        x = mk([n], D.normal(n, 6, 0.0, 1.0, quantum=16.0))
+        if name.startswith("c4.last."):
+            code = {"sum": L.SUM, "mean": L.MEAN, "max": L.MAX, "argmax": L.ARGMAX}[name[8:]]
+            fn = lambda: L.check(lib.ktc_reduce_axis(code, small.storeReference, x.storeReference, n // 4096, 4096, 1))
+        elif name.startswith("c4.mid."):
+            code = {"sum": L.SUM, "max": L.MAX}[name[7:]]
+            fn = lambda: L.check(lib.ktc_reduce_axis(code, small.storeReference, x.storeReference, max(1, n // (4096 * 128)), 4096, 128))
+        else:
+            fn = lambda: L.check(lib.ktc_reduce_all(L.SUM, small.storeReference, x.storeReference, n))
+    fn()
+    ops.synchronize()
+    L.check(lib.ktc_timer_start(0))
+    for _ in range(args.reps):
+        fn()
+    ms = C.c_float(0)
+    L.check(lib.ktc_timer_stop(0, C.byref(ms)))
+    per = ms.value / args.reps
+    print(json.dumps({"case": name, "elements": n, "ms": per, "gbs": spec["bytes"] * scale / per / 1e6}))
+    return 0
+
+
 def load_traffic(kernel: str):
     """dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the
     committed ncu summary (profiles/dram_traffic.json); None when no capture exists."""
@@ -487,17 +616,23 @@ def load_traffic(kernel: str):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="kten_b200", choices=["kten_b200", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--cpu-sample-log2", type=int, default=None, help="log2 of the CPU sample size (default 25 for cpu_baseline, 24 for --impl reference)")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
+    ap.add_argument("--no-sharded-graph", dest="sharded_graph", action="store_false")
+    ap.add_argument("--case", default=None, help="run one op of the sweep alone (profiling workload), e.g. c2.plus, c4.last.max")
+    ap.add_argument("--log2n", type=int, default=26)
+    ap.add_argument("--reps", type=int, default=3)
     args = ap.parse_args()
     if args.cpu_sample_log2 is None:
         args.cpu_sample_log2 = 24 if args.impl == "reference" else 25
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.case:
+        return run_single_case(args)
     return run_gpu_arm(args)
 
 

@@ -38,16 +38,15 @@ template <int U, class F>
 __global__ void __launch_bounds__(256) k_map1_vec(const float4* __restrict__ a, float4* __restrict__ out, int64_t n4, F f) {
     const int64_t tile = (int64_t)blockDim.x * U;
     for (int64_t base = (int64_t)blockIdx.x * tile; base < n4; base += (int64_t)gridDim.x * tile) {
+        const int64_t i0 = base + threadIdx.x;
         float4 va[U];
-        #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int64_t i = base + (int64_t)u * blockDim.x + threadIdx.x;
-            if (i < n4) va[u] = ld_stream(a + i);
-        }
-        #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int64_t i = base + (int64_t)u * blockDim.x + threadIdx.x;
-            if (i < n4) st_stream(out + i, apply1(f, va[u]));
+        if (base + tile <= n4) {                                   // whole tile: every load before the first use, no guards
+            #pragma unroll
+            for (int u = 0; u < U; ++u) va[u] = ld_stream(a + i0 + (int64_t)u * blockDim.x);
+            #pragma unroll
+            for (int u = 0; u < U; ++u) st_stream(out + i0 + (int64_t)u * blockDim.x, apply1(f, va[u]));
+        } else {
+            for (int64_t i = i0; i < n4; i += blockDim.x) st_stream(out + i, apply1(f, ld_stream(a + i)));
         }
     }
 }
@@ -57,16 +56,15 @@ __global__ void __launch_bounds__(256) k_map2_vec(const float4* __restrict__ a, 
                                                   float4* __restrict__ out, int64_t n4, F f) {
     const int64_t tile = (int64_t)blockDim.x * U;
     for (int64_t base = (int64_t)blockIdx.x * tile; base < n4; base += (int64_t)gridDim.x * tile) {
+        const int64_t i0 = base + threadIdx.x;
         float4 va[U], vb[U];
-        #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int64_t i = base + (int64_t)u * blockDim.x + threadIdx.x;
-            if (i < n4) { va[u] = ld_stream(a + i); vb[u] = ld_stream(b + i); }
-        }
-        #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int64_t i = base + (int64_t)u * blockDim.x + threadIdx.x;
-            if (i < n4) st_stream(out + i, apply2(f, va[u], vb[u]));
+        if (base + tile <= n4) {
+            #pragma unroll
+            for (int u = 0; u < U; ++u) { va[u] = ld_stream(a + i0 + (int64_t)u * blockDim.x); vb[u] = ld_stream(b + i0 + (int64_t)u * blockDim.x); }
+            #pragma unroll
+            for (int u = 0; u < U; ++u) st_stream(out + i0 + (int64_t)u * blockDim.x, apply2(f, va[u], vb[u]));
+        } else {
+            for (int64_t i = i0; i < n4; i += blockDim.x) st_stream(out + i, apply2(f, ld_stream(a + i), ld_stream(b + i)));
         }
     }
 }
@@ -256,14 +254,21 @@ __device__ __forceinline__ float4 load_operand(const float* sm, const float* til
     return make_float4(0.f, 0.f, 0.f, 0.f);
 }
 
+// A thread owns one column group (4 floats) and the rows ty, ty + TYC, ... of the tile,
+// at most U = 8 of them per batch (a tile of 8192 floats is one batch).  The loads of the
+// full-size (DIRECT) operands are issued first, then the broadcast operand is staged in
+// shared memory, so the staging latency overlaps the main stream instead of preceding it.
 template <int MODE_A, int MODE_B, class F>
 __global__ void __launch_bounds__(256) k_bcast3(BcastArgs p, F f) {
     extern __shared__ __align__(16) float smem[];
     constexpr bool STAGE_A = (MODE_A == AM_SMEMROW || MODE_A == AM_ROWSCALAR);
     constexpr bool STAGE_B = (MODE_B == AM_SMEMROW || MODE_B == AM_ROWSCALAR);
+    constexpr int U = 8;
     const int sm_stride = max(p.cols_per_tile, (p.rows_per_tile + 3) & ~3);
     float* sm_a = smem;
     float* sm_b = smem + (STAGE_A ? sm_stride : 0);
+    const int tx = threadIdx.x & (p.txc - 1), ty = threadIdx.x >> p.txc_log2;
+    const int tyc = blockDim.x >> p.txc_log2;
 
     const int64_t tiles_per_i0 = p.tiles_d1 * p.tiles_d2;
     const int64_t n_tiles = p.D0 * tiles_per_i0;
@@ -275,39 +280,44 @@ __global__ void __launch_bounds__(256) k_bcast3(BcastArgs p, F f) {
         const int64_t r0 = td1 * p.rows_per_tile, c0 = td2 * (int64_t)p.cols_per_tile;
         const int rows = (int)min((int64_t)p.rows_per_tile, p.D1 - r0);
         const int cols4 = (int)(min((int64_t)p.cols_per_tile, p.D2 - c0) >> 2);
-
-        if (STAGE_A || STAGE_B) {
-            __syncthreads();                     // readers of the previous tile are done
-            if (STAGE_A) stage_operand<MODE_A>(sm_a, p.a + i0 * p.as0, p.as1, r0, c0, rows, cols4);
-            if (STAGE_B) stage_operand<MODE_B>(sm_b, p.b + i0 * p.bs0, p.bs1, r0, c0, rows, cols4);
-            __syncthreads();
-        }
-
         const float* abase = (MODE_A == AM_DIRECT) ? p.a + i0 * p.as0 + r0 * p.as1 + c0 : nullptr;
         const float* bbase = (MODE_B == AM_DIRECT) ? p.b + i0 * p.bs0 + r0 * p.bs1 + c0 : nullptr;
         float* obase = p.out + (i0 * p.D1 + r0) * p.D2 + c0;
+        bool staged = false;
 
-        // thread (tx, ty): fixed column group, rows ty, ty + TYC, ... -- no per-item division
-        const int tx = threadIdx.x & (p.txc - 1), ty = threadIdx.x >> p.txc_log2;
-        const int tyc = blockDim.x >> p.txc_log2;
-        constexpr int U = 4;
-        for (int c4 = tx; c4 < cols4; c4 += p.txc) {
+        for (int c4 = tx; c4 < cols4 || !staged; c4 += p.txc) {
             const int col = c4 << 2;
-            for (int r = ty; r < rows; r += tyc * U) {
+            const bool col_ok = c4 < cols4;
+            for (int r = ty; r < rows || !staged; r += tyc * U) {
                 float4 va[U], vb[U];
+                // 1. direct operands of this batch
                 #pragma unroll
                 for (int u = 0; u < U; ++u) {
                     const int row = r + u * tyc;
-                    if (row < rows) {
-                        va[u] = load_operand<MODE_A>(sm_a, abase, p.as1, row, col, p.a_stream);
-                        vb[u] = load_operand<MODE_B>(sm_b, bbase, p.bs1, row, col, p.b_stream);
+                    if (col_ok && row < rows) {
+                        if (MODE_A == AM_DIRECT) va[u] = load_operand<MODE_A>(sm_a, abase, p.as1, row, col, p.a_stream);
+                        if (MODE_B == AM_DIRECT) vb[u] = load_operand<MODE_B>(sm_b, bbase, p.bs1, row, col, p.b_stream);
                     }
                 }
+                // 2. stage the broadcast operand(s) once per tile (every thread reaches this point in its first batch)
+                if (!staged) {
+                    if (STAGE_A || STAGE_B) {
+                        __syncthreads();                 // readers of the previous tile are done
+                        if (STAGE_A) stage_operand<MODE_A>(sm_a, p.a + i0 * p.as0, p.as1, r0, c0, rows, cols4);
+                        if (STAGE_B) stage_operand<MODE_B>(sm_b, p.b + i0 * p.bs0, p.bs1, r0, c0, rows, cols4);
+                        __syncthreads();
+                    }
+                    staged = true;
+                }
+                // 3. staged operands, arithmetic, store
                 #pragma unroll
                 for (int u = 0; u < U; ++u) {
                     const int row = r + u * tyc;
-                    if (row < rows)
+                    if (col_ok && row < rows) {
+                        if (MODE_A != AM_DIRECT) va[u] = load_operand<MODE_A>(sm_a, abase, p.as1, row, col, 0);
+                        if (MODE_B != AM_DIRECT) vb[u] = load_operand<MODE_B>(sm_b, bbase, p.bs1, row, col, 0);
                         st_stream(reinterpret_cast<float4*>(obase + (int64_t)row * p.D2 + col), apply2(f, va[u], vb[u]));
+                    }
                 }
             }
         }

@@ -33,14 +33,16 @@ __device__ __forceinline__ float jmin(float a, float b) {
 }
 
 // ---- transcendental functions -----------------------------------------------------
-// Reference path: evaluate in double and narrow once, exactly as the JVM does.
-__device__ __forceinline__ float exp_ref(float x)  { return (float)exp((double)x); }
+// Reference path: evaluate in double and narrow once, exactly as the JVM does.  Kept out
+// of line: these are the rarely taken slow paths of the float-only functions below, and
+// inlining them into every unrolled element blows up the instruction footprint.
+static __device__ __noinline__ float exp_ref(float x)  { return (float)exp((double)x); }
 __device__ __forceinline__ float log_ref(float x)  { return (float)log((double)x); }
 __device__ __forceinline__ float tanh_ref(float x) { return (float)tanh((double)x); }
 
 // Math.pow differs from C99 pow in two corners: a NaN exponent gives NaN even
 // for base 1, and |base| == 1 with an infinite exponent gives NaN.
-__device__ __forceinline__ float pow_ref(float x, float y) {
+static __device__ __noinline__ float pow_ref(float x, float y) {
     if (y == 0.0f) return 1.0f;
     if (y != y || x != x) return CUDART_NAN_F;
     if (isinf(y) && fabsf(x) == 1.0f) return CUDART_NAN_F;

@@ -150,15 +150,19 @@ __global__ void __launch_bounds__(256) k_rows_small(const float* __restrict__ in
     if (row < outer) {
         const float* p = in + row * A;
         constexpr int U = 8;
-        for (int64_t j = lane_in_group; j < A; j += (int64_t)G * U) {
+        int64_t j = lane_in_group;
+        for (; j + (int64_t)G * (U - 1) < A; j += (int64_t)G * U) {      // full batches: all loads first, no guards
             float v[U];
             #pragma unroll
-            for (int u = 0; u < U; ++u) { const int64_t jj = j + (int64_t)u * G; if (jj < A) v[u] = __ldg(p + jj); }
+            for (int u = 0; u < U; ++u) v[u] = __ldg(p + j + (int64_t)u * G);
             acc.begin();
             #pragma unroll
-            for (int u = 0; u < U; ++u) { const int64_t jj = j + (int64_t)u * G; if (jj < A) acc.add(v[u], (int)jj); }
+            for (int u = 0; u < U; ++u) acc.add(v[u], (int)(j + (int64_t)u * G));
             acc.end();
         }
+        acc.begin();
+        for (; j < A; j += G) acc.add(__ldg(p + j), (int)j);              // at most U - 1 values
+        acc.end();
     }
     #pragma unroll
     for (int off = G >> 1; off > 0; off >>= 1) acc.shfl_merge(0xffffffffu, off);
@@ -189,25 +193,33 @@ __global__ void __launch_bounds__(256) k_rows_warp(const float* __restrict__ in,
     if (VEC == 4) {
         const float4* p4 = reinterpret_cast<const float4*>(p);
         const int64_t q1 = j1 >> 2;
-        for (int64_t q = (j0 >> 2) + lane; q < q1; q += 32 * U) {
+        int64_t q = (j0 >> 2) + lane;
+        for (; q + 32 * (U - 1) < q1; q += 32 * U) {                       // full batches: all loads first, no guards
             float4 v[U];
             #pragma unroll
-            for (int u = 0; u < U; ++u) { const int64_t k = q + 32 * u; if (k < q1) v[u] = __ldcs(p4 + k); }
+            for (int u = 0; u < U; ++u) v[u] = __ldcs(p4 + q + 32 * u);
             acc.begin();
             #pragma unroll
-            for (int u = 0; u < U; ++u) { const int64_t k = q + 32 * u; if (k < q1) acc.add4(v[u], (int)(k << 2)); }
+            for (int u = 0; u < U; ++u) acc.add4(v[u], (int)((q + 32 * u) << 2));
             acc.end();
         }
+        acc.begin();
+        for (; q < q1; q += 32) acc.add4(__ldcs(p4 + q), (int)(q << 2));   // at most U - 1 vectors
+        acc.end();
     } else {
-        for (int64_t j = j0 + lane; j < j1; j += 32 * U) {
+        int64_t j = j0 + lane;
+        for (; j + 32 * (U - 1) < j1; j += 32 * U) {
             float v[U];
             #pragma unroll
-            for (int u = 0; u < U; ++u) { const int64_t k = j + 32 * u; if (k < j1) v[u] = __ldg(p + k); }
+            for (int u = 0; u < U; ++u) v[u] = __ldg(p + j + 32 * u);
             acc.begin();
             #pragma unroll
-            for (int u = 0; u < U; ++u) { const int64_t k = j + 32 * u; if (k < j1) acc.add(v[u], (int)k); }
+            for (int u = 0; u < U; ++u) acc.add(v[u], (int)(j + 32 * u));
             acc.end();
         }
+        acc.begin();
+        for (; j < j1; j += 32) acc.add(__ldg(p + j), (int)j);
+        acc.end();
     }
     #pragma unroll
     for (int off = 16; off > 0; off >>= 1) acc.shfl_merge(0xffffffffu, off);
@@ -254,29 +266,45 @@ __global__ void __launch_bounds__(256) k_cols_warp(const float* __restrict__ in,
     if (c < inner) {
         const float* p = in + o * A * inner + c;
         constexpr int U = 8;
-        for (int64_t j = j0 + tyw; j < j1; j += (int64_t)TYW * U) {
-            if (VEC == 4) {
+        const int64_t step = (int64_t)TYW * inner;            // floats between this lane's consecutive rows
+        int64_t j = j0 + tyw;
+        const float* pj = p + j * inner;
+        if (VEC == 4) {
+            for (; j + (int64_t)TYW * (U - 1) < j1; j += (int64_t)TYW * U, pj += step * U) {   // full batches, no guards
                 float4 v[U];
                 #pragma unroll
-                for (int u = 0; u < U; ++u) { const int64_t jj = j + (int64_t)u * TYW; if (jj < j1) v[u] = __ldcs(reinterpret_cast<const float4*>(p + jj * inner)); }
+                for (int u = 0; u < U; ++u) v[u] = __ldcs(reinterpret_cast<const float4*>(pj + step * u));
                 #pragma unroll
                 for (int k = 0; k < VEC; ++k) acc[k].begin();
                 #pragma unroll
                 for (int u = 0; u < U; ++u) {
-                    const int64_t jj = j + (int64_t)u * TYW;
-                    if (jj < j1) { acc[0].add(v[u].x, (int)jj); acc[1 % VEC].add(v[u].y, (int)jj); acc[2 % VEC].add(v[u].z, (int)jj); acc[3 % VEC].add(v[u].w, (int)jj); }
+                    const int jj = (int)(j + (int64_t)u * TYW);
+                    acc[0].add(v[u].x, jj); acc[1 % VEC].add(v[u].y, jj); acc[2 % VEC].add(v[u].z, jj); acc[3 % VEC].add(v[u].w, jj);
                 }
                 #pragma unroll
                 for (int k = 0; k < VEC; ++k) acc[k].end();
-            } else {
+            }
+            #pragma unroll
+            for (int k = 0; k < VEC; ++k) acc[k].begin();
+            for (; j < j1; j += TYW, pj += step) {
+                const float4 v = __ldcs(reinterpret_cast<const float4*>(pj));
+                acc[0].add(v.x, (int)j); acc[1 % VEC].add(v.y, (int)j); acc[2 % VEC].add(v.z, (int)j); acc[3 % VEC].add(v.w, (int)j);
+            }
+            #pragma unroll
+            for (int k = 0; k < VEC; ++k) acc[k].end();
+        } else {
+            for (; j + (int64_t)TYW * (U - 1) < j1; j += (int64_t)TYW * U, pj += step * U) {
                 float v[U];
                 #pragma unroll
-                for (int u = 0; u < U; ++u) { const int64_t jj = j + (int64_t)u * TYW; if (jj < j1) v[u] = __ldg(p + jj * inner); }
+                for (int u = 0; u < U; ++u) v[u] = __ldg(pj + step * u);
                 acc[0].begin();
                 #pragma unroll
-                for (int u = 0; u < U; ++u) { const int64_t jj = j + (int64_t)u * TYW; if (jj < j1) acc[0].add(v[u], (int)jj); }
+                for (int u = 0; u < U; ++u) acc[0].add(v[u], (int)(j + (int64_t)u * TYW));
                 acc[0].end();
             }
+            acc[0].begin();
+            for (; j < j1; j += TYW, pj += step) acc[0].add(__ldg(pj), (int)j);
+            acc[0].end();
         }
     }
     for (int off = TX; off < 32; off <<= 1) {            // merge the row groups (all lanes take part)
@@ -387,7 +415,7 @@ static Plan make_plan(Device* d, const float* in, int64_t outer, int64_t A, int6
     p.col_tiles = ceil_div(lanes_needed, tx);
     // a warp streams about reduce_cols_item_kb; the partial traffic must stay under ~3 % of the input
     const int64_t row_bytes = (int64_t)tx * p.vec * 4;
-    int64_t seg = tune("reduce_cols_item_kb", 64) * 1024 / row_bytes;
+    int64_t seg = tune("reduce_cols_item_kb", 32) * 1024 / row_bytes;
     const int64_t min_seg = (int64_t)partial_bytes * 8;           // S * partial_bytes <= A * 4 / 32
     if (seg < min_seg) seg = min_seg;
     if (A > seg + seg / 2) { p.S = (int)ceil_div(A, seg); p.seg_len = seg; }

@@ -1,0 +1,106 @@
+"""Batch-leading data parallelism for the hot path: one process per GPU, each owning a
+contiguous block of rows of the leading dimension.
+
+The reference has no multi-device execution (a tensor lives on exactly one platform,
+kten-api/.../tensor/Tensor.kt:143); what shards here is the path itself:
+
+  * elementwise ops whose small operand has leading extent 1 (or lower rank) and
+    reductions over a non-leading axis need no communication: replicate the small
+    operand, work on the local rows;
+  * full reductions and sum-to-shape over the leading axis (the loss and the weight /
+    bias gradients) leave one partial per rank; the partials are packed into one
+    buffer and summed in place with a single all-reduce.
+
+`ShardedSigmoidGraph` is the sharded autograd step of the benchmark configuration
+"x[262144,1024], w[1,1024], b[1024]: loss = sum(sigmoid(x*w + b) pow 2)", issued as the
+same raw-tensor call sequence kten's autograd issues (kten_b200.autograd), generic over
+the backend so that it runs on the CUDA backend and, in tests, on a CPU backend.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Sequence, Tuple
+
+import numpy as np
+
+from . import autograd as AG
+
+
+def shard_rows(n_rows: int, world: int, rank: int) -> Tuple[int, int]:
+    """(first row, row count) of `rank`'s block: equal contiguous blocks, the first
+    n_rows % world ranks take one extra row."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"rank {rank} of {world}")
+    base, extra = divmod(n_rows, world)
+    count = base + (1 if rank < extra else 0)
+    first = rank * base + min(rank, extra)
+    return first, count
+
+
+class NcclCollective:
+    """Sum small raw tensors across ranks: pack -> one in-place all-reduce on the
+    device's compute stream -> unpack (ktc_allreduce_sum)."""
+
+    def __init__(self, ops, comm: int):
+        self.ops, self.comm = ops, comm
+        self._packed = None
+
+    def allreduce_sum(self, raws: Sequence) -> None:
+        from . import _lib as L
+        lib = self.ops.lib
+        total = sum(r.size for r in raws)
+        if self._packed is None or self._packed.size < total:
+            if self._packed is not None:
+                self._packed.release()
+            self._packed = self.ops.createRaw([total])
+            self._packed.mustSurviveGC = True
+        off = 0
+        for r in raws:
+            L.check(lib.ktc_d2d(self._packed.storeReference, off, r.storeReference, 0, r.size)); off += r.size
+        L.check(lib.ktc_allreduce_sum(self.comm, self._packed.storeReference, 0, total))
+        off = 0
+        for r in raws:
+            L.check(lib.ktc_d2d(r.storeReference, 0, self._packed.storeReference, off, r.size)); off += r.size
+
+
+class LocalCollective:
+    """World size 1: nothing to exchange."""
+
+    def allreduce_sum(self, raws: Sequence) -> None:
+        return None
+
+
+class ShardedSigmoidGraph:
+    """loss = sum(sigmoid(x*w + b) pow 2) with x sharded by rows; backward gives the
+    gradients of w ([1, C], via sum(0, keepDims)) and b ([C], via sum(0)); loss, gw
+    and gb are then summed over the ranks.  `fused_unexpand` uses the backend's one-call
+    sum-to-shape instead of the chain of axis sums."""
+
+    def __init__(self, ops, x_raw, w_raw, b_raw, collective=None):
+        self.ops = ops
+        self.x = AG.NoGradVariable(ops, x_raw)
+        self.w = AG.Variable(ops, w_raw)
+        self.b = AG.Variable(ops, b_raw)
+        self.collective = collective or LocalCollective()
+
+    def step(self):
+        """One forward + backward + exchange.  Returns raw tensors (loss [1], grad w
+        [1, C], grad b [C]) holding the global sums; valid until the next step."""
+        self.w.zeroGrad()
+        self.b.zeroGrad()
+        loss = ((self.x * self.w + self.b).sigmoid().pow(2.0)).sum()
+        loss.forward()                                  # keeps the loss value across backward()
+        loss.backward()
+        out = [loss.getRawValue(), self.w.gradient, self.b.gradient]
+        self.collective.allreduce_sum(out)
+        self._last_loss_fn = loss
+        return out
+
+    def release_step(self):
+        """Drop the graph of the last step (its retained loss value)."""
+        fn = getattr(self, "_last_loss_fn", None)
+        if fn is not None:
+            fn.keepOutput = False
+            fn.freeOutput = True
+            fn.releaseUnusedInGraph()
+            self._last_loss_fn = None

@@ -403,6 +403,62 @@ def test_config1_plumbing_graph(cuda_ops, gc_scope):
     assert np.all(np.abs(r.astype(np.float64) - ro) <= RED_RTOL * sq64.sum(axis=2))
 
 
+def test_config5_sharded_graph_on_one_gpu(cuda_ops, gc_scope):
+    """loss = sum(sigmoid(x*w + b) pow 2) with gradients for w [1,C] and b [C] (sum-to-shape over
+    the leading axis); whole tensor vs two row shards summed, vs the CPU oracle running the same
+    call sequence, vs float64 ground truth."""
+    from kten_b200.sharded import ShardedSigmoidGraph, shard_rows
+    rows, cols = 2048, 1024
+    x = D.uniform(rows * cols, 0, -1.0, 1.0, stream=0)
+    w = D.normal(cols, 0, 0.0, 0.02, stream=1)
+    b = D.uniform(cols, 0, -0.1, 0.1, stream=2)
+
+    def run(ops, xs, n, fused=False):
+        g = ShardedSigmoidGraph(ops, ops.createRaw([n, cols], xs), ops.createRaw([1, cols], w), ops.createRaw([cols], b))
+        loss, gw, gb = g.step()
+        return float(loss.toArray()[0]), gw.toArray().reshape(-1).astype(np.float64), gb.toArray().astype(np.float64)
+
+    loss, gw, gb = run(cuda_ops, x, rows)
+    parts = [run(cuda_ops, x[f * cols:(f + c) * cols], c) for f, c in (shard_rows(rows, 2, r) for r in range(2))]
+    lo, gwo, gbo = run(O.OracleTensorOperations(1), x, rows)
+    X = x.reshape(rows, cols).astype(np.float64)
+    s = 1.0 / (1.0 + np.exp(-(X * w + b)))
+    g = 2 * s * s * (1 - s)
+    for got_loss, got_gw, got_gb in ((loss, gw, gb), (parts[0][0] + parts[1][0], parts[0][1] + parts[1][1], parts[0][2] + parts[1][2])):
+        assert abs(got_loss - (s * s).sum()) <= RED_RTOL * (s * s).sum()
+        assert abs(got_loss - lo) <= RED_RTOL * (s * s).sum()
+        assert np.all(np.abs(got_gb - g.sum(axis=0)) <= RED_RTOL * np.abs(g).sum(axis=0))
+        assert np.all(np.abs(got_gw - (g * X).sum(axis=0)) <= RED_RTOL * np.abs(g * X).sum(axis=0))
+        assert np.all(np.abs(got_gb - gbo) <= RED_RTOL * np.abs(g).sum(axis=0))
+        assert np.all(np.abs(got_gw - gwo) <= RED_RTOL * np.abs(g * X).sum(axis=0))
+
+
+def test_single_rank_communicator_and_injected_failure(cuda_ops, gc_scope):
+    """A one-rank communicator exercises the collective wrapper on one GPU: the all-reduce
+    is the identity; a failure injected on the host is reported as KTC_ECOMM (nothing on the
+    GPU is made to fail) and the next call works again."""
+    lib = cuda_ops.lib
+    ident = C.create_string_buffer(L.COMM_ID_BYTES)
+    L.check(lib.ktc_comm_unique_id(ident))
+    comm = C.c_uint64(0)
+    L.check(lib.ktc_comm_init_rank(0, 1, 0, ident.raw, C.byref(comm)))
+    try:
+        x = D.uniform(2049, 3, -1.0, 1.0)
+        r = cuda_ops.createRaw([2049], x)
+        L.check(lib.ktc_allreduce_sum(comm.value, r.storeReference, 0, 2049))
+        assert same_bits(r.toArray(), x)
+        L.check(lib.ktc_test_inject_comm_error(1))
+        assert lib.ktc_allreduce_sum(comm.value, r.storeReference, 0, 2049) == L.KTC_ECOMM
+        assert b"injected" in lib.ktc_last_error()
+        L.check(lib.ktc_allreduce_sum(comm.value, r.storeReference, 1, 2048))
+        assert same_bits(r.toArray(), x)
+        assert lib.ktc_allreduce_sum(comm.value, r.storeReference, 2, 2048) == L.KTC_EINVAL      # range outside the buffer
+        assert lib.ktc_allreduce_sum(comm.value + 7, r.storeReference, 0, 1) == L.KTC_ESTATE
+    finally:
+        L.check(lib.ktc_test_inject_comm_error(0))
+        L.check(lib.ktc_comm_destroy(comm.value))
+
+
 # --------------------------------------------------------------------------------------
 # runtime behaviour: handles, pool, transfers, errors
 # --------------------------------------------------------------------------------------
