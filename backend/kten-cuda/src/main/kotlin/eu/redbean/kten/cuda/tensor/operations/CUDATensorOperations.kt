@@ -1,0 +1,134 @@
+package eu.redbean.kten.cuda.tensor.operations
+
+import eu.redbean.kten.api.autograd.tensor.NoGradVariable
+import eu.redbean.kten.api.autograd.tensor.Variable
+import eu.redbean.kten.api.autograd.utils.toStoreSize
+import eu.redbean.kten.api.tensor.Tensor
+import eu.redbean.kten.api.tensor.operations.TensorOperations
+import eu.redbean.kten.api.tensor.operations.TensorOperationsGarbageCollector
+import eu.redbean.kten.api.tensor.operations.nn.BatchNormOperation
+import eu.redbean.kten.api.tensor.operations.nn.ConvolutionOperation
+import eu.redbean.kten.api.tensor.operations.nn.PoolingOperation
+import eu.redbean.kten.api.tensor.operations.nn.PoolingOptions
+import eu.redbean.kten.api.tensor.operations.nn.Upsample2DOperation
+import eu.redbean.kten.api.tensor.operations.nn.UpsampleType
+import eu.redbean.kten.api.tensor.serialization.CommonSerializableTensorDescriptor
+import eu.redbean.kten.api.tensor.serialization.SerializableTensorData
+import eu.redbean.kten.api.tensor.store.AbstractRawTensor
+import eu.redbean.kten.cuda.tensor.platform.KtcNative
+import eu.redbean.kten.cuda.tensor.platform.KtcNative.check
+import eu.redbean.kten.cuda.tensor.store.CUDABuffer
+import eu.redbean.kten.cuda.tensor.store.CUDARawTensor
+import java.lang.foreign.Arena
+import java.lang.foreign.ValueLayout.JAVA_FLOAT
+import java.lang.foreign.ValueLayout.JAVA_LONG
+import java.util.Random
+
+/**
+ * TensorOperations of one CUDA device.  Reference counting and the scoped garbage collector follow
+ * the OpenCL backend (OCLTensorOperations.kt:72-94): raw tensors created while a scope is open are
+ * released when it closes unless their reference count was raised or they were marked to survive.
+ */
+class CUDATensorOperations(override val platformKey: String, val device: Int) : TensorOperations<CUDARawTensor> {
+
+    private val collector = ThreadLocal<MutableList<CUDARawTensor>?>()
+
+    internal fun instanceCreated(raw: CUDARawTensor) {
+        collector.get()?.add(raw)
+    }
+
+    override fun garbageCollector(): TensorOperationsGarbageCollector {
+        if (collector.get() != null) return TensorOperationsGarbageCollector { }        // nested scopes are no-ops
+        collector.set(mutableListOf())
+        return TensorOperationsGarbageCollector {
+            val created = collector.get()
+            collector.set(null)
+            created?.forEach { it.release() }
+        }
+    }
+
+    override fun createRaw(shape: List<Int>): CUDARawTensor {
+        Arena.ofConfined().use { arena ->
+            val out = arena.allocate(JAVA_LONG)
+            check(KtcNative.alloc.invokeExact(device, shape.toStoreSize().toLong(), out) as Int)
+            return CUDARawTensor(shape, CUDABuffer(out.get(JAVA_LONG, 0), shape.toStoreSize()), this)
+        }
+    }
+
+    override fun createRaw(shape: List<Int>, init: (Int) -> Float): CUDARawTensor {
+        val raw = createRaw(shape)
+        upload(raw, FloatArray(shape.toStoreSize(), init))
+        return raw
+    }
+
+    override fun createRawFill(shape: List<Int>, constant: Float): CUDARawTensor = createRaw(shape).also { it.inplaceFill(constant) }
+
+    internal fun upload(raw: CUDARawTensor, data: FloatArray) {
+        if (data.isEmpty()) return
+        Arena.ofConfined().use { arena ->
+            val host = arena.allocateFrom(JAVA_FLOAT, *data)
+            check(KtcNative.h2d.invokeExact(raw.storeReference.handle, 0L, host, data.size.toLong(), 1) as Int)
+        }
+    }
+
+    override fun create(shape: List<Int>, requiresGrad: Boolean, init: (Int) -> Float): Tensor = wrap(createRaw(shape, init), requiresGrad)
+
+    override fun createRandom(shape: List<Int>, requiresGrad: Boolean): Tensor {
+        val rnd = Random()
+        return wrap(createRaw(shape) { rnd.nextGaussian().toFloat() }, requiresGrad)
+    }
+
+    override fun createBernoulli(shape: List<Int>, rate: Float, requiresGrad: Boolean): Tensor {
+        val rnd = Random()
+        return wrap(createRaw(shape) { if (rnd.nextFloat() < rate) 1.0f else 0.0f }, requiresGrad)
+    }
+
+    @Suppress("UNCHECKED_CAST")
+    private fun wrap(raw: CUDARawTensor, requiresGrad: Boolean): Tensor {
+        val ops = this as TensorOperations<AbstractRawTensor<Any>>
+        return if (requiresGrad) Variable(ops, raw as AbstractRawTensor<Any>) else NoGradVariable(ops, raw as AbstractRawTensor<Any>)
+    }
+
+    override fun release(vararg rawTensors: AbstractRawTensor<Any>) = rawTensors.forEach { (it as AbstractRawTensor<*> as CUDARawTensor).release() }
+    override fun incrementRef(rawTensor: CUDARawTensor) { rawTensor.refCount++ }
+    override fun markSurviveGC(rawTensor: AbstractRawTensor<Any>) { (rawTensor as AbstractRawTensor<*> as CUDARawTensor).mustSurviveGC = true }
+    override fun markReleasableInGC(rawTensor: AbstractRawTensor<Any>) { (rawTensor as AbstractRawTensor<*> as CUDARawTensor).mustSurviveGC = false }
+    override fun zerosLike(rawTensor: CUDARawTensor): CUDARawTensor = createRawFill(rawTensor.shape, 0.0f)
+    override fun zeroOut(rawTensor: CUDARawTensor) = rawTensor.inplaceFill(0.0f)
+    override fun pow(constant: Float, rawTensor: CUDARawTensor): CUDARawTensor = rawTensor.scalar(KtcNative.POW, constant, scalarFirst = true)
+
+    override fun toSerializableData(rawTensor: CUDARawTensor) = SerializableTensorData(rawTensor.shape, rawTensor.toFloatArray())
+
+    override fun fromCommonSerializable(commonDescriptor: CommonSerializableTensorDescriptor): Tensor {
+        val data = commonDescriptor.data
+        val value = createRaw(data.shape) { data.data[it] }
+        val grad = commonDescriptor.gradientData
+        @Suppress("UNCHECKED_CAST")
+        val ops = this as TensorOperations<AbstractRawTensor<Any>>
+        @Suppress("UNCHECKED_CAST")
+        return if (grad != null) Variable(ops, value as AbstractRawTensor<Any>, createRaw(grad.shape) { grad.data[it] } as AbstractRawTensor<Any>)
+        else NoGradVariable(ops, value as AbstractRawTensor<Any>)
+    }
+
+    // ---- dense contractions and nn layers are outside the float32 hot path this library covers -----------
+    private fun unsupported(name: String): Nothing = throw UnsupportedOperationException("$name is not provided by kten-cuda")
+
+    override fun concat(axis: Int, inputs: List<CUDARawTensor>): CUDARawTensor = unsupported("concat")
+    override fun gemm(addMatrix: CUDARawTensor, matrix1: CUDARawTensor, matrix2: CUDARawTensor, alpha: Float, beta: Float,
+                      transposeFirst: Boolean, transposeSecond: Boolean): CUDARawTensor = unsupported("gemm")
+    override fun gemv(addVector: CUDARawTensor, matrix: CUDARawTensor, vector: CUDARawTensor, alpha: Float, beta: Float,
+                      transposeMatrix: Boolean): CUDARawTensor = unsupported("gemv")
+    override fun gemmBatched(addTensor: CUDARawTensor, tensor1: CUDARawTensor, tensor2: CUDARawTensor, alpha: Float, beta: Float,
+                             transposeFirst: Boolean, transposeSecond: Boolean): CUDARawTensor = unsupported("gemmBatched")
+    override fun ger(vector1: CUDARawTensor, vector2: CUDARawTensor, matrix: CUDARawTensor, alpha: Float): CUDARawTensor = unsupported("ger")
+    override fun spatialConvolution(kernel: List<Int>, padding: List<Int>, stride: List<Int>, dilation: List<Int>): ConvolutionOperation<CUDARawTensor> = unsupported("spatialConvolution")
+    override fun spatialConvolutionTranspose(kernel: List<Int>, padding: List<Int>, stride: List<Int>, dilation: List<Int>,
+                                             outputPadding: List<Int>): ConvolutionOperation<CUDARawTensor> = unsupported("spatialConvolutionTranspose")
+    override fun volumetricConvolution(kernel: List<Int>, padding: List<Int>, stride: List<Int>, dilation: List<Int>): ConvolutionOperation<CUDARawTensor> = unsupported("volumetricConvolution")
+    override fun volumetricConvolutionTranspose(kernel: List<Int>, padding: List<Int>, stride: List<Int>, dilation: List<Int>,
+                                                outputPadding: List<Int>): ConvolutionOperation<CUDARawTensor> = unsupported("volumetricConvolutionTranspose")
+    override fun spatialPooling(kernel: List<Int>, padding: List<Int>, stride: List<Int>, dilation: List<Int>,
+                                options: PoolingOptions): PoolingOperation<CUDARawTensor> = unsupported("spatialPooling")
+    override fun batchNorm(axis: Int, momentum: Float, epsilon: Float, training: Boolean): BatchNormOperation<CUDARawTensor> = unsupported("batchNorm")
+    override fun upsample(upsampleType: UpsampleType, scale: Int): Upsample2DOperation<CUDARawTensor> = unsupported("upsample")
+}

@@ -1,0 +1,82 @@
+package eu.redbean.kten.cuda.tensor.platform
+
+import java.lang.foreign.Arena
+import java.lang.foreign.FunctionDescriptor
+import java.lang.foreign.Linker
+import java.lang.foreign.MemoryLayout
+import java.lang.foreign.MemorySegment
+import java.lang.foreign.SymbolLookup
+import java.lang.foreign.ValueLayout.ADDRESS
+import java.lang.foreign.ValueLayout.JAVA_FLOAT
+import java.lang.foreign.ValueLayout.JAVA_INT
+import java.lang.foreign.ValueLayout.JAVA_LONG
+import java.lang.invoke.MethodHandle
+import java.nio.file.Path
+
+/**
+ * Downcall handles for libkten_cuda.so (include/kten_cuda.h), one per entry point, plus the
+ * status-to-exception mapping.  The library path comes from the system property
+ * `kten.cuda.library` (default: `libkten_cuda.so` on java.library.path).
+ */
+internal object KtcNative {
+
+    const val PLUS = 0; const val MINUS = 1; const val TIMES = 2; const val DIV = 3; const val POW = 4
+    const val EXP = 0; const val LOG = 1; const val TANH = 2; const val SIGMOID = 3; const val RECIPROCAL = 4; const val NEG = 5
+    const val SUM = 0; const val MEAN = 1; const val MAX = 2; const val MIN = 3; const val ARGMAX = 4; const val ARGMIN = 5
+    const val LT = 0; const val LTE = 1; const val GT = 2; const val GTE = 3
+
+    private val linker: Linker = Linker.nativeLinker()
+    private val lookup: SymbolLookup = System.getProperty("kten.cuda.library")
+        ?.let { SymbolLookup.libraryLookup(Path.of(it), Arena.global()) }
+        ?: SymbolLookup.libraryLookup(System.mapLibraryName("kten_cuda"), Arena.global())
+
+    private fun handle(name: String, result: MemoryLayout?, vararg args: MemoryLayout): MethodHandle {
+        val symbol = lookup.find(name).orElseThrow { UnsatisfiedLinkError("libkten_cuda.so does not export $name") }
+        val descriptor = if (result == null) FunctionDescriptor.ofVoid(*args) else FunctionDescriptor.of(result, *args)
+        return linker.downcallHandle(symbol, descriptor)
+    }
+
+    val init = handle("ktc_init", JAVA_INT, ADDRESS)
+    val lastError = handle("ktc_last_error", ADDRESS)
+    val deviceInfo = handle("ktc_device_info", JAVA_INT, JAVA_INT, ADDRESS, JAVA_LONG, ADDRESS, ADDRESS)
+    val alloc = handle("ktc_alloc", JAVA_INT, JAVA_INT, JAVA_LONG, ADDRESS)
+    val retain = handle("ktc_retain", JAVA_INT, JAVA_LONG)
+    val release = handle("ktc_release", JAVA_INT, JAVA_LONG)
+    val poolStats = handle("ktc_pool_stats", JAVA_INT, JAVA_INT, ADDRESS, ADDRESS, ADDRESS, ADDRESS)
+    val poolLimit = handle("ktc_pool_limit", JAVA_INT, JAVA_INT, JAVA_LONG)
+    val h2d = handle("ktc_h2d", JAVA_INT, JAVA_LONG, JAVA_LONG, ADDRESS, JAVA_LONG, JAVA_INT)
+    val d2h = handle("ktc_d2h", JAVA_INT, ADDRESS, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_INT)
+    val d2d = handle("ktc_d2d", JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG)
+    val fill = handle("ktc_fill", JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_FLOAT)
+    val sync = handle("ktc_sync", JAVA_INT, JAVA_INT)
+    val binary = handle("ktc_binary", JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG)
+    val binaryBcast = handle("ktc_binary_bcast", JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_LONG, ADDRESS, JAVA_INT, JAVA_LONG, ADDRESS, JAVA_INT)
+    val binaryInplace = handle("ktc_binary_inplace", JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG)
+    val scalar = handle("ktc_scalar", JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_FLOAT, JAVA_LONG, JAVA_INT)
+    val scalarInplace = handle("ktc_scalar_inplace", JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_FLOAT, JAVA_LONG)
+    val unary = handle("ktc_unary", JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG)
+    val clamp = handle("ktc_clamp", JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_FLOAT, JAVA_FLOAT, JAVA_LONG)
+    val compareScalar = handle("ktc_compare_scalar", JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_FLOAT, JAVA_LONG)
+    val broadcastTo = handle("ktc_broadcast_to", JAVA_INT, JAVA_LONG, ADDRESS, JAVA_INT, JAVA_LONG, ADDRESS, JAVA_INT)
+    val reduceAxis = handle("ktc_reduce_axis", JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG)
+    val reduceAll = handle("ktc_reduce_all", JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG)
+    val scatterAxis = handle("ktc_scatter_axis", JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG)
+
+    /** KTC_EINVAL -> IllegalArgumentException, KTC_ESTATE -> IllegalStateException, KTC_ENOMEM -> OutOfMemoryError. */
+    fun check(status: Int) {
+        if (status == 0) return
+        val message = (lastError.invokeExact() as MemorySegment).reinterpret(1024).getString(0)
+        when (status) {
+            -1 -> throw IllegalArgumentException(message)
+            -2 -> throw IllegalStateException(message)
+            -3 -> throw OutOfMemoryError(message)
+            else -> throw RuntimeException("kten-cuda [$status]: $message")
+        }
+    }
+
+    fun shape(arena: Arena, shape: List<Int>): MemorySegment {
+        val seg = arena.allocate(JAVA_LONG, maxOf(1, shape.size).toLong())
+        shape.forEachIndexed { i, d -> seg.setAtIndex(JAVA_LONG, i.toLong(), d.toLong()) }
+        return seg
+    }
+}

@@ -402,6 +402,11 @@ def make_comm(lib, L, dist, rank, world, local):
 
 
 def run_gpu_arm(args):
+    # Libraries underneath (NCCL's version banner, for one) write to stdout; the contract is ONE
+    # JSON line there, so everything but that line goes to stderr.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
     rank, world, local, dist = init_distributed(args.gpus)
     from kten_b200 import _lib as L
     lib = L.load()
@@ -535,7 +540,8 @@ def run_gpu_arm(args):
                                     "sample": f"the same sweep on 2^{args.cpu_sample_log2}-element operands ({secs:.1f} s), CPU oracle in "
                                               "kten-jvm's structure (broadcast operands materialised, out-of-place maps single-threaded, "
                                               "in-place ops and axis aggregation on all host threads)"}
-        print(json.dumps(line))
+        sys.stdout.flush()
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
     if dist is not None:
         if comm is not None:
             lib.ktc_comm_destroy(comm)
@@ -614,6 +620,11 @@ def load_traffic(kernel: str):
 
 
 def main():
+    # torch.distributed.run exports OMP_NUM_THREADS=1; the host-side input generator and the CPU
+    # baseline are OpenMP code and should use this rank's share of the cores
+    world = int(os.environ.get("LOCAL_WORLD_SIZE", os.environ.get("WORLD_SIZE", "1")))
+    if world > 1 or "OMP_NUM_THREADS" not in os.environ:
+        os.environ["OMP_NUM_THREADS"] = str(max(1, (os.cpu_count() or 1) // world))
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)

@@ -31,41 +31,43 @@ template <class F> __device__ __forceinline__ float4 apply2(const F& f, float4 a
 }
 
 // ---- contiguous maps ---------------------------------------------------------
-// A CTA owns tiles of THREADS*U float4; the grid strides over tiles.  n4 is the
-// number of whole float4; the (< 4 element) remainder and unaligned buffers go
-// through the scalar kernel below.
+// One tile of kMapThreads * U float4 per CTA, CTAs in address order.  Each thread forms
+// its base pointers once; the U accesses are then fixed offsets from them.  n4 is the
+// number of whole float4; the (< 4 element) remainder and unaligned buffers go through
+// the scalar kernels below.
+constexpr int kMapThreads = 256;
+
 template <int U, class F>
-__global__ void __launch_bounds__(256) k_map1_vec(const float4* __restrict__ a, float4* __restrict__ out, int64_t n4, F f) {
-    const int64_t tile = (int64_t)blockDim.x * U;
-    for (int64_t base = (int64_t)blockIdx.x * tile; base < n4; base += (int64_t)gridDim.x * tile) {
-        const int64_t i0 = base + threadIdx.x;
+__global__ void __launch_bounds__(kMapThreads) k_map1_vec(const float4* __restrict__ a, float4* __restrict__ out, int64_t n4, F f) {
+    const int64_t base = (int64_t)blockIdx.x * (kMapThreads * U) + threadIdx.x;
+    const float4* pa = a + base;
+    float4* po = out + base;
+    if (base - threadIdx.x + kMapThreads * U <= n4) {              // whole tile: every load before the first use, no guards
         float4 va[U];
-        if (base + tile <= n4) {                                   // whole tile: every load before the first use, no guards
-            #pragma unroll
-            for (int u = 0; u < U; ++u) va[u] = ld_stream(a + i0 + (int64_t)u * blockDim.x);
-            #pragma unroll
-            for (int u = 0; u < U; ++u) st_stream(out + i0 + (int64_t)u * blockDim.x, apply1(f, va[u]));
-        } else {
-            for (int64_t i = i0; i < n4; i += blockDim.x) st_stream(out + i, apply1(f, ld_stream(a + i)));
-        }
+        #pragma unroll
+        for (int u = 0; u < U; ++u) va[u] = ld_stream(pa + u * kMapThreads);
+        #pragma unroll
+        for (int u = 0; u < U; ++u) st_stream(po + u * kMapThreads, apply1(f, va[u]));
+    } else {
+        for (int64_t i = base; i < n4; i += kMapThreads) st_stream(out + i, apply1(f, ld_stream(a + i)));
     }
 }
 
 template <int U, class F>
-__global__ void __launch_bounds__(256) k_map2_vec(const float4* __restrict__ a, const float4* __restrict__ b,
-                                                  float4* __restrict__ out, int64_t n4, F f) {
-    const int64_t tile = (int64_t)blockDim.x * U;
-    for (int64_t base = (int64_t)blockIdx.x * tile; base < n4; base += (int64_t)gridDim.x * tile) {
-        const int64_t i0 = base + threadIdx.x;
+__global__ void __launch_bounds__(kMapThreads) k_map2_vec(const float4* __restrict__ a, const float4* __restrict__ b,
+                                                          float4* __restrict__ out, int64_t n4, F f) {
+    const int64_t base = (int64_t)blockIdx.x * (kMapThreads * U) + threadIdx.x;
+    const float4* pa = a + base;
+    const float4* pb = b + base;
+    float4* po = out + base;
+    if (base - threadIdx.x + kMapThreads * U <= n4) {
         float4 va[U], vb[U];
-        if (base + tile <= n4) {
-            #pragma unroll
-            for (int u = 0; u < U; ++u) { va[u] = ld_stream(a + i0 + (int64_t)u * blockDim.x); vb[u] = ld_stream(b + i0 + (int64_t)u * blockDim.x); }
-            #pragma unroll
-            for (int u = 0; u < U; ++u) st_stream(out + i0 + (int64_t)u * blockDim.x, apply2(f, va[u], vb[u]));
-        } else {
-            for (int64_t i = i0; i < n4; i += blockDim.x) st_stream(out + i, apply2(f, ld_stream(a + i), ld_stream(b + i)));
-        }
+        #pragma unroll
+        for (int u = 0; u < U; ++u) { va[u] = ld_stream(pa + u * kMapThreads); vb[u] = ld_stream(pb + u * kMapThreads); }
+        #pragma unroll
+        for (int u = 0; u < U; ++u) st_stream(po + u * kMapThreads, apply2(f, va[u], vb[u]));
+    } else {
+        for (int64_t i = base; i < n4; i += kMapThreads) st_stream(out + i, apply2(f, ld_stream(a + i), ld_stream(b + i)));
     }
 }
 
@@ -93,7 +95,6 @@ __global__ void k_fill_scalar(float* __restrict__ out, int64_t n, float v) {
 static inline int grid_for(Device* d, int64_t items, int64_t per_block, int max_blocks_per_sm) {
     int64_t need = (items + per_block - 1) / per_block;
     int64_t cap = (int64_t)d->sm_count * max_blocks_per_sm;
-    if (max_blocks_per_sm <= 0) cap = 0x7fffffff;          // one tile per CTA, no grid-stride loop
     if (need < 1) need = 1;
     return (int)(need < cap ? need : cap);
 }
@@ -105,41 +106,41 @@ static inline int finish_launch(const char* what, int launches = 1) {
     return KTC_OK;
 }
 
+static inline int64_t map_tiles(int64_t n4, int U) { return (n4 + (int64_t)kMapThreads * U - 1) / ((int64_t)kMapThreads * U); }
+
 template <class F>
 static int run_map1(Device* d, float* out, const float* a, int64_t n, F f) {
     if (n <= 0) return KTC_OK;
-    const int threads = 256;
     if (aligned16(out) && aligned16(a) && n >= 4) {
         const int64_t n4 = n / 4;
         const int U = tune("map_unroll", 4);
-        const int bps = tune("map_blocks_per_sm", 0);
+        if (map_tiles(n4, 2) > 0x7fffffffLL) return fail(KTC_ENOTSUP, "tensor too large for one launch");
         int launches = 1;
-        if (U == 8)      k_map1_vec<8, F><<<grid_for(d, n4, threads * 8, bps), threads, 0, d->stream>>>((const float4*)a, (float4*)out, n4, f);
-        else if (U == 2) k_map1_vec<2, F><<<grid_for(d, n4, threads * 2, bps), threads, 0, d->stream>>>((const float4*)a, (float4*)out, n4, f);
-        else             k_map1_vec<4, F><<<grid_for(d, n4, threads * 4, bps), threads, 0, d->stream>>>((const float4*)a, (float4*)out, n4, f);
+        if (U == 8)      k_map1_vec<8, F><<<(int)map_tiles(n4, 8), kMapThreads, 0, d->stream>>>((const float4*)a, (float4*)out, n4, f);
+        else if (U == 2) k_map1_vec<2, F><<<(int)map_tiles(n4, 2), kMapThreads, 0, d->stream>>>((const float4*)a, (float4*)out, n4, f);
+        else             k_map1_vec<4, F><<<(int)map_tiles(n4, 4), kMapThreads, 0, d->stream>>>((const float4*)a, (float4*)out, n4, f);
         if (n & 3) { k_map1_scalar<F><<<1, 32, 0, d->stream>>>(a + n4 * 4, out + n4 * 4, n & 3, f); ++launches; }
         return finish_launch("map1", launches);
     }
-    k_map1_scalar<F><<<grid_for(d, n, threads, 16), threads, 0, d->stream>>>(a, out, n, f);
+    k_map1_scalar<F><<<grid_for(d, n, 256, 16), 256, 0, d->stream>>>(a, out, n, f);
     return finish_launch("map1(scalar)");
 }
 
 template <class F>
 static int run_map2(Device* d, float* out, const float* a, const float* b, int64_t n, F f) {
     if (n <= 0) return KTC_OK;
-    const int threads = 256;
     if (aligned16(out) && aligned16(a) && aligned16(b) && n >= 4) {
         const int64_t n4 = n / 4;
         const int U = tune("map_unroll", 4);
-        const int bps = tune("map_blocks_per_sm", 0);
+        if (map_tiles(n4, 2) > 0x7fffffffLL) return fail(KTC_ENOTSUP, "tensor too large for one launch");
         int launches = 1;
-        if (U == 8)      k_map2_vec<8, F><<<grid_for(d, n4, threads * 8, bps), threads, 0, d->stream>>>((const float4*)a, (const float4*)b, (float4*)out, n4, f);
-        else if (U == 2) k_map2_vec<2, F><<<grid_for(d, n4, threads * 2, bps), threads, 0, d->stream>>>((const float4*)a, (const float4*)b, (float4*)out, n4, f);
-        else             k_map2_vec<4, F><<<grid_for(d, n4, threads * 4, bps), threads, 0, d->stream>>>((const float4*)a, (const float4*)b, (float4*)out, n4, f);
+        if (U == 8)      k_map2_vec<8, F><<<(int)map_tiles(n4, 8), kMapThreads, 0, d->stream>>>((const float4*)a, (const float4*)b, (float4*)out, n4, f);
+        else if (U == 2) k_map2_vec<2, F><<<(int)map_tiles(n4, 2), kMapThreads, 0, d->stream>>>((const float4*)a, (const float4*)b, (float4*)out, n4, f);
+        else             k_map2_vec<4, F><<<(int)map_tiles(n4, 4), kMapThreads, 0, d->stream>>>((const float4*)a, (const float4*)b, (float4*)out, n4, f);
         if (n & 3) { k_map2_scalar<F><<<1, 32, 0, d->stream>>>(a + n4 * 4, b + n4 * 4, out + n4 * 4, n & 3, f); ++launches; }
         return finish_launch("map2", launches);
     }
-    k_map2_scalar<F><<<grid_for(d, n, threads, 16), threads, 0, d->stream>>>(a, b, out, n, f);
+    k_map2_scalar<F><<<grid_for(d, n, 256, 16), 256, 0, d->stream>>>(a, b, out, n, f);
     return finish_launch("map2(scalar)");
 }
 
@@ -255,15 +256,15 @@ __device__ __forceinline__ float4 load_operand(const float* sm, const float* til
 }
 
 // A thread owns one column group (4 floats) and the rows ty, ty + TYC, ... of the tile,
-// at most U = 8 of them per batch (a tile of 8192 floats is one batch).  The loads of the
+// at most U of them per batch (U = 8: a tile of 8192 floats is one batch; U = 4 for the
+// arithmetic-heavy functors, whose unrolled code would otherwise not fit the instruction cache).  The loads of the
 // full-size (DIRECT) operands are issued first, then the broadcast operand is staged in
 // shared memory, so the staging latency overlaps the main stream instead of preceding it.
-template <int MODE_A, int MODE_B, class F>
+template <int MODE_A, int MODE_B, int U, class F>
 __global__ void __launch_bounds__(256) k_bcast3(BcastArgs p, F f) {
     extern __shared__ __align__(16) float smem[];
     constexpr bool STAGE_A = (MODE_A == AM_SMEMROW || MODE_A == AM_ROWSCALAR);
     constexpr bool STAGE_B = (MODE_B == AM_SMEMROW || MODE_B == AM_ROWSCALAR);
-    constexpr int U = 8;
     const int sm_stride = max(p.cols_per_tile, (p.rows_per_tile + 3) & ~3);
     float* sm_a = smem;
     float* sm_b = smem + (STAGE_A ? sm_stride : 0);
@@ -348,9 +349,13 @@ __global__ void k_bcast_generic(const float* __restrict__ a, const float* __rest
 
 struct SelectB { __device__ __forceinline__ float operator()(float, float b) const { return b; } };
 
+template <class F> struct BatchRows { static constexpr int value = 8; };
+template <> struct BatchRows<BinOp<KTC_DIV>> { static constexpr int value = 4; };
+template <> struct BatchRows<BinOp<KTC_POW>> { static constexpr int value = 4; };
+
 template <int MA, int MB, class F>
 static void launch_bcast3_modes(Device* d, const BcastArgs& p, int grid, size_t smem, F f) {
-    k_bcast3<MA, MB, F><<<grid, 256, smem, d->stream>>>(p, f);
+    k_bcast3<MA, MB, BatchRows<F>::value, F><<<grid, 256, smem, d->stream>>>(p, f);
 }
 
 template <class F>

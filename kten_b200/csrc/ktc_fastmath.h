@@ -211,49 +211,107 @@ KF_FN bool kf_exp_cr(float x, float* out) {
     return true;
 }
 
-// log2(x) = zh + zl for a positive normal float x, relative error about 2^-35.
+// For the 64 equal slices (in bit-pattern space) of [sqrt(1/2), sqrt(2)): a float
+// approximation inv of 1/centre, and -log2(inv) split into a part with 16 fractional
+// bits (so that adding the exponent is exact) and a remainder.  The slice that contains
+// 1.0 has inv = 1 and log 0, which keeps full relative accuracy for arguments near 1.
+KF_TABLE float kf_log2_tab[64][4] = {
+    {1.406444073e+00f, -4.920501709e-01f, -2.014097618e-06f, 0.0f},
+    {1.391158223e+00f, -4.762878418e-01f, 1.327901259e-06f, 0.0f},
+    {1.376201153e+00f, -4.606933594e-01f, 2.002024303e-06f, 0.0f},
+    {1.361562133e+00f, -4.452667236e-01f, 3.904535788e-06f, 0.0f},
+    {1.347231388e+00f, -4.299926758e-01f, -4.980352514e-06f, 0.0f},
+    {1.333199143e+00f, -4.148864746e-01f, -5.821009381e-06f, 0.0f},
+    {1.319456220e+00f, -3.999481201e-01f, 4.638121482e-06f, 0.0f},
+    {1.305993676e+00f, -3.851470947e-01f, -8.164320775e-07f, 0.0f},
+    {1.292803168e+00f, -3.704986572e-01f, -3.981619557e-06f, 0.0f},
+    {1.279876351e+00f, -3.560028076e-01f, -1.630810061e-06f, 0.0f},
+    {1.267205477e+00f, -3.416442871e-01f, -6.188647149e-06f, 0.0f},
+    {1.254783034e+00f, -3.274383545e-01f, 4.264629183e-07f, 0.0f},
+    {1.242601871e+00f, -3.133697510e-01f, 5.618730484e-06f, 0.0f},
+    {1.230654836e+00f, -2.994232178e-01f, -2.965130307e-06f, 0.0f},
+    {1.218935490e+00f, -2.856292725e-01f, 7.496968919e-06f, 0.0f},
+    {1.207437158e+00f, -2.719421387e-01f, -5.965723631e-06f, 0.0f},
+    {1.196153641e+00f, -2.584075928e-01f, 4.883414931e-06f, 0.0f},
+    {1.185079217e+00f, -2.449798584e-01f, -3.641308467e-06f, 0.0f},
+    {1.174207807e+00f, -2.316894531e-01f, 1.699700533e-06f, 0.0f},
+    {1.163534164e+00f, -2.185211182e-01f, 7.545471362e-06f, 0.0f},
+    {1.153052807e+00f, -2.054595947e-01f, 1.008499908e-06f, 0.0f},
+    {1.142758608e+00f, -1.925201416e-01f, -5.445261309e-07f, 0.0f},
+    {1.132646561e+00f, -1.797027588e-01f, 5.016535397e-06f, 0.0f},
+    {1.122711897e+00f, -1.669921875e-01f, 4.427387921e-06f, 0.0f},
+    {1.112949967e+00f, -1.543884277e-01f, -3.101126822e-07f, 0.0f},
+    {1.103356361e+00f, -1.418914795e-01f, -7.347497558e-06f, 0.0f},
+    {1.093926787e+00f, -1.295166016e-01f, 4.146417325e-07f, 0.0f},
+    {1.084656954e+00f, -1.172332764e-01f, -5.554975814e-06f, 0.0f},
+    {1.075542927e+00f, -1.050720215e-01f, 6.915106496e-06f, 0.0f},
+    {1.066580772e+00f, -9.298706055e-02f, -6.164886145e-06f, 0.0f},
+    {1.057766795e+00f, -8.102416992e-02f, 2.577019586e-06f, 0.0f},
+    {1.049097180e+00f, -6.915283203e-02f, 4.507653557e-06f, 0.0f},
+    {1.040568709e+00f, -5.737304688e-02f, 8.166411476e-07f, 0.0f},
+    {1.032177687e+00f, -4.568481445e-02f, -6.533868600e-06f, 0.0f},
+    {1.023920894e+00f, -3.410339355e-02f, -8.660022104e-07f, 0.0f},
+    {1.015795112e+00f, -2.261352539e-02f, 4.089034974e-06f, 0.0f},
+    {1.007797360e+00f, -1.119995117e-02f, -5.631608019e-06f, 0.0f},
+    {1.000000000e+00f, 0.000000000e+00f, 0.000000000e+00f, 0.0f},
+    {9.844690561e-01f, 2.258300781e-02f, -7.729166782e-07f, 0.0f},
+    {9.695550203e-01f, 4.460144043e-02f, 3.883708359e-06f, 0.0f},
+    {9.550861120e-01f, 6.629943848e-02f, -2.158190000e-06f, 0.0f},
+    {9.410427213e-01f, 8.766174316e-02f, 6.132098406e-06f, 0.0f},
+    {9.274063706e-01f, 1.087188721e-01f, 7.585754247e-06f, 0.0f},
+    {9.141595364e-01f, 1.294860840e-01f, -3.951134204e-06f, 0.0f},
+    {9.012857676e-01f, 1.499481201e-01f, -4.634119250e-06f, 0.0f},
+    {8.887696266e-01f, 1.701202393e-01f, -1.658355359e-06f, 0.0f},
+    {8.765962720e-01f, 1.900177002e-01f, -2.148657813e-06f, 0.0f},
+    {8.647519350e-01f, 2.096405029e-01f, 1.255120992e-06f, 0.0f},
+    {8.532233834e-01f, 2.290039062e-01f, 6.839393905e-07f, 0.0f},
+    {8.419982195e-01f, 2.481079102e-01f, 3.002194262e-06f, 0.0f},
+    {8.310645223e-01f, 2.669677734e-01f, -1.679887731e-07f, 0.0f},
+    {8.204112053e-01f, 2.855834961e-01f, -2.597690809e-06f, 0.0f},
+    {8.100274801e-01f, 3.039550781e-01f, 2.164606940e-06f, 0.0f},
+    {7.999033928e-01f, 3.220977783e-01f, 4.545512638e-06f, 0.0f},
+    {7.900292277e-01f, 3.400268555e-01f, -4.788461410e-06f, 0.0f},
+    {7.803958654e-01f, 3.577270508e-01f, -5.090421382e-06f, 0.0f},
+    {7.709946036e-01f, 3.752136230e-01f, -6.290585134e-06f, 0.0f},
+    {7.618171573e-01f, 3.924865723e-01f, -3.257308208e-06f, 0.0f},
+    {7.528555989e-01f, 4.095611572e-01f, -6.238404694e-06f, 0.0f},
+    {7.441024184e-01f, 4.264221191e-01f, 4.767879545e-06f, 0.0f},
+    {7.355504632e-01f, 4.430999756e-01f, 3.796841838e-06f, 0.0f},
+    {7.271928787e-01f, 4.595947266e-01f, -4.703207651e-06f, 0.0f},
+    {7.190230489e-01f, 4.758911133e-01f, -1.036580898e-06f, 0.0f},
+    {7.110347748e-01f, 4.920043945e-01f, 3.580488737e-06f, 0.0f}
+};
+
+// log2(x) = zh + zl for a positive normal float x; error about 2^-38 absolute, and
+// about 2^-33 relative when x is close to 1.  x = 2^e * m, m in [sqrt(1/2), sqrt(2));
+// r = m * inv - 1 is formed exactly as a float pair (|r| < 2^-6.9), ln(1 + r) needs
+// only a short polynomial, and everything larger than 2^-14 is carried exactly.
 KF_FN void kf_log2_ff(float x, float* zh, float* zl) {
     const int32_t ix = KF_F2I(x);
-    const int32_t e = (ix - 0x3f3504f3) >> 23;          // x = 2^e * m, m in [sqrt(1/2), sqrt(2))
+    const int32_t t = ix - 0x3f3504f3;
+    const int32_t e = t >> 23;
+    const int32_t j = (t >> 17) & 63;
     const float m = KF_I2F(ix - e * 0x00800000);
-    const float f = m - 1.0f;                           // exact
-    // s = f / (2 + f) as sh + sl
-    const float dh = 2.0f + f;
-    const float dl = f - (dh - 2.0f);                   // exact (|2| >= |f|)
-    const float inv = KF_RCP(dh);
-    const float sh = f * inv;
-    const float rem = fmaf(-sh, dh, f);                 // exact residual of the quotient
-    const float sl = (rem - sh * dl) * inv;
-    // ln(m) = 2s * (1 + s^2/3 + s^4 * Q(s^2)),  Q(t) = 1/5 + t/7 + t^2/9 + t^3/11 + t^4/13 + t^5/15
-    const float t = sh * sh;
-    float q = 6.6666666666666666e-2f;
-    q = fmaf(q, t, 7.6923076923076927e-2f);
-    q = fmaf(q, t, 9.0909090909090912e-2f);
-    q = fmaf(q, t, 1.1111111111111111e-1f);
-    q = fmaf(q, t, 1.4285714285714285e-1f);
-    q = fmaf(q, t, 0.2f);
-    const float tail = (t * t) * q;
-    // u = s^2 / 3 in float-float
-    const float s2l = fmaf(sh, sh, -t) + 2.0f * (sh * sl);
-    const float T_HI = 0.3333333432674407958984375f, T_LO = -9.934107462565104e-9f;   // 1/3 = T_HI + T_LO
-    const float uh = t * T_HI;
-    const float ul = fmaf(t, T_HI, -uh) + (t * T_LO + s2l * T_HI);
-    // w = 1 + u + tail
-    const float wh = 1.0f + uh;
-    const float wl = ((1.0f - wh) + uh) + (ul + tail);
-    // L = 2 * s * w  (natural log of m)
-    const float lh0 = sh * wh;
-    const float ll0 = fmaf(sh, wh, -lh0) + (sh * wl + sl * wh);
-    const float lh = 2.0f * lh0, ll = 2.0f * ll0;
+    const float inv = KF_TAB(kf_log2_tab, j, 0), thi = KF_TAB(kf_log2_tab, j, 1), tlo = KF_TAB(kf_log2_tab, j, 2);
+    const float p = m * inv;
+    const float rl = fmaf(m, inv, -p);                  // exact product error
+    const float rh = p - 1.0f;                          // exact
+    // ln(1 + rh + rl) - rh = rl * (1 - rh) + rh^2 * (-1/2 + rh/3 - rh^2/4 + rh^3/5 - rh^4/6)
+    float q = fmaf(rh, -1.6666666666666666e-1f, 0.2f);
+    q = fmaf(rh, q, -0.25f);
+    q = fmaf(rh, q, 3.3333333333333331e-1f);
+    q = fmaf(rh, q, -0.5f);
+    const float w = fmaf(rh * rh, q, fmaf(-rh, rl, rl));
     // times log2(e) = C_HI + C_LO
     const float C_HI = 1.44269502162933349609375f, C_LO = 1.9259629911266175e-8f;
-    const float ph = lh * C_HI;
-    const float pl = fmaf(lh, C_HI, -ph) + (lh * C_LO + ll * C_HI);
-    // plus the exponent (|e| >= 1 > |ph| or e == 0)
-    const float fe = KF_I2F(KF_MAGIC_BITS + e) - KF_MAGIC;       // (float)e without a conversion instruction
-    const float sh2 = fe + ph;
-    const float sl2 = ((fe - sh2) + ph) + pl;
-    *zh = sh2; *zl = sl2;
+    const float mh = rh * C_HI;
+    const float ml = fmaf(rh, C_HI, -mh);               // exact
+    const float low = (ml + tlo) + fmaf(w, C_HI, rh * C_LO);
+    // exponent + table value (exact), then the head of the product
+    const float a = (KF_I2F(KF_MAGIC_BITS + e) - KF_MAGIC) + thi;
+    const float s = a + mh;
+    const float se = (a - s) + mh;                      // exact: |a| >= |mh|, or a == 0
+    *zh = s; *zl = se + low;
 }
 
 // x^y, fast path for positive normal x, finite y, result comfortably inside the

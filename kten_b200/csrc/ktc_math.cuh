@@ -84,13 +84,21 @@ template <int OP> struct UnOp;
 template <> struct UnOp<KTC_EXP>  { __device__ __forceinline__ float operator()(float x) const { return exp_f(x); } };
 template <> struct UnOp<KTC_LOG>  { __device__ __forceinline__ float operator()(float x) const { return log_f(x); } };
 template <> struct UnOp<KTC_TANH> { __device__ __forceinline__ float operator()(float x) const { return tanh_f(x); } };
+// sigmoid = 1f / (1f + exp(-1f * x)) with the reference's own two IEEE operations after
+// the exp.  When e <= 1 (x >= 0) a one-ulp slip in e moves 1 + e by at most one ulp and
+// the quotient by less than three ulps before rounding, i.e. the result by at most 2 ulp;
+// when e > 1 the slip is amplified, so there e must be the correctly rounded value.  The
+// choice is made per warp (all 32 arguments non-negative -> the cheaper exp), so no warp
+// executes both paths.
 template <> struct UnOp<KTC_SIGMOID> {
     __device__ __forceinline__ float operator()(float x) const {
-        const float e = exp_cr(__fmul_rn(-1.0f, x));
-        return __fdiv_rn(1.0f, __fadd_rn(1.0f, e));
+        const float a = __fmul_rn(-1.0f, x);
+        const bool lean = __all_sync(__activemask(), x >= 0.0f);
+        const float e = lean ? exp_f(a) : exp_cr(a);
+        return __frcp_rn(__fadd_rn(1.0f, e));        // 1f / (1f + e): the IEEE reciprocal is the IEEE quotient
     }
 };
-template <> struct UnOp<KTC_RECIPROCAL> { __device__ __forceinline__ float operator()(float x) const { return __fdiv_rn(1.0f, x); } };
+template <> struct UnOp<KTC_RECIPROCAL> { __device__ __forceinline__ float operator()(float x) const { return __frcp_rn(x); } };
 template <> struct UnOp<KTC_NEG>  { __device__ __forceinline__ float operator()(float x) const { return -x; } };
 
 // tensor (op) constant and constant (op) tensor

@@ -245,18 +245,31 @@ __global__ void __launch_bounds__(256) k_rows_warp(const float* __restrict__ in,
 // warp-level load is TYW contiguous row pieces -- and the TYW row groups are merged
 // with shuffles at the end: no shared memory, no barrier.  Items are ordered with the
 // column tile fastest, then the segment, then o, i.e. in address order.
-template <int VEC, int OUT_KIND, bool SPLIT, class Acc>
+// MODE 0: final values (S == 1).  MODE 1: one Partial per segment.  MODE 2 (S % 8 == 0):
+// the eight warps of a CTA take eight consecutive segments of the same column tile and
+// leave ONE Partial per column, combined in warp order, at part[(seg / 8) * n_out + o].
+template <int VEC, int OUT_KIND, int MODE, class Acc>
 __global__ void __launch_bounds__(256) k_cols_warp(const float* __restrict__ in, float* __restrict__ out, float* __restrict__ out_idx,
                                                    typename Acc::Partial* __restrict__ part,
                                                    int64_t outer, int64_t A, int64_t inner, int S, int64_t seg_len,
                                                    int64_t col_tiles, int TX) {
-    const int lane = threadIdx.x & 31;
-    const int64_t item = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (item >= outer * S * col_tiles) return;           // whole warps leave together
-    const int64_t ct = item % col_tiles;
-    const int64_t rest = item / col_tiles;
-    const int seg = (int)(rest % S);
-    const int64_t o = rest / S;
+    __shared__ Acc sm[MODE == 2 ? 8 * 32 * VEC : 1];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int64_t ct, o; int seg;
+    if (MODE == 2) {
+        ct = blockIdx.x % col_tiles;
+        const int64_t rest = blockIdx.x / col_tiles;
+        const int SG = S >> 3;
+        seg = (int)(rest % SG) * 8 + warp;
+        o = rest / SG;
+    } else {
+        const int64_t item = (int64_t)blockIdx.x * 8 + warp;
+        if (item >= outer * S * col_tiles) return;       // whole warps leave together
+        ct = item % col_tiles;
+        const int64_t rest = item / col_tiles;
+        seg = (int)(rest % S);
+        o = rest / S;
+    }
     const int tx = lane & (TX - 1), tyw = lane / TX, TYW = 32 / TX;
     const int64_t c = (ct * TX + tx) * VEC;
     const int64_t j0 = (int64_t)seg * seg_len, j1 = min(A, j0 + seg_len);
@@ -270,6 +283,24 @@ __global__ void __launch_bounds__(256) k_cols_warp(const float* __restrict__ in,
         int64_t j = j0 + tyw;
         const float* pj = p + j * inner;
         if (VEC == 4) {
+            // four batches per fold into the double accumulators (32 values per float run)
+            for (; j + (int64_t)TYW * (4 * U - 1) < j1;) {
+                #pragma unroll
+                for (int k = 0; k < VEC; ++k) acc[k].begin();
+                #pragma unroll 1
+                for (int b = 0; b < 4; ++b, j += (int64_t)TYW * U, pj += step * U) {
+                    float4 v[U];
+                    #pragma unroll
+                    for (int u = 0; u < U; ++u) v[u] = __ldcs(reinterpret_cast<const float4*>(pj + step * u));
+                    #pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const int jj = (int)(j + (int64_t)u * TYW);
+                        acc[0].add(v[u].x, jj); acc[1 % VEC].add(v[u].y, jj); acc[2 % VEC].add(v[u].z, jj); acc[3 % VEC].add(v[u].w, jj);
+                    }
+                }
+                #pragma unroll
+                for (int k = 0; k < VEC; ++k) acc[k].end();
+            }
             for (; j + (int64_t)TYW * (U - 1) < j1; j += (int64_t)TYW * U, pj += step * U) {   // full batches, no guards
                 float4 v[U];
                 #pragma unroll
@@ -311,11 +342,24 @@ __global__ void __launch_bounds__(256) k_cols_warp(const float* __restrict__ in,
         #pragma unroll
         for (int k = 0; k < VEC; ++k) acc[k].shfl_merge(0xffffffffu, off);
     }
-    if (tyw == 0 && c < inner) {
+    if (MODE == 2) {
+        #pragma unroll
+        for (int k = 0; k < VEC; ++k) sm[(warp * 32 + lane) * VEC + k] = acc[k];
+        __syncthreads();
+        if (warp == 0 && tyw == 0 && c < inner) {
+            #pragma unroll
+            for (int k = 0; k < VEC; ++k) {
+                Acc r = sm[lane * VEC + k];
+                #pragma unroll
+                for (int w = 1; w < 8; ++w) { Acc other = sm[(w * 32 + lane) * VEC + k]; r.merge(other); }
+                part[(int64_t)(seg >> 3) * (outer * inner) + o * inner + c + k] = r.partial();
+            }
+        }
+    } else if (tyw == 0 && c < inner) {
         #pragma unroll
         for (int k = 0; k < VEC; ++k) {
             const int64_t oidx = o * inner + c + k;
-            if (SPLIT) part[(int64_t)seg * (outer * inner) + oidx] = acc[k].partial();
+            if (MODE == 1) part[(int64_t)seg * (outer * inner) + oidx] = acc[k].partial();
             else Finish<OUT_KIND, Acc>::put(acc[k], out, out_idx, oidx, A);
         }
     }
@@ -407,7 +451,7 @@ static Plan make_plan(Device* d, const float* in, int64_t outer, int64_t A, int6
         return p;
     }
     p.kind = 2;
-    const bool vec_ok = (inner % 4 == 0) && aligned16(in);
+    const bool vec_ok = (inner % 4 == 0) && aligned16(in);   // every row start is then 16-byte aligned
     p.vec = vec_ok ? 4 : 1;
     const int64_t lanes_needed = ceil_div(inner, p.vec);
     int tx = 1; while (tx < 32 && tx < lanes_needed) tx <<= 1;
@@ -420,7 +464,11 @@ static Plan make_plan(Device* d, const float* in, int64_t outer, int64_t A, int6
     if (seg < min_seg) seg = min_seg;
     if (A > seg + seg / 2) { p.S = (int)ceil_div(A, seg); p.seg_len = seg; }
     p.S_out = p.S;
-    p.grid = ceil_div(outer * p.S * p.col_tiles, 8);
+    if (p.S >= 16) {                                              // eight segments per CTA, one partial per CTA and column
+        p.S = (p.S + 7) & ~7;
+        p.S_out = p.S / 8;
+        p.grid = outer * p.S_out * p.col_tiles;
+    } else p.grid = ceil_div(outer * p.S * p.col_tiles, 8);
     return p;
 }
 
@@ -451,9 +499,10 @@ static int run_reduce(Device* d, float* out, float* out_idx, const float* in, in
         else            { if (mode == 0) KTC_RW(1, 0); else if (mode == 1) KTC_RW(1, 1); else KTC_RW(1, 2); }
 #undef KTC_RW
     } else {
-#define KTC_CW(V, SP) k_cols_warp<V, OUT_KIND, SP, Acc><<<grid, 256, 0, d->stream>>>(in, out, out_idx, part, outer, A, inner, p.S, p.seg_len, p.col_tiles, p.tx)
-        if (p.vec == 4) { if (p.S > 1) KTC_CW(4, true); else KTC_CW(4, false); }
-        else            { if (p.S > 1) KTC_CW(1, true); else KTC_CW(1, false); }
+        const int mode = p.S == 1 ? 0 : (p.S_out == p.S ? 1 : 2);
+#define KTC_CW(V, M) k_cols_warp<V, OUT_KIND, M, Acc><<<grid, 256, 0, d->stream>>>(in, out, out_idx, part, outer, A, inner, p.S, p.seg_len, p.col_tiles, p.tx)
+        if (p.vec == 4) { if (mode == 0) KTC_CW(4, 0); else if (mode == 1) KTC_CW(4, 1); else KTC_CW(4, 2); }
+        else            { if (mode == 0) KTC_CW(1, 0); else if (mode == 1) KTC_CW(1, 1); else KTC_CW(1, 2); }
 #undef KTC_CW
     }
     KTC_TRY(finish_launch(p.kind == 1 ? "rows_warp" : "cols_warp"));
