@@ -80,10 +80,13 @@ KTC_API const char* ktc_version(void);
  * ktc_alloc: createRaw(shape) (TOPS:16; OCLM lazy cl_mem + reuse pool OCLE:98-107,191-200).
  * ktc_retain / ktc_release: incrementRef / release (TOPS:22-28; OCLM:108-145).
  * ktc_wrap: adopt caller-owned device memory (not pooled, never freed here).
+ * ktc_view: a handle on a sub-range of a buffer (the slices of get / narrow, JVM:270-275, and the chunks
+ *           of a pipelined upload); it keeps the parent alive.
  * ktc_pool_limit: PlatformProvider.memoryUsageScaleHint (PlatformProvider.kt:12-40, OCLE:53-54).
  * ktc_pool_stats: PlatformMetricsProvider.getMetrics (PlatformMetricsProvider.kt:3-6, OCLE:89-96). */
 KTC_API int ktc_alloc(int dev, int64_t n_floats, ktc_buf* out);
 KTC_API int ktc_wrap(int dev, void* device_ptr, int64_t n_floats, ktc_buf* out);
+KTC_API int ktc_view(ktc_buf buf, int64_t off, int64_t n_floats, ktc_buf* out);   /* sub-range handle; holds a reference on `buf` */
 KTC_API int ktc_retain(ktc_buf buf);
 KTC_API int ktc_release(ktc_buf buf);
 KTC_API int ktc_refcount(ktc_buf buf, int* count);
@@ -101,13 +104,28 @@ KTC_API int ktc_host_free(float* p);
  * d2h: toSerializableData, getSingleValue, item() (TOPS:133; OCLM:189-207, 357-361).
  * d2d: copy(shallow=false) (JVM:257-262; CLBlastScopy at OCLM:242).
  * fill: createRawFill / zerosLike / zeroOut / inplaceFill (TOPS:18-26; kernels.cl:73-76).
- * h2d/d2h are asynchronous when `sync` is 0 (the host range must then stay
- * valid and, for real overlap, pinned, until ktc_sync). */
-KTC_API int ktc_h2d(ktc_buf dst, int64_t dst_off, const float* src, int64_t n, int sync);
-KTC_API int ktc_d2h(float* dst, ktc_buf src, int64_t src_off, int64_t n, int sync);
+ * Copy modes of h2d / d2h:
+ *   KTC_COPY_ASYNC    enqueue on the compute stream and return (the host range must stay valid, and
+ *                     pinned for a truly asynchronous copy, until ktc_sync);
+ *   KTC_COPY_SYNC     the same, then wait for the compute stream;
+ *   KTC_COPY_OVERLAP  run on a dedicated upload / download stream, ordered after the compute work
+ *                     queued so far and before the compute work queued afterwards (safe without
+ *                     further thought, but a download then holds back the following upload);
+ *   KTC_COPY_OVERLAP_UNFENCED  the pipelining form.  An upload does not wait for queued compute work
+ *                     (the caller guarantees nothing queued still reads the destination); later
+ *                     compute work waits for it.  A download waits for the compute work queued so
+ *                     far, but later compute work does NOT wait for it: before queuing work that
+ *                     overwrites the source, call ktc_copy_fence.  Uploads, kernels and downloads of
+ *                     neighbouring chunks then overlap (full-duplex copy engines).
+ * ktc_sync waits for the copy streams too; ktc_copy_fence makes compute work queued afterwards wait
+ * for every overlapped copy issued so far (no host wait). */
+enum { KTC_COPY_ASYNC = 0, KTC_COPY_SYNC = 1, KTC_COPY_OVERLAP = 2, KTC_COPY_OVERLAP_UNFENCED = 3 };
+KTC_API int ktc_h2d(ktc_buf dst, int64_t dst_off, const float* src, int64_t n, int mode);
+KTC_API int ktc_d2h(float* dst, ktc_buf src, int64_t src_off, int64_t n, int mode);
 KTC_API int ktc_d2d(ktc_buf dst, int64_t dst_off, ktc_buf src, int64_t src_off, int64_t n);
 KTC_API int ktc_fill(ktc_buf buf, int64_t off, int64_t n, float value);
 KTC_API int ktc_sync(int dev);
+KTC_API int ktc_copy_fence(int dev);
 
 /* ---- elementwise -----------------------------------------------------------
  * ktc_binary:         elementwiseOpOnCommonShapedTensors (JVM:75-79), kernels.cl:96-99.
@@ -170,6 +188,36 @@ KTC_API int ktc_sum_to_shape(ktc_buf out, const int64_t* old_shape, int old_ndim
 #define KTC_NOALLOC_SCRATCH_BYTES 16384
 #define KTC_NOALLOC_MAX_ELEMS ((int64_t)1 << 30)
 KTC_API int ktc_reduce_all_noalloc(int op, ktc_buf out, ktc_buf in, int64_t n);
+
+/* ---- fused elementwise chains (no single counterpart in the reference) ---------------------
+ * kten's autograd issues one raw-tensor call per line of doForward / doBackward
+ * (BasicFunctions.kt, PointwiseFunctions.kt), each a full pass over memory.  A backend may
+ * defer elementwise calls and submit the accumulated chain here: a program for a small
+ * register machine (registers hold 4 neighbouring elements) whose instructions are exactly the
+ * operations above -- the same arithmetic, rounded per operation, so the fused result equals
+ * the chain of separate calls bit for bit.  Instruction word: op | dst << 8 | a << 12 | b << 16 |
+ * k << 20 (k: leaf / store / immediate index).  `shape` is the iteration space; leaf_shapes holds
+ * n_leaves rows of `ndim` right-aligned extents (1 where the leaf is broadcast; nothing is
+ * materialised).  Sinks: STORE_ONLY (results leave through STORE instructions into full-size
+ * buffers), SUM_ALL (ACC values summed, or averaged with mean != 0, into sink_out[0]: sum() /
+ * mean(), JVM:146-152), SUM_ROWS (ACC values summed over all but the innermost dimension into
+ * sink_out[shape[ndim-1]]: the leading-axis sum of mayUnexpand, Utils.kt:14-41).
+ * KTC_ENOTSUP means "not fusable" (more than 3 collapsed dimensions, innermost extent not a
+ * multiple of 4, unaligned rows): issue the separate calls instead. */
+#define KTC_EXPR_MAX_INSTR 32
+#define KTC_EXPR_MAX_IMM 16
+#define KTC_EXPR_MAX_LEAVES 6
+#define KTC_EXPR_MAX_STORES 3
+#define KTC_EXPR_REGS 8
+enum { KTC_X_LOAD = 1, KTC_X_CONST, KTC_X_ADD, KTC_X_SUB, KTC_X_MUL, KTC_X_DIV, KTC_X_POW, KTC_X_NEG, KTC_X_RCP,
+       KTC_X_SQUARE, KTC_X_EXP, KTC_X_LOG, KTC_X_TANH, KTC_X_SIGMOID, KTC_X_CLAMP, KTC_X_CMP_LT, KTC_X_CMP_LTE,
+       KTC_X_CMP_GT, KTC_X_CMP_GTE, KTC_X_STORE, KTC_X_ACC };
+enum { KTC_EXPR_STORE_ONLY = 0, KTC_EXPR_SUM_ALL = 1, KTC_EXPR_SUM_ROWS = 2 };
+KTC_API int ktc_expr_eval(const uint32_t* code, int n_code, const float* imm, int n_imm,
+                          const int64_t* shape, int ndim,
+                          const ktc_buf* leaves, const int64_t* leaf_shapes, int n_leaves,
+                          const ktc_buf* stores, int n_stores,
+                          int sink, ktc_buf sink_out, int mean);
 
 /* inplaceScatter along an axis with one index per [outer, inner] position:
  * the Max/Min backward (AggregatingFunctions.kt:68-79; JVM:227-256,

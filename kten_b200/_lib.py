@@ -21,7 +21,13 @@ EXP, LOG, TANH, SIGMOID, RECIPROCAL, NEG = range(6)
 SUM, MEAN, MAX, MIN, ARGMAX, ARGMIN = range(6)
 LT, LTE, GT, GTE = range(4)
 MAX_DIMS = 10
+COPY_ASYNC, COPY_SYNC, COPY_OVERLAP, COPY_OVERLAP_UNFENCED = 0, 1, 2, 3
 COMM_ID_BYTES = 128
+# fused expression programs (ktc_expr_eval)
+(X_LOAD, X_CONST, X_ADD, X_SUB, X_MUL, X_DIV, X_POW, X_NEG, X_RCP, X_SQUARE, X_EXP, X_LOG, X_TANH, X_SIGMOID, X_CLAMP,
+ X_CMP_LT, X_CMP_LTE, X_CMP_GT, X_CMP_GTE, X_STORE, X_ACC) = range(1, 22)
+EXPR_STORE_ONLY, EXPR_SUM_ALL, EXPR_SUM_ROWS = 0, 1, 2
+EXPR_MAX_INSTR, EXPR_MAX_IMM, EXPR_MAX_LEAVES, EXPR_MAX_STORES, EXPR_REGS = 32, 16, 6, 3, 8
 NOALLOC_SCRATCH_BYTES = 16384
 NOALLOC_MAX_ELEMS = 1 << 30
 
@@ -36,6 +42,7 @@ _PROTOTYPES = {
     "ktc_version": (C.c_char_p, []),
     "ktc_alloc": (i32, [i32, i64, p_u64]),
     "ktc_wrap": (i32, [i32, C.c_void_p, i64, p_u64]),
+    "ktc_view": (i32, [u64, i64, i64, p_u64]),
     "ktc_retain": (i32, [u64]),
     "ktc_release": (i32, [u64]),
     "ktc_refcount": (i32, [u64, p_i32]),
@@ -50,6 +57,7 @@ _PROTOTYPES = {
     "ktc_d2d": (i32, [u64, i64, u64, i64, i64]),
     "ktc_fill": (i32, [u64, i64, i64, f32]),
     "ktc_sync": (i32, [i32]),
+    "ktc_copy_fence": (i32, [i32]),
     "ktc_binary": (i32, [i32, u64, u64, u64, i64]),
     "ktc_binary_bcast": (i32, [i32, u64, u64, p_i64, i32, u64, p_i64, i32]),
     "ktc_binary_inplace": (i32, [i32, u64, u64, i64]),
@@ -63,6 +71,7 @@ _PROTOTYPES = {
     "ktc_reduce_axis_validx": (i32, [i32, u64, u64, u64, i64, i64, i64]),
     "ktc_reduce_all": (i32, [i32, u64, u64, i64]),
     "ktc_reduce_all_noalloc": (i32, [i32, u64, u64, i64]),
+    "ktc_expr_eval": (i32, [C.POINTER(C.c_uint32), i32, p_f32, i32, p_i64, i32, p_u64, p_i64, i32, p_u64, i32, i32, u64, i32]),
     "ktc_sum_to_shape": (i32, [u64, p_i64, i32, u64, p_i64, i32]),
     "ktc_scatter_axis": (i32, [u64, u64, u64, i64, i64, i64]),
     "ktc_comm_unique_id": (i32, [C.c_char_p]),

@@ -23,7 +23,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ_DIR = os.path.join(HERE, "csrc", "build")
 LIB = os.path.join(HERE, "libkten_cuda.so")
 
-SOURCES = ["ktc_runtime.cu", "ktc_api.cu", "ktc_elementwise.cu", "ktc_reduce.cu", "ktc_comm.cu", "ktc_noalloc.cu"]
+SOURCES = ["ktc_runtime.cu", "ktc_api.cu", "ktc_elementwise.cu", "ktc_reduce.cu", "ktc_comm.cu", "ktc_noalloc.cu", "ktc_expr.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

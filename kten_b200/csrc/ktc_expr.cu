@@ -1,0 +1,336 @@
+// ktc_expr.cu -- fused evaluation of a chain of elementwise ops, optionally ending in a sum.
+//
+// kten's autograd issues one raw-tensor call per line of doForward / doBackward
+// (kten-api/.../autograd/functions/BasicFunctions.kt, PointwiseFunctions.kt), and every call
+// is a full pass over HBM: the sharded-graph benchmark step moves 34 tensor volumes where
+// reading the input once or twice would do.  A backend can defer elementwise calls behind
+// the SPI and hand the accumulated expression to this kernel when a value is finally needed
+// (a host read, a reduction, an op outside the hot path).
+//
+// The expression arrives as a short program for a register machine:
+//   * every register holds one float4 (four neighbouring elements of the innermost axis);
+//   * each instruction applies ONE reference operation to whole registers, with exactly the
+//     arithmetic of the stand-alone kernels (ktc_math.cuh), so a fused chain produces the same
+//     bits as the chain of separate calls -- nothing is contracted or re-associated;
+//   * LOAD reads a leaf tensor through its broadcast strides (0 where the leaf is broadcast;
+//     nothing is materialised), STORE writes a full-size result, ACC feeds a sum.
+// Registers live in shared memory (a dynamically indexed array cannot stay in hardware
+// registers), laid out so that a warp's access is one conflict-free 128-bit row.
+//
+// Iteration space: the collapsed view [D0, D1, D2] of the result shape; a warp owns a
+// 128-column tile (lane = 4 columns) of a segment of rows, like k_cols_warp.  Sinks:
+//   KTC_EXPR_STORE_ONLY   results are written by STORE instructions;
+//   KTC_EXPR_SUM_ALL      ACC values are summed over everything  -> out[1]  (optionally / count);
+//   KTC_EXPR_SUM_ROWS     ACC values are summed over D0 and D1   -> out[D2] (the broadcast-gradient
+//                         sum-to-shape of a row vector: mayUnexpand, Utils.kt:14-41).
+// Sums use the accumulation scheme of ktc_reduce.cu (float runs folded into doubles, fixed
+// combination order: eight segments per CTA, then a second pass).
+#include "ktc_accum.cuh"
+
+namespace ktc {
+
+constexpr int kExprMaxInstr = KTC_EXPR_MAX_INSTR;
+constexpr int kExprMaxImm = KTC_EXPR_MAX_IMM;
+constexpr int kExprMaxLeaves = KTC_EXPR_MAX_LEAVES;
+constexpr int kExprMaxStores = KTC_EXPR_MAX_STORES;
+constexpr int kExprRegs = KTC_EXPR_REGS;
+
+struct ExprArgs {
+    int n_code;
+    uint32_t code[kExprMaxInstr];          // op | dst << 8 | a << 12 | b << 16 | k << 20
+    float imm[kExprMaxImm];
+    const float* leaf[kExprMaxLeaves];
+    int64_t ls0[kExprMaxLeaves], ls1[kExprMaxLeaves];
+    int ls2[kExprMaxLeaves];               // 0 or 1
+    float* store[kExprMaxStores];
+    int64_t D0, D1, D2;
+    int64_t col_tiles;                     // ceil(D2 / 128)
+    int64_t seg_rows;                      // rows (of D0*D1) per warp
+    int S;                                 // segments of the row space (multiple of 8 for the summing sinks)
+    double* part;                          // partial sums of the summing sinks
+    float* out;                            // final result when a single CTA suffices (unused otherwise)
+    double divisor;                        // > 0: mean
+};
+
+__device__ __forceinline__ float4 f4(float v) { return make_float4(v, v, v, v); }
+#define KTC_EACH(expr_x, expr_y, expr_z, expr_w) make_float4(expr_x, expr_y, expr_z, expr_w)
+
+// out-of-line so that the switch below stays small; same functors as the stand-alone kernels
+static __device__ __noinline__ float4 expr_pow(float4 x, float4 y) {
+    BinOp<KTC_POW> f; return KTC_EACH(f(x.x, y.x), f(x.y, y.y), f(x.z, y.z), f(x.w, y.w));
+}
+static __device__ __noinline__ float4 expr_sigmoid(float4 x) {
+    UnOp<KTC_SIGMOID> f; return KTC_EACH(f(x.x), f(x.y), f(x.z), f(x.w));
+}
+static __device__ __noinline__ float4 expr_exp(float4 x) {
+    UnOp<KTC_EXP> f; return KTC_EACH(f(x.x), f(x.y), f(x.z), f(x.w));
+}
+static __device__ __noinline__ float4 expr_log(float4 x) {
+    UnOp<KTC_LOG> f; return KTC_EACH(f(x.x), f(x.y), f(x.z), f(x.w));
+}
+static __device__ __noinline__ float4 expr_tanh(float4 x) {
+    UnOp<KTC_TANH> f; return KTC_EACH(f(x.x), f(x.y), f(x.z), f(x.w));
+}
+
+template <int SINK>
+__global__ void __launch_bounds__(256) k_expr(const __grid_constant__ ExprArgs p) {
+    __shared__ float4 regs[kExprRegs][256];
+    __shared__ double sm_part[SINK == KTC_EXPR_SUM_ROWS ? 8 * 32 * 4 : 8];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    // item -> (row segment, column tile); the column tile varies fastest (address order)
+    int64_t ct, seg;
+    if (SINK == KTC_EXPR_STORE_ONLY) {
+        const int64_t item = (int64_t)blockIdx.x * 8 + warp;
+        if (item >= (int64_t)p.S * p.col_tiles) return;        // whole warps leave together; no barrier in this mode
+        ct = item % p.col_tiles; seg = item / p.col_tiles;
+    } else {
+        ct = blockIdx.x % p.col_tiles;
+        seg = (blockIdx.x / p.col_tiles) * 8 + warp;             // eight consecutive segments per CTA
+    }
+    const int64_t col = (ct * 32 + lane) * 4;
+    const bool col_ok = col < p.D2;
+    const int64_t rows_total = p.D0 * p.D1;
+    const int64_t r0 = seg * p.seg_rows, r1 = min(rows_total, r0 + p.seg_rows);
+
+    SumAcc acc[4];
+    #pragma unroll
+    for (int k = 0; k < 4; ++k) acc[k].init();
+
+    if (col_ok && r0 < r1) {
+        int64_t i0 = r0 / p.D1, i1 = r0 - i0 * p.D1;
+        for (int64_t r = r0; r < r1; ++r) {
+            #pragma unroll 1
+            for (int pc = 0; pc < p.n_code; ++pc) {
+                const uint32_t ins = p.code[pc];
+                const int op = ins & 0xff, d = (ins >> 8) & 0xf, ra = (ins >> 12) & 0xf, rb = (ins >> 16) & 0xf, k = ins >> 20;
+                const float4 x = regs[ra][tid], y = regs[rb][tid];
+                float4 v;
+                switch (op) {
+                case KTC_X_LOAD: {
+                    const float* base = p.leaf[k] + i0 * p.ls0[k] + i1 * p.ls1[k];
+                    if (p.ls2[k]) v = __ldg(reinterpret_cast<const float4*>(base + col));
+                    else v = f4(__ldg(base));
+                    break;
+                }
+                case KTC_X_CONST: v = f4(p.imm[k]); break;
+                case KTC_X_ADD: v = KTC_EACH(__fadd_rn(x.x, y.x), __fadd_rn(x.y, y.y), __fadd_rn(x.z, y.z), __fadd_rn(x.w, y.w)); break;
+                case KTC_X_SUB: v = KTC_EACH(__fsub_rn(x.x, y.x), __fsub_rn(x.y, y.y), __fsub_rn(x.z, y.z), __fsub_rn(x.w, y.w)); break;
+                case KTC_X_MUL: v = KTC_EACH(__fmul_rn(x.x, y.x), __fmul_rn(x.y, y.y), __fmul_rn(x.z, y.z), __fmul_rn(x.w, y.w)); break;
+                case KTC_X_DIV: v = KTC_EACH(__fdiv_rn(x.x, y.x), __fdiv_rn(x.y, y.y), __fdiv_rn(x.z, y.z), __fdiv_rn(x.w, y.w)); break;
+                case KTC_X_POW: v = expr_pow(x, y); break;
+                case KTC_X_NEG: v = KTC_EACH(-x.x, -x.y, -x.z, -x.w); break;
+                case KTC_X_RCP: v = KTC_EACH(__frcp_rn(x.x), __frcp_rn(x.y), __frcp_rn(x.z), __frcp_rn(x.w)); break;
+                case KTC_X_SQUARE: v = KTC_EACH(__fmul_rn(x.x, x.x), __fmul_rn(x.y, x.y), __fmul_rn(x.z, x.z), __fmul_rn(x.w, x.w)); break;
+                case KTC_X_EXP: v = expr_exp(x); break;
+                case KTC_X_LOG: v = expr_log(x); break;
+                case KTC_X_TANH: v = expr_tanh(x); break;
+                case KTC_X_SIGMOID: v = expr_sigmoid(x); break;
+                case KTC_X_CLAMP: { ClampOp c{p.imm[k], p.imm[k + 1]}; v = KTC_EACH(c(x.x), c(x.y), c(x.z), c(x.w)); break; }
+                case KTC_X_CMP_LT: { const float t = p.imm[k]; v = KTC_EACH(x.x < t ? 1.f : 0.f, x.y < t ? 1.f : 0.f, x.z < t ? 1.f : 0.f, x.w < t ? 1.f : 0.f); break; }
+                case KTC_X_CMP_LTE: { const float t = p.imm[k]; v = KTC_EACH(x.x <= t ? 1.f : 0.f, x.y <= t ? 1.f : 0.f, x.z <= t ? 1.f : 0.f, x.w <= t ? 1.f : 0.f); break; }
+                case KTC_X_CMP_GT: { const float t = p.imm[k]; v = KTC_EACH(x.x > t ? 1.f : 0.f, x.y > t ? 1.f : 0.f, x.z > t ? 1.f : 0.f, x.w > t ? 1.f : 0.f); break; }
+                case KTC_X_CMP_GTE: { const float t = p.imm[k]; v = KTC_EACH(x.x >= t ? 1.f : 0.f, x.y >= t ? 1.f : 0.f, x.z >= t ? 1.f : 0.f, x.w >= t ? 1.f : 0.f); break; }
+                case KTC_X_STORE:
+                    __stcs(reinterpret_cast<float4*>(p.store[k] + r * p.D2 + col), x);
+                    continue;
+                case KTC_X_ACC:
+                    if (SINK == KTC_EXPR_SUM_ROWS) {
+                        acc[0].add(x.x, 0); acc[1].add(x.y, 0); acc[2].add(x.z, 0); acc[3].add(x.w, 0);
+                    } else {
+                        acc[0].add4(x, 0);
+                    }
+                    continue;
+                default: continue;
+                }
+                regs[d][tid] = v;
+            }
+            if (SINK != KTC_EXPR_STORE_ONLY && ((r - r0) & 7) == 7) {       // fold the float runs every 8 rows (<= 32 values)
+                #pragma unroll
+                for (int k = 0; k < 4; ++k) acc[k].end();
+            }
+            if (++i1 == p.D1) { i1 = 0; ++i0; }
+        }
+        #pragma unroll
+        for (int k = 0; k < 4; ++k) acc[k].end();
+    }
+
+    if (SINK == KTC_EXPR_SUM_ALL) {
+        double v = acc[0].acc;
+        #pragma unroll
+        for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+        if (lane == 0) sm_part[warp] = v;
+        __syncthreads();
+        if (tid == 0) {
+            double t = sm_part[0];
+            #pragma unroll
+            for (int w = 1; w < 8; ++w) t += sm_part[w];
+            if (gridDim.x == 1) p.out[0] = (float)(p.divisor > 0.0 ? t / p.divisor : t);
+            else p.part[blockIdx.x] = t;
+        }
+    } else if (SINK == KTC_EXPR_SUM_ROWS) {
+        #pragma unroll
+        for (int k = 0; k < 4; ++k) sm_part[(warp * 32 + lane) * 4 + k] = acc[k].acc;
+        __syncthreads();
+        if (warp == 0 && col_ok) {
+            #pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                double t = sm_part[lane * 4 + k];
+                #pragma unroll
+                for (int w = 1; w < 8; ++w) t += sm_part[(w * 32 + lane) * 4 + k];
+                p.part[(blockIdx.x / p.col_tiles) * p.D2 + col + k] = t;
+            }
+        }
+    }
+}
+
+static inline int finish_launch_expr(const char* what) {
+    count_launch(1);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(KTC_ECUDA, "launch of %s failed: %s", what, cudaGetErrorString(e));
+    return KTC_OK;
+}
+
+}  // namespace ktc
+
+using namespace ktc;
+
+extern "C" int ktc_expr_eval(const uint32_t* code, int n_code, const float* imm, int n_imm,
+                             const int64_t* shape, int ndim,
+                             const ktc_buf* leaves, const int64_t* leaf_shapes, int n_leaves,
+                             const ktc_buf* stores, int n_stores,
+                             int sink, ktc_buf sink_out, int mean) {
+    if (!code || n_code < 1 || n_code > kExprMaxInstr) return fail(KTC_EINVAL, "ktc_expr_eval: program of %d instructions (1..%d allowed)", n_code, kExprMaxInstr);
+    if (n_imm < 0 || n_imm > kExprMaxImm || (n_imm > 0 && !imm)) return fail(KTC_EINVAL, "ktc_expr_eval: %d immediates (at most %d)", n_imm, kExprMaxImm);
+    if (n_leaves < 0 || n_leaves > kExprMaxLeaves || n_stores < 0 || n_stores > kExprMaxStores)
+        return fail(KTC_EINVAL, "ktc_expr_eval: %d leaves / %d stores (at most %d / %d)", n_leaves, n_stores, kExprMaxLeaves, kExprMaxStores);
+    if (ndim < 1 || ndim > KTC_MAX_DIMS || !shape) return fail(KTC_EINVAL, "ktc_expr_eval: bad shape");
+    if (sink < KTC_EXPR_STORE_ONLY || sink > KTC_EXPR_SUM_ROWS) return fail(KTC_EINVAL, "ktc_expr_eval: unknown sink %d", sink);
+    int64_t total = 1;
+    for (int i = 0; i < ndim; ++i) { if (shape[i] < 1) return fail(KTC_EINVAL, "ktc_expr_eval: empty iteration space"); total *= shape[i]; }
+    if (total > ((int64_t)1 << 40)) return fail(KTC_EINVAL, "ktc_expr_eval: iteration space too large");
+
+    ExprArgs a{};
+    Device* d = nullptr; int dev = -1;
+    auto adopt = [&](const Buf& b) -> int {
+        if (dev < 0) { dev = b.dev; d = device(dev); if (!d) return KTC_ESTATE; return use_device(d); }
+        if (b.dev != dev) return fail(KTC_EINVAL, "ktc_expr_eval: buffers live on different devices");
+        return KTC_OK;
+    };
+
+    // leaf strides through the right-aligned iteration shape (0 where the leaf is broadcast)
+    int64_t lstr[kExprMaxLeaves][KTC_MAX_DIMS];
+    for (int l = 0; l < n_leaves; ++l) {
+        Buf b; KTC_TRY(resolve(leaves[l], &b)); KTC_TRY(adopt(b));
+        const int64_t* ls = leaf_shapes + (int64_t)l * ndim;
+        int64_t st = 1, vol = 1;
+        for (int i = ndim - 1; i >= 0; --i) {
+            if (!(ls[i] == shape[i] || ls[i] == 1)) return fail(KTC_EINVAL, "ktc_expr_eval: leaf %d extent %lld does not broadcast to %lld", l, (long long)ls[i], (long long)shape[i]);
+            lstr[l][i] = (ls[i] == shape[i] && shape[i] != 1) ? st : 0;
+            st *= ls[i]; vol *= ls[i];
+        }
+        if (b.n < vol) return fail(KTC_EINVAL, "ktc_expr_eval: leaf %d holds %lld floats, %lld needed", l, (long long)b.n, (long long)vol);
+        a.leaf[l] = b.ptr;
+    }
+    for (int s = 0; s < n_stores; ++s) {
+        Buf b; KTC_TRY(resolve(stores[s], &b)); KTC_TRY(adopt(b));
+        if (b.n < total) return fail(KTC_EINVAL, "ktc_expr_eval: store target %d holds %lld floats, %lld needed", s, (long long)b.n, (long long)total);
+        if (!aligned16(b.ptr)) return fail(KTC_ENOTSUP, "ktc_expr_eval: store target is not 16-byte aligned");
+        a.store[s] = b.ptr;
+    }
+
+    // collapse to [D0, D1, D2]; for SUM_ROWS the innermost dimension of `shape` is the kept one and is not merged
+    int64_t S[KTC_MAX_DIMS]; int64_t LS[kExprMaxLeaves][KTC_MAX_DIMS]; int m = 0;
+    for (int i = 0; i < ndim; ++i) {
+        if (shape[i] == 1) continue;
+        bool merge = m > 0 && !(sink == KTC_EXPR_SUM_ROWS && i == ndim - 1);
+        for (int l = 0; l < n_leaves && merge; ++l) merge = (LS[l][m - 1] == lstr[l][i] * shape[i]);
+        if (merge) { S[m - 1] *= shape[i]; for (int l = 0; l < n_leaves; ++l) LS[l][m - 1] = lstr[l][i]; }
+        else { S[m] = shape[i]; for (int l = 0; l < n_leaves; ++l) LS[l][m] = lstr[l][i]; ++m; }
+    }
+    if (m == 0) { S[0] = 1; for (int l = 0; l < n_leaves; ++l) LS[l][0] = 0; m = 1; }
+    if (sink == KTC_EXPR_SUM_ROWS && shape[ndim - 1] == 1) return fail(KTC_ENOTSUP, "ktc_expr_eval: SUM_ROWS needs a kept innermost dimension");
+    if (m > 3) return fail(KTC_ENOTSUP, "ktc_expr_eval: %d collapsed dimensions (at most 3 are fused)", m);
+    int64_t D[3] = {1, 1, 1};
+    for (int i = 0; i < m; ++i) D[3 - m + i] = S[i];
+    if (D[2] % 4 != 0) return fail(KTC_ENOTSUP, "ktc_expr_eval: innermost extent %lld is not a multiple of 4", (long long)D[2]);
+    for (int l = 0; l < n_leaves; ++l) {
+        int64_t s3[3] = {0, 0, 0};
+        for (int i = 0; i < m; ++i) s3[3 - m + i] = LS[l][i];
+        if (s3[2] != 0 && s3[2] != 1) return fail(KTC_ENOTSUP, "ktc_expr_eval: leaf %d is not contiguous along the innermost axis", l);
+        if (s3[2] == 1 && (!aligned16(a.leaf[l]) || (s3[0] & 3) || (s3[1] & 3))) return fail(KTC_ENOTSUP, "ktc_expr_eval: leaf %d rows are not 16-byte aligned", l);
+        a.ls0[l] = s3[0]; a.ls1[l] = s3[1]; a.ls2[l] = (int)s3[2];
+    }
+    a.D0 = D[0]; a.D1 = D[1]; a.D2 = D[2];
+
+    // validate the program: register and operand indices, opcodes
+    a.n_code = n_code;
+    bool has_acc = false;
+    for (int i = 0; i < n_code; ++i) {
+        const uint32_t ins = code[i];
+        const int op = ins & 0xff, dreg = (ins >> 8) & 0xf, ra = (ins >> 12) & 0xf, rb = (ins >> 16) & 0xf, k = ins >> 20;
+        if (op < KTC_X_LOAD || op > KTC_X_ACC) return fail(KTC_EINVAL, "ktc_expr_eval: unknown opcode %d at %d", op, i);
+        if (dreg >= kExprRegs || ra >= kExprRegs || rb >= kExprRegs) return fail(KTC_EINVAL, "ktc_expr_eval: register index out of range at %d", i);
+        if (op == KTC_X_LOAD && k >= n_leaves) return fail(KTC_EINVAL, "ktc_expr_eval: LOAD of leaf %d (have %d)", k, n_leaves);
+        if (op == KTC_X_STORE && k >= n_stores) return fail(KTC_EINVAL, "ktc_expr_eval: STORE to target %d (have %d)", k, n_stores);
+        if ((op == KTC_X_CONST || (op >= KTC_X_CMP_LT && op <= KTC_X_CMP_GTE)) && k >= n_imm) return fail(KTC_EINVAL, "ktc_expr_eval: immediate %d (have %d)", k, n_imm);
+        if (op == KTC_X_CLAMP && k + 1 >= n_imm) return fail(KTC_EINVAL, "ktc_expr_eval: clamp immediates %d,%d (have %d)", k, k + 1, n_imm);
+        if (op == KTC_X_ACC) { if (sink == KTC_EXPR_STORE_ONLY) return fail(KTC_EINVAL, "ktc_expr_eval: ACC without a summing sink"); has_acc = true; }
+        a.code[i] = ins;
+    }
+    for (int i = 0; i < n_imm; ++i) a.imm[i] = imm[i];
+    if (sink != KTC_EXPR_STORE_ONLY && !has_acc) return fail(KTC_EINVAL, "ktc_expr_eval: a summing sink needs an ACC instruction");
+
+    const int64_t rows = D[0] * D[1];
+    a.col_tiles = (D[2] / 4 + 31) / 32;
+    int64_t seg_rows = tune("expr_item_kb", 32) * 1024 / 512;      // rows of 128 columns per warp
+    if (seg_rows < 8) seg_rows = 8;
+    if (seg_rows > rows) seg_rows = rows;
+    a.seg_rows = seg_rows;
+    int64_t Sg = (rows + seg_rows - 1) / seg_rows;
+
+    Buf bout{}; Scratch scratch;
+    if (sink != KTC_EXPR_STORE_ONLY) {
+        KTC_TRY(resolve(sink_out, &bout)); KTC_TRY(adopt(bout));
+        const int64_t need_out = sink == KTC_EXPR_SUM_ALL ? 1 : D[2];
+        if (bout.n < need_out) return fail(KTC_EINVAL, "ktc_expr_eval: sink output holds %lld floats, %lld needed", (long long)bout.n, (long long)need_out);
+        Sg = (Sg + 7) & ~(int64_t)7;
+    }
+    if (!d) return fail(KTC_EINVAL, "ktc_expr_eval: no buffers given");
+    a.S = (int)Sg;
+
+    if (sink == KTC_EXPR_STORE_ONLY) {
+        const int64_t grid = (Sg * a.col_tiles + 7) / 8;
+        if (grid > 0x7fffffffLL) return fail(KTC_ENOTSUP, "ktc_expr_eval: grid too large");
+        k_expr<KTC_EXPR_STORE_ONLY><<<(int)grid, 256, 0, d->stream>>>(a);
+        return finish_launch_expr("expr(store)");
+    }
+    const int64_t groups = Sg / 8;
+    const int64_t grid = groups * a.col_tiles;
+    if (grid > 0x7fffffffLL) return fail(KTC_ENOTSUP, "ktc_expr_eval: grid too large");
+    a.divisor = mean ? (double)total : 0.0;
+    if (sink == KTC_EXPR_SUM_ALL) {
+        a.out = bout.ptr;
+        if (grid > 1) { KTC_TRY(scratch.get(d, grid * 2)); a.part = reinterpret_cast<double*>(scratch.ptr); }
+        k_expr<KTC_EXPR_SUM_ALL><<<(int)grid, 256, 0, d->stream>>>(a);
+        KTC_TRY(finish_launch_expr("expr(sum_all)"));
+        if (grid > 1) {
+            if (mean) k_combine_block<1, SumAcc><<<1, 512, 0, d->stream>>>(a.part, bout.ptr, nullptr, 1, (int)grid, total);
+            else      k_combine_block<0, SumAcc><<<1, 512, 0, d->stream>>>(a.part, bout.ptr, nullptr, 1, (int)grid, total);
+            KTC_TRY(finish_launch_expr("expr(combine)"));
+        }
+        return KTC_OK;
+    }
+    // SUM_ROWS: partial[group][column] then one pass over the groups
+    KTC_TRY(scratch.get(d, groups * D[2] * 2));
+    a.part = reinterpret_cast<double*>(scratch.ptr);
+    k_expr<KTC_EXPR_SUM_ROWS><<<(int)grid, 256, 0, d->stream>>>(a);
+    KTC_TRY(finish_launch_expr("expr(sum_rows)"));
+    if (groups >= 64 || D[2] < 4096) {
+        const int64_t blocks = (D[2] * 32 + 255) / 256;
+        k_combine_warp<0, SumAcc><<<(int)blocks, 256, 0, d->stream>>>(a.part, bout.ptr, nullptr, D[2], (int)groups, rows);
+    } else {
+        k_combine_thread<0, SumAcc><<<(int)((D[2] + 255) / 256), 256, 0, d->stream>>>(a.part, bout.ptr, nullptr, D[2], (int)groups, rows);
+    }
+    return finish_launch_expr("expr(combine)");
+}

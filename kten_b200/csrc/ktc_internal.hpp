@@ -28,6 +28,10 @@ struct Device {
     int id = -1;
     bool ready = false;
     cudaStream_t stream = nullptr;
+    cudaStream_t stream_up = nullptr, stream_down = nullptr;   // overlapped host<->device copies (mode KTC_COPY_OVERLAP)
+    static constexpr int kEventRing = 256;
+    cudaEvent_t ring[kEventRing] = {nullptr};                  // ordering events, reused round-robin
+    int ring_next = 0;
     cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
     int sm_count = 0;
     size_t total_mem = 0;
@@ -51,6 +55,7 @@ struct BufRec {
     int refcount = 0;
     bool owned = false;
     uint32_t gen = 0;
+    ktc_buf parent = 0;     // views hold one reference on the buffer they alias
 };
 
 // resolved view of a handle, valid while the caller holds a reference

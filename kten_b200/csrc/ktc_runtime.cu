@@ -72,6 +72,9 @@ int use_device(Device* d) {
         std::lock_guard<std::mutex> lk(d->pool_mu);
         if (!d->ready) {
             KTC_CUDA(cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
+            KTC_CUDA(cudaStreamCreateWithFlags(&d->stream_up, cudaStreamNonBlocking));
+            KTC_CUDA(cudaStreamCreateWithFlags(&d->stream_down, cudaStreamNonBlocking));
+            for (int i = 0; i < Device::kEventRing; ++i) KTC_CUDA(cudaEventCreateWithFlags(&d->ring[i], cudaEventDisableTiming));
             KTC_CUDA(cudaEventCreate(&d->ev_start));
             KTC_CUDA(cudaEventCreate(&d->ev_stop));
             KTC_CUDA(cudaMalloc(&d->err_flag, 2 * sizeof(int)));
@@ -145,13 +148,13 @@ int resolve(ktc_buf h, Buf* out) {
     return KTC_OK;
 }
 
-static ktc_buf new_handle(int dev, float* ptr, int64_t n, size_t bytes, bool owned) {
+static ktc_buf new_handle(int dev, float* ptr, int64_t n, size_t bytes, bool owned, ktc_buf parent = 0) {
     std::lock_guard<std::mutex> lk(g_mu);
     uint32_t slot;
     if (!g_free_slots.empty()) { slot = g_free_slots.back(); g_free_slots.pop_back(); }
     else { g_bufs.emplace_back(); slot = (uint32_t)g_bufs.size(); }
     BufRec& r = g_bufs[slot - 1];
-    r.dev = dev; r.ptr = ptr; r.n = n; r.bytes = bytes; r.owned = owned; r.refcount = 1;
+    r.dev = dev; r.ptr = ptr; r.n = n; r.bytes = bytes; r.owned = owned; r.refcount = 1; r.parent = parent;
     r.gen += 1; if (r.gen == 0) r.gen = 1;
     return ((uint64_t)r.gen << 32) | slot;
 }
@@ -200,6 +203,8 @@ int ktc_shutdown(void) {
             if (d->l2_flush) cudaFree(d->l2_flush);
             cudaFree(d->err_flag);
             cudaEventDestroy(d->ev_start); cudaEventDestroy(d->ev_stop);
+            for (int i = 0; i < Device::kEventRing; ++i) cudaEventDestroy(d->ring[i]);
+            cudaStreamDestroy(d->stream_up); cudaStreamDestroy(d->stream_down);
             cudaStreamDestroy(d->stream);
         }
         delete d;
@@ -255,6 +260,17 @@ int ktc_release(ktc_buf h) {
         if (--r.refcount == 0) { dead = r; free_it = true; r.ptr = nullptr; g_free_slots.push_back(slot); }
     }
     if (free_it && dead.owned) pool_free(g_devices[dead.dev], dead.ptr, dead.bytes);
+    if (free_it && dead.parent) return ktc_release(dead.parent);
+    return KTC_OK;
+}
+
+int ktc_view(ktc_buf buf, int64_t off, int64_t n, ktc_buf* out) {
+    if (!out) return fail(KTC_EINVAL, "ktc_view: out is null");
+    Buf b; KTC_TRY(resolve(buf, &b));
+    if (off < 0 || n < 0 || off + n > b.n)
+        return fail(KTC_EINVAL, "ktc_view: range [%lld, %lld) outside a buffer of %lld floats", (long long)off, (long long)(off + n), (long long)b.n);
+    KTC_TRY(ktc_retain(buf));
+    *out = new_handle(b.dev, b.ptr + off, n, 0, false, buf);
     return KTC_OK;
 }
 
@@ -324,23 +340,61 @@ static int check_range(const Buf& b, int64_t off, int64_t n, const char* who) {
     return KTC_OK;
 }
 
-int ktc_h2d(ktc_buf dst, int64_t dst_off, const float* src, int64_t n, int sync) {
-    Buf b; KTC_TRY(resolve(dst, &b)); KTC_TRY(check_range(b, dst_off, n, "ktc_h2d"));
-    if (n == 0) return KTC_OK;
-    if (!src) return fail(KTC_EINVAL, "ktc_h2d: src is null");
-    Device* d = device(b.dev); if (!d) return KTC_ESTATE; KTC_TRY(use_device(d));
-    KTC_CUDA(cudaMemcpyAsync(b.ptr + dst_off, src, (size_t)n * 4, cudaMemcpyHostToDevice, d->stream));
-    if (sync) KTC_CUDA(cudaStreamSynchronize(d->stream));
+// Overlapped copies run on their own streams so that uploads, kernels and downloads of a
+// chunked pipeline proceed at the same time (the copy engines are full duplex).  Ordering is
+// conservative: an upload starts after all compute work queued so far (which may still read the
+// destination) and later compute work waits for it; a download starts after all compute work
+// queued so far (which produces the source) and later compute work, which may overwrite the
+// source, waits for it.
+static cudaEvent_t next_event(Device* d) {
+    std::lock_guard<std::mutex> lk(d->pool_mu);
+    cudaEvent_t e = d->ring[d->ring_next];
+    d->ring_next = (d->ring_next + 1) % Device::kEventRing;
+    return e;
+}
+
+static int overlapped_copy(Device* d, cudaStream_t side, void* dst, const void* src, size_t bytes, cudaMemcpyKind kind, bool fenced) {
+    if (fenced) {
+        cudaEvent_t before = next_event(d);
+        KTC_CUDA(cudaEventRecord(before, d->stream));
+        KTC_CUDA(cudaStreamWaitEvent(side, before, 0));
+    } else if (kind == cudaMemcpyDeviceToHost) {
+        // a download always follows the compute work that produces its source
+        cudaEvent_t before = next_event(d);
+        KTC_CUDA(cudaEventRecord(before, d->stream));
+        KTC_CUDA(cudaStreamWaitEvent(side, before, 0));
+    }
+    KTC_CUDA(cudaMemcpyAsync(dst, src, bytes, kind, side));
+    if (fenced || kind == cudaMemcpyHostToDevice) {
+        // compute work queued from now on sees the uploaded data / may overwrite the downloaded source
+        cudaEvent_t after = next_event(d);
+        KTC_CUDA(cudaEventRecord(after, side));
+        KTC_CUDA(cudaStreamWaitEvent(d->stream, after, 0));
+    }
     return KTC_OK;
 }
 
-int ktc_d2h(float* dst, ktc_buf src, int64_t src_off, int64_t n, int sync) {
+int ktc_h2d(ktc_buf dst, int64_t dst_off, const float* src, int64_t n, int mode) {
+    Buf b; KTC_TRY(resolve(dst, &b)); KTC_TRY(check_range(b, dst_off, n, "ktc_h2d"));
+    if (n == 0) return KTC_OK;
+    if (!src) return fail(KTC_EINVAL, "ktc_h2d: src is null");
+    if (mode < 0 || mode > KTC_COPY_OVERLAP_UNFENCED) return fail(KTC_EINVAL, "ktc_h2d: unknown copy mode %d", mode);
+    Device* d = device(b.dev); if (!d) return KTC_ESTATE; KTC_TRY(use_device(d));
+    if (mode >= KTC_COPY_OVERLAP) return overlapped_copy(d, d->stream_up, b.ptr + dst_off, src, (size_t)n * 4, cudaMemcpyHostToDevice, mode == KTC_COPY_OVERLAP);
+    KTC_CUDA(cudaMemcpyAsync(b.ptr + dst_off, src, (size_t)n * 4, cudaMemcpyHostToDevice, d->stream));
+    if (mode == KTC_COPY_SYNC) KTC_CUDA(cudaStreamSynchronize(d->stream));
+    return KTC_OK;
+}
+
+int ktc_d2h(float* dst, ktc_buf src, int64_t src_off, int64_t n, int mode) {
     Buf b; KTC_TRY(resolve(src, &b)); KTC_TRY(check_range(b, src_off, n, "ktc_d2h"));
     if (n == 0) return KTC_OK;
     if (!dst) return fail(KTC_EINVAL, "ktc_d2h: dst is null");
+    if (mode < 0 || mode > KTC_COPY_OVERLAP_UNFENCED) return fail(KTC_EINVAL, "ktc_d2h: unknown copy mode %d", mode);
     Device* d = device(b.dev); if (!d) return KTC_ESTATE; KTC_TRY(use_device(d));
+    if (mode >= KTC_COPY_OVERLAP) return overlapped_copy(d, d->stream_down, dst, b.ptr + src_off, (size_t)n * 4, cudaMemcpyDeviceToHost, mode == KTC_COPY_OVERLAP);
     KTC_CUDA(cudaMemcpyAsync(dst, b.ptr + src_off, (size_t)n * 4, cudaMemcpyDeviceToHost, d->stream));
-    if (sync) KTC_CUDA(cudaStreamSynchronize(d->stream));
+    if (mode == KTC_COPY_SYNC) KTC_CUDA(cudaStreamSynchronize(d->stream));
     return KTC_OK;
 }
 
@@ -364,6 +418,18 @@ int ktc_fill(ktc_buf buf, int64_t off, int64_t n, float value) {
 int ktc_sync(int dev) {
     Device* d = device(dev); if (!d) return KTC_ESTATE; KTC_TRY(use_device(d));
     KTC_CUDA(cudaStreamSynchronize(d->stream));
+    KTC_CUDA(cudaStreamSynchronize(d->stream_up));
+    KTC_CUDA(cudaStreamSynchronize(d->stream_down));
+    return KTC_OK;
+}
+
+int ktc_copy_fence(int dev) {
+    Device* d = device(dev); if (!d) return KTC_ESTATE; KTC_TRY(use_device(d));
+    cudaEvent_t up = next_event(d), down = next_event(d);
+    KTC_CUDA(cudaEventRecord(up, d->stream_up));
+    KTC_CUDA(cudaEventRecord(down, d->stream_down));
+    KTC_CUDA(cudaStreamWaitEvent(d->stream, up, 0));
+    KTC_CUDA(cudaStreamWaitEvent(d->stream, down, 0));
     return KTC_OK;
 }
 

@@ -534,6 +534,64 @@ def test_transfers_fill_copy_and_ranges(cuda_ops, gc_scope):
     assert lib.ktc_reduce_axis(L.SUM, r.storeReference, r.storeReference, 1, 1000, 1) == L.KTC_EINVAL      # aliasing
 
 
+def test_views_and_overlapped_copy_pipeline(cuda_ops, gc_scope):
+    """Sub-range handles keep their parent alive, and a chunked upload / compute / download
+    pipeline in KTC_COPY_OVERLAP mode gives the same bits as the one-shot path."""
+    lib = cuda_ops.lib
+    n, chunk = 1 << 20, 1 << 16
+    a, b = D.uniform(n, 21, -1.0, 1.0), D.uniform(n, 22, 0.5, 2.0)
+    want = O.binary_same(O.DIV, a, b)
+    ra, rb, ro = cuda_ops.createRaw([n]), cuda_ops.createRaw([n]), cuda_ops.createRaw([n])
+    views = []
+    for mode in (L.COPY_OVERLAP, L.COPY_OVERLAP_UNFENCED):
+        got = np.zeros(n, dtype=np.float32)
+        L.check(lib.ktc_copy_fence(0))
+        for i in range(n // chunk):
+            hs = [C.c_uint64(0) for _ in range(3)]
+            for h, r in zip(hs, (ra, rb, ro)):
+                L.check(lib.ktc_view(r.storeReference, i * chunk, chunk, C.byref(h)))
+            va, vb, vo = (h.value for h in hs)
+            sl = slice(i * chunk, (i + 1) * chunk)
+            L.check(lib.ktc_h2d(va, 0, a[sl].ctypes.data_as(C.c_void_p), chunk, mode))
+            L.check(lib.ktc_h2d(vb, 0, b[sl].ctypes.data_as(C.c_void_p), chunk, mode))
+            L.check(lib.ktc_binary(L.DIV, vo, va, vb, chunk))
+            L.check(lib.ktc_d2h(got[sl].ctypes.data_as(C.c_void_p), vo, 0, chunk, mode))
+            for v in (va, vb, vo):
+                L.check(lib.ktc_release(v))
+        cuda_ops.synchronize()
+        assert same_bits(got, want)
+        ro.inplaceFill(0.0)
+    got = np.zeros(n, dtype=np.float32)
+    for i in range(n // chunk):
+        hs = [C.c_uint64(0) for _ in range(3)]
+        for h, r in zip(hs, (ra, rb, ro)):
+            L.check(lib.ktc_view(r.storeReference, i * chunk, chunk, C.byref(h)))
+        va, vb, vo = (h.value for h in hs)
+        views += [va, vb, vo]
+        sl = slice(i * chunk, (i + 1) * chunk)
+        L.check(lib.ktc_h2d(va, 0, a[sl].ctypes.data_as(C.c_void_p), chunk, L.COPY_OVERLAP))
+        L.check(lib.ktc_h2d(vb, 0, b[sl].ctypes.data_as(C.c_void_p), chunk, L.COPY_OVERLAP))
+        L.check(lib.ktc_binary(L.DIV, vo, va, vb, chunk))
+        L.check(lib.ktc_d2h(got[sl].ctypes.data_as(C.c_void_p), vo, 0, chunk, L.COPY_OVERLAP))
+    cuda_ops.synchronize()
+    assert same_bits(got, want)
+    assert same_bits(ro.toArray(), want)
+    # a view outlives the tensor object that created its parent
+    cnt = C.c_int(0)
+    L.check(lib.ktc_refcount(ra.storeReference, C.byref(cnt))); assert cnt.value == 1 + n // chunk
+    h_parent = ra.storeReference
+    ra.release()
+    L.check(lib.ktc_refcount(h_parent, C.byref(cnt))); assert cnt.value == n // chunk
+    out = np.zeros(4, dtype=np.float32)
+    L.check(lib.ktc_d2h(out.ctypes.data_as(C.c_void_p), views[0], 0, 4, L.COPY_SYNC))
+    assert same_bits(out, a[:4])
+    h = C.c_uint64(0)
+    assert lib.ktc_view(rb.storeReference, n - 2, 4, C.byref(h)) == L.KTC_EINVAL
+    for v in views:
+        L.check(lib.ktc_release(v))
+    assert lib.ktc_d2h(out.ctypes.data_as(C.c_void_p), h_parent, 0, 4, L.COPY_SYNC) == L.KTC_ESTATE   # last view gone -> parent freed
+
+
 def test_wrap_external_device_memory(cuda_ops, gc_scope):
     torch = pytest.importorskip("torch")
     t = torch.arange(4096, dtype=torch.float32, device="cuda:0")
