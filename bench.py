@@ -399,7 +399,6 @@ def run_sharded_graph(ops, lib, L, D, rank, world, comm, steps, warmup, dist):
     b = ops.createRawFill([cols], 0.0)
     del hx
     graph = ShardedSigmoidGraph(ops, x, w, b, NcclCollective(ops, comm) if comm is not None else None)
-    ms = C.c_float(0)
 
     def one_step():
         with ops.garbageCollector():
@@ -407,31 +406,44 @@ def run_sharded_graph(ops, lib, L, D, rank, world, comm, steps, warmup, dist):
             graph.release_step()
         return out
 
-    for _ in range(max(warmup, 3)):
-        out = one_step()
-    ops.synchronize()
-    if dist is not None:
-        dist.barrier()
-    launches0 = lib.ktc_launch_count()
-    L.check(lib.ktc_timer_start(ops.device))
-    for _ in range(steps):
-        out = one_step()
-    L.check(lib.ktc_timer_stop(ops.device, C.byref(ms)))
-    launches = lib.ktc_launch_count() - launches0
-    # the loss tensor of the last step was released with its graph; gw / gb are the Variables' gradients
-    gw, gb = graph.w.gradient.toArray().reshape(-1), graph.b.gradient.toArray()
-    t = float(ms.value)
-    if dist is not None:
-        import torch
-        tt = torch.tensor([t], dtype=torch.float64)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        t = float(tt[0])
+    def timed(deferred):
+        """`steps` steps, call by call (every raw-tensor call one library call) or with the elementwise
+        calls deferred and fused (kten_b200.lazy)."""
+        ops.lazy = deferred
+        ms = C.c_float(0)
+        for _ in range(max(warmup, 3)):
+            one_step()
+        ops.synchronize()
+        if dist is not None:
+            dist.barrier()
+        launches0 = lib.ktc_launch_count()
+        L.check(lib.ktc_timer_start(ops.device))
+        for _ in range(steps):
+            one_step()
+        L.check(lib.ktc_timer_stop(ops.device, C.byref(ms)))
+        launches = lib.ktc_launch_count() - launches0
+        ops.lazy = False
+        # the loss tensor of the last step was released with its graph; gw / gb are the Variables' gradients
+        gw, gb = graph.w.gradient.toArray().reshape(-1), graph.b.gradient.toArray()
+        t = float(ms.value)
+        if dist is not None:
+            import torch
+            tt = torch.tensor([t], dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            t = float(tt[0])
+        return {"ms_per_step": t / steps, "gelem_per_s": rows * cols / (t / steps) / 1e6,
+                "kernel_launches_per_step": launches / steps,
+                "grad_w_abs_sum": float(np.abs(gw).sum()), "grad_b_abs_sum": float(np.abs(gb).sum())}
+
+    eager = timed(False)
+    fused = timed(True)
     for r in (x, w, b):
         r.release()
-    return {"workload": "x[262144,1024] row-sharded, loss = sum(sigmoid(x*w+b) pow 2), backward + all-reduce of (loss, gw, gb)",
-            "scaling": "strong", "ms_per_step": t / steps, "gelem_per_s": rows * cols / (t / steps) / 1e6,
-            "kernel_launches_per_step": launches / steps, "rows_per_gpu": count,
-            "grad_w_abs_sum": float(np.abs(gw).sum()), "grad_b_abs_sum": float(np.abs(gb).sum())}
+    res = {"workload": "x[262144,1024] row-sharded, loss = sum(sigmoid(x*w+b) pow 2), backward + all-reduce of (loss, gw, gb)",
+           "scaling": "strong", "rows_per_gpu": count}
+    res.update(eager)                                   # the raw-tensor call sequence of kten's autograd, call by call
+    res["deferred"] = fused                             # the same sequence with elementwise calls fused into the sums
+    return res
 
 
 def init_distributed(n_gpus):

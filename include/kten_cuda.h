@@ -219,6 +219,18 @@ KTC_API int ktc_expr_eval(const uint32_t* code, int n_code, const float* imm, in
                           const ktc_buf* stores, int n_stores,
                           int sink, ktc_buf sink_out, int mean);
 
+/* For iteration spaces of at least `expr_jit_min_elems` elements (tunable, default 2^20; tunable
+ * `expr_jit` = 0 turns it off) ktc_expr_eval does not interpret the program: it generates CUDA
+ * source for it -- straight-line code over hardware registers built from the library's own
+ * per-operation arithmetic, so results stay bit-identical --, compiles it once with NVRTC for
+ * sm_100a and caches the kernel by program, as kten-opencl builds its kernels from source at
+ * start-up (OCLKernels.kt).  Without NVRTC the interpreter kernel runs.
+ * ktc_expr_stats fills out6 with: kernels compiled, launches of generated kernels, launches of the
+ * interpreter kernel, failed compilations, microseconds spent compiling, NVRTC present (1 / 0 /
+ * -1 = not tried yet).  ktc_expr_jit_log copies the log of the last failed compilation. */
+KTC_API int ktc_expr_stats(int64_t* out6);
+KTC_API int ktc_expr_jit_log(char* buf, int len);
+
 /* inplaceScatter along an axis with one index per [outer, inner] position:
  * the Max/Min backward (AggregatingFunctions.kt:68-79; JVM:227-256,
  * kernels.cl:521-546).  target is [outer, axis_len, inner]; index and src are
@@ -246,7 +258,13 @@ KTC_API int ktc_tune_set(const char* key, int value);      /* launch-shape tunab
 
 /* ---- test hooks (host-side failure injection; nothing here faults a GPU) ---- */
 KTC_API int ktc_test_inject_comm_error(int n_calls);        /* next n collective calls report KTC_ECOMM */
-KTC_API int ktc_test_bounded_wait(int dev, int64_t limit_ns, int* status); /* waits on a flag nothing sets */
+KTC_API int ktc_test_bounded_wait(int dev, int64_t limit_ns, int* status);
+/* Generates and compiles (NVRTC, no device needed) the kernel for an expression program: the
+ * build check for run-time generated code.  leaf_inner[l] != 0: leaf l varies along the innermost
+ * axis; leaf_fixed[l] != 0: it does not depend on the row.  rank3: three collapsed dimensions.
+ * KTC_ENOTSUP when NVRTC is not installed. */
+KTC_API int ktc_test_expr_compile(const uint32_t* code, int n_code, int n_leaves, const int* leaf_inner, const int* leaf_fixed,
+                                  int rank3, int sink, int64_t* cubin_bytes, double* compile_ms); /* waits on a flag nothing sets */
 
 #ifdef __cplusplus
 }

@@ -72,6 +72,9 @@ _PROTOTYPES = {
     "ktc_reduce_all": (i32, [i32, u64, u64, i64]),
     "ktc_reduce_all_noalloc": (i32, [i32, u64, u64, i64]),
     "ktc_expr_eval": (i32, [C.POINTER(C.c_uint32), i32, p_f32, i32, p_i64, i32, p_u64, p_i64, i32, p_u64, i32, i32, u64, i32]),
+    "ktc_expr_stats": (i32, [p_i64]),
+    "ktc_expr_jit_log": (i32, [C.c_char_p, i32]),
+    "ktc_test_expr_compile": (i32, [C.POINTER(C.c_uint32), i32, i32, C.POINTER(C.c_int), C.POINTER(C.c_int), i32, i32, p_i64, C.POINTER(C.c_double)]),
     "ktc_sum_to_shape": (i32, [u64, p_i64, i32, u64, p_i64, i32]),
     "ktc_scatter_axis": (i32, [u64, u64, u64, i64, i64, i64]),
     "ktc_comm_unique_id": (i32, [C.c_char_p]),

@@ -26,31 +26,11 @@
 // Sums use the accumulation scheme of ktc_reduce.cu (float runs folded into doubles, fixed
 // combination order: eight segments per CTA, then a second pass).
 #include "ktc_accum.cuh"
+#include "ktc_expr_args.h"
+#include "ktc_jit.hpp"
 
 namespace ktc {
 
-constexpr int kExprMaxInstr = KTC_EXPR_MAX_INSTR;
-constexpr int kExprMaxImm = KTC_EXPR_MAX_IMM;
-constexpr int kExprMaxLeaves = KTC_EXPR_MAX_LEAVES;
-constexpr int kExprMaxStores = KTC_EXPR_MAX_STORES;
-constexpr int kExprRegs = KTC_EXPR_REGS;
-
-struct ExprArgs {
-    int n_code;
-    uint32_t code[kExprMaxInstr];          // op | dst << 8 | a << 12 | b << 16 | k << 20
-    float imm[kExprMaxImm];
-    const float* leaf[kExprMaxLeaves];
-    int64_t ls0[kExprMaxLeaves], ls1[kExprMaxLeaves];
-    int ls2[kExprMaxLeaves];               // 0 or 1
-    float* store[kExprMaxStores];
-    int64_t D0, D1, D2;
-    int64_t col_tiles;                     // ceil(D2 / 128)
-    int64_t seg_rows;                      // rows (of D0*D1) per warp
-    int S;                                 // segments of the row space (multiple of 8 for the summing sinks)
-    double* part;                          // partial sums of the summing sinks
-    float* out;                            // final result when a single CTA suffices (unused otherwise)
-    double divisor;                        // > 0: mean
-};
 
 __device__ __forceinline__ float4 f4(float v) { return make_float4(v, v, v, v); }
 #define KTC_EACH(expr_x, expr_y, expr_z, expr_w) make_float4(expr_x, expr_y, expr_z, expr_w)
@@ -191,6 +171,20 @@ static inline int finish_launch_expr(const char* what) {
     return KTC_OK;
 }
 
+// The first pass over the iteration space: the kernel generated for this program when the space is
+// large enough to pay for a compilation (tunable expr_jit_min_elems), else the interpreter.
+static int launch_expr(Device* d, const ExprArgs& a, int n_leaves, int sink, int64_t grid, int64_t total) {
+    if (tune("expr_jit", 1) && total >= (int64_t)tune("expr_jit_min_elems", 1 << 20)) {
+        const int rc = jit_launch(d, a, n_leaves, sink, grid);
+        if (rc != KTC_ENOTSUP) return rc;
+    }
+    jit_count_interpreter_launch();
+    if (sink == KTC_EXPR_STORE_ONLY) k_expr<KTC_EXPR_STORE_ONLY><<<(int)grid, 256, 0, d->stream>>>(a);
+    else if (sink == KTC_EXPR_SUM_ALL) k_expr<KTC_EXPR_SUM_ALL><<<(int)grid, 256, 0, d->stream>>>(a);
+    else k_expr<KTC_EXPR_SUM_ROWS><<<(int)grid, 256, 0, d->stream>>>(a);
+    return finish_launch_expr("expr");
+}
+
 }  // namespace ktc
 
 using namespace ktc;
@@ -302,8 +296,7 @@ extern "C" int ktc_expr_eval(const uint32_t* code, int n_code, const float* imm,
     if (sink == KTC_EXPR_STORE_ONLY) {
         const int64_t grid = (Sg * a.col_tiles + 7) / 8;
         if (grid > 0x7fffffffLL) return fail(KTC_ENOTSUP, "ktc_expr_eval: grid too large");
-        k_expr<KTC_EXPR_STORE_ONLY><<<(int)grid, 256, 0, d->stream>>>(a);
-        return finish_launch_expr("expr(store)");
+        return launch_expr(d, a, n_leaves, sink, grid, total);
     }
     const int64_t groups = Sg / 8;
     const int64_t grid = groups * a.col_tiles;
@@ -312,8 +305,7 @@ extern "C" int ktc_expr_eval(const uint32_t* code, int n_code, const float* imm,
     if (sink == KTC_EXPR_SUM_ALL) {
         a.out = bout.ptr;
         if (grid > 1) { KTC_TRY(scratch.get(d, grid * 2)); a.part = reinterpret_cast<double*>(scratch.ptr); }
-        k_expr<KTC_EXPR_SUM_ALL><<<(int)grid, 256, 0, d->stream>>>(a);
-        KTC_TRY(finish_launch_expr("expr(sum_all)"));
+        KTC_TRY(launch_expr(d, a, n_leaves, sink, grid, total));
         if (grid > 1) {
             if (mean) k_combine_block<1, SumAcc><<<1, 512, 0, d->stream>>>(a.part, bout.ptr, nullptr, 1, (int)grid, total);
             else      k_combine_block<0, SumAcc><<<1, 512, 0, d->stream>>>(a.part, bout.ptr, nullptr, 1, (int)grid, total);
@@ -324,8 +316,7 @@ extern "C" int ktc_expr_eval(const uint32_t* code, int n_code, const float* imm,
     // SUM_ROWS: partial[group][column] then one pass over the groups
     KTC_TRY(scratch.get(d, groups * D[2] * 2));
     a.part = reinterpret_cast<double*>(scratch.ptr);
-    k_expr<KTC_EXPR_SUM_ROWS><<<(int)grid, 256, 0, d->stream>>>(a);
-    KTC_TRY(finish_launch_expr("expr(sum_rows)"));
+    KTC_TRY(launch_expr(d, a, n_leaves, sink, grid, total));
     if (groups >= 64 || D[2] < 4096) {
         const int64_t blocks = (D[2] * 32 + 255) / 256;
         k_combine_warp<0, SumAcc><<<(int)blocks, 256, 0, d->stream>>>(a.part, bout.ptr, nullptr, D[2], (int)groups, rows);

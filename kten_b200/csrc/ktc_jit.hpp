@@ -1,0 +1,15 @@
+// ktc_jit.hpp -- run-time generated variants of the fused expression kernel (ktc_jit.cu).
+#pragma once
+
+#include "ktc_expr_args.h"
+#include "ktc_internal.hpp"
+
+namespace ktc {
+
+// Launches the kernel generated for a's program on d's compute stream with the grid of k_expr.
+// KTC_OK: launched.  KTC_ENOTSUP: no generated kernel for this program (NVRTC missing, compilation
+// failed): the caller runs the interpreter kernel.  Other codes: launch errors.
+int jit_launch(Device* d, const ExprArgs& a, int n_leaves, int sink, int64_t grid);
+void jit_count_interpreter_launch();
+
+}  // namespace ktc

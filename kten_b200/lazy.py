@@ -1,0 +1,270 @@
+"""Deferred elementwise expressions behind the RawTensor SPI.
+
+kten's autograd issues one raw-tensor call per line of doForward / doBackward
+(kten-api/.../autograd/functions/BasicFunctions.kt, PointwiseFunctions.kt,
+AggregatingFunctions.kt); executed one by one, the sharded-graph step of the benchmark
+moves 34 tensor volumes through HBM.  With `ops.lazy = True` a CUDARawTensor produced by
+an elementwise call holds an expression node instead of storage; the expression is
+compiled into a program for `ktc_expr_eval` when a value is needed -- a host read, a sum
+(`sum()`, `mean()`, the leading-axis sums of mayUnexpand), or any call outside the
+elementwise set.  Every instruction of the program is one of the library's reference
+operations with its own rounding, so results equal the call-by-call execution bit for
+bit; only the order of summation inside a fused sum differs (within the reduction
+tolerance, exact on exactly summable data).
+
+Rules that keep the semantics of the eager backend:
+  * nodes are immutable; an in-place call on a deferred tensor replaces its node, an
+    in-place call on a stored tensor is evaluated at once into its own buffer;
+  * before a stored tensor is written in place, every deferred tensor that reads it is
+    evaluated (a registry maps buffers to the deferred tensors depending on them);
+  * a shallow copy of a deferred tensor evaluates it first, so aliases keep sharing
+    storage exactly as in the eager backend;
+  * an interior node is recomputed inside at most `ops.recomputeLimit` programs (recomputing a
+    short chain from an operand that is read anyway costs no memory traffic); the next
+    evaluation, if its tensor is still alive, stores it as a side output and later programs
+    read it from memory.
+Whatever the kernel does not fuse (more than three collapsed dimensions, an innermost
+extent that is not a multiple of four, programs beyond its size limits) falls back to
+the library's separate calls -- never to the host.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import weakref
+from typing import Dict, List, Optional, Sequence, Tuple
+
+from . import _lib as L
+from . import shape_functions as SF
+
+BIN_X = {L.PLUS: L.X_ADD, L.MINUS: L.X_SUB, L.TIMES: L.X_MUL, L.DIV: L.X_DIV, L.POW: L.X_POW}
+UN_X = {L.EXP: L.X_EXP, L.LOG: L.X_LOG, L.TANH: L.X_TANH, L.SIGMOID: L.X_SIGMOID, L.RECIPROCAL: L.X_RCP, L.NEG: L.X_NEG}
+CMP_X = {L.LT: L.X_CMP_LT, L.LTE: L.X_CMP_LTE, L.GT: L.X_CMP_GT, L.GTE: L.X_CMP_GTE}
+
+
+class BufferRef:
+    """One retained reference on a library buffer, dropped when the last node using it dies."""
+
+    __slots__ = ("lib", "handle", "__weakref__")
+
+    def __init__(self, lib, handle: int, retain: bool = True):
+        self.lib, self.handle = lib, handle
+        if retain:
+            L.check(lib.ktc_retain(handle))
+
+    def __del__(self):
+        try:
+            self.lib.ktc_release(self.handle)
+        except Exception:
+            pass
+
+
+class Node:
+    """kind: leaf | const | un | bin | clamp | cmp | square | bcast.  Immutable value; `buf` is set
+    once the value has been written to memory (the node then acts as a leaf)."""
+
+    __slots__ = ("kind", "op", "args", "shape", "imm", "buf", "leaves", "evals", "owner", "parents", "__weakref__")
+
+    def __init__(self, kind, shape, op=0, args=(), imm=(), buf: Optional[BufferRef] = None):
+        self.kind, self.op, self.args, self.shape, self.imm, self.buf = kind, op, tuple(args), list(shape), tuple(imm), buf
+        self.evals = 0
+        self.owner = None                      # weakref to the storage cell (raw_tensor._Cell) waiting for this value
+        self.parents = weakref.WeakSet()
+        handles = set()
+        if buf is not None:
+            handles.add(buf.handle)
+        for a in self.args:
+            handles |= ({a.buf.handle} if a.buf is not None else a.leaves)
+            a.parents.add(self)
+        self.leaves = handles                  # buffers this value is read from (grows when a descendant is stored)
+
+    def stored(self) -> bool:
+        return self.buf is not None
+
+    def ancestors(self):
+        seen, stack = set(), list(self.parents)
+        while stack:
+            n = stack.pop()
+            if id(n) in seen:
+                continue
+            seen.add(id(n))
+            yield n
+            stack.extend(n.parents)
+
+    def set_stored(self, buf: BufferRef, registry) -> None:
+        """The value now lives in `buf`: forget how it was computed, and make everything that is
+        computed from it depend on the new buffer."""
+        self.buf = buf
+        self.args = ()
+        for anc in self.ancestors():
+            anc.leaves.add(buf.handle)
+            cell = anc.owner() if anc.owner is not None else None
+            if cell is not None:
+                registry.setdefault(buf.handle, weakref.WeakSet()).add(cell)
+
+
+def leaf(lib, handle: int, shape) -> Node:
+    return Node("leaf", shape, buf=BufferRef(lib, handle))
+
+
+def const(value: float) -> Node:
+    return Node("const", [1], imm=(float(value),))
+
+
+class NotFusable(Exception):
+    pass
+
+
+class Program:
+    def __init__(self, shape):
+        self.shape = list(shape)
+        self.code: List[int] = []
+        self.imm: List[float] = []
+        self.leaves: List[Tuple[int, List[int]]] = []       # (handle, right-aligned shape)
+        self.n_stores = 0
+        self.free = list(range(L.EXPR_REGS - 1, -1, -1))
+
+    def emit(self, op, d=0, a=0, b=0, k=0):
+        if len(self.code) >= L.EXPR_MAX_INSTR:
+            raise NotFusable("program too long")
+        self.code.append(op | (d << 8) | (a << 12) | (b << 16) | (k << 20))
+
+    def imm_index(self, values) -> int:
+        if len(self.imm) + len(values) > L.EXPR_MAX_IMM:
+            raise NotFusable("too many immediates")
+        k = len(self.imm)
+        self.imm.extend(values)
+        return k
+
+    def leaf_index(self, handle, shape) -> int:
+        nd = len(self.shape)
+        padded = [1] * (nd - len(shape)) + list(shape)
+        if len(padded) != nd:
+            raise NotFusable("leaf has more dimensions than the iteration space")
+        for i, (h, s) in enumerate(self.leaves):
+            if h == handle and s == padded:
+                return i
+        if len(self.leaves) >= L.EXPR_MAX_LEAVES:
+            raise NotFusable("too many leaves")
+        self.leaves.append((handle, padded))
+        return len(self.leaves) - 1
+
+    def alloc(self) -> int:
+        if not self.free:
+            raise NotFusable("out of registers")
+        return self.free.pop()
+
+
+def strip(n: Node) -> Node:
+    """Look through broadcast markers: they change the shape, not the value of an element."""
+    while n.kind == "bcast" and not n.stored():
+        n = n.args[0]
+    return n
+
+
+def _toposort(roots: Sequence[Node]) -> Tuple[List[Node], Dict[int, int]]:
+    order, uses, seen = [], {}, set()
+
+    def visit(n: Node):
+        n = strip(n)
+        uses[id(n)] = uses.get(id(n), 0) + 1
+        if id(n) in seen:
+            return
+        seen.add(id(n))
+        if not n.stored():
+            for a in n.args:
+                visit(a)
+        order.append(n)
+
+    for r in roots:
+        visit(r)
+    return order, uses
+
+
+def compile_program(shape, stores: Sequence[Node], acc: Optional[Node], side_candidates: int):
+    """Linearise the DAG under `stores` + `acc` into a register program over the iteration
+    space `shape`.  Returns (Program, nodes written by STORE, in store-index order; the first
+    len(stores) entries are the requested ones).  `side_candidates`: 0 = store nothing but what was
+    asked for; k > 0 = a value that was already computed k times, and that a tensor still waits for,
+    is stored on the side.  Raises NotFusable."""
+    prog = Program(shape)
+    sinks = [strip(n) for n in stores] + ([strip(acc)] if acc is not None else [])
+    order, uses = _toposort(sinks)
+    reg: Dict[int, int] = {}
+    store_nodes: List[Node] = [strip(n) for n in stores]
+    n_requested = len(store_nodes)
+    full_volume = SF.to_store_size(shape)
+    acc_node = strip(acc) if acc is not None else None
+    # An interior node that was evaluated `side_candidates` times before and whose tensor still waits
+    # for it is stored on the way (the tensor then owns storage and later programs load it): the
+    # recomputation of any value is bounded, and so is the work on graphs that reuse values deeply.  Nodes below such a node are not
+    # candidates: nothing reaches them any more once it is in memory.
+    if side_candidates:
+        seen, stack = set(), list(sinks)
+        while stack:
+            n = strip(stack.pop())
+            if id(n) in seen or n.stored() or n.kind in ("const", "leaf"):
+                continue
+            seen.add(id(n))
+            cell = n.owner() if n.owner is not None else None
+            if not any(n is s for s in sinks) and n.evals >= side_candidates and cell is not None and cell.store is None \
+                    and cell.node is n and SF.to_store_size(n.shape) == full_volume \
+                    and len(store_nodes) < L.EXPR_MAX_STORES:
+                store_nodes.append(n)
+                uses[id(n)] += 1
+                continue
+            stack.extend(n.args)
+
+    def release_use(n: Node):
+        uses[id(n)] -= 1
+        if uses[id(n)] == 0:
+            prog.free.append(reg[id(n)])
+
+    for n in order:
+        if n.stored():
+            d = prog.alloc()
+            prog.emit(L.X_LOAD, d, k=prog.leaf_index(n.buf.handle, n.shape))
+        elif n.kind == "const":
+            d = prog.alloc()
+            prog.emit(L.X_CONST, d, k=prog.imm_index([n.imm[0]]))
+        else:
+            children = [strip(a) for a in n.args]
+            srcs = [reg[id(c)] for c in children]
+            for c in children:
+                release_use(c)
+            d = prog.alloc()                    # may reuse a source register: the kernel reads before it writes
+            if n.kind == "bin":
+                prog.emit(BIN_X[n.op], d, srcs[0], srcs[1])
+            elif n.kind == "un":
+                prog.emit(UN_X[n.op], d, srcs[0])
+            elif n.kind == "square":
+                prog.emit(L.X_SQUARE, d, srcs[0])
+            elif n.kind == "clamp":
+                prog.emit(L.X_CLAMP, d, srcs[0], k=prog.imm_index(list(n.imm)))
+            elif n.kind == "cmp":
+                prog.emit(CMP_X[n.op], d, srcs[0], k=prog.imm_index([n.imm[0]]))
+            else:
+                raise NotFusable(f"unknown node kind {n.kind}")
+        reg[id(n)] = d
+        for k, sn in enumerate(store_nodes):
+            if sn is n:
+                prog.emit(L.X_STORE, a=d, k=k)
+                release_use(n)
+        if acc_node is not None and n is acc_node:
+            prog.emit(L.X_ACC, a=d)
+            release_use(n)
+    prog.n_stores = len(store_nodes)
+    return prog, store_nodes, n_requested
+
+
+def run_program(ops, prog: Program, store_handles: Sequence[int], sink: int, sink_out: int, mean: bool) -> int:
+    lib = ops.lib
+    nd = len(prog.shape)
+    code = (C.c_uint32 * len(prog.code))(*prog.code)
+    imm = (C.c_float * max(1, len(prog.imm)))(*prog.imm)
+    shape = (C.c_int64 * nd)(*prog.shape)
+    nl = len(prog.leaves)
+    leaves = (C.c_uint64 * max(1, nl))(*[h for h, _ in prog.leaves])
+    lshapes = (C.c_int64 * max(1, nl * nd))(*[d for _, s in prog.leaves for d in s])
+    stores = (C.c_uint64 * max(1, len(store_handles)))(*store_handles)
+    return lib.ktc_expr_eval(code, len(prog.code), imm, len(prog.imm), shape, nd, leaves, lshapes, nl,
+                             stores, len(store_handles), sink, sink_out, 1 if mean else 0)

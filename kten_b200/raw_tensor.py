@@ -25,17 +25,49 @@ from . import _lib as L
 from . import shape_functions as SF
 
 
-class CUDARawTensor:
-    __slots__ = ("shape", "storeReference", "ops", "refCount", "mustSurviveGC", "_released")
+class _Cell:
+    """Storage slot of one or more tensors: a buffer handle (one owned reference), or a pending
+    expression, or both (the node then is the cached leaf for the buffer).  Shallow copies of a
+    deferred tensor share the cell, so that they end up sharing storage exactly as in the
+    reference; every other tensor has a cell of its own."""
 
-    def __init__(self, shape: Sequence[int], store: int, ops: "CUDATensorOperations"):
+    __slots__ = ("store", "node", "share", "__weakref__")
+
+    def __init__(self, store, node):
+        self.store, self.node, self.share = store, node, 1
+
+
+class CUDARawTensor:
+    __slots__ = ("shape", "_cell", "ops", "refCount", "mustSurviveGC", "_released", "__weakref__")
+
+    def __init__(self, shape: Sequence[int], store: Optional[int], ops: "CUDATensorOperations", node=None, cell=None):
         self.shape: List[int] = [int(d) for d in shape]
-        self.storeReference: int = store          # ktc_buf handle (holds one reference)
+        if cell is None:
+            cell = _Cell(store, node)               # store: ktc_buf handle (one reference); None while deferred
+        else:
+            cell.share += 1
+        self._cell = cell
         self.ops = ops
         self.refCount = 1
         self.mustSurviveGC = False
         self._released = False
         ops._instance_created(self)
+
+    @property
+    def _store(self) -> Optional[int]:
+        return self._cell.store
+
+    @_store.setter
+    def _store(self, h) -> None:
+        self._cell.store = h
+
+    @property
+    def _node(self):
+        return self._cell.node
+
+    @_node.setter
+    def _node(self, n) -> None:
+        self._cell.node = n
 
     # ---- bookkeeping -------------------------------------------------------
     @property
@@ -46,10 +78,21 @@ class CUDARawTensor:
     def size(self) -> int:
         return SF.to_store_size(self.shape)
 
+    @property
+    def isDeferred(self) -> bool:
+        return self._store is None and self._node is not None
+
+    @property
+    def storeReference(self) -> int:
+        """The buffer handle; a deferred tensor is evaluated first."""
+        return self._buf()
+
     def _buf(self) -> int:
         if self._released:
             raise RuntimeError("Raw tensor already released")   # OCLMemoryObject.kt:167-170
-        return self.storeReference
+        if self._store is None:
+            self.ops._materialize(self)
+        return self._store
 
     def incrementRef(self) -> None:
         self.refCount += 1
@@ -62,13 +105,34 @@ class CUDARawTensor:
         if not self.mustSurviveGC:
             self.refCount -= 1
         if self.refCount <= 0:
-            L.check(self.ops.lib.ktc_release(self.storeReference))
+            cell = self._cell
+            cell.share -= 1
+            if cell.share <= 0:
+                if cell.store is not None:
+                    L.check(self.ops.lib.ktc_release(cell.store))
+                cell.node = None
             self._released = True
             return True
         return False
 
     def _new(self, shape: Sequence[int]) -> "CUDARawTensor":
         return self.ops.createRaw(list(shape))
+
+    def _as_node(self):
+        """This tensor as an operand of a deferred expression."""
+        from . import lazy
+        if self._released:
+            raise RuntimeError("Raw tensor already released")
+        if self._store is None:
+            return self._node
+        if self._node is None or not self._node.stored() or self._node.buf.handle != self._store or self._node.shape != self.shape:
+            self._node = lazy.leaf(self.ops.lib, self._store, self.shape)
+        return self._node
+
+    def _before_inplace_write(self) -> None:
+        """Deferred tensors that read this buffer are evaluated before it changes."""
+        if self._store is not None:
+            self.ops._flush_dependents(self._store)
 
     # ---- host reads ----------------------------------------------------------
     def toArray(self) -> np.ndarray:
@@ -101,6 +165,9 @@ class CUDARawTensor:
     def _binary(self, op: int, other: "CUDARawTensor") -> "CUDARawTensor":
         """elementwiseOpOnTensors (JVMRawTensor.kt:81-87) without materialising the
         broadcast operand."""
+        if self.ops.lazy:
+            common = self.shape if self.shape == other.shape else SF.infer_implicit_broadcast_shape(self.shape, other.shape)
+            return self.ops._deferred("bin", common, op, (self._as_node(), other._as_node()))
         if self.shape == other.shape:
             res = self._new(self.shape)
             L.check(self.ops.lib.ktc_binary(op, res._buf(), self._buf(), other._buf(), self.size))
@@ -117,17 +184,41 @@ class CUDARawTensor:
         if self.shape != other.shape:
             raise ValueError("Shapes does not match for inplace operation on tensors with shapes: "
                              f"{self.shape} and {other.shape}.")
+        if self.ops.lazy:
+            self.ops._deferred_assign(self, "bin", op, (self._as_node(), other._as_node()))
+            return
+        self._before_inplace_write()
         L.check(self.ops.lib.ktc_binary_inplace(op, self._buf(), other._buf(), self.size))
 
+    def _scalar_node(self, op: int, s: float, scalar_first: bool):
+        from . import lazy
+        me = self._as_node()
+        if op == L.POW and not scalar_first and float(s) == 2.0:
+            return "square", 0, (me,)
+        args = (lazy.const(s), me) if scalar_first else (me, lazy.const(s))
+        return "bin", op, args
+
     def _scalar(self, op: int, s: float, scalar_first: bool = False) -> "CUDARawTensor":
+        if self.ops.lazy:
+            if op == L.POW and not scalar_first and float(s) == 1.0:
+                return self.ops._deferred_alias(self)
+            kind, o, args = self._scalar_node(op, s, scalar_first)
+            return self.ops._deferred(kind, self.shape, o, args)
         res = self._new(self.shape)
         L.check(self.ops.lib.ktc_scalar(op, res._buf(), self._buf(), float(s), self.size, 1 if scalar_first else 0))
         return res
 
     def _scalar_assign(self, op: int, s: float) -> None:
+        if self.ops.lazy:
+            kind, o, args = self._scalar_node(op, s, False)
+            self.ops._deferred_assign(self, kind, o, args)
+            return
+        self._before_inplace_write()
         L.check(self.ops.lib.ktc_scalar_inplace(op, self._buf(), float(s), self.size))
 
     def _unary(self, op: int) -> "CUDARawTensor":
+        if self.ops.lazy:
+            return self.ops._deferred("un", self.shape, op, (self._as_node(),))
         res = self._new(self.shape)
         L.check(self.ops.lib.ktc_unary(op, res._buf(), self._buf(), self.size))
         return res
@@ -181,11 +272,15 @@ class CUDARawTensor:
         return self._unary(L.SIGMOID)
 
     def clamp(self, min: float, max: float):
+        if self.ops.lazy:
+            return self.ops._deferred("clamp", self.shape, 0, (self._as_node(),), imm=(float(min), float(max)))
         res = self._new(self.shape)
         L.check(self.ops.lib.ktc_clamp(res._buf(), self._buf(), float(min), float(max), self.size))
         return res
 
     def _compare(self, op: int, value: float):
+        if self.ops.lazy:
+            return self.ops._deferred("cmp", self.shape, op, (self._as_node(),), imm=(float(value),))
         res = self._new(self.shape)
         L.check(self.ops.lib.ktc_compare_scalar(op, res._buf(), self._buf(), float(value), self.size))
         return res
@@ -209,6 +304,8 @@ class CUDARawTensor:
         if self.shape == shape:
             return self
         SF.infer_explicit_broadcast_shape(self.shape, shape)
+        if self.ops.lazy:
+            return self.ops._deferred("bcast", shape, 0, (self._as_node(),))
         res = self._new(shape)
         so, no = L.shape_array(shape)
         sa, na = L.shape_array(self.shape)
@@ -219,8 +316,12 @@ class CUDARawTensor:
         """copy(shallow) (JVMRawTensor.kt:257-262; OCLRawTensor.kt:252-258): a shallow
         copy shares the storage (one more reference on the buffer)."""
         if shallow:
+            if self.isDeferred:                                 # aliases share the pending value, later its storage
+                return CUDARawTensor(self.shape, None, self.ops, cell=self._cell)
             L.check(self.ops.lib.ktc_retain(self._buf()))
-            return CUDARawTensor(self.shape, self.storeReference, self.ops)
+            return CUDARawTensor(self.shape, self._store, self.ops)
+        if self.isDeferred:
+            return self.ops._deferred_alias(self)               # nodes are immutable values: a deep copy can share one
         res = self._new(self.shape)
         L.check(self.ops.lib.ktc_d2d(res._buf(), 0, self._buf(), 0, self.size))
         return res
@@ -229,7 +330,7 @@ class CUDARawTensor:
         """view (JVMRawTensor.kt:264-268): same storage, new shape."""
         new_shape = SF.reshape(self.shape, shape)
         L.check(self.ops.lib.ktc_retain(self._buf()))
-        return CUDARawTensor(new_shape, self.storeReference, self.ops)
+        return CUDARawTensor(new_shape, self._store, self.ops)
 
     def reshape(self, shape: Sequence[int]) -> "CUDARawTensor":
         """reshape (ART:79-84): a deep copy with the new shape."""
@@ -239,9 +340,11 @@ class CUDARawTensor:
         return res
 
     def inplaceReshape(self, shape: Sequence[int]) -> None:
+        self._buf()                                             # a deferred expression is tied to its shape
         self.shape = SF.reshape(self.shape, shape)
 
     def inplaceSqueeze(self, axis: int) -> None:
+        self._buf()
         s = list(self.shape)
         del s[SF.normalize_axis(self.shape, axis)]
         self.shape = s
@@ -252,6 +355,7 @@ class CUDARawTensor:
         return res
 
     def inplaceUnsqueeze(self, axis: int) -> None:
+        self._buf()
         self.shape = SF.unsqueeze(self.shape, axis)
 
     def unsqueeze(self, axis: int):
@@ -260,6 +364,12 @@ class CUDARawTensor:
         return res
 
     def inplaceFill(self, value: float) -> None:
+        if self.isDeferred:                                     # the pending value is overwritten: just take storage
+            self._node = None
+            h = C.c_uint64(0)
+            L.check(self.ops.lib.ktc_alloc(self.ops.device, self.size, C.byref(h)))
+            self._store = h.value
+        self._before_inplace_write()
         L.check(self.ops.lib.ktc_fill(self._buf(), 0, self.size, float(value)))
 
     # ---- reductions --------------------------------------------------------------
@@ -269,8 +379,13 @@ class CUDARawTensor:
         a = SF.normalize_axis(self.shape, axis)
         res_shape = SF.aggregate_over(self.shape, a, True)
         outer, length, inner = SF.collapse_axis(self.shape, a)
-        res = self._new(res_shape)
-        L.check(self.ops.lib.ktc_reduce_axis(op, res._buf(), self._buf(), outer, length, inner))
+        res = None
+        if self.isDeferred and op == L.SUM and a == 0 and len(self.shape) >= 2:
+            res = self.ops._sum_leading_axis(self)              # fused with the pending expression when possible
+        if res is None:
+            res = self._new(res_shape)
+            L.check(self.ops.lib.ktc_reduce_axis(op, res._buf(), self._buf(), outer, length, inner))
+        res.shape = list(res_shape)
         if not keep_dimensions and len(res_shape) > 1:
             del res_shape[a]
             res.shape = res_shape
@@ -278,6 +393,10 @@ class CUDARawTensor:
 
     def sum(self, axis: Optional[int] = None, keepDimensions: bool = False):
         if axis is None:
+            if self.isDeferred:
+                res = self.ops._sum_all(self, mean=False)
+                if res is not None:
+                    return res
             res = self._new([1])                     # sum() -> shape [1] (JVMRawTensor.kt:146-148)
             L.check(self.ops.lib.ktc_reduce_all(L.SUM, res._buf(), self._buf(), self.size))
             return res
@@ -285,6 +404,10 @@ class CUDARawTensor:
 
     def mean(self, axis: Optional[int] = None, keepDimensions: bool = False):
         if axis is None:
+            if self.isDeferred:
+                res = self.ops._sum_all(self, mean=True)
+                if res is not None:
+                    return res
             res = self._new([1])                     # mean() -> shape [1] (JVMRawTensor.kt:150-152)
             L.check(self.ops.lib.ktc_reduce_all(L.MEAN, res._buf(), self._buf(), self.size))
             return res
@@ -336,7 +459,10 @@ class CUDARawTensor:
         if index.shape[a] != 1 or index.shape != src.shape:
             raise NotImplementedError("kten-cuda scatters one index per position along the axis (selection backward)")
         outer, length, inner = SF.collapse_axis(self.shape, a)
+        self._buf()
+        self._before_inplace_write()
         L.check(self.ops.lib.ktc_scatter_axis(self._buf(), index._buf(), src._buf(), outer, length, inner))
 
     def __repr__(self) -> str:
-        return f"CUDARawTensor(shape={self.shape}, buf=0x{self.storeReference:x}, refs={self.refCount})"
+        where = "deferred" if self.isDeferred else f"buf=0x{(self._store or 0):x}"
+        return f"CUDARawTensor(shape={self.shape}, {where}, refs={self.refCount})"

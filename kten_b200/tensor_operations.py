@@ -13,11 +13,13 @@ from __future__ import annotations
 
 import ctypes as C
 import threading
+import weakref
 from typing import Callable, List, Optional, Sequence
 
 import numpy as np
 
 from . import _lib as L
+from . import lazy as Z
 from . import shape_functions as SF
 from .raw_tensor import CUDARawTensor
 
@@ -65,6 +67,13 @@ class CUDATensorOperations:
         self.deviceName, self.totalMemory, self.smCount = name.value.decode(), mem.value, sms.value
         self.platformKey = f"CUDA - {device} - {self.deviceName}"
         self._tls = threading.local()
+        # deferred elementwise expressions (kten_b200.lazy): off = every call runs at once, like kten-jvm
+        self.lazy = False
+        self._deps = {}                     # buffer handle -> WeakSet of storage cells whose pending expressions read it
+        self._deps_purge_at = 1024
+        self.recomputeLimit = 2             # a pending value is recomputed at most this often before it is stored
+        self.fusedEvaluations = 0           # programs run by ktc_expr_eval
+        self.unfusedEvaluations = 0         # deferred expressions that fell back to separate calls
 
     # ---- GC scope ----------------------------------------------------------------
     def _collector(self) -> Optional[list]:
@@ -104,7 +113,7 @@ class CUDATensorOperations:
                 host = np.ascontiguousarray(np.asarray(init, dtype=np.float32).reshape(-1))
                 if host.size != n:
                     raise ValueError(f"init holds {host.size} values, shape {shape} needs {n}")
-            L.check(self.lib.ktc_h2d(raw.storeReference, 0, host.ctypes.data_as(C.c_void_p), n, 1))
+            L.check(self.lib.ktc_h2d(raw._store, 0, host.ctypes.data_as(C.c_void_p), n, 1))
         return raw
 
     def createRawFill(self, shape: Sequence[int], constant: float) -> CUDARawTensor:
@@ -117,6 +126,242 @@ class CUDATensorOperations:
 
     def zeroOut(self, raw: CUDARawTensor) -> None:
         raw.inplaceFill(0.0)
+
+    # ---- deferred expressions (kten_b200.lazy) ------------------------------------------------
+    # A deferred tensor's cell holds an expression node instead of a buffer.  `_deps` maps a buffer
+    # handle to the cells whose pending expressions read it, so that an in-place write to the buffer
+    # can evaluate them first.
+    def _register(self, cell, node) -> None:
+        node.owner = weakref.ref(cell)
+        for h in node.leaves:
+            self._deps.setdefault(h, weakref.WeakSet()).add(cell)
+        if len(self._deps) > self._deps_purge_at:
+            self._deps = {h: ws for h, ws in self._deps.items() if len(ws)}
+            self._deps_purge_at = max(1024, 2 * len(self._deps))
+
+    def _deferred(self, kind, shape, op, args, imm=()) -> CUDARawTensor:
+        node = Z.Node(kind, shape, op, args, imm)
+        t = CUDARawTensor(shape, None, self, node=node)
+        self._register(t._cell, node)
+        return t
+
+    def _deferred_alias(self, src: CUDARawTensor) -> CUDARawTensor:
+        """A new tensor with the same value and storage of its own (a deep copy that is not made yet)."""
+        return self._deferred("bcast", src.shape, 0, (src._as_node(),))
+
+    def _deferred_assign(self, target: CUDARawTensor, kind, op, args, imm=()) -> None:
+        """target = f(target, ...) in place: a deferred target takes the new node; a stored target is
+        evaluated now, into its own buffer."""
+        node = Z.Node(kind, target.shape, op, args, imm)
+        if target.isDeferred:
+            target._node = node
+            self._register(target._cell, node)
+            return
+        h = target._buf()
+        self._flush_dependents(h)
+        if self._try_fused(target.shape, [node], [h], [False]):
+            return
+        self.unfusedEvaluations += 1
+        n = target.size
+        if kind == "square":
+            L.check(self.lib.ktc_scalar_inplace(L.POW, h, 2.0, n))
+            return
+        other = Z.strip(args[1])
+        if other.kind == "const":
+            L.check(self.lib.ktc_scalar_inplace(op, h, other.imm[0], n))
+        else:
+            hb, shp = self._force(other)
+            if SF.to_store_size(shp) != n:                         # a broadcast marker over a smaller value
+                tmp = self._alloc_handle(n)
+                try:
+                    self._eager_into(args[1], target.shape, tmp)
+                    L.check(self.lib.ktc_binary_inplace(op, h, tmp, n))
+                finally:
+                    self.lib.ktc_release(tmp)
+            else:
+                L.check(self.lib.ktc_binary_inplace(op, h, hb, n))
+
+    def _flush_dependents(self, handle: int) -> None:
+        cells = self._deps.pop(handle, None)
+        if not cells:
+            return
+        for cell in list(cells):
+            if cell.store is None and cell.node is not None and cell.share > 0 and handle in cell.node.leaves:
+                self._materialize_cell(cell)
+
+    def _alloc_handle(self, n: int) -> int:
+        h = C.c_uint64(0)
+        L.check(self.lib.ktc_alloc(self.device, n, C.byref(h)))
+        return h.value
+
+    def _adopt(self, node, handle: int) -> None:
+        """`handle` (one owned reference) now holds node's value: the node keeps it, and the cell that
+        owns the node -- if it is still waiting for exactly this value -- takes it as its storage."""
+        cell = node.owner() if node.owner is not None else None
+        if cell is not None and cell.store is None and cell.node is node and cell.share > 0:
+            cell.store = handle                                                  # the cell takes the owned reference,
+            node.set_stored(Z.BufferRef(self.lib, handle), self._deps)           # the node retains one of its own
+        else:
+            node.set_stored(Z.BufferRef(self.lib, handle, retain=False), self._deps)
+
+    def _try_fused(self, shape, stores, handles, own, acc=None, sink=None, sink_out=0, mean=False, reshape=None) -> bool:
+        """Compile `stores` (+ the summed node `acc`) and run them as one kernel.  handles[i] receives
+        stores[i]; own[i]: the handle is a fresh buffer that node i adopts.  Nodes stored on the side
+        get fresh buffers.  False: not fusable, nothing was run."""
+        try:
+            prog, store_nodes, n_req = Z.compile_program(shape, stores, acc, side_candidates=self.recomputeLimit)
+            if reshape is not None and not reshape(prog):
+                return False
+        except Z.NotFusable:
+            return False
+        total = SF.to_store_size(shape)
+        extra = [self._alloc_handle(total) for _ in store_nodes[n_req:]]
+        rc = Z.run_program(self, prog, list(handles) + extra, L.EXPR_STORE_ONLY if sink is None else sink, sink_out, mean)
+        if rc != L.KTC_OK:
+            for h in extra:
+                self.lib.ktc_release(h)
+            if rc == L.KTC_ENOTSUP:
+                return False
+            L.check(rc)
+        self.fusedEvaluations += 1
+        order, _ = Z._toposort([Z.strip(r) for r in list(stores) + ([acc] if acc is not None else [])])
+        for nd in order:
+            nd.evals += 1
+        for nd, h, o in zip(store_nodes[:n_req], handles, own):
+            if o:
+                self._adopt(nd, h)
+        for nd, h in zip(store_nodes[n_req:], extra):
+            self._adopt(nd, h)
+        return True
+
+    def _force(self, node):
+        """Make sure the value under `node` (looking through broadcast markers) is in memory; returns
+        (handle, shape).  The handle stays valid while the node is alive."""
+        nd = Z.strip(node)
+        if not nd.stored():
+            h = self._alloc_handle(SF.to_store_size(nd.shape))
+            if not self._try_fused(nd.shape, [nd], [h], [True]):
+                self.unfusedEvaluations += 1
+                self._eager_into(nd, nd.shape, h)
+                self._adopt(nd, h)
+        return nd.buf.handle, nd.shape
+
+    def _materialize(self, t: CUDARawTensor) -> None:
+        """Give a deferred tensor storage."""
+        self._materialize_cell(t._cell)
+
+    def _materialize_cell(self, cell) -> None:
+        node = cell.node
+        if Z.strip(node) is node and not node.stored():
+            self._force(node)                                       # adopted by the cell through node.owner
+            if cell.store is None:
+                raise RuntimeError("deferred tensor did not receive its storage")
+            return
+        # an alias of / a broadcast over another value: storage of its own
+        h = self._alloc_handle(SF.to_store_size(node.shape))
+        if not self._try_fused(node.shape, [node], [h], [False]):
+            self.unfusedEvaluations += 1
+            self._eager_into(node, node.shape, h)
+        cell.store, cell.node = h, None
+
+    def _sum_all(self, t: CUDARawTensor, mean: bool) -> Optional[CUDARawTensor]:
+        """sum() / mean() of a deferred tensor fused with its expression; None: not fusable."""
+        out = self.createRaw([1])
+        if self._try_fused(t.shape, [], [], [], acc=t._node, sink=L.EXPR_SUM_ALL, sink_out=out._store, mean=mean):
+            return out
+        out.release()
+        return None
+
+    def _sum_leading_axis(self, t: CUDARawTensor) -> Optional[CUDARawTensor]:
+        """sum over axis 0 of a deferred [A, ...] tensor fused with its expression (the leading-axis
+        sums of mayUnexpand, Utils.kt:14-41): the iteration space is viewed as [A, rest], possible when
+        every operand is either full or broadcast over the trailing dimensions."""
+        rest = SF.to_store_size(t.shape[1:])
+        full_tail = list(t.shape[1:])
+
+        def as_rows(prog) -> bool:
+            leaves2 = []
+            for h, s in prog.leaves:
+                if s[1:] == full_tail:
+                    leaves2.append((h, [s[0], rest]))
+                elif all(d == 1 for d in s[1:]):
+                    leaves2.append((h, [s[0], 1]))
+                else:
+                    return False
+            prog.shape, prog.leaves = [t.shape[0], rest], leaves2
+            return True
+
+        out = self.createRaw([rest])
+        if self._try_fused(t.shape, [], [], [], acc=t._node, sink=L.EXPR_SUM_ROWS, sink_out=out._store, reshape=as_rows):
+            return out
+        out.release()
+        return None
+
+    def _eager_into(self, node, shape, out_handle: int) -> None:
+        """One step of the call-by-call evaluation: the operands of `node` are forced into memory
+        (each as a fused program where possible), then the library call for `node` itself runs at the
+        operation's natural shape -- the common shape of its operands with broadcast markers looked
+        through -- and the result is spread to `shape` if that is larger."""
+        lib = self.lib
+        nd = Z.strip(node)
+        n = SF.to_store_size(shape)
+
+        def spread(h, shp):
+            if SF.to_store_size(shp) == n:
+                L.check(lib.ktc_d2d(out_handle, 0, h, 0, n))
+            else:
+                so, no = L.shape_array(shape)
+                sa, na = L.shape_array(shp)
+                L.check(lib.ktc_broadcast_to(out_handle, so, no, h, sa, na))
+
+        if nd.stored():
+            spread(nd.buf.handle, nd.shape)
+            return
+        kids = [Z.strip(c) for c in nd.args]
+        tensors = [c for c in kids if c.kind != "const"]
+        natural = list(tensors[0].shape)
+        if len(tensors) == 2 and tensors[0].shape != tensors[1].shape:
+            natural = SF.infer_implicit_broadcast_shape(tensors[0].shape, tensors[1].shape)
+        m = SF.to_store_size(natural)
+        if m == n:
+            self._call_op(nd, kids, out_handle, m)
+            return
+        tmp = self._alloc_handle(m)
+        try:
+            self._call_op(nd, kids, tmp, m)
+            spread(tmp, natural)
+        finally:
+            lib.ktc_release(tmp)
+
+    def _call_op(self, nd, kids, out_handle: int, m: int) -> None:
+        """The library call of one node; `m` elements at the natural shape."""
+        lib = self.lib
+        if nd.kind == "bin":
+            a, b = kids
+            if a.kind == "const" or b.kind == "const":
+                first = a.kind == "const"
+                h, _ = self._force(b if first else a)
+                L.check(lib.ktc_scalar(nd.op, out_handle, h, (a if first else b).imm[0], m, 1 if first else 0))
+                return
+            (ha, sa_), (hb, sb_) = self._force(a), self._force(b)
+            if sa_ == sb_:
+                L.check(lib.ktc_binary(nd.op, out_handle, ha, hb, m))
+            else:
+                pa, na = L.shape_array(sa_)
+                pb, nb = L.shape_array(sb_)
+                L.check(lib.ktc_binary_bcast(nd.op, out_handle, ha, pa, na, hb, pb, nb))
+            return
+        h, _ = self._force(kids[0])
+        if nd.kind == "un":
+            L.check(lib.ktc_unary(nd.op, out_handle, h, m))
+        elif nd.kind == "square":
+            L.check(lib.ktc_scalar(L.POW, out_handle, h, 2.0, m, 0))
+        elif nd.kind == "clamp":
+            L.check(lib.ktc_clamp(out_handle, h, nd.imm[0], nd.imm[1], m))
+        elif nd.kind == "cmp":
+            L.check(lib.ktc_compare_scalar(nd.op, out_handle, h, nd.imm[0], m))
+        else:
+            raise RuntimeError(f"cannot evaluate expression node of kind {nd.kind}")
 
     # ---- reference counting --------------------------------------------------------
     def release(self, *raws: CUDARawTensor) -> None:
