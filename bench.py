@@ -441,8 +441,9 @@ def run_sharded_graph(ops, lib, L, D, rank, world, comm, steps, warmup, dist):
         r.release()
     res = {"workload": "x[262144,1024] row-sharded, loss = sum(sigmoid(x*w+b) pow 2), backward + all-reduce of (loss, gw, gb)",
            "scaling": "strong", "rows_per_gpu": count}
-    res.update(eager)                                   # the raw-tensor call sequence of kten's autograd, call by call
-    res["deferred"] = fused                             # the same sequence with elementwise calls fused into the sums
+    res.update(fused)                                   # the raw-tensor call sequence of kten's autograd with the elementwise
+    res["execution"] = "deferred elementwise calls fused into the sums (ops.lazy)"      # calls deferred and fused,
+    res["call_by_call"] = eager                         # and the same sequence with every call one library call
     return res
 
 
@@ -633,6 +634,34 @@ def run_single_case(args):
     n = 1 << args.log2n
     scale = n / N28
     name = args.case
+    if name in ("c5.graph_eager", "c5.graph_deferred"):
+        # the sharded-graph step on one device with n = rows * 1024 elements of x
+        from kten_b200.sharded import ShardedSigmoidGraph
+        cols = 1024
+        rows = max(1, n // cols)
+        x = ops.createRaw([rows, cols], D.uniform(rows * cols, 0, -1.0, 1.0))
+        w = ops.createRaw([1, cols], D.normal(cols, 0, 0.0, 0.02, stream=1))
+        b = ops.createRawFill([cols], 0.0)
+        graph = ShardedSigmoidGraph(ops, x, w, b)
+        ops.lazy = name.endswith("deferred")
+
+        def step():
+            with ops.garbageCollector():
+                graph.step()
+                graph.release_step()
+
+        for _ in range(3):
+            step()
+        ops.synchronize()
+        l0 = lib.ktc_launch_count()
+        L.check(lib.ktc_timer_start(0))
+        for _ in range(args.reps):
+            step()
+        ms = C.c_float(0)
+        L.check(lib.ktc_timer_stop(0, C.byref(ms)))
+        print(json.dumps({"case": name, "elements": rows * cols, "ms": ms.value / args.reps,
+                          "launches_per_step": (lib.ktc_launch_count() - l0) / args.reps}))
+        return 0
     spec = {s_["name"]: s_ for s_ in sweep_spec()}[name]
     mk = ops.createRaw
     out = mk([n])

@@ -180,12 +180,25 @@ def _toposort(roots: Sequence[Node]) -> Tuple[List[Node], Dict[int, int]]:
     return order, uses
 
 
-def compile_program(shape, stores: Sequence[Node], acc: Optional[Node], side_candidates: int):
+# rough issue cost of recomputing one element of a node, in units of a float add
+HEAVY = {L.EXP: 10, L.LOG: 10, L.TANH: 12, L.SIGMOID: 16, L.RECIPROCAL: 2, L.NEG: 1}
+
+
+def _weight(n: Node) -> int:
+    if n.kind == "un":
+        return HEAVY.get(n.op, 1)
+    if n.kind == "bin":
+        return 30 if n.op == L.POW else 3 if n.op == L.DIV else 1
+    return 0 if n.kind in ("leaf", "const", "bcast") else 1
+
+
+def compile_program(shape, stores: Sequence[Node], acc: Optional[Node], recompute_limit: int = 0, store_cost: int = 0):
     """Linearise the DAG under `stores` + `acc` into a register program over the iteration
     space `shape`.  Returns (Program, nodes written by STORE, in store-index order; the first
-    len(stores) entries are the requested ones).  `side_candidates`: 0 = store nothing but what was
-    asked for; k > 0 = a value that was already computed k times, and that a tensor still waits for,
-    is stored on the side.  Raises NotFusable."""
+    len(stores) entries are the requested ones).  Side outputs: a value that a tensor still waits
+    for is stored on the way when it was already computed `recompute_limit` times, or when
+    recomputing it from memory would cost `store_cost` or more (both 0: nothing is stored but what
+    was asked for).  Raises NotFusable."""
     prog = Program(shape)
     sinks = [strip(n) for n in stores] + ([strip(acc)] if acc is not None else [])
     order, uses = _toposort(sinks)
@@ -194,21 +207,33 @@ def compile_program(shape, stores: Sequence[Node], acc: Optional[Node], side_can
     n_requested = len(store_nodes)
     full_volume = SF.to_store_size(shape)
     acc_node = strip(acc) if acc is not None else None
-    # An interior node that was evaluated `side_candidates` times before and whose tensor still waits
-    # for it is stored on the way (the tensor then owns storage and later programs load it): the
-    # recomputation of any value is bounded, and so is the work on graphs that reuse values deeply.  Nodes below such a node are not
-    # candidates: nothing reaches them any more once it is in memory.
-    if side_candidates:
+    # Side outputs.  Recomputing a short chain from an operand that is read anyway costs no memory
+    # traffic, so cheap values are recomputed (a bounded number of times); a value behind a
+    # transcendental is stored the first time -- the kernel that computes it is issue-bound and the
+    # store rides along -- and later programs load it.  Chosen bottom-up (a chosen value makes what
+    # is built on it cheap), then pruned top-down: nothing reaches below a stored value any more.
+    if recompute_limit > 0 or store_cost > 0:
+        cost: Dict[int, int] = {}
+        chosen = set()
+        for n in order:
+            if n.stored() or n.kind in ("const", "leaf"):
+                cost[id(n)] = 0
+                continue
+            c = _weight(n) + sum(cost[id(strip(a))] for a in n.args)
+            cell = n.owner() if n.owner is not None else None
+            waiting = cell is not None and cell.store is None and cell.node is n
+            if waiting and SF.to_store_size(n.shape) == full_volume and not any(n is s for s in store_nodes) \
+                    and ((recompute_limit > 0 and n.evals >= recompute_limit) or (store_cost > 0 and c >= store_cost)):
+                chosen.add(id(n))
+                c = 0
+            cost[id(n)] = c
         seen, stack = set(), list(sinks)
         while stack:
             n = strip(stack.pop())
-            if id(n) in seen or n.stored() or n.kind in ("const", "leaf"):
+            if id(n) in seen or n.stored():
                 continue
             seen.add(id(n))
-            cell = n.owner() if n.owner is not None else None
-            if not any(n is s for s in sinks) and n.evals >= side_candidates and cell is not None and cell.store is None \
-                    and cell.node is n and SF.to_store_size(n.shape) == full_volume \
-                    and len(store_nodes) < L.EXPR_MAX_STORES:
+            if id(n) in chosen and len(store_nodes) < L.EXPR_MAX_STORES:
                 store_nodes.append(n)
                 uses[id(n)] += 1
                 continue

@@ -72,6 +72,7 @@ class CUDATensorOperations:
         self._deps = {}                     # buffer handle -> WeakSet of storage cells whose pending expressions read it
         self._deps_purge_at = 1024
         self.recomputeLimit = 2             # a pending value is recomputed at most this often before it is stored
+        self.storeCost = 8                  # ... unless recomputing costs this much (a transcendental): stored at once
         self.fusedEvaluations = 0           # programs run by ktc_expr_eval
         self.unfusedEvaluations = 0         # deferred expressions that fell back to separate calls
 
@@ -209,7 +210,7 @@ class CUDATensorOperations:
         stores[i]; own[i]: the handle is a fresh buffer that node i adopts.  Nodes stored on the side
         get fresh buffers.  False: not fusable, nothing was run."""
         try:
-            prog, store_nodes, n_req = Z.compile_program(shape, stores, acc, side_candidates=self.recomputeLimit)
+            prog, store_nodes, n_req = Z.compile_program(shape, stores, acc, self.recomputeLimit, self.storeCost)
             if reshape is not None and not reshape(prog):
                 return False
         except Z.NotFusable:

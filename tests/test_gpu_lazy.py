@@ -153,25 +153,28 @@ def test_inplace_and_alias_rules(lazy_ops):
     assert same_bits(lazy[4], np.full(n, 7.0, np.float32))
 
 
-def test_value_recomputed_up_to_the_limit_then_stored(lazy_ops):
+def test_cheap_values_are_recomputed_heavy_ones_stored(lazy_ops):
     ops = lazy_ops
-    assert ops.recomputeLimit == 2
+    assert ops.recomputeLimit == 2 and ops.storeCost == 8
     n = 1 << 14
     xv = D.uniform(n, 13, -2.0, 2.0)
     x = ops.createRaw([n], xv)
-    s = x.sigmoid()
-    first = s.plus(1.0).sum()             # evaluates s inside the fused sum
-    second = s.times(s).sum()             # recomputes it: x is read either way
-    assert s.isDeferred
-    third = s.times(0.5).sum()            # the third use stores it
+    c = x.times(2.0).plus(1.0)            # cheap: recomputed from x, which is read either way
+    first = c.plus(1.0).sum()
+    second = c.times(c).sum()
+    assert c.isDeferred
+    third = c.times(0.5).sum()            # the third use stores it
+    assert not c.isDeferred
+    s = x.sigmoid()                       # behind a transcendental: stored by the first program that computes it
+    fourth = s.times(s).sum()
     assert not s.isDeferred
     ops.lazy = False
-    want = ops.createRaw([n], xv).sigmoid()
-    assert same_bits(s.toArray(), want.toArray())
-    s64 = want.toArray().astype(np.float64)
-    assert abs(float(first.toArray()[0]) - (s64 + 1).sum()) <= RED_RTOL * (s64 + 1).sum()
-    assert abs(float(second.toArray()[0]) - (s64 * s64).sum()) <= RED_RTOL * (s64 * s64).sum()
-    assert abs(float(third.toArray()[0]) - (s64 * 0.5).sum()) <= RED_RTOL * (s64 * 0.5).sum()
+    xe = ops.createRaw([n], xv)
+    assert same_bits(c.toArray(), xe.times(2.0).plus(1.0).toArray())
+    assert same_bits(s.toArray(), xe.sigmoid().toArray())
+    c64, s64 = c.toArray().astype(np.float64), s.toArray().astype(np.float64)
+    for got, want in ((first, c64 + 1), (second, c64 * c64), (third, c64 * 0.5), (fourth, s64 * s64)):
+        assert abs(float(got.toArray()[0]) - want.sum()) <= RED_RTOL * np.abs(want).sum()
 
 
 def test_programs_beyond_the_kernel_limits_are_split(lazy_ops):

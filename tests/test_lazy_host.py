@@ -98,7 +98,7 @@ def test_program_equals_direct_evaluation(env):
     sq = Z.Node("square", shape, 0, (e,))
     out = bin_(L.MINUS, sq, bin_(L.DIV, z, Z.const(4.0), shape), shape)            # z is used twice
     cl = Z.Node("clamp", shape, 0, (out,), imm=(0.0, 50.0))
-    prog, store_nodes, n_req = Z.compile_program(shape, [cl, z], e, side_candidates=1)
+    prog, store_nodes, n_req = Z.compile_program(shape, [cl, z], e, recompute_limit=1)
     assert n_req == 2 and len(store_nodes) == 2 and prog.n_stores == 2
     stores, acc = interpret(prog, bufs, 2)
     X, W, B = bufs[1].reshape(shape), bufs[2].reshape(1, 8), bufs[3].reshape(8)
@@ -118,7 +118,7 @@ def test_broadcast_markers_cost_nothing(env):
     gb = Z.Node("bcast", [4, 8], 0, (g,))
     alias = Z.Node("bcast", [4, 8], 0, (x,))                                        # a deep copy that is not made yet
     prod = bin_(L.TIMES, gb, alias, [4, 8])
-    prog, nodes, _ = Z.compile_program([4, 8], [prod], None, side_candidates=0)
+    prog, nodes, _ = Z.compile_program([4, 8], [prod], None, recompute_limit=0)
     stores, _ = interpret(prog, bufs, 1)
     assert np.array_equal(stores[0], (bufs[5][0] * bufs[6]).reshape(4, 8))
     assert len(prog.code) == 4                                                     # 2 loads, 1 multiply, 1 store
@@ -179,6 +179,14 @@ def test_side_outputs_only_for_values_a_tensor_still_waits_for(env):
     cells["s"].node = None                                                          # the tensor moved on: no side output
     _, nodes, _ = Z.compile_program(shape, [top], None, 1)
     assert nodes[1:] == [z]                                                         # ... but z, now reachable, is a candidate
+    # cost rule: a value behind a transcendental is stored the first time, a cheap one is not
+    cells["s"].node = s
+    z.evals = s.evals = 0
+    _, nodes, _ = Z.compile_program(shape, [top], None, 2, store_cost=8)
+    assert nodes[1:] == [s]
+    cells["s"].node = None
+    _, nodes, _ = Z.compile_program(shape, [top], None, 2, store_cost=8)
+    assert len(nodes) == 1                                                          # z alone is one addition
 
 
 def test_set_stored_updates_dependents_and_references(env):
