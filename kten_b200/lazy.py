@@ -68,27 +68,42 @@ class Node:
         self.kind, self.op, self.args, self.shape, self.imm, self.buf = kind, op, tuple(args), list(shape), tuple(imm), buf
         self.evals = 0
         self.owner = None                      # weakref to the storage cell (raw_tensor._Cell) waiting for this value
-        self.parents = weakref.WeakSet()
-        handles = set()
+        self.parents = None                    # weak references to the nodes built on this one (list, pruned as it grows)
         if buf is not None:
-            handles.add(buf.handle)
+            self.leaves = {buf.handle}
+            return
+        handles = set()
+        me = None
         for a in self.args:
-            handles |= ({a.buf.handle} if a.buf is not None else a.leaves)
-            a.parents.add(self)
+            if a.buf is not None:
+                handles.add(a.buf.handle)
+            else:
+                handles |= a.leaves
+            if a.kind != "const":
+                if me is None:
+                    me = weakref.ref(self)
+                ps = a.parents
+                if ps is None:
+                    a.parents = [me]
+                else:
+                    ps.append(me)
+                    if len(ps) > 64 and (len(ps) & (len(ps) - 1)) == 0:      # at powers of two: drop the dead ones
+                        a.parents = [r for r in ps if r() is not None]
         self.leaves = handles                  # buffers this value is read from (grows when a descendant is stored)
 
     def stored(self) -> bool:
         return self.buf is not None
 
     def ancestors(self):
-        seen, stack = set(), list(self.parents)
+        seen, stack = set(), [r() for r in (self.parents or ())]
         while stack:
             n = stack.pop()
-            if id(n) in seen:
+            if n is None or n in seen:
                 continue
-            seen.add(id(n))
+            seen.add(n)
             yield n
-            stack.extend(n.parents)
+            if n.parents:
+                stack.extend(r() for r in n.parents)
 
     def set_stored(self, buf: BufferRef, registry) -> None:
         """The value now lives in `buf`: forget how it was computed, and make everything that is
@@ -161,22 +176,34 @@ def strip(n: Node) -> Node:
     return n
 
 
-def _toposort(roots: Sequence[Node]) -> Tuple[List[Node], Dict[int, int]]:
-    order, uses, seen = [], {}, set()
-
-    def visit(n: Node):
-        n = strip(n)
-        uses[id(n)] = uses.get(id(n), 0) + 1
-        if id(n) in seen:
-            return
-        seen.add(id(n))
-        if not n.stored():
-            for a in n.args:
-                visit(a)
-        order.append(n)
-
+def _toposort(roots: Sequence[Node]) -> Tuple[List[Node], Dict[Node, int]]:
+    """Children-first order of the unstored DAG under `roots` (broadcast markers looked through) and
+    the number of uses of every node (one per consumer, one per root)."""
+    order: List[Node] = []
+    uses: Dict[Node, int] = {}
+    stack = []
     for r in roots:
-        visit(r)
+        while r.kind == "bcast" and r.buf is None:
+            r = r.args[0]
+        stack.append((r, False))
+    # iterative post-order; a node is expanded the first time it is seen
+    stack.reverse()
+    while stack:
+        n, done = stack.pop()
+        if done:
+            order.append(n)
+            continue
+        c = uses.get(n)
+        if c is not None:
+            uses[n] = c + 1
+            continue
+        uses[n] = 1
+        stack.append((n, True))
+        if n.buf is None:
+            for a in reversed(n.args):
+                while a.kind == "bcast" and a.buf is None:
+                    a = a.args[0]
+                stack.append((a, False))
     return order, uses
 
 
@@ -202,7 +229,7 @@ def compile_program(shape, stores: Sequence[Node], acc: Optional[Node], recomput
     prog = Program(shape)
     sinks = [strip(n) for n in stores] + ([strip(acc)] if acc is not None else [])
     order, uses = _toposort(sinks)
-    reg: Dict[int, int] = {}
+    reg: Dict[Node, int] = {}
     store_nodes: List[Node] = [strip(n) for n in stores]
     n_requested = len(store_nodes)
     full_volume = SF.to_store_size(shape)
@@ -213,36 +240,36 @@ def compile_program(shape, stores: Sequence[Node], acc: Optional[Node], recomput
     # store rides along -- and later programs load it.  Chosen bottom-up (a chosen value makes what
     # is built on it cheap), then pruned top-down: nothing reaches below a stored value any more.
     if recompute_limit > 0 or store_cost > 0:
-        cost: Dict[int, int] = {}
+        cost: Dict[Node, int] = {}
         chosen = set()
         for n in order:
             if n.stored() or n.kind in ("const", "leaf"):
-                cost[id(n)] = 0
+                cost[n] = 0
                 continue
-            c = _weight(n) + sum(cost[id(strip(a))] for a in n.args)
+            c = _weight(n) + sum(cost[strip(a)] for a in n.args)
             cell = n.owner() if n.owner is not None else None
             waiting = cell is not None and cell.store is None and cell.node is n
             if waiting and SF.to_store_size(n.shape) == full_volume and not any(n is s for s in store_nodes) \
                     and ((recompute_limit > 0 and n.evals >= recompute_limit) or (store_cost > 0 and c >= store_cost)):
-                chosen.add(id(n))
+                chosen.add(n)
                 c = 0
-            cost[id(n)] = c
+            cost[n] = c
         seen, stack = set(), list(sinks)
         while stack:
             n = strip(stack.pop())
-            if id(n) in seen or n.stored():
+            if n in seen or n.stored():
                 continue
-            seen.add(id(n))
-            if id(n) in chosen and len(store_nodes) < L.EXPR_MAX_STORES:
+            seen.add(n)
+            if n in chosen and len(store_nodes) < L.EXPR_MAX_STORES:
                 store_nodes.append(n)
-                uses[id(n)] += 1
+                uses[n] += 1
                 continue
             stack.extend(n.args)
 
     def release_use(n: Node):
-        uses[id(n)] -= 1
-        if uses[id(n)] == 0:
-            prog.free.append(reg[id(n)])
+        uses[n] -= 1
+        if uses[n] == 0:
+            prog.free.append(reg[n])
 
     for n in order:
         if n.stored():
@@ -253,7 +280,7 @@ def compile_program(shape, stores: Sequence[Node], acc: Optional[Node], recomput
             prog.emit(L.X_CONST, d, k=prog.imm_index([n.imm[0]]))
         else:
             children = [strip(a) for a in n.args]
-            srcs = [reg[id(c)] for c in children]
+            srcs = [reg[c] for c in children]
             for c in children:
                 release_use(c)
             d = prog.alloc()                    # may reuse a source register: the kernel reads before it writes
@@ -269,7 +296,7 @@ def compile_program(shape, stores: Sequence[Node], acc: Optional[Node], recomput
                 prog.emit(CMP_X[n.op], d, srcs[0], k=prog.imm_index([n.imm[0]]))
             else:
                 raise NotFusable(f"unknown node kind {n.kind}")
-        reg[id(n)] = d
+        reg[n] = d
         for k, sn in enumerate(store_nodes):
             if sn is n:
                 prog.emit(L.X_STORE, a=d, k=k)
@@ -278,6 +305,7 @@ def compile_program(shape, stores: Sequence[Node], acc: Optional[Node], recomput
             prog.emit(L.X_ACC, a=d)
             release_use(n)
     prog.n_stores = len(store_nodes)
+    prog.order = order
     return prog, store_nodes, n_requested
 
 

@@ -225,8 +225,7 @@ class CUDATensorOperations:
                 return False
             L.check(rc)
         self.fusedEvaluations += 1
-        order, _ = Z._toposort([Z.strip(r) for r in list(stores) + ([acc] if acc is not None else [])])
-        for nd in order:
+        for nd in prog.order:
             nd.evals += 1
         for nd, h, o in zip(store_nodes[:n_req], handles, own):
             if o:
