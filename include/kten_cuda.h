@@ -59,12 +59,15 @@ enum {
 
 /* elementwise binary ops: JVM:110-140, kernels.cl calc_by_elwise_op (kernels.cl:79-94) */
 enum { KTC_PLUS = 0, KTC_MINUS = 1, KTC_TIMES = 2, KTC_DIV = 3, KTC_POW = 4 };
-/* unary maps: JVM:122,142,144,395-399, kernels.cl tensor_mapping_op (kernels.cl:132-156) */
-enum { KTC_EXP = 0, KTC_LOG = 1, KTC_TANH = 2, KTC_SIGMOID = 3, KTC_RECIPROCAL = 4, KTC_NEG = 5 };
+/* unary maps: JVM:122,142,144,395-435, kernels.cl tensor_mapping_op (kernels.cl:132-156) */
+enum { KTC_EXP = 0, KTC_LOG = 1, KTC_TANH = 2, KTC_SIGMOID = 3, KTC_RECIPROCAL = 4, KTC_NEG = 5,
+       KTC_SINH = 6, KTC_COSH = 7, KTC_ABS = 8, KTC_SIGN = 9, KTC_SQRT = 10, KTC_SIN = 11, KTC_COS = 12, KTC_TAN = 13,
+       KTC_ASIN = 14, KTC_ACOS = 15, KTC_ATAN = 16, KTC_FLOOR = 17, KTC_CEIL = 18, KTC_ROUND = 19, KTC_TRUNC = 20,
+       KTC_RSQRT = 21 };
 /* aggregations: kten-api/.../tensor/store/AggregatingOperation.kt:3-4 */
 enum { KTC_SUM = 0, KTC_MEAN = 1, KTC_MAX = 2, KTC_MIN = 3, KTC_ARGMAX = 4, KTC_ARGMIN = 5 };
-/* compares used by Clamp.doBackward (PointwiseFunctions.kt:154-162; JVM:355-393) */
-enum { KTC_LT = 0, KTC_LTE = 1, KTC_GT = 2, KTC_GTE = 3 };
+/* compares (JVM:355-393); lt..gte are used by Clamp.doBackward (PointwiseFunctions.kt:154-162) */
+enum { KTC_LT = 0, KTC_LTE = 1, KTC_GT = 2, KTC_GTE = 3, KTC_EQ = 4, KTC_NEQ = 5 };
 
 /* ---- lifecycle / devices ------------------------------------------------
  * Stands in for OCLPlatformInitializer device enumeration
@@ -150,6 +153,18 @@ KTC_API int ktc_scalar_inplace(int op, ktc_buf a, float s, int64_t n);
 KTC_API int ktc_unary(int op, ktc_buf out, ktc_buf a, int64_t n);
 KTC_API int ktc_clamp(ktc_buf out, ktc_buf a, float lo, float hi, int64_t n);
 KTC_API int ktc_compare_scalar(int op, ktc_buf out, ktc_buf a, float value, int64_t n);
+/* ktc_compare_scalar_eps: eq / neq (value) as |x - value| < epsilon (JVM:387-393; epsilon is
+ *                         PlatformProvider.epsilon, 1e-7f by default, PlatformProvider.kt:12).
+ * ktc_compare_tensor:     lt/lte/gt/gte/eq/neq (tensor), equal shapes -> 1.0f / 0.0f (JVM:355-377;
+ *                         kten-jvm does not broadcast tensor compares).
+ * ktc_masked_fill:        maskedFill (JVM:537-540): out = mask == 1f ? value : a, the mask broadcast
+ *                         to a's shape without being materialised.
+ * ktc_contains_nan:       containsNan (JVM:520-522) evaluated on the device; *result = 0 / 1.  Waits. */
+KTC_API int ktc_compare_scalar_eps(int op, ktc_buf out, ktc_buf a, float value, float epsilon, int64_t n);
+KTC_API int ktc_compare_tensor(int op, ktc_buf out, ktc_buf a, ktc_buf b, float epsilon, int64_t n);
+KTC_API int ktc_masked_fill(ktc_buf out, ktc_buf a, const int64_t* a_shape, int a_ndim,
+                            ktc_buf mask, const int64_t* mask_shape, int mask_ndim, float value);
+KTC_API int ktc_contains_nan(ktc_buf a, int64_t n, int* result);
 
 /* broadcastTo for callers that really need the expanded tensor
  * (Sum/Mean/Expand backward: AggregatingFunctions.kt:19-25,40-53; JVM:51-73). */
@@ -230,6 +245,40 @@ KTC_API int ktc_expr_eval(const uint32_t* code, int n_code, const float* imm, in
  * -1 = not tried yet).  ktc_expr_jit_log copies the log of the last failed compilation. */
 KTC_API int ktc_expr_stats(int64_t* out6);
 KTC_API int ktc_expr_jit_log(char* buf, int len);
+
+/* ---- slices, permutes, gather / scatter -----------------------------------------
+ * ktc_copy_strided:  dst[dst_offset + i.dst_strides] = src[src_offset + i.src_strides] for every i in the
+ *                    box `shape`; strides in elements, >= 0.  With a contiguous dst this is get(ranges)
+ *                    (JVM:276-280), narrow (JVM:468-482), transpose / permute (JVM:437-466; the source
+ *                    strides permuted); with a contiguous src it is set(ranges, tensor) (JVM:291-304)
+ *                    and the pieces of TensorOperations.concat.  Transposes go through a shared-memory
+ *                    tile so that both sides are accessed in whole lines.
+ * ktc_fill_strided:  set(index / ranges, value) (JVM:306-315).
+ * ktc_gather_axis:   gather (JVM:334-353): out[c] = in[c with c[axis] = index[c]], out and index of
+ *                    shape index_shape (<= in_shape off the axis), all of `ndim` dimensions.
+ * ktc_scatter_axis_nd: inplaceScatter / inplaceScatterAdd / inplaceScatter(value) (JVM:227-255, 317-332;
+ *                    shape rules ShapeFunctions.kt:346-371): for every index position c, in the order
+ *                    of the position along the axis, target[c with c[axis] = index[c]] = / += src[c] /
+ *                    = constant.  Repeated indices resolve as in the reference's sequential loop.
+ * ktc_index_select:  indexSelect (JVM:484-502) on the [outer, axis_len, inner] view, 1-D index.
+ * ktc_index_add:     indexAdd (JVM:504-518): target[o, index[k], n] += src[o, k, n] * alpha, k ascending.
+ * An index outside [0, extent) returns KTC_EINVAL (the reference throws IllegalArgumentException);
+ * these five calls wait for the device in order to report it. */
+enum { KTC_SCATTER_SET = 0, KTC_SCATTER_ADD = 1, KTC_SCATTER_CONST = 2 };
+KTC_API int ktc_copy_strided(ktc_buf dst, int64_t dst_offset, const int64_t* dst_strides,
+                             ktc_buf src, int64_t src_offset, const int64_t* src_strides,
+                             const int64_t* shape, int ndim);
+KTC_API int ktc_fill_strided(ktc_buf dst, int64_t dst_offset, const int64_t* dst_strides,
+                             const int64_t* shape, int ndim, float value);
+KTC_API int ktc_gather_axis(ktc_buf out, ktc_buf in, const int64_t* in_shape,
+                            ktc_buf index, const int64_t* index_shape, int ndim, int axis);
+KTC_API int ktc_scatter_axis_nd(int mode, ktc_buf target, const int64_t* target_shape,
+                                ktc_buf index, const int64_t* index_shape,
+                                ktc_buf src, const int64_t* src_shape, int ndim, int axis, float constant);
+KTC_API int ktc_index_select(ktc_buf out, ktc_buf in, ktc_buf index,
+                             int64_t outer, int64_t axis_len, int64_t n_index, int64_t inner);
+KTC_API int ktc_index_add(ktc_buf target, ktc_buf index, ktc_buf src, float alpha,
+                          int64_t outer, int64_t axis_len, int64_t n_index, int64_t inner);
 
 /* inplaceScatter along an axis with one index per [outer, inner] position:
  * the Max/Min backward (AggregatingFunctions.kt:68-79; JVM:227-256,

@@ -19,7 +19,9 @@ KTC_OK, KTC_EINVAL, KTC_ESTATE, KTC_ENOMEM, KTC_ECUDA, KTC_ECOMM, KTC_ETIMEOUT, 
 PLUS, MINUS, TIMES, DIV, POW = range(5)
 EXP, LOG, TANH, SIGMOID, RECIPROCAL, NEG = range(6)
 SUM, MEAN, MAX, MIN, ARGMAX, ARGMIN = range(6)
-LT, LTE, GT, GTE = range(4)
+(SINH, COSH, ABS, SIGN, SQRT, SIN, COS, TAN, ASIN, ACOS, ATAN, FLOOR, CEIL, ROUND, TRUNC, RSQRT) = range(6, 22)
+LT, LTE, GT, GTE, EQ, NEQ = range(6)
+SCATTER_SET, SCATTER_ADD, SCATTER_CONST = 0, 1, 2
 MAX_DIMS = 10
 COPY_ASYNC, COPY_SYNC, COPY_OVERLAP, COPY_OVERLAP_UNFENCED = 0, 1, 2, 3
 COMM_ID_BYTES = 128
@@ -66,6 +68,16 @@ _PROTOTYPES = {
     "ktc_unary": (i32, [i32, u64, u64, i64]),
     "ktc_clamp": (i32, [u64, u64, f32, f32, i64]),
     "ktc_compare_scalar": (i32, [i32, u64, u64, f32, i64]),
+    "ktc_compare_scalar_eps": (i32, [i32, u64, u64, f32, f32, i64]),
+    "ktc_compare_tensor": (i32, [i32, u64, u64, u64, f32, i64]),
+    "ktc_masked_fill": (i32, [u64, u64, p_i64, i32, u64, p_i64, i32, f32]),
+    "ktc_contains_nan": (i32, [u64, i64, p_i32]),
+    "ktc_copy_strided": (i32, [u64, i64, p_i64, u64, i64, p_i64, p_i64, i32]),
+    "ktc_fill_strided": (i32, [u64, i64, p_i64, p_i64, i32, f32]),
+    "ktc_gather_axis": (i32, [u64, u64, p_i64, u64, p_i64, i32, i32]),
+    "ktc_scatter_axis_nd": (i32, [i32, u64, p_i64, u64, p_i64, u64, p_i64, i32, i32, f32]),
+    "ktc_index_select": (i32, [u64, u64, u64, i64, i64, i64, i64]),
+    "ktc_index_add": (i32, [u64, u64, u64, f32, i64, i64, i64, i64]),
     "ktc_broadcast_to": (i32, [u64, p_i64, i32, u64, p_i64, i32]),
     "ktc_reduce_axis": (i32, [i32, u64, u64, i64, i64, i64]),
     "ktc_reduce_axis_validx": (i32, [i32, u64, u64, u64, i64, i64, i64]),

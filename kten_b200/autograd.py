@@ -14,6 +14,11 @@ Reference, by class:
   Exp, Log, Tanh, Sigmoid, Clamp                      functions/PointwiseFunctions.kt:8-82, 135-163
   Sum, Mean, Max, Min                                 functions/AggregatingFunctions.kt:7-93
   Expand                                              functions/TensorFunctions.kt:232-284
+  Sinh ... Rsqrt, Floor/Ceil/Round/Sign/Trunc         functions/PointwiseFunctions.kt:84-133, 165-360
+  Index, IndexSet*, Transpose, Reshape, Permute,
+  IndexSelect, Concat, Copy, Squeeze, Unsqueeze,
+  Gather, Scatter, MaskedFill                         functions/TensorFunctions.kt:33-586
+  get / set redirection after an in-place set         tensor/AGTensor.kt:24-83
   mayUnexpand                                         functions/Utils.kt:14-41
   Variable, NoGradVariable                            tensor/Variable.kt, tensor/NoGradVariable.kt
 """
@@ -56,6 +61,12 @@ class Tensor:
 
     def __init__(self, ops):
         self.ops = ops
+        self._inplaceSafeThis = None
+
+    def inplaceSafe(self):
+        """AGTensor.inplaceSafe (AGTensor.kt:24-35): after `t[index] = value` every later use of t goes
+        through the function node that performed the set."""
+        return self._inplaceSafeThis if self._inplaceSafeThis is not None else self
 
     # -- to be provided by subclasses
     @property
@@ -134,15 +145,90 @@ class Tensor:
     def argMin(self, axis: int = 0, keepDimensions: bool = False):
         return NoGradVariable(self.ops, self._forwarded().argMin(axis, keepDimensions))
 
+    def sinh(self): return Sinh(self.ops)(self.inplaceSafe())
+    def cosh(self): return Cosh(self.ops)(self.inplaceSafe())
+    def abs(self): return Abs(self.ops)(self.inplaceSafe())
+    def sign(self): return Sign(self.ops)(self.inplaceSafe())
+    def sqrt(self): return Sqrt(self.ops)(self.inplaceSafe())
+    def sin(self): return Sin(self.ops)(self.inplaceSafe())
+    def cos(self): return Cos(self.ops)(self.inplaceSafe())
+    def tan(self): return Tan(self.ops)(self.inplaceSafe())
+    def asin(self): return Asin(self.ops)(self.inplaceSafe())
+    def acos(self): return Acos(self.ops)(self.inplaceSafe())
+    def atan(self): return Atan(self.ops)(self.inplaceSafe())
+    def reciprocal(self): return Reciprocal(self.ops)(self.inplaceSafe())
+    def floor(self): return Floor(self.ops)(self.inplaceSafe())
+    def ceil(self): return Ceil(self.ops)(self.inplaceSafe())
+    def round(self): return Round(self.ops)(self.inplaceSafe())
+    def trunc(self): return Trunc(self.ops)(self.inplaceSafe())
+    def rsqrt(self): return Rsqrt(self.ops)(self.inplaceSafe())
+
+    # -- indexing and data movement (AGTensor.kt:61-83; Tensor.kt)
+    @staticmethod
+    def _is_int_index(index) -> bool:
+        return all(isinstance(i, int) for i in index)
+
+    def __getitem__(self, index):
+        index = list(index) if isinstance(index, (tuple, list)) else [index]
+        return Index(self.ops)(self.inplaceSafe(), index)
+
+    def __setitem__(self, index, value):
+        index = list(index) if isinstance(index, (tuple, list)) else [index]
+        me = self.inplaceSafe()
+        if isinstance(value, Tensor):
+            self._inplaceSafeThis = IndexSetTensor(self.ops)(me, index, value.inplaceSafe())
+        else:
+            self._inplaceSafeThis = IndexSetConstant(self.ops)(me, index, float(value))
+
+    def transpose(self, axis1: int, axis2: int):
+        return Transpose(self.ops)(self.inplaceSafe(), axis1, axis2)
+
+    def permute(self, *axes):
+        if len(axes) == 1 and isinstance(axes[0], (list, tuple)):
+            axes = axes[0]
+        return Permute(self.ops)(self.inplaceSafe(), list(axes))
+
+    def reshape(self, *shape):
+        if len(shape) == 1 and isinstance(shape[0], (list, tuple)):
+            shape = shape[0]
+        return Reshape(self.ops)(self.inplaceSafe(), list(shape))
+
+    def view(self, *shape):
+        if len(shape) == 1 and isinstance(shape[0], (list, tuple)):
+            shape = shape[0]
+        return Reshape(self.ops, viewMode=True)(self.inplaceSafe(), list(shape))
+
+    def squeeze(self, axis: int):
+        return Squeeze(self.ops)(self.inplaceSafe(), axis)
+
+    def unsqueeze(self, axis: int):
+        return Unsqueeze(self.ops)(self.inplaceSafe(), axis)
+
+    def copy(self):
+        return Copy(self.ops)(self.inplaceSafe())
+
+    def gather(self, axis: int, index: "Tensor"):
+        return Gather(self.ops)(self.inplaceSafe(), axis, index)
+
+    def scatter(self, axis: int, index: "Tensor", source: "Tensor"):
+        return Scatter(self.ops)(self.inplaceSafe(), axis, index, source.inplaceSafe())
+
+    def indexSelect(self, axis: int, index: "Tensor"):
+        return IndexSelect(self.ops)(self.inplaceSafe(), index, axis)
+
+    def maskedFill(self, mask: "Tensor", value: float):
+        return MaskedFill(self.ops)(self.inplaceSafe(), mask, float(value))
+
     def expand(self, *shape):
         if len(shape) == 1 and isinstance(shape[0], (list, tuple)):
             shape = shape[0]
         return Expand(self.ops)(self, list(shape))
 
     def _forwarded(self):
-        if isinstance(self, Function) and not self.hasValue():
-            self.forward()
-        return self.getRawValue()
+        me = self.inplaceSafe()                                  # AGTensor.inplaceSafeForwarded (AGTensor.kt:52-59)
+        if isinstance(me, Function) and not me.hasValue():
+            me.forward()
+        return me.getRawValue()
 
     def item(self) -> float:
         raw = self._forwarded()
@@ -152,6 +238,13 @@ class Tensor:
 
     def toArray(self):
         return self._forwarded().toArray()
+
+    def noGrad(self):
+        return NoGradVariable(self.ops, self._forwarded())
+
+    def asVariable(self, requiresGrad: bool = False):
+        raw = self._forwarded()
+        return Variable(self.ops, raw) if requiresGrad else NoGradVariable(self.ops, raw)
 
 
 class NoGradVariable(Tensor):
@@ -171,6 +264,23 @@ class NoGradVariable(Tensor):
 
     def asVariable(self, requiresGrad: bool = False):
         return Variable(self.ops, self.raw) if requiresGrad else self
+
+    def noGrad(self):
+        return self
+
+    # NoGradVariable.kt:42-64: indexing acts on the raw tensor at once
+    def __getitem__(self, index):
+        index = list(index) if isinstance(index, (tuple, list)) else [index]
+        return NoGradVariable(self.ops, self.raw.get(index))
+
+    def __setitem__(self, index, value):
+        index = list(index) if isinstance(index, (tuple, list)) else [index]
+        self.raw.set(index, value._forwarded() if isinstance(value, Tensor) else float(value))
+
+    def expand(self, *shape):                      # NoGradVariable.kt:178
+        if len(shape) == 1 and isinstance(shape[0], (list, tuple)):
+            shape = shape[0]
+        return NoGradVariable(self.ops, self.raw.broadcastTo(list(shape)))
 
 
 class Variable(Tensor):
@@ -330,6 +440,7 @@ class UnaryTensorFunction(Function):
     modifiesShape = False
 
     def __call__(self, tensor: Tensor):
+        tensor = tensor.inplaceSafe()
         if not self.modifiesShape:
             self.cachedShape = list(tensor.shape)
         self.tensor = tensor
@@ -353,6 +464,7 @@ class UnaryTensorFunction(Function):
 
 class BiTensorFunction(Function):
     def __call__(self, a: Tensor, b: Tensor):
+        a, b = a.inplaceSafe(), b.inplaceSafe()
         self.cachedShape = SF.infer_implicit_broadcast_shape(a.shape, b.shape)
         self.inputs = (a, b)
         return self
@@ -694,6 +806,452 @@ class Expand(UnaryTensorFunction):
 
     def doBackward(self, g):
         return [may_unexpand(g, self.inShape, self.ops)]
+
+
+# ---- PointwiseFunctions.kt: the remaining maps ------------------------------------------------
+class _SavedInputUnary(UnaryTensorFunction):
+    """doForward saves the input and applies `op`; doBackward is written per function."""
+    op = ""
+
+    def doForward(self, x):
+        self.saveForBackward(x)
+        self.output = getattr(x, self.op)()
+
+
+class Sinh(_SavedInputUnary):                     # PointwiseFunctions.kt:84-99
+    op = "sinh"
+
+    def doBackward(self, g):
+        grad = self.valuesSaved[0].cosh()
+        grad.timesAssign(g)
+        return [grad]
+
+
+class Cosh(_SavedInputUnary):                     # :101-116
+    op = "cosh"
+
+    def doBackward(self, g):
+        grad = self.valuesSaved[0].sinh()
+        grad.timesAssign(g)
+        return [grad]
+
+
+class Abs(_SavedInputUnary):                      # :118-133
+    op = "abs"
+
+    def doBackward(self, g):
+        grad = self.valuesSaved[0].sign()
+        grad.timesAssign(g)
+        return [grad]
+
+
+class Sqrt(_SavedInputUnary):                     # :165-182
+    op = "sqrt"
+
+    def doBackward(self, g):
+        grad = self.valuesSaved[0].pow(-0.5)
+        grad.timesAssign(g)
+        grad.divAssign(2.0)
+        return [grad]
+
+
+class Sin(_SavedInputUnary):                      # :184-199
+    op = "sin"
+
+    def doBackward(self, g):
+        grad = self.valuesSaved[0].cos()
+        grad.timesAssign(g)
+        return [grad]
+
+
+class Cos(_SavedInputUnary):                      # :201-217
+    op = "cos"
+
+    def doBackward(self, g):
+        grad = self.valuesSaved[0].sin()
+        grad.timesAssign(g)
+        grad.timesAssign(-1.0)
+        return [grad]
+
+
+class Tan(_SavedInputUnary):                      # :219-236
+    op = "tan"
+
+    def doBackward(self, g):
+        c = self.valuesSaved[0].cos()
+        c2 = c.pow(2.0)
+        grad = g.div(c2)
+        self.ops.release(c, c2)
+        return [grad]
+
+
+class Asin(_SavedInputUnary):                     # :238-251
+    op = "asin"
+
+    def doBackward(self, g):
+        x = self.valuesSaved[0]
+        return [g.times(x.times(x).unaryMinus().plus(1.0).sqrt().reciprocal())]
+
+
+class Acos(_SavedInputUnary):                     # :253-266
+    op = "acos"
+
+    def doBackward(self, g):
+        x = self.valuesSaved[0]
+        return [g.times(x.times(x).unaryMinus().plus(1.0).sqrt().reciprocal().unaryMinus())]
+
+
+class Atan(_SavedInputUnary):                     # :268-281
+    op = "atan"
+
+    def doBackward(self, g):
+        x = self.valuesSaved[0]
+        return [g.times(x.times(x).plus(1.0).reciprocal())]
+
+
+class Reciprocal(UnaryTensorFunction):            # :283-301
+    def doForward(self, x):
+        res = x.reciprocal()
+        self.saveForBackward(res)
+        self.output = res
+
+    def doBackward(self, g):
+        (res,) = self.valuesSaved
+        sq = res.times(res)
+        neg = sq.unaryMinus()
+        grad = g.times(neg)
+        self.ops.release(sq, neg)
+        return [grad]
+
+
+class ConstantGrad(UnaryTensorFunction):          # :303-320
+    op = ""
+    gradientValue = 0.0
+
+    def doForward(self, x):
+        self.inputShape = list(x.shape)
+        self.output = getattr(x, self.op)()
+
+    def doBackward(self, g):
+        return [may_unexpand(g.times(self.gradientValue), self.inputShape, self.ops)]
+
+
+class Floor(ConstantGrad):
+    op = "floor"
+
+
+class Ceil(ConstantGrad):
+    op = "ceil"
+
+
+class Round(ConstantGrad):
+    op = "round"
+
+
+class Sign(ConstantGrad):
+    op = "sign"
+
+
+class Trunc(ConstantGrad):
+    op = "trunc"
+
+
+class Rsqrt(UnaryTensorFunction):                 # :343-360
+    def doForward(self, x):
+        res = x.rsqrt()
+        self.saveForBackward(res)
+        self.output = res
+
+    def doBackward(self, g):
+        (res,) = self.valuesSaved
+        gr = res.pow(3.0)
+        gr.divAssign(-2.0)
+        grad = g.times(gr)
+        self.ops.release(gr)
+        return [grad]
+
+
+# ---- TensorFunctions.kt: indexing and data movement ---------------------------------------------
+def _norm_index(shape, index):
+    """(normalised index, indexed shape, is_int_index) -- normalizedIndexedShape, ShapeFunctions.kt:232-268."""
+    if all(isinstance(i, int) for i in index):
+        n, s = SF.normalized_indexed_shape(shape, index)
+        return n, s, True
+    n, s = SF.normalized_indexed_shape_ranges(shape, index)
+    return n, s, False
+
+
+class Index(UnaryTensorFunction):                 # TensorFunctions.kt:33-80
+    modifiesShape = True
+
+    def __call__(self, tensor: Tensor, index):
+        self.index, self.cachedShape, _ = _norm_index(tensor.shape, index)
+        return super().__call__(tensor)
+
+    def doForward(self, x):
+        self.inputShape = list(x.shape)
+        self.output = x.get(self.index)
+
+    def doBackward(self, g):
+        grad = self.ops.createRawFill(self.inputShape, 0.0)
+        grad.set(self.index, g)
+        return [grad]
+
+
+class IndexSetTensor(BiTensorFunction):           # :82-127
+    def __call__(self, tensor: Tensor, index, value: Tensor):
+        self.index, indexed_shape, _ = _norm_index(tensor.shape, index)
+        self.valueShape = list(value.shape)
+        if self.valueShape != indexed_shape:
+            raise ValueError(f"Cannot set value with shape: {self.valueShape} at index: {list(index)} on tensor with shape: {tensor.shape}")
+        self.inputs = (tensor.inplaceSafe(), value.inplaceSafe())
+        self.cachedShape = list(tensor.shape)
+        return self
+
+    def doForward(self, a, b):
+        self.ops.incrementRef(a)                  # the input is written in place and becomes the output
+        a.set(self.index, b)
+        self.output = a
+
+    def doBackward(self, g):
+        grad_input = g.copy()
+        grad_input.set(self.index, 0.0)
+        grad_value = g.get(self.index).view(self.valueShape)
+        return [grad_input, grad_value]
+
+
+class IndexSetConstant(UnaryTensorFunction):      # :129-170
+    def __call__(self, tensor: Tensor, index, value: float):
+        self.index, _, _ = _norm_index(tensor.shape, index)
+        if len(self.index) != len(tensor.shape):
+            raise ValueError(f"Cannot set value at index: {list(index)} on tensor with shape: {tensor.shape} "
+                             "(All tensor dimensions must be indexed to set a constant value)")
+        self.value = float(value)
+        return super().__call__(tensor)
+
+    def doForward(self, x):
+        self.ops.incrementRef(x)
+        x.set(self.index, self.value)
+        self.output = x
+
+    def doBackward(self, g):
+        grad = g.copy()
+        grad.set(self.index, 0.0)
+        return [grad]
+
+
+class Transpose(UnaryTensorFunction):             # :172-198
+    modifiesShape = True
+
+    def __call__(self, tensor: Tensor, axis1: int, axis2: int):
+        self.cachedShape = SF.transpose_normalize_axes(tensor.shape, axis1, axis2)[0]
+        self.axis1, self.axis2 = axis1, axis2
+        return super().__call__(tensor)
+
+    def doForward(self, x):
+        self.output = x.transpose(self.axis1, self.axis2)
+
+    def doBackward(self, g):
+        return [g.transpose(self.axis1, self.axis2)]
+
+
+class Reshape(UnaryTensorFunction):               # :200-231 (viewMode = View)
+    modifiesShape = True
+
+    def __init__(self, ops, viewMode: bool = False):
+        super().__init__(ops)
+        self.viewMode = viewMode
+
+    def __call__(self, tensor: Tensor, new_shape):
+        self.cachedShape = SF.reshape(tensor.shape, new_shape)
+        self.newShape = list(new_shape)
+        return super().__call__(tensor)
+
+    def doForward(self, x):
+        self.oldShape = list(x.shape)
+        self.output = x.view(self.newShape) if self.viewMode else x.reshape(self.newShape)
+
+    def doBackward(self, g):
+        return [g.view(self.oldShape) if self.viewMode else g.reshape(self.oldShape)]
+
+
+class Permute(UnaryTensorFunction):               # :286-314
+    modifiesShape = True
+
+    def __call__(self, tensor: Tensor, axes):
+        self.cachedShape = SF.permute(tensor.shape, axes)
+        self.axes = list(axes)
+        return super().__call__(tensor)
+
+    def doForward(self, x):
+        self.reverse = [self.axes.index(i) for i in range(len(self.axes))]
+        self.output = x.permute(self.axes)
+
+    def doBackward(self, g):
+        return [g.permute(self.reverse)]
+
+
+class IndexSelect(UnaryTensorFunction):           # :316-348
+    modifiesShape = True
+
+    def __call__(self, tensor: Tensor, index: Tensor, axis: int):
+        if index.requiresGrad:
+            raise ValueError("Index select cannot differentiate the index. The index tensor passed to index select should "
+                             "never require gradients.")
+        self.axis, self.cachedShape = SF.index_select_norm_axis_shape(tensor.shape, axis, index.shape)
+        self.originalShape = list(tensor.shape)
+        self.index = index
+        return super().__call__(tensor)
+
+    def doForward(self, x):
+        self.output = x.indexSelect(self.axis, self.index.getRawValue())
+
+    def doBackward(self, g):
+        grad = self.ops.createRawFill(self.originalShape, 0.0)
+        grad.indexAdd(self.axis, self.index.getRawValue(), g)
+        return [grad]
+
+
+class AnyTensorFunction(Function):                # AnyTensorFunction.kt
+    def getInputsAsList(self):
+        return list(self.inputTensors)
+
+    def internalForward(self) -> None:
+        super().internalForward()
+        if self.hasValue():
+            return
+        fns = [t for t in self.inputTensors if isinstance(t, Function)]
+        for f in fns:
+            f.internalForward()
+        if not self.hasValue():
+            self.doForward([t.getRawValue() for t in self.inputTensors])
+        for f in fns:
+            f.mayFreeOutput()
+
+
+class Concat(AnyTensorFunction):                  # TensorFunctions.kt:350-375
+    def __call__(self, axis: int, tensors):
+        tensors = [t.inplaceSafe() for t in tensors]
+        self.cachedShape = SF.concat_shapes([t.shape for t in tensors], axis)
+        self.inputTensors = tensors
+        self.axis = SF.normalize_axis(self.cachedShape, axis)
+        return self
+
+    def doForward(self, inputs):
+        self.inputSizes = [r.shape[self.axis] for r in inputs]
+        self.output = self.ops.concat(self.axis, inputs)
+
+    def doBackward(self, g):
+        grads, end = [], 0
+        for size in self.inputSizes:
+            end += size
+            grads.append(g.narrow(self.axis, end - size, size))
+        return grads
+
+
+class Copy(UnaryTensorFunction):                  # :377-388
+    def doForward(self, x):
+        self.output = x.copy()
+
+    def doBackward(self, g):
+        return [g.copy(shallow=True)]
+
+
+class Squeeze(UnaryTensorFunction):               # :390-416
+    modifiesShape = True
+
+    def __call__(self, tensor: Tensor, axis: int):
+        self.cachedShape = SF.squeeze(tensor.shape, axis)
+        self.axis = axis
+        return super().__call__(tensor)
+
+    def doForward(self, x):
+        self.inputShape = list(x.shape)
+        self.output = x.squeeze(self.axis)
+
+    def doBackward(self, g):
+        return [g.reshape(self.inputShape)]
+
+
+class Unsqueeze(UnaryTensorFunction):             # :418-442
+    modifiesShape = True
+
+    def __call__(self, tensor: Tensor, axis: int):
+        self.cachedShape = SF.unsqueeze(tensor.shape, axis)
+        self.axis = axis
+        return super().__call__(tensor)
+
+    def doForward(self, x):
+        self.output = x.unsqueeze(self.axis)
+
+    def doBackward(self, g):
+        return [g.squeeze(self.axis)]
+
+
+class Gather(UnaryTensorFunction):                # :444-479
+    modifiesShape = True
+
+    def __call__(self, tensor: Tensor, axis: int, index: Tensor):
+        if index.requiresGrad:
+            raise ValueError("Gather cannot differentiate the index. The index tensor passed to gather should never require gradients.")
+        self.cachedShape = list(index.shape)
+        self.axis, self.index = axis, index
+        return super().__call__(tensor)
+
+    def doForward(self, x):
+        self.inputShape = list(x.shape)
+        idx = self.index.getRawValue()
+        self.saveForBackward(idx)
+        self.output = x.gather(self.axis, idx)
+
+    def doBackward(self, g):
+        grad = self.ops.createRawFill(self.inputShape, 0.0)
+        grad.inplaceScatterAdd(self.axis, self.valuesSaved[0], g)
+        return [grad]
+
+
+class Scatter(BiTensorFunction):                  # :481-527
+    def __call__(self, tensor: Tensor, axis: int, index: Tensor, source: Tensor):
+        if index.requiresGrad:
+            raise ValueError("Scatter cannot differentiate the index. The index tensor passed to scatter should never require gradients.")
+        a, b = tensor.inplaceSafe(), source.inplaceSafe()
+        self.inputs = (a, b)
+        self.cachedShape = list(a.shape)
+        self.axis, self.index = axis, index
+        return self
+
+    def doForward(self, t, source):
+        idx = self.index.getRawValue()
+        self.saveForBackward(idx)
+        self.output = t.scatter(self.axis, idx, source)
+
+    def doBackward(self, g):
+        (idx,) = self.valuesSaved
+        if list(idx.shape) != self.bShape:
+            raise ValueError(f"Index shape: {idx.shape} is not compatible with source shape: {self.bShape}")
+        grad_input = g.scatter(self.axis, idx, 0.0) if self.inputs[0].requiresGrad else None
+        grad_source = g.gather(self.axis, idx) if self.inputs[1].requiresGrad else None
+        return [grad_input, grad_source]
+
+
+class MaskedFill(UnaryTensorFunction):            # :559-584
+    def __call__(self, tensor: Tensor, mask: Tensor, value: float):
+        if mask.requiresGrad:
+            raise ValueError("Masked fill only accepts mask that doesn't require gradients")
+        self.mask, self.value = mask.getRawValue(), float(value)
+        return super().__call__(tensor)
+
+    def doForward(self, x):
+        self.output = x.maskedFill(self.mask, self.value)
+
+    def doBackward(self, g):
+        return [g.maskedFill(self.mask, 0.0)]
+
+
+def concat(tensors, axis: int = 0) -> Tensor:
+    """Tensor.concat (Tensor.kt): along `axis`, default 0."""
+    tensors = list(tensors)
+    return Concat(tensors[0].ops)(axis, tensors)
 
 
 # ---- factories (Tensor.Companion, Tensor.kt:1630-1786) -------------------------------------

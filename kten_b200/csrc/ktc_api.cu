@@ -132,11 +132,59 @@ int ktc_scalar(int op, ktc_buf out, ktc_buf a, float s, int64_t n, int scalar_fi
 int ktc_scalar_inplace(int op, ktc_buf a, float s, int64_t n) { return ktc_scalar(op, a, a, s, n, 0); }
 
 int ktc_unary(int op, ktc_buf out, ktc_buf a, int64_t n) {
-    if (op < KTC_EXP || op > KTC_NEG) return fail(KTC_EINVAL, "ktc_unary: unknown op %d", op);
+    if (op < KTC_EXP || op > KTC_RSQRT) return fail(KTC_EINVAL, "ktc_unary: unknown op %d", op);
     Buf bo, ba; KTC_TRY(resolve(out, &bo)); KTC_TRY(resolve(a, &ba));
     Args g; KTC_TRY(g.take(bo, "ktc_unary")); KTC_TRY(g.take(ba, "ktc_unary"));
     KTC_TRY(need(bo, n, "ktc_unary", "out")); KTC_TRY(need(ba, n, "ktc_unary", "a"));
+    if (op > KTC_NEG) return launch_map1_more(g.d, op, bo.ptr, ba.ptr, n);
     return launch_map1(g.d, M1_UNARY, op, bo.ptr, ba.ptr, n, 0.f, 0.f);
+}
+
+int ktc_compare_scalar_eps(int op, ktc_buf out, ktc_buf a, float value, float epsilon, int64_t n) {
+    if (op >= KTC_LT && op <= KTC_GTE) return ktc_compare_scalar(op, out, a, value, n);
+    if (op != KTC_EQ && op != KTC_NEQ) return fail(KTC_EINVAL, "ktc_compare_scalar_eps: unknown op %d", op);
+    Buf bo, ba; KTC_TRY(resolve(out, &bo)); KTC_TRY(resolve(a, &ba));
+    Args g; KTC_TRY(g.take(bo, "ktc_compare_scalar_eps")); KTC_TRY(g.take(ba, "ktc_compare_scalar_eps"));
+    KTC_TRY(need(bo, n, "ktc_compare_scalar_eps", "out")); KTC_TRY(need(ba, n, "ktc_compare_scalar_eps", "a"));
+    return launch_eq_scalar(g.d, op, bo.ptr, ba.ptr, n, value, epsilon);
+}
+
+int ktc_compare_tensor(int op, ktc_buf out, ktc_buf a, ktc_buf b, float epsilon, int64_t n) {
+    if (op < KTC_LT || op > KTC_NEQ) return fail(KTC_EINVAL, "ktc_compare_tensor: unknown op %d", op);
+    Buf bo, ba, bb; KTC_TRY(resolve(out, &bo)); KTC_TRY(resolve(a, &ba)); KTC_TRY(resolve(b, &bb));
+    Args g; KTC_TRY(g.take(bo, "ktc_compare_tensor")); KTC_TRY(g.take(ba, "ktc_compare_tensor")); KTC_TRY(g.take(bb, "ktc_compare_tensor"));
+    KTC_TRY(need(bo, n, "ktc_compare_tensor", "out")); KTC_TRY(need(ba, n, "ktc_compare_tensor", "a")); KTC_TRY(need(bb, n, "ktc_compare_tensor", "b"));
+    return launch_compare_tensor(g.d, op, bo.ptr, ba.ptr, bb.ptr, n, epsilon);
+}
+
+int ktc_masked_fill(ktc_buf out, ktc_buf a, const int64_t* a_shape, int a_ndim,
+                    ktc_buf mask, const int64_t* mask_shape, int mask_ndim, float value) {
+    Buf bo, ba, bm; KTC_TRY(resolve(out, &bo)); KTC_TRY(resolve(a, &ba)); KTC_TRY(resolve(mask, &bm));
+    Args g; KTC_TRY(g.take(bo, "ktc_masked_fill")); KTC_TRY(g.take(ba, "ktc_masked_fill")); KTC_TRY(g.take(bm, "ktc_masked_fill"));
+    int64_t va, vm;
+    KTC_TRY(check_shape(a_shape, a_ndim, "ktc_masked_fill(a)", &va));
+    KTC_TRY(check_shape(mask_shape, mask_ndim, "ktc_masked_fill(mask)", &vm));
+    if (mask_ndim > a_ndim)
+        return fail(KTC_EINVAL, "Tensor with %d dimensions cannot be broadcasted to a shape with %d dimensions", mask_ndim, a_ndim);
+    for (int i = 0; i < mask_ndim; ++i) {
+        const int64_t dm = mask_shape[i], dt = a_shape[a_ndim - mask_ndim + i];
+        if (!(dm == dt || dm == 1))
+            return fail(KTC_EINVAL, "Shape must match the target for every non-singleton dimension: extent %lld vs %lld", (long long)dm, (long long)dt);
+    }
+    KTC_TRY(need(ba, va, "ktc_masked_fill", "a")); KTC_TRY(need(bm, vm, "ktc_masked_fill", "mask")); KTC_TRY(need(bo, va, "ktc_masked_fill", "out"));
+    if (va == 0) return KTC_OK;
+    int64_t as[KTC_MAX_DIMS], ms[KTC_MAX_DIMS];
+    bcast_strides(a_shape, a_ndim, a_shape, a_ndim, as);
+    bcast_strides(mask_shape, mask_ndim, a_shape, a_ndim, ms);
+    return launch_bcast(g.d, kBcastMaskedFill, bo.ptr, a_shape, a_ndim, ba.ptr, as, bm.ptr, ms, value);
+}
+
+int ktc_contains_nan(ktc_buf a, int64_t n, int* result) {
+    if (!result) return fail(KTC_EINVAL, "ktc_contains_nan: null result");
+    Buf ba; KTC_TRY(resolve(a, &ba));
+    Args g; KTC_TRY(g.take(ba, "ktc_contains_nan"));
+    KTC_TRY(need(ba, n, "ktc_contains_nan", "a"));
+    return launch_contains_nan(g.d, ba.ptr, n, result);
 }
 
 int ktc_clamp(ktc_buf out, ktc_buf a, float lo, float hi, int64_t n) {

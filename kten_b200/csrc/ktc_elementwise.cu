@@ -15,72 +15,10 @@
 //           broadcast operand is never materialised in global memory
 //           (the reference writes and re-reads a full-size copy:
 //           JVMRawTensor.kt:51-73, kernels.cl:44-70).
-#include "ktc_internal.hpp"
-#include "ktc_math.cuh"
+#include "ktc_map.cuh"
+#include "ktc_math_more.cuh"
 
 namespace ktc {
-
-__device__ __forceinline__ float4 ld_stream(const float4* p) { return __ldcs(p); }
-__device__ __forceinline__ void st_stream(float4* p, float4 v) { __stcs(p, v); }
-
-template <class F> __device__ __forceinline__ float4 apply1(const F& f, float4 a) {
-    return make_float4(f(a.x), f(a.y), f(a.z), f(a.w));
-}
-template <class F> __device__ __forceinline__ float4 apply2(const F& f, float4 a, float4 b) {
-    return make_float4(f(a.x, b.x), f(a.y, b.y), f(a.z, b.z), f(a.w, b.w));
-}
-
-// ---- contiguous maps ---------------------------------------------------------
-// One tile of kMapThreads * U float4 per CTA, CTAs in address order.  Each thread forms
-// its base pointers once; the U accesses are then fixed offsets from them.  n4 is the
-// number of whole float4; the (< 4 element) remainder and unaligned buffers go through
-// the scalar kernels below.
-constexpr int kMapThreads = 256;
-
-template <int U, class F>
-__global__ void __launch_bounds__(kMapThreads) k_map1_vec(const float4* __restrict__ a, float4* __restrict__ out, int64_t n4, F f) {
-    const int64_t base = (int64_t)blockIdx.x * (kMapThreads * U) + threadIdx.x;
-    const float4* pa = a + base;
-    float4* po = out + base;
-    if (base - threadIdx.x + kMapThreads * U <= n4) {              // whole tile: every load before the first use, no guards
-        float4 va[U];
-        #pragma unroll
-        for (int u = 0; u < U; ++u) va[u] = ld_stream(pa + u * kMapThreads);
-        #pragma unroll
-        for (int u = 0; u < U; ++u) st_stream(po + u * kMapThreads, apply1(f, va[u]));
-    } else {
-        for (int64_t i = base; i < n4; i += kMapThreads) st_stream(out + i, apply1(f, ld_stream(a + i)));
-    }
-}
-
-template <int U, class F>
-__global__ void __launch_bounds__(kMapThreads) k_map2_vec(const float4* __restrict__ a, const float4* __restrict__ b,
-                                                          float4* __restrict__ out, int64_t n4, F f) {
-    const int64_t base = (int64_t)blockIdx.x * (kMapThreads * U) + threadIdx.x;
-    const float4* pa = a + base;
-    const float4* pb = b + base;
-    float4* po = out + base;
-    if (base - threadIdx.x + kMapThreads * U <= n4) {
-        float4 va[U], vb[U];
-        #pragma unroll
-        for (int u = 0; u < U; ++u) { va[u] = ld_stream(pa + u * kMapThreads); vb[u] = ld_stream(pb + u * kMapThreads); }
-        #pragma unroll
-        for (int u = 0; u < U; ++u) st_stream(po + u * kMapThreads, apply2(f, va[u], vb[u]));
-    } else {
-        for (int64_t i = base; i < n4; i += kMapThreads) st_stream(out + i, apply2(f, ld_stream(a + i), ld_stream(b + i)));
-    }
-}
-
-template <class F>
-__global__ void k_map1_scalar(const float* __restrict__ a, float* __restrict__ out, int64_t n, F f) {
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
-        out[i] = f(a[i]);
-}
-template <class F>
-__global__ void k_map2_scalar(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out, int64_t n, F f) {
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
-        out[i] = f(a[i], b[i]);
-}
 
 __global__ void __launch_bounds__(256) k_fill_vec(float4* __restrict__ out, int64_t n4, float v) {
     const float4 vv = make_float4(v, v, v, v);
@@ -90,58 +28,6 @@ __global__ void __launch_bounds__(256) k_fill_vec(float4* __restrict__ out, int6
 __global__ void k_fill_scalar(float* __restrict__ out, int64_t n, float v) {
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
         out[i] = v;
-}
-
-static inline int grid_for(Device* d, int64_t items, int64_t per_block, int max_blocks_per_sm) {
-    int64_t need = (items + per_block - 1) / per_block;
-    int64_t cap = (int64_t)d->sm_count * max_blocks_per_sm;
-    if (need < 1) need = 1;
-    return (int)(need < cap ? need : cap);
-}
-
-static inline int finish_launch(const char* what, int launches = 1) {
-    count_launch(launches);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return fail(KTC_ECUDA, "launch of %s failed: %s", what, cudaGetErrorString(e));
-    return KTC_OK;
-}
-
-static inline int64_t map_tiles(int64_t n4, int U) { return (n4 + (int64_t)kMapThreads * U - 1) / ((int64_t)kMapThreads * U); }
-
-template <class F>
-static int run_map1(Device* d, float* out, const float* a, int64_t n, F f) {
-    if (n <= 0) return KTC_OK;
-    if (aligned16(out) && aligned16(a) && n >= 4) {
-        const int64_t n4 = n / 4;
-        const int U = tune("map_unroll", 4);
-        if (map_tiles(n4, 2) > 0x7fffffffLL) return fail(KTC_ENOTSUP, "tensor too large for one launch");
-        int launches = 1;
-        if (U == 8)      k_map1_vec<8, F><<<(int)map_tiles(n4, 8), kMapThreads, 0, d->stream>>>((const float4*)a, (float4*)out, n4, f);
-        else if (U == 2) k_map1_vec<2, F><<<(int)map_tiles(n4, 2), kMapThreads, 0, d->stream>>>((const float4*)a, (float4*)out, n4, f);
-        else             k_map1_vec<4, F><<<(int)map_tiles(n4, 4), kMapThreads, 0, d->stream>>>((const float4*)a, (float4*)out, n4, f);
-        if (n & 3) { k_map1_scalar<F><<<1, 32, 0, d->stream>>>(a + n4 * 4, out + n4 * 4, n & 3, f); ++launches; }
-        return finish_launch("map1", launches);
-    }
-    k_map1_scalar<F><<<grid_for(d, n, 256, 16), 256, 0, d->stream>>>(a, out, n, f);
-    return finish_launch("map1(scalar)");
-}
-
-template <class F>
-static int run_map2(Device* d, float* out, const float* a, const float* b, int64_t n, F f) {
-    if (n <= 0) return KTC_OK;
-    if (aligned16(out) && aligned16(a) && aligned16(b) && n >= 4) {
-        const int64_t n4 = n / 4;
-        const int U = tune("map_unroll", 4);
-        if (map_tiles(n4, 2) > 0x7fffffffLL) return fail(KTC_ENOTSUP, "tensor too large for one launch");
-        int launches = 1;
-        if (U == 8)      k_map2_vec<8, F><<<(int)map_tiles(n4, 8), kMapThreads, 0, d->stream>>>((const float4*)a, (const float4*)b, (float4*)out, n4, f);
-        else if (U == 2) k_map2_vec<2, F><<<(int)map_tiles(n4, 2), kMapThreads, 0, d->stream>>>((const float4*)a, (const float4*)b, (float4*)out, n4, f);
-        else             k_map2_vec<4, F><<<(int)map_tiles(n4, 4), kMapThreads, 0, d->stream>>>((const float4*)a, (const float4*)b, (float4*)out, n4, f);
-        if (n & 3) { k_map2_scalar<F><<<1, 32, 0, d->stream>>>(a + n4 * 4, b + n4 * 4, out + n4 * 4, n & 3, f); ++launches; }
-        return finish_launch("map2", launches);
-    }
-    k_map2_scalar<F><<<grid_for(d, n, 256, 16), 256, 0, d->stream>>>(a, b, out, n, f);
-    return finish_launch("map2(scalar)");
 }
 
 int launch_fill(Device* d, float* out, int64_t n, float v) {
@@ -442,9 +328,10 @@ static int run_bcast(Device* d, float* out, const int64_t* oshape, int ndim, con
 
 // op < 0 selects the copy of operand b (broadcast_to)
 int launch_bcast(Device* d, int op, float* out, const int64_t* oshape, int ndim,
-                 const float* a, const int64_t* astride, const float* b, const int64_t* bstride) {
+                 const float* a, const int64_t* astride, const float* b, const int64_t* bstride, float param) {
     switch (op) {
-    case -1:        return run_bcast(d, out, oshape, ndim, nullptr, nullptr, b, bstride, SelectB());
+    case kBcastSelectB:    return run_bcast(d, out, oshape, ndim, nullptr, nullptr, b, bstride, SelectB());
+    case kBcastMaskedFill: return run_bcast(d, out, oshape, ndim, a, astride, b, bstride, MaskedFill{param});
     case KTC_PLUS:  return run_bcast(d, out, oshape, ndim, a, astride, b, bstride, BinOp<KTC_PLUS>());
     case KTC_MINUS: return run_bcast(d, out, oshape, ndim, a, astride, b, bstride, BinOp<KTC_MINUS>());
     case KTC_TIMES: return run_bcast(d, out, oshape, ndim, a, astride, b, bstride, BinOp<KTC_TIMES>());

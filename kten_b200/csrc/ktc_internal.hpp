@@ -93,7 +93,12 @@ int launch_map1(Device* d, int kind, int op, float* out, const float* a, int64_t
 int launch_map2(Device* d, int op, float* out, const float* a, const float* b, int64_t n);
 int launch_fill(Device* d, float* out, int64_t n, float v);
 int launch_bcast(Device* d, int op, float* out, const int64_t* oshape, int ndim,
-                 const float* a, const int64_t* astride, const float* b, const int64_t* bstride);
+                 const float* a, const int64_t* astride, const float* b, const int64_t* bstride, float param = 0.f);
+constexpr int kBcastSelectB = -1, kBcastMaskedFill = 100;      // internal op codes of launch_bcast
+int launch_map1_more(Device* d, int op, float* out, const float* a, int64_t n);
+int launch_eq_scalar(Device* d, int op, float* out, const float* a, int64_t n, float value, float eps);
+int launch_compare_tensor(Device* d, int op, float* out, const float* a, const float* b, int64_t n, float eps);
+int launch_contains_nan(Device* d, const float* a, int64_t n, int* result);
 int launch_reduce_axis(Device* d, int op, float* out, float* out_idx, const float* in,
                        int64_t outer, int64_t A, int64_t inner);
 int launch_scatter_axis(Device* d, float* target, const float* index, const float* src,

@@ -159,7 +159,10 @@ class CUDARawTensor:
         return float(out[0])
 
     def containsNan(self) -> bool:
-        return bool(np.isnan(self.toArray()).any())
+        """containsNan (JVMRawTensor.kt:520-522), evaluated on the device."""
+        res = C.c_int(0)
+        L.check(self.ops.lib.ktc_contains_nan(self._buf(), self.size, C.byref(res)))
+        return bool(res.value)
 
     # ---- elementwise: tensor (op) tensor ------------------------------------------
     def _binary(self, op: int, other: "CUDARawTensor") -> "CUDARawTensor":
@@ -217,7 +220,7 @@ class CUDARawTensor:
         L.check(self.ops.lib.ktc_scalar_inplace(op, self._buf(), float(s), self.size))
 
     def _unary(self, op: int) -> "CUDARawTensor":
-        if self.ops.lazy:
+        if self.ops.lazy and op <= L.NEG:                       # the ops the fused expression kernels implement
             return self.ops._deferred("un", self.shape, op, (self._as_node(),))
         res = self._new(self.shape)
         L.check(self.ops.lib.ktc_unary(op, res._buf(), self._buf(), self.size))
@@ -271,6 +274,55 @@ class CUDARawTensor:
     def sigmoid(self):
         return self._unary(L.SIGMOID)
 
+    # the remaining unary maps (JVMRawTensor.kt:401-435)
+    def sinh(self):
+        return self._unary(L.SINH)
+
+    def cosh(self):
+        return self._unary(L.COSH)
+
+    def abs(self):
+        return self._unary(L.ABS)
+
+    def sign(self):
+        return self._unary(L.SIGN)
+
+    def sqrt(self):
+        return self._unary(L.SQRT)
+
+    def sin(self):
+        return self._unary(L.SIN)
+
+    def cos(self):
+        return self._unary(L.COS)
+
+    def tan(self):
+        return self._unary(L.TAN)
+
+    def asin(self):
+        return self._unary(L.ASIN)
+
+    def acos(self):
+        return self._unary(L.ACOS)
+
+    def atan(self):
+        return self._unary(L.ATAN)
+
+    def floor(self):
+        return self._unary(L.FLOOR)
+
+    def ceil(self):
+        return self._unary(L.CEIL)
+
+    def round(self):
+        return self._unary(L.ROUND)
+
+    def trunc(self):
+        return self._unary(L.TRUNC)
+
+    def rsqrt(self):
+        return self._unary(L.RSQRT)
+
     def clamp(self, min: float, max: float):
         if self.ops.lazy:
             return self.ops._deferred("clamp", self.shape, 0, (self._as_node(),), imm=(float(min), float(max)))
@@ -285,17 +337,47 @@ class CUDARawTensor:
         L.check(self.ops.lib.ktc_compare_scalar(op, res._buf(), self._buf(), float(value), self.size))
         return res
 
-    def lt(self, value: float):
-        return self._compare(L.LT, value)
+    def _compare_any(self, op: int, other):
+        """lt/lte/gt/gte/eq/neq with a constant (JVMRawTensor.kt:379-393) or with a tensor of the same
+        shape (JVM:355-377: elementwiseOpOnCommonShapedTensors, no broadcasting)."""
+        if isinstance(other, CUDARawTensor):
+            if self.shape != other.shape:
+                raise ValueError(f"Tensor compare needs equal shapes, got {self.shape} and {other.shape}")
+            res = self._new(self.shape)
+            L.check(self.ops.lib.ktc_compare_tensor(op, res._buf(), self._buf(), other._buf(), self.ops.epsilon, self.size))
+            return res
+        if op in (L.EQ, L.NEQ):
+            res = self._new(self.shape)
+            L.check(self.ops.lib.ktc_compare_scalar_eps(op, res._buf(), self._buf(), float(other), self.ops.epsilon, self.size))
+            return res
+        return self._compare(op, other)
 
-    def lte(self, value: float):
-        return self._compare(L.LTE, value)
+    def lt(self, other):
+        return self._compare_any(L.LT, other)
 
-    def gt(self, value: float):
-        return self._compare(L.GT, value)
+    def lte(self, other):
+        return self._compare_any(L.LTE, other)
 
-    def gte(self, value: float):
-        return self._compare(L.GTE, value)
+    def gt(self, other):
+        return self._compare_any(L.GT, other)
+
+    def gte(self, other):
+        return self._compare_any(L.GTE, other)
+
+    def eq(self, other):
+        return self._compare_any(L.EQ, other)
+
+    def neq(self, other):
+        return self._compare_any(L.NEQ, other)
+
+    def maskedFill(self, mask: "CUDARawTensor", value: float) -> "CUDARawTensor":
+        """maskedFill (JVMRawTensor.kt:537-540): the mask is broadcast to this shape (never materialised)."""
+        SF.infer_explicit_broadcast_shape(mask.shape, self.shape)
+        res = self._new(self.shape)
+        sa, na = L.shape_array(self.shape)
+        sm, nm = L.shape_array(mask.shape)
+        L.check(self.ops.lib.ktc_masked_fill(res._buf(), self._buf(), sa, na, mask._buf(), sm, nm, float(value)))
+        return res
 
     # ---- broadcast / copies / shape-only ops -------------------------------------------
     def broadcastTo(self, shape: Sequence[int]) -> "CUDARawTensor":
@@ -448,20 +530,180 @@ class CUDARawTensor:
         L.check(self.ops.lib.ktc_sum_to_shape(res._buf(), so, no, self._buf(), si, ni))
         return res
 
-    def inplaceScatter(self, axis: int, index: "CUDARawTensor", src: "CUDARawTensor") -> None:
-        """inplaceScatter restricted to one index per position along `axis`
-        (index/src extent 1 there): the Max/Min backward
-        (AggregatingFunctions.kt:68-79; JVMRawTensor.kt:227-256)."""
+    def inplaceScatter(self, axis: int, index: "CUDARawTensor", src) -> None:
+        """inplaceScatter (JVMRawTensor.kt:227-251; with a constant: JVM:317-332).  One index per position
+        along `axis` over the whole target -- the Max/Min backward (AggregatingFunctions.kt:68-79) -- takes a
+        fully parallel kernel; every other form the general one."""
+        if not isinstance(src, CUDARawTensor):
+            self._scatter_nd(L.SCATTER_CONST, axis, index, float(src))
+            return
         a = SF.normalize_axis(self.shape, axis)
         if len(index.shape) != len(self.shape) or len(src.shape) != len(self.shape):
             raise ValueError("Scatter expects tensors (target, index, source) to have the same dimensions, but got "
                              f"tensors with shapes: target: {self.shape}, index: {index.shape}, source: {src.shape}")
-        if index.shape[a] != 1 or index.shape != src.shape:
-            raise NotImplementedError("kten-cuda scatters one index per position along the axis (selection backward)")
+        if index.shape[a] != 1 or index.shape != src.shape or index.shape[:a] + index.shape[a + 1:] != self.shape[:a] + self.shape[a + 1:]:
+            self._scatter_nd(L.SCATTER_SET, axis, index, src)       # several positions along the axis / smaller index
+            return
         outer, length, inner = SF.collapse_axis(self.shape, a)
         self._buf()
         self._before_inplace_write()
         L.check(self.ops.lib.ktc_scatter_axis(self._buf(), index._buf(), src._buf(), outer, length, inner))
+
+    # ---- slices, permutes, gather / scatter (JVMRawTensor.kt:227-353, 437-518) -----------------
+    def _box(self, ranges):
+        """(offset, box shape) of a normalised range index; trailing dimensions are taken whole."""
+        st = SF.strides_of(self.shape)
+        off = sum(f * st[d] for d, (f, _) in enumerate(ranges))
+        return off, [l - f + 1 for f, l in ranges] + list(self.shape[len(ranges):]), st
+
+    def get(self, index) -> "CUDARawTensor":
+        """get(IntArray) / get(Array<IntRange>) (JVM:270-280): a copy of the addressed sub-tensor.  `index` is a
+        sequence of ints, or of ranges (see shape_functions.as_range)."""
+        index = list(index)
+        if all(isinstance(i, (int, np.integer)) for i in index):
+            norm, res_shape = SF.normalized_indexed_shape(self.shape, index)
+            sub = SF.to_store_size(self.shape[len(norm):])
+            start = 0
+            for d, i in enumerate(norm):
+                start = start * self.shape[d] + i
+            res = self._new(res_shape)
+            L.check(self.ops.lib.ktc_d2d(res._buf(), 0, self._buf(), start * sub, sub))
+            return res
+        norm, res_shape = SF.normalized_indexed_shape_ranges(self.shape, index)
+        off, box, st = self._box(norm)
+        res = self._new(res_shape)
+        pb, nb = L.shape_array(box)
+        ps, _ = L.shape_array(st)
+        pd, _ = L.shape_array(SF.strides_of(box))
+        L.check(self.ops.lib.ktc_copy_strided(res._buf(), 0, pd, self._buf(), off, ps, pb, nb))
+        return res
+
+    def set(self, index, value) -> None:
+        """set(index, tensor | constant) (JVM:282-315): the value tensor is taken in store order and only its
+        element count has to match the addressed box."""
+        index = list(index)
+        if all(isinstance(i, (int, np.integer)) for i in index):
+            norm = SF.normalize_index(self.shape, index)
+            ranges = [(i, i) for i in norm]
+        else:
+            ranges = SF.normalize_index_ranges(self.shape, index)
+        off, box, st = self._box(ranges)
+        n = SF.to_store_size(box)
+        self._buf()
+        self._before_inplace_write()
+        pb, nb = L.shape_array(box)
+        ps, _ = L.shape_array(st)
+        if isinstance(value, CUDARawTensor):
+            if value.size != n:
+                raise ValueError(f"Cannot set tensor with shape: {value.shape} to tensor with shape: {self.shape} at index: {index}")
+            pv, _ = L.shape_array(SF.strides_of(box))
+            L.check(self.ops.lib.ktc_copy_strided(self._buf(), off, ps, value._buf(), 0, pv, pb, nb))
+        else:
+            L.check(self.ops.lib.ktc_fill_strided(self._buf(), off, ps, pb, nb, float(value)))
+
+    def narrow(self, axis: int, start: int, length: int) -> "CUDARawTensor":
+        """narrow (JVM:468-482)."""
+        a = SF.normalize_axis(self.shape, axis)
+        ranges = [(0, d - 1) for d in self.shape]
+        ranges[a] = (start, start + length - 1)
+        return self.get(ranges)
+
+    def permute(self, axes: Sequence[int]) -> "CUDARawTensor":
+        """permute (JVM:453-466): result dimension i is this tensor's dimension axes[i]."""
+        axes = [int(a) for a in axes]
+        new_shape = SF.permute(self.shape, axes)
+        st = SF.strides_of(self.shape)
+        res = self._new(new_shape)
+        pb, nb = L.shape_array(new_shape)
+        ps, _ = L.shape_array([st[a] for a in axes])
+        pd, _ = L.shape_array(SF.strides_of(new_shape))
+        L.check(self.ops.lib.ktc_copy_strided(res._buf(), 0, pd, self._buf(), 0, ps, pb, nb))
+        return res
+
+    def transpose(self, axis1: int, axis2: int) -> "CUDARawTensor":
+        """transpose (JVM:437-451)."""
+        _, a1, a2 = SF.transpose_normalize_axes(self.shape, axis1, axis2)
+        axes = list(range(len(self.shape)))
+        axes[a1], axes[a2] = a2, a1
+        return self.permute(axes)
+
+    def gather(self, axis: int, index: "CUDARawTensor") -> "CUDARawTensor":
+        """gather (JVM:334-353): the result has the index's shape."""
+        a = SF.normalize_axis(self.shape, axis)
+        if len(index.shape) != len(self.shape):
+            raise ValueError(f"Gather expects the index to have the tensor's dimensions, got {index.shape} for {self.shape}")
+        res = self._new(index.shape)
+        pi, n = L.shape_array(self.shape)
+        px, _ = L.shape_array(index.shape)
+        L.check(self.ops.lib.ktc_gather_axis(res._buf(), self._buf(), pi, index._buf(), px, n, a))
+        return res
+
+    def _scatter_nd(self, mode: int, axis: int, index: "CUDARawTensor", src) -> None:
+        if mode == L.SCATTER_CONST:
+            a = SF.normalize_axis(self.shape, axis)
+            if len(index.shape) != len(self.shape):
+                raise ValueError(f"Scatter expects the index to have the target's dimensions, got {index.shape} for {self.shape}")
+        else:
+            a = SF.normalized_axis_scatter(self.shape, axis, index.shape, src.shape)
+        self._buf()
+        self._before_inplace_write()
+        pt, n = L.shape_array(self.shape)
+        px, _ = L.shape_array(index.shape)
+        if mode == L.SCATTER_CONST:
+            L.check(self.ops.lib.ktc_scatter_axis_nd(mode, self._buf(), pt, index._buf(), px, 0, None, n, a, float(src)))
+        else:
+            ps, _ = L.shape_array(src.shape)
+            L.check(self.ops.lib.ktc_scatter_axis_nd(mode, self._buf(), pt, index._buf(), px, src._buf(), ps, n, a, 0.0))
+
+    def inplaceScatterAdd(self, axis: int, index: "CUDARawTensor", src: "CUDARawTensor") -> None:
+        """inplaceScatterAdd (JVM:253-255)."""
+        self._scatter_nd(L.SCATTER_ADD, axis, index, src)
+
+    def scatter(self, axis: int, index: "CUDARawTensor", src) -> "CUDARawTensor":
+        """scatter (AbstractRawTensor.kt: copy, then the in-place form); src is a tensor or a constant."""
+        res = self.copy()
+        res.inplaceScatter(axis, index, src)
+        return res
+
+    def scatterAdd(self, axis: int, index: "CUDARawTensor", src: "CUDARawTensor") -> "CUDARawTensor":
+        res = self.copy()
+        res.inplaceScatterAdd(axis, index, src)
+        return res
+
+    def indexSelect(self, axis: int, index: "CUDARawTensor") -> "CUDARawTensor":
+        """indexSelect (JVM:484-502)."""
+        a, res_shape = SF.index_select_norm_axis_shape(self.shape, axis, index.shape)
+        outer, length, inner = SF.collapse_axis(self.shape, a)
+        res = self._new(res_shape)
+        L.check(self.ops.lib.ktc_index_select(res._buf(), self._buf(), index._buf(), outer, length, index.shape[0], inner))
+        return res
+
+    def indexAdd(self, axis: int, index: "CUDARawTensor", src: "CUDARawTensor", alpha: float = 1.0) -> None:
+        """indexAdd (JVM:504-518)."""
+        a = SF.index_add_check_shapes_norm_axis(self.shape, axis, index.shape, src.shape)
+        outer, length, inner = SF.collapse_axis(self.shape, a)
+        self._buf()
+        self._before_inplace_write()
+        L.check(self.ops.lib.ktc_index_add(self._buf(), index._buf(), src._buf(), float(alpha), outer, length, index.shape[0], inner))
+
+    def inplaceResize(self, *shape) -> None:
+        """inplaceResize (JVM:524-531): the store is copied into one of the new size (zero-padded or cut)."""
+        if len(shape) == 1 and isinstance(shape[0], (list, tuple)):
+            shape = shape[0]
+        new_shape = [int(d) for d in shape]
+        n_new, n_old = SF.to_store_size(new_shape), self.size
+        old = self._buf()
+        h = C.c_uint64(0)
+        L.check(self.ops.lib.ktc_alloc(self.ops.device, n_new, C.byref(h)))
+        keep = min(n_new, n_old)
+        if keep:
+            L.check(self.ops.lib.ktc_d2d(h.value, 0, old, 0, keep))
+        if n_new > keep:
+            L.check(self.ops.lib.ktc_fill(h.value, keep, n_new - keep, 0.0))
+        self._before_inplace_write()
+        L.check(self.ops.lib.ktc_release(old))
+        self._store, self._node = h.value, None
+        self.shape = new_shape
 
     def __repr__(self) -> str:
         where = "deferred" if self.isDeferred else f"buf=0x{(self._store or 0):x}"

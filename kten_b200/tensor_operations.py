@@ -67,6 +67,7 @@ class CUDATensorOperations:
         self.deviceName, self.totalMemory, self.smCount = name.value.decode(), mem.value, sms.value
         self.platformKey = f"CUDA - {device} - {self.deviceName}"
         self._tls = threading.local()
+        self.epsilon = 1e-7                 # PlatformProvider.epsilon (PlatformProvider.kt:12): eq / neq tolerance
         # deferred elementwise expressions (kten_b200.lazy): off = every call runs at once, like kten-jvm
         self.lazy = False
         self._deps = {}                     # buffer handle -> WeakSet of storage cells whose pending expressions read it
@@ -378,6 +379,22 @@ class CUDATensorOperations:
         raw.mustSurviveGC = False
 
     # ---- ops that live on the operations object ---------------------------------------
+    def concat(self, axis: int, inputs: Sequence[CUDARawTensor]) -> CUDARawTensor:
+        """concat (AbstractJVMTensorOperations.kt:106-120): each input is written into its range of the result."""
+        shapes = [t.shape for t in inputs]
+        res_shape = SF.concat_shapes(shapes, axis)
+        a = SF.normalize_axis(shapes[0], axis)
+        res = self.createRaw(res_shape)
+        ranges = [(0, d - 1) for d in res_shape]
+        last = 0
+        for t in inputs:
+            if t.shape[a] == 0:
+                continue
+            ranges[a] = (last, last + t.shape[a] - 1)
+            res.set(ranges, t)
+            last += t.shape[a]
+        return res
+
     def pow(self, constant: float, raw: CUDARawTensor) -> CUDARawTensor:
         """pow(constant, raw) = constant ^ raw (TensorOperations.kt:39)."""
         return raw._scalar(L.POW, constant, scalar_first=True)

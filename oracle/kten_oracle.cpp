@@ -42,7 +42,10 @@ enum { KTO_OK = 0, KTO_EINVAL = -1 };
 
 // op codes shared with include/kten_cuda.h
 enum { OP_PLUS = 0, OP_MINUS = 1, OP_TIMES = 2, OP_DIV = 3, OP_POW = 4 };
-enum { U_EXP = 0, U_LOG = 1, U_TANH = 2, U_SIGMOID = 3, U_RECIPROCAL = 4, U_NEG = 5 };
+enum { U_EXP = 0, U_LOG = 1, U_TANH = 2, U_SIGMOID = 3, U_RECIPROCAL = 4, U_NEG = 5,
+       U_SINH = 6, U_COSH = 7, U_ABS = 8, U_SIGN = 9, U_SQRT = 10, U_SIN = 11, U_COS = 12, U_TAN = 13,
+       U_ASIN = 14, U_ACOS = 15, U_ATAN = 16, U_FLOOR = 17, U_CEIL = 18, U_ROUND = 19, U_TRUNC = 20, U_RSQRT = 21 };
+enum { C_LT = 0, C_LTE = 1, C_GT = 2, C_GTE = 3, C_EQ = 4, C_NEQ = 5 };
 enum { R_SUM = 0, R_MEAN = 1, R_MAX = 2, R_MIN = 3, R_ARGMAX = 4, R_ARGMIN = 5 };
 
 // ---------------------------------------------------------------------------
@@ -100,7 +103,41 @@ static inline float un_op(int op, float x) {
         return 1.0f / (1.0f + e);
     }
     case U_RECIPROCAL: return 1.0f / x;                            // JVM:142
-    default:      return -x;                                       // JVM:122
+    case U_NEG:   return -x;                                       // JVM:122
+    // kotlin.math.f(Float) = Math.f(x.toDouble()).toFloat() for the functions below
+    case U_SINH:  return (float)std::sinh((double)x);              // JVM:401
+    case U_COSH:  return (float)std::cosh((double)x);              // JVM:403
+    case U_ABS:   return std::fabs(x);                             // JVM:405
+    case U_SIGN:  return (x != x || x == 0.0f) ? x : (x > 0.0f ? 1.0f : -1.0f);   // JVM:407, Math.signum
+    case U_SQRT:  return (float)std::sqrt((double)x);              // JVM:413
+    case U_SIN:   return (float)std::sin((double)x);               // JVM:415
+    case U_COS:   return (float)std::cos((double)x);               // JVM:417
+    case U_TAN:   return (float)std::tan((double)x);               // JVM:419
+    case U_ASIN:  return (float)std::asin((double)x);              // JVM:421
+    case U_ACOS:  return (float)std::acos((double)x);              // JVM:423
+    case U_ATAN:  return (float)std::atan((double)x);              // JVM:425
+    case U_FLOOR: return (float)std::floor((double)x);             // JVM:427
+    case U_CEIL:  return (float)std::ceil((double)x);              // JVM:429
+    case U_ROUND: {                                                // JVM:431: Math.round(float).toFloat()
+        if (x != x) return 0.0f;                                   // (int) NaN == 0
+        double r = std::floor((double)x + 0.5);                    // exact in double; ties go up
+        if (r >= 2147483647.0) return (float)2147483647;           // saturates at the Int range
+        if (r <= -2147483648.0) return (float)(-2147483647 - 1);
+        return (float)(int32_t)r;                                  // through an Int: never -0
+    }
+    case U_TRUNC: return (x != x || std::isinf(x)) ? x : (x > 0.0f ? (float)std::floor((double)x) : (float)std::ceil((double)x));  // JVM:433, kotlin.math.truncate
+    default:      return 1.0f / (float)std::sqrt((double)x);       // JVM:435: 1f / sqrt(x)
+    }
+}
+
+static inline float cmp_op(int op, float a, float b, float eps) {   // JVM:355-393
+    switch (op) {
+    case C_LT:  return a < b ? 1.0f : 0.0f;
+    case C_LTE: return a <= b ? 1.0f : 0.0f;
+    case C_GT:  return a > b ? 1.0f : 0.0f;
+    case C_GTE: return a >= b ? 1.0f : 0.0f;
+    case C_EQ:  return std::fabs(a - b) < eps ? 1.0f : 0.0f;
+    default:    return std::fabs(a - b) < eps ? 0.0f : 1.0f;
     }
 }
 
@@ -224,6 +261,28 @@ KTO_API int kto_unary(int op, const float* a, float* out, int64_t n, int tuned) 
     } else {
         for (int64_t i = 0; i < n; ++i) out[i] = un_op(op, a[i]);
     }
+    return KTO_OK;
+}
+
+// tensor (cmp) tensor on equal shapes and tensor (cmp) constant (JVM:355-393): 1.0f / 0.0f.
+KTO_API int kto_compare_tensor(int op, const float* a, const float* b, float eps, float* out, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) out[i] = cmp_op(op, a[i], b[i], eps);
+    return KTO_OK;
+}
+KTO_API int kto_compare_scalar(int op, const float* a, float v, float eps, float* out, int64_t n) {
+    for (int64_t i = 0; i < n; ++i) out[i] = cmp_op(op, a[i], v, eps);
+    return KTO_OK;
+}
+
+// maskedFill (JVM:537-540): the mask is broadcast to the tensor's shape, then
+// out = (mask == 1f) ? value : this.
+KTO_API int kto_masked_fill(const float* a, const int64_t* ashape, int an, const float* mask, const int64_t* mshape, int mn,
+                            float value, float* out) {
+    int64_t n = 1;
+    for (int i = 0; i < an; ++i) n *= ashape[i];
+    std::vector<float> m((size_t)n);
+    if (kto_broadcast_to(mask, mshape, mn, ashape, an, m.data()) != KTO_OK) return KTO_EINVAL;
+    for (int64_t i = 0; i < n; ++i) out[i] = (m[(size_t)i] == 1.0f) ? value : a[i];
     return KTO_OK;
 }
 

@@ -29,6 +29,8 @@ LIB_PATH = os.path.join(HERE, "libkten_oracle.so")
 
 PLUS, MINUS, TIMES, DIV, POW = range(5)
 EXP, LOG, TANH, SIGMOID, RECIPROCAL, NEG = range(6)
+(SINH, COSH, ABS, SIGN, SQRT, SIN, COS, TAN, ASIN, ACOS, ATAN, FLOOR, CEIL, ROUND, TRUNC, RSQRT) = range(6, 22)
+LT, LTE, GT, GTE, EQ, NEQ = range(6)
 SUM, MEAN, MAX, MIN, ARGMAX, ARGMIN = range(6)
 
 _lib = None
@@ -58,6 +60,9 @@ def lib() -> C.CDLL:
         l.kto_scalar_inplace.argtypes = [C.c_int, p_f32, C.c_float, C.c_int64]
         l.kto_unary.argtypes = [C.c_int, p_f32, p_f32, C.c_int64, C.c_int]
         l.kto_clamp.argtypes = [p_f32, C.c_float, C.c_float, p_f32, C.c_int64, C.c_int]
+        l.kto_compare_tensor.argtypes = [C.c_int, p_f32, p_f32, C.c_float, p_f32, C.c_int64]
+        l.kto_compare_scalar.argtypes = [C.c_int, p_f32, C.c_float, C.c_float, p_f32, C.c_int64]
+        l.kto_masked_fill.argtypes = [p_f32, p_i64, C.c_int, p_f32, p_i64, C.c_int, C.c_float, p_f32]
         l.kto_fill.argtypes = [p_f32, C.c_float, C.c_int64]
         l.kto_aggregate_axis.argtypes = [C.c_int, p_f32, C.c_int64, C.c_int64, C.c_int64, p_f32, C.c_int]
         l.kto_reduce_all.argtypes = [C.c_int, p_f32, C.c_int64, p_f32, C.c_int]
@@ -159,6 +164,29 @@ def clamp(a, lo: float, hi: float, tuned: bool = False) -> np.ndarray:
     return out
 
 
+def compare(op: int, a, other, eps: float = 1e-7) -> np.ndarray:
+    """lt/lte/gt/gte/eq/neq against a same-shape tensor or a constant (JVMRawTensor.kt:355-393)."""
+    a = _flat(a)
+    out = np.empty_like(a)
+    if isinstance(other, np.ndarray):
+        b = _flat(other)
+        assert b.size == a.size
+        lib().kto_compare_tensor(op, _f(a), _f(b), C.c_float(eps), _f(out), a.size)
+    else:
+        lib().kto_compare_scalar(op, _f(a), C.c_float(other), C.c_float(eps), _f(out), a.size)
+    return out
+
+
+def masked_fill(a, a_shape, mask, mask_shape, value: float) -> np.ndarray:
+    a, mask = _flat(a), _flat(mask)
+    out = np.empty_like(a)
+    sa, na = _s(a_shape)
+    sm, nm = _s(mask_shape)
+    if lib().kto_masked_fill(_f(a), sa, na, _f(mask), sm, nm, C.c_float(value), _f(out)) != 0:
+        raise ValueError(f"mask with shape {list(mask_shape)} cannot be broadcast to {list(a_shape)}")
+    return out
+
+
 def aggregate(op: int, a, outer: int, axis_len: int, inner: int, mode: int = 1) -> np.ndarray:
     a = _flat(a)
     assert a.size == outer * axis_len * inner
@@ -218,6 +246,12 @@ def _normalize_axis(shape, axis):
     return r
 
 
+def _SF():
+    """The host shape algebra (a restatement of ShapeFunctions.kt) is shared with the backend's host side."""
+    from kten_b200 import shape_functions
+    return shape_functions
+
+
 class OracleRawTensor:
     def __init__(self, shape, data: np.ndarray, ops: "OracleTensorOperations"):
         self.shape = [int(d) for d in shape]
@@ -267,10 +301,183 @@ class OracleRawTensor:
     def tanh(self): return self._wrap(unary(TANH, self.data))
     def sigmoid(self): return self._wrap(unary(SIGMOID, self.data))
     def clamp(self, min, max): return self._wrap(clamp(self.data, min, max))
-    def gte(self, v): return self._wrap((self.data >= np.float32(v)).astype(np.float32))
-    def lte(self, v): return self._wrap((self.data <= np.float32(v)).astype(np.float32))
-    def gt(self, v): return self._wrap((self.data > np.float32(v)).astype(np.float32))
-    def lt(self, v): return self._wrap((self.data < np.float32(v)).astype(np.float32))
+    # the remaining unary maps (JVMRawTensor.kt:401-435)
+    def sinh(self): return self._wrap(unary(SINH, self.data))
+    def cosh(self): return self._wrap(unary(COSH, self.data))
+    def abs(self): return self._wrap(unary(ABS, self.data))
+    def sign(self): return self._wrap(unary(SIGN, self.data))
+    def sqrt(self): return self._wrap(unary(SQRT, self.data))
+    def sin(self): return self._wrap(unary(SIN, self.data))
+    def cos(self): return self._wrap(unary(COS, self.data))
+    def tan(self): return self._wrap(unary(TAN, self.data))
+    def asin(self): return self._wrap(unary(ASIN, self.data))
+    def acos(self): return self._wrap(unary(ACOS, self.data))
+    def atan(self): return self._wrap(unary(ATAN, self.data))
+    def floor(self): return self._wrap(unary(FLOOR, self.data))
+    def ceil(self): return self._wrap(unary(CEIL, self.data))
+    def round(self): return self._wrap(unary(ROUND, self.data))
+    def trunc(self): return self._wrap(unary(TRUNC, self.data))
+    def rsqrt(self): return self._wrap(unary(RSQRT, self.data))
+
+    def _cmp(self, op, other):
+        # JVMRawTensor.kt:355-393: tensor compares need equal shapes (elementwiseOpOnCommonShapedTensors)
+        if isinstance(other, OracleRawTensor):
+            if self.shape != other.shape:
+                raise ValueError(f"Tensor compare needs equal shapes, got {self.shape} and {other.shape}")
+            return self._wrap(compare(op, self.data, other.data, self.ops.epsilon))
+        return self._wrap(compare(op, self.data, float(other), self.ops.epsilon))
+
+    def lt(self, o): return self._cmp(LT, o)
+    def lte(self, o): return self._cmp(LTE, o)
+    def gt(self, o): return self._cmp(GT, o)
+    def gte(self, o): return self._cmp(GTE, o)
+    def eq(self, o): return self._cmp(EQ, o)
+    def neq(self, o): return self._cmp(NEQ, o)
+
+    def maskedFill(self, mask, value):
+        return self._wrap(masked_fill(self.data, self.shape, mask.data, mask.shape, value))
+
+    def containsNan(self):
+        return bool(np.isnan(self.data).any())                      # JVMRawTensor.kt:520-522
+
+    # ---- slices, permutes, gather / scatter: index arithmetic restated with numpy ----------------
+    def _nd(self):
+        return self.data.reshape(self.shape)
+
+    def view(self, shape):
+        return self._wrap(self.data, _SF().reshape(self.shape, shape))    # JVM:264-268: same store
+
+    def reshape(self, shape):
+        return self._wrap(self.data.copy(), _SF().reshape(self.shape, shape))
+
+    def inplaceReshape(self, shape):
+        self.shape = _SF().reshape(self.shape, shape)
+
+    def inplaceSqueeze(self, axis):
+        s = list(self.shape)
+        del s[_normalize_axis(self.shape, axis)]
+        self.shape = s
+
+    def squeeze(self, axis):
+        res = self.copy()
+        res.inplaceSqueeze(axis)
+        return res
+
+    def unsqueeze(self, axis):
+        res = self.copy()
+        res.inplaceUnsqueeze(axis)
+        return res
+
+    def get(self, index):
+        """JVM:270-280: an IntArray addresses one contiguous store range, IntRanges a box."""
+        SF = _SF()
+        index = list(index)
+        if all(isinstance(i, (int, np.integer)) for i in index):
+            norm, res_shape = SF.normalized_indexed_shape(self.shape, index)
+            return self._wrap(self._nd()[tuple(norm)].reshape(-1).copy(), res_shape)
+        norm, res_shape = SF.normalized_indexed_shape_ranges(self.shape, index)
+        return self._wrap(self._nd()[tuple(slice(f, l + 1) for f, l in norm)].reshape(-1).copy(), res_shape)
+
+    def set(self, index, value):
+        """JVM:282-315: the value is taken in store order; only its element count must match."""
+        SF = _SF()
+        index = list(index)
+        if all(isinstance(i, (int, np.integer)) for i in index):
+            sel = tuple(SF.normalize_index(self.shape, index))
+        else:
+            sel = tuple(slice(f, l + 1) for f, l in SF.normalize_index_ranges(self.shape, index))
+        target = self._nd()
+        box = target[sel]
+        if isinstance(value, OracleRawTensor):
+            if value.data.size != box.size:
+                raise ValueError(f"Cannot set tensor with shape: {value.shape} to tensor with shape: {self.shape} at index: {index}")
+            target[sel] = value.data.reshape(box.shape)
+        else:
+            target[sel] = np.float32(value)
+
+    def narrow(self, axis, start, length):                          # JVM:468-482
+        a = _normalize_axis(self.shape, axis)
+        ranges = [(0, d - 1) for d in self.shape]
+        ranges[a] = (start, start + length - 1)
+        return self.get(ranges)
+
+    def permute(self, axes):                                        # JVM:453-466: res dim i = this dim axes[i]
+        new_shape = _SF().permute(self.shape, axes)
+        return self._wrap(np.ascontiguousarray(np.transpose(self._nd(), axes)).reshape(-1), new_shape)
+
+    def transpose(self, axis1, axis2):                              # JVM:437-451
+        new_shape, a1, a2 = _SF().transpose_normalize_axes(self.shape, axis1, axis2)
+        return self._wrap(np.ascontiguousarray(np.swapaxes(self._nd(), a1, a2)).reshape(-1), new_shape)
+
+    def gather(self, axis, index):
+        """JVM:334-353: res[c] = this[c with c[axis] = index[c]] for every position c of the index."""
+        a = _normalize_axis(self.shape, axis)
+        idx = index.data.reshape(index.shape).astype(np.int64)      # Float.toInt(): truncation
+        if ((idx < 0) | (idx >= self.shape[a])).any():
+            raise ValueError(f"Gather got invalid index, index value is out of bounds 0 and {self.shape[a]} at axis: {axis}")
+        src = self._nd()[tuple(slice(0, d) if k != a else slice(None) for k, d in enumerate(index.shape))]
+        return self._wrap(np.take_along_axis(src, idx, axis=a).reshape(-1).astype(np.float32), list(index.shape))
+
+    def _scatter(self, axis, index, src, add):
+        """internalInplaceScatter (JVM:227-247) / inplaceScatter(value) (JVM:317-332): sequential in the index
+        position along the axis, so repeated indices resolve in that order."""
+        const = not isinstance(src, OracleRawTensor)
+        if const:
+            a = _normalize_axis(self.shape, axis)
+        else:
+            a = _SF().normalized_axis_scatter(self.shape, axis, index.shape, src.shape)
+        idx = index.data.reshape(index.shape).astype(np.int64)
+        if ((idx < 0) | (idx >= self.shape[a])).any():
+            raise ValueError(f"Scatter got invalid index, index value is out of bounds 0 and {self.shape[a]} at axis: {axis}")
+        target = self._nd()
+        other = [np.arange(d) for k, d in enumerate(index.shape) if k != a]
+        grids = np.meshgrid(*other, indexing="ij") if other else []
+        srcv = None if const else src.data.reshape(src.shape)
+        for i in range(index.shape[a]):
+            coords = list(grids)
+            coords.insert(a, np.take(idx, i, axis=a))
+            scoords = list(grids)
+            scoords.insert(a, np.full_like(coords[a], i))
+            if const:
+                target[tuple(coords)] = np.float32(src)
+            elif add:
+                target[tuple(coords)] = target[tuple(coords)] + srcv[tuple(scoords)]
+            else:
+                target[tuple(coords)] = srcv[tuple(scoords)]
+
+    def inplaceScatter(self, axis, index, src): self._scatter(axis, index, src, False)
+    def inplaceScatterAdd(self, axis, index, src): self._scatter(axis, index, src, True)
+
+    def scatter(self, axis, index, src):                            # AbstractRawTensor.kt:150-160
+        res = self.copy()
+        res.inplaceScatter(axis, index, src)
+        return res
+
+    def indexSelect(self, axis, index):                             # JVM:484-502
+        a, res_shape = _SF().index_select_norm_axis_shape(self.shape, axis, index.shape)
+        idx = index.data.astype(np.int64)
+        if ((idx < 0) | (idx >= self.shape[a])).any():
+            raise ValueError(f"Index select got invalid index, index value is out of bounds 0 and {self.shape[a]} at axis: {axis}")
+        return self._wrap(np.ascontiguousarray(np.take(self._nd(), idx, axis=a)).reshape(-1), res_shape)
+
+    def indexAdd(self, axis, index, src, alpha=1.0):                # JVM:504-518: k ascending, += src * alpha
+        a = _SF().index_add_check_shapes_norm_axis(self.shape, axis, index.shape, src.shape)
+        idx = index.data.astype(np.int64)
+        if ((idx < 0) | (idx >= self.shape[a])).any():
+            raise ValueError(f"Index Add got invalid index, index value is out of bounds 0 and {self.shape[a]} at axis: {axis}")
+        target, srcv = self._nd(), src.data.reshape(src.shape)
+        for k, j in enumerate(idx):
+            sel_t = tuple(slice(None) if d != a else int(j) for d in range(len(self.shape)))
+            sel_s = tuple(slice(None) if d != a else k for d in range(len(self.shape)))
+            target[sel_t] = target[sel_t] + srcv[sel_s] * np.float32(alpha)
+
+    def inplaceResize(self, *shape):                                # JVM:524-531
+        if len(shape) == 1 and isinstance(shape[0], (list, tuple)):
+            shape = shape[0]
+        new = np.zeros(volume(shape), dtype=np.float32)
+        keep = min(new.size, self.data.size)
+        new[:keep] = self.data[:keep]
+        self.data, self.shape = new, [int(d) for d in shape]
 
     def broadcastTo(self, shape):
         shape = [int(d) for d in shape]
@@ -322,17 +529,6 @@ class OracleRawTensor:
     def sumToShape(self, old_shape):
         return self._wrap(sum_to_shape(self.data, self.shape, old_shape, self.ops.mode), list(old_shape))
 
-    def inplaceScatter(self, axis, index, src):
-        # internalInplaceScatter (JVMRawTensor.kt:227-248) for index extent 1 along the axis
-        a = _normalize_axis(self.shape, axis)
-        outer, A, inner = volume(self.shape[:a]), self.shape[a], volume(self.shape[a + 1:])
-        t = self.data.reshape(outer, A, inner)
-        idx = index.data.reshape(outer, inner).astype(np.int64)
-        if ((idx < 0) | (idx >= A)).any():
-            raise ValueError(f"Scatter got invalid index, index value is out of bounds 0 and {A} at axis: {axis}")
-        o, i = np.meshgrid(np.arange(outer), np.arange(inner), indexing="ij")
-        t[o, idx, i] = src.data.reshape(outer, inner)
-
 
 class _Scope:
     def __enter__(self): return self
@@ -348,6 +544,7 @@ class OracleTensorOperations:
 
     def __init__(self, mode: int = 1):
         self.mode = mode
+        self.epsilon = 1e-7                     # PlatformProvider.epsilon (PlatformProvider.kt:12)
 
     def createRaw(self, shape, init=None):
         n = volume(shape)
@@ -372,3 +569,19 @@ class OracleTensorOperations:
 
     def pow(self, constant, raw):
         return OracleRawTensor(raw.shape, scalar(POW, raw.data, float(constant), scalar_first=True), self)
+
+    def concat(self, axis, inputs):
+        """AbstractJVMTensorOperations.kt:106-120: every input is set into its range of the result."""
+        SF = _SF()
+        res_shape = SF.concat_shapes([t.shape for t in inputs], axis)
+        a = _normalize_axis(inputs[0].shape, axis)
+        res = self.createRaw(res_shape)
+        ranges = [(0, d - 1) for d in res_shape]
+        last = 0
+        for t in inputs:
+            if t.shape[a] == 0:
+                continue
+            ranges[a] = (last, last + t.shape[a] - 1)
+            res.set(ranges, t)
+            last += t.shape[a]
+        return res

@@ -113,5 +113,93 @@ def run_case(ops, case):
         out.backward(_t(ops, ones))
         assert_tensor_equals(case["grad_a"], t1.grad(), tol)
         assert_tensor_equals(case["grad_b"], t2.grad(), tol)
+    elif g in ("unary_sum_after_set", "unary_chain_sum"):
+        if g == "unary_sum_after_set":                     # elementwiseTestTensor().noGrad(); t1[1, 1] = -0.4f; asVariable
+            a = _t(ops, case["a"])
+            a[tuple(case["set_index"])] = case["set_value"]
+            a = a.asVariable(requiresGrad=True)
+            res = getattr(a, case["op"])()
+        else:
+            a = _t(ops, case["a"], True)
+            res = a
+            for op in case["ops"]:
+                res = getattr(res, op)()
+        assert_tensor_equals(case["res"], res, tol)
+        res.sum().backward()
+        assert_tensor_equals(case["grad_a"], a.grad(), tol)
+    elif g == "set_element_from_tensor":
+        t1, t2 = _t(ops, case["t1"], True), _t(ops, case["t2"], True)
+        t2[1, 1] = t1[1].pow(2.0)
+        t2.sum().backward()
+        t1.sum().backward()
+        assert_tensor_equals(case["res_t2"], t2, tol)
+        assert_tensor_equals(case["grad_t1"], t1.grad(), tol)
+    elif g == "set_element_range_from_tensor":
+        t1 = AG.tensorOf(ops, [0.1]).expand(3, 3).asVariable(requiresGrad=True)
+        t2 = AG.tensorOf(ops, [1.0]).expand(3, 3, 3).asVariable(requiresGrad=True)
+        t2[(1, 1), None, (1, -1)] = t1[None, (1, -1)].pow(2.0).unsqueeze(0)
+        t2.sum().backward()
+        t1.sum().backward()
+        assert_tensor_equals(case["res_t2"], t2, tol)
+        assert_tensor_equals(case["grad_t1"], t1.grad(), tol)
+    elif g == "set_constant":
+        t1 = AG.tensorOf(ops, [0.1]).expand(2, 4).asVariable(requiresGrad=True)
+        index = tuple(tuple(i) if isinstance(i, list) else i for i in case["index"])
+        t1[index] = case["value"]
+        assert_tensor_equals(case["res"], t1, tol)
+        t1.sum().backward()
+        assert_tensor_equals(case["res"], t1, tol)
+        assert_tensor_equals(case["grad"], t1.grad(), tol)
+    elif g == "transpose":
+        a = _t(ops, case["a"], True)
+        res = a.transpose(0, 1)
+        assert_tensor_equals(case["res"], res, tol)
+        res.backward(_t(ops, case["seed"]))
+        assert_tensor_equals(case["grad_a"], a.grad(), tol)
+    elif g == "permute":
+        a = _t(ops, case["a"], True)
+        res = a.permute(*case["axes"])
+        assert_tensor_equals(case["res"], res, tol)
+        res.pow(2.0).sum().backward()
+        assert_tensor_equals(case["grad_a"], a.grad(), tol)
+    elif g == "concat":
+        t1 = AG.tensorOf(ops, [1.0, 2.0, 3.0]).expand(2, 3).asVariable(requiresGrad=True)
+        t2 = AG.tensorOf(ops, [4.0, 5.0, 6.0]).expand(1, 3).asVariable(requiresGrad=True)
+        t3 = AG.tensorOf(ops, [7.0, 8.0, 9.0]).expand(1, 3).asVariable(requiresGrad=True)
+        res = AG.concat([t1, t2, t3])
+        assert_tensor_equals(case["res"], res, tol)
+        res.pow(2.0).sum().backward()
+        for t, key in ((t1, "grad_t1"), (t2, "grad_t2"), (t3, "grad_t3")):
+            assert_tensor_equals(case[key], t.grad(), tol)
+    elif g == "gather":
+        a = _t(ops, case["a"], True)
+        res = a.gather(case["axis"], _t(ops, case["index"]))
+        assert_tensor_equals(case["res"], res, tol)
+        res.sum().backward()
+        assert_tensor_equals(case["grad_a"], a.grad(), tol)
+    elif g == "scatter":
+        t1 = AG.tensorOf(ops, np.arange(1, 11, dtype=np.float32), [2, 5])          # Tensor.arrange(11f, start = 1f).reshape(2, 5)
+        zeros = lambda: AG.tensorOf(ops, np.zeros(15, dtype=np.float32), [3, 5])
+        assert_tensor_equals(case["res1"], zeros().scatter(0, _t(ops, case["index1"]), t1), tol)
+        assert_tensor_equals(case["res2"], zeros().scatter(1, _t(ops, case["index2"]), t1), tol)
+    elif g == "scatter_with_grads":
+        t1 = AG.tensorOf(ops, np.arange(1, 11, dtype=np.float32), [2, 5], requiresGrad=True)
+        target = AG.tensorOf(ops, np.zeros(15, dtype=np.float32), [3, 5], requiresGrad=True)
+        res = (target + 1.0).scatter(1, _t(ops, case["index"]), t1).pow(2.0)
+        assert_tensor_equals(case["res"], res, tol)
+        res.sum().backward()
+        assert_tensor_equals(case["grad_t1"], t1.grad(), tol)
+        assert_tensor_equals(case["grad_target"], target.grad(), tol)
+    elif g == "index_select":
+        t = AG.tensorOf(ops, np.arange(27, dtype=np.float32), [3, 3, 3], requiresGrad=True)
+        res = t.indexSelect(case["axis"], _t(ops, case["index"]))
+        assert_tensor_equals(case["res"], res, tol)
+        res.sum().backward()
+        assert_tensor_equals(case["grad"], t.grad(), tol)
+    elif g == "fill_partially":
+        t1 = AG.tensorOf(ops, np.ones(6, dtype=np.float32), [2, 3])
+        t1.getRawValue().timesAssign(2.0)                                           # t1 *= 2f on a no-grad tensor
+        t1[(0, 0), (1, 2)] = 0.0
+        assert_tensor_equals(case["res"], t1, tol)
     else:
         raise AssertionError(f"unknown graph {g}")

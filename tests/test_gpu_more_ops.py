@@ -1,0 +1,232 @@
+"""GPU parity of the raw-tensor ops beside the benchmarked sweep: the remaining unary maps, compares,
+maskedFill, containsNan, slices / permutes and gather / scatter / index ops, against the CPU oracle
+(oracle/) on the same seeded inputs, through the C ABI.  Exact for everything that is IEEE or index
+arithmetic; at most 2 ulp for the transcendental maps."""
+import numpy as np
+import pytest
+
+from kten_b200 import _lib as L
+from kten_b200 import datagen as D
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def same_bits(a, b):
+    a, b = np.asarray(a, np.float32), np.asarray(b, np.float32)
+    return a.shape == b.shape and np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+def same_values(a, b):
+    """Bit-equal, except that any NaN matches any NaN."""
+    a, b = np.asarray(a, np.float32), np.asarray(b, np.float32)
+    if a.shape != b.shape:
+        return False
+    na, nb = np.isnan(a), np.isnan(b)
+    return np.array_equal(na, nb) and np.array_equal(a.view(np.uint32)[~na], b.view(np.uint32)[~nb])
+
+
+ORACLE = O.OracleTensorOperations(1)
+EXACT_UNARY = ["abs", "sign", "sqrt", "floor", "ceil", "round", "trunc", "rsqrt"]
+ULP_UNARY = ["sinh", "cosh", "sin", "cos", "tan", "asin", "acos", "atan"]
+
+
+def special_values():
+    v = [0.0, -0.0, 0.5, -0.5, 1.5, -1.5, 2.5, -2.5, 0.49999997, -0.49999997, 0.50000006, 1.0, -1.0, 8388607.5, 8388608.0, 16777216.0,
+         -16777216.0, 2147483520.0, 2147483648.0, -2147483648.0, 4e9, -4e9, 1e-45, -1e-45, 1.1754944e-38, 3.4028235e38, -3.4028235e38,
+         np.inf, -np.inf, np.nan, 0.1, 0.9999999, 1.0000001, 4.0, 2.0, 0.25]
+    return np.array(v, dtype=np.float32)
+
+
+@pytest.mark.parametrize("name", EXACT_UNARY)
+def test_exact_unary_maps(cuda_ops, gc_scope, name):
+    x = np.concatenate([special_values(), D.uniform(100003, 31, -50.0, 50.0), np.round(D.uniform(4096, 32, -20.0, 20.0) * 2) / 2])
+    got = getattr(cuda_ops.createRaw([x.size], x), name)().toArray()
+    want = getattr(ORACLE.createRaw([x.size], x), name)().toArray()
+    assert same_values(got, want), name
+
+
+@pytest.mark.parametrize("name", ULP_UNARY)
+def test_transcendental_unary_maps_within_2_ulp(cuda_ops, gc_scope, name):
+    lo, hi = {"asin": (-1.0, 1.0), "acos": (-1.0, 1.0), "sinh": (-20.0, 20.0), "cosh": (-20.0, 20.0), "tan": (-1.5, 1.5)}.get(name, (-30.0, 30.0))
+    x = np.concatenate([D.uniform(1 << 18, 33, lo, hi), D.uniform(1 << 16, 34, lo / 64, hi / 64),
+                        np.array([0.0, -0.0, 1e-20, -1e-20, lo, hi], dtype=np.float32)])
+    if name in ("sin", "cos", "tan", "atan"):
+        x = np.concatenate([x, D.uniform(1 << 14, 35, -1e4, 1e4)]).astype(np.float32)
+    got = getattr(cuda_ops.createRaw([x.size], x), name)().toArray()
+    want = getattr(ORACLE.createRaw([x.size], x), name)().toArray()
+    ulp = O.ulp_distance(got, want)
+    assert int(ulp.max()) <= 2, f"{name}: {int(ulp.max())} ulp at x = {x[int(ulp.argmax())]!r}"
+
+
+def test_compares_and_masked_fill(cuda_ops, gc_scope):
+    n = 70001
+    a = np.round(D.uniform(n, 41, -3.0, 3.0) * 4) / 4
+    b = np.round(D.uniform(n, 42, -3.0, 3.0) * 4) / 4
+    a[:6] = [np.nan, 1.0, np.inf, -0.0, 1.0, 2.0]
+    b[:6] = [1.0, np.nan, np.inf, 0.0, 1.0 + 5e-8, 2.0 + 3e-7]
+    ga, gb = cuda_ops.createRaw([n], a), cuda_ops.createRaw([n], b)
+    oa, ob = ORACLE.createRaw([n], a), ORACLE.createRaw([n], b)
+    for name in ("lt", "lte", "gt", "gte", "eq", "neq"):
+        assert same_bits(getattr(ga, name)(gb).toArray(), getattr(oa, name)(ob).toArray()), name
+        assert same_bits(getattr(ga, name)(0.75).toArray(), getattr(oa, name)(0.75).toArray()), name
+    with pytest.raises(ValueError):
+        ga.lt(cuda_ops.createRaw([n - 1]))
+    # maskedFill: mask broadcast over leading / middle / trailing dimensions, values other than 1 do not select
+    shape = [6, 20, 36]
+    x = D.normal(6 * 20 * 36, 43)
+    for mshape in ([6, 20, 36], [36], [20, 1], [6, 1, 36], [1], [6, 1, 1]):
+        m = (D.uniform(int(np.prod(mshape)), 44, 0.0, 1.0) > 0.5).astype(np.float32)
+        m.reshape(-1)[0] = 2.0
+        got = cuda_ops.createRaw(shape, x).maskedFill(cuda_ops.createRaw(mshape, m), -7.5).toArray()
+        want = ORACLE.createRaw(shape, x).maskedFill(ORACLE.createRaw(mshape, m), -7.5).toArray()
+        assert same_bits(got, want), mshape
+    with pytest.raises(ValueError):
+        cuda_ops.createRaw(shape, x).maskedFill(cuda_ops.createRaw([5]), 0.0)
+
+
+def test_contains_nan(cuda_ops, gc_scope):
+    x = D.normal(300007, 45)
+    t = cuda_ops.createRaw([x.size], x)
+    assert t.containsNan() is False
+    x[123456] = np.nan
+    assert cuda_ops.createRaw([x.size], x).containsNan() is True
+    assert t.containsNan() is False                              # the flag of the previous call was cleared
+    x[:] = np.inf
+    assert cuda_ops.createRaw([x.size], x).containsNan() is False
+
+
+def pair(ops_list, shape, seed):
+    x = D.normal(int(np.prod(shape)), seed)
+    return [o.createRaw(shape, x) for o in ops_list]
+
+
+def test_get_set_narrow(cuda_ops, gc_scope):
+    shape = [5, 12, 7, 8]
+    g, o = pair((cuda_ops, ORACLE), shape, 51)
+    for index in ([2], [4, 11], [-1, -2, 3], [0, 0, 0, 7], [(1, 3)], [(0, 4), (2, 9)], [None, (3, 3), None, (4, 7)],
+                  [(-2, -1), None, (1, 5)], [slice(1, 4), slice(None), slice(2, 6), slice(0, 8)]):
+        assert same_bits(g.get(index).toArray(), o.get(index).toArray()), index
+        assert g.get(index).shape == o.get(index).shape
+    for axis, start, length in ((0, 1, 3), (1, 4, 8), (-1, 0, 4), (2, 6, 1)):
+        assert same_bits(g.narrow(axis, start, length).toArray(), o.narrow(axis, start, length).toArray())
+    # set: tensors and constants into boxes and single positions
+    for index, vshape in (([1], [12, 7, 8]), ([(1, 2), (0, 11), (3, 5)], [2, 12, 3, 8]), ([3, 2, (1, 1)][:2], [7, 8]),
+                          ([None, None, None, (4, 7)], [5 * 12 * 7 * 4])):
+        gv, ov = pair((cuda_ops, ORACLE), vshape, 52)
+        g.set(index, gv); o.set(index, ov)
+        assert same_bits(g.toArray(), o.toArray()), index
+    for index, value in (([0, 0, 0, 0], 9.0), ([(4, 4), (0, 5)], -1.0), ([2], 0.5), ([None, None, (6, 6), (1, 6)], 3.0)):
+        g.set(index, value); o.set(index, value)
+        assert same_bits(g.toArray(), o.toArray()), index
+    with pytest.raises(ValueError):
+        g.get([5])
+    with pytest.raises(ValueError):
+        g.get([(3, 2)])
+    with pytest.raises(ValueError):
+        g.set([1], cuda_ops.createRaw([3]))
+
+
+PERMUTES = [([64, 96], [1, 0]), ([7, 33, 65], [2, 1, 0]), ([7, 33, 65], [1, 0, 2]), ([4, 6, 40, 24], [0, 2, 1, 3]),
+            ([4, 6, 40, 24], [3, 2, 1, 0]), ([3, 5, 2, 4, 6], [4, 0, 3, 1, 2]), ([1, 17, 1, 9], [3, 1, 2, 0]), ([130, 1], [1, 0]),
+            ([2, 3, 4], [0, 1, 2]), ([300, 5], [1, 0])]
+
+
+@pytest.mark.parametrize("shape,axes", PERMUTES, ids=[f"{s}->{a}" for s, a in PERMUTES])
+def test_permute_and_transpose(cuda_ops, gc_scope, shape, axes):
+    g, o = pair((cuda_ops, ORACLE), shape, 53)
+    got, want = g.permute(axes), o.permute(axes)
+    assert got.shape == want.shape and same_bits(got.toArray(), want.toArray())
+    if len(shape) >= 2:
+        assert same_bits(g.transpose(0, -1).toArray(), o.transpose(0, -1).toArray())
+    L.check(cuda_ops.lib.ktc_tune_set(b"copy_force_generic", 1))         # the per-element kernel on the same case
+    try:
+        assert same_bits(g.permute(axes).toArray(), want.toArray())
+    finally:
+        L.check(cuda_ops.lib.ktc_tune_set(b"copy_force_generic", 0))
+    with pytest.raises(ValueError):
+        g.permute(axes[:-1])
+    with pytest.raises(ValueError):
+        g.transpose(0, 0)
+
+
+def test_concat_and_resize(cuda_ops, gc_scope):
+    parts_g, parts_o = [], []
+    for k, ext in enumerate((3, 1, 5)):
+        g, o = pair((cuda_ops, ORACLE), [4, ext, 6], 60 + k)
+        parts_g.append(g); parts_o.append(o)
+    for axis in (1, -2):
+        assert same_bits(cuda_ops.concat(axis, parts_g).toArray(), ORACLE.concat(axis, parts_o).toArray())
+    with pytest.raises(ValueError):
+        cuda_ops.concat(0, parts_g)
+    g, o = pair((cuda_ops, ORACLE), [5, 7], 63)
+    for new_shape in ([3, 4], [9, 9], [35]):
+        g.inplaceResize(*new_shape); o.inplaceResize(*new_shape)
+        assert g.shape == o.shape and same_bits(g.toArray(), o.toArray())
+
+
+def index_tensor(ops_list, shape, extent, seed):
+    idx = np.floor(D.uniform(int(np.prod(shape)), seed, 0.0, float(extent))).astype(np.float32)
+    idx = np.minimum(idx, extent - 1)
+    return [o.createRaw(shape, idx) for o in ops_list]
+
+
+def test_gather_scatter_index_ops(cuda_ops, gc_scope):
+    both = (cuda_ops, ORACLE)
+    shape = [6, 9, 10]
+    g, o = pair(both, shape, 71)
+    for axis, ishape in ((0, [4, 9, 10]), (1, [6, 20, 10]), (2, [6, 9, 3]), (1, [2, 5, 4]), (-1, [6, 9, 10])):
+        a = axis % 3
+        gi, oi = index_tensor(both, ishape, shape[a], 72 + axis)
+        assert same_bits(g.gather(axis, gi).toArray(), o.gather(axis, oi).toArray()), (axis, ishape)
+        # scatter back: repeated indices resolve in index order (last write wins / sums in order)
+        gs, os_ = pair(both, ishape, 80 + axis)
+        for method in ("scatter", "scatterAdd"):
+            if method == "scatterAdd":
+                gt, ot = g.copy(), o.copy()
+                gt.inplaceScatterAdd(axis, gi, gs); ot.inplaceScatterAdd(axis, oi, os_)
+            else:
+                gt, ot = g.scatter(axis, gi, gs), o.scatter(axis, oi, os_)
+            assert same_bits(gt.toArray(), ot.toArray()), (method, axis, ishape)
+        assert same_bits(g.scatter(axis, gi, 2.5).toArray(), o.scatter(axis, oi, 2.5).toArray())
+    # index select / index add with repeated indices
+    for axis in (0, 1, 2):
+        gi, oi = index_tensor(both, [13], shape[axis], 90 + axis)
+        sel_g, sel_o = g.indexSelect(axis, gi), o.indexSelect(axis, oi)
+        assert sel_g.shape == sel_o.shape and same_bits(sel_g.toArray(), sel_o.toArray())
+        gt, ot = g.copy(), o.copy()
+        gt.indexAdd(axis, gi, sel_g, 0.3); ot.indexAdd(axis, oi, sel_o, 0.3)
+        assert same_bits(gt.toArray(), ot.toArray()), axis
+    # invalid indices are reported, not faulted on, and the device stays usable
+    bad = cuda_ops.createRaw([6, 1, 10], np.full(60, 9.0, dtype=np.float32))
+    with pytest.raises(ValueError, match="invalid index"):
+        g.gather(1, bad)
+    with pytest.raises(ValueError, match="invalid index"):
+        g.copy().inplaceScatterAdd(1, bad, cuda_ops.createRaw([6, 1, 10]))
+    with pytest.raises(ValueError, match="invalid index"):
+        g.indexSelect(2, cuda_ops.createRaw([2], np.array([0.0, -1.0], dtype=np.float32)))
+    with pytest.raises(ValueError):
+        g.indexAdd(0, cuda_ops.createRaw([2]), cuda_ops.createRaw([3, 9, 10]))
+    assert same_bits(g.toArray(), o.toArray())
+
+
+def test_data_movement_full_size_properties(cuda_ops, gc_scope):
+    """2^26-element tensors: a transpose is undone by the inverse permutation, narrow pieces concatenate back
+    (exact comparisons through the elementwise and reduction kernels)."""
+    rows, cols = 8192, 8192
+    x = cuda_ops.createRaw([rows, cols], D.uniform(rows * cols, 77, -1.0, 1.0))
+    t = x.transpose(0, 1)
+    back = t.transpose(0, 1)
+    diff = back.minus(x)
+    assert float(diff.abs().sum().toArray()[0]) == 0.0
+    assert t.getSingleValue([5, 4097]) == x.getSingleValue([4097, 5])
+    t.release(); back.release(); diff.release()
+    p = x.view([64, 128, 8192]).permute([1, 2, 0])
+    q = p.permute([2, 0, 1])
+    d2 = q.view([rows, cols]).minus(x)
+    assert float(d2.abs().sum().toArray()[0]) == 0.0
+    p.release(); q.release(); d2.release()
+    left, right = x.narrow(1, 0, 1000), x.narrow(1, 1000, cols - 1000)
+    joined = cuda_ops.concat(1, [left, right])
+    d3 = joined.minus(x)
+    assert float(d3.abs().sum().toArray()[0]) == 0.0
