@@ -447,6 +447,56 @@ def run_sharded_graph(ops, lib, L, D, rank, world, comm, steps, warmup, dist):
     return res
 
 
+def run_other_ops(ops, lib, L, D, steps):
+    """The raw-tensor ops beside the sweep (slices, permutes, gather / scatter, the remaining maps), timed the same
+    way on 2^28-element tensors: GB/s of algorithmic bytes (inputs read once + output written once)."""
+    n = N28
+    G = float(1 << 30)
+    ms = C.c_float(0)
+    out = []
+    x = ops.createRaw([16384, 16384], D.uniform(n, 11, 0.1, 2.0))
+    idx_h = np.floor(D.uniform(n, 12, 0.0, 16384.0)).astype(np.float32)
+    np.minimum(idx_h, 16383.0, out=idx_h)
+    idx = ops.createRaw([16384, 16384], idx_h)
+    rows_h = np.floor(D.uniform(262144, 13, 0.0, 262144.0)).astype(np.float32)
+    np.minimum(rows_h, 262143.0, out=rows_h)
+    rows = ops.createRaw([262144], rows_h)
+    mask = ops.createRaw([1, 1024, 1], (D.uniform(1024, 14, 0.0, 1.0) > 0.5).astype(np.float32))
+    del idx_h, rows_h
+    x3, xr, xm = x.view([64, 4096, 1024]), x.view([262144, 1024]), x.view([1024, 1024, 256])
+    left, right = x.narrow(1, 0, 8192), x.narrow(1, 8192, 8192)
+    acc = ops.createRawFill([262144, 1024], 0.0)
+    cases = [
+        ("transpose [16384,16384]", 2 * G, lambda: x.transpose(0, 1)),
+        ("permute [64,4096,1024] -> (2,0,1)", 2 * G, lambda: x3.permute([2, 0, 1])),
+        ("permute [64,4096,1024] -> (1,0,2)", 2 * G, lambda: x3.permute([1, 0, 2])),
+        ("narrow [16384,16384] -> [16384,8192]", G, lambda: x.narrow(1, 4096, 8192)),
+        ("concat 2 x [16384,8192] on axis 1", 2 * G, lambda: ops.concat(1, [left, right])),
+        ("gather axis 1, index [16384,16384]", 3 * G, lambda: x.gather(1, idx)),
+        ("indexSelect 262144 rows of [262144,1024]", 2 * G, lambda: xr.indexSelect(0, rows)),
+        ("indexAdd 262144 rows into [262144,1024]", 3 * G, lambda: acc.indexAdd(0, rows, xr)),
+        ("maskedFill [1024,1024,256], mask [1,1024,1]", 2 * G, lambda: xm.maskedFill(mask, 0.0)),
+        ("sqrt", 2 * G, lambda: x.sqrt()),
+        ("sin", 2 * G, lambda: x.sin()),
+        ("eq (tensor, tensor)", 3 * G, lambda: x.eq(idx)),
+    ]
+    reps = max(2, min(steps, 10))
+    for name, nbytes, fn in cases:
+        with ops.garbageCollector():
+            fn()
+        ops.synchronize()
+        L.check(lib.ktc_timer_start(ops.device))
+        for _ in range(reps):
+            with ops.garbageCollector():
+                fn()
+        L.check(lib.ktc_timer_stop(ops.device, C.byref(ms)))
+        per = ms.value / reps
+        out.append({"name": name, "ms": round(per, 4), "gbs": round(nbytes / per / 1e6, 1)})
+    for r in (x3, xr, xm, left, right, acc, idx, rows, mask, x):
+        r.release()
+    return out
+
+
 def init_distributed(n_gpus):
     """(rank, world, local_rank, dist module or None).  torch.distributed is plumbing only:
     rendezvous, the barrier and the max over ranks."""
@@ -555,6 +605,14 @@ def run_gpu_arm(args):
         L.check(lib.ktc_pool_trim(local))
         sharded = run_sharded_graph(sweep.ops, lib, L, D, rank, world, comm, max(2, min(args.steps, 5)), args.warmup, dist)
 
+    other_ops = None
+    if args.other_ops and rank == 0 and world == 1:
+        if not args.sharded_graph:
+            for r in (sweep.a2, sweep.b2, sweep.a3, sweep.t3, sweep.x4, sweep.out):
+                r.release()
+        L.check(lib.ktc_pool_trim(local))
+        other_ops = run_other_ops(sweep.ops, lib, L, D, args.steps)
+
     # ---- max over ranks -----------------------------------------------------------------------------
     if dist is not None:
         import torch
@@ -604,6 +662,10 @@ def run_gpu_arm(args):
     }
     if sharded is not None:
         line["sharded_graph"] = sharded
+    if other_ops is not None:
+        for o in other_ops:
+            o["frac_measured"] = round(o["gbs"] / peak, 3)
+        line["other_ops"] = other_ops
     if rank == 0:
         if args.cpu_baseline:
             secs, nbytes, _ = cpu_sample_pass(args.cpu_sample_log2)
@@ -661,6 +723,33 @@ def run_single_case(args):
         L.check(lib.ktc_timer_stop(0, C.byref(ms)))
         print(json.dumps({"case": name, "elements": rows * cols, "ms": ms.value / args.reps,
                           "launches_per_step": (lib.ktc_launch_count() - l0) / args.reps}))
+        return 0
+    if name.startswith("x."):
+        # data-movement ops beside the sweep, on a [rows, 4096] tensor of n elements
+        cols = 4096
+        rows = max(1, n // cols)
+        x = ops.createRaw([rows, cols], D.uniform(rows * cols, 11, 0.1, 2.0))
+        pick = np.minimum(np.floor(D.uniform(rows, 13, 0.0, float(rows))), rows - 1).astype(np.float32)
+        ridx = ops.createRaw([rows], pick)
+        acc = ops.createRawFill([rows, cols], 0.0)
+        fns = {"x.transpose": (lambda: x.transpose(0, 1), 2), "x.permute_rows": (lambda: x.view([rows // 64, 64, cols]).permute([1, 0, 2]), 2),
+               "x.narrow": (lambda: x.narrow(1, 1024, 2048), 1), "x.index_select": (lambda: x.indexSelect(0, ridx), 2),
+               "x.index_add": (lambda: acc.indexAdd(0, ridx, x), 3)}
+        if name == "x.gather":
+            gidx = ops.createRaw([rows, cols], np.minimum(np.floor(D.uniform(rows * cols, 12, 0.0, float(cols))), cols - 1).astype(np.float32))
+            fns[name] = (lambda: x.gather(1, gidx), 3)
+        fn, volumes = fns[name]
+        with ops.garbageCollector():
+            fn()
+        ops.synchronize()
+        L.check(lib.ktc_timer_start(0))
+        for _ in range(args.reps):
+            with ops.garbageCollector():
+                fn()
+        ms = C.c_float(0)
+        L.check(lib.ktc_timer_stop(0, C.byref(ms)))
+        per = ms.value / args.reps
+        print(json.dumps({"case": name, "elements": rows * cols, "ms": per, "gbs": volumes * 4.0 * rows * cols / per / 1e6}))
         return 0
     spec = {s_["name"]: s_ for s_ in sweep_spec()}[name]
     mk = ops.createRaw
@@ -743,6 +832,8 @@ def main():
     ap.add_argument("--cpu-sample-log2", type=int, default=None, help="log2 of the CPU sample size (default 25 for cpu_baseline, 24 for --impl reference)")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     ap.add_argument("--no-sharded-graph", dest="sharded_graph", action="store_false")
+    ap.add_argument("--no-other-ops", dest="other_ops", action="store_false",
+                    help="skip timing the raw-tensor ops beside the sweep (slices, permutes, gather / scatter)")
     ap.add_argument("--case", default=None, help="run one op of the sweep alone (profiling workload), e.g. c2.plus, c4.last.max")
     ap.add_argument("--log2n", type=int, default=26)
     ap.add_argument("--reps", type=int, default=3)

@@ -8,7 +8,7 @@
 //                        dimensions are collapsed on the host; when both sides are contiguous
 //                        along the innermost axis and 16-byte aligned the element type is float4;
 //   * k_transpose_tiled  when the two sides are contiguous along DIFFERENT axes (transpose,
-//                        permutes that move the innermost axis) a 32x32 tile goes through shared
+//                        permutes that move the innermost axis) a 64x64 tile goes through shared
 //                        memory so that both the read and the write are coalesced;
 //   * k_gather_axis / k_index_select   one thread per output element;
 //   * k_scatter_axis_nd / k_index_add  one thread per column (all coordinates but the axis),
@@ -36,33 +36,47 @@ inline int finish(const char* what) {
     return KTC_OK;
 }
 
-// T = float or float4; FILL: no source
-template <class T, bool FILL>
+// T = float or float4; FILL: no source; I = type of the linear index that is decomposed (32-bit when the
+// box is small enough).  A thread moves four items, 256 apart, and issues its four loads before the stores.
+template <class T, bool FILL, class I>
 __global__ void __launch_bounds__(256) k_copy_nd(T* __restrict__ dst, const T* __restrict__ src, const __grid_constant__ NdArgs a, T v) {
-    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
-    if (i >= a.total) return;
-    int64_t rem = i, doff = 0, soff = 0;
-    #pragma unroll 1
-    for (int d = a.ndim - 1; d > 0; --d) {
-        const int64_t q = rem / a.shape[d], c = rem - q * a.shape[d];
-        doff += c * a.dstr[d];
-        if (!FILL) soff += c * a.sstr[d];
-        rem = q;
+    const int64_t base = (int64_t)blockIdx.x * 1024 + threadIdx.x;
+    int64_t doff[4], soff[4];
+    #pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int64_t i = base + u * 256;
+        I rem = (I)(i < a.total ? i : 0);
+        int64_t dd = 0, ss = 0;
+        #pragma unroll 1
+        for (int d = a.ndim - 1; d > 0; --d) {
+            const I ext = (I)a.shape[d];
+            const I q = rem / ext, c = rem - q * ext;
+            dd += (int64_t)c * a.dstr[d];
+            if (!FILL) ss += (int64_t)c * a.sstr[d];
+            rem = q;
+        }
+        doff[u] = dd + (int64_t)rem * a.dstr[0];
+        soff[u] = FILL ? 0 : ss + (int64_t)rem * a.sstr[0];
     }
-    doff += rem * a.dstr[0];
-    if (!FILL) soff += rem * a.sstr[0];
-    dst[doff] = FILL ? v : src[soff];
+    T val[4];
+    #pragma unroll
+    for (int u = 0; u < 4; ++u) val[u] = FILL ? v : ((base + u * 256 < a.total) ? src[soff[u]] : v);
+    #pragma unroll
+    for (int u = 0; u < 4; ++u) if (base + u * 256 < a.total) dst[doff[u]] = val[u];
 }
 
-// src is contiguous along dimension P, dst along dimension Q (P != Q): tiles of 32 x 32 over (P, Q).
+// src is contiguous along dimension P, dst along dimension Q (P != Q): tiles of 64 x 64 over (P, Q); a thread
+// holds 16 elements and issues all its loads before the first shared-memory store.
 struct TrArgs {
     int ndim, P, Q;
     int64_t shape[KTC_MAX_DIMS], dstr[KTC_MAX_DIMS], sstr[KTC_MAX_DIMS];
     int64_t tiles_p, tiles_q;
 };
 
+constexpr int kTrTile = 64;
+
 __global__ void __launch_bounds__(256) k_transpose_tiled(float* __restrict__ dst, const float* __restrict__ src, const __grid_constant__ TrArgs a) {
-    __shared__ float tile[32][33];
+    __shared__ float tile[kTrTile][kTrTile + 1];
     int64_t b = blockIdx.x;
     const int64_t tp = b % a.tiles_p; b /= a.tiles_p;
     const int64_t tq = b % a.tiles_q; b /= a.tiles_q;
@@ -74,18 +88,29 @@ __global__ void __launch_bounds__(256) k_transpose_tiled(float* __restrict__ dst
         doff += c * a.dstr[d]; soff += c * a.sstr[d];
         b = q;
     }
-    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-    const int64_t p0 = tp * 32, q0 = tq * 32;
-    #pragma unroll
-    for (int k = 0; k < 4; ++k) {                        // read: tx runs along P (stride 1 in src)
-        const int64_t p = p0 + tx, q = q0 + ty + k * 8;
-        if (p < a.shape[a.P] && q < a.shape[a.Q]) tile[ty + k * 8][tx] = src[soff + p * a.sstr[a.P] + q * a.sstr[a.Q]];
+    const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;            // 64 x 4 threads, 16 rows each
+    const int64_t p0 = tp * kTrTile, q0 = tq * kTrTile;
+    const int64_t SP = a.shape[a.P], SQ = a.shape[a.Q];
+    const float* sp = src + soff + (p0 + tx) * a.sstr[a.P] + (q0 + ty) * a.sstr[a.Q];
+    float v[16];
+    if (p0 + kTrTile <= SP && q0 + kTrTile <= SQ) {                       // whole tile: every load before the first use
+        #pragma unroll
+        for (int k = 0; k < 16; ++k) v[k] = __ldcs(sp + (int64_t)(k * 4) * a.sstr[a.Q]);
+    } else {
+        #pragma unroll
+        for (int k = 0; k < 16; ++k) v[k] = (p0 + tx < SP && q0 + ty + k * 4 < SQ) ? sp[(int64_t)(k * 4) * a.sstr[a.Q]] : 0.f;
     }
-    __syncthreads();
     #pragma unroll
-    for (int k = 0; k < 4; ++k) {                        // write: tx runs along Q (stride 1 in dst)
-        const int64_t q = q0 + tx, p = p0 + ty + k * 8;
-        if (p < a.shape[a.P] && q < a.shape[a.Q]) dst[doff + p * a.dstr[a.P] + q * a.dstr[a.Q]] = tile[tx][ty + k * 8];
+    for (int k = 0; k < 16; ++k) tile[ty + k * 4][tx] = v[k];              // tile[q][p]
+    __syncthreads();
+    float* dp = dst + doff + (q0 + tx) * a.dstr[a.Q] + (p0 + ty) * a.dstr[a.P];
+    if (p0 + kTrTile <= SP && q0 + kTrTile <= SQ) {
+        #pragma unroll
+        for (int k = 0; k < 16; ++k) __stcs(dp + (int64_t)(k * 4) * a.dstr[a.P], tile[tx][ty + k * 4]);
+    } else {
+        #pragma unroll
+        for (int k = 0; k < 16; ++k)
+            if (q0 + tx < SQ && p0 + ty + k * 4 < SP) dp[(int64_t)(k * 4) * a.dstr[a.P]] = tile[tx][ty + k * 4];
     }
 }
 
@@ -111,6 +136,58 @@ __global__ void __launch_bounds__(256) k_gather_axis(float* __restrict__ out, co
     const int idx = (int)index[i];                        // Float.toInt(): truncation
     if (idx < 0 || idx >= a.t_axis_len) { *err = 1; return; }
     out[i] = in[toff + idx * a.tstr[a.axis]];
+}
+
+// gather when the index covers the input off the axis: both are [outer, *, inner]; a thread produces four
+// consecutive outputs (one 128-bit index load, four independent gathers, one 128-bit store)
+template <class I>
+__global__ void __launch_bounds__(256) k_gather_axis3(float* __restrict__ out, const float* __restrict__ in, const float* __restrict__ index,
+                                                      I A_in, I A_idx, I inner, I total4, int* err) {
+    const I t = (I)blockIdx.x * 256 + threadIdx.x;
+    if (t >= total4) return;
+    const I i = t * 4;
+    const float4 iv = __ldcs(reinterpret_cast<const float4*>(index) + t);
+    I n = i % inner, r = i / inner, k = r % A_idx, o = r / A_idx;
+    const float idxf[4] = {iv.x, iv.y, iv.z, iv.w};
+    float res[4];
+    bool bad = false;
+    #pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int idx = (int)idxf[j];
+        const bool ok = idx >= 0 && (I)idx < A_in;
+        bad |= !ok;
+        res[j] = ok ? in[(o * A_in + (I)idx) * inner + n] : 0.f;
+        if (++n == inner) { n = 0; if (++k == A_idx) { k = 0; ++o; } }
+    }
+    if (bad) { *err = 1; return; }
+    __stcs(reinterpret_cast<float4*>(out) + t, make_float4(res[0], res[1], res[2], res[3]));
+}
+
+// index select with a vectorisable inner extent: a thread moves four float4 of the output, 256 apart,
+// and issues its four row loads before the stores
+template <class I>
+__global__ void __launch_bounds__(256) k_index_select_vec(float4* __restrict__ out, const float4* __restrict__ in, const float* __restrict__ index,
+                                                          I A, I n_idx, I inner4, I total4, int* err) {
+    const I base = (I)blockIdx.x * 1024 + threadIdx.x;
+    float4 v[4];
+    bool bad = false;
+    #pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const I t = base + (I)(u * 256);
+        if (t < total4) {
+            const I n = t % inner4, r = t / inner4, k = r % n_idx, o = r / n_idx;
+            const int idx = (int)index[k];
+            const bool ok = idx >= 0 && (I)idx < A;
+            bad |= !ok;
+            if (ok) v[u] = in[(o * A + (I)idx) * inner4 + n];
+        }
+    }
+    if (bad) { *err = 1; return; }
+    #pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const I t = base + (I)(u * 256);
+        if (t < total4) __stcs(out + t, v[u]);
+    }
 }
 
 // MODE 0: target[.., idx, ..] = src   1: += src   2: = constant
@@ -161,6 +238,127 @@ __global__ void __launch_bounds__(128) k_index_add(float* __restrict__ target, c
     }
 }
 
+// ---- index add with many indices ------------------------------------------------------------
+// One thread per column and a sequential walk over the indices has no parallelism when the
+// columns are few and the indices many (an embedding gradient: 10^5 indices, 10^3 columns).
+// The indices are therefore grouped by target row first -- count per row, exclusive scan,
+// placement, and a sort of each row's (short) list by index position -- and then every
+// (row, column) element adds its sources in index-position order: the same additions in the
+// same order as the sequential loop of the reference (JVM:508-516), fully parallel over rows.
+struct IaStats { int err; int max_count; };
+
+__global__ void __launch_bounds__(256) k_ia_count(const float* __restrict__ index, int64_t n_idx, int64_t A, int* __restrict__ count, IaStats* st) {
+    const int64_t k = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (k >= n_idx) return;
+    const int idx = (int)index[k];
+    if (idx < 0 || idx >= A) { st->err = 1; return; }
+    const int c = atomicAdd(&count[idx], 1) + 1;
+    if (c > 1) atomicMax(&st->max_count, c);
+}
+
+// exclusive scan of count[0, A) in three steps over blocks of 1024 rows
+__global__ void __launch_bounds__(1024) k_ia_block_sums(const int* __restrict__ count, int64_t A, int* __restrict__ bsum) {
+    __shared__ int sm[32];
+    const int64_t j = (int64_t)blockIdx.x * 1024 + threadIdx.x;
+    int v = j < A ? count[j] : 0;
+    #pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        int t = sm[threadIdx.x];
+        #pragma unroll
+        for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
+        if (threadIdx.x == 0) bsum[blockIdx.x] = t;
+    }
+}
+__global__ void __launch_bounds__(1024) k_ia_scan_block_sums(int* bsum, int64_t nb) {      // one CTA, 1024 values per round
+    __shared__ int sm[32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int carry = 0;
+    for (int64_t base = 0; base < nb; base += 1024) {
+        const int64_t b = base + threadIdx.x;
+        const int c = b < nb ? bsum[b] : 0;
+        int v = c;
+        #pragma unroll
+        for (int off = 1; off < 32; off <<= 1) { const int t = __shfl_up_sync(0xffffffffu, v, off); if (lane >= off) v += t; }
+        if (lane == 31) sm[warp] = v;
+        __syncthreads();
+        if (warp == 0) {
+            int t = sm[lane];
+            #pragma unroll
+            for (int off = 1; off < 32; off <<= 1) { const int u = __shfl_up_sync(0xffffffffu, t, off); if (lane >= off) t += u; }
+            sm[lane] = t;
+        }
+        __syncthreads();
+        if (b < nb) bsum[b] = carry + v - c + (warp > 0 ? sm[warp - 1] : 0);
+        carry += sm[31];
+        __syncthreads();
+    }
+}
+__global__ void __launch_bounds__(1024) k_ia_offsets(const int* __restrict__ count, int64_t A, const int* __restrict__ bsum,
+                                                     int* __restrict__ offsets, int* __restrict__ cursor) {
+    __shared__ int sm[32];
+    const int64_t j = (int64_t)blockIdx.x * 1024 + threadIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int c = j < A ? count[j] : 0;
+    int v = c;                                                         // inclusive scan inside the warp
+    #pragma unroll
+    for (int off = 1; off < 32; off <<= 1) { const int t = __shfl_up_sync(0xffffffffu, v, off); if (lane >= off) v += t; }
+    if (lane == 31) sm[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        int t = sm[lane];
+        #pragma unroll
+        for (int off = 1; off < 32; off <<= 1) { const int u = __shfl_up_sync(0xffffffffu, t, off); if (lane >= off) t += u; }
+        sm[lane] = t;
+    }
+    __syncthreads();
+    const int excl = v - c + (warp > 0 ? sm[warp - 1] : 0) + bsum[blockIdx.x];
+    if (j < A) { offsets[j] = excl; cursor[j] = excl; }
+}
+__global__ void __launch_bounds__(256) k_ia_place(const float* __restrict__ index, int64_t n_idx, int* __restrict__ cursor, int* __restrict__ perm) {
+    const int64_t k = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (k >= n_idx) return;
+    perm[atomicAdd(&cursor[(int)index[k]], 1)] = (int)k;
+}
+__global__ void __launch_bounds__(256) k_ia_sort_lists(const int* __restrict__ offsets, const int* __restrict__ count, int64_t A, int* __restrict__ perm) {
+    const int64_t j = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (j >= A) return;
+    const int c = count[j];
+    if (c < 2) return;
+    int* p = perm + offsets[j];
+    for (int a = 1; a < c; ++a) {                                       // insertion sort: the placement order is arbitrary, lists are short
+        const int v = p[a];
+        int b = a - 1;
+        while (b >= 0 && p[b] > v) { p[b + 1] = p[b]; --b; }
+        p[b + 1] = v;
+    }
+}
+// one thread per (outer, row, float4 of columns) or per element when V == 1
+template <class T>
+__global__ void __launch_bounds__(256) k_ia_apply(T* __restrict__ target, const T* __restrict__ src, const int* __restrict__ offsets,
+                                                  const int* __restrict__ count, const int* __restrict__ perm, float alpha,
+                                                  int64_t outer, int64_t A, int64_t n_idx, int64_t innerT) {
+    const int64_t t = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (t >= outer * A * innerT) return;
+    const int64_t n = t % innerT, r = t / innerT, j = r % A, o = r / A;
+    const int c = count[j];
+    if (c == 0) return;
+    const int* p = perm + offsets[j];
+    T acc = target[t];
+    for (int a = 0; a < c; ++a) {
+        const T v = src[(o * n_idx + p[a]) * innerT + n];
+        if constexpr (sizeof(T) == 16) {
+            acc.x = __fadd_rn(acc.x, __fmul_rn(v.x, alpha)); acc.y = __fadd_rn(acc.y, __fmul_rn(v.y, alpha));
+            acc.z = __fadd_rn(acc.z, __fmul_rn(v.z, alpha)); acc.w = __fadd_rn(acc.w, __fmul_rn(v.w, alpha));
+        } else {
+            acc = __fadd_rn(acc, __fmul_rn(v, alpha));
+        }
+    }
+    target[t] = acc;
+}
+
 // reads the device error word (set by a kernel that met an invalid index), clears it, waits
 int take_index_error(Device* d, const char* what, int64_t axis_len, int axis) {
     int h = 0;
@@ -204,7 +402,7 @@ int launch_copy_nd(Device* d, float* dst, const int64_t* dstr, const float* src,
             a.ndim = m; a.P = P; a.Q = Q;
             int64_t batch = 1;
             for (int i = 0; i < m; ++i) { a.shape[i] = S[i]; a.dstr[i] = DS[i]; a.sstr[i] = SS[i]; if (i != P && i != Q) batch *= S[i]; }
-            a.tiles_p = (S[P] + 31) / 32; a.tiles_q = (S[Q] + 31) / 32;
+            a.tiles_p = (S[P] + kTrTile - 1) / kTrTile; a.tiles_q = (S[Q] + kTrTile - 1) / kTrTile;
             const int64_t grid = a.tiles_p * a.tiles_q * batch;
             if (grid <= 0x7fffffffLL) {
                 k_transpose_tiled<<<(int)grid, 256, 0, d->stream>>>(dst, src, a);
@@ -223,18 +421,26 @@ int launch_copy_nd(Device* d, float* dst, const int64_t* dstr, const float* src,
         a.shape[m - 1] /= 4;
         for (int i = 0; i < m - 1; ++i) { a.dstr[i] /= 4; a.sstr[i] /= 4; }
         a.total = total / 4;
-        const int64_t grid = grid_of(a.total, 256);
+        const int64_t grid = grid_of(a.total, 1024);
         if (grid > 0x7fffffffLL) return fail(KTC_ENOTSUP, "tensor too large for one launch");
         const float4 v4 = make_float4(value, value, value, value);
-        if (fill) k_copy_nd<float4, true><<<(int)grid, 256, 0, d->stream>>>(reinterpret_cast<float4*>(dst), nullptr, a, v4);
-        else k_copy_nd<float4, false><<<(int)grid, 256, 0, d->stream>>>(reinterpret_cast<float4*>(dst), reinterpret_cast<const float4*>(src), a, v4);
+        float4* d4 = reinterpret_cast<float4*>(dst);
+        const float4* s4 = reinterpret_cast<const float4*>(src);
+        const bool small = a.total < (1LL << 31);
+        if (fill) { if (small) k_copy_nd<float4, true, uint32_t><<<(int)grid, 256, 0, d->stream>>>(d4, nullptr, a, v4);
+                    else k_copy_nd<float4, true, int64_t><<<(int)grid, 256, 0, d->stream>>>(d4, nullptr, a, v4); }
+        else      { if (small) k_copy_nd<float4, false, uint32_t><<<(int)grid, 256, 0, d->stream>>>(d4, s4, a, v4);
+                    else k_copy_nd<float4, false, int64_t><<<(int)grid, 256, 0, d->stream>>>(d4, s4, a, v4); }
         return finish("copy_nd(vec)");
     }
     a.total = total;
-    const int64_t grid = grid_of(total, 256);
+    const int64_t grid = grid_of(total, 1024);
     if (grid > 0x7fffffffLL) return fail(KTC_ENOTSUP, "tensor too large for one launch");
-    if (fill) k_copy_nd<float, true><<<(int)grid, 256, 0, d->stream>>>(dst, nullptr, a, value);
-    else k_copy_nd<float, false><<<(int)grid, 256, 0, d->stream>>>(dst, src, a, value);
+    const bool small = total < (1LL << 31);
+    if (fill) { if (small) k_copy_nd<float, true, uint32_t><<<(int)grid, 256, 0, d->stream>>>(dst, nullptr, a, value);
+                else k_copy_nd<float, true, int64_t><<<(int)grid, 256, 0, d->stream>>>(dst, nullptr, a, value); }
+    else      { if (small) k_copy_nd<float, false, uint32_t><<<(int)grid, 256, 0, d->stream>>>(dst, src, a, value);
+                else k_copy_nd<float, false, int64_t><<<(int)grid, 256, 0, d->stream>>>(dst, src, a, value); }
     return finish("copy_nd");
 }
 
@@ -252,6 +458,25 @@ int launch_gather_axis(Device* d, float* out, const float* in, const int64_t* in
     a.total = 1;
     for (int i = 0; i < ndim; ++i) { a.ishape[i] = index_shape[i]; a.total *= index_shape[i]; }
     if (a.total == 0) return KTC_OK;
+    bool covers = true;                                   // the index spans the input off the axis: [outer, *, inner] on both sides
+    int64_t outer = 1, inner = 1;
+    for (int i = 0; i < ndim; ++i) {
+        if (i == axis) continue;
+        covers = covers && index_shape[i] == in_shape[i];
+        if (i < axis) outer *= index_shape[i]; else inner *= index_shape[i];
+    }
+    const int64_t in_total = outer * in_shape[axis] * inner;
+    if (covers && a.total % 4 == 0 && aligned16(index) && aligned16(out) && tune("index_force_generic", 0) == 0) {
+        const int64_t total4 = a.total / 4, grid = grid_of(total4, 256);
+        if (grid > 0x7fffffffLL) return fail(KTC_ENOTSUP, "tensor too large for one launch");
+        if (a.total < (1LL << 31) && in_total < (1LL << 31))
+            k_gather_axis3<uint32_t><<<(int)grid, 256, 0, d->stream>>>(out, in, index, (uint32_t)in_shape[axis], (uint32_t)index_shape[axis],
+                                                                        (uint32_t)inner, (uint32_t)total4, d->err_flag);
+        else
+            k_gather_axis3<int64_t><<<(int)grid, 256, 0, d->stream>>>(out, in, index, in_shape[axis], index_shape[axis], inner, total4, d->err_flag);
+        KTC_TRY(finish("gather_axis3"));
+        return take_index_error(d, "Gather", a.t_axis_len, axis);
+    }
     const int64_t grid = grid_of(a.total, 256);
     if (grid > 0x7fffffffLL) return fail(KTC_ENOTSUP, "tensor too large for one launch");
     k_gather_axis<<<(int)grid, 256, 0, d->stream>>>(out, in, index, a, d->err_flag);
@@ -283,6 +508,17 @@ int launch_index_select(Device* d, float* out, const float* in, const float* ind
     if (total == 0) return KTC_OK;
     const int64_t grid = grid_of(total, 256);
     if (grid > 0x7fffffffLL) return fail(KTC_ENOTSUP, "tensor too large for one launch");
+    if (inner % 4 == 0 && aligned16(out) && aligned16(in) && tune("index_force_generic", 0) == 0) {
+        const int64_t total4 = total / 4, g4 = grid_of(total4, 1024);
+        if (total < (1LL << 31) && outer * A * inner < (1LL << 31))
+            k_index_select_vec<uint32_t><<<(int)g4, 256, 0, d->stream>>>(reinterpret_cast<float4*>(out), reinterpret_cast<const float4*>(in), index,
+                                                                         (uint32_t)A, (uint32_t)n_idx, (uint32_t)(inner / 4), (uint32_t)total4, d->err_flag);
+        else
+            k_index_select_vec<int64_t><<<(int)g4, 256, 0, d->stream>>>(reinterpret_cast<float4*>(out), reinterpret_cast<const float4*>(in), index,
+                                                                        A, n_idx, inner / 4, total4, d->err_flag);
+        KTC_TRY(finish("index_select(vec)"));
+        return take_index_error(d, "Index select", A, -1);
+    }
     k_index_select<<<(int)grid, 256, 0, d->stream>>>(out, in, index, outer, A, n_idx, inner, d->err_flag);
     KTC_TRY(finish("index_select"));
     return take_index_error(d, "Index select", A, -1);
@@ -292,6 +528,43 @@ int launch_index_add(Device* d, float* target, const float* index, const float* 
                      int64_t outer, int64_t A, int64_t n_idx, int64_t inner) {
     const int64_t cols = outer * inner;
     if (cols == 0 || n_idx == 0) return KTC_OK;
+    // many indices: group them by target row (see above); else one thread per column
+    if (n_idx >= tune("index_add_group_min", 64) && A < (1LL << 31) && n_idx < (1LL << 31)) {
+        const int64_t nb = (A + 1023) / 1024;
+        Scratch sc;                                                      // count | offsets | cursor | block sums | perm | stats
+        KTC_TRY(sc.get(d, 3 * A + nb + n_idx + 2));
+        int* count = reinterpret_cast<int*>(sc.ptr);
+        int* offsets = count + A; int* cursor = offsets + A; int* bsum = cursor + A; int* perm = bsum + nb;
+        IaStats* st = reinterpret_cast<IaStats*>(perm + n_idx);
+        KTC_CUDA(cudaMemsetAsync(count, 0, sizeof(int) * A, d->stream));
+        KTC_CUDA(cudaMemsetAsync(st, 0, sizeof(IaStats), d->stream));
+        k_ia_count<<<(int)grid_of(n_idx, 256), 256, 0, d->stream>>>(index, n_idx, A, count, st);
+        KTC_TRY(finish("index_add(count)"));
+        IaStats h{};
+        KTC_CUDA(cudaMemcpyAsync(&h, st, sizeof(IaStats), cudaMemcpyDeviceToHost, d->stream));
+        KTC_CUDA(cudaStreamSynchronize(d->stream));
+        if (h.err) return fail(KTC_EINVAL, "Index Add got invalid index, index value is out of bounds 0 and %lld", (long long)A);
+        if (h.max_count <= tune("index_add_max_list", 256)) {
+            k_ia_block_sums<<<(int)nb, 1024, 0, d->stream>>>(count, A, bsum);
+            k_ia_scan_block_sums<<<1, 1024, 0, d->stream>>>(bsum, nb);
+            k_ia_offsets<<<(int)nb, 1024, 0, d->stream>>>(count, A, bsum, offsets, cursor);
+            k_ia_place<<<(int)grid_of(n_idx, 256), 256, 0, d->stream>>>(index, n_idx, cursor, perm);
+            if (h.max_count > 1) k_ia_sort_lists<<<(int)grid_of(A, 256), 256, 0, d->stream>>>(offsets, count, A, perm);
+            count_launch(h.max_count > 1 ? 4 : 3);
+            if (inner % 4 == 0 && aligned16(target) && aligned16(src)) {
+                const int64_t items = outer * A * (inner / 4);
+                if (grid_of(items, 256) > 0x7fffffffLL) return fail(KTC_ENOTSUP, "tensor too large for one launch");
+                k_ia_apply<float4><<<(int)grid_of(items, 256), 256, 0, d->stream>>>(reinterpret_cast<float4*>(target), reinterpret_cast<const float4*>(src),
+                                                                                    offsets, count, perm, alpha, outer, A, n_idx, inner / 4);
+            } else {
+                const int64_t items = outer * A * inner;
+                if (grid_of(items, 256) > 0x7fffffffLL) return fail(KTC_ENOTSUP, "tensor too large for one launch");
+                k_ia_apply<float><<<(int)grid_of(items, 256), 256, 0, d->stream>>>(target, src, offsets, count, perm, alpha, outer, A, n_idx, inner);
+            }
+            return finish("index_add(apply)");
+        }
+        // a row with a very long list: the sequential walk below handles it (its columns are the parallelism)
+    }
     const int64_t grid = grid_of(cols, 128);
     if (grid > 0x7fffffffLL) return fail(KTC_ENOTSUP, "tensor too large for one launch");
     k_index_add<<<(int)grid, 128, 0, d->stream>>>(target, index, src, alpha, outer, A, n_idx, inner, d->err_flag);

@@ -210,6 +210,24 @@ def test_gather_scatter_index_ops(cuda_ops, gc_scope):
     assert same_bits(g.toArray(), o.toArray())
 
 
+@pytest.mark.parametrize("n_idx,rows,inner,outer", [(5000, 300, 16, 3), (5000, 300, 5, 1), (3000, 4000, 8, 2), (2000, 3, 64, 1), (70, 70, 4, 1)])
+def test_index_add_many_indices_keeps_the_sequential_order(cuda_ops, gc_scope, n_idx, rows, inner, outer):
+    """Many (repeated) indices: the grouped kernels must add in index-position order, bit for bit like the
+    reference's sequential loop; (2000, 3, ...) has lists beyond the grouping limit and takes the per-column walk."""
+    both = (cuda_ops, ORACLE)
+    gt, ot = pair(both, [outer, rows, inner], 101)
+    gs, os_ = pair(both, [outer, n_idx, inner], 102)
+    gi, oi = index_tensor(both, [n_idx], rows, 103)
+    gt.indexAdd(1, gi, gs, 0.7); ot.indexAdd(1, oi, os_, 0.7)
+    assert same_bits(gt.toArray(), ot.toArray())
+    gt.indexAdd(1, gi, gs); ot.indexAdd(1, oi, os_)                     # alpha = 1, accumulated on top
+    assert same_bits(gt.toArray(), ot.toArray())
+    bad = np.zeros(n_idx, dtype=np.float32); bad[n_idx // 2] = rows
+    with pytest.raises(ValueError, match="invalid index"):
+        gt.indexAdd(1, cuda_ops.createRaw([n_idx], bad), gs)
+    assert same_bits(gt.toArray(), ot.toArray())                          # nothing was applied
+
+
 def test_data_movement_full_size_properties(cuda_ops, gc_scope):
     """2^26-element tensors: a transpose is undone by the inverse permutation, narrow pieces concatenate back
     (exact comparisons through the elementwise and reduction kernels)."""
