@@ -441,9 +441,15 @@ def run_sharded_graph(ops, lib, L, D, rank, world, comm, steps, warmup, dist):
         r.release()
     res = {"workload": "x[262144,1024] row-sharded, loss = sum(sigmoid(x*w+b) pow 2), backward + all-reduce of (loss, gw, gb)",
            "scaling": "strong", "rows_per_gpu": count}
-    res.update(fused)                                   # the raw-tensor call sequence of kten's autograd with the elementwise
-    res["execution"] = "deferred elementwise calls fused into the sums (ops.lazy)"      # calls deferred and fused,
-    res["call_by_call"] = eager                         # and the same sequence with every call one library call
+    # the same raw-tensor call sequence of kten's autograd in the backend's two execution modes; the headline
+    # figures are those of the faster one (the deferred mode is bound by this Python host side once a rank's
+    # shard takes less device time than building and compiling the step's expressions)
+    best = fused if fused["ms_per_step"] <= eager["ms_per_step"] else eager
+    res.update(best)
+    res["execution"] = ("deferred elementwise calls fused into the sums (ops.lazy)" if best is fused
+                        else "call by call (every raw-tensor call one library call)")
+    res["deferred"] = fused
+    res["call_by_call"] = eager
     return res
 
 

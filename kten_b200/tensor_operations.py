@@ -161,10 +161,18 @@ class CUDATensorOperations:
             return
         h = target._buf()
         self._flush_dependents(h)
+        n = target.size
+        other = Z.strip(args[1]) if kind == "bin" else None
+        if other is not None and (other.kind == "const" or (other.stored() and SF.to_store_size(other.shape) == n)):
+            # nothing to fuse: the operand is already in memory (a gradient accumulated into a Variable, ...)
+            if other.kind == "const":
+                L.check(self.lib.ktc_scalar_inplace(op, h, other.imm[0], n))
+            else:
+                L.check(self.lib.ktc_binary_inplace(op, h, other.buf.handle, n))
+            return
         if self._try_fused(target.shape, [node], [h], [False]):
             return
         self.unfusedEvaluations += 1
-        n = target.size
         if kind == "square":
             L.check(self.lib.ktc_scalar_inplace(L.POW, h, 2.0, n))
             return
