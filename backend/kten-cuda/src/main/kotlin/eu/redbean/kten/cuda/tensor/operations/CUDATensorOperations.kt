@@ -2,6 +2,8 @@ package eu.redbean.kten.cuda.tensor.operations
 
 import eu.redbean.kten.api.autograd.tensor.NoGradVariable
 import eu.redbean.kten.api.autograd.tensor.Variable
+import eu.redbean.kten.api.autograd.utils.concatShapes
+import eu.redbean.kten.api.autograd.utils.normalizeAxis
 import eu.redbean.kten.api.autograd.utils.toStoreSize
 import eu.redbean.kten.api.tensor.Tensor
 import eu.redbean.kten.api.tensor.operations.TensorOperations
@@ -113,7 +115,21 @@ class CUDATensorOperations(override val platformKey: String, val device: Int) : 
     // ---- dense contractions and nn layers are outside the float32 hot path this library covers -----------
     private fun unsupported(name: String): Nothing = throw UnsupportedOperationException("$name is not provided by kten-cuda")
 
-    override fun concat(axis: Int, inputs: List<CUDARawTensor>): CUDARawTensor = unsupported("concat")
+    // AbstractJVMTensorOperations.kt:106-120: every input is set into its range of the result
+    override fun concat(axis: Int, inputs: List<CUDARawTensor>): CUDARawTensor {
+        val shapes = inputs.map { it.shape }
+        val resShape = concatShapes(shapes, axis)
+        val normAxis = shapes[0].normalizeAxis(axis)
+        val ranges = resShape.map { 0 until it }.toTypedArray()
+        val res = createRaw(resShape)
+        var last = 0
+        for (input in inputs) {
+            ranges[normAxis] = last until (last + input.shape[normAxis])
+            res[ranges] = input
+            last += input.shape[normAxis]
+        }
+        return res
+    }
     override fun gemm(addMatrix: CUDARawTensor, matrix1: CUDARawTensor, matrix2: CUDARawTensor, alpha: Float, beta: Float,
                       transposeFirst: Boolean, transposeSecond: Boolean): CUDARawTensor = unsupported("gemm")
     override fun gemv(addVector: CUDARawTensor, matrix: CUDARawTensor, vector: CUDARawTensor, alpha: Float, beta: Float,

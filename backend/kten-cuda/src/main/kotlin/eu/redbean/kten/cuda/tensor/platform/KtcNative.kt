@@ -23,7 +23,11 @@ internal object KtcNative {
     const val PLUS = 0; const val MINUS = 1; const val TIMES = 2; const val DIV = 3; const val POW = 4
     const val EXP = 0; const val LOG = 1; const val TANH = 2; const val SIGMOID = 3; const val RECIPROCAL = 4; const val NEG = 5
     const val SUM = 0; const val MEAN = 1; const val MAX = 2; const val MIN = 3; const val ARGMAX = 4; const val ARGMIN = 5
-    const val LT = 0; const val LTE = 1; const val GT = 2; const val GTE = 3
+    const val SINH = 6; const val COSH = 7; const val ABS = 8; const val SIGN = 9; const val SQRT = 10; const val SIN = 11
+    const val COS = 12; const val TAN = 13; const val ASIN = 14; const val ACOS = 15; const val ATAN = 16; const val FLOOR = 17
+    const val CEIL = 18; const val ROUND = 19; const val TRUNC = 20; const val RSQRT = 21
+    const val LT = 0; const val LTE = 1; const val GT = 2; const val GTE = 3; const val EQ = 4; const val NEQ = 5
+    const val SCATTER_SET = 0; const val SCATTER_ADD = 1; const val SCATTER_CONST = 2
 
     private val linker: Linker = Linker.nativeLinker()
     private val lookup: SymbolLookup = System.getProperty("kten.cuda.library")
@@ -61,6 +65,16 @@ internal object KtcNative {
     val reduceAxis = handle("ktc_reduce_axis", JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG)
     val reduceAll = handle("ktc_reduce_all", JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG)
     val scatterAxis = handle("ktc_scatter_axis", JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG)
+    val compareScalarEps = handle("ktc_compare_scalar_eps", JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_FLOAT, JAVA_FLOAT, JAVA_LONG)
+    val compareTensor = handle("ktc_compare_tensor", JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_FLOAT, JAVA_LONG)
+    val maskedFill = handle("ktc_masked_fill", JAVA_INT, JAVA_LONG, JAVA_LONG, ADDRESS, JAVA_INT, JAVA_LONG, ADDRESS, JAVA_INT, JAVA_FLOAT)
+    val containsNan = handle("ktc_contains_nan", JAVA_INT, JAVA_LONG, JAVA_LONG, ADDRESS)
+    val copyStrided = handle("ktc_copy_strided", JAVA_INT, JAVA_LONG, JAVA_LONG, ADDRESS, JAVA_LONG, JAVA_LONG, ADDRESS, ADDRESS, JAVA_INT)
+    val fillStrided = handle("ktc_fill_strided", JAVA_INT, JAVA_LONG, JAVA_LONG, ADDRESS, ADDRESS, JAVA_INT, JAVA_FLOAT)
+    val gatherAxis = handle("ktc_gather_axis", JAVA_INT, JAVA_LONG, JAVA_LONG, ADDRESS, JAVA_LONG, ADDRESS, JAVA_INT, JAVA_INT)
+    val scatterAxisNd = handle("ktc_scatter_axis_nd", JAVA_INT, JAVA_INT, JAVA_LONG, ADDRESS, JAVA_LONG, ADDRESS, JAVA_LONG, ADDRESS, JAVA_INT, JAVA_INT, JAVA_FLOAT)
+    val indexSelect = handle("ktc_index_select", JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG)
+    val indexAdd = handle("ktc_index_add", JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_FLOAT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG)
 
     /** KTC_EINVAL -> IllegalArgumentException, KTC_ESTATE -> IllegalStateException, KTC_ENOMEM -> OutOfMemoryError. */
     fun check(status: Int) {

@@ -1,16 +1,26 @@
 package eu.redbean.kten.cuda.tensor.store
 
+import eu.redbean.kten.api.autograd.utils.indexAddCheckShapesNormAxis
+import eu.redbean.kten.api.autograd.utils.indexSelectNormAxisShape
 import eu.redbean.kten.api.autograd.utils.inferExplicitBroadcastShape
 import eu.redbean.kten.api.autograd.utils.normalizeAxis
+import eu.redbean.kten.api.autograd.utils.normalizeIndex
+import eu.redbean.kten.api.autograd.utils.normalizedAxisScatter
+import eu.redbean.kten.api.autograd.utils.normalizedIndexedShape
+import eu.redbean.kten.api.autograd.utils.permute
 import eu.redbean.kten.api.autograd.utils.reshape
 import eu.redbean.kten.api.autograd.utils.toStoreSize
+import eu.redbean.kten.api.autograd.utils.transposeNormalizeAxes
+import eu.redbean.kten.api.tensor.platform.PlatformProvider
 import eu.redbean.kten.api.tensor.store.AbstractRawTensor
 import eu.redbean.kten.api.tensor.store.AggregatingOperation
 import eu.redbean.kten.cuda.tensor.operations.CUDATensorOperations
 import eu.redbean.kten.cuda.tensor.platform.KtcNative
 import eu.redbean.kten.cuda.tensor.platform.KtcNative.check
 import java.lang.foreign.Arena
+import java.lang.foreign.MemorySegment
 import java.lang.foreign.ValueLayout.JAVA_FLOAT
+import java.lang.foreign.ValueLayout.JAVA_INT
 
 /** Device storage: one reference-counted buffer handle of libkten_cuda.so. */
 class CUDABuffer(val handle: Long, val size: Int)
@@ -154,14 +164,31 @@ class CUDARawTensor(
         check(KtcNative.reduceAll.invokeExact(KtcNative.MEAN, it.handle, handle, volume) as Int)
     }
 
+    // one index per position along the axis over the whole target (Max / Min backward): fully parallel kernel;
+    // every other form: the general kernel, sequential along the axis like JVMRawTensor.kt:227-247
     override fun inplaceScatter(axis: Int, index: AbstractRawTensor<CUDABuffer>, src: AbstractRawTensor<CUDABuffer>) {
-        val a = shape.normalizeAxis(axis)
-        if (index.shape[a] != 1 || index.shape != src.shape)
-            throw UnsupportedOperationException("kten-cuda scatters one index per position along the axis (selection backward)")
-        val outer = shape.take(a).toStoreSize().toLong()
-        val inner = shape.drop(a + 1).toStoreSize().toLong()
-        check(KtcNative.scatterAxis.invokeExact(handle, (index as CUDARawTensor).handle, (src as CUDARawTensor).handle,
-                                                outer, shape[a].toLong(), inner) as Int)
+        val a = shape.normalizedAxisScatter(axis, index.shape, src.shape)
+        val offAxis = { s: List<Int> -> s.filterIndexed { i, _ -> i != a } }
+        if (index.shape[a] == 1 && index.shape == src.shape && offAxis(index.shape) == offAxis(shape)) {
+            val outer = shape.take(a).toStoreSize().toLong()
+            val inner = shape.drop(a + 1).toStoreSize().toLong()
+            check(KtcNative.scatterAxis.invokeExact(handle, (index as CUDARawTensor).handle, (src as CUDARawTensor).handle,
+                                                    outer, shape[a].toLong(), inner) as Int)
+        } else scatterNd(KtcNative.SCATTER_SET, a, index as CUDARawTensor, src as CUDARawTensor, 0f)
+    }
+
+    override fun inplaceScatterAdd(axis: Int, index: AbstractRawTensor<CUDABuffer>, src: AbstractRawTensor<CUDABuffer>) =
+        scatterNd(KtcNative.SCATTER_ADD, shape.normalizedAxisScatter(axis, index.shape, src.shape), index as CUDARawTensor, src as CUDARawTensor, 0f)
+
+    override fun inplaceScatter(axis: Int, index: AbstractRawTensor<CUDABuffer>, src: Float) =
+        scatterNd(KtcNative.SCATTER_CONST, shape.normalizeAxis(axis), index as CUDARawTensor, null, src)
+
+    private fun scatterNd(mode: Int, axis: Int, index: CUDARawTensor, src: CUDARawTensor?, constant: Float) {
+        Arena.ofConfined().use { arena ->
+            check(KtcNative.scatterAxisNd.invokeExact(mode, handle, KtcNative.shape(arena, shape), index.handle, KtcNative.shape(arena, index.shape),
+                                                      src?.handle ?: 0L, if (src == null) MemorySegment.NULL else KtcNative.shape(arena, src.shape),
+                                                      shape.size, axis, constant) as Int)
+        }
     }
 
     // ---- broadcast, copies, host access ------------------------------------------------------------------
@@ -211,51 +238,161 @@ class CUDARawTensor(
 
     override fun inplaceFill(value: Float) = check(KtcNative.fill.invokeExact(handle, 0L, volume, value) as Int)
 
-    override fun containsNan(): Boolean = toFloatArray().any { it.isNaN() }
+    override fun containsNan(): Boolean = Arena.ofConfined().use { arena ->
+        val res = arena.allocate(JAVA_INT)
+        check(KtcNative.containsNan.invokeExact(handle, volume, res) as Int)
+        res.get(JAVA_INT, 0) != 0
+    }
 
-    // ---- outside the float32 hot path: not provided by libkten_cuda.so yet -------------------------------
-    private fun notOnHotPath(name: String): Nothing =
-        throw UnsupportedOperationException("$name is not part of the kten-cuda hot path yet")
+    // ---- the remaining maps and compares (JVMRawTensor.kt:355-435) ---------------------------------------
+    override fun sinh() = unary(KtcNative.SINH)
+    override fun cosh() = unary(KtcNative.COSH)
+    override fun abs() = unary(KtcNative.ABS)
+    override fun sign() = unary(KtcNative.SIGN)
+    override fun sqrt() = unary(KtcNative.SQRT)
+    override fun sin() = unary(KtcNative.SIN)
+    override fun cos() = unary(KtcNative.COS)
+    override fun tan() = unary(KtcNative.TAN)
+    override fun asin() = unary(KtcNative.ASIN)
+    override fun acos() = unary(KtcNative.ACOS)
+    override fun atan() = unary(KtcNative.ATAN)
+    override fun floor() = unary(KtcNative.FLOOR)
+    override fun ceil() = unary(KtcNative.CEIL)
+    override fun round() = unary(KtcNative.ROUND)
+    override fun trunc() = unary(KtcNative.TRUNC)
+    override fun rsqrt() = unary(KtcNative.RSQRT)
 
-    override fun get(index: IntArray): AbstractRawTensor<CUDABuffer> = notOnHotPath("get")
-    override fun get(index: Array<out IntRange>): AbstractRawTensor<CUDABuffer> = notOnHotPath("get")
-    override fun set(index: IntArray, value: AbstractRawTensor<CUDABuffer>) = notOnHotPath("set")
-    override fun set(index: Array<out IntRange>, value: AbstractRawTensor<CUDABuffer>) = notOnHotPath("set")
-    override fun set(index: IntArray, value: Float) = notOnHotPath("set")
-    override fun set(index: Array<out IntRange>, value: Float) = notOnHotPath("set")
-    override fun inplaceScatterAdd(axis: Int, index: AbstractRawTensor<CUDABuffer>, src: AbstractRawTensor<CUDABuffer>) = notOnHotPath("inplaceScatterAdd")
-    override fun inplaceScatter(axis: Int, index: AbstractRawTensor<CUDABuffer>, src: Float) = notOnHotPath("inplaceScatter(constant)")
-    override fun gather(axis: Int, index: AbstractRawTensor<CUDABuffer>): AbstractRawTensor<CUDABuffer> = notOnHotPath("gather")
-    override fun lt(tensor: AbstractRawTensor<CUDABuffer>): AbstractRawTensor<CUDABuffer> = notOnHotPath("lt(tensor)")
-    override fun lte(tensor: AbstractRawTensor<CUDABuffer>): AbstractRawTensor<CUDABuffer> = notOnHotPath("lte(tensor)")
-    override fun gt(tensor: AbstractRawTensor<CUDABuffer>): AbstractRawTensor<CUDABuffer> = notOnHotPath("gt(tensor)")
-    override fun gte(tensor: AbstractRawTensor<CUDABuffer>): AbstractRawTensor<CUDABuffer> = notOnHotPath("gte(tensor)")
-    override fun eq(tensor: AbstractRawTensor<CUDABuffer>): AbstractRawTensor<CUDABuffer> = notOnHotPath("eq(tensor)")
-    override fun neq(tensor: AbstractRawTensor<CUDABuffer>): AbstractRawTensor<CUDABuffer> = notOnHotPath("neq(tensor)")
-    override fun eq(value: Float): AbstractRawTensor<CUDABuffer> = notOnHotPath("eq")
-    override fun neq(value: Float): AbstractRawTensor<CUDABuffer> = notOnHotPath("neq")
-    override fun sinh(): AbstractRawTensor<CUDABuffer> = notOnHotPath("sinh")
-    override fun cosh(): AbstractRawTensor<CUDABuffer> = notOnHotPath("cosh")
-    override fun abs(): AbstractRawTensor<CUDABuffer> = notOnHotPath("abs")
-    override fun sign(): AbstractRawTensor<CUDABuffer> = notOnHotPath("sign")
-    override fun sqrt(): AbstractRawTensor<CUDABuffer> = notOnHotPath("sqrt")
-    override fun sin(): AbstractRawTensor<CUDABuffer> = notOnHotPath("sin")
-    override fun cos(): AbstractRawTensor<CUDABuffer> = notOnHotPath("cos")
-    override fun tan(): AbstractRawTensor<CUDABuffer> = notOnHotPath("tan")
-    override fun asin(): AbstractRawTensor<CUDABuffer> = notOnHotPath("asin")
-    override fun acos(): AbstractRawTensor<CUDABuffer> = notOnHotPath("acos")
-    override fun atan(): AbstractRawTensor<CUDABuffer> = notOnHotPath("atan")
-    override fun floor(): AbstractRawTensor<CUDABuffer> = notOnHotPath("floor")
-    override fun ceil(): AbstractRawTensor<CUDABuffer> = notOnHotPath("ceil")
-    override fun round(): AbstractRawTensor<CUDABuffer> = notOnHotPath("round")
-    override fun trunc(): AbstractRawTensor<CUDABuffer> = notOnHotPath("trunc")
-    override fun rsqrt(): AbstractRawTensor<CUDABuffer> = notOnHotPath("rsqrt")
-    override fun transpose(axis1: Int, axis2: Int): AbstractRawTensor<CUDABuffer> = notOnHotPath("transpose")
-    override fun permute(axes: List<Int>): AbstractRawTensor<CUDABuffer> = notOnHotPath("permute")
-    override fun narrow(axis: Int, start: Int, length: Int): AbstractRawTensor<CUDABuffer> = notOnHotPath("narrow")
-    override fun dot(vector: AbstractRawTensor<CUDABuffer>): AbstractRawTensor<CUDABuffer> = notOnHotPath("dot")
-    override fun indexSelect(axis: Int, index: AbstractRawTensor<CUDABuffer>): AbstractRawTensor<CUDABuffer> = notOnHotPath("indexSelect")
-    override fun indexAdd(axis: Int, index: AbstractRawTensor<CUDABuffer>, src: AbstractRawTensor<CUDABuffer>, alpha: Float) = notOnHotPath("indexAdd")
-    override fun inplaceResize(vararg shape: Int) = notOnHotPath("inplaceResize")
-    override fun maskedFill(mask: AbstractRawTensor<CUDABuffer>, value: Float): AbstractRawTensor<CUDABuffer> = notOnHotPath("maskedFill")
+    private fun compareTensor(op: Int, tensor: AbstractRawTensor<CUDABuffer>): CUDARawTensor {
+        if (shape != tensor.shape)                               // kten-jvm's tensor compares do not broadcast
+            throw IllegalArgumentException("Tensor compare needs equal shapes, got $shape and ${tensor.shape}")
+        val res = ops.createRaw(shape)
+        check(KtcNative.compareTensor.invokeExact(op, res.handle, handle, (tensor as CUDARawTensor).handle, PlatformProvider.epsilon, volume) as Int)
+        return res
+    }
+
+    private fun compareEps(op: Int, value: Float): CUDARawTensor {
+        val res = ops.createRaw(shape)
+        check(KtcNative.compareScalarEps.invokeExact(op, res.handle, handle, value, PlatformProvider.epsilon, volume) as Int)
+        return res
+    }
+
+    override fun lt(tensor: AbstractRawTensor<CUDABuffer>) = compareTensor(KtcNative.LT, tensor)
+    override fun lte(tensor: AbstractRawTensor<CUDABuffer>) = compareTensor(KtcNative.LTE, tensor)
+    override fun gt(tensor: AbstractRawTensor<CUDABuffer>) = compareTensor(KtcNative.GT, tensor)
+    override fun gte(tensor: AbstractRawTensor<CUDABuffer>) = compareTensor(KtcNative.GTE, tensor)
+    override fun eq(tensor: AbstractRawTensor<CUDABuffer>) = compareTensor(KtcNative.EQ, tensor)
+    override fun neq(tensor: AbstractRawTensor<CUDABuffer>) = compareTensor(KtcNative.NEQ, tensor)
+    override fun eq(value: Float) = compareEps(KtcNative.EQ, value)
+    override fun neq(value: Float) = compareEps(KtcNative.NEQ, value)
+
+    override fun maskedFill(mask: AbstractRawTensor<CUDABuffer>, value: Float): CUDARawTensor {
+        mask.shape.inferExplicitBroadcastShape(shape)
+        val res = ops.createRaw(shape)
+        Arena.ofConfined().use { arena ->
+            check(KtcNative.maskedFill.invokeExact(res.handle, handle, KtcNative.shape(arena, shape), shape.size,
+                                                   (mask as CUDARawTensor).handle, KtcNative.shape(arena, mask.shape), mask.shape.size, value) as Int)
+        }
+        return res
+    }
+
+    // ---- slices, permutes, gather / index ops (JVMRawTensor.kt:270-353, 437-518) -----------------------------
+    private fun strides(s: List<Int>): List<Int> = s.indices.map { s.drop(it + 1).toStoreSize() }
+
+    /** offset, box shape and this tensor's strides for a normalised range index (trailing dimensions whole) */
+    private fun box(ranges: List<IntRange>): Triple<Long, List<Int>, List<Int>> {
+        val st = strides(shape)
+        val offset = ranges.foldIndexed(0L) { d, acc, r -> acc + r.first.toLong() * st[d] }
+        return Triple(offset, ranges.map { it.last - it.first + 1 } + shape.drop(ranges.size), st)
+    }
+
+    private fun copyBox(dst: CUDARawTensor, dstOffset: Long, dstStrides: List<Int>, src: CUDARawTensor, srcOffset: Long, srcStrides: List<Int>, box: List<Int>) =
+        Arena.ofConfined().use { arena ->
+            check(KtcNative.copyStrided.invokeExact(dst.handle, dstOffset, KtcNative.shape(arena, dstStrides), src.handle, srcOffset,
+                                                    KtcNative.shape(arena, srcStrides), KtcNative.shape(arena, box), box.size) as Int)
+        }
+
+    override fun get(index: IntArray): CUDARawTensor {
+        val (norm, resShape) = shape.normalizedIndexedShape(index)
+        val sub = shape.drop(norm.size).toStoreSize().toLong()
+        val start = norm.foldIndexed(0L) { d, acc, i -> acc * shape[d] + i }
+        val res = ops.createRaw(resShape)
+        check(KtcNative.d2d.invokeExact(res.handle, 0L, handle, start * sub, sub) as Int)
+        return res
+    }
+
+    override fun get(index: Array<out IntRange>): CUDARawTensor {
+        val (norm, resShape) = shape.normalizedIndexedShape(index)
+        val (offset, boxShape, st) = box(norm.toList())
+        val res = ops.createRaw(resShape)
+        copyBox(res, 0L, strides(boxShape), this, offset, st, boxShape)
+        return res
+    }
+
+    private fun setBox(ranges: List<IntRange>, value: CUDARawTensor?, constant: Float, indexForMessage: List<*>) {
+        val (offset, boxShape, st) = box(ranges)
+        if (value != null) {
+            if (value.volume != boxShape.toStoreSize().toLong())
+                throw IllegalArgumentException("Cannot set tensor with shape: ${value.shape} to tensor with shape: $shape at index: $indexForMessage")
+            copyBox(this, offset, st, value, 0L, strides(boxShape), boxShape)
+        } else Arena.ofConfined().use { arena ->
+            check(KtcNative.fillStrided.invokeExact(handle, offset, KtcNative.shape(arena, st), KtcNative.shape(arena, boxShape), boxShape.size, constant) as Int)
+        }
+    }
+
+    override fun set(index: IntArray, value: AbstractRawTensor<CUDABuffer>) =
+        setBox(shape.normalizeIndex(index).map { it..it }, value as CUDARawTensor, 0f, index.toList())
+    override fun set(index: Array<out IntRange>, value: AbstractRawTensor<CUDABuffer>) =
+        setBox(shape.normalizeIndex(index).toList(), value as CUDARawTensor, 0f, index.toList())
+    override fun set(index: IntArray, value: Float) = setBox(shape.normalizeIndex(index).map { it..it }, null, value, index.toList())
+    override fun set(index: Array<out IntRange>, value: Float) = setBox(shape.normalizeIndex(index).toList(), null, value, index.toList())
+
+    override fun narrow(axis: Int, start: Int, length: Int): CUDARawTensor {
+        val ranges = shape.map { 0 until it }.toTypedArray()
+        ranges[shape.normalizeAxis(axis)] = start until (start + length)
+        return get(ranges)
+    }
+
+    override fun permute(axes: List<Int>): CUDARawTensor {
+        val newShape = shape.permute(axes)
+        val st = strides(shape)
+        val res = ops.createRaw(newShape)
+        copyBox(res, 0L, strides(newShape), this, 0L, axes.map { st[it] }, newShape)     // result dimension i = this dimension axes[i]
+        return res
+    }
+
+    override fun transpose(axis1: Int, axis2: Int): CUDARawTensor {
+        val (_, a1, a2) = shape.transposeNormalizeAxes(axis1, axis2)
+        return permute(shape.indices.map { if (it == a1) a2 else if (it == a2) a1 else it })
+    }
+
+    override fun gather(axis: Int, index: AbstractRawTensor<CUDABuffer>): CUDARawTensor {
+        val res = ops.createRaw(index.shape)
+        Arena.ofConfined().use { arena ->
+            check(KtcNative.gatherAxis.invokeExact(res.handle, handle, KtcNative.shape(arena, shape), (index as CUDARawTensor).handle,
+                                                   KtcNative.shape(arena, index.shape), shape.size, shape.normalizeAxis(axis)) as Int)
+        }
+        return res
+    }
+
+    override fun indexSelect(axis: Int, index: AbstractRawTensor<CUDABuffer>): CUDARawTensor {
+        val (a, resShape) = shape.indexSelectNormAxisShape(axis, index.shape)
+        val res = ops.createRaw(resShape)
+        check(KtcNative.indexSelect.invokeExact(res.handle, handle, (index as CUDARawTensor).handle, shape.take(a).toStoreSize().toLong(),
+                                                shape[a].toLong(), index.shape[0].toLong(), shape.drop(a + 1).toStoreSize().toLong()) as Int)
+        return res
+    }
+
+    override fun indexAdd(axis: Int, index: AbstractRawTensor<CUDABuffer>, src: AbstractRawTensor<CUDABuffer>, alpha: Float) {
+        val a = shape.indexAddCheckShapesNormAxis(axis, index.shape, src.shape)
+        check(KtcNative.indexAdd.invokeExact(handle, (index as CUDARawTensor).handle, (src as CUDARawTensor).handle, alpha,
+                                             shape.take(a).toStoreSize().toLong(), shape[a].toLong(), index.shape[0].toLong(),
+                                             shape.drop(a + 1).toStoreSize().toLong()) as Int)
+    }
+
+    // ---- BLAS: not provided by libkten_cuda.so ---------------------------------------------------------------
+    override fun dot(vector: AbstractRawTensor<CUDABuffer>): AbstractRawTensor<CUDABuffer> =
+        throw UnsupportedOperationException("dot is a BLAS operation; kten-cuda does not provide BLAS yet")
+
+    override fun inplaceResize(vararg shape: Int) =
+        throw UnsupportedOperationException("inplaceResize swaps the store object; bind it where CUDABuffer is made replaceable")
 }
