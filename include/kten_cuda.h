@@ -120,8 +120,9 @@ KTC_API int ktc_host_free(float* p);
  *                     far, but later compute work does NOT wait for it: before queuing work that
  *                     overwrites the source, call ktc_copy_fence.  Uploads, kernels and downloads of
  *                     neighbouring chunks then overlap (full-duplex copy engines).
- * ktc_sync waits for the copy streams too; ktc_copy_fence makes compute work queued afterwards wait
- * for every overlapped copy issued so far (no host wait). */
+ * ktc_sync waits for the copy streams too; ktc_copy_fence orders both ways without a host wait:
+ * compute work queued afterwards waits for every overlapped copy issued so far, and overlapped
+ * copies issued afterwards wait for the compute work queued so far. */
 enum { KTC_COPY_ASYNC = 0, KTC_COPY_SYNC = 1, KTC_COPY_OVERLAP = 2, KTC_COPY_OVERLAP_UNFENCED = 3 };
 KTC_API int ktc_h2d(ktc_buf dst, int64_t dst_off, const float* src, int64_t n, int mode);
 KTC_API int ktc_d2h(float* dst, ktc_buf src, int64_t src_off, int64_t n, int mode);

@@ -430,6 +430,12 @@ int ktc_copy_fence(int dev) {
     KTC_CUDA(cudaEventRecord(down, d->stream_down));
     KTC_CUDA(cudaStreamWaitEvent(d->stream, up, 0));
     KTC_CUDA(cudaStreamWaitEvent(d->stream, down, 0));
+    // ... and copies issued after the fence start after the compute work issued before it (an unfenced
+    // upload may then overwrite what earlier kernels read)
+    cudaEvent_t done = next_event(d);
+    KTC_CUDA(cudaEventRecord(done, d->stream));
+    KTC_CUDA(cudaStreamWaitEvent(d->stream_up, done, 0));
+    KTC_CUDA(cudaStreamWaitEvent(d->stream_down, done, 0));
     return KTC_OK;
 }
 
