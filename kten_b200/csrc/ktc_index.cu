@@ -1,7 +1,7 @@
 // ktc_index.cu -- data movement of the raw-tensor SPI: slices, transposes / permutes, gather /
 // scatter / index-select / index-add (JVMRawTensor.kt:227-353, 437-518).
 //
-// Everything here is index arithmetic plus one pass over memory, so the kernels are judged by
+// Everything here is index arithmetic plus one pass over memory, so what matters for these kernels is
 // how close that pass comes to the HBM rate:
 //   * k_copy_nd          dst[doff + i.dstr] = src[soff + i.sstr] over an N-d box (get / set by
 //                        ranges, narrow, concat pieces, permutes that keep the innermost axis):

@@ -12,7 +12,7 @@ Two layers:
     autograd caller can be run on both and compared.
 
 `mode`: 0 = jvm-faithful accumulation (float, axis order; sum() sequential
-float), 1 = exact (double accumulators, one narrowing).  Reductions are judged
+float), 1 = exact (double accumulators, one narrowing).  Reductions are compared
 against mode 1; mode 0 is what kten-jvm itself would print.
 """
 from __future__ import annotations
