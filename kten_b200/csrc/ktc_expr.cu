@@ -37,13 +37,13 @@ __device__ __forceinline__ float4 f4(float v) { return make_float4(v, v, v, v); 
 
 // out-of-line so that the switch below stays small; same functors as the stand-alone kernels
 static __device__ __noinline__ float4 expr_pow(float4 x, float4 y) {
-    BinOp<KTC_POW> f; return KTC_EACH(f(x.x, y.x), f(x.y, y.y), f(x.z, y.z), f(x.w, y.w));
+    return apply2(BinOp<KTC_POW>(), x, y);
 }
 static __device__ __noinline__ float4 expr_sigmoid(float4 x) {
-    UnOp<KTC_SIGMOID> f; return KTC_EACH(f(x.x), f(x.y), f(x.z), f(x.w));
+    return apply1(UnOp<KTC_SIGMOID>(), x);
 }
 static __device__ __noinline__ float4 expr_exp(float4 x) {
-    UnOp<KTC_EXP> f; return KTC_EACH(f(x.x), f(x.y), f(x.z), f(x.w));
+    return apply1(UnOp<KTC_EXP>(), x);
 }
 static __device__ __noinline__ float4 expr_log(float4 x) {
     UnOp<KTC_LOG> f; return KTC_EACH(f(x.x), f(x.y), f(x.z), f(x.w));

@@ -28,6 +28,11 @@
 #else
 #define KF_TABLE static const
 #endif
+#if defined(__CUDACC__)
+#define KF_ALIGN16 __align__(16)
+#else
+#define KF_ALIGN16 __attribute__((aligned(16)))
+#endif
 #if defined(__CUDA_ARCH__)
 #define KF_TAB(t, j, c) __ldg(&(t)[j][c])
 #else
@@ -215,7 +220,7 @@ KF_FN bool kf_exp_cr(float x, float* out) {
 // approximation inv of 1/centre, and -log2(inv) split into a part with 16 fractional
 // bits (so that adding the exponent is exact) and a remainder.  The slice that contains
 // 1.0 has inv = 1 and log 0, which keeps full relative accuracy for arguments near 1.
-KF_TABLE float kf_log2_tab[64][4] = {
+KF_TABLE KF_ALIGN16 float kf_log2_tab[64][4] = {   /* rows are read with one 128-bit load by the packed variant */
     {1.406444073e+00f, -4.920501709e-01f, -2.014097618e-06f, 0.0f},
     {1.391158223e+00f, -4.762878418e-01f, 1.327901259e-06f, 0.0f},
     {1.376201153e+00f, -4.606933594e-01f, 2.002024303e-06f, 0.0f},

@@ -17,6 +17,7 @@
 
 #include "../../include/kten_cuda.h"
 #include "ktc_fastmath.h"
+#include "ktc_fastmath2.cuh"
 
 namespace ktc {
 
@@ -84,17 +85,13 @@ template <int OP> struct UnOp;
 template <> struct UnOp<KTC_EXP>  { __device__ __forceinline__ float operator()(float x) const { return exp_f(x); } };
 template <> struct UnOp<KTC_LOG>  { __device__ __forceinline__ float operator()(float x) const { return log_f(x); } };
 template <> struct UnOp<KTC_TANH> { __device__ __forceinline__ float operator()(float x) const { return tanh_f(x); } };
-// sigmoid = 1f / (1f + exp(-1f * x)) with the reference's own two IEEE operations after
-// the exp.  When e <= 1 (x >= 0) a one-ulp slip in e moves 1 + e by at most one ulp and
-// the quotient by less than three ulps before rounding, i.e. the result by at most 2 ulp;
-// when e > 1 the slip is amplified, so there e must be the correctly rounded value.  The
-// choice is made per warp (all 32 arguments non-negative -> the cheaper exp), so no warp
-// executes both paths.
+// sigmoid = 1f / (1f + exp(-1f * x)) with the reference's own two IEEE operations after the exp.  A one-ulp
+// slip in e = exp(-x) can move the result by up to 3 ulp (1 + e rounds away a bit of e, and the reciprocal can
+// double a relative error when its mantissa wraps), so e is always the CORRECTLY ROUNDED exp: the result is
+// then the reference's, bit for bit, for every argument, and does not depend on which kernel evaluates it.
 template <> struct UnOp<KTC_SIGMOID> {
     __device__ __forceinline__ float operator()(float x) const {
-        const float a = __fmul_rn(-1.0f, x);
-        const bool lean = __all_sync(__activemask(), x >= 0.0f);
-        const float e = lean ? exp_f(a) : exp_cr(a);
+        const float e = exp_cr(__fmul_rn(-1.0f, x));
         return __frcp_rn(__fadd_rn(1.0f, e));        // 1f / (1f + e): the IEEE reciprocal is the IEEE quotient
     }
 };
@@ -108,6 +105,42 @@ template <int OP> struct ScalarLeft  { float s; __device__ __forceinline__ float
 // 48 significant bits, so Math.pow's result narrows to the float product.
 struct Square { __device__ __forceinline__ float operator()(float a) const { return __fmul_rn(a, a); } };
 struct Identity { __device__ __forceinline__ float operator()(float a) const { return a; } };
+
+// ---- two elements per instruction (ktc_fastmath2.cuh); each lane equals the scalar function above ----------
+__device__ __forceinline__ void exp_f_pair(float x0, float x1, float& o0, float& o1) {
+    const f2 r = kf2_exp(make_float2(x0, x1));
+    o0 = kf_exp_in_domain(x0) ? r.x : exp_ref(x0);
+    o1 = kf_exp_in_domain(x1) ? r.y : exp_ref(x1);
+}
+__device__ __forceinline__ void exp_cr_pair(float x0, float x1, float& o0, float& o1) {
+    bool ok0, ok1;
+    const f2 r = kf2_exp_cr(make_float2(x0, x1), &ok0, &ok1);
+    o0 = ok0 ? r.x : exp_ref(x0);
+    o1 = ok1 ? r.y : exp_ref(x1);
+}
+__device__ __forceinline__ void pow_f_pair(float x0, float x1, float y0, float y1, float& o0, float& o1) {
+    bool ok0, ok1;
+    const f2 r = kf2_pow(make_float2(x0, x1), make_float2(y0, y1), &ok0, &ok1);
+    o0 = (y0 == 0.0f) ? 1.0f : (ok0 ? r.x : pow_ref(x0, y0));
+    o1 = (y1 == 0.0f) ? 1.0f : (ok1 ? r.y : pow_ref(x1, y1));
+}
+__device__ __forceinline__ void sigmoid_pair(float x0, float x1, float& o0, float& o1) {
+    const f2 a = mul2(make_float2(x0, x1), F2(-1.0f));
+    float e0, e1;
+    exp_cr_pair(a.x, a.y, e0, e1);
+    const f2 d = add2(F2(1.0f), make_float2(e0, e1));
+    o0 = __frcp_rn(d.x); o1 = __frcp_rn(d.y);
+}
+// float4 forms picked by the map kernels (overloads of the generic per-element application)
+__device__ __forceinline__ float4 apply1(const UnOp<KTC_EXP>&, float4 a) {
+    float4 o; exp_f_pair(a.x, a.y, o.x, o.y); exp_f_pair(a.z, a.w, o.z, o.w); return o;
+}
+__device__ __forceinline__ float4 apply1(const UnOp<KTC_SIGMOID>&, float4 a) {
+    float4 o; sigmoid_pair(a.x, a.y, o.x, o.y); sigmoid_pair(a.z, a.w, o.z, o.w); return o;
+}
+__device__ __forceinline__ float4 apply2(const BinOp<KTC_POW>&, float4 a, float4 b) {
+    float4 o; pow_f_pair(a.x, a.y, b.x, b.y, o.x, o.y); pow_f_pair(a.z, a.w, b.z, b.w, o.z, o.w); return o;
+}
 
 struct ClampOp { float lo, hi; __device__ __forceinline__ float operator()(float x) const { return jmin(jmax(x, lo), hi); } };
 

@@ -624,3 +624,37 @@ def test_bounded_device_wait_times_out_cleanly(cuda_ops):
     r = cuda_ops.createRawFill([16], 1.0)
     assert float(r.sum().toArray()[0]) == 16.0
     r.release()
+
+
+def test_packed_math_equals_scalar_math(cuda_ops, gc_scope):
+    """exp, sigmoid and pow run two elements per instruction (float2 add / mul / fma of sm_100) in the vector
+    kernels and one element per instruction in the scalar kernels that serve unaligned buffers: every lane
+    must produce the scalar bits.  The unaligned case is a view that starts one float into the buffer."""
+    lib = cuda_ops.lib
+    n = (1 << 18) + 1
+    x = np.concatenate([D.uniform(n - 40, 61, -30.0, 30.0), special_values()[:20], np.array([88.0, -88.0, 87.0, -87.0, 100.0, -100.0, 0.0, -0.0,
+                        1e-30, -1e-30, 1.0, -1.0, 0.5, 2.0, 3.0, 1e5, -1e5, 1e-10, 40.0, -40.0], dtype=np.float32)])[:n].astype(np.float32)
+    y = np.concatenate([D.uniform(n - 8, 62, -4.0, 4.0), np.array([0.0, -0.0, 1.0, 2.0, 0.5, -1.0, 1e3, -1e3], dtype=np.float32)])[:n].astype(np.float32)
+    base = np.abs(x) + np.float32(1e-3)
+    ta, tb = cuda_ops.createRaw([n], x), cuda_ops.createRaw([n], y)
+    tp = cuda_ops.createRaw([n], base)
+    out_v, out_s = cuda_ops.createRaw([n]), cuda_ops.createRaw([n])
+
+    def view(t):
+        h = C.c_uint64(0)
+        L.check(lib.ktc_view(t.storeReference, 1, n - 1, C.byref(h)))
+        return h.value
+
+    va, vb, vp, vo = view(ta), view(tb), view(tp), view(out_s)
+    for code in (L.EXP, L.SIGMOID):
+        L.check(lib.ktc_unary(code, out_v.storeReference, ta.storeReference, n))          # aligned: packed
+        L.check(lib.ktc_unary(code, vo, va, n - 1))                                       # unaligned: scalar
+        assert same_bits(out_v.toArray()[1:], out_s.toArray()[1:]), code
+    L.check(lib.ktc_binary(L.POW, out_v.storeReference, tp.storeReference, tb.storeReference, n))
+    L.check(lib.ktc_binary(L.POW, vo, vp, vb, n - 1))
+    assert same_bits(out_v.toArray()[1:], out_s.toArray()[1:])
+    for h in (va, vb, vp, vo):
+        L.check(lib.ktc_release(h))
+    # sigmoid is the reference's value bit for bit (correctly rounded exp, then the reference's two IEEE operations)
+    got = ta.sigmoid().toArray()
+    assert same_bits(got, O.unary(O.SIGMOID, x))
