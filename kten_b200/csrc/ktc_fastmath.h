@@ -102,7 +102,7 @@ KF_FN bool kf_exp(float x, float* out) {
 }
 
 // 2^(j/64), j = 0..63, as high + low floats
-KF_TABLE float kf_exp2_tab[64][2] = {
+KF_TABLE KF_ALIGN16 float kf_exp2_tab[64][2] = {   /* rows are read with one 64-bit load by the packed variant */
     {1.000000000e+00f, 0.000000000e+00f},
     {1.010889292e+00f, -5.711605411e-09f},
     {1.021897197e+00f, -4.811559862e-08f},

@@ -77,8 +77,9 @@ __device__ __forceinline__ f2 kf2_exp_cr(f2 x, bool* ok0, bool* ok1) {
     const f2 e1 = add2(sub2(r1, sub2(r, bb)), sub2(neg2(p2), bb));
     const f2 rl = fma2(kf, F2(-2.5310171168115014e-13f), sub2(e1, p2e));
     const int32_t j0 = k0 & 63, j1 = k1 & 63;
-    const f2 th = make_float2(KF_TAB(kf_exp2_tab, j0, 0), KF_TAB(kf_exp2_tab, j1, 0));
-    const f2 tl = make_float2(KF_TAB(kf_exp2_tab, j0, 1), KF_TAB(kf_exp2_tab, j1, 1));
+    const float2 row0 = __ldg(reinterpret_cast<const float2*>(&kf_exp2_tab[j0][0]));     // (high, low) of 2^(j/64)
+    const float2 row1 = __ldg(reinterpret_cast<const float2*>(&kf_exp2_tab[j1][0]));
+    const f2 th = make_float2(row0.x, row1.x), tl = make_float2(row0.y, row1.y);
     f2 q = fma2(r, F2(4.1666666666666664e-2f), F2(1.6666666666666666e-1f));
     q = fma2(r, q, F2(0.5f));
     const f2 e = fma2(mul2(r, r), q, fma2(r, rl, rl));
