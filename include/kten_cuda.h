@@ -298,6 +298,39 @@ KTC_API int ktc_comm_init_rank(int dev, int n_ranks, int rank, const unsigned ch
 KTC_API int ktc_allreduce_sum(ktc_comm comm, ktc_buf buf, int64_t off, int64_t n);
 KTC_API int ktc_comm_destroy(ktc_comm comm);
 
+/* ---- all-reduce through peer memory (one process per GPU, one kernel per call) -------------
+ * No counterpart in the reference (a kten tensor lives on one platform, Tensor.kt:143).  The sum of a
+ * few small tensors -- the loss partial and the broadcast-gradient results of the sharded path --
+ * across the GPUs of one box, without a collective library: each rank owns a mailbox in device
+ * memory that every peer maps through a CUDA IPC handle; ONE kernel per rank stores the values into
+ * every peer's mailbox (ordinary peer stores over NVLink), waits -- for a bounded time -- until all
+ * ranks have done so, and adds the mailbox slots in rank order, in place.  All ranks perform the
+ * same additions in the same order: results are identical on every rank and from run to run.
+ *   ktc_p2p_create   allocates this rank's mailbox and returns its 64-byte IPC handle; the caller
+ *                    gathers the handles of all ranks (any host channel) ...
+ *   ktc_p2p_connect  ... and passes them, rank-major, n_ranks * 64 bytes.  A host barrier must
+ *                    separate connect from the first all-reduce, and the last all-reduce from destroy.
+ *   ktc_p2p_allreduce_sum  enqueues the kernel on the device's compute stream: up to
+ *                    KTC_P2P_MAX_TENSORS tensors, KTC_P2P_MAX_FLOATS floats in total per call.  Every
+ *                    rank must make the same sequence of calls.
+ *   ktc_p2p_status   waits for the stream; *status = KTC_OK, or KTC_ETIMEOUT if a rank failed to
+ *                    arrive within the limit (tunable p2p_wait_ms, default 2000): the kernel then
+ *                    returned without summing, the context stays usable, the communicator does not
+ *                    (destroy it).
+ * ktc_test_p2p_connect_self wires every peer slot to this rank's own mailbox, so that the absent ranks
+ * never arrive: the time-out path on a single GPU, without a second process. */
+#define KTC_P2P_HANDLE_BYTES 64
+#define KTC_P2P_MAX_RANKS 16
+#define KTC_P2P_MAX_FLOATS 16384
+#define KTC_P2P_MAX_TENSORS 8
+typedef uint64_t ktc_p2p;
+KTC_API int ktc_p2p_create(int dev, int n_ranks, int rank, ktc_p2p* out, unsigned char handle_out[KTC_P2P_HANDLE_BYTES]);
+KTC_API int ktc_p2p_connect(ktc_p2p p, const unsigned char* all_handles);
+KTC_API int ktc_p2p_allreduce_sum(ktc_p2p p, const ktc_buf* bufs, const int64_t* counts, int n_bufs);
+KTC_API int ktc_p2p_status(ktc_p2p p, int* status);
+KTC_API int ktc_p2p_destroy(ktc_p2p p);
+KTC_API int ktc_test_p2p_connect_self(ktc_p2p p);
+
 /* ---- measurement -----------------------------------------------------------
  * CUDA events recorded on the device's compute stream; launch counter. */
 KTC_API int ktc_timer_start(int dev);

@@ -25,6 +25,7 @@ SCATTER_SET, SCATTER_ADD, SCATTER_CONST = 0, 1, 2
 MAX_DIMS = 10
 COPY_ASYNC, COPY_SYNC, COPY_OVERLAP, COPY_OVERLAP_UNFENCED = 0, 1, 2, 3
 COMM_ID_BYTES = 128
+P2P_HANDLE_BYTES, P2P_MAX_RANKS, P2P_MAX_FLOATS, P2P_MAX_TENSORS = 64, 16, 16384, 8
 # fused expression programs (ktc_expr_eval)
 (X_LOAD, X_CONST, X_ADD, X_SUB, X_MUL, X_DIV, X_POW, X_NEG, X_RCP, X_SQUARE, X_EXP, X_LOG, X_TANH, X_SIGMOID, X_CLAMP,
  X_CMP_LT, X_CMP_LTE, X_CMP_GT, X_CMP_GTE, X_STORE, X_ACC) = range(1, 22)
@@ -93,6 +94,12 @@ _PROTOTYPES = {
     "ktc_comm_init_rank": (i32, [i32, i32, i32, C.c_char_p, p_u64]),
     "ktc_allreduce_sum": (i32, [u64, u64, i64, i64]),
     "ktc_comm_destroy": (i32, [u64]),
+    "ktc_p2p_create": (i32, [i32, i32, i32, p_u64, C.c_char_p]),
+    "ktc_p2p_connect": (i32, [u64, C.c_char_p]),
+    "ktc_p2p_allreduce_sum": (i32, [u64, p_u64, p_i64, i32]),
+    "ktc_p2p_status": (i32, [u64, p_i32]),
+    "ktc_p2p_destroy": (i32, [u64]),
+    "ktc_test_p2p_connect_self": (i32, [u64]),
     "ktc_timer_start": (i32, [i32]),
     "ktc_timer_stop": (i32, [i32, p_f32]),
     "ktc_launch_count": (i64, []),

@@ -8,8 +8,9 @@ kten-api/.../tensor/Tensor.kt:143); what shards here is the path itself:
     reductions over a non-leading axis need no communication: replicate the small
     operand, work on the local rows;
   * full reductions and sum-to-shape over the leading axis (the loss and the weight /
-    bias gradients) leave one partial per rank; the partials are packed into one
-    buffer and summed in place with a single all-reduce.
+    bias gradients) leave one partial per rank; the partials are summed in place across
+    the ranks -- by one kernel per rank over peer memory (PeerMemoryCollective), or
+    packed into one buffer and passed to a single NCCL all-reduce (NcclCollective).
 
 `ShardedSigmoidGraph` is the sharded autograd step of the benchmark configuration
 "x[262144,1024], w[1,1024], b[1024]: loss = sum(sigmoid(x*w + b) pow 2)", issued as the
@@ -61,6 +62,50 @@ class NcclCollective:
         off = 0
         for r in raws:
             L.check(lib.ktc_d2d(r.storeReference, 0, self._packed.storeReference, off, r.size)); off += r.size
+
+
+class PeerMemoryCollective:
+    """Sum small raw tensors across ranks with ONE kernel per rank over NVLink peer memory
+    (ktc_p2p_allreduce_sum): values go straight from the tensors into every peer's mailbox, a bounded
+    wait, then a rank-ordered sum written back in place -- no packing, no collective library.
+    `exchange(my_bytes) -> list of every rank's bytes` carries the 64-byte IPC handles between the
+    processes (e.g. torch.distributed.all_gather_object); `barrier()` is a host barrier."""
+
+    def __init__(self, ops, world: int, rank: int, exchange, barrier):
+        from . import _lib as L
+        self.ops, self.world, self.rank, self._barrier = ops, world, rank, barrier
+        self._L = L
+        handle = C.create_string_buffer(L.P2P_HANDLE_BYTES)
+        comm = C.c_uint64(0)
+        L.check(ops.lib.ktc_p2p_create(ops.device, world, rank, C.byref(comm), handle))
+        self.comm = comm.value
+        everyone = exchange(bytes(handle.raw))
+        if len(everyone) != world or any(len(h) != L.P2P_HANDLE_BYTES for h in everyone):
+            raise RuntimeError("handle exchange returned a wrong number of handles")
+        L.check(ops.lib.ktc_p2p_connect(self.comm, b"".join(everyone)))
+        barrier()                                   # every mailbox is mapped everywhere before the first store
+
+    def allreduce_sum(self, raws: Sequence) -> None:
+        L = self._L
+        for i in range(0, len(raws), L.P2P_MAX_TENSORS):
+            group = raws[i:i + L.P2P_MAX_TENSORS]
+            bufs = (C.c_uint64 * len(group))(*[r.storeReference for r in group])
+            counts = (C.c_int64 * len(group))(*[r.size for r in group])
+            L.check(self.ops.lib.ktc_p2p_allreduce_sum(self.comm, bufs, counts, len(group)))
+
+    def check(self) -> None:
+        """Waits for the device; raises if a rank did not arrive within the limit."""
+        st = C.c_int(0)
+        self._L.check(self.ops.lib.ktc_p2p_status(self.comm, C.byref(st)))
+        if st.value != self._L.KTC_OK:
+            raise TimeoutError("peer-memory all-reduce: a rank did not arrive within the time limit")
+
+    def close(self) -> None:
+        if self.comm:
+            self.ops.synchronize()
+            self._barrier()                         # nobody frees a mailbox a peer may still write
+            self._L.check(self.ops.lib.ktc_p2p_destroy(self.comm))
+            self.comm = 0
 
 
 class LocalCollective:

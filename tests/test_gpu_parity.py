@@ -658,3 +658,47 @@ def test_packed_math_equals_scalar_math(cuda_ops, gc_scope):
     # sigmoid is the reference's value bit for bit (correctly rounded exp, then the reference's two IEEE operations)
     got = ta.sigmoid().toArray()
     assert same_bits(got, O.unary(O.SIGMOID, x))
+
+
+def test_peer_memory_allreduce_single_rank_and_bounded_wait(cuda_ops, gc_scope):
+    """World of one: the kernel publishes into its own mailbox and sums one slot (identity), several
+    tensors per call, twice in a row (both slot sets).  Then a communicator whose second rank never
+    arrives: the wait must give up after its limit, report KTC_ETIMEOUT, leave the tensors untouched
+    and the device usable."""
+    lib = cuda_ops.lib
+    vals = [D.uniform(n, 70 + i, -1.0, 1.0) for i, n in enumerate((1, 1024, 1024, 5000))]
+    ts = [cuda_ops.createRaw([v.size], v) for v in vals]
+    handle = C.create_string_buffer(L.P2P_HANDLE_BYTES)
+    comm = C.c_uint64(0)
+    L.check(lib.ktc_p2p_create(0, 1, 0, C.byref(comm), handle))
+    L.check(lib.ktc_p2p_connect(comm.value, handle.raw))
+    bufs = (C.c_uint64 * 4)(*[t.storeReference for t in ts])
+    counts = (C.c_int64 * 4)(*[t.size for t in ts])
+    st = C.c_int(-99)
+    for _ in range(3):
+        L.check(lib.ktc_p2p_allreduce_sum(comm.value, bufs, counts, 4))
+    L.check(lib.ktc_p2p_status(comm.value, C.byref(st)))
+    assert st.value == L.KTC_OK
+    for t, v in zip(ts, vals):
+        assert same_bits(t.toArray(), v)
+    too_many = (C.c_int64 * 1)(L.P2P_MAX_FLOATS + 1)
+    big = cuda_ops.createRaw([L.P2P_MAX_FLOATS + 1])
+    assert lib.ktc_p2p_allreduce_sum(comm.value, (C.c_uint64 * 1)(big.storeReference), too_many, 1) == L.KTC_EINVAL
+    L.check(lib.ktc_p2p_destroy(comm.value))
+    assert lib.ktc_p2p_allreduce_sum(comm.value, bufs, counts, 4) == L.KTC_ESTATE
+    # a rank that never arrives
+    L.check(lib.ktc_tune_set(b"p2p_wait_ms", 50))
+    try:
+        L.check(lib.ktc_p2p_create(0, 2, 0, C.byref(comm), handle))
+        L.check(lib.ktc_test_p2p_connect_self(comm.value))
+        L.check(lib.ktc_p2p_allreduce_sum(comm.value, bufs, counts, 4))
+        L.check(lib.ktc_p2p_status(comm.value, C.byref(st)))
+        assert st.value == L.KTC_ETIMEOUT
+        L.check(lib.ktc_p2p_status(comm.value, C.byref(st)))
+        assert st.value == L.KTC_OK                                   # the flag was cleared by the read
+        L.check(lib.ktc_p2p_destroy(comm.value))
+    finally:
+        L.check(lib.ktc_tune_set(b"p2p_wait_ms", 2000))
+    for t, v in zip(ts, vals):
+        assert same_bits(t.toArray(), v)                              # nothing was summed
+    assert same_bits(ts[1].plus(ts[2]).toArray(), vals[1] + vals[2])  # the device still works
