@@ -219,13 +219,14 @@ def run_reference_arm(args):
 # GPU arm
 # ----------------------------------------------------------------------------------------------
 class GpuSweep:
-    def __init__(self, device: int, rank: int, comm=None):
+    def __init__(self, device: int, rank: int, comm=None, collective=None):
         from kten_b200 import _lib as L
         from kten_b200 import datagen as D
         from kten_b200.tensor_operations import CUDATensorOperations
         self.L, self.D = L, D
         self.ops = CUDATensorOperations(device)
         self.lib, self.dev, self.rank, self.comm = self.ops.lib, device, rank, comm
+        self.collective = collective             # object with allreduce_sum(raws), made once the ops exist (set_collective)
         first = rank * N28                       # this rank's shard of the N-times larger batch
         t0 = time.time()
         self.h_in = [self._pinned(N28), self._pinned(N28)]
@@ -243,6 +244,8 @@ class GpuSweep:
         D.normal(N28, 6, 0.0, 1.0, first=first, quantum=16.0, out=self.h_in[0]); self.x4 = mk([N28]); self._up(self.x4, self.h_in[0])
         self.out = mk([N28])
         self.small = mk([65536])
+        self.full_sum_out = mk([1])                   # where the full sum lands (summed across the ranks in place)
+        self.full_sum_e2e = mk([1])
         self.small_host = np.empty(65536, dtype=np.float32)
         self.ops.synchronize()
         self.setup_s = time.time() - t0
@@ -284,9 +287,9 @@ class GpuSweep:
         elif name.startswith("c4.mid."):
             ck(lib.ktc_reduce_axis({"sum": L.SUM, "max": L.MAX}[name[7:]], self.small.storeReference, self.x4.storeReference, 512, 4096, 128))
         else:
-            ck(lib.ktc_reduce_all(L.SUM, self.small.storeReference, self.x4.storeReference, N28))
-            if self.comm is not None:            # the one exchange step of the sharded path
-                ck(lib.ktc_allreduce_sum(self.comm, self.small.storeReference, 0, 1))
+            ck(lib.ktc_reduce_all(L.SUM, self.full_sum_out.storeReference, self.x4.storeReference, N28))
+            if self.collective is not None:      # the one exchange step of the sharded path
+                self.collective.allreduce_sum([self.full_sum_out])
 
     # ---- one op through the public API with HOST buffers (copies inside the timed region) -------
     CHUNK = 1 << 22          # 16 MiB pieces: upload of piece i+1, kernel of piece i and download of piece i-1 overlap
@@ -319,7 +322,7 @@ class GpuSweep:
         ptr = lambda h, off: C.c_void_p(h.ctypes.data + 4 * off)
         if not hasattr(self, "outs"):
             self.outs = [self.out] + [self.ops.createRaw([N28]) for _ in range(7)]      # one result buffer per op of a group
-            self.smalls = [self.small] + [self.ops.createRaw([65536]) for _ in range(6)]
+            self.smalls = [self.small] + [self.ops.createRaw([65536]) for _ in range(5)]
         h2d = d2h = 0
         # ---- contiguous elementwise: a, b -> plus times div pow (a, b), exp log tanh sigmoid (a) ----------------
         va, vb = self._views(self.a2, CH, nch), self._views(self.b2, CH, nch)
@@ -364,12 +367,12 @@ class GpuSweep:
                 ck(lib.ktc_reduce_axis(code, vs_last[k][i], vx[i], r, 4096, 1))
             for k, code in enumerate((L.SUM, L.MAX)):
                 ck(lib.ktc_reduce_axis(code, vs_mid[k][i], vx[i], o, 4096, 128))
-        ck(lib.ktc_reduce_all(L.SUM, self.smalls[6].storeReference, self.x4.storeReference, N28))
-        if self.comm is not None:
-            ck(lib.ktc_allreduce_sum(self.comm, self.smalls[6].storeReference, 0, 1))
+        ck(lib.ktc_reduce_all(L.SUM, self.full_sum_e2e.storeReference, self.x4.storeReference, N28))
+        if self.collective is not None:
+            self.collective.allreduce_sum([self.full_sum_e2e])
         for k in range(6):
             ck(lib.ktc_d2h(ptr(self.small_host, 0), self.smalls[k].storeReference, 0, 65536, OV))
-        ck(lib.ktc_d2h(ptr(self.small_host, 0), self.smalls[6].storeReference, 0, 1, OV))
+        ck(lib.ktc_d2h(ptr(self.small_host, 0), self.full_sum_e2e.storeReference, 0, 1, OV))
         h2d += 4 * N28; d2h += 4 * (6 * 65536 + 1)
         ck(lib.ktc_copy_fence(self.dev))                  # the step ends when its last download has landed
         return h2d, d2h
@@ -383,11 +386,11 @@ class GpuSweep:
         return float(ms.value)
 
 
-def run_sharded_graph(ops, lib, L, D, rank, world, comm, steps, warmup, dist):
+def run_sharded_graph(ops, lib, L, D, rank, world, collective, steps, warmup, dist):
     """The sharded autograd configuration: x[262144,1024] ~ U(-1,1) split by rows over the ranks
     (strong scaling: the global tensor is fixed), w[1,1024] ~ N(0,0.02), b[1024] = 0;
     loss = sum(sigmoid(x*w + b) pow 2), backward for w and b, partials all-reduced."""
-    from kten_b200.sharded import NcclCollective, ShardedSigmoidGraph, shard_rows
+    from kten_b200.sharded import ShardedSigmoidGraph, shard_rows
     rows, cols = 262144, 1024
     first, count = shard_rows(rows, world, rank)
     hx = D.uniform(count * cols, 0, -1.0, 1.0, stream=0, first=first * cols)
@@ -396,7 +399,7 @@ def run_sharded_graph(ops, lib, L, D, rank, world, comm, steps, warmup, dist):
     w = ops.createRaw([1, cols], hw)
     b = ops.createRawFill([cols], 0.0)
     del hx
-    graph = ShardedSigmoidGraph(ops, x, w, b, NcclCollective(ops, comm) if comm is not None else None)
+    graph = ShardedSigmoidGraph(ops, x, w, b, collective)
 
     def one_step():
         with ops.garbageCollector():
@@ -539,6 +542,29 @@ def run_gpu_arm(args):
     L.check(lib.ktc_init(C.byref(n)))
     comm = make_comm(lib, L, dist, rank, world, local) if dist is not None else None
     sweep = GpuSweep(local, rank, comm)
+    collective, collective_name = None, "none (one rank)"
+    if dist is not None:
+        from kten_b200.sharded import NcclCollective, PeerMemoryCollective
+        if args.collective == "p2p":
+            def exchange(mine):
+                everyone = [None] * world
+                dist.all_gather_object(everyone, mine)
+                return everyone
+            try:
+                collective = PeerMemoryCollective(sweep.ops, world, rank, exchange, dist.barrier)
+                collective_name = "one kernel per rank over peer memory (ktc_p2p_allreduce_sum)"
+            except Exception as exc:                      # e.g. CUDA IPC not permitted between these processes
+                sys.stderr.write(f"peer-memory collective unavailable ({exc}); using NCCL\n")
+        agree = [None] * world
+        dist.all_gather_object(agree, collective is not None)
+        if not all(agree):                                # every rank must take the same path
+            if collective is not None:
+                collective.close(barrier=False)           # nothing was exchanged yet; the ranks that failed are not waiting
+            collective = None
+        if collective is None:
+            collective = NcclCollective(sweep.ops, comm)
+            collective_name = "pack + NCCL all-reduce + unpack (ktc_allreduce_sum)"
+    sweep.collective = collective
     spec = sweep_spec()
     names = [s["name"] for s in spec]
     step_bytes = float(sum(s["bytes"] for s in spec))
@@ -607,7 +633,8 @@ def run_gpu_arm(args):
         for r in [sweep.a2, sweep.b2, sweep.a3, sweep.t3, sweep.x4] + getattr(sweep, "outs", [sweep.out]):
             r.release()                               # hand the sweep's buffers back to the pool first
         L.check(lib.ktc_pool_trim(local))
-        sharded = run_sharded_graph(sweep.ops, lib, L, D, rank, world, comm, max(2, min(args.steps, 5)), args.warmup, dist)
+        sharded = run_sharded_graph(sweep.ops, lib, L, D, rank, world, collective, max(2, min(args.steps, 5)), args.warmup, dist)
+        sharded["collective"] = collective_name
 
     other_ops = None
     if args.other_ops and rank == 0 and world == 1:
@@ -616,6 +643,13 @@ def run_gpu_arm(args):
                 r.release()
         L.check(lib.ktc_pool_trim(local))
         other_ops = run_other_ops(sweep.ops, lib, L, D, args.steps)
+
+    collective_error = None
+    if hasattr(collective, "check"):
+        try:
+            collective.check()
+        except TimeoutError as exc:
+            collective_error = str(exc)
 
     # ---- max over ranks -----------------------------------------------------------------------------
     if dist is not None:
@@ -646,7 +680,7 @@ def run_gpu_arm(args):
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": "C2+C3+C4 sweep (contiguous elementwise, broadcast binary, axis/full reductions), one shard per GPU",
                    "elements_per_operand": N28, "ops_per_step": len(names), "algorithmic_bytes_per_step_per_gpu": step_bytes,
-                   "l2": "inputs larger than L2 (every operand >= 1 GiB, L2 is 126 MB)", "parallelism": f"batch-sharded x{world}"},
+                   "l2": "inputs larger than L2 (every operand >= 1 GiB, L2 is 126 MB)", "parallelism": f"batch-sharded x{world}", "collective": collective_name},
         "frac_of_measured_peak": value / world / peak, "frac_of_nominal_8TBs": value / world / NOMINAL_HBM_GBS,
         "gelem_per_s": world * sum(s["elements"] for s in spec) / (ms_per_step * 1e6),
         "gpu_launches": int(launches),
@@ -665,6 +699,8 @@ def run_gpu_arm(args):
         "clocks": clocks,
         "setup_s": round(sweep.setup_s, 1),
     }
+    if collective_error is not None:
+        line["collective_error"] = collective_error
     if sharded is not None:
         line["sharded_graph"] = sharded
     if other_ops is not None:
@@ -682,6 +718,8 @@ def run_gpu_arm(args):
         sys.stdout.flush()
         os.write(json_fd, (json.dumps(line) + "\n").encode())
     if dist is not None:
+        if hasattr(collective, "close"):
+            collective.close()
         if comm is not None:
             lib.ktc_comm_destroy(comm)
         dist.barrier()
@@ -836,6 +874,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--cpu-sample-log2", type=int, default=None, help="log2 of the CPU sample size (default 25 for cpu_baseline, 24 for --impl reference)")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
+    ap.add_argument("--collective", choices=("p2p", "nccl"), default="p2p",
+                    help="N > 1: sum of the partials across ranks by one kernel over peer memory (default) or through NCCL")
     ap.add_argument("--no-sharded-graph", dest="sharded_graph", action="store_false")
     ap.add_argument("--no-other-ops", dest="other_ops", action="store_false",
                     help="skip timing the raw-tensor ops beside the sweep (slices, permutes, gather / scatter)")

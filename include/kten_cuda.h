@@ -314,7 +314,7 @@ KTC_API int ktc_comm_destroy(ktc_comm comm);
  *                    KTC_P2P_MAX_TENSORS tensors, KTC_P2P_MAX_FLOATS floats in total per call.  Every
  *                    rank must make the same sequence of calls.
  *   ktc_p2p_status   waits for the stream; *status = KTC_OK, or KTC_ETIMEOUT if a rank failed to
- *                    arrive within the limit (tunable p2p_wait_ms, default 2000): the kernel then
+ *                    arrive within the limit (tunable p2p_wait_ms, default 10000): the kernel then
  *                    returned without summing, the context stays usable, the communicator does not
  *                    (destroy it).
  * ktc_test_p2p_connect_self wires every peer slot to this rank's own mailbox, so that the absent ranks

@@ -207,7 +207,7 @@ int ktc_p2p_allreduce_sum(ktc_p2p p, const ktc_buf* bufs, const int64_t* counts,
     a.mine = r.mine;
     for (int q = 0; q < r.world; ++q) a.peer[q] = r.peer[q];
     a.world = r.world; a.rank = r.rank; a.epoch = epoch; a.n_bufs = n_bufs;
-    a.limit_ns = (long long)tune("p2p_wait_ms", 2000) * 1000000LL;
+    a.limit_ns = (long long)tune("p2p_wait_ms", 10000) * 1000000LL;
     k_p2p_allreduce<<<1, 1024, 0, d->stream>>>(a);
     count_launch(1);
     cudaError_t e = cudaGetLastError();

@@ -100,10 +100,12 @@ class PeerMemoryCollective:
         if st.value != self._L.KTC_OK:
             raise TimeoutError("peer-memory all-reduce: a rank did not arrive within the time limit")
 
-    def close(self) -> None:
+    def close(self, barrier: bool = True) -> None:
+        """`barrier=False` only where no all-reduce was ever issued (e.g. another rank failed to connect)."""
         if self.comm:
             self.ops.synchronize()
-            self._barrier()                         # nobody frees a mailbox a peer may still write
+            if barrier:
+                self._barrier()                     # nobody frees a mailbox a peer may still write
             self._L.check(self.ops.lib.ktc_p2p_destroy(self.comm))
             self.comm = 0
 
