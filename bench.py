@@ -581,6 +581,22 @@ def run_gpu_arm(args):
     for _ in range(max(args.warmup, 3)):
         run_step()
     barrier()
+    if hasattr(collective, "check"):
+        # the warm-up steps went through the peer-memory exchange: if any rank saw a wait run out, every rank
+        # switches to the NCCL path before anything is timed
+        try:
+            collective.check()
+            healthy = True
+        except TimeoutError:
+            healthy = False
+        verdicts = [None] * world
+        dist.all_gather_object(verdicts, healthy)
+        if not all(verdicts):
+            collective.close()
+            collective = NcclCollective(sweep.ops, comm)
+            collective_name = "pack + NCCL all-reduce + unpack (ktc_allreduce_sum); the peer-memory exchange timed out in warm-up"
+            sweep.collective = collective
+            barrier()
 
     # ---- timed region: exactly K steps, device-timed on the launching stream ----------------------
     sampler = ClockSampler(local)
