@@ -16,7 +16,7 @@
 // handles (the caller carries the 64-byte handles between processes).  Two slot sets alternate by
 // call so that a rank that runs ahead cannot overwrite values a slower rank is still reading: a
 // rank can only be one call ahead, because finishing a call needs every peer's flag for it.
-// No multicast and no collective library are involved.
+// Only ordinary loads and stores on mapped peer memory are used; no collective library is involved.
 #include "ktc_internal.hpp"
 
 #include <cstring>
