@@ -74,6 +74,12 @@ internal object KtcNative {
     val gatherAxis = handle("ktc_gather_axis", JAVA_INT, JAVA_LONG, JAVA_LONG, ADDRESS, JAVA_LONG, ADDRESS, JAVA_INT, JAVA_INT)
     val scatterAxisNd = handle("ktc_scatter_axis_nd", JAVA_INT, JAVA_INT, JAVA_LONG, ADDRESS, JAVA_LONG, ADDRESS, JAVA_LONG, ADDRESS, JAVA_INT, JAVA_INT, JAVA_FLOAT)
     val indexSelect = handle("ktc_index_select", JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG)
+    // sum of a few small tensors across the GPUs of one box, one kernel per rank over peer memory
+    val p2pCreate = handle("ktc_p2p_create", JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT, ADDRESS, ADDRESS)
+    val p2pConnect = handle("ktc_p2p_connect", JAVA_INT, JAVA_LONG, ADDRESS)
+    val p2pAllreduceSum = handle("ktc_p2p_allreduce_sum", JAVA_INT, JAVA_LONG, ADDRESS, ADDRESS, JAVA_INT)
+    val p2pStatus = handle("ktc_p2p_status", JAVA_INT, JAVA_LONG, ADDRESS)
+    val p2pDestroy = handle("ktc_p2p_destroy", JAVA_INT, JAVA_LONG)
     val indexAdd = handle("ktc_index_add", JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_FLOAT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG)
 
     /** KTC_EINVAL -> IllegalArgumentException, KTC_ESTATE -> IllegalStateException, KTC_ENOMEM -> OutOfMemoryError. */
