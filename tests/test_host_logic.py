@@ -78,3 +78,50 @@ def test_generator_distributions():
     assert np.array_equal(x * 16, np.rint(x * 16))               # multiples of 1/16: ties will occur
     u = D.uniform(1 << 20, 4, -1.0, 1.0)
     assert abs(float(u.mean())) < 5e-3 and abs(float(u.var()) - 1.0 / 3.0) < 5e-3
+
+
+# ---- shape algebra of indexing and data movement (ShapeFunctions.kt:85-129, 203-293, 346-371) ----------------
+def test_index_normalisation_and_indexed_shapes():
+    s = [4, 5, 6]
+    assert SF.normalized_indexed_shape(s, [1]) == ([1], [5, 6])
+    assert SF.normalized_indexed_shape(s, [-1, -5, 2]) == ([3, 0, 2], [1])          # a full index selects a [1] tensor
+    for bad in ([4], [0, 5], [0, -6], [0, 0, 0, 0]):
+        with pytest.raises(ValueError):
+            SF.normalize_index(s, bad)
+    assert SF.normalized_indexed_shape_ranges(s, [(1, 2), None]) == ([(1, 2), (0, 4)], [2, 5, 6])
+    assert SF.normalized_indexed_shape_ranges(s, [(0, -1), (-2, -1), (3, 3)]) == ([(0, 3), (3, 4), (3, 3)], [4, 2, 1])
+    assert SF.normalize_index_ranges(s, [slice(1, 3), slice(None), slice(2, None)]) == [(1, 2), (0, 4), (2, 5)]
+    assert SF.normalize_index_ranges(s, [range(0, 4), slice(0, -1)]) == [(0, 3), (0, 3)]
+    for bad in ([(2, 1)], [(0, 4)], [(-5, 0)], [None, None, None, None], [slice(0, 4, 2)]):
+        with pytest.raises(ValueError):
+            SF.normalize_index_ranges(s, bad)
+
+
+def test_permute_transpose_concat_shapes():
+    assert SF.permute([2, 3, 4], [2, 0, 1]) == [4, 2, 3]
+    for bad in ([0, 1], [0, 1, 1], [0, 1, 3]):
+        with pytest.raises(ValueError):
+            SF.permute([2, 3, 4], bad)
+    assert SF.transpose_normalize_axes([2, 3, 4], 0, -1) == ([4, 3, 2], 0, 2)
+    with pytest.raises(ValueError):
+        SF.transpose_normalize_axes([2, 3, 4], 1, -2)
+    assert SF.concat_shapes([[2, 3], [1, 3], [4, 3]], 0) == [7, 3]
+    assert SF.concat_shapes([[2, 3], [2, 5]], -1) == [2, 8]
+    for bad in ([[2, 3], [2, 4]], [[2, 3], [2, 3, 1]]):
+        with pytest.raises(ValueError):
+            SF.concat_shapes(bad, 0)
+    assert SF.strides_of([2, 3, 4]) == [12, 4, 1] and SF.strides_of([]) == []
+
+
+def test_index_op_shape_checks():
+    assert SF.index_select_norm_axis_shape([3, 4, 5], -2, [7]) == (1, [3, 7, 5])
+    with pytest.raises(ValueError):
+        SF.index_select_norm_axis_shape([3, 4, 5], 0, [2, 2])
+    assert SF.index_add_check_shapes_norm_axis([3, 4, 5], 1, [2], [3, 2, 5]) == 1
+    for idx_shape, src_shape in (([2, 1], [3, 2, 5]), ([2], [3, 3, 5]), ([2], [3, 2])):
+        with pytest.raises(ValueError):
+            SF.index_add_check_shapes_norm_axis([3, 4, 5], 1, idx_shape, src_shape)
+    assert SF.normalized_axis_scatter([3, 5], -1, [2, 9], [2, 9]) == 1              # the axis itself may be longer than the target
+    for idx_shape, src_shape in (([2], [2]), ([4, 5], [4, 5]), ([2, 5], [2, 4])):
+        with pytest.raises(ValueError):
+            SF.normalized_axis_scatter([3, 5], 1, idx_shape, src_shape)
