@@ -1,0 +1,211 @@
+"""A host stand-in for libkten_cuda.so, for CPU tests of the host logic only.
+
+The deferred-expression layer (kten_b200.lazy, raw_tensor._Cell, tensor_operations) is pure
+host code: which calls it makes, in which order, with which buffers, decides whether aliases,
+in-place writes and side outputs keep the semantics of the eager backend.  This module
+implements the few C-ABI entry points that logic drives -- buffers, copies, the elementwise
+calls, the full reduction and ktc_expr_eval (a numpy interpreter of the program encoding) --
+with the CPU oracle's arithmetic, so that the same script can be run call by call and deferred
+on a machine without a GPU and the two results compared.  It is test infrastructure: nothing in
+the product imports it, and it says nothing about the CUDA kernels.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from kten_b200 import _lib as L
+from kten_b200.tensor_operations import CUDATensorOperations
+from oracle import oracle as O
+
+BIN = {L.PLUS: O.PLUS, L.MINUS: O.MINUS, L.TIMES: O.TIMES, L.DIV: O.DIV, L.POW: O.POW}
+
+
+def _ints(ptr, n):
+    return [int(ptr[i]) for i in range(n)]
+
+
+class FakeLib:
+    def __init__(self):
+        self.bufs = {}          # handle -> [ndarray, refcount]
+        self.next = 1
+        self.launches = 0
+        self.expr_calls = 0
+        self.calls = []         # names of compute calls, in order
+        self.error = b""
+
+    # ---- buffers -----------------------------------------------------------------------------
+    def _get(self, h):
+        rec = self.bufs.get(int(h))
+        if rec is None or rec[1] <= 0:
+            raise AssertionError(f"use of a released or unknown buffer {h}")
+        return rec[0]
+
+    def ktc_alloc(self, dev, n, ref):
+        h = self.next
+        self.next += 1
+        self.bufs[h] = [np.full(int(n), np.nan, dtype=np.float32), 1]      # fresh memory holds garbage
+        ref._obj.value = h
+        return 0
+
+    def ktc_retain(self, h):
+        self._get(h)
+        self.bufs[int(h)][1] += 1
+        return 0
+
+    def ktc_release(self, h):
+        self._get(h)
+        self.bufs[int(h)][1] -= 1
+        return 0
+
+    def live_buffers(self):
+        return sum(1 for a, c in self.bufs.values() if c > 0)
+
+    def ktc_last_error(self):
+        return self.error
+
+    def ktc_launch_count(self):
+        return self.launches
+
+    def ktc_sync(self, dev):
+        return 0
+
+    def ktc_h2d(self, h, off, src, n, mode):
+        addr = src.value if isinstance(src, C.c_void_p) else C.cast(src, C.c_void_p).value
+        self._get(h)[off:off + n] = np.ctypeslib.as_array((C.c_float * n).from_address(addr))
+        return 0
+
+    def ktc_d2h(self, dst, h, off, n, mode):
+        addr = dst.value if isinstance(dst, C.c_void_p) else C.addressof(dst)
+        np.ctypeslib.as_array((C.c_float * n).from_address(addr))[:] = self._get(h)[off:off + n]
+        return 0
+
+    def ktc_d2d(self, dst, doff, src, soff, n):
+        self._get(dst)[doff:doff + n] = self._get(src)[soff:soff + n]
+        return 0
+
+    def ktc_fill(self, h, off, n, v):
+        self._get(h)[off:off + n] = np.float32(v)
+        self.launches += 1
+        return 0
+
+    # ---- elementwise calls and the full reduction --------------------------------------------------
+    def _note(self, name):
+        self.calls.append(name)
+        self.launches += 1
+
+    def ktc_binary(self, op, out, a, b, n):
+        self._note("binary")
+        self._get(out)[:n] = O.binary_same(BIN[op], self._get(a)[:n].copy(), self._get(b)[:n].copy())
+        return 0
+
+    def ktc_binary_inplace(self, op, a, b, n):
+        return self.ktc_binary(op, a, a, b, n)
+
+    def ktc_binary_bcast(self, op, out, a, sa, na, b, sb, nb):
+        self._note("binary_bcast")
+        sha, shb = _ints(sa, na), _ints(sb, nb)
+        res, cs = O.binary(BIN[op], self._get(a)[:int(np.prod(sha))], sha, self._get(b)[:int(np.prod(shb))], shb)
+        self._get(out)[:res.size] = res
+        return 0
+
+    def ktc_scalar(self, op, out, a, s, n, scalar_first):
+        self._note("scalar")
+        self._get(out)[:n] = O.scalar(BIN[op], self._get(a)[:n].copy(), float(s), scalar_first=bool(scalar_first))
+        return 0
+
+    def ktc_scalar_inplace(self, op, a, s, n):
+        return self.ktc_scalar(op, a, a, s, n, 0)
+
+    def ktc_unary(self, op, out, a, n):
+        self._note("unary")
+        self._get(out)[:n] = O.unary(op, self._get(a)[:n].copy())
+        return 0
+
+    def ktc_clamp(self, out, a, lo, hi, n):
+        self._note("clamp")
+        self._get(out)[:n] = O.clamp(self._get(a)[:n].copy(), lo, hi)
+        return 0
+
+    def ktc_compare_scalar(self, op, out, a, v, n):
+        self._note("compare")
+        self._get(out)[:n] = O.compare(op, self._get(a)[:n].copy(), float(v))
+        return 0
+
+    def ktc_broadcast_to(self, out, so, no, a, sa, na):
+        self._note("broadcast_to")
+        sho, sha = _ints(so, no), _ints(sa, na)
+        self._get(out)[:int(np.prod(sho))] = O.broadcast_to(self._get(a)[:int(np.prod(sha))], sha, sho)
+        return 0
+
+    def ktc_reduce_all(self, op, out, a, n):
+        self._note("reduce_all")
+        self._get(out)[0] = O.reduce_all(op, self._get(a)[:n].copy())
+        return 0
+
+    def ktc_reduce_axis(self, op, out, a, outer, length, inner):
+        self._note("reduce_axis")
+        self._get(out)[:outer * inner] = O.aggregate(op, self._get(a)[:outer * length * inner].copy(), outer, length, inner)
+        return 0
+
+    # ---- the fused expression call: the program encoding interpreted with the oracle's arithmetic ----
+    def ktc_expr_eval(self, code, n_code, imm, n_imm, shape, ndim, leaves, lshapes, n_leaves, stores, n_stores, sink, sink_out, mean):
+        shp = _ints(shape, ndim)
+        if shp[-1] % 4 != 0 or len([d for d in shp if d != 1]) > 3:
+            self.error = b"not fusable (stand-in rule: innermost extent must be a multiple of 4, at most 3 non-unit dims)"
+            return L.KTC_ENOTSUP
+        self.expr_calls += 1
+        self._note("expr_eval")
+        total = int(np.prod(shp))
+        regs = [None] * L.EXPR_REGS
+        acc = None
+        flat = lambda v: np.ascontiguousarray(v, dtype=np.float32).reshape(-1)
+        for pc in range(n_code):
+            w = int(code[pc])
+            op, d, a, b, k = w & 0xFF, (w >> 8) & 0xF, (w >> 12) & 0xF, (w >> 16) & 0xF, w >> 20
+            if op == L.X_LOAD:
+                ls = _ints(lshapes, (k + 1) * ndim)[k * ndim:]
+                src = self._get(leaves[k])[:int(np.prod(ls))]
+                regs[d] = flat(np.broadcast_to(src.reshape(ls), shp))
+            elif op == L.X_CONST:
+                regs[d] = np.full(total, imm[k], np.float32)
+            elif op in (L.X_ADD, L.X_SUB, L.X_MUL, L.X_DIV, L.X_POW):
+                o = {L.X_ADD: O.PLUS, L.X_SUB: O.MINUS, L.X_MUL: O.TIMES, L.X_DIV: O.DIV, L.X_POW: O.POW}[op]
+                regs[d] = O.binary_same(o, regs[a], regs[b])
+            elif op in (L.X_NEG, L.X_RCP, L.X_EXP, L.X_LOG, L.X_TANH, L.X_SIGMOID):
+                o = {L.X_NEG: O.NEG, L.X_RCP: O.RECIPROCAL, L.X_EXP: O.EXP, L.X_LOG: O.LOG, L.X_TANH: O.TANH, L.X_SIGMOID: O.SIGMOID}[op]
+                regs[d] = O.unary(o, regs[a])
+            elif op == L.X_SQUARE:
+                regs[d] = O.binary_same(O.TIMES, regs[a], regs[a])
+            elif op == L.X_CLAMP:
+                regs[d] = O.clamp(regs[a], imm[k], imm[k + 1])
+            elif L.X_CMP_LT <= op <= L.X_CMP_GTE:
+                regs[d] = O.compare(op - L.X_CMP_LT, regs[a], float(imm[k]))
+            elif op == L.X_STORE:
+                self._get(stores[k])[:total] = regs[a]
+            elif op == L.X_ACC:
+                acc = regs[a].astype(np.float64)
+            else:
+                raise AssertionError(f"bad opcode {op}")
+        if sink == L.EXPR_SUM_ALL:
+            self._get(sink_out)[0] = np.float32(acc.sum() / (total if mean else 1))
+        elif sink == L.EXPR_SUM_ROWS:
+            self._get(sink_out)[:shp[-1]] = acc.reshape(-1, shp[-1]).sum(axis=0).astype(np.float32)
+        return 0
+
+
+def make_ops() -> CUDATensorOperations:
+    """A CUDATensorOperations whose library is the stand-in above (no device, no shared object)."""
+    import threading
+    ops = object.__new__(CUDATensorOperations)
+    ops.lib = FakeLib()
+    ops.device, ops.deviceName, ops.totalMemory, ops.smCount = 0, "host stand-in", 0, 0
+    ops.platformKey = "CUDA - host stand-in"
+    ops._tls = threading.local()
+    ops.epsilon = 1e-7
+    ops.lazy = False
+    ops._deps, ops._deps_purge_at = {}, 1024
+    ops.recomputeLimit, ops.storeCost = 2, 8
+    ops.fusedEvaluations = ops.unfusedEvaluations = 0
+    return ops
