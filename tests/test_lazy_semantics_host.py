@@ -142,3 +142,32 @@ def test_programs_the_kernel_declines_are_split():
     for x, y in zip(eager, lazy):
         assert same_bits(x, y)
     assert stats[1][4] > 0 and stats[1][0] == 0
+
+
+def test_sharded_graph_step_deferred_equals_call_by_call():
+    """The config-5 autograd step through the stand-in: same loss and gradients in both execution modes, three fused
+    programs with a sum plus the in-place gradient accumulation instead of two dozen calls, nothing left allocated."""
+    from kten_b200.sharded import ShardedSigmoidGraph
+    rows, cols = 32, 16
+    x, w, b = D.uniform(rows * cols, 0, -1.0, 1.0), D.normal(cols, 0, 0.0, 0.5, stream=1), D.uniform(cols, 0, -0.1, 0.1, stream=2)
+    res = []
+    for mode in (False, True):
+        ops = make_ops()
+        ops.lazy = mode
+        with ops.garbageCollector():
+            g = ShardedSigmoidGraph(ops, ops.createRaw([rows, cols], x), ops.createRaw([1, cols], w), ops.createRaw([cols], b))
+            for _ in range(2):
+                n0 = len(ops.lib.calls)
+                loss, gw, gb = g.step()
+                vals = (loss.toArray().copy(), gw.toArray().copy(), gb.toArray().copy())
+                g.release_step()
+            res.append((vals, ops.lib.calls[n0:]))
+            for v in (g.x, g.w, g.b):
+                v.getRawValue().release()
+            g.w.gradient.release(); g.b.gradient.release()
+        gc.collect()
+        assert ops.lib.live_buffers() == 0
+    (ve, ce), (vl, cl) = res
+    for a, c in zip(ve, vl):
+        assert np.allclose(a, c, rtol=1e-6, atol=1e-6)
+    assert ce.count("expr_eval") == 0 and cl.count("expr_eval") == 3 and len(cl) < len(ce) / 2
