@@ -137,20 +137,24 @@ class Program:
         self.leaves: List[Tuple[int, List[int]]] = []       # (handle, right-aligned shape)
         self.n_stores = 0
         self.free = list(range(L.EXPR_REGS - 1, -1, -1))
+        self.imm_src: List[Tuple[int, int]] = []             # per immediate: (position of its node in the order, index in node.imm)
+        self.leaf_src: List[int] = []                        # per leaf: position of the (first) stored node it came from
+        self.order: List["Node"] = []
 
     def emit(self, op, d=0, a=0, b=0, k=0):
         if len(self.code) >= L.EXPR_MAX_INSTR:
             raise NotFusable("program too long")
         self.code.append(op | (d << 8) | (a << 12) | (b << 16) | (k << 20))
 
-    def imm_index(self, values) -> int:
+    def imm_index(self, values, src: int = -1) -> int:
         if len(self.imm) + len(values) > L.EXPR_MAX_IMM:
             raise NotFusable("too many immediates")
         k = len(self.imm)
         self.imm.extend(values)
+        self.imm_src.extend((src, j) for j in range(len(values)))
         return k
 
-    def leaf_index(self, handle, shape) -> int:
+    def leaf_index(self, handle, shape, src: int = -1) -> int:
         nd = len(self.shape)
         padded = [1] * (nd - len(shape)) + list(shape)
         if len(padded) != nd:
@@ -161,6 +165,7 @@ class Program:
         if len(self.leaves) >= L.EXPR_MAX_LEAVES:
             raise NotFusable("too many leaves")
         self.leaves.append((handle, padded))
+        self.leaf_src.append(src)
         return len(self.leaves) - 1
 
     def alloc(self) -> int:
@@ -226,13 +231,63 @@ def compile_program(shape, stores: Sequence[Node], acc: Optional[Node], recomput
     for is stored on the way when it was already computed `recompute_limit` times, or when
     recomputing it from memory would cost `store_cost` or more (both 0: nothing is stored but what
     was asked for).  Raises NotFusable."""
-    prog = Program(shape)
     sinks = [strip(n) for n in stores] + ([strip(acc)] if acc is not None else [])
     order, uses = _toposort(sinks)
+    full_volume = SF.to_store_size(shape)
+    # The program depends on the structure of the DAG (operations, sharing, which values are in memory and which
+    # leaves are the same buffer) and on the per-node facts the side-output rule looks at -- not on buffer handles
+    # or constants.  Graphs are rebuilt with fresh nodes every step, so the compiled form is cached by that
+    # structure and re-bound to the current nodes: immediates, leaf handles and store nodes are looked up by
+    # position in the topological order.
+    pos = {n: i for i, n in enumerate(order)}
+    sig, first_leaf = [], {}
+    for i, n in enumerate(order):
+        if n.buf is not None:
+            sig.append((0, tuple(n.shape), first_leaf.setdefault((n.buf.handle, tuple(n.shape)), i)))
+        elif n.kind == "const":
+            sig.append(1)
+        else:
+            cell = n.owner() if n.owner is not None else None
+            waiting = cell is not None and cell.store is None and cell.node is n and SF.to_store_size(n.shape) == full_volume
+            sig.append((n.kind, n.op, len(n.imm), tuple([pos[strip(a)] for a in n.args]), waiting,
+                        recompute_limit > 0 and n.evals >= recompute_limit))
+    key = (tuple(shape), tuple([pos[strip(n)] for n in stores]), pos[strip(acc)] if acc is not None else -1,
+           recompute_limit, store_cost, tuple(sig))
+    hit = _PROGRAM_CACHE.get(key)
+    if hit is not None:
+        if hit is _NOT_FUSABLE:
+            raise NotFusable("not fusable (cached)")
+        code, imm_src, leaf_plan, store_plan, n_requested = hit
+        prog = Program(shape)
+        prog.code = code                                     # shared, never modified
+        prog.imm = [order[p].imm[j] for p, j in imm_src]
+        prog.leaves = [(order[p].buf.handle, padded) for p, padded in leaf_plan]
+        prog.n_stores = len(store_plan)
+        prog.order = order
+        return prog, [order[p] for p in store_plan], n_requested
+    try:
+        prog, store_nodes, n_requested = _compile(shape, stores, acc, recompute_limit, store_cost, sinks, order, uses, pos, full_volume)
+    except NotFusable:
+        if len(_PROGRAM_CACHE) < _PROGRAM_CACHE_MAX:
+            _PROGRAM_CACHE[key] = _NOT_FUSABLE
+        raise
+    if len(_PROGRAM_CACHE) < _PROGRAM_CACHE_MAX:
+        _PROGRAM_CACHE[key] = (prog.code, list(prog.imm_src), [(p, padded) for p, (_, padded) in zip(prog.leaf_src, prog.leaves)],
+                               [pos[n] for n in store_nodes], n_requested)
+    return prog, store_nodes, n_requested
+
+
+_PROGRAM_CACHE: Dict[tuple, object] = {}
+_PROGRAM_CACHE_MAX = 4096
+_NOT_FUSABLE = object()
+
+
+def _compile(shape, stores, acc, recompute_limit, store_cost, sinks, order, uses, pos, full_volume):
+    """The uncached compilation: side-output choice, register allocation, emission."""
+    prog = Program(shape)
     reg: Dict[Node, int] = {}
     store_nodes: List[Node] = [strip(n) for n in stores]
     n_requested = len(store_nodes)
-    full_volume = SF.to_store_size(shape)
     acc_node = strip(acc) if acc is not None else None
     # Side outputs.  Recomputing a short chain from an operand that is read anyway costs no memory
     # traffic, so cheap values are recomputed (a bounded number of times); a value behind a
@@ -274,10 +329,10 @@ def compile_program(shape, stores: Sequence[Node], acc: Optional[Node], recomput
     for n in order:
         if n.stored():
             d = prog.alloc()
-            prog.emit(L.X_LOAD, d, k=prog.leaf_index(n.buf.handle, n.shape))
+            prog.emit(L.X_LOAD, d, k=prog.leaf_index(n.buf.handle, n.shape, pos[n]))
         elif n.kind == "const":
             d = prog.alloc()
-            prog.emit(L.X_CONST, d, k=prog.imm_index([n.imm[0]]))
+            prog.emit(L.X_CONST, d, k=prog.imm_index([n.imm[0]], pos[n]))
         else:
             children = [strip(a) for a in n.args]
             srcs = [reg[c] for c in children]
@@ -291,9 +346,9 @@ def compile_program(shape, stores: Sequence[Node], acc: Optional[Node], recomput
             elif n.kind == "square":
                 prog.emit(L.X_SQUARE, d, srcs[0])
             elif n.kind == "clamp":
-                prog.emit(L.X_CLAMP, d, srcs[0], k=prog.imm_index(list(n.imm)))
+                prog.emit(L.X_CLAMP, d, srcs[0], k=prog.imm_index(list(n.imm), pos[n]))
             elif n.kind == "cmp":
-                prog.emit(CMP_X[n.op], d, srcs[0], k=prog.imm_index([n.imm[0]]))
+                prog.emit(CMP_X[n.op], d, srcs[0], k=prog.imm_index([n.imm[0]], pos[n]))
             else:
                 raise NotFusable(f"unknown node kind {n.kind}")
         reg[n] = d

@@ -22,6 +22,7 @@ from typing import List, Optional, Sequence
 import numpy as np
 
 from . import _lib as L
+from . import lazy
 from . import shape_functions as SF
 
 
@@ -120,7 +121,6 @@ class CUDARawTensor:
 
     def _as_node(self):
         """This tensor as an operand of a deferred expression."""
-        from . import lazy
         if self._released:
             raise RuntimeError("Raw tensor already released")
         if self._store is None:
@@ -194,7 +194,6 @@ class CUDARawTensor:
         L.check(self.ops.lib.ktc_binary_inplace(op, self._buf(), other._buf(), self.size))
 
     def _scalar_node(self, op: int, s: float, scalar_first: bool):
-        from . import lazy
         me = self._as_node()
         if op == L.POW and not scalar_first and float(s) == 2.0:
             return "square", 0, (me,)
