@@ -112,9 +112,8 @@ class Node:
         self.args = ()
         for anc in self.ancestors():
             anc.leaves.add(buf.handle)
-            cell = anc.owner() if anc.owner is not None else None
-            if cell is not None:
-                registry.setdefault(buf.handle, weakref.WeakSet()).add(cell)
+            if anc.owner is not None and anc.owner() is not None:
+                registry.setdefault(buf.handle, []).append(anc.owner)
 
 
 def leaf(lib, handle: int, shape) -> Node:

@@ -70,7 +70,7 @@ class CUDATensorOperations:
         self.epsilon = 1e-7                 # PlatformProvider.epsilon (PlatformProvider.kt:12): eq / neq tolerance
         # deferred elementwise expressions (kten_b200.lazy): off = every call runs at once, like kten-jvm
         self.lazy = False
-        self._deps = {}                     # buffer handle -> WeakSet of storage cells whose pending expressions read it
+        self._deps = {}                     # buffer handle -> weak references to the storage cells whose pending expressions read it
         self._deps_purge_at = 1024
         self.recomputeLimit = 2             # a pending value is recomputed at most this often before it is stored
         self.storeCost = 8                  # ... unless recomputing costs this much (a transcendental): stored at once
@@ -134,11 +134,18 @@ class CUDATensorOperations:
     # handle to the cells whose pending expressions read it, so that an in-place write to the buffer
     # can evaluate them first.
     def _register(self, cell, node) -> None:
-        node.owner = weakref.ref(cell)
+        ref = node.owner = weakref.ref(cell)
+        deps = self._deps
         for h in node.leaves:
-            self._deps.setdefault(h, weakref.WeakSet()).add(cell)
-        if len(self._deps) > self._deps_purge_at:
-            self._deps = {h: ws for h, ws in self._deps.items() if len(ws)}
+            refs = deps.get(h)
+            if refs is None:
+                deps[h] = [ref]
+            else:
+                refs.append(ref)
+                if len(refs) > 64 and (len(refs) & (len(refs) - 1)) == 0:      # at powers of two: drop the dead ones
+                    deps[h] = [r for r in refs if r() is not None]
+        if len(deps) > self._deps_purge_at:
+            self._deps = {h: live for h, live in ((h, [r for r in refs if r() is not None]) for h, refs in deps.items()) if live}
             self._deps_purge_at = max(1024, 2 * len(self._deps))
 
     def _deferred(self, kind, shape, op, args, imm=()) -> CUDARawTensor:
@@ -192,11 +199,12 @@ class CUDATensorOperations:
                 L.check(self.lib.ktc_binary_inplace(op, h, hb, n))
 
     def _flush_dependents(self, handle: int) -> None:
-        cells = self._deps.pop(handle, None)
-        if not cells:
+        refs = self._deps.pop(handle, None)
+        if not refs:
             return
-        for cell in list(cells):
-            if cell.store is None and cell.node is not None and cell.share > 0 and handle in cell.node.leaves:
+        for ref in refs:
+            cell = ref()
+            if cell is not None and cell.store is None and cell.node is not None and cell.share > 0 and handle in cell.node.leaves:
                 self._materialize_cell(cell)
 
     def _alloc_handle(self, n: int) -> int:
