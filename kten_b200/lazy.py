@@ -22,7 +22,10 @@ Rules that keep the semantics of the eager backend:
   * an interior node is recomputed inside at most `ops.recomputeLimit` programs (recomputing a
     short chain from an operand that is read anyway costs no memory traffic); the next
     evaluation, if its tensor is still alive, stores it as a side output and later programs
-    read it from memory.
+    read it from memory; a value behind a transcendental (`ops.storeCost`) is stored by the
+    first program that computes it, since that program is issue-bound and the store rides along;
+  * compiled programs are cached by the structure of the expression DAG, so a training step that
+    rebuilds the same graph with fresh tensors pays for register allocation once.
 Whatever the kernel does not fuse (more than three collapsed dimensions, an innermost
 extent that is not a multiple of four, programs beyond its size limits) falls back to
 the library's separate calls -- never to the host.
