@@ -10,7 +10,8 @@
 //   * k_transpose_tiled  when the two sides are contiguous along DIFFERENT axes (transpose,
 //                        permutes that move the innermost axis) a 64x64 tile goes through shared
 //                        memory so that both the read and the write are coalesced;
-//   * k_gather_axis / k_index_select   one thread per output element;
+//   * k_gather_axis / k_index_select   one thread per output element (or per four); a gather along the last
+//                        axis stages each input row in shared memory so that DRAM sees every element once;
 //   * k_scatter_axis_nd / k_index_add  one thread per column (all coordinates but the axis),
 //                        sequential along the axis: the reference's loops are sequential in the
 //                        index position (JVM:234-246, 508-516), so duplicates resolve in the same
@@ -28,6 +29,8 @@ struct NdArgs {
     int64_t shape[KTC_MAX_DIMS], dstr[KTC_MAX_DIMS], sstr[KTC_MAX_DIMS];
     int64_t total;
 };
+
+__device__ __forceinline__ bool aligned16_dev(const void* p) { return (reinterpret_cast<unsigned long long>(p) & 15ull) == 0; }
 
 inline int finish(const char* what) {
     count_launch(1);
@@ -161,6 +164,41 @@ __global__ void __launch_bounds__(256) k_gather_axis3(float* __restrict__ out, c
     }
     if (bad) { *err = 1; return; }
     __stcs(reinterpret_cast<float4*>(out) + t, make_float4(res[0], res[1], res[2], res[3]));
+}
+
+// gather along the LAST axis with rows that fit in shared memory: one CTA per row stages the input row
+// with coalesced loads, then serves the row's random reads from shared memory, so DRAM sees every input,
+// index and output element exactly once (the generic kernels above read 32-byte sectors for 4-byte values)
+__global__ void __launch_bounds__(512) k_gather_lastaxis_smem(float* __restrict__ out, const float* __restrict__ in, const float* __restrict__ index,
+                                                              int A_in, int A_idx, int* err) {
+    extern __shared__ float row[];
+    const int64_t o = blockIdx.x;
+    const float* src = in + o * A_in;
+    const float* idx = index + o * A_idx;
+    float* dst = out + o * A_idx;
+    if ((A_in & 3) == 0 && aligned16_dev(src)) {
+        for (int i = threadIdx.x; i < A_in / 4; i += 512) reinterpret_cast<float4*>(row)[i] = __ldcs(reinterpret_cast<const float4*>(src) + i);
+    } else {
+        for (int i = threadIdx.x; i < A_in; i += 512) row[i] = src[i];
+    }
+    __syncthreads();
+    bool bad = false;
+    if ((A_idx & 3) == 0 && aligned16_dev(idx) && aligned16_dev(dst)) {
+        for (int k = threadIdx.x; k < A_idx / 4; k += 512) {
+            const float4 iv = __ldcs(reinterpret_cast<const float4*>(idx) + k);
+            const int j0 = (int)iv.x, j1 = (int)iv.y, j2 = (int)iv.z, j3 = (int)iv.w;
+            const bool ok = (unsigned)j0 < (unsigned)A_in && (unsigned)j1 < (unsigned)A_in && (unsigned)j2 < (unsigned)A_in && (unsigned)j3 < (unsigned)A_in;
+            if (!ok) { bad = true; continue; }
+            __stcs(reinterpret_cast<float4*>(dst) + k, make_float4(row[j0], row[j1], row[j2], row[j3]));
+        }
+    } else {
+        for (int k = threadIdx.x; k < A_idx; k += 512) {
+            const int j = (int)idx[k];
+            if ((unsigned)j >= (unsigned)A_in) { bad = true; continue; }
+            dst[k] = row[j];
+        }
+    }
+    if (bad) *err = 1;
 }
 
 // index select with a vectorisable inner extent: a thread moves four float4 of the output, 256 apart,
@@ -466,6 +504,16 @@ int launch_gather_axis(Device* d, float* out, const float* in, const int64_t* in
         if (i < axis) outer *= index_shape[i]; else inner *= index_shape[i];
     }
     const int64_t in_total = outer * in_shape[axis] * inner;
+    // last axis, rows of 4 KB ... 160 KB: one CTA per row, the row staged in shared memory
+    if (covers && inner == 1 && in_shape[axis] >= 1024 && in_shape[axis] <= 40960 && index_shape[axis] < (1LL << 31) &&
+        outer <= 0x7fffffffLL && tune("gather_smem", 1) != 0) {
+        const size_t smem = (size_t)in_shape[axis] * sizeof(float);
+        if (smem > 48 * 1024)                                       // per device: cheap enough to repeat
+            KTC_CUDA(cudaFuncSetAttribute(k_gather_lastaxis_smem, cudaFuncAttributeMaxDynamicSharedMemorySize, 40960 * (int)sizeof(float)));
+        k_gather_lastaxis_smem<<<(int)outer, 512, smem, d->stream>>>(out, in, index, (int)in_shape[axis], (int)index_shape[axis], d->err_flag);
+        KTC_TRY(finish("gather_lastaxis_smem"));
+        return take_index_error(d, "Gather", a.t_axis_len, axis);
+    }
     if (covers && a.total % 4 == 0 && aligned16(index) && aligned16(out) && tune("index_force_generic", 0) == 0) {
         const int64_t total4 = a.total / 4, grid = grid_of(total4, 256);
         if (grid > 0x7fffffffLL) return fail(KTC_ENOTSUP, "tensor too large for one launch");

@@ -210,6 +210,25 @@ def test_gather_scatter_index_ops(cuda_ops, gc_scope):
     assert same_bits(g.toArray(), o.toArray())
 
 
+@pytest.mark.parametrize("shape,idx_cols", [([37, 2048], 2048), ([5, 1027], 3001), ([3, 4, 4096], 512), ([2, 40960], 8)])
+def test_gather_along_the_last_axis_with_long_rows(cuda_ops, gc_scope, shape, idx_cols):
+    """Rows of 4 KB and more are staged in shared memory by one CTA each; same results as the generic kernel."""
+    both = (cuda_ops, ORACLE)
+    g, o = pair(both, shape, 111)
+    ishape = shape[:-1] + [idx_cols]
+    gi, oi = index_tensor(both, ishape, shape[-1], 112)
+    want = o.gather(-1, oi).toArray()
+    assert same_bits(g.gather(-1, gi).toArray(), want)
+    L.check(cuda_ops.lib.ktc_tune_set(b"gather_smem", 0))
+    try:
+        assert same_bits(g.gather(-1, gi).toArray(), want)
+    finally:
+        L.check(cuda_ops.lib.ktc_tune_set(b"gather_smem", 1))
+    bad = gi.toArray().copy(); bad.reshape(-1)[7] = shape[-1]
+    with pytest.raises(ValueError, match="invalid index"):
+        g.gather(-1, cuda_ops.createRaw(ishape, bad))
+
+
 @pytest.mark.parametrize("n_idx,rows,inner,outer", [(5000, 300, 16, 3), (5000, 300, 5, 1), (3000, 4000, 8, 2), (2000, 3, 64, 1), (70, 70, 4, 1)])
 def test_index_add_many_indices_keeps_the_sequential_order(cuda_ops, gc_scope, n_idx, rows, inner, outer):
     """Many (repeated) indices: the grouped kernels must add in index-position order, bit for bit like the
