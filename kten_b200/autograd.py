@@ -92,6 +92,9 @@ class Tensor:
     def __rsub__(self, c):
         return MinusConstant(self.ops)(self, float(c), tensor_first=False)
 
+    def __neg__(self):
+        return 0.0 - self                                        # Tensor.unaryMinus (Tensor.kt:553-555)
+
     def __mul__(self, o):
         return Times(self.ops)(self, o) if isinstance(o, Tensor) else TimesConstant(self.ops)(self, float(o))
 
@@ -218,6 +221,11 @@ class Tensor:
 
     def maskedFill(self, mask: "Tensor", value: float):
         return MaskedFill(self.ops)(self.inplaceSafe(), mask, float(value))
+
+    def softmaxCrossEntropy(self, targets: "Tensor"):
+        """Tensor.softmaxCrossEntropy (functions/nn/TensorExtensions.kt:252-255)."""
+        res = SoftmaxCrossEntropy(self.ops)(self, targets)
+        return res if self.requiresGrad else res.noGrad()
 
     def expand(self, *shape):
         if len(shape) == 1 and isinstance(shape[0], (list, tuple)):
@@ -1246,6 +1254,67 @@ class MaskedFill(UnaryTensorFunction):            # :559-584
 
     def doBackward(self, g):
         return [g.maskedFill(self.mask, 0.0)]
+
+
+class SoftmaxCrossEntropy(UnaryTensorFunction):    # functions/nn/SoftmaxCrossEntropy.kt:10-81
+    """Mean negative log-likelihood of integer class targets under softmax(logits), written as
+    the reference writes it: a sequence of backend calls (row maximum, shifted exp, two
+    normalisations, clamp to [epsilon, 1 - epsilon], log, gather at the targets, mean), so every
+    backend rounds at the same places.  Backward is (softmax - onehot(targets)) / rows."""
+    modifiesShape = True
+
+    def __call__(self, logits: Tensor, targets: Tensor):
+        super().__call__(logits)
+        self.cachedShape = [1]
+        if targets.requiresGrad:
+            raise ValueError("SoftmaxCrossEntropy only accept targets that don't require gradients")
+        if len(logits.shape) != 2:
+            raise ValueError(f"SoftmaxCrossEntropy requires 2D logits, but got tensor with shape {logits.shape}")
+        if len(targets.shape) != 1:
+            raise ValueError(f"SoftmaxCrossEntropy requires 1D targets, but got tensor with shape {targets.shape}")
+        if logits.shape[0] != targets.shape[0]:
+            raise ValueError("Logits must have the same size at the first dimension as targets, "
+                             f"but got tensors with shape: logits: {logits.shape}, targets: {targets.shape}")
+        self.targets = targets.unsqueeze(-1)
+        self.rows = targets.shape[0]
+        return self
+
+    def doForward(self, x):
+        ops, eps = self.ops, self.ops.epsilon
+        idx = self.targets._forwarded()
+        max_val = x.max(-1, keepDimensions=True)
+        shifted = x.minus(max_val)
+        exp_val = shifted.exp()
+        exp_sum = exp_val.sum(-1, keepDimensions=True)
+        softmax = exp_val.div(exp_sum)
+        self.saveForBackward(softmax)
+        softmax_sum = softmax.sum(-1, keepDimensions=True)
+        softmax_norm = softmax.div(softmax_sum)
+        clipped = softmax_norm.clamp(eps, _f32(1.0 - _f32(eps)))
+        log_softmax = clipped.log()
+        at_targets = log_softmax.gather(-1, idx)
+        nll = at_targets.unaryMinus()
+        self.output = nll.mean()
+        ops.release(max_val, shifted, exp_val, exp_sum, softmax_sum, softmax_norm, clipped, log_softmax, at_targets, nll)
+
+    def doBackward(self, g):
+        grad_in = self.ops.zerosLike(self.valuesSaved[0])
+        grad_in.inplaceScatter(-1, self.targets._forwarded(), -1.0)
+        grad_in.plusAssign(self.valuesSaved[0])
+        grad_in.divAssign(float(self.rows))
+        return [grad_in]
+
+
+def oneHot(ops, targets: Tensor, classes: int) -> Tensor:
+    """Tensor.oneHot (Tensor.kt:1712-1721): built on the host, element by element, then uploaded."""
+    import numpy as np
+    if len(targets.shape) != 1:
+        raise ValueError(f"One hot encoding can only be applied to 1D tensors, but got tensor with shape: {targets.shape}")
+    t = targets.toArray().astype(np.int64)
+    hot = np.zeros((t.shape[0], classes), dtype=np.float32)
+    ok = (t >= 0) & (t < classes)
+    hot[np.nonzero(ok)[0], t[ok]] = 1.0
+    return NoGradVariable(ops, ops.createRaw([t.shape[0], classes], hot.reshape(-1)))
 
 
 def concat(tensors, axis: int = 0) -> Tensor:

@@ -203,3 +203,36 @@ def run_case(ops, case):
         assert_tensor_equals(case["res"], t1, tol)
     else:
         raise AssertionError(f"unknown graph {g}")
+
+
+def softmax_cross_entropy_property(ops, rows=256, classes=2048, seed=77, tol=1e-6):
+    """should_calculate_softmax_cross_entropy_from_logits (kten-testing/.../TensorTestsBase.kt:2204-2224):
+    the fused function node and the same loss spelled with one-hot targets agree in value and in
+    gradient within assertTensorEquals' default tolerance.  The reference draws the logits and the
+    targets from an unseeded generator; here they are seeded (standard-normal-range logits, uniform
+    integer targets).  Returns (loss, gradient, logits, targets) as arrays for further checks."""
+    rng = np.random.default_rng(seed)
+    x = rng.uniform(-1.0, 1.0, (rows, classes)).astype(np.float32)
+    t = rng.integers(0, classes, rows).astype(np.float32)
+    tensor = AG.tensorOf(ops, x, requiresGrad=True)
+    tensor2 = tensor.copy().asVariable(requiresGrad=True)
+    targets = AG.tensorOf(ops, t)
+    one_hot = AG.oneHot(ops, targets, classes)
+
+    res = tensor.softmaxCrossEntropy(targets)
+    res.backward()
+
+    exp_val = (tensor2 - tensor2.max(-1, keepDimensions=True)).exp()
+    softmax = exp_val / exp_val.sum(-1, keepDimensions=True)
+    eps = ops.epsilon
+    softmax_norm = (softmax / softmax.sum(-1, keepDimensions=True)).clamp(eps, 1.0 - eps)
+    res2 = (-(one_hot * softmax_norm.log()).sum(-1)).mean()
+    res2.backward()
+
+    got, want = res.toArray(), res2.toArray()
+    assert got.shape == want.shape == (1,)
+    assert abs(float(got[0]) - float(want[0])) <= tol, (got, want)
+    g1, g2 = tensor.grad().toArray(), tensor2.grad().toArray()
+    assert g1.shape == g2.shape == (rows, classes)
+    assert float(np.abs(g1.astype(np.float64) - g2.astype(np.float64)).max()) <= tol
+    return got, g1, x, t

@@ -267,3 +267,20 @@ def test_data_movement_full_size_properties(cuda_ops, gc_scope):
     joined = cuda_ops.concat(1, [left, right])
     d3 = joined.minus(x)
     assert float(d3.abs().sum().toArray()[0]) == 0.0
+
+
+@pytest.mark.parametrize("deferred", [False, True], ids=["call_by_call", "deferred"])
+def test_softmax_cross_entropy_matches_oracle(cuda_ops, gc_scope, deferred):
+    """SoftmaxCrossEntropy at the reference test's size ([256, 2048] logits): the reference's own
+    property holds on the device, and loss and gradient agree with the CPU oracle running the same
+    call sequence.  Not bit-exact: exp and log are within 2 ulp and the row sums use a different tree,
+    so the tolerance is 2e-6 on the loss (4 ulp at log 2048 = 7.6) and 1e-8 on the gradient (entries < 4e-3)."""
+    from tests.kten_cases import softmax_cross_entropy_property
+    cuda_ops.lazy = deferred
+    try:
+        loss, grad, _, _ = softmax_cross_entropy_property(cuda_ops)
+    finally:
+        cuda_ops.lazy = False
+    want_loss, want_grad, _, _ = softmax_cross_entropy_property(ORACLE)
+    assert abs(float(loss[0]) - float(want_loss[0])) <= 2e-6
+    assert float(np.abs(grad.astype(np.float64) - want_grad.astype(np.float64)).max()) <= 1e-8

@@ -81,3 +81,31 @@ def test_broadcast_shape_errors():
         O.common_shape([2, 3], [4, 3])
     assert O.common_shape([32, 64, 128], [64, 1]) == [32, 64, 128]
     assert O.common_shape([3], [2, 1]) == [2, 3]
+
+
+def test_softmax_cross_entropy_property_and_closed_form(oracle_ops):
+    """The reference's own property (function node == one-hot spelling), then the closed form in
+    float64: loss = mean(-log softmax[target]), gradient = (softmax - onehot) / rows."""
+    from tests.kten_cases import softmax_cross_entropy_property
+    loss, grad, x, t = softmax_cross_entropy_property(oracle_ops, rows=64, classes=512)
+    xs = x.astype(np.float64)
+    p = np.exp(xs - xs.max(1, keepdims=True))
+    p /= p.sum(1, keepdims=True)
+    rows = np.arange(x.shape[0])
+    assert abs(float(loss[0]) + np.log(p[rows, t.astype(int)]).mean()) < 1e-5
+    g = p.copy()
+    g[rows, t.astype(int)] -= 1.0
+    assert np.abs(g / x.shape[0] - grad).max() < 1e-7
+
+
+def test_softmax_cross_entropy_argument_checks(oracle_ops):
+    from kten_b200 import autograd as AG
+    logits = AG.tensorOf(oracle_ops, np.zeros((2, 3), np.float32), requiresGrad=True)
+    with pytest.raises(ValueError, match="2D logits"):
+        AG.tensorOf(oracle_ops, np.zeros(3, np.float32), requiresGrad=True).softmaxCrossEntropy(AG.tensorOf(oracle_ops, [0.0, 1.0, 2.0]))
+    with pytest.raises(ValueError, match="1D targets"):
+        logits.softmaxCrossEntropy(AG.tensorOf(oracle_ops, np.zeros((2, 1), np.float32)))
+    with pytest.raises(ValueError, match="same size at the first dimension"):
+        logits.softmaxCrossEntropy(AG.tensorOf(oracle_ops, [0.0, 1.0, 2.0]))
+    with pytest.raises(ValueError, match="don't require gradients"):
+        logits.softmaxCrossEntropy(AG.tensorOf(oracle_ops, [0.0, 1.0], requiresGrad=True))
