@@ -225,15 +225,35 @@ KTC_API int ktc_reduce_all_noalloc(int op, ktc_buf out, ktc_buf in, int64_t n);
 #define KTC_EXPR_MAX_LEAVES 6
 #define KTC_EXPR_MAX_STORES 3
 #define KTC_EXPR_REGS 8
+#define KTC_EXPR_MAX_SINKS 4
 enum { KTC_X_LOAD = 1, KTC_X_CONST, KTC_X_ADD, KTC_X_SUB, KTC_X_MUL, KTC_X_DIV, KTC_X_POW, KTC_X_NEG, KTC_X_RCP,
        KTC_X_SQUARE, KTC_X_EXP, KTC_X_LOG, KTC_X_TANH, KTC_X_SIGMOID, KTC_X_CLAMP, KTC_X_CMP_LT, KTC_X_CMP_LTE,
        KTC_X_CMP_GT, KTC_X_CMP_GTE, KTC_X_STORE, KTC_X_ACC };
-enum { KTC_EXPR_STORE_ONLY = 0, KTC_EXPR_SUM_ALL = 1, KTC_EXPR_SUM_ROWS = 2 };
+enum { KTC_EXPR_STORE_ONLY = 0, KTC_EXPR_SUM_ALL = 1, KTC_EXPR_SUM_ROWS = 2, KTC_EXPR_MULTI = 3 };
 KTC_API int ktc_expr_eval(const uint32_t* code, int n_code, const float* imm, int n_imm,
                           const int64_t* shape, int ndim,
                           const ktc_buf* leaves, const int64_t* leaf_shapes, int n_leaves,
                           const ktc_buf* stores, int n_stores,
                           int sink, ktc_buf sink_out, int mean);
+
+/* Several sums of one pass: the loss and both broadcast gradients of a training step share their
+ * operands (Mean.doForward, AggregatingFunctions.kt; the mayUnexpand sums of Plus / Times backward,
+ * BasicFunctions.kt:12-55), so a backend that defers the sums as well can read those operands once.
+ * Same program encoding; an ACC instruction's k field names the sink (0 .. n_sinks-1, at most
+ * KTC_EXPR_MAX_SINKS), sink j is of kind sink_kinds[j] (KTC_EXPR_SUM_ALL or KTC_EXPR_SUM_ROWS, with
+ * means[j] != 0 dividing a SUM_ALL by the element count) and writes sink_outs[j].  The iteration
+ * space is partitioned as for a single SUM_ROWS sink, and every sink accumulates as its single-sink
+ * call does (float runs folded into doubles, fixed combination order): SUM_ROWS results equal those
+ * of separate ktc_expr_eval calls bit for bit, a SUM_ALL result is the same sum taken over a
+ * possibly different partition (equal within the reduction tolerance, exact on exactly summable
+ * data).  Runs only as a
+ * generated kernel (see below): KTC_ENOTSUP also when the iteration space is below
+ * `expr_jit_min_elems` or NVRTC is missing -- issue the single-sink calls instead. */
+KTC_API int ktc_expr_eval_multi(const uint32_t* code, int n_code, const float* imm, int n_imm,
+                                const int64_t* shape, int ndim,
+                                const ktc_buf* leaves, const int64_t* leaf_shapes, int n_leaves,
+                                const ktc_buf* stores, int n_stores,
+                                const int* sink_kinds, const ktc_buf* sink_outs, const int* means, int n_sinks);
 
 /* For iteration spaces of at least `expr_jit_min_elems` elements (tunable, default 2^20; tunable
  * `expr_jit` = 0 turns it off) ktc_expr_eval does not interpret the program: it generates CUDA
@@ -341,13 +361,16 @@ KTC_API int ktc_tune_set(const char* key, int value);      /* launch-shape tunab
 
 /* ---- test hooks (host-side failure injection; nothing here faults a GPU) ---- */
 KTC_API int ktc_test_inject_comm_error(int n_calls);        /* next n collective calls report KTC_ECOMM */
-KTC_API int ktc_test_bounded_wait(int dev, int64_t limit_ns, int* status);
+KTC_API int ktc_test_bounded_wait(int dev, int64_t limit_ns, int* status);   /* waits on a flag nothing sets */
 /* Generates and compiles (NVRTC, no device needed) the kernel for an expression program: the
  * build check for run-time generated code.  leaf_inner[l] != 0: leaf l varies along the innermost
  * axis; leaf_fixed[l] != 0: it does not depend on the row.  rank3: three collapsed dimensions.
  * KTC_ENOTSUP when NVRTC is not installed. */
 KTC_API int ktc_test_expr_compile(const uint32_t* code, int n_code, int n_leaves, const int* leaf_inner, const int* leaf_fixed,
-                                  int rank3, int sink, int64_t* cubin_bytes, double* compile_ms); /* waits on a flag nothing sets */
+                                  int rank3, int sink, int64_t* cubin_bytes, double* compile_ms);
+/* The same for a program with several sums (ktc_expr_eval_multi). */
+KTC_API int ktc_test_expr_compile_multi(const uint32_t* code, int n_code, int n_leaves, const int* leaf_inner, const int* leaf_fixed,
+                                        int rank3, const int* sink_kinds, int n_sinks, int64_t* cubin_bytes, double* compile_ms);
 
 #ifdef __cplusplus
 }

@@ -178,6 +178,7 @@ static int launch_expr(Device* d, const ExprArgs& a, int n_leaves, int sink, int
         const int rc = jit_launch(d, a, n_leaves, sink, grid);
         if (rc != KTC_ENOTSUP) return rc;
     }
+    if (sink == KTC_EXPR_MULTI) return fail(KTC_ENOTSUP, "ktc_expr_eval_multi: no generated kernel for this program (iteration space below expr_jit_min_elems, or NVRTC unavailable)");
     jit_count_interpreter_launch();
     if (sink == KTC_EXPR_STORE_ONLY) k_expr<KTC_EXPR_STORE_ONLY><<<(int)grid, 256, 0, d->stream>>>(a);
     else if (sink == KTC_EXPR_SUM_ALL) k_expr<KTC_EXPR_SUM_ALL><<<(int)grid, 256, 0, d->stream>>>(a);
@@ -189,17 +190,27 @@ static int launch_expr(Device* d, const ExprArgs& a, int n_leaves, int sink, int
 
 using namespace ktc;
 
-extern "C" int ktc_expr_eval(const uint32_t* code, int n_code, const float* imm, int n_imm,
-                             const int64_t* shape, int ndim,
-                             const ktc_buf* leaves, const int64_t* leaf_shapes, int n_leaves,
-                             const ktc_buf* stores, int n_stores,
-                             int sink, ktc_buf sink_out, int mean) {
+// sink == KTC_EXPR_MULTI: n_sinks sums described by sink_kinds / sink_outs / means; otherwise the single
+// sink (sink, sink_out, mean).
+static int expr_eval(const uint32_t* code, int n_code, const float* imm, int n_imm,
+                     const int64_t* shape, int ndim,
+                     const ktc_buf* leaves, const int64_t* leaf_shapes, int n_leaves,
+                     const ktc_buf* stores, int n_stores,
+                     int sink, ktc_buf sink_out, int mean,
+                     const int* sink_kinds, const ktc_buf* sink_outs, const int* means, int n_sinks) {
     if (!code || n_code < 1 || n_code > kExprMaxInstr) return fail(KTC_EINVAL, "ktc_expr_eval: program of %d instructions (1..%d allowed)", n_code, kExprMaxInstr);
     if (n_imm < 0 || n_imm > kExprMaxImm || (n_imm > 0 && !imm)) return fail(KTC_EINVAL, "ktc_expr_eval: %d immediates (at most %d)", n_imm, kExprMaxImm);
     if (n_leaves < 0 || n_leaves > kExprMaxLeaves || n_stores < 0 || n_stores > kExprMaxStores)
         return fail(KTC_EINVAL, "ktc_expr_eval: %d leaves / %d stores (at most %d / %d)", n_leaves, n_stores, kExprMaxLeaves, kExprMaxStores);
     if (ndim < 1 || ndim > KTC_MAX_DIMS || !shape) return fail(KTC_EINVAL, "ktc_expr_eval: bad shape");
-    if (sink < KTC_EXPR_STORE_ONLY || sink > KTC_EXPR_SUM_ROWS) return fail(KTC_EINVAL, "ktc_expr_eval: unknown sink %d", sink);
+    if (sink < KTC_EXPR_STORE_ONLY || sink > KTC_EXPR_MULTI) return fail(KTC_EINVAL, "ktc_expr_eval: unknown sink %d", sink);
+    const bool multi = sink == KTC_EXPR_MULTI;
+    if (multi) {
+        if (n_sinks < 1 || n_sinks > kExprMaxSinks || !sink_kinds || !sink_outs || !means) return fail(KTC_EINVAL, "ktc_expr_eval_multi: %d sinks (1..%d allowed)", n_sinks, kExprMaxSinks);
+        for (int j = 0; j < n_sinks; ++j)
+            if (sink_kinds[j] != KTC_EXPR_SUM_ALL && sink_kinds[j] != KTC_EXPR_SUM_ROWS) return fail(KTC_EINVAL, "ktc_expr_eval_multi: sink %d is of unknown kind %d", j, sink_kinds[j]);
+    }
+    const bool keep_inner = sink == KTC_EXPR_SUM_ROWS || multi;      // the innermost dimension of `shape` is not merged
     int64_t total = 1;
     for (int i = 0; i < ndim; ++i) { if (shape[i] < 1) return fail(KTC_EINVAL, "ktc_expr_eval: empty iteration space"); total *= shape[i]; }
     if (total > ((int64_t)1 << 40)) return fail(KTC_EINVAL, "ktc_expr_eval: iteration space too large");
@@ -237,13 +248,13 @@ extern "C" int ktc_expr_eval(const uint32_t* code, int n_code, const float* imm,
     int64_t S[KTC_MAX_DIMS]; int64_t LS[kExprMaxLeaves][KTC_MAX_DIMS]; int m = 0;
     for (int i = 0; i < ndim; ++i) {
         if (shape[i] == 1) continue;
-        bool merge = m > 0 && !(sink == KTC_EXPR_SUM_ROWS && i == ndim - 1);
+        bool merge = m > 0 && !(keep_inner && i == ndim - 1);
         for (int l = 0; l < n_leaves && merge; ++l) merge = (LS[l][m - 1] == lstr[l][i] * shape[i]);
         if (merge) { S[m - 1] *= shape[i]; for (int l = 0; l < n_leaves; ++l) LS[l][m - 1] = lstr[l][i]; }
         else { S[m] = shape[i]; for (int l = 0; l < n_leaves; ++l) LS[l][m] = lstr[l][i]; ++m; }
     }
     if (m == 0) { S[0] = 1; for (int l = 0; l < n_leaves; ++l) LS[l][0] = 0; m = 1; }
-    if (sink == KTC_EXPR_SUM_ROWS && shape[ndim - 1] == 1) return fail(KTC_ENOTSUP, "ktc_expr_eval: SUM_ROWS needs a kept innermost dimension");
+    if (keep_inner && shape[ndim - 1] == 1) return fail(KTC_ENOTSUP, "ktc_expr_eval: SUM_ROWS needs a kept innermost dimension");
     if (m > 3) return fail(KTC_ENOTSUP, "ktc_expr_eval: %d collapsed dimensions (at most 3 are fused)", m);
     int64_t D[3] = {1, 1, 1};
     for (int i = 0; i < m; ++i) D[3 - m + i] = S[i];
@@ -260,6 +271,7 @@ extern "C" int ktc_expr_eval(const uint32_t* code, int n_code, const float* imm,
     // validate the program: register and operand indices, opcodes
     a.n_code = n_code;
     bool has_acc = false;
+    bool fed[kExprMaxSinks] = {false};
     for (int i = 0; i < n_code; ++i) {
         const uint32_t ins = code[i];
         const int op = ins & 0xff, dreg = (ins >> 8) & 0xf, ra = (ins >> 12) & 0xf, rb = (ins >> 16) & 0xf, k = ins >> 20;
@@ -269,11 +281,19 @@ extern "C" int ktc_expr_eval(const uint32_t* code, int n_code, const float* imm,
         if (op == KTC_X_STORE && k >= n_stores) return fail(KTC_EINVAL, "ktc_expr_eval: STORE to target %d (have %d)", k, n_stores);
         if ((op == KTC_X_CONST || (op >= KTC_X_CMP_LT && op <= KTC_X_CMP_GTE)) && k >= n_imm) return fail(KTC_EINVAL, "ktc_expr_eval: immediate %d (have %d)", k, n_imm);
         if (op == KTC_X_CLAMP && k + 1 >= n_imm) return fail(KTC_EINVAL, "ktc_expr_eval: clamp immediates %d,%d (have %d)", k, k + 1, n_imm);
-        if (op == KTC_X_ACC) { if (sink == KTC_EXPR_STORE_ONLY) return fail(KTC_EINVAL, "ktc_expr_eval: ACC without a summing sink"); has_acc = true; }
+        if (op == KTC_X_ACC) {
+            if (sink == KTC_EXPR_STORE_ONLY) return fail(KTC_EINVAL, "ktc_expr_eval: ACC without a summing sink");
+            if (multi) {
+                if (k >= n_sinks || fed[k]) return fail(KTC_EINVAL, "ktc_expr_eval_multi: ACC at %d feeds sink %d (%d sinks, one ACC each)", i, k, n_sinks);
+                fed[k] = true;
+            }
+            has_acc = true;
+        }
         a.code[i] = ins;
     }
     for (int i = 0; i < n_imm; ++i) a.imm[i] = imm[i];
     if (sink != KTC_EXPR_STORE_ONLY && !has_acc) return fail(KTC_EINVAL, "ktc_expr_eval: a summing sink needs an ACC instruction");
+    for (int j = 0; multi && j < n_sinks; ++j) if (!fed[j]) return fail(KTC_EINVAL, "ktc_expr_eval_multi: sink %d has no ACC instruction", j);
 
     const int64_t rows = D[0] * D[1];
     a.col_tiles = (D[2] / 4 + 31) / 32;
@@ -284,7 +304,15 @@ extern "C" int ktc_expr_eval(const uint32_t* code, int n_code, const float* imm,
     int64_t Sg = (rows + seg_rows - 1) / seg_rows;
 
     Buf bout{}; Scratch scratch;
-    if (sink != KTC_EXPR_STORE_ONLY) {
+    Buf mout[kExprMaxSinks];
+    if (multi) {
+        for (int j = 0; j < n_sinks; ++j) {
+            KTC_TRY(resolve(sink_outs[j], &mout[j])); KTC_TRY(adopt(mout[j]));
+            const int64_t need_out = sink_kinds[j] == KTC_EXPR_SUM_ALL ? 1 : D[2];
+            if (mout[j].n < need_out) return fail(KTC_EINVAL, "ktc_expr_eval_multi: output of sink %d holds %lld floats, %lld needed", j, (long long)mout[j].n, (long long)need_out);
+        }
+        Sg = (Sg + 7) & ~(int64_t)7;
+    } else if (sink != KTC_EXPR_STORE_ONLY) {
         KTC_TRY(resolve(sink_out, &bout)); KTC_TRY(adopt(bout));
         const int64_t need_out = sink == KTC_EXPR_SUM_ALL ? 1 : D[2];
         if (bout.n < need_out) return fail(KTC_EINVAL, "ktc_expr_eval: sink output holds %lld floats, %lld needed", (long long)bout.n, (long long)need_out);
@@ -301,6 +329,34 @@ extern "C" int ktc_expr_eval(const uint32_t* code, int n_code, const float* imm,
     const int64_t groups = Sg / 8;
     const int64_t grid = groups * a.col_tiles;
     if (grid > 0x7fffffffLL) return fail(KTC_ENOTSUP, "ktc_expr_eval: grid too large");
+    if (multi) {
+        // one partial-sum area per sink, laid out as the single-sink launches lay theirs out, then each
+        // sink's own second pass
+        int64_t need = 0;
+        for (int j = 0; j < n_sinks; ++j) need += sink_kinds[j] == KTC_EXPR_SUM_ALL ? grid : groups * D[2];
+        KTC_TRY(scratch.get(d, need * 2));
+        double* base = reinterpret_cast<double*>(scratch.ptr);
+        a.n_sinks = n_sinks;
+        for (int j = 0; j < n_sinks; ++j) {
+            a.sink_kind[j] = sink_kinds[j];
+            a.mpart[j] = base;
+            base += sink_kinds[j] == KTC_EXPR_SUM_ALL ? grid : groups * D[2];
+        }
+        KTC_TRY(launch_expr(d, a, n_leaves, sink, grid, total));
+        for (int j = 0; j < n_sinks; ++j) {
+            if (sink_kinds[j] == KTC_EXPR_SUM_ALL) {
+                if (means[j]) k_combine_block<1, SumAcc><<<1, 512, 0, d->stream>>>(a.mpart[j], mout[j].ptr, nullptr, 1, (int)grid, total);
+                else          k_combine_block<0, SumAcc><<<1, 512, 0, d->stream>>>(a.mpart[j], mout[j].ptr, nullptr, 1, (int)grid, total);
+            } else if (groups >= 64 || D[2] < 4096) {
+                const int64_t blocks = (D[2] * 32 + 255) / 256;
+                k_combine_warp<0, SumAcc><<<(int)blocks, 256, 0, d->stream>>>(a.mpart[j], mout[j].ptr, nullptr, D[2], (int)groups, rows);
+            } else {
+                k_combine_thread<0, SumAcc><<<(int)((D[2] + 255) / 256), 256, 0, d->stream>>>(a.mpart[j], mout[j].ptr, nullptr, D[2], (int)groups, rows);
+            }
+            KTC_TRY(finish_launch_expr("expr(combine)"));
+        }
+        return KTC_OK;
+    }
     a.divisor = mean ? (double)total : 0.0;
     if (sink == KTC_EXPR_SUM_ALL) {
         a.out = bout.ptr;
@@ -324,4 +380,21 @@ extern "C" int ktc_expr_eval(const uint32_t* code, int n_code, const float* imm,
         k_combine_thread<0, SumAcc><<<(int)((D[2] + 255) / 256), 256, 0, d->stream>>>(a.part, bout.ptr, nullptr, D[2], (int)groups, rows);
     }
     return finish_launch_expr("expr(combine)");
+}
+
+extern "C" int ktc_expr_eval(const uint32_t* code, int n_code, const float* imm, int n_imm,
+                             const int64_t* shape, int ndim,
+                             const ktc_buf* leaves, const int64_t* leaf_shapes, int n_leaves,
+                             const ktc_buf* stores, int n_stores,
+                             int sink, ktc_buf sink_out, int mean) {
+    if (sink == KTC_EXPR_MULTI) return fail(KTC_EINVAL, "ktc_expr_eval: several sinks go through ktc_expr_eval_multi");
+    return expr_eval(code, n_code, imm, n_imm, shape, ndim, leaves, leaf_shapes, n_leaves, stores, n_stores, sink, sink_out, mean, nullptr, nullptr, nullptr, 0);
+}
+
+extern "C" int ktc_expr_eval_multi(const uint32_t* code, int n_code, const float* imm, int n_imm,
+                                   const int64_t* shape, int ndim,
+                                   const ktc_buf* leaves, const int64_t* leaf_shapes, int n_leaves,
+                                   const ktc_buf* stores, int n_stores,
+                                   const int* sink_kinds, const ktc_buf* sink_outs, const int* means, int n_sinks) {
+    return expr_eval(code, n_code, imm, n_imm, shape, ndim, leaves, leaf_shapes, n_leaves, stores, n_stores, KTC_EXPR_MULTI, 0, 0, sink_kinds, sink_outs, means, n_sinks);
 }

@@ -12,6 +12,7 @@ constexpr int kExprMaxImm = KTC_EXPR_MAX_IMM;
 constexpr int kExprMaxLeaves = KTC_EXPR_MAX_LEAVES;
 constexpr int kExprMaxStores = KTC_EXPR_MAX_STORES;
 constexpr int kExprRegs = KTC_EXPR_REGS;
+constexpr int kExprMaxSinks = KTC_EXPR_MAX_SINKS;
 
 // Iteration space: the collapsed view [D0, D1, D2] of the result shape; a warp owns a 128-column
 // tile (lane = 4 columns) of `seg_rows` consecutive rows of the D0*D1 row space.
@@ -30,6 +31,10 @@ struct ExprArgs {
     double* part;                          // partial sums of the summing sinks
     float* out;                            // final result when a single CTA suffices (unused otherwise)
     double divisor;                        // > 0: mean
+    // several sums in one pass (KTC_EXPR_MULTI): an ACC instruction's k field names its sink
+    int n_sinks;
+    int sink_kind[kExprMaxSinks];          // KTC_EXPR_SUM_ALL or KTC_EXPR_SUM_ROWS
+    double* mpart[kExprMaxSinks];          // partial sums of each sink
 };
 
 }  // namespace ktc

@@ -24,6 +24,11 @@ Rules that keep the semantics of the eager backend:
     evaluation, if its tensor is still alive, stores it as a side output and later programs
     read it from memory; a value behind a transcendental (`ops.storeCost`) is stored by the
     first program that computes it, since that program is issue-bound and the store rides along;
+  * with `ops.deferSums`, sum() / mean() and the leading-axis sums of a deferred tensor are
+    deferred as well, and `stored += pending sum` (a gradient accumulated into a Variable) is
+    remembered as a pending update of that buffer; the first read of any of them -- or of the
+    updated buffer -- runs all pending sums, those over the same iteration space as ONE pass with
+    several sinks (the loss and both broadcast gradients of a training step read x once);
   * compiled programs are cached by the structure of the expression DAG, so a training step that
     rebuilds the same graph with fresh tensors pays for register allocation once.
 Whatever the kernel does not fuse (more than three collapsed dimensions, an innermost
@@ -62,22 +67,29 @@ class BufferRef:
 
 
 class Node:
-    """kind: leaf | const | un | bin | clamp | cmp | square | bcast.  Immutable value; `buf` is set
-    once the value has been written to memory (the node then acts as a leaf)."""
+    """kind: leaf | const | un | bin | clamp | cmp | square | bcast | reduce.  Immutable value; `buf`
+    is set once the value has been written to memory (the node then acts as a leaf).  A `reduce`
+    node is a sum that has not run yet: args[0] is the summed expression, op the sink kind
+    (EXPR_SUM_ALL / EXPR_SUM_ROWS), imm[0] != 0 a mean; it is never part of a program -- whoever
+    needs its value runs the pending sums first, several of them in one pass where they share an
+    iteration space."""
 
-    __slots__ = ("kind", "op", "args", "shape", "imm", "buf", "leaves", "evals", "owner", "parents", "__weakref__")
+    __slots__ = ("kind", "op", "args", "shape", "imm", "buf", "leaves", "evals", "owner", "parents", "has_sum", "__weakref__")
 
     def __init__(self, kind, shape, op=0, args=(), imm=(), buf: Optional[BufferRef] = None):
         self.kind, self.op, self.args, self.shape, self.imm, self.buf = kind, op, tuple(args), list(shape), tuple(imm), buf
         self.evals = 0
         self.owner = None                      # weakref to the storage cell (raw_tensor._Cell) waiting for this value
         self.parents = None                    # weak references to the nodes built on this one (list, pruned as it grows)
+        self.has_sum = kind == "reduce"        # a pending sum may sit underneath (never reset: a stale True only costs a look)
         if buf is not None:
             self.leaves = {buf.handle}
             return
         handles = set()
         me = None
         for a in self.args:
+            if a.has_sum and a.buf is None:
+                self.has_sum = True
             if a.buf is not None:
                 handles.add(a.buf.handle)
             else:
@@ -226,14 +238,16 @@ def _weight(n: Node) -> int:
     return 0 if n.kind in ("leaf", "const", "bcast") else 1
 
 
-def compile_program(shape, stores: Sequence[Node], acc: Optional[Node], recompute_limit: int = 0, store_cost: int = 0):
+def compile_program(shape, stores: Sequence[Node], acc, recompute_limit: int = 0, store_cost: int = 0):
     """Linearise the DAG under `stores` + `acc` into a register program over the iteration
-    space `shape`.  Returns (Program, nodes written by STORE, in store-index order; the first
+    space `shape`.  `acc`: the summed node of a single-sink program (or None), or a list of
+    nodes, one per sink of a multi-sink program (the ACC of list entry j carries sink index j).  Returns (Program, nodes written by STORE, in store-index order; the first
     len(stores) entries are the requested ones).  Side outputs: a value that a tensor still waits
     for is stored on the way when it was already computed `recompute_limit` times, or when
     recomputing it from memory would cost `store_cost` or more (both 0: nothing is stored but what
     was asked for).  Raises NotFusable."""
-    sinks = [strip(n) for n in stores] + ([strip(acc)] if acc is not None else [])
+    accs = [strip(a) for a in acc] if isinstance(acc, (list, tuple)) else ([strip(acc)] if acc is not None else [])
+    sinks = [strip(n) for n in stores] + accs
     order, uses = _toposort(sinks)
     full_volume = SF.to_store_size(shape)
     # The program depends on the structure of the DAG (operations, sharing, which values are in memory and which
@@ -253,7 +267,7 @@ def compile_program(shape, stores: Sequence[Node], acc: Optional[Node], recomput
             waiting = cell is not None and cell.store is None and cell.node is n and SF.to_store_size(n.shape) == full_volume
             sig.append((n.kind, n.op, len(n.imm), tuple([pos[strip(a)] for a in n.args]), waiting,
                         recompute_limit > 0 and n.evals >= recompute_limit))
-    key = (tuple(shape), tuple([pos[strip(n)] for n in stores]), pos[strip(acc)] if acc is not None else -1,
+    key = (tuple(shape), tuple([pos[strip(n)] for n in stores]), tuple([pos[a] for a in accs]), isinstance(acc, (list, tuple)),
            recompute_limit, store_cost, tuple(sig))
     hit = _PROGRAM_CACHE.get(key)
     if hit is not None:
@@ -268,7 +282,7 @@ def compile_program(shape, stores: Sequence[Node], acc: Optional[Node], recomput
         prog.order = order
         return prog, [order[p] for p in store_plan], n_requested
     try:
-        prog, store_nodes, n_requested = _compile(shape, stores, acc, recompute_limit, store_cost, sinks, order, uses, pos, full_volume)
+        prog, store_nodes, n_requested = _compile(shape, stores, accs, recompute_limit, store_cost, sinks, order, uses, pos, full_volume)
     except NotFusable:
         if len(_PROGRAM_CACHE) < _PROGRAM_CACHE_MAX:
             _PROGRAM_CACHE[key] = _NOT_FUSABLE
@@ -284,13 +298,12 @@ _PROGRAM_CACHE_MAX = 4096
 _NOT_FUSABLE = object()
 
 
-def _compile(shape, stores, acc, recompute_limit, store_cost, sinks, order, uses, pos, full_volume):
+def _compile(shape, stores, accs, recompute_limit, store_cost, sinks, order, uses, pos, full_volume):
     """The uncached compilation: side-output choice, register allocation, emission."""
     prog = Program(shape)
     reg: Dict[Node, int] = {}
     store_nodes: List[Node] = [strip(n) for n in stores]
     n_requested = len(store_nodes)
-    acc_node = strip(acc) if acc is not None else None
     # Side outputs.  Recomputing a short chain from an operand that is read anyway costs no memory
     # traffic, so cheap values are recomputed (a bounded number of times); a value behind a
     # transcendental is stored the first time -- the kernel that computes it is issue-bound and the
@@ -358,9 +371,10 @@ def _compile(shape, stores, acc, recompute_limit, store_cost, sinks, order, uses
             if sn is n:
                 prog.emit(L.X_STORE, a=d, k=k)
                 release_use(n)
-        if acc_node is not None and n is acc_node:
-            prog.emit(L.X_ACC, a=d)
-            release_use(n)
+        for j, an in enumerate(accs):
+            if an is n:
+                prog.emit(L.X_ACC, a=d, k=j)
+                release_use(n)
     prog.n_stores = len(store_nodes)
     prog.order = order
     return prog, store_nodes, n_requested
@@ -378,3 +392,34 @@ def run_program(ops, prog: Program, store_handles: Sequence[int], sink: int, sin
     stores = (C.c_uint64 * max(1, len(store_handles)))(*store_handles)
     return lib.ktc_expr_eval(code, len(prog.code), imm, len(prog.imm), shape, nd, leaves, lshapes, nl,
                              stores, len(store_handles), sink, sink_out, 1 if mean else 0)
+
+
+def run_program_multi(ops, prog: Program, store_handles: Sequence[int], kinds: Sequence[int], outs: Sequence[int], means: Sequence[bool]) -> int:
+    """ktc_expr_eval_multi: the ACC of sink j feeds a sum of kind kinds[j] written to outs[j]."""
+    lib = ops.lib
+    nd = len(prog.shape)
+    code = (C.c_uint32 * len(prog.code))(*prog.code)
+    imm = (C.c_float * max(1, len(prog.imm)))(*prog.imm)
+    shape = (C.c_int64 * nd)(*prog.shape)
+    nl = len(prog.leaves)
+    leaves = (C.c_uint64 * max(1, nl))(*[h for h, _ in prog.leaves])
+    lshapes = (C.c_int64 * max(1, nl * nd))(*[d for _, s in prog.leaves for d in s])
+    stores = (C.c_uint64 * max(1, len(store_handles)))(*store_handles)
+    ns = len(kinds)
+    return lib.ktc_expr_eval_multi(code, len(prog.code), imm, len(prog.imm), shape, nd, leaves, lshapes, nl,
+                                   stores, len(store_handles), (C.c_int * ns)(*kinds), (C.c_uint64 * ns)(*outs),
+                                   (C.c_int * ns)(*[1 if m else 0 for m in means]), ns)
+
+
+def has_pending_sum(roots: Sequence[Node]) -> bool:
+    """True when an unevaluated `reduce` node is reachable from `roots` through unstored nodes."""
+    seen, stack = set(), [r for r in roots if r.has_sum]
+    while stack:
+        n = stack.pop()
+        if n in seen or n.buf is not None:
+            continue
+        seen.add(n)
+        if n.kind == "reduce":
+            return True
+        stack.extend(a for a in n.args if a.has_sum)
+    return False

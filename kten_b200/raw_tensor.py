@@ -93,6 +93,8 @@ class CUDARawTensor:
             raise RuntimeError("Raw tensor already released")   # OCLMemoryObject.kt:167-170
         if self._store is None:
             self.ops._materialize(self)
+        elif self.ops._pending_targets and self._store in self.ops._pending_targets:
+            self.ops._run_pending()                             # a `+= pending sum` update of this buffer is due
         return self._store
 
     def incrementRef(self) -> None:
@@ -125,6 +127,8 @@ class CUDARawTensor:
             raise RuntimeError("Raw tensor already released")
         if self._store is None:
             return self._node
+        if self.ops._pending_targets and self._store in self.ops._pending_targets:
+            self.ops._run_pending()
         if self._node is None or not self._node.stored() or self._node.buf.handle != self._store or self._node.shape != self.shape:
             self._node = lazy.leaf(self.ops.lib, self._store, self.shape)
         return self._node
@@ -461,8 +465,9 @@ class CUDARawTensor:
         res_shape = SF.aggregate_over(self.shape, a, True)
         outer, length, inner = SF.collapse_axis(self.shape, a)
         res = None
-        if self.isDeferred and op == L.SUM and a == 0 and len(self.shape) >= 2:
-            res = self.ops._sum_leading_axis(self)              # fused with the pending expression when possible
+        if self.isDeferred and op == L.SUM and a == 0 and len(self.shape) >= 2 and self._node.kind != "reduce":
+            final = list(res_shape) if keep_dimensions else list(res_shape[1:])
+            res = self.ops._sum_leading_axis(self, final)       # fused with the pending expression when possible
         if res is None:
             res = self._new(res_shape)
             L.check(self.ops.lib.ktc_reduce_axis(op, res._buf(), self._buf(), outer, length, inner))

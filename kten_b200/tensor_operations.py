@@ -74,6 +74,10 @@ class CUDATensorOperations:
         self._deps_purge_at = 1024
         self.recomputeLimit = 2             # a pending value is recomputed at most this often before it is stored
         self.storeCost = 8                  # ... unless recomputing costs this much (a transcendental): stored at once
+        self.deferSums = True               # with lazy: sums of deferred tensors wait too, and run several per pass
+        self._pending = []                  # [weak reference to a reduce node, the node itself once an update hangs on it, [target BufferRefs]]
+        self._pending_targets = {}          # buffer handle -> number of pending `+= sum` updates
+        self.multiSinkEvaluations = 0       # passes that produced more than one sum
         self.fusedEvaluations = 0           # programs run by ktc_expr_eval
         self.unfusedEvaluations = 0         # deferred expressions that fell back to separate calls
 
@@ -170,6 +174,11 @@ class CUDATensorOperations:
         self._flush_dependents(h)
         n = target.size
         other = Z.strip(args[1]) if kind == "bin" else None
+        if node.has_sum and self._pending:
+            if other is not None and op == L.PLUS and other.kind == "reduce" and not other.stored() and SF.to_store_size(other.shape) == n \
+                    and Z.strip(args[0]).stored() and self._add_pending_update(other, h):
+                return                                              # target += pending sum: applied when the sums run
+            self._run_pending()
         if other is not None and (other.kind == "const" or (other.stored() and SF.to_store_size(other.shape) == n)):
             # nothing to fuse: the operand is already in memory (a gradient accumulated into a Variable, ...)
             if other.kind == "const":
@@ -199,6 +208,15 @@ class CUDATensorOperations:
                 L.check(self.lib.ktc_binary_inplace(op, h, hb, n))
 
     def _flush_dependents(self, handle: int) -> None:
+        if self._pending:
+            if handle in self._pending_targets:
+                self._run_pending()
+            else:
+                for ref, strong, _ in self._pending:
+                    nd = strong if strong is not None else ref()
+                    if nd is not None and handle in nd.leaves:
+                        self._run_pending()
+                        break
         refs = self._deps.pop(handle, None)
         if not refs:
             return
@@ -226,6 +244,8 @@ class CUDATensorOperations:
         """Compile `stores` (+ the summed node `acc`) and run them as one kernel.  handles[i] receives
         stores[i]; own[i]: the handle is a fresh buffer that node i adopts.  Nodes stored on the side
         get fresh buffers.  False: not fusable, nothing was run."""
+        if self._pending and Z.has_pending_sum(list(stores) + ([acc] if acc is not None else [])):
+            self._run_pending()
         try:
             prog, store_nodes, n_req = Z.compile_program(shape, stores, acc, self.recomputeLimit, self.storeCost)
             if reshape is not None and not reshape(prog):
@@ -255,6 +275,10 @@ class CUDATensorOperations:
         """Make sure the value under `node` (looking through broadcast markers) is in memory; returns
         (handle, shape).  The handle stays valid while the node is alive."""
         nd = Z.strip(node)
+        if nd.kind == "reduce" and not nd.stored():
+            self._run_pending()
+            if not nd.stored():
+                raise RuntimeError("a pending sum was not evaluated")
         if not nd.stored():
             h = self._alloc_handle(SF.to_store_size(nd.shape))
             if not self._try_fused(nd.shape, [nd], [h], [True]):
@@ -283,18 +307,20 @@ class CUDATensorOperations:
 
     def _sum_all(self, t: CUDARawTensor, mean: bool) -> Optional[CUDARawTensor]:
         """sum() / mean() of a deferred tensor fused with its expression; None: not fusable."""
+        if self.deferSums:
+            return self._defer_sum(t, L.EXPR_SUM_ALL, mean, [1])
         out = self.createRaw([1])
         if self._try_fused(t.shape, [], [], [], acc=t._node, sink=L.EXPR_SUM_ALL, sink_out=out._store, mean=mean):
             return out
         out.release()
         return None
 
-    def _sum_leading_axis(self, t: CUDARawTensor) -> Optional[CUDARawTensor]:
-        """sum over axis 0 of a deferred [A, ...] tensor fused with its expression (the leading-axis
-        sums of mayUnexpand, Utils.kt:14-41): the iteration space is viewed as [A, rest], possible when
-        every operand is either full or broadcast over the trailing dimensions."""
-        rest = SF.to_store_size(t.shape[1:])
-        full_tail = list(t.shape[1:])
+    @staticmethod
+    def _as_rows(shape):
+        """The reshape hook that views the iteration space [A, ...] as [A, rest]: possible when every
+        operand is either full or broadcast over the trailing dimensions."""
+        rest = SF.to_store_size(shape[1:])
+        full_tail = list(shape[1:])
 
         def as_rows(prog) -> bool:
             leaves2 = []
@@ -305,14 +331,127 @@ class CUDATensorOperations:
                     leaves2.append((h, [s[0], 1]))
                 else:
                     return False
-            prog.shape, prog.leaves = [t.shape[0], rest], leaves2
+            prog.shape, prog.leaves = [shape[0], rest], leaves2
             return True
 
+        return as_rows
+
+    def _sum_leading_axis(self, t: CUDARawTensor, res_shape=None) -> Optional[CUDARawTensor]:
+        """sum over axis 0 of a deferred [A, ...] tensor fused with its expression (the leading-axis
+        sums of mayUnexpand, Utils.kt:14-41): the iteration space is viewed as [A, rest]."""
+        rest = SF.to_store_size(t.shape[1:])
+        if self.deferSums and res_shape is not None:
+            return self._defer_sum(t, L.EXPR_SUM_ROWS, False, res_shape)
         out = self.createRaw([rest])
-        if self._try_fused(t.shape, [], [], [], acc=t._node, sink=L.EXPR_SUM_ROWS, sink_out=out._store, reshape=as_rows):
+        if self._try_fused(t.shape, [], [], [], acc=t._node, sink=L.EXPR_SUM_ROWS, sink_out=out._store, reshape=self._as_rows(t.shape)):
             return out
         out.release()
         return None
+
+    # ---- pending sums --------------------------------------------------------------------------
+    def _defer_sum(self, t: CUDARawTensor, kind: int, mean: bool, res_shape) -> CUDARawTensor:
+        res = self._deferred("reduce", list(res_shape), kind, (t._node,), (1.0 if mean else 0.0,))
+        self._pending.append([weakref.ref(res._node), None, []])
+        return res
+
+    def _add_pending_update(self, node, handle: int) -> bool:
+        """Remember `buffer handle += node` (node: a pending sum).  The node is kept alive from here on."""
+        for entry in self._pending:
+            if entry[0]() is node:
+                entry[1] = node
+                entry[2].append(Z.BufferRef(self.lib, handle))
+                self._pending_targets[handle] = self._pending_targets.get(handle, 0) + 1
+                return True
+        return False
+
+    def _run_pending(self) -> None:
+        """Evaluate every pending sum that is still wanted, then apply the pending updates in the order
+        they were requested.  Sums over the same iteration space run as one multi-sink pass (up to
+        KTC_EXPR_MAX_SINKS per pass); a sum whose expression contains another pending sum waits for it."""
+        entries, self._pending, self._pending_targets = self._pending, [], {}
+        todo = []
+        for ref, strong, targets in entries:
+            nd = strong if strong is not None else ref()
+            if nd is not None and not nd.stored():
+                todo.append((nd, targets))
+        waiting = [nd for nd, _ in todo]
+        while waiting:
+            ready = [nd for nd in waiting if not Z.has_pending_sum([nd.args[0]])]
+            if not ready:
+                raise RuntimeError("pending sums depend on one another")
+            waiting = [nd for nd in waiting if not any(nd is r for r in ready)]
+            groups = {}
+            for nd in ready:
+                groups.setdefault(tuple(nd.args[0].shape), []).append(nd)
+            for shape, nodes in groups.items():
+                for i in range(0, len(nodes), L.EXPR_MAX_SINKS):
+                    chunk = nodes[i:i + L.EXPR_MAX_SINKS]
+                    if len(chunk) > 1 and self._try_fused_sums(list(shape), chunk):
+                        continue
+                    for nd in chunk:
+                        self._run_one_sum(nd)
+        for nd, targets in todo:
+            for ref in targets:
+                L.check(self.lib.ktc_binary_inplace(L.PLUS, ref.handle, nd.buf.handle, SF.to_store_size(nd.shape)))
+
+    def _try_fused_sums(self, shape, nodes) -> bool:
+        """One pass over `shape` feeding every sum of `nodes`.  False: not fusable, nothing was run."""
+        exprs = [nd.args[0] for nd in nodes]
+        kinds = [nd.op for nd in nodes]
+        try:
+            # every consumer known so far sits in this pass: nothing is stored on the side for its cost alone
+            prog, store_nodes, n_req = Z.compile_program(shape, [], list(exprs), self.recomputeLimit, 0)
+            if any(k == L.EXPR_SUM_ROWS for k in kinds) and not self._as_rows(list(shape))(prog):
+                return False
+        except Z.NotFusable:
+            return False
+        total = SF.to_store_size(shape)
+        outs = [self._alloc_handle(SF.to_store_size(nd.shape)) for nd in nodes]
+        extra = [self._alloc_handle(total) for _ in store_nodes]
+        rc = Z.run_program_multi(self, prog, extra, kinds, outs, [nd.imm[0] != 0 for nd in nodes])
+        if rc != L.KTC_OK:
+            for h in outs + extra:
+                self.lib.ktc_release(h)
+            if rc == L.KTC_ENOTSUP:
+                return False
+            L.check(rc)
+        self.fusedEvaluations += 1
+        self.multiSinkEvaluations += 1
+        for nd in prog.order:
+            nd.evals += 1
+        for nd, h in zip(store_nodes, extra):
+            self._adopt(nd, h)
+        for nd, h in zip(nodes, outs):
+            self._adopt(nd, h)
+        return True
+
+    def _run_one_sum(self, nd) -> None:
+        """A single pending sum: fused with its expression, else the expression is evaluated and reduced
+        by the library's reduction call."""
+        expr = nd.args[0]
+        shape = list(expr.shape)
+        out = self._alloc_handle(SF.to_store_size(nd.shape))
+        mean = nd.imm[0] != 0
+        if nd.op == L.EXPR_SUM_ALL:
+            ok = self._try_fused(shape, [], [], [], acc=expr, sink=L.EXPR_SUM_ALL, sink_out=out, mean=mean)
+        else:
+            ok = self._try_fused(shape, [], [], [], acc=expr, sink=L.EXPR_SUM_ROWS, sink_out=out, reshape=self._as_rows(shape))
+        if not ok:
+            self.unfusedEvaluations += 1
+            h, shp = self._force(expr)
+            n, tmp = SF.to_store_size(shape), None
+            if SF.to_store_size(shp) != n:                          # a broadcast marker over a smaller value
+                tmp = h = self._alloc_handle(n)
+                self._eager_into(expr, shape, tmp)
+            try:
+                if nd.op == L.EXPR_SUM_ALL:
+                    L.check(self.lib.ktc_reduce_all(L.MEAN if mean else L.SUM, out, h, n))
+                else:
+                    L.check(self.lib.ktc_reduce_axis(L.SUM, out, h, 1, shape[0], n // shape[0]))
+            finally:
+                if tmp is not None:
+                    self.lib.ktc_release(tmp)
+        self._adopt(nd, out)
 
     def _eager_into(self, node, shape, out_handle: int) -> None:
         """One step of the call-by-call evaluation: the operands of `node` are forced into memory

@@ -32,6 +32,7 @@ class FakeLib:
         self.next = 1
         self.launches = 0
         self.expr_calls = 0
+        self.multi_calls = 0
         self.calls = []         # names of compute calls, in order
         self.error = b""
 
@@ -150,7 +151,12 @@ class FakeLib:
         return 0
 
     # ---- the fused expression call: the program encoding interpreted with the oracle's arithmetic ----
-    def ktc_expr_eval(self, code, n_code, imm, n_imm, shape, ndim, leaves, lshapes, n_leaves, stores, n_stores, sink, sink_out, mean):
+    def ktc_expr_eval_multi(self, code, n_code, imm, n_imm, shape, ndim, leaves, lshapes, n_leaves, stores, n_stores, kinds, outs, means, n_sinks):
+        self.multi_calls += 1
+        return self.ktc_expr_eval(code, n_code, imm, n_imm, shape, ndim, leaves, lshapes, n_leaves, stores, n_stores,
+                                  L.EXPR_MULTI, 0, 0, sinks=[(int(kinds[j]), int(outs[j]), int(means[j])) for j in range(n_sinks)])
+
+    def ktc_expr_eval(self, code, n_code, imm, n_imm, shape, ndim, leaves, lshapes, n_leaves, stores, n_stores, sink, sink_out, mean, sinks=None):
         shp = _ints(shape, ndim)
         if shp[-1] % 4 != 0 or len([d for d in shp if d != 1]) > 3:
             self.error = b"not fusable (stand-in rule: innermost extent must be a multiple of 4, at most 3 non-unit dims)"
@@ -160,6 +166,7 @@ class FakeLib:
         total = int(np.prod(shp))
         regs = [None] * L.EXPR_REGS
         acc = None
+        accs = {}
         flat = lambda v: np.ascontiguousarray(v, dtype=np.float32).reshape(-1)
         for pc in range(n_code):
             w = int(code[pc])
@@ -186,12 +193,17 @@ class FakeLib:
                 self._get(stores[k])[:total] = regs[a]
             elif op == L.X_ACC:
                 acc = regs[a].astype(np.float64)
+                accs[k] = acc
             else:
                 raise AssertionError(f"bad opcode {op}")
-        if sink == L.EXPR_SUM_ALL:
-            self._get(sink_out)[0] = np.float32(acc.sum() / (total if mean else 1))
-        elif sink == L.EXPR_SUM_ROWS:
-            self._get(sink_out)[:shp[-1]] = acc.reshape(-1, shp[-1]).sum(axis=0).astype(np.float32)
+        if sinks is None:
+            sinks = [(sink, sink_out, mean)] if sink != L.EXPR_STORE_ONLY else []
+            accs = {0: acc}
+        for j, (kind, out, mean_j) in enumerate(sinks):
+            if kind == L.EXPR_SUM_ALL:
+                self._get(out)[0] = np.float32(accs[j].sum() / (total if mean_j else 1))
+            else:
+                self._get(out)[:shp[-1]] = accs[j].reshape(-1, shp[-1]).sum(axis=0).astype(np.float32)
         return 0
 
 
@@ -207,5 +219,6 @@ def make_ops() -> CUDATensorOperations:
     ops.lazy = False
     ops._deps, ops._deps_purge_at = {}, 1024
     ops.recomputeLimit, ops.storeCost = 2, 8
+    ops.deferSums, ops._pending, ops._pending_targets, ops.multiSinkEvaluations = True, [], {}, 0
     ops.fusedEvaluations = ops.unfusedEvaluations = 0
     return ops

@@ -24,7 +24,19 @@ def same_bits(a, b):
 
 @pytest.fixture()
 def lazy_ops(cuda_ops):
-    cuda_ops.lazy = True
+    """Deferred elementwise calls; every sum runs where it is written (one sink per program)."""
+    cuda_ops.lazy, cuda_ops.deferSums = True, False
+    try:
+        with cuda_ops.garbageCollector():
+            yield cuda_ops
+    finally:
+        cuda_ops.lazy, cuda_ops.deferSums = False, True
+
+
+@pytest.fixture()
+def lazy_sums_ops(cuda_ops):
+    """The default deferred mode: sums wait as well and share passes (ops.deferSums)."""
+    cuda_ops.lazy, cuda_ops.deferSums = True, True
     try:
         with cuda_ops.garbageCollector():
             yield cuda_ops
@@ -48,6 +60,11 @@ def both(ops, fn):
 @pytest.mark.parametrize("case", CASES, ids=CASE_IDS)
 def test_reference_vectors_deferred(lazy_ops, case):
     run_case(lazy_ops, case)
+
+
+@pytest.mark.parametrize("case", CASES, ids=CASE_IDS)
+def test_reference_vectors_deferred_with_pending_sums(lazy_sums_ops, case):
+    run_case(lazy_sums_ops, case)
 
 
 SHAPES = [([64, 128], [64, 128], [128]), ([8, 16, 32], [16, 1], [32]), ([5, 12], [1, 12], [5, 1]),
@@ -312,3 +329,94 @@ def test_large_programs_use_generated_kernels_by_default(lazy_ops):
     assert after["jit_launches"] == before["jit_launches"] + 1 and after["failures"] == before["failures"]
     want = np.tanh(x.toArray().astype(np.float64) * 2.0 + 1.0)
     assert np.all(np.abs(got - want.sum(axis=0)) <= RED_RTOL * np.abs(want).sum(axis=0))
+
+
+def test_config5_step_is_one_pass_with_three_sinks(lazy_sums_ops):
+    """With the sums deferred as well, loss, weight gradient and bias gradient of the sharded step come out
+    of ONE generated kernel that reads x once.  The gradients equal those of the one-sink-per-program mode
+    bit for bit (same element values, same partition, same combination order); the loss agrees within the
+    reduction tolerance."""
+    from kten_b200.sharded import ShardedSigmoidGraph
+    ops = lazy_sums_ops
+    rows, cols = 4096, 1024                                   # 2^22 elements: generated kernels by default
+    x = D.uniform(rows * cols, 0, -1.0, 1.0, stream=0)
+    w = D.normal(cols, 0, 0.0, 0.02, stream=1)
+    b = D.uniform(cols, 0, -0.1, 0.1, stream=2)
+    res = []
+    for defer in (False, True):
+        ops.deferSums = defer
+        with ops.garbageCollector():
+            g = ShardedSigmoidGraph(ops, ops.createRaw([rows, cols], x), ops.createRaw([1, cols], w), ops.createRaw([cols], b))
+            m0, l0, before = ops.multiSinkEvaluations, ops.lib.ktc_launch_count(), expr_stats(ops)
+            for _ in range(2):
+                loss, gw, gb = g.step()
+                vals = (loss.toArray().copy(), gw.toArray().copy(), gb.toArray().copy())
+                g.release_step()
+            after = expr_stats(ops)
+            res.append(vals + (ops.multiSinkEvaluations - m0, ops.lib.ktc_launch_count() - l0, after["failures"] - before["failures"]))
+    ops.deferSums = True
+    (l1, gw1, gb1, m1, n1, f1), (l2, gw2, gb2, m2, n2, f2) = res
+    assert f1 == 0 and f2 == 0
+    assert m1 == 0 and m2 == 2                                # one multi-sink pass per step
+    assert n2 < n1
+    assert same_bits(gw1, gw2) and same_bits(gb1, gb2)
+    assert abs(float(l1[0]) - float(l2[0])) <= RED_RTOL * abs(float(l1[0]))
+
+
+def test_pending_sums_keep_the_semantics_of_sums_that_run_at_once(lazy_sums_ops):
+    rows, cols = 2048, 512                                    # 2^20 elements: the multi-sink kernel runs
+    xv, yv = D.uniform(rows * cols, 21, -1.0, 1.0), D.uniform(rows * cols, 22, -1.0, 1.0)
+    gv = D.uniform(cols, 23, -1.0, 1.0)
+
+    def script(o):
+        x, y = o.createRaw([rows, cols], xv), o.createRaw([rows, cols], yv)
+        g1, g2 = o.createRaw([1, cols], gv), o.createRaw([cols], gv)
+        d = x.minus(y)
+        loss = d.pow(2.0).mean()                          # pending
+        x.timesAssign(2.0)                                # overwrites an operand: the mean is of the old x
+        g1.plusAssign(d.times(y).sum(0, keepDimensions=True))
+        g1.plusAssign(d.sum(0, keepDimensions=True))      # a second update of the same buffer, in order
+        g2.plusAssign(d.times(0.5).sum(0))
+        g2.timesAssign(3.0)                               # in-place write to a buffer with a pending update
+        nested = d.minus(d.mean()).pow(2.0).sum()         # a sum over an expression that holds a pending sum
+        spread = g2.broadcastTo([rows, cols]).plus(1.0).sum()
+        p, q, r, t = d.exp().sum(), d.exp().sum(0), d.times(d).mean(), d.plus(y).sum(0, keepDimensions=True)    # four sinks, one pass
+        view = g1.view([cols])
+        return [loss, g1, g2, nested, spread, p, q, r, t, view, x]
+
+    m0 = lazy_sums_ops.multiSinkEvaluations
+    eager, lazy = both(lazy_sums_ops, script)
+    assert lazy_sums_ops.multiSinkEvaluations > m0
+    for k, (a, c) in enumerate(zip(eager, lazy)):
+        scale = np.abs(a).max() + 1.0
+        assert np.all(np.abs(a.astype(np.float64) - c) <= 2e-5 * scale), f"result {k}"
+    assert same_bits(eager[10], lazy[10]) and same_bits(lazy[1].reshape(-1), lazy[9])
+
+
+def test_multi_sink_call_checks_its_arguments(cuda_ops, gc_scope):
+    lib = cuda_ops.lib
+    rows, cols = 8, 128
+    x = cuda_ops.createRaw([rows, cols], D.uniform(rows * cols, 31, -1.0, 1.0))
+    o1, o2 = cuda_ops.createRaw([1]), cuda_ops.createRaw([cols])
+    ins = lambda op, d=0, a=0, b=0, k=0: op | (d << 8) | (a << 12) | (b << 16) | (k << 20)
+    shape, leaves, lsh = (C.c_int64 * 2)(rows, cols), (C.c_uint64 * 1)(x._buf()), (C.c_int64 * 2)(rows, cols)
+    outs, means = (C.c_uint64 * 2)(o1._buf(), o2._buf()), (C.c_int * 2)(0, 0)
+
+    def call(code, kinds, n_sinks=2):
+        arr = (C.c_uint32 * len(code))(*code)
+        return lib.ktc_expr_eval_multi(arr, len(code), None, 0, shape, 2, leaves, lsh, 1, None, 0, (C.c_int * 2)(*kinds), outs, means, n_sinks)
+
+    good = [ins(L.X_LOAD, 0, k=0), ins(L.X_ACC, a=0, k=0), ins(L.X_ACC, a=0, k=1)]
+    assert call(good, (L.EXPR_SUM_ALL, L.EXPR_SUM_ROWS)) == L.KTC_ENOTSUP           # 1024 elements: below expr_jit_min_elems
+    assert call(good, (L.EXPR_SUM_ALL, L.EXPR_STORE_ONLY)) == L.KTC_EINVAL          # not a summing kind
+    assert call(good[:2], (L.EXPR_SUM_ALL, L.EXPR_SUM_ROWS)) == L.KTC_EINVAL        # sink 1 is never fed
+    assert call(good, (L.EXPR_SUM_ALL, L.EXPR_SUM_ROWS), n_sinks=5) == L.KTC_EINVAL
+    assert call([ins(L.X_LOAD, 0, k=0), ins(L.X_ACC, a=0, k=0), ins(L.X_ACC, a=0, k=0)], (L.EXPR_SUM_ALL, L.EXPR_SUM_ROWS)) == L.KTC_EINVAL
+    L.check(lib.ktc_tune_set(b"expr_jit_min_elems", 0))
+    try:
+        L.check(call(good, (L.EXPR_SUM_ALL, L.EXPR_SUM_ROWS)))
+    finally:
+        L.check(lib.ktc_tune_set(b"expr_jit_min_elems", 1 << 20))
+    xa = x.toArray().astype(np.float64)
+    assert abs(float(o1.toArray()[0]) - xa.sum()) <= RED_RTOL * np.abs(xa).sum()
+    assert np.all(np.abs(o2.toArray() - xa.sum(axis=0)) <= RED_RTOL * np.abs(xa).sum(axis=0))

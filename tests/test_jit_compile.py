@@ -66,3 +66,37 @@ def test_program_from_the_expression_compiler_compiles():
     fixed = [1 if sh[0] == 1 else 0 for _, sh in prog.leaves]
     nbytes, ms = compile_only(prog.code, inner, fixed, 0, L.EXPR_SUM_ROWS)
     assert ms < 20000
+
+
+def test_multi_sink_program_compiles():
+    """Loss, weight gradient and bias gradient of the sharded step as ONE program with three sinks
+    (SUM_ALL mean, SUM_ROWS, SUM_ROWS), as the deferred layer emits it once sums are deferred too."""
+    lib = FakeLib()
+    shape = [4096, 1024]
+    x, w, b, y, g = (Z.leaf(lib, 1, shape), Z.leaf(lib, 2, [1, 1024]), Z.leaf(lib, 3, [1024]), Z.leaf(lib, 5, shape), Z.leaf(lib, 4, [1]))
+    bin_ = lambda op, p, q: Z.Node("bin", shape, op, (p, q))
+    s = Z.Node("un", shape, L.SIGMOID, (bin_(L.PLUS, bin_(L.TIMES, x, w), b),))
+    d = bin_(L.MINUS, s, y)
+    loss = Z.Node("square", shape, 0, (d,))
+    gp = bin_(L.TIMES, bin_(L.TIMES, Z.Node("bcast", shape, 0, (g,)), Z.const(2.0)), d)
+    t = bin_(L.PLUS, Z.Node("un", shape, L.NEG, (s,)), Z.const(1.0))
+    dz = bin_(L.TIMES, bin_(L.TIMES, t, s), gp)
+    prog, _, _ = Z.compile_program(shape, [], [loss, bin_(L.TIMES, dz, x), dz], 0)
+    accs = [(c >> 20) for c in prog.code if (c & 0xff) == L.X_ACC]
+    assert sorted(accs) == [0, 1, 2]
+    inner = [1 if sh[-1] != 1 else 0 for _, sh in prog.leaves]
+    fixed = [1 if sh[0] == 1 else 0 for _, sh in prog.leaves]
+    lib_ = L.load()
+    code = (C.c_uint32 * len(prog.code))(*prog.code)
+    n = len(inner)
+    nbytes, ms = C.c_int64(0), C.c_double(0)
+    kinds = (C.c_int * 3)(L.EXPR_SUM_ALL, L.EXPR_SUM_ROWS, L.EXPR_SUM_ROWS)
+    for rank3 in (0, 1):
+        rc = lib_.ktc_test_expr_compile_multi(code, len(prog.code), n, (C.c_int * n)(*inner), (C.c_int * n)(*fixed), rank3, kinds, 3,
+                                              C.byref(nbytes), C.byref(ms))
+        if rc == L.KTC_ENOTSUP:
+            pytest.skip("NVRTC is not installed here: " + lib_.ktc_last_error().decode())
+        assert rc == L.KTC_OK, lib_.ktc_last_error().decode()[:4000]
+        assert nbytes.value > 1000
+    bad = (C.c_int * 1)(L.EXPR_STORE_ONLY)
+    assert lib_.ktc_test_expr_compile_multi(code, len(prog.code), n, (C.c_int * n)(*inner), (C.c_int * n)(*fixed), 0, bad, 1, None, None) == L.KTC_EINVAL
