@@ -261,6 +261,11 @@ KTC_API int ktc_expr_eval_multi(const uint32_t* code, int n_code, const float* i
  * per-operation arithmetic, so results stay bit-identical --, compiles it once with NVRTC for
  * sm_100a and caches the kernel by program, as kten-opencl builds its kernels from source at
  * start-up (OCLKernels.kt).  Without NVRTC the interpreter kernel runs.
+ * Shape of the generated code (tunables, part of the cache key; `expr_jit_multi_*` for programs
+ * with several sums): `expr_jit_rows` rows per thread and batch (4), `expr_jit_min_blocks` resident
+ * CTAs per SM asked of the compiler (none; 3 for several sums), `expr_jit_smem_acc` the double
+ * accumulators of the sums live in shared memory (off; on for several sums, whose nine accumulators
+ * would otherwise cost 18 registers).  None of them changes a result bit.
  * ktc_expr_stats fills out6 with: kernels compiled, launches of generated kernels, launches of the
  * interpreter kernel, failed compilations, microseconds spent compiling, NVRTC present (1 / 0 /
  * -1 = not tried yet).  ktc_expr_jit_log copies the log of the last failed compilation. */

@@ -420,3 +420,36 @@ def test_multi_sink_call_checks_its_arguments(cuda_ops, gc_scope):
     xa = x.toArray().astype(np.float64)
     assert abs(float(o1.toArray()[0]) - xa.sum()) <= RED_RTOL * np.abs(xa).sum()
     assert np.all(np.abs(o2.toArray() - xa.sum(axis=0)) <= RED_RTOL * np.abs(xa).sum(axis=0))
+
+
+def test_generated_kernel_shape_tunables_do_not_change_a_bit(lazy_sums_ops):
+    """Rows per batch, the occupancy hint and where the double accumulators live only reshape the generated code:
+    the sharded step's loss and gradients are the same bits under every setting."""
+    from kten_b200.sharded import ShardedSigmoidGraph
+    ops = lazy_sums_ops
+    rows, cols = 2048, 1024
+    x = D.uniform(rows * cols, 40, -1.0, 1.0)
+    w = D.normal(cols, 40, 0.0, 0.5, stream=1)
+    b = D.uniform(cols, 40, -0.1, 0.1, stream=2)
+    keys = (b"expr_jit_multi_rows", b"expr_jit_multi_min_blocks", b"expr_jit_multi_smem_acc")
+    results = []
+    before = expr_stats(ops)
+    try:
+        for setting in ((4, 3, 1), (1, 0, 0), (2, 4, 1), (8, 0, 0), (4, 0, 0)):
+            for key, v in zip(keys, setting):
+                L.check(ops.lib.ktc_tune_set(key, v))
+            with ops.garbageCollector():
+                g = ShardedSigmoidGraph(ops, ops.createRaw([rows, cols], x), ops.createRaw([1, cols], w), ops.createRaw([cols], b))
+                m0 = ops.multiSinkEvaluations
+                loss, gw, gb = g.step()
+                results.append((loss.toArray().copy(), gw.toArray().copy(), gb.toArray().copy()))
+                assert ops.multiSinkEvaluations == m0 + 1
+                g.release_step()
+    finally:
+        for key, v in zip(keys, (4, 3, 1)):
+            L.check(ops.lib.ktc_tune_set(key, v))
+    after = expr_stats(ops)
+    assert after["failures"] == before["failures"] and after["compiled"] >= before["compiled"] + 4
+    for other in results[1:]:
+        for p, q in zip(results[0], other):
+            assert same_bits(p, q)
