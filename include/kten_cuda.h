@@ -229,7 +229,7 @@ KTC_API int ktc_reduce_all_noalloc(int op, ktc_buf out, ktc_buf in, int64_t n);
 enum { KTC_X_LOAD = 1, KTC_X_CONST, KTC_X_ADD, KTC_X_SUB, KTC_X_MUL, KTC_X_DIV, KTC_X_POW, KTC_X_NEG, KTC_X_RCP,
        KTC_X_SQUARE, KTC_X_EXP, KTC_X_LOG, KTC_X_TANH, KTC_X_SIGMOID, KTC_X_CLAMP, KTC_X_CMP_LT, KTC_X_CMP_LTE,
        KTC_X_CMP_GT, KTC_X_CMP_GTE, KTC_X_STORE, KTC_X_ACC };
-enum { KTC_EXPR_STORE_ONLY = 0, KTC_EXPR_SUM_ALL = 1, KTC_EXPR_SUM_ROWS = 2, KTC_EXPR_MULTI = 3 };
+enum { KTC_EXPR_STORE_ONLY = 0, KTC_EXPR_SUM_ALL = 1, KTC_EXPR_SUM_ROWS = 2, KTC_EXPR_MULTI = 3, KTC_EXPR_SUM_LAST = 4 };
 KTC_API int ktc_expr_eval(const uint32_t* code, int n_code, const float* imm, int n_imm,
                           const int64_t* shape, int ndim,
                           const ktc_buf* leaves, const int64_t* leaf_shapes, int n_leaves,
@@ -240,8 +240,11 @@ KTC_API int ktc_expr_eval(const uint32_t* code, int n_code, const float* imm, in
  * operands (Mean.doForward, AggregatingFunctions.kt; the mayUnexpand sums of Plus / Times backward,
  * BasicFunctions.kt:12-55), so a backend that defers the sums as well can read those operands once.
  * Same program encoding; an ACC instruction's k field names the sink (0 .. n_sinks-1, at most
- * KTC_EXPR_MAX_SINKS), sink j is of kind sink_kinds[j] (KTC_EXPR_SUM_ALL or KTC_EXPR_SUM_ROWS, with
- * means[j] != 0 dividing a SUM_ALL by the element count) and writes sink_outs[j].  The iteration
+ * KTC_EXPR_MAX_SINKS), sink j is of kind sink_kinds[j] (KTC_EXPR_SUM_ALL, KTC_EXPR_SUM_ROWS or
+ * KTC_EXPR_SUM_LAST, with means[j] != 0 dividing a SUM_ALL by the element count) and writes
+ * sink_outs[j].  SUM_LAST sums over the innermost dimension of `shape` -- sum(-1), the row sums of a
+ * softmax (SoftmaxCrossEntropy.kt:44,49) -- into one float per row (all leading dimensions
+ * flattened); ktc_expr_eval accepts it as a single sink as well.  The iteration
  * space is partitioned as for a single SUM_ROWS sink, and every sink accumulates as its single-sink
  * call does (float runs folded into doubles, fixed combination order): SUM_ROWS results equal those
  * of separate ktc_expr_eval calls bit for bit, a SUM_ALL result is the same sum taken over a

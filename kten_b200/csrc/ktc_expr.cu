@@ -203,12 +203,13 @@ static int expr_eval(const uint32_t* code, int n_code, const float* imm, int n_i
     if (n_leaves < 0 || n_leaves > kExprMaxLeaves || n_stores < 0 || n_stores > kExprMaxStores)
         return fail(KTC_EINVAL, "ktc_expr_eval: %d leaves / %d stores (at most %d / %d)", n_leaves, n_stores, kExprMaxLeaves, kExprMaxStores);
     if (ndim < 1 || ndim > KTC_MAX_DIMS || !shape) return fail(KTC_EINVAL, "ktc_expr_eval: bad shape");
-    if (sink < KTC_EXPR_STORE_ONLY || sink > KTC_EXPR_MULTI) return fail(KTC_EINVAL, "ktc_expr_eval: unknown sink %d", sink);
+    if (sink < KTC_EXPR_STORE_ONLY || sink > KTC_EXPR_MULTI) return fail(KTC_EINVAL, "ktc_expr_eval: unknown sink %d", sink);      // SUM_LAST arrives as a one-sink MULTI
     const bool multi = sink == KTC_EXPR_MULTI;
     if (multi) {
         if (n_sinks < 1 || n_sinks > kExprMaxSinks || !sink_kinds || !sink_outs || !means) return fail(KTC_EINVAL, "ktc_expr_eval_multi: %d sinks (1..%d allowed)", n_sinks, kExprMaxSinks);
         for (int j = 0; j < n_sinks; ++j)
-            if (sink_kinds[j] != KTC_EXPR_SUM_ALL && sink_kinds[j] != KTC_EXPR_SUM_ROWS) return fail(KTC_EINVAL, "ktc_expr_eval_multi: sink %d is of unknown kind %d", j, sink_kinds[j]);
+            if (sink_kinds[j] != KTC_EXPR_SUM_ALL && sink_kinds[j] != KTC_EXPR_SUM_ROWS && sink_kinds[j] != KTC_EXPR_SUM_LAST) return fail(KTC_EINVAL, "ktc_expr_eval_multi: sink %d is of unknown kind %d", j, sink_kinds[j]);
+            else if (sink_kinds[j] != KTC_EXPR_SUM_ALL && means[j]) return fail(KTC_EINVAL, "ktc_expr_eval_multi: sink %d: only a SUM_ALL sink can be a mean", j);
     }
     const bool keep_inner = sink == KTC_EXPR_SUM_ROWS || multi;      // the innermost dimension of `shape` is not merged
     int64_t total = 1;
@@ -308,7 +309,7 @@ static int expr_eval(const uint32_t* code, int n_code, const float* imm, int n_i
     if (multi) {
         for (int j = 0; j < n_sinks; ++j) {
             KTC_TRY(resolve(sink_outs[j], &mout[j])); KTC_TRY(adopt(mout[j]));
-            const int64_t need_out = sink_kinds[j] == KTC_EXPR_SUM_ALL ? 1 : D[2];
+            const int64_t need_out = sink_kinds[j] == KTC_EXPR_SUM_ALL ? 1 : sink_kinds[j] == KTC_EXPR_SUM_ROWS ? D[2] : rows;
             if (mout[j].n < need_out) return fail(KTC_EINVAL, "ktc_expr_eval_multi: output of sink %d holds %lld floats, %lld needed", j, (long long)mout[j].n, (long long)need_out);
         }
         Sg = (Sg + 7) & ~(int64_t)7;
@@ -332,21 +333,25 @@ static int expr_eval(const uint32_t* code, int n_code, const float* imm, int n_i
     if (multi) {
         // one partial-sum area per sink, laid out as the single-sink launches lay theirs out, then each
         // sink's own second pass
+        auto part_size = [&](int kind) { return kind == KTC_EXPR_SUM_ALL ? grid : kind == KTC_EXPR_SUM_ROWS ? groups * D[2] : a.col_tiles * rows; };
         int64_t need = 0;
-        for (int j = 0; j < n_sinks; ++j) need += sink_kinds[j] == KTC_EXPR_SUM_ALL ? grid : groups * D[2];
+        for (int j = 0; j < n_sinks; ++j) need += part_size(sink_kinds[j]);
         KTC_TRY(scratch.get(d, need * 2));
         double* base = reinterpret_cast<double*>(scratch.ptr);
         a.n_sinks = n_sinks;
         for (int j = 0; j < n_sinks; ++j) {
             a.sink_kind[j] = sink_kinds[j];
             a.mpart[j] = base;
-            base += sink_kinds[j] == KTC_EXPR_SUM_ALL ? grid : groups * D[2];
+            base += part_size(sink_kinds[j]);
         }
         KTC_TRY(launch_expr(d, a, n_leaves, sink, grid, total));
         for (int j = 0; j < n_sinks; ++j) {
             if (sink_kinds[j] == KTC_EXPR_SUM_ALL) {
                 if (means[j]) k_combine_block<1, SumAcc><<<1, 512, 0, d->stream>>>(a.mpart[j], mout[j].ptr, nullptr, 1, (int)grid, total);
                 else          k_combine_block<0, SumAcc><<<1, 512, 0, d->stream>>>(a.mpart[j], mout[j].ptr, nullptr, 1, (int)grid, total);
+            } else if (sink_kinds[j] == KTC_EXPR_SUM_LAST) {
+                // partial[column tile][row]: one thread per row adds the tiles in order
+                k_combine_thread<0, SumAcc><<<(int)((rows + 255) / 256), 256, 0, d->stream>>>(a.mpart[j], mout[j].ptr, nullptr, rows, (int)a.col_tiles, D[2]);
             } else if (groups >= 64 || D[2] < 4096) {
                 const int64_t blocks = (D[2] * 32 + 255) / 256;
                 k_combine_warp<0, SumAcc><<<(int)blocks, 256, 0, d->stream>>>(a.mpart[j], mout[j].ptr, nullptr, D[2], (int)groups, rows);
@@ -388,6 +393,10 @@ extern "C" int ktc_expr_eval(const uint32_t* code, int n_code, const float* imm,
                              const ktc_buf* stores, int n_stores,
                              int sink, ktc_buf sink_out, int mean) {
     if (sink == KTC_EXPR_MULTI) return fail(KTC_EINVAL, "ktc_expr_eval: several sinks go through ktc_expr_eval_multi");
+    if (sink == KTC_EXPR_SUM_LAST) {
+        const int kind = KTC_EXPR_SUM_LAST;
+        return expr_eval(code, n_code, imm, n_imm, shape, ndim, leaves, leaf_shapes, n_leaves, stores, n_stores, KTC_EXPR_MULTI, 0, 0, &kind, &sink_out, &mean, 1);
+    }
     return expr_eval(code, n_code, imm, n_imm, shape, ndim, leaves, leaf_shapes, n_leaves, stores, n_stores, sink, sink_out, mean, nullptr, nullptr, nullptr, 0);
 }
 

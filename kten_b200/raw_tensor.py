@@ -468,6 +468,10 @@ class CUDARawTensor:
         if self.isDeferred and op == L.SUM and a == 0 and len(self.shape) >= 2 and self._node.kind != "reduce":
             final = list(res_shape) if keep_dimensions else list(res_shape[1:])
             res = self.ops._sum_leading_axis(self, final)       # fused with the pending expression when possible
+        elif self.isDeferred and op == L.SUM and a == len(self.shape) - 1 and len(self.shape) >= 2 and self.shape[a] > 1 \
+                and self._node.kind != "reduce" and self.ops.deferSums:
+            final = list(res_shape) if keep_dimensions else list(res_shape[:-1])
+            res = self.ops._defer_sum(self, L.EXPR_SUM_LAST, False, final)      # row sums: a pending sum over the last axis
         if res is None:
             res = self._new(res_shape)
             L.check(self.ops.lib.ktc_reduce_axis(op, res._buf(), self._buf(), outer, length, inner))

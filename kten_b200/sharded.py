@@ -111,10 +111,13 @@ class PeerMemoryCollective:
 
 
 class LocalCollective:
-    """World size 1: nothing to exchange."""
+    """World size 1: nothing to exchange.  The values are still looked up the way a collective looks
+    them up (their buffer handles), so that whatever the backend deferred -- pending expressions,
+    pending sums -- is computed inside the step, exactly as on a rank of a larger world."""
 
     def allreduce_sum(self, raws: Sequence) -> None:
-        return None
+        for r in raws:
+            getattr(r, "storeReference", None)          # a backend without deferred values has nothing to look up
 
 
 class ShardedSigmoidGraph:

@@ -380,10 +380,22 @@ class CUDATensorOperations:
             if not ready:
                 raise RuntimeError("pending sums depend on one another")
             waiting = [nd for nd in waiting if not any(nd is r for r in ready)]
-            groups = {}
+            # one pass per iteration space; leading-axis sums view the space as [A, rest], last-axis sums need its
+            # innermost dimension, so the two kinds do not share a pass (full sums join either)
+            by_shape = {}
             for nd in ready:
-                groups.setdefault(tuple(nd.args[0].shape), []).append(nd)
-            for shape, nodes in groups.items():
+                by_shape.setdefault(tuple(nd.args[0].shape), []).append(nd)
+            groups = []
+            for shape, nodes in by_shape.items():
+                last = [nd for nd in nodes if nd.op == L.EXPR_SUM_LAST]
+                rows = [nd for nd in nodes if nd.op == L.EXPR_SUM_ROWS]
+                full = [nd for nd in nodes if nd.op == L.EXPR_SUM_ALL]
+                if rows or not last:
+                    groups.append((shape, rows + full))
+                    full = []
+                if last:
+                    groups.append((shape, last + full))
+            for shape, nodes in groups:
                 for i in range(0, len(nodes), L.EXPR_MAX_SINKS):
                     chunk = nodes[i:i + L.EXPR_MAX_SINKS]
                     if len(chunk) > 1 and self._try_fused_sums(list(shape), chunk):
@@ -434,6 +446,8 @@ class CUDATensorOperations:
         mean = nd.imm[0] != 0
         if nd.op == L.EXPR_SUM_ALL:
             ok = self._try_fused(shape, [], [], [], acc=expr, sink=L.EXPR_SUM_ALL, sink_out=out, mean=mean)
+        elif nd.op == L.EXPR_SUM_LAST:
+            ok = self._try_fused(shape, [], [], [], acc=expr, sink=L.EXPR_SUM_LAST, sink_out=out)
         else:
             ok = self._try_fused(shape, [], [], [], acc=expr, sink=L.EXPR_SUM_ROWS, sink_out=out, reshape=self._as_rows(shape))
         if not ok:
@@ -446,6 +460,8 @@ class CUDATensorOperations:
             try:
                 if nd.op == L.EXPR_SUM_ALL:
                     L.check(self.lib.ktc_reduce_all(L.MEAN if mean else L.SUM, out, h, n))
+                elif nd.op == L.EXPR_SUM_LAST:
+                    L.check(self.lib.ktc_reduce_axis(L.SUM, out, h, n // shape[-1], shape[-1], 1))
                 else:
                     L.check(self.lib.ktc_reduce_axis(L.SUM, out, h, 1, shape[0], n // shape[0]))
             finally:

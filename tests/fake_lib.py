@@ -202,6 +202,8 @@ class FakeLib:
         for j, (kind, out, mean_j) in enumerate(sinks):
             if kind == L.EXPR_SUM_ALL:
                 self._get(out)[0] = np.float32(accs[j].sum() / (total if mean_j else 1))
+            elif kind == L.EXPR_SUM_LAST:
+                self._get(out)[:total // shp[-1]] = accs[j].reshape(-1, shp[-1]).sum(axis=1).astype(np.float32)
             else:
                 self._get(out)[:shp[-1]] = accs[j].reshape(-1, shp[-1]).sum(axis=0).astype(np.float32)
         return 0

@@ -103,3 +103,55 @@ def test_config4_reductions_checksums(cuda_ops, gc_scope):
     assert np.array_equal(mid_max.toArray(), h3.max(axis=1))
     # the grand maximum through both routes
     assert float(row_max.max(0).toArray()[0]) == float(mid_max.max(0).max(0).toArray()[0]) == float(hx.max())
+
+
+def test_config5_step_modes_agree_at_full_size(cuda_ops, gc_scope):
+    """The sharded-graph step on the whole x[262144, 1024] in the backend's three execution modes -- call by call,
+    deferred with one sum per pass, deferred with loss and both gradients in ONE pass -- and as two row shards
+    whose partial results are added (what the ranks of a sharded run compute).  The two deferred modes give the
+    same gradient bits; everything else agrees within 1e-5 of the sum of the absolute terms, which the device
+    computes itself (the terms of the loss and of grad b are positive, so those sums are their own bound)."""
+    from kten_b200.sharded import ShardedSigmoidGraph
+    ops = cuda_ops
+    rows, cols = 262144, 1024
+    hx = D.uniform(rows * cols, 0, -1.0, 1.0)
+    hw = D.normal(cols, 0, 0.0, 0.02, stream=1)
+    hb = D.uniform(cols, 0, -0.1, 0.1, stream=2)
+    x, w, b = ops.createRaw([rows, cols], hx), ops.createRaw([1, cols], hw), ops.createRaw([cols], hb)
+
+    def run(xr, lazy, defer):
+        ops.lazy, ops.deferSums = lazy, defer
+        try:
+            g = ShardedSigmoidGraph(ops, xr, w, b)
+            loss, gw, gb = g.step()
+            out = (float(loss.toArray()[0]), gw.toArray().reshape(-1).astype(np.float64), gb.toArray().astype(np.float64))
+            g.release_step()
+            return out
+        finally:
+            ops.lazy, ops.deferSums = False, True
+
+    m0 = ops.multiSinkEvaluations
+    eager = run(x, False, True)
+    single = run(x, True, False)
+    multi = run(x, True, True)
+    assert ops.multiSinkEvaluations == m0 + 1
+    half = rows // 2
+    top, bottom = x.narrow(0, 0, half), x.narrow(0, half, half)
+    parts = [run(top, True, True), run(bottom, True, True)]
+    sharded = tuple(p + q for p, q in zip(*parts))
+    # bound on the absolute terms: s = sigmoid(x*w+b), gz = 2 s s (1-s) >= 0, so sum|gz| = grad b and sum|gz x| = sum(gz |x|)
+    s = x.times(w).plus(b).sigmoid()
+    gz = s.times(s).times(s.unaryMinus().plus(1.0)).times(2.0)
+    abs_gw = gz.times(x.abs()).sum(0).toArray().astype(np.float64)
+    assert np.array_equal(single[1], multi[1]) and np.array_equal(single[2], multi[2])
+    for other in (single, multi, sharded):
+        assert abs(other[0] - eager[0]) <= 1e-5 * eager[0]
+        assert np.all(np.abs(other[2] - eager[2]) <= 1e-5 * eager[2])
+        assert np.all(np.abs(other[1] - eager[1]) <= 1e-5 * abs_gw)
+    # closed form in float64 on a sample of columns
+    colsamp = [0, 1, 511, 1023]
+    X = hx.reshape(rows, cols)[:, colsamp].astype(np.float64)
+    S = 1.0 / (1.0 + np.exp(-(X * hw[colsamp] + hb[colsamp])))
+    GZ = 2.0 * S * S * (1.0 - S)
+    assert np.all(np.abs(multi[2][colsamp] - GZ.sum(axis=0)) <= 1e-5 * GZ.sum(axis=0))
+    assert np.all(np.abs(multi[1][colsamp] - (GZ * X).sum(axis=0)) <= 1e-5 * np.abs(GZ * X).sum(axis=0))

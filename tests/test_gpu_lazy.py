@@ -453,3 +453,58 @@ def test_generated_kernel_shape_tunables_do_not_change_a_bit(lazy_sums_ops):
     for other in results[1:]:
         for p, q in zip(results[0], other):
             assert same_bits(p, q)
+
+
+@pytest.mark.parametrize("shape", [[4096, 260], [64, 32, 516], [1024, 1024], [3, 128, 2052]], ids=str)
+def test_last_axis_sum_sink(cuda_ops, gc_scope, shape):
+    """ktc_expr_eval with the SUM_LAST sink (generated kernel): exp(x) stored and summed along the innermost axis, on
+    extents that leave the last 128-column tile partly (or almost entirely) empty."""
+    lib = cuda_ops.lib
+    n = int(np.prod(shape))
+    rows = n // shape[-1]
+    xv = D.uniform(n, 51, -1.0, 1.0)
+    x = cuda_ops.createRaw(shape, xv)
+    e, sums = cuda_ops.createRaw(shape), cuda_ops.createRaw([rows])
+    ins = lambda op, d=0, a=0, b=0, k=0: op | (d << 8) | (a << 12) | (b << 16) | (k << 20)
+    code = [ins(L.X_LOAD, 0, k=0), ins(L.X_EXP, 1, 0), ins(L.X_STORE, a=1, k=0), ins(L.X_ACC, a=1, k=0)]
+    arr = (C.c_uint32 * len(code))(*code)
+    nd = len(shape)
+    shp = (C.c_int64 * nd)(*shape)
+    L.check(lib.ktc_tune_set(b"expr_jit_min_elems", 0))
+    try:
+        before = expr_stats(cuda_ops)
+        L.check(lib.ktc_expr_eval(arr, len(code), None, 0, shp, nd, (C.c_uint64 * 1)(x._buf()), shp, 1, (C.c_uint64 * 1)(e._buf()), 1,
+                                  L.EXPR_SUM_LAST, sums._buf(), 0))
+        after = expr_stats(cuda_ops)
+    finally:
+        L.check(lib.ktc_tune_set(b"expr_jit_min_elems", 1 << 20))
+    assert after["jit_launches"] == before["jit_launches"] + 1 and after["failures"] == before["failures"]
+    got_e = e.toArray().reshape(rows, shape[-1])
+    assert same_bits(got_e.reshape(-1), cuda_ops.createRaw([n], xv).exp().toArray())
+    want = got_e.astype(np.float64).sum(axis=1)
+    assert np.all(np.abs(sums.toArray() - want) <= RED_RTOL * want)
+    assert lib.ktc_expr_eval(arr, len(code), None, 0, shp, nd, (C.c_uint64 * 1)(x._buf()), shp, 1, (C.c_uint64 * 1)(e._buf()), 1,
+                             L.EXPR_SUM_LAST, sums._buf(), 1) == L.KTC_EINVAL          # a mean over the last axis is not offered
+
+
+def test_softmax_normalisations_as_pending_last_axis_sums(lazy_sums_ops):
+    rows, cols = 2048, 512                                   # 2^20 elements: generated kernels
+    xv = D.uniform(rows * cols, 31, -2.0, 2.0)
+
+    def script(o):
+        x = o.createRaw([rows, cols], xv)
+        m = x.max(-1, keepDimensions=True)
+        e = x.minus(m).exp()
+        z = e.sum(-1, keepDimensions=True)
+        total = e.sum()                                    # same iteration space: one pass with two sinks
+        sm = e.div(z)
+        z2 = sm.sum(-1)                                    # holds the pending z: waits for it
+        norm = sm.div(z2.view([rows, 1])).clamp(1e-7, 1.0 - 1e-7).log()
+        return [z, total, z2, norm, sm]
+
+    m0, u0 = lazy_sums_ops.multiSinkEvaluations, lazy_sums_ops.unfusedEvaluations
+    eager, lazy = both(lazy_sums_ops, script)
+    assert lazy_sums_ops.multiSinkEvaluations == m0 + 1 and lazy_sums_ops.unfusedEvaluations == u0
+    for k, (a, c) in enumerate(zip(eager, lazy)):
+        assert a.shape == c.shape
+        assert np.all(np.abs(a.astype(np.float64) - c) <= 1e-5 * (np.abs(a) + 1e-3)), f"result {k}"

@@ -269,18 +269,19 @@ def test_data_movement_full_size_properties(cuda_ops, gc_scope):
     assert float(d3.abs().sum().toArray()[0]) == 0.0
 
 
-@pytest.mark.parametrize("deferred", [False, True], ids=["call_by_call", "deferred"])
-def test_softmax_cross_entropy_matches_oracle(cuda_ops, gc_scope, deferred):
-    """SoftmaxCrossEntropy at the reference test's size ([256, 2048] logits): the reference's own
+@pytest.mark.parametrize("deferred,rows", [(False, 256), (True, 256), (True, 1024)], ids=["call_by_call", "deferred", "deferred_generated_kernels"])
+def test_softmax_cross_entropy_matches_oracle(cuda_ops, gc_scope, deferred, rows):
+    """SoftmaxCrossEntropy at the reference test's size ([256, 2048] logits; [1024, 2048] is large enough for the
+    deferred mode to run generated kernels with last-axis sums): the reference's own
     property holds on the device, and loss and gradient agree with the CPU oracle running the same
     call sequence.  Not bit-exact: exp and log are within 2 ulp and the row sums use a different tree,
     so the tolerance is 2e-6 on the loss (4 ulp at log 2048 = 7.6) and 1e-8 on the gradient (entries < 4e-3)."""
     from tests.kten_cases import softmax_cross_entropy_property
     cuda_ops.lazy = deferred
     try:
-        loss, grad, _, _ = softmax_cross_entropy_property(cuda_ops)
+        loss, grad, _, _ = softmax_cross_entropy_property(cuda_ops, rows=rows)
     finally:
         cuda_ops.lazy = False
-    want_loss, want_grad, _, _ = softmax_cross_entropy_property(ORACLE)
+    want_loss, want_grad, _, _ = softmax_cross_entropy_property(ORACLE, rows=rows)
     assert abs(float(loss[0]) - float(want_loss[0])) <= 2e-6
     assert float(np.abs(grad.astype(np.float64) - want_grad.astype(np.float64)).max()) <= 1e-8

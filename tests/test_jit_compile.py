@@ -100,3 +100,22 @@ def test_multi_sink_program_compiles():
         assert nbytes.value > 1000
     bad = (C.c_int * 1)(L.EXPR_STORE_ONLY)
     assert lib_.ktc_test_expr_compile_multi(code, len(prog.code), n, (C.c_int * n)(*inner), (C.c_int * n)(*fixed), 0, bad, 1, None, None) == L.KTC_EINVAL
+
+
+def test_last_axis_sum_sink_compiles():
+    """exp(x - rowmax) with its row sums (the first softmax normalisation), alone and beside other sums."""
+    body = [ins(L.X_LOAD, 0, k=0), ins(L.X_LOAD, 1, k=1), ins(L.X_SUB, 2, 0, 1), ins(L.X_EXP, 3, 2), ins(L.X_STORE, a=3, k=0)]
+    lib = L.load()
+    for kinds, tail in (((L.EXPR_SUM_LAST,), [ins(L.X_ACC, a=3, k=0)]),
+                        ((L.EXPR_SUM_LAST, L.EXPR_SUM_ALL), [ins(L.X_ACC, a=3, k=0), ins(L.X_ACC, a=2, k=1)]),
+                        ((L.EXPR_SUM_ROWS, L.EXPR_SUM_LAST, L.EXPR_SUM_LAST), [ins(L.X_ACC, a=3, k=0), ins(L.X_ACC, a=3, k=1), ins(L.X_ACC, a=2, k=2)])):
+        prog = body + tail
+        code = (C.c_uint32 * len(prog))(*prog)
+        for rank3 in (0, 1):
+            nbytes = C.c_int64(0)
+            rc = lib.ktc_test_expr_compile_multi(code, len(prog), 2, (C.c_int * 2)(1, 0), (C.c_int * 2)(0, 0), rank3,
+                                                 (C.c_int * len(kinds))(*kinds), len(kinds), C.byref(nbytes), None)
+            if rc == L.KTC_ENOTSUP:
+                pytest.skip("NVRTC is not installed here: " + lib.ktc_last_error().decode())
+            assert rc == L.KTC_OK, lib.ktc_last_error().decode()[:4000]
+            assert nbytes.value > 1000

@@ -218,3 +218,29 @@ def test_a_pending_sum_nobody_reads_is_never_computed():
         assert kept.toArray().shape == (8,)
         assert ops.lib.calls == ["expr_eval"] and ops.lib.multi_calls == 0     # only the sum that was read
     assert ops.lib.live_buffers() == 0
+
+
+def test_last_axis_sums_wait_and_share_a_pass():
+    """The two normalisations of a softmax (SoftmaxCrossEntropy.kt:40-52): the row sums are pending sums over the
+    last axis, the second one waits for the first, and a full sum over the same expression joins the pass."""
+    rows, cols = 12, 16
+    xv = D.uniform(rows * cols, 31, -2.0, 2.0)
+
+    def script(o):
+        x = o.createRaw([rows, cols], xv)
+        m = x.max(-1, keepDimensions=True)
+        e = x.minus(m).exp()
+        z = e.sum(-1, keepDimensions=True)
+        total = e.sum()                                    # same iteration space: one pass with two sinks
+        sm = e.div(z)
+        z2 = sm.sum(-1)                                    # holds the pending z: waits for it
+        norm = sm.div(z2.view([rows, 1])).clamp(1e-7, 1.0 - 1e-7).log()
+        return [z, total, z2, norm, sm]
+
+    eager, lazy, stats = both(script)
+    for k, (a, c) in enumerate(zip(eager, lazy)):
+        assert a.shape == c.shape and np.allclose(a, c, rtol=2e-6, atol=1e-6), f"result {k}"
+    assert eager[0].shape == (rows, 1) and eager[2].shape == (rows,)
+    assert stats[1][0] == 0
+    calls = stats[1][2]
+    assert "unary" not in calls and calls.count("reduce_axis") == 1          # only the row maximum ran as a reduction call
