@@ -505,8 +505,43 @@ def run_other_ops(ops, lib, L, D, steps):
         L.check(lib.ktc_timer_stop(ops.device, C.byref(ms)))
         per = ms.value / reps
         out.append({"name": name, "ms": round(per, 4), "gbs": round(nbytes / per / 1e6, 1)})
-    for r in (x3, xr, xm, left, right, acc, idx, rows, mask, x):
+    for r in (x3, xr, xm, left, right, acc, idx, rows, mask):
         r.release()
+    # SoftmaxCrossEntropy forward + backward (functions/nn/SoftmaxCrossEntropy.kt) on [131072, 2048] logits through the
+    # autograd caller, call by call and with elementwise calls and row sums deferred; algorithmic bytes: the logits
+    # read once, their gradient written once
+    from kten_b200 import autograd as AG
+    logits = AG.Variable(ops, x.view([131072, 2048]))
+    targets = AG.NoGradVariable(ops, ops.createRaw([131072], np.floor(D.uniform(131072, 15, 0.0, 2047.99)).astype(np.float32)))
+
+    def xent():
+        logits.zeroGrad()
+        loss = logits.softmaxCrossEntropy(targets)
+        loss.backward()
+        logits.gradient.storeReference
+
+    for mode, label in ((False, "call by call"), (True, "deferred")):
+        ops.lazy = mode
+        try:
+            for _ in range(4):                              # the buffer pool settles over the first steps
+                with ops.garbageCollector():
+                    xent()
+            ops.synchronize()
+            l0 = lib.ktc_launch_count()
+            L.check(lib.ktc_timer_start(ops.device))
+            for _ in range(reps):
+                with ops.garbageCollector():
+                    xent()
+            L.check(lib.ktc_timer_stop(ops.device, C.byref(ms)))
+        finally:
+            ops.lazy = False
+        per = ms.value / reps
+        out.append({"name": f"softmaxCrossEntropy [131072,2048] forward + backward, {label}", "ms": round(per, 4), "gbs": round(2 * G / per / 1e6, 1),
+                    "launches": (lib.ktc_launch_count() - l0) / reps})
+    logits.gradient.release()
+    logits.getRawValue().release()
+    targets.getRawValue().release()
+    x.release()
     return out
 
 
@@ -788,6 +823,34 @@ def run_single_case(args):
         ms = C.c_float(0)
         L.check(lib.ktc_timer_stop(0, C.byref(ms)))
         print(json.dumps({"case": name, "elements": rows * cols, "ms": ms.value / args.reps,
+                          "launches_per_step": (lib.ktc_launch_count() - l0) / args.reps}))
+        return 0
+    if name in ("x.softmax_eager", "x.softmax_deferred"):
+        # SoftmaxCrossEntropy forward + backward on [n / 2048, 2048] logits through the autograd caller
+        from kten_b200 import autograd as AG
+        cols = 2048
+        rows = max(1, n // cols)
+        logits = AG.Variable(ops, ops.createRaw([rows, cols], D.uniform(rows * cols, 11, 0.1, 2.0)))
+        targets = AG.NoGradVariable(ops, ops.createRaw([rows], np.floor(D.uniform(rows, 15, 0.0, cols - 0.01)).astype(np.float32)))
+        ops.lazy = name.endswith("deferred")
+
+        def xent():
+            with ops.garbageCollector():
+                logits.zeroGrad()
+                logits.softmaxCrossEntropy(targets).backward()
+                logits.gradient.storeReference
+
+        for _ in range(4):                                  # the buffer pool settles over the first steps
+            xent()
+        ops.synchronize()
+        l0 = lib.ktc_launch_count()
+        L.check(lib.ktc_timer_start(0))
+        for _ in range(args.reps):
+            xent()
+        ms = C.c_float(0)
+        L.check(lib.ktc_timer_stop(0, C.byref(ms)))
+        per = ms.value / args.reps
+        print(json.dumps({"case": name, "elements": rows * cols, "ms": per, "gbs": 2 * 4.0 * rows * cols / per / 1e6,
                           "launches_per_step": (lib.ktc_launch_count() - l0) / args.reps}))
         return 0
     if name.startswith("x."):

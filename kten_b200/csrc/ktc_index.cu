@@ -504,8 +504,11 @@ int launch_gather_axis(Device* d, float* out, const float* in, const int64_t* in
         if (i < axis) outer *= index_shape[i]; else inner *= index_shape[i];
     }
     const int64_t in_total = outer * in_shape[axis] * inner;
-    // last axis, rows of 4 KB ... 160 KB: one CTA per row, the row staged in shared memory
+    // last axis, rows of 4 KB ... 160 KB: one CTA per row, the row staged in shared memory -- when the index picks at
+    // least one element in eight (a direct read costs a 32-byte sector per element; fewer picks, such as the one target
+    // per row of SoftmaxCrossEntropy, are cheaper read directly)
     if (covers && inner == 1 && in_shape[axis] >= 1024 && in_shape[axis] <= 40960 && index_shape[axis] < (1LL << 31) &&
+        index_shape[axis] * 8 >= in_shape[axis] &&
         outer <= 0x7fffffffLL && tune("gather_smem", 1) != 0) {
         const size_t smem = (size_t)in_shape[axis] * sizeof(float);
         if (smem > 48 * 1024)                                       // per device: cheap enough to repeat

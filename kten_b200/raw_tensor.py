@@ -640,6 +640,10 @@ class CUDARawTensor:
         a = SF.normalize_axis(self.shape, axis)
         if len(index.shape) != len(self.shape):
             raise ValueError(f"Gather expects the index to have the tensor's dimensions, got {index.shape} for {self.shape}")
+        if self.isDeferred and self.ops.lazy:
+            res = self.ops._gather_deferred(self, a, index)     # few picks from a pending expression: gather its operands instead
+            if res is not None:
+                return res
         res = self._new(index.shape)
         pi, n = L.shape_array(self.shape)
         px, _ = L.shape_array(index.shape)

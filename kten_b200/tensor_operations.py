@@ -469,6 +469,70 @@ class CUDATensorOperations:
                     self.lib.ktc_release(tmp)
         self._adopt(nd, out)
 
+    def _gather_deferred(self, t: CUDARawTensor, axis: int, index: CUDARawTensor) -> Optional[CUDARawTensor]:
+        """gather(axis, index) of a deferred tensor when the index picks few of its elements (the one target per
+        row of SoftmaxCrossEntropy.kt:53): elementwise operations commute with the pick, so the operands that are
+        in memory are gathered and the expression is rebuilt over the index's shape -- the same operations with
+        the same roundings on just the picked elements, and the full-size value is never written.  None: not
+        applicable, gather the evaluated tensor as usual."""
+        shape, ishape = list(t.shape), list(index.shape)
+        nd = len(shape)
+        if shape[axis] <= 1 or SF.to_store_size(ishape) * 8 > SF.to_store_size(shape):
+            return None
+        root = Z.strip(t._node)
+        if root.stored():
+            return None
+        # children-first walk of the unstored part; pending sums underneath are evaluated first (they are operands in memory then)
+        if self._pending and Z.has_pending_sum([root]):
+            self._run_pending()
+        order, _ = Z._toposort([root])
+        plan = {}                                             # node -> ("same",) | ("gather", padded shape) for operands in memory
+        for n in order:
+            if n.kind == "const" or not n.stored():
+                if n.kind == "reduce":
+                    return None
+                continue
+            padded = [1] * (nd - len(n.shape)) + list(n.shape)
+            if len(padded) != nd:
+                return None
+            if padded[axis] == 1:                             # broadcast along the axis: the pick does not touch it
+                if any(p != 1 and p != i for k, (p, i) in enumerate(zip(padded, ishape)) if k != axis):
+                    return None
+                plan[n] = ("same",)
+            elif padded[axis] == shape[axis] and all(p >= i for k, (p, i) in enumerate(zip(padded, ishape)) if k != axis):
+                plan[n] = ("gather", padded)
+            else:
+                return None
+        px, _ = L.shape_array(ishape)
+        new = {}
+        for n in order:
+            if n.kind == "const":
+                new[n] = n
+            elif n.stored():
+                if plan[n][0] == "same":
+                    new[n] = n
+                else:
+                    h = self._alloc_handle(SF.to_store_size(ishape))
+                    pi, _ = L.shape_array(plan[n][1])
+                    rc = self.lib.ktc_gather_axis(h, n.buf.handle, pi, index._buf(), px, nd, axis)
+                    if rc != L.KTC_OK:
+                        self.lib.ktc_release(h)
+                        L.check(rc)
+                    new[n] = Z.Node("leaf", ishape, buf=Z.BufferRef(self.lib, h, retain=False))
+            else:
+                args = [new[Z.strip(a)] for a in n.args]
+                out_shape = [1]
+                for a in args:
+                    if a.kind != "const":
+                        out_shape = SF.infer_implicit_broadcast_shape(out_shape, a.shape)
+                new[n] = Z.Node(n.kind, out_shape, n.op, args, n.imm)
+        node = new[root]
+        if list(node.shape) != ishape:
+            node = Z.Node("bcast", ishape, 0, (node,))
+        res = CUDARawTensor(ishape, None, self, node=node)
+        self._register(res._cell, node)
+        return res
+
     def _eager_into(self, node, shape, out_handle: int) -> None:
         """One step of the call-by-call evaluation: the operands of `node` are forced into memory
         (each as a fused program where possible), then the library call for `node` itself runs at the

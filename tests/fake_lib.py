@@ -150,6 +150,44 @@ class FakeLib:
         self._get(out)[:outer * inner] = O.aggregate(op, self._get(a)[:outer * length * inner].copy(), outer, length, inner)
         return 0
 
+    def ktc_gather_axis(self, out, inp, in_shape, index, index_shape, ndim, axis):
+        self._note("gather")
+        ins, ixs = _ints(in_shape, ndim), _ints(index_shape, ndim)
+        src = self._get(inp)[:int(np.prod(ins))].reshape(ins)
+        idx = self._get(index)[:int(np.prod(ixs))].reshape(ixs).astype(np.int64)
+        box = tuple(slice(None) if d == axis else slice(0, ixs[d]) for d in range(ndim))
+        self._get(out)[:idx.size] = np.take_along_axis(src[box], idx, axis).reshape(-1)
+        return 0
+
+    def ktc_scatter_axis_nd(self, mode, target, target_shape, index, index_shape, src, src_shape, ndim, axis, constant):
+        self._note("scatter")
+        ts, ixs = _ints(target_shape, ndim), _ints(index_shape, ndim)
+        tgt = self._get(target)[:int(np.prod(ts))].reshape(ts)
+        idx = self._get(index)[:int(np.prod(ixs))].reshape(ixs).astype(np.int64)
+        if mode != L.SCATTER_CONST:
+            ss = _ints(src_shape, ndim)
+            source = self._get(src)[:int(np.prod(ss))].reshape(ss)
+        for pos in np.ndindex(*ixs):                       # the reference's order: row-major over the index
+            dst = list(pos)
+            dst[axis] = idx[pos]
+            dst = tuple(dst)
+            if mode == L.SCATTER_CONST:
+                tgt[dst] = np.float32(constant)
+            elif mode == L.SCATTER_ADD:
+                tgt[dst] = np.float32(tgt[dst] + source[pos])
+            else:
+                tgt[dst] = source[pos]
+        return 0
+
+    def ktc_scatter_axis(self, target, index, src, outer, length, inner):
+        self._note("scatter")
+        tgt = self._get(target)[:outer * length * inner].reshape(outer, length, inner)
+        idx = self._get(index)[:outer * inner].reshape(outer, inner).astype(np.int64)
+        source = self._get(src)[:outer * inner].reshape(outer, inner)
+        o, i = np.meshgrid(np.arange(outer), np.arange(inner), indexing="ij")
+        tgt[o, idx, i] = source
+        return 0
+
     # ---- the fused expression call: the program encoding interpreted with the oracle's arithmetic ----
     def ktc_expr_eval_multi(self, code, n_code, imm, n_imm, shape, ndim, leaves, lshapes, n_leaves, stores, n_stores, kinds, outs, means, n_sinks):
         self.multi_calls += 1
