@@ -122,6 +122,28 @@ class KtenCudaError(RuntimeError):
         self.status = status
 
 
+def _preload_newest_nccl() -> None:
+    """libkten_cuda.so binds `libnccl.so.2` with dlopen at its first collective call, and a process holds one
+    library per soname.  Where a Python environment ships its own NCCL next to PyTorch (the `nvidia.nccl`
+    wheel), that copy must be the one in the process: if the system's older libnccl were picked up first, a
+    later `import torch` in the same process would fail on the symbols it lacks.  Loading the wheel's copy
+    here (when there is one) makes the order of imports irrelevant; without the wheel the system library is
+    used."""
+    import importlib.util
+    try:
+        spec = importlib.util.find_spec("nvidia.nccl")
+    except (ImportError, ValueError):
+        spec = None
+    for base in (spec.submodule_search_locations if spec is not None and spec.submodule_search_locations else []):
+        path = os.path.join(base, "lib", "libnccl.so.2")
+        if os.path.exists(path):
+            try:
+                C.CDLL(path, mode=C.RTLD_GLOBAL if hasattr(C, "RTLD_GLOBAL") else 0)
+            except OSError:
+                pass
+            return
+
+
 def load() -> C.CDLL:
     """Load the shared library (once) and attach the prototypes."""
     global _lib
@@ -131,6 +153,7 @@ def load() -> C.CDLL:
         raise ImportError(
             f"{LIB_PATH} is missing: build it with `python -m kten_b200.build` "
             "(nvcc, sm_100a).  kten_b200 has no CPU or PyTorch fallback.")
+    _preload_newest_nccl()
     lib = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL if hasattr(C, "RTLD_GLOBAL") else 0)
     for name, (res, args) in _PROTOTYPES.items():
         fn = getattr(lib, name)          # AttributeError if the symbol is not exported

@@ -75,6 +75,7 @@ class CUDATensorOperations:
         self.recomputeLimit = 2             # a pending value is recomputed at most this often before it is stored
         self.storeCost = 8                  # ... unless recomputing costs this much (a transcendental): stored at once
         self.deferSums = True               # with lazy: sums of deferred tensors wait too, and run several per pass
+        self.deferInplace = True            # with lazy: an in-place call with a pending operand on a buffer nobody else holds waits too
         self._pending = []                  # [weak reference to a reduce node, the node itself once an update hangs on it, [target BufferRefs]]
         self._pending_targets = {}          # buffer handle -> number of pending `+= sum` updates
         self.multiSinkEvaluations = 0       # passes that produced more than one sum
@@ -186,6 +187,8 @@ class CUDATensorOperations:
             else:
                 L.check(self.lib.ktc_binary_inplace(op, h, other.buf.handle, n))
             return
+        if self.deferInplace and self._rebind_inplace(target, h, node):
+            return
         if self._try_fused(target.shape, [node], [h], [False]):
             return
         self.unfusedEvaluations += 1
@@ -206,6 +209,25 @@ class CUDATensorOperations:
                     self.lib.ktc_release(tmp)
             else:
                 L.check(self.lib.ktc_binary_inplace(op, h, hb, n))
+
+    def _rebind_inplace(self, target: CUDARawTensor, h: int, node) -> bool:
+        """target = f(target, pending expression) where nobody else holds target's buffer: instead of a pass that
+        rewrites the buffer now, the tensor becomes deferred -- its node reads the old buffer as an operand -- so that
+        the in-place calls that follow (SoftmaxCrossEntropy.kt:74-77: `+=`, `/=`, then the accumulation into the
+        Variable) join one program.  Nobody can tell the difference: a buffer with a second holder (a view, a shallow
+        copy, a pending expression that still reads it) is written in place as before."""
+        cell = target._cell
+        own = cell.node
+        if own is None or not own.stored() or own.buf.handle != h or not any(a is own for a in node.args):
+            return False
+        cnt = C.c_int(0)
+        L.check(self.lib.ktc_refcount(h, C.byref(cnt)))
+        if cnt.value != 2:                                          # the cell's reference and its cached leaf's
+            return False
+        cell.store, cell.node = None, node
+        L.check(self.lib.ktc_release(h))                            # the cell's reference; the leaf inside `node` keeps the buffer
+        self._register(cell, node)
+        return True
 
     def _flush_dependents(self, handle: int) -> None:
         if self._pending:

@@ -60,6 +60,11 @@ class FakeLib:
         self.bufs[int(h)][1] -= 1
         return 0
 
+    def ktc_refcount(self, h, ref):
+        self._get(h)
+        ref._obj.value = self.bufs[int(h)][1]
+        return 0
+
     def live_buffers(self):
         return sum(1 for a, c in self.bufs.values() if c > 0)
 
@@ -260,5 +265,6 @@ def make_ops() -> CUDATensorOperations:
     ops._deps, ops._deps_purge_at = {}, 1024
     ops.recomputeLimit, ops.storeCost = 2, 8
     ops.deferSums, ops._pending, ops._pending_targets, ops.multiSinkEvaluations = True, [], {}, 0
+    ops.deferInplace = True
     ops.fusedEvaluations = ops.unfusedEvaluations = 0
     return ops

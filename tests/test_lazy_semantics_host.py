@@ -289,3 +289,33 @@ def test_softmax_cross_entropy_on_the_stand_in():
     # exp runs inside a program; what is left as separate calls are the operations on the picked [rows, 1] values, which
     # this stand-in (unlike the library, which collapses the trailing 1) declines to fuse
     assert len(cl) < len(ce) and cl.count("unary") < ce.count("unary") / 2
+
+
+def test_inplace_chain_on_a_buffer_nobody_else_holds_waits():
+    """`g += pending; g /= c; acc += g` (the backward of SoftmaxCrossEntropy.kt:74-77 and the accumulation into the
+    Variable): with no second holder of g's or acc's buffer the three in-place calls become one program; a buffer that a
+    view also holds is written in place at once, and the view sees it."""
+    rows, cols = 8, 16
+    xv, zv, av = D.uniform(rows * cols, 51, -1.0, 1.0), D.uniform(rows, 52, 1.0, 2.0), D.uniform(rows * cols, 53, -1.0, 1.0)
+
+    def script(o):
+        x, z = o.createRaw([rows, cols], xv), o.createRaw([rows, 1], zv)
+        g = o.createRawFill([rows, cols], 0.0)
+        g.inplaceScatter(-1, o.createRaw([rows, 1], np.arange(rows, dtype=np.float32)), -1.0)
+        g.plusAssign(x.exp().div(z))
+        g.divAssign(float(rows))
+        acc = o.createRaw([rows, cols], av)
+        acc.plusAssign(g)
+        held = o.createRaw([rows, cols], av)
+        view = held.view([cols, rows])                     # a second holder of the buffer
+        held.plusAssign(x.exp().div(z))
+        return [acc, g, held, view]
+
+    eager, lazy, stats = both(script)
+    for k, (a, c) in enumerate(zip(eager, lazy)):
+        assert same_bits(a, c), f"result {k}"
+    assert same_bits(lazy[2].reshape(-1), lazy[3].reshape(-1))
+    assert stats[1][0] == 0 and stats[0][0] == 0
+    calls = stats[1][2]
+    # deferred: acc and g in one program each when they are read (g's is a side output or a second program), held at once
+    assert calls.count("expr_eval") <= 3 and calls.count("binary") == 0 and calls.count("scalar") == 0
