@@ -80,6 +80,12 @@ internal object KtcNative {
     val p2pAllreduceSum = handle("ktc_p2p_allreduce_sum", JAVA_INT, JAVA_LONG, ADDRESS, ADDRESS, JAVA_INT)
     val p2pStatus = handle("ktc_p2p_status", JAVA_INT, JAVA_LONG, ADDRESS)
     val p2pDestroy = handle("ktc_p2p_destroy", JAVA_INT, JAVA_LONG)
+    // fused expression programs (optional: a binder that defers elementwise calls and sums submits them here)
+    val exprEval = handle("ktc_expr_eval", JAVA_INT, ADDRESS, JAVA_INT, ADDRESS, JAVA_INT, ADDRESS, JAVA_INT, ADDRESS, ADDRESS, JAVA_INT,
+        ADDRESS, JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_INT)
+    val exprEvalMulti = handle("ktc_expr_eval_multi", JAVA_INT, ADDRESS, JAVA_INT, ADDRESS, JAVA_INT, ADDRESS, JAVA_INT, ADDRESS, ADDRESS, JAVA_INT,
+        ADDRESS, JAVA_INT, ADDRESS, ADDRESS, ADDRESS, JAVA_INT)
+    val refcount = handle("ktc_refcount", JAVA_INT, JAVA_LONG, ADDRESS)
     val indexAdd = handle("ktc_index_add", JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_FLOAT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG)
 
     /** KTC_EINVAL -> IllegalArgumentException, KTC_ESTATE -> IllegalStateException, KTC_ENOMEM -> OutOfMemoryError. */
