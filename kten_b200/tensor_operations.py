@@ -669,7 +669,9 @@ class CUDATensorOperations:
         L.check(self.lib.ktc_pool_stats(self.device, C.byref(live), C.byref(cached), C.byref(calls), C.byref(hits)))
         return {"liveMB": live.value / 2**20, "pooledMB": cached.value / 2**20,
                 "allocCalls": float(calls.value), "poolHits": float(hits.value),
-                "kernelLaunches": float(self.lib.ktc_launch_count())}
+                "kernelLaunches": float(self.lib.ktc_launch_count()),
+                "fusedEvaluations": float(self.fusedEvaluations), "unfusedEvaluations": float(self.unfusedEvaluations),
+                "multiSinkEvaluations": float(self.multiSinkEvaluations), "pendingSums": float(len(self._pending))}
 
     def setMemoryUsageScaleHint(self, fraction: float) -> None:
         """PlatformProvider.memoryUsageScaleHint (PlatformProvider.kt:12-40): cap the pool."""
