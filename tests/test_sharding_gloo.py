@@ -84,3 +84,58 @@ def test_two_gloo_ranks_match_the_unsharded_graph(tmp_path):
                   1e-5 * (g_terms * np.abs(x.reshape(ROWS, COLS))).sum(axis=0) + 1e-12)
     # and against float64 ground truth
     assert abs(float(loss[0]) - float((s * s).sum())) <= 1e-5 * float((s * s).sum())
+
+
+class GlooHandleCollective:
+    """For the CUDA backend's host mirror over the stand-in library: looks the values up by buffer handle
+    (which makes the backend run whatever it deferred), all-reduces them over gloo and writes them back in place."""
+
+    def __init__(self, lib):
+        self.lib = lib
+
+    def allreduce_sum(self, raws):
+        handles = [r.storeReference for r in raws]
+        flat = torch.from_numpy(np.concatenate([self.lib._get(h)[:r.size] for h, r in zip(handles, raws)]).astype(np.float32))
+        dist.all_reduce(flat, op=dist.ReduceOp.SUM)
+        off = 0
+        for h, r in zip(handles, raws):
+            r._before_inplace_write()
+            self.lib._get(h)[:r.size] = flat[off:off + r.size].numpy(); off += r.size
+
+
+def _deferred_worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from tests.fake_lib import make_ops
+        x, w, b = inputs()
+        first, count = shard_rows(ROWS, world, rank)
+        ops = make_ops()
+        ops.lazy = True                                        # elementwise calls, sums and gradient updates all wait
+        with ops.garbageCollector():
+            loss, gw, gb = run_graph(ops, x[first * COLS:(first + count) * COLS], count, w, b, GlooHandleCollective(ops.lib))
+        np.savez(os.path.join(out_dir, f"deferred{rank}.npz"), loss=loss, gw=gw, gb=gb, multi=ops.lib.multi_calls)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(120)
+def test_two_gloo_ranks_with_the_deferred_backend(tmp_path):
+    """The sharded step with everything deferred on each rank: the exchange is what forces the one pass with three
+    sinks, and the global sums equal the unsharded CPU result within the reduction tolerance."""
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_deferred_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    x, w, b = inputs()
+    loss, gw, gb = run_graph(O.OracleTensorOperations(mode=1), x, ROWS, w, b)
+    r0, r1 = np.load(tmp_path / "deferred0.npz"), np.load(tmp_path / "deferred1.npz")
+    for key in ("loss", "gw", "gb"):
+        assert np.array_equal(r0[key], r1[key])
+    assert int(r0["multi"]) == 1 and int(r1["multi"]) == 1
+    s = 1.0 / (1.0 + np.exp(-(x.reshape(ROWS, COLS).astype(np.float64) * w + b)))
+    g_terms = np.abs(2 * s * s * (1 - s))
+    assert abs(float(r0["loss"][0]) - float(loss[0])) <= 1e-5 * float((s * s).sum())
+    assert np.all(np.abs(r0["gb"].astype(np.float64) - gb) <= 1e-5 * g_terms.sum(axis=0) + 1e-12)
+    assert np.all(np.abs(r0["gw"].reshape(-1).astype(np.float64) - gw.reshape(-1)) <=
+                  1e-5 * (g_terms * np.abs(x.reshape(ROWS, COLS))).sum(axis=0) + 1e-12)
