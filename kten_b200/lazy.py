@@ -29,6 +29,11 @@ Rules that keep the semantics of the eager backend:
     remembered as a pending update of that buffer; the first read of any of them -- or of the
     updated buffer -- runs all pending sums, those over the same iteration space as ONE pass with
     several sinks (the loss and both broadcast gradients of a training step read x once);
+  * `gather` with few picks from a pending expression gathers the expression's operands and rebuilds the
+    expression over the index's shape (elementwise operations commute with the pick);
+  * with `ops.deferInplace`, an in-place call with a pending operand on a stored tensor whose buffer nobody
+    else holds makes the tensor deferred (its node reads the old buffer) instead of rewriting the buffer at
+    once, so that a chain of in-place calls becomes one program;
   * compiled programs are cached by the structure of the expression DAG, so a training step that
     rebuilds the same graph with fresh tensors pays for register allocation once.
 Whatever the kernel does not fuse (more than three collapsed dimensions, an innermost
