@@ -16,8 +16,7 @@
 #include <math_constants.h>
 
 #include "../../include/kten_cuda.h"
-#include "ktc_fastmath.h"
-#include "ktc_fastmath2.cuh"
+#include "ktc_fastmath_d.h"
 
 namespace ktc {
 
@@ -34,15 +33,16 @@ __device__ __forceinline__ float jmin(float a, float b) {
 }
 
 // ---- transcendental functions -----------------------------------------------------
-// Reference path: evaluate in double and narrow once, exactly as the JVM does.  Kept out
-// of line: these are the rarely taken slow paths of the float-only functions below, and
-// inlining them into every unrolled element blows up the instruction footprint.
-static __device__ __noinline__ float exp_ref(float x)  { return (float)exp((double)x); }
-__device__ __forceinline__ float log_ref(float x)  { return (float)log((double)x); }
-__device__ __forceinline__ float tanh_ref(float x) { return (float)tanh((double)x); }
-
-// Math.pow differs from C99 pow in two corners: a NaN exponent gives NaN even
-// for base 1, and |base| == 1 with an infinite exponent gives NaN.
+// kten-jvm evaluates these on the widened double and narrows once.  exp, sigmoid and pow do the same
+// with a short table-driven double evaluation (ktc_fastmath_d.h): the value before narrowing is within
+// 2^-41 of the true one, so the result is the reference's float except for about one argument in 10^7
+// (one ulp there; sigmoid at most two).  pow arguments outside that routine's domain -- zero, negative,
+// subnormal or non-finite base, non-finite exponent, results far outside the float range -- take the
+// double-precision library routine below, which also carries Math.pow's special cases.  It is kept out
+// of line: it is rarely taken, and inlining it into every unrolled element blows up the kernel.
+//
+// Math.pow differs from C99 pow in two corners: a NaN exponent gives NaN even for base 1, and
+// |base| == 1 with an infinite exponent gives NaN.
 static __device__ __noinline__ float pow_ref(float x, float y) {
     if (y == 0.0f) return 1.0f;
     if (y != y || x != x) return CUDART_NAN_F;
@@ -50,24 +50,11 @@ static __device__ __noinline__ float pow_ref(float x, float y) {
     return (float)pow((double)x, (double)y);
 }
 
-// Fast paths (ktc_fastmath.h): float-only exp and pow, about 0.5-0.6 ulp, verified on
-// the host against the double libm; arguments outside their domain (results that
-// leave the normal range, zero / negative / non-finite operands) take the double path,
-// which also carries Math.pow's special cases.
-__device__ __forceinline__ float exp_f(float x) {
-    float r;
-    return kf_exp(x, &r) ? r : exp_ref(x);
-}
-// correctly rounded exp for the sigmoid composite: e is then bit-identical to the
-// JVM's (float)Math.exp, and the two IEEE operations that follow reproduce it exactly
-__device__ __forceinline__ float exp_cr(float x) {
-    float r;
-    return kf_exp_cr(x, &r) ? r : exp_ref(x);
-}
+__device__ __forceinline__ float exp_f(float x) { return kd_expf(x); }
 __device__ __forceinline__ float pow_f(float x, float y) {
-    if (y == 0.0f) return 1.0f;
-    float r;
-    return kf_pow(x, y, &r) ? r : pow_ref(x, y);
+    bool ok;
+    const float r = kd_pow(x, y, &ok);
+    return ok ? r : pow_ref(x, y);
 }
 // log and tanh: CUDA's logf (max error 1 ulp) and tanhf (2 ulp) stay within the
 // 2-ulp bar against the correctly rounded value kten-jvm returns.
@@ -85,16 +72,9 @@ template <int OP> struct UnOp;
 template <> struct UnOp<KTC_EXP>  { __device__ __forceinline__ float operator()(float x) const { return exp_f(x); } };
 template <> struct UnOp<KTC_LOG>  { __device__ __forceinline__ float operator()(float x) const { return log_f(x); } };
 template <> struct UnOp<KTC_TANH> { __device__ __forceinline__ float operator()(float x) const { return tanh_f(x); } };
-// sigmoid = 1f / (1f + exp(-1f * x)) with the reference's own two IEEE operations after the exp.  A one-ulp
-// slip in e = exp(-x) can move the result by up to 3 ulp (1 + e rounds away a bit of e, and the reciprocal can
-// double a relative error when its mantissa wraps), so e is always the CORRECTLY ROUNDED exp: the result is
-// then the reference's, bit for bit, for every argument, and does not depend on which kernel evaluates it.
-template <> struct UnOp<KTC_SIGMOID> {
-    __device__ __forceinline__ float operator()(float x) const {
-        const float e = exp_cr(__fmul_rn(-1.0f, x));
-        return __frcp_rn(__fadd_rn(1.0f, e));        // 1f / (1f + e): the IEEE reciprocal is the IEEE quotient
-    }
-};
+// sigmoid = 1f / (1f + exp(-1f * x)) with the reference's own two IEEE operations after the exp
+// (JVMRawTensor.kt:399); e is Math.exp's narrowed value (see kd_sigmoid).
+template <> struct UnOp<KTC_SIGMOID> { __device__ __forceinline__ float operator()(float x) const { return kd_sigmoid(x); } };
 template <> struct UnOp<KTC_RECIPROCAL> { __device__ __forceinline__ float operator()(float x) const { return __frcp_rn(x); } };
 template <> struct UnOp<KTC_NEG>  { __device__ __forceinline__ float operator()(float x) const { return -x; } };
 
@@ -106,41 +86,39 @@ template <int OP> struct ScalarLeft  { float s; __device__ __forceinline__ float
 struct Square { __device__ __forceinline__ float operator()(float a) const { return __fmul_rn(a, a); } };
 struct Identity { __device__ __forceinline__ float operator()(float a) const { return a; } };
 
-// ---- two elements per instruction (ktc_fastmath2.cuh); each lane equals the scalar function above ----------
-__device__ __forceinline__ void exp_f_pair(float x0, float x1, float& o0, float& o1) {
-    const f2 r = kf2_exp(make_float2(x0, x1));
-    o0 = kf_exp_in_domain(x0) ? r.x : exp_ref(x0);
-    o1 = kf_exp_in_domain(x1) ? r.y : exp_ref(x1);
-}
-__device__ __forceinline__ void exp_cr_pair(float x0, float x1, float& o0, float& o1) {
-    bool ok0, ok1;
-    const f2 r = kf2_exp_cr(make_float2(x0, x1), &ok0, &ok1);
-    o0 = ok0 ? r.x : exp_ref(x0);
-    o1 = ok1 ? r.y : exp_ref(x1);
-}
-__device__ __forceinline__ void pow_f_pair(float x0, float x1, float y0, float y1, float& o0, float& o1) {
-    bool ok0, ok1;
-    const f2 r = kf2_pow(make_float2(x0, x1), make_float2(y0, y1), &ok0, &ok1);
-    o0 = (y0 == 0.0f) ? 1.0f : (ok0 ? r.x : pow_ref(x0, y0));
-    o1 = (y1 == 0.0f) ? 1.0f : (ok1 ? r.y : pow_ref(x1, y1));
-}
-__device__ __forceinline__ void sigmoid_pair(float x0, float x1, float& o0, float& o1) {
-    const f2 a = mul2(make_float2(x0, x1), F2(-1.0f));
-    float e0, e1;
-    exp_cr_pair(a.x, a.y, e0, e1);
-    const f2 d = add2(F2(1.0f), make_float2(e0, e1));
-    o0 = __frcp_rn(d.x); o1 = __frcp_rn(d.y);
-}
-// float4 forms picked by the map kernels (overloads of the generic per-element application)
+// ---- float4 forms picked by the map kernels, the interpreter and the generated kernels ---------------------
+// Same values as the scalar functors; the rare slow paths (IEEE reciprocal for a subnormal sigmoid, the
+// library pow) are tested once per float4 instead of once per element, which keeps the common path free of
+// branches and reconvergence points.
 __device__ __forceinline__ float4 apply1(const UnOp<KTC_EXP>&, float4 a) {
-    float4 o; exp_f_pair(a.x, a.y, o.x, o.y); exp_f_pair(a.z, a.w, o.z, o.w); return o;
+    return make_float4(kd_expf(a.x), kd_expf(a.y), kd_expf(a.z), kd_expf(a.w));
 }
 __device__ __forceinline__ float4 apply1(const UnOp<KTC_SIGMOID>&, float4 a) {
-    float4 o; sigmoid_pair(a.x, a.y, o.x, o.y); sigmoid_pair(a.z, a.w, o.z, o.w); return o;
+    const float d0 = kd_sigmoid_den(a.x), d1 = kd_sigmoid_den(a.y), d2 = kd_sigmoid_den(a.z), d3 = kd_sigmoid_den(a.w);
+    float4 o = make_float4(kd_rcp_fast(d0), kd_rcp_fast(d1), kd_rcp_fast(d2), kd_rcp_fast(d3));
+    if (!(fmaxf(fmaxf(d0, d1), fmaxf(d2, d3)) < KD_RCP_FAST_LIMIT)) {          // huge, infinite or all-NaN denominators
+        if (!(d0 < KD_RCP_FAST_LIMIT)) o.x = kd_rcp_ieee(d0);
+        if (!(d1 < KD_RCP_FAST_LIMIT)) o.y = kd_rcp_ieee(d1);
+        if (!(d2 < KD_RCP_FAST_LIMIT)) o.z = kd_rcp_ieee(d2);
+        if (!(d3 < KD_RCP_FAST_LIMIT)) o.w = kd_rcp_ieee(d3);
+    }
+    return o;
 }
-__device__ __forceinline__ float4 apply2(const BinOp<KTC_POW>&, float4 a, float4 b) {
-    float4 o; pow_f_pair(a.x, a.y, b.x, b.y, o.x, o.y); pow_f_pair(a.z, a.w, b.z, b.w, o.z, o.w); return o;
+__device__ __forceinline__ float4 pow4(float4 a, float4 b) {
+    bool k0, k1, k2, k3;
+    float4 o;
+    o.x = kd_pow(a.x, b.x, &k0); o.y = kd_pow(a.y, b.y, &k1); o.z = kd_pow(a.z, b.z, &k2); o.w = kd_pow(a.w, b.w, &k3);
+    if (!(k0 && k1 && k2 && k3)) {
+        if (!k0) o.x = pow_ref(a.x, b.x);
+        if (!k1) o.y = pow_ref(a.y, b.y);
+        if (!k2) o.z = pow_ref(a.z, b.z);
+        if (!k3) o.w = pow_ref(a.w, b.w);
+    }
+    return o;
 }
+__device__ __forceinline__ float4 apply2(const BinOp<KTC_POW>&, float4 a, float4 b) { return pow4(a, b); }
+__device__ __forceinline__ float4 apply1(const ScalarRight<KTC_POW>& f, float4 a) { return pow4(a, make_float4(f.s, f.s, f.s, f.s)); }
+__device__ __forceinline__ float4 apply1(const ScalarLeft<KTC_POW>& f, float4 a) { return pow4(make_float4(f.s, f.s, f.s, f.s), a); }
 
 struct ClampOp { float lo, hi; __device__ __forceinline__ float operator()(float x) const { return jmin(jmax(x, lo), hi); } };
 

@@ -1,6 +1,7 @@
-"""Accuracy of the float-only exp / pow fast paths (kten_b200/csrc/ktc_fastmath.h),
-measured on the host.  The header uses only IEEE float + - * / fma and integer
-operations, so the bits checked here are the bits the GPU produces."""
+"""Accuracy of the table-driven exp / sigmoid / pow (kten_b200/csrc/ktc_fastmath_d.h), measured
+on the host.  The header uses only IEEE float and double add / mul / fma, conversions and
+integer operations, so the bits checked here are the bits the GPU produces
+(tests/test_gpu_parity.py compares the two)."""
 import ctypes as C
 import os
 import subprocess
@@ -13,99 +14,103 @@ from oracle import oracle as O
 HERE = os.path.dirname(os.path.abspath(__file__))
 SRC = os.path.join(HERE, "host_math", "fastmath_host.cpp")
 SO = os.path.join(HERE, "host_math", "libfastmath_host.so")
+HDR = os.path.join(HERE, "..", "kten_b200", "csrc", "ktc_fastmath_d.h")
+
+
+def host_math_library():
+    """Builds (when stale) and loads the host build of the header."""
+    if not os.path.exists(SO) or os.path.getmtime(SO) < max(os.path.getmtime(SRC), os.path.getmtime(HDR)):
+        flags = ["-O2", "-fopenmp", "-fPIC", "-shared", "-ffp-contract=off", "-std=c++17"]
+        with open("/proc/cpuinfo") as fh:
+            if " fma " in fh.read():
+                flags.append("-mfma")            # std::fma as one instruction; the library routine gives the same bits
+        subprocess.run(["g++", *flags, "-o", SO, SRC], check=True)
+    lib = C.CDLL(SO)
+    lib.kfh_sweep.restype = C.c_int64
+    lib.kfh_sweep.argtypes = [C.c_int, C.c_uint32, C.POINTER(C.c_int64)]
+    return lib
 
 
 @pytest.fixture(scope="module")
 def fm():
-    hdr = os.path.join(HERE, "..", "kten_b200", "csrc", "ktc_fastmath.h")
-    if not os.path.exists(SO) or os.path.getmtime(SO) < max(os.path.getmtime(SRC), os.path.getmtime(hdr)):
-        subprocess.run(["g++", "-O2", "-fopenmp", "-fPIC", "-shared", "-ffp-contract=off", "-std=c++17", "-o", SO, SRC], check=True)
-    lib = C.CDLL(SO)
-    lib.kfh_exp_sweep.restype = C.c_int64
-    lib.kfh_exp_sweep.argtypes = [C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
-    return lib
+    return host_math_library()
 
 
-def _pow(lib, x, y):
+def host_unary(lib, fn, x):
+    out = np.empty_like(x)
+    getattr(lib, fn)(x.ctypes.data_as(C.c_void_p), out.ctypes.data_as(C.c_void_p), C.c_int64(x.size))
+    return out
+
+
+def host_pow(lib, x, y):
     out, ok = np.empty_like(x), np.empty(x.size, dtype=np.uint8)
     lib.kfh_pow(x.ctypes.data_as(C.c_void_p), y.ctypes.data_as(C.c_void_p), out.ctypes.data_as(C.c_void_p),
                 ok.ctypes.data_as(C.c_void_p), C.c_int64(x.size))
     return out, ok.astype(bool)
 
 
-def test_exp_fast_path_every_seventh_float(fm):
-    """All float bit patterns with |x| <= 87, stride 7: at most 1 ulp from the narrowed
-    double exp, and bit-identical for more than 99.8 % of the inputs."""
-    for lo, hi in ((0x00000000, 0x42AE0000), (0x80000000, 0xC2AE0000)):
-        counts, n_fast = (C.c_int64 * 4)(), C.c_int64(0)
-        worst = fm.kfh_exp_sweep(lo, hi, 7, counts, C.byref(n_fast))
-        assert n_fast.value > 150_000_000
-        assert worst <= 1
-        assert counts[0] / n_fast.value > 0.998
+def test_exp_every_eleventh_float(fm):
+    """Every 11th float bit pattern -- both signs, subnormals, arguments whose exp overflows or
+    underflows, infinities, NaNs: at most 1 ulp from the narrowed double exp, and fewer than one
+    argument in a million differs at all."""
+    counts = (C.c_int64 * 4)()
+    worst = fm.kfh_sweep(0, 11, counts)
+    n = sum(counts)
+    assert n > 390_000_000
+    assert worst <= 1
+    assert counts[1] <= n // 1_000_000
 
 
-def test_exp_fast_path_declines_what_it_cannot_do(fm):
-    x = np.array([88.0, -88.0, np.inf, -np.inf, np.nan, 100.0, -104.0], dtype=np.float32)
-    out, ok = np.empty_like(x), np.empty(x.size, dtype=np.uint8)
-    fm.kfh_exp(x.ctypes.data_as(C.c_void_p), out.ctypes.data_as(C.c_void_p), ok.ctypes.data_as(C.c_void_p), C.c_int64(x.size))
-    assert not ok.any()
+def test_sigmoid_every_eleventh_float(fm):
+    """The composite 1f / (1f + (float)exp(-1f * x)) over every 11th float: at most 2 ulp from the
+    reference's value, fewer than one argument in a million differs."""
+    counts = (C.c_int64 * 4)()
+    worst = fm.kfh_sweep(1, 11, counts)
+    n = sum(counts)
+    assert worst <= 2
+    assert counts[1] + counts[2] <= n // 1_000_000 and counts[3] == 0
 
 
-@pytest.mark.parametrize("domain", ["config2", "wide", "large_exponent", "huge_base", "near_one"])
-def test_pow_fast_path(fm, domain):
-    rng = np.random.default_rng(hash(domain) % 1000)
+@pytest.mark.parametrize("domain", ["config2", "wide", "large_exponent", "huge_base", "near_one", "subnormal_result"])
+def test_pow(fm, domain):
+    rng = np.random.default_rng(len(domain) * 131)
     n = 4_000_000
     if domain == "config2":
         x, y = rng.uniform(0.1, 2.0, n), rng.uniform(0.1, 2.0, n)
     elif domain == "wide":
         x, y = np.exp(rng.uniform(np.log(1e-3), np.log(1e3), n)), rng.uniform(-8, 8, n)
     elif domain == "large_exponent":
-        x, y = rng.uniform(0.5, 2.0, n), rng.uniform(-120, 120, n)
+        x, y = rng.uniform(0.5, 2.0, n), rng.uniform(-150, 150, n)
     elif domain == "huge_base":
         x, y = np.exp(rng.uniform(np.log(1e-30), np.log(1e30), n)), rng.uniform(-1.2, 1.2, n)
+    elif domain == "near_one":
+        x, y = 1.0 + rng.uniform(-1e-3, 1e-3, n), rng.uniform(-1e5, 1e5, n)
     else:
-        x, y = 1.0 + rng.uniform(-1e-3, 1e-3, n), rng.uniform(-1000, 1000, n)
+        x, y = rng.uniform(0.01, 0.5, n), rng.uniform(20, 60, n)      # results from 1e-30 down through the subnormals to 0
     x, y = x.astype(np.float32), y.astype(np.float32)
-    got, ok = _pow(fm, x, y)
-    assert ok.mean() > 0.9
+    got, ok = host_pow(fm, x, y)
+    assert ok.mean() > 0.85
     want = O.binary_same(O.POW, x, y, tuned=True)
     d = O.ulp_distance(got[ok], want[ok])
     assert d.max() <= 1
-    assert (d == 0).mean() > 0.98
+    assert int((d > 0).sum()) <= n // 100_000
 
 
-def test_pow_fast_path_declines_special_operands(fm):
-    x = np.array([0.0, -1.0, np.inf, np.nan, 1e-40, 2.0, 2.0, 2.0, 1.0, 1.0, 3.0, 0.5], dtype=np.float32)
-    y = np.array([2.0, 2.0, 2.0, 2.0, 2.0, np.inf, np.nan, 200.0, np.nan, np.inf, -130.0, 140.0], dtype=np.float32)
-    _, ok = _pow(fm, x, y)
+def test_pow_declines_special_operands_and_keeps_zero_exponents(fm):
+    x = np.array([0.0, -1.0, np.inf, np.nan, 1e-40, 2.0, 2.0, 2.0, 1.0, 1.0, 3.0, 0.5, -0.0, -np.inf], dtype=np.float32)
+    y = np.array([2.0, 2.0, 2.0, 2.0, 2.0, np.inf, np.nan, 200.0, np.nan, np.inf, -130.0, 170.0, 3.0, 3.0], dtype=np.float32)
+    _, ok = host_pow(fm, x, y)
     assert not ok.any()
+    x = np.array([2.0, 0.5, 1.0, 3.4e38, 1.2e-38], dtype=np.float32)
+    got, ok = host_pow(fm, x, np.array([0.0, -0.0, 0.0, 0.0, -0.0], dtype=np.float32))
+    assert ok.all() and np.all(got == 1.0)
 
 
-def _unary(lib, fn, x):
-    out, ok = np.empty_like(x), np.empty(x.size, dtype=np.uint8)
-    getattr(lib, fn)(x.ctypes.data_as(C.c_void_p), out.ctypes.data_as(C.c_void_p), ok.ctypes.data_as(C.c_void_p), C.c_int64(x.size))
-    return out, ok.astype(bool)
-
-
-@pytest.mark.parametrize("lo,hi", [(-2.0, 2.0), (-20.0, 20.0), (-87.0, 87.0), (-0.05, 0.05)])
-def test_exp_correctly_rounded_path(fm, lo, hi):
-    """kf_exp_cr either returns the correctly rounded float or declines (rounding test);
-    what it returns is bit-identical to the narrowed double exp."""
-    x = np.random.default_rng(int(hi * 10)).uniform(lo, hi, 10_000_000).astype(np.float32)
-    got, ok = _unary(fm, "kfh_exp_cr", x)
-    assert 0.99 < ok.mean() < 1.0 or hi < 0.1
-    want = O.unary(O.EXP, x, tuned=True)
-    d = O.ulp_distance(got[ok], want[ok])
-    # the narrowed double exp is itself not correctly rounded once in ~2^29 arguments
-    assert d.max() <= 1 and int((d > 0).sum()) <= 1
-
-
-@pytest.mark.parametrize("lo,hi", [(-2.0, 2.0), (-20.0, 20.0), (-87.0, 87.0), (0.1, 2.0)])
-def test_sigmoid_composite_is_bit_exact(fm, lo, hi):
-    """e = exp(-1f*x) through the correctly rounded path, then the reference's own two
-    IEEE operations: the result matches the oracle bit for bit."""
-    x = np.random.default_rng(int(hi * 7) + 1).uniform(lo, hi, 10_000_000).astype(np.float32)
-    got = np.empty_like(x)
-    fm.kfh_sigmoid(x.ctypes.data_as(C.c_void_p), got.ctypes.data_as(C.c_void_p), C.c_int64(x.size))
-    d = O.ulp_distance(got, O.unary(O.SIGMOID, x, tuned=True))
-    assert d.max() <= 2 and int((d > 0).sum()) <= 1
+def test_special_arguments_of_exp_and_sigmoid(fm):
+    x = np.array([np.inf, -np.inf, np.nan, 88.7228394, 88.72284, 89.0, 1e30, -103.97, -103.98, -104.5, -1e30, 0.0, -0.0,
+                  -88.5, -88.8, -87.0, -86.0, 17.0, 30.0, 31.0, 1e-45, -1e-45], dtype=np.float32)
+    for fn, code in (("kfh_exp", O.EXP), ("kfh_sigmoid", O.SIGMOID)):
+        got, want = host_unary(fm, fn, x), O.unary(code, x, tuned=True)
+        assert np.array_equal(np.isnan(got), np.isnan(want)), fn
+        keep = ~np.isnan(want)
+        assert np.array_equal(got[keep].view(np.uint32), want[keep].view(np.uint32)), (fn, got, want)

@@ -626,10 +626,12 @@ def test_bounded_device_wait_times_out_cleanly(cuda_ops):
     r.release()
 
 
-def test_packed_math_equals_scalar_math(cuda_ops, gc_scope):
-    """exp, sigmoid and pow run two elements per instruction (float2 add / mul / fma of sm_100) in the vector
-    kernels and one element per instruction in the scalar kernels that serve unaligned buffers: every lane
-    must produce the scalar bits.  The unaligned case is a view that starts one float into the buffer."""
+def test_vector_math_equals_scalar_math_and_the_host_build(cuda_ops, gc_scope):
+    """exp, sigmoid and pow test their rare slow paths once per float4 in the vector kernels and once per
+    element in the scalar kernels that serve unaligned buffers: both must produce the same bits.  The
+    unaligned case is a view that starts one float into the buffer.  The same header compiled for the host
+    (tests/host_math) must give the device's bits too, which is what makes the accuracy measured on the CPU
+    (tests/test_fastmath_host.py) a statement about the GPU."""
     lib = cuda_ops.lib
     n = (1 << 18) + 1
     x = np.concatenate([D.uniform(n - 40, 61, -30.0, 30.0), special_values()[:20], np.array([88.0, -88.0, 87.0, -87.0, 100.0, -100.0, 0.0, -0.0,
@@ -655,9 +657,16 @@ def test_packed_math_equals_scalar_math(cuda_ops, gc_scope):
     assert same_bits(out_v.toArray()[1:], out_s.toArray()[1:])
     for h in (va, vb, vp, vo):
         L.check(lib.ktc_release(h))
-    # sigmoid is the reference's value bit for bit (correctly rounded exp, then the reference's two IEEE operations)
+    from tests.test_fastmath_host import host_math_library, host_unary, host_pow
+    host = host_math_library()
     got = ta.sigmoid().toArray()
-    assert same_bits(got, O.unary(O.SIGMOID, x))
+    assert same_bits(got, host_unary(host, "kfh_sigmoid", x))
+    assert same_bits(ta.exp().toArray(), host_unary(host, "kfh_exp", x))
+    want, ok = host_pow(host, base, y)
+    assert ok.mean() > 0.9 and same_bits(tp.pow(tb).toArray()[ok], want[ok])
+    # against the reference: e = (float)Math.exp(-1f * x), then its two IEEE operations (JVMRawTensor.kt:399)
+    d = O.ulp_distance(got, O.unary(O.SIGMOID, x))
+    assert d.max() <= 2 and int((d > 0).sum()) <= 2
 
 
 def test_peer_memory_allreduce_single_rank_and_bounded_wait(cuda_ops, gc_scope):
