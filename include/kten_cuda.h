@@ -275,6 +275,63 @@ KTC_API int ktc_expr_eval_multi(const uint32_t* code, int n_code, const float* i
 KTC_API int ktc_expr_stats(int64_t* out6);
 KTC_API int ktc_expr_jit_log(char* buf, int len);
 
+/* ---- deferred-expression recorder (no counterpart in the reference; it absorbs the reference's call
+ * sequence) ------------------------------------------------------------------------------------------
+ * kten's Function nodes call the backend once per line of doForward / doBackward (Function.kt:54-68,
+ * 108-141; BasicFunctions.kt:37-45, 182-204; PointwiseFunctions.kt:66-81; Utils.kt:14-41;
+ * Variable.kt:44-46).  A binding may pass its elementwise calls to this recorder instead of running
+ * them: each call returns a CELL -- the storage slot of one raw tensor -- whose value is a pending
+ * expression until somebody needs it; the recorder then compiles the expression DAG into a program for
+ * ktc_expr_eval / ktc_expr_eval_multi (programs are cached by DAG structure and re-bound to the step's
+ * fresh operands), or falls back to the separate calls above where the kernel declines.  Results equal
+ * the call-by-call results bit for bit; fused sums differ only in summation order.
+ *   ktc_lazy_leaf            a cell over a stored buffer (retains it): how stored tensors enter expressions.
+ *   ktc_lazy_unary/binary/scalar/clamp/compare_scalar/broadcast_to
+ *                            record one operation; the result cell is pending (op codes as for ktc_unary,
+ *                            KTC_EXP..KTC_NEG only, ktc_binary, ktc_compare_scalar KTC_LT..KTC_GTE; shapes
+ *                            broadcast as in ktc_binary_bcast; broadcast_to with the operand's own shape
+ *                            is a deep copy that is not made yet).
+ *   ktc_lazy_assign_binary/scalar   target = target op other, in place (inplaceElementwiseOpOnTensors,
+ *                            JVM:89-97, 105-108).  *state: 0 the target's buffer was written; 1 the
+ *                            target cell is pending now -- a caller that holds a reference on its old
+ *                            buffer drops it; 2 the call was `stored += pending sum` and is remembered as
+ *                            an update of the buffer, applied when the pending sums run (ktc_lazy_buffer,
+ *                            ktc_lazy_flush and every recorder call that reads the buffer apply it first).
+ *                            The caller is expected to hold exactly one reference of its own on a stored
+ *                            target's buffer; the recorder reads "nobody else holds it" off the count.
+ *   ktc_lazy_sum             sum() / mean() (KTC_EXPR_SUM_ALL), sum over axis 0 (KTC_EXPR_SUM_ROWS) or over
+ *                            the innermost axis (KTC_EXPR_SUM_LAST) of a cell; with option defer_sums the
+ *                            sum of a pending cell is pending too, and pending sums over one iteration
+ *                            space run as ONE pass with several sinks.
+ *   ktc_lazy_buffer          the buffer holding the cell's value, computed if pending; adds one reference
+ *                            for the caller.
+ *   ktc_lazy_flush           to be called before `buf` is written by any call that is not recorded here:
+ *                            pending expressions that read it are evaluated first.
+ *   ktc_lazy_free            drops the cell (values other expressions still need stay alive).
+ *   ktc_lazy_option          recompute_limit (2), store_cost (8), defer_sums (1), defer_inplace (1).
+ *   ktc_lazy_stats           out8: programs run, expressions run as separate calls, passes with several
+ *                            sums, sums pending now, program-cache hits, programs compiled, live nodes,
+ *                            live cells.
+ * All calls are serialised by one lock; cells of different devices must not meet in one expression. */
+typedef uint64_t ktc_lazy_cell;
+KTC_API int ktc_lazy_leaf(ktc_buf buf, const int64_t* shape, int ndim, ktc_lazy_cell* out);
+KTC_API int ktc_lazy_free(ktc_lazy_cell cell);
+KTC_API int ktc_lazy_unary(int op, ktc_lazy_cell a, ktc_lazy_cell* out);
+KTC_API int ktc_lazy_binary(int op, ktc_lazy_cell a, ktc_lazy_cell b, ktc_lazy_cell* out);
+KTC_API int ktc_lazy_scalar(int op, ktc_lazy_cell a, float s, int scalar_first, ktc_lazy_cell* out);
+KTC_API int ktc_lazy_clamp(ktc_lazy_cell a, float lo, float hi, ktc_lazy_cell* out);
+KTC_API int ktc_lazy_compare_scalar(int op, ktc_lazy_cell a, float value, ktc_lazy_cell* out);
+KTC_API int ktc_lazy_broadcast_to(ktc_lazy_cell a, const int64_t* shape, int ndim, ktc_lazy_cell* out);
+KTC_API int ktc_lazy_assign_binary(int op, ktc_lazy_cell target, ktc_lazy_cell other, int* state);
+KTC_API int ktc_lazy_assign_scalar(int op, ktc_lazy_cell target, float s, int* state);
+KTC_API int ktc_lazy_sum(ktc_lazy_cell a, int kind, int mean, const int64_t* res_shape, int res_ndim, ktc_lazy_cell* out);
+KTC_API int ktc_lazy_buffer(ktc_lazy_cell cell, ktc_buf* out);
+KTC_API int ktc_lazy_info(ktc_lazy_cell cell, int* pending, int* is_sum, int64_t* shape, int* ndim);
+KTC_API int ktc_lazy_flush(ktc_buf buf);
+KTC_API int ktc_lazy_run_pending(void);
+KTC_API int ktc_lazy_option(const char* name, int value);
+KTC_API int ktc_lazy_stats(int64_t* out8);
+
 /* ---- slices, permutes, gather / scatter -----------------------------------------
  * ktc_copy_strided:  dst[dst_offset + i.dst_strides] = src[src_offset + i.src_strides] for every i in the
  *                    box `shape`; strides in elements, >= 0.  With a contiguous dst this is get(ranges)

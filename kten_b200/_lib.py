@@ -90,6 +90,23 @@ _PROTOTYPES = {
     "ktc_expr_eval_multi": (i32, [C.POINTER(C.c_uint32), i32, p_f32, i32, p_i64, i32, p_u64, p_i64, i32, p_u64, i32, C.POINTER(C.c_int), p_u64, C.POINTER(C.c_int), i32]),
     "ktc_test_expr_compile_multi": (i32, [C.POINTER(C.c_uint32), i32, i32, C.POINTER(C.c_int), C.POINTER(C.c_int), i32, C.POINTER(C.c_int), i32, p_i64, C.POINTER(C.c_double)]),
     "ktc_test_expr_compile": (i32, [C.POINTER(C.c_uint32), i32, i32, C.POINTER(C.c_int), C.POINTER(C.c_int), i32, i32, p_i64, C.POINTER(C.c_double)]),
+    "ktc_lazy_leaf": (i32, [u64, p_i64, i32, p_u64]),
+    "ktc_lazy_free": (i32, [u64]),
+    "ktc_lazy_unary": (i32, [i32, u64, p_u64]),
+    "ktc_lazy_binary": (i32, [i32, u64, u64, p_u64]),
+    "ktc_lazy_scalar": (i32, [i32, u64, f32, i32, p_u64]),
+    "ktc_lazy_clamp": (i32, [u64, f32, f32, p_u64]),
+    "ktc_lazy_compare_scalar": (i32, [i32, u64, f32, p_u64]),
+    "ktc_lazy_broadcast_to": (i32, [u64, p_i64, i32, p_u64]),
+    "ktc_lazy_assign_binary": (i32, [i32, u64, u64, p_i32]),
+    "ktc_lazy_assign_scalar": (i32, [i32, u64, f32, p_i32]),
+    "ktc_lazy_sum": (i32, [u64, i32, i32, p_i64, i32, p_u64]),
+    "ktc_lazy_buffer": (i32, [u64, p_u64]),
+    "ktc_lazy_info": (i32, [u64, p_i32, p_i32, p_i64, p_i32]),
+    "ktc_lazy_flush": (i32, [u64]),
+    "ktc_lazy_run_pending": (i32, []),
+    "ktc_lazy_option": (i32, [C.c_char_p, i32]),
+    "ktc_lazy_stats": (i32, [p_i64]),
     "ktc_sum_to_shape": (i32, [u64, p_i64, i32, u64, p_i64, i32]),
     "ktc_scatter_axis": (i32, [u64, u64, u64, i64, i64, i64]),
     "ktc_comm_unique_id": (i32, [C.c_char_p]),

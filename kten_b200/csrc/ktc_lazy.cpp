@@ -1,0 +1,1276 @@
+// ktc_lazy.cpp -- the deferred-expression recorder behind the C ABI (ktc_lazy_*).
+//
+// kten's autograd issues one raw-tensor call per line of doForward / doBackward
+// (kten-api/.../autograd/functions/BasicFunctions.kt, PointwiseFunctions.kt,
+// AggregatingFunctions.kt, Utils.kt:14-41, Variable.kt:44-46); executed one by one, the
+// sharded-graph step of the benchmark moves 34 tensor volumes through HBM.  A backend binding
+// (the Kotlin CUDARawTensor, the Python mirror) can hand its elementwise calls to this recorder
+// instead: a call returns a CELL -- the storage slot of a raw tensor -- that holds an expression
+// node instead of a buffer.  The expression is compiled into a program for ktc_expr_eval when a
+// value is needed: ktc_lazy_buffer (a host read or a call outside the elementwise set), a sum, an
+// in-place write to one of its operands.  Every program instruction is one reference operation
+// with its own rounding, so results equal the call-by-call execution bit for bit; only the
+// order of summation inside a fused sum differs.
+//
+// Rules that keep the semantics of the eager backend:
+//   * nodes are immutable values; an in-place call on a pending cell replaces its node, an
+//     in-place call on a stored cell is evaluated into its own buffer (or recorded, see below);
+//   * before a buffer is written in place (ktc_lazy_flush, or an in-place call here) every
+//     pending expression that reads it is evaluated: a registry maps buffers to the cells whose
+//     pending expressions depend on them;
+//   * an interior value is recomputed inside at most `recompute_limit` programs; after that, if a
+//     cell still waits for it, it is stored as a side output; a value behind a transcendental
+//     (`store_cost`) is stored by the first program that computes it;
+//   * with `defer_sums`, sums of pending cells are pending too and `stored += pending sum` is
+//     remembered as an update of that buffer; the first need of any of them runs all pending
+//     sums, those over one iteration space as ONE pass with several sinks;
+//   * with `defer_inplace`, an in-place call with a pending operand on a stored cell whose
+//     buffer nobody else holds makes the cell pending (its node reads the old buffer);
+//   * compiled programs are cached by the structure of the expression DAG and re-bound to the
+//     step's fresh nodes, so a training step that rebuilds the same graph pays for ordering and
+//     register allocation once.
+// Whatever ktc_expr_eval declines (KTC_ENOTSUP) runs as the library's separate calls.
+//
+// The file is plain C++ and reaches the rest of the library only through a table of the C ABI's
+// own entry points, so that it can be compiled alone (KTC_LAZY_STANDALONE) and driven by a
+// stand-in library on a machine without a GPU.
+#include <algorithm>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/kten_cuda.h"
+
+namespace ktc {
+#ifndef KTC_LAZY_STANDALONE
+void set_error(const char* fmt, ...);
+#endif
+namespace lz {
+
+// ---- the calls the recorder makes --------------------------------------------------------------
+struct Backend {
+    int (*alloc)(int, int64_t, ktc_buf*);
+    int (*retain)(ktc_buf);
+    int (*release)(ktc_buf);
+    int (*refcount)(ktc_buf, int*);
+    int (*buf_info)(ktc_buf, int*, int64_t*, void**);
+    int (*d2d)(ktc_buf, int64_t, ktc_buf, int64_t, int64_t);
+    int (*binary)(int, ktc_buf, ktc_buf, ktc_buf, int64_t);
+    int (*binary_bcast)(int, ktc_buf, ktc_buf, const int64_t*, int, ktc_buf, const int64_t*, int);
+    int (*binary_inplace)(int, ktc_buf, ktc_buf, int64_t);
+    int (*scalar)(int, ktc_buf, ktc_buf, float, int64_t, int);
+    int (*scalar_inplace)(int, ktc_buf, float, int64_t);
+    int (*unary)(int, ktc_buf, ktc_buf, int64_t);
+    int (*clamp)(ktc_buf, ktc_buf, float, float, int64_t);
+    int (*compare_scalar)(int, ktc_buf, ktc_buf, float, int64_t);
+    int (*broadcast_to)(ktc_buf, const int64_t*, int, ktc_buf, const int64_t*, int);
+    int (*reduce_axis)(int, ktc_buf, ktc_buf, int64_t, int64_t, int64_t);
+    int (*reduce_all)(int, ktc_buf, ktc_buf, int64_t);
+    int (*expr_eval)(const uint32_t*, int, const float*, int, const int64_t*, int, const ktc_buf*, const int64_t*, int,
+                     const ktc_buf*, int, int, ktc_buf, int);
+    int (*expr_eval_multi)(const uint32_t*, int, const float*, int, const int64_t*, int, const ktc_buf*, const int64_t*, int,
+                           const ktc_buf*, int, const int*, const ktc_buf*, const int*, int);
+};
+constexpr int kBackendEntries = sizeof(Backend) / sizeof(void*);
+
+#ifdef KTC_LAZY_STANDALONE
+static Backend B = {};
+static thread_local char g_err[512];
+static void set_error_v(const char* fmt, va_list ap) { vsnprintf(g_err, sizeof(g_err), fmt, ap); }
+#else
+static Backend B = {ktc_alloc, ktc_retain, ktc_release, ktc_refcount, ktc_buf_info, ktc_d2d, ktc_binary, ktc_binary_bcast,
+                    ktc_binary_inplace, ktc_scalar, ktc_scalar_inplace, ktc_unary, ktc_clamp, ktc_compare_scalar, ktc_broadcast_to,
+                    ktc_reduce_axis, ktc_reduce_all, ktc_expr_eval, ktc_expr_eval_multi};
+static void set_error_v(const char* fmt, va_list ap) { char b[512]; vsnprintf(b, sizeof(b), fmt, ap); ::ktc::set_error("%s", b); }
+#endif
+
+static int fail(int code, const char* fmt, ...) {
+    va_list ap; va_start(ap, fmt); set_error_v(fmt, ap); va_end(ap);
+    return code;
+}
+#define LZ_TRY(call) do { int s_ = (call); if (s_ != KTC_OK) return s_; } while (0)
+
+constexpr int MAXD = KTC_MAX_DIMS;
+enum Kind : uint8_t { K_LEAF = 0, K_CONST, K_UN, K_BIN, K_CLAMP, K_CMP, K_SQUARE, K_BCAST, K_REDUCE };
+
+struct Shape {
+    int nd = 0;
+    int64_t d[MAXD];
+    int64_t volume() const { int64_t v = 1; for (int i = 0; i < nd; ++i) v *= d[i]; return v; }
+    bool operator==(const Shape& o) const { return nd == o.nd && std::equal(d, d + nd, o.d); }
+    bool operator!=(const Shape& o) const { return !(*this == o); }
+};
+static Shape make_shape(const int64_t* s, int nd) { Shape r; r.nd = nd; for (int i = 0; i < nd; ++i) r.d[i] = s[i]; return r; }
+
+// A value.  `buf` is set once the value is in memory (the node then acts as a leaf and forgets how it was
+// computed).  A K_REDUCE node is a sum that has not run yet: args[0] is the summed expression, op the sink
+// kind, imm[0] != 0 a mean; it is never part of a program -- whoever needs its value runs the pending sums.
+struct Node {
+    int refs = 0;
+    Kind kind = K_LEAF;
+    int op = 0;
+    int nargs = 0;
+    Node* args[2] = {nullptr, nullptr};     // strong
+    int nimm = 0;
+    float imm[2] = {0.f, 0.f};
+    Shape shape;
+    ktc_buf buf = 0;                        // one reference while non-zero
+    int dev = -1;
+    int evals = 0;
+    uint64_t owner = 0;                     // id of the cell that waits for this value (weak)
+    std::vector<Node*> parents;             // nodes built on this one (weak; a dying node unlinks itself)
+    bool has_sum = false;                   // a pending sum may sit underneath (never reset: a stale true only costs a look)
+    std::vector<ktc_buf> leaves;            // buffers this value is read from (sorted, unique)
+    // scratch of the walks (valid for one epoch)
+    uint32_t epoch = 0;
+    int pos = -1, uses = 0, reg = -1, cost = 0;
+    bool chosen = false;
+    bool stored() const { return buf != 0; }
+};
+
+struct Cell {
+    uint32_t gen = 1;
+    bool live = false;
+    Node* node = nullptr;                   // strong
+};
+
+struct Pending {
+    Node* node;                             // weak until an update hangs on it (then one reference is held)
+    bool strong;
+    std::vector<ktc_buf> targets;           // buffers to which this sum is added when it has run (one reference each)
+    std::vector<uint64_t> seq;              // request order of those updates
+};
+
+struct Cached {
+    bool fusable = false;
+    std::vector<uint32_t> code;
+    std::vector<std::pair<int, int>> imm_src;            // (position in the order, index in node.imm)
+    std::vector<std::pair<int, Shape>> leaf_plan;        // (position of the stored node, right-aligned shape)
+    std::vector<int> store_plan;                         // positions of the nodes written by STORE
+    int n_requested = 0;
+};
+
+struct Program {
+    Shape shape;
+    std::vector<uint32_t> code;
+    std::vector<float> imm;
+    std::vector<std::pair<ktc_buf, Shape>> leaves;
+    std::vector<std::pair<int, int>> imm_src;
+    std::vector<int> leaf_src;
+    std::vector<int> free_regs;
+    std::vector<Node*> order;
+    bool ok = true;                                       // false: not fusable
+};
+
+// ---- state (one recorder per process, guarded by one mutex) ---------------------------------------
+static std::mutex g_mu;
+static std::vector<Cell> g_cells;
+static std::vector<uint32_t> g_free_cells;
+static std::unordered_map<ktc_buf, std::vector<uint64_t>> g_deps;      // buffer -> cells whose pending expressions read it
+static size_t g_deps_purge_at = 1024;
+static std::vector<Pending> g_pending;
+static std::unordered_map<ktc_buf, int> g_pending_targets;            // buffer -> number of pending `+= sum` updates
+static uint64_t g_update_seq = 0;
+static std::unordered_map<std::string, Cached> g_cache;
+static constexpr size_t kCacheMax = 4096;
+static uint32_t g_epoch = 0;
+static int64_t g_live_nodes = 0;
+static int opt_recompute_limit = 2, opt_store_cost = 8, opt_defer_sums = 1, opt_defer_inplace = 1;
+static int64_t st_fused = 0, st_unfused = 0, st_multi = 0, st_cache_hits = 0, st_compiles = 0;
+
+// ---- nodes ----------------------------------------------------------------------------------------
+static void node_unref(Node* n);
+static Node* node_ref(Node* n) { if (n) ++n->refs; return n; }
+
+static void drop_args(Node* n, std::vector<Node*>& dead) {
+    for (int i = 0; i < n->nargs; ++i) {
+        Node* a = n->args[i];
+        if (!a) continue;
+        if (a->kind != K_CONST) {
+            auto& ps = a->parents;
+            auto it = std::find(ps.begin(), ps.end(), n);
+            if (it != ps.end()) { *it = ps.back(); ps.pop_back(); }
+        }
+        if (--a->refs == 0) dead.push_back(a);
+        n->args[i] = nullptr;
+    }
+    n->nargs = 0;
+}
+
+static void node_unref(Node* n) {
+    if (!n || --n->refs > 0) return;
+    std::vector<Node*> dead{n};
+    while (!dead.empty()) {                               // iterative: chains can be long
+        Node* d = dead.back(); dead.pop_back();
+        if (d->kind == K_REDUCE) {
+            for (size_t i = 0; i < g_pending.size(); ++i)
+                if (g_pending[i].node == d) { g_pending.erase(g_pending.begin() + i); break; }
+        }
+        drop_args(d, dead);
+        if (d->buf) B.release(d->buf);
+        --g_live_nodes;
+        delete d;
+    }
+}
+
+static void merge_leaves(std::vector<ktc_buf>& into, const std::vector<ktc_buf>& from) {
+    for (ktc_buf h : from) {
+        auto it = std::lower_bound(into.begin(), into.end(), h);
+        if (it == into.end() || *it != h) into.insert(it, h);
+    }
+}
+static void add_leaf(std::vector<ktc_buf>& into, ktc_buf h) {
+    auto it = std::lower_bound(into.begin(), into.end(), h);
+    if (it == into.end() || *it != h) into.insert(it, h);
+}
+static bool has_leaf(const Node* n, ktc_buf h) { return std::binary_search(n->leaves.begin(), n->leaves.end(), h); }
+
+// a new node holds one reference on each argument
+static Node* new_node(Kind kind, const Shape& shape, int op, Node* a0, Node* a1, const float* imm, int nimm) {
+    Node* n = new Node();
+    ++g_live_nodes;
+    n->kind = kind; n->op = op; n->shape = shape;
+    n->nimm = nimm; for (int i = 0; i < nimm; ++i) n->imm[i] = imm[i];
+    n->has_sum = kind == K_REDUCE;
+    Node* as[2] = {a0, a1};
+    for (int i = 0; i < 2; ++i) {
+        Node* a = as[i];
+        if (!a) continue;
+        n->args[n->nargs++] = node_ref(a);
+        if (a->has_sum && !a->stored()) n->has_sum = true;
+        if (a->dev >= 0) n->dev = a->dev;
+        if (a->stored()) add_leaf(n->leaves, a->buf); else merge_leaves(n->leaves, a->leaves);
+        if (a->kind != K_CONST) a->parents.push_back(n);
+    }
+    return n;
+}
+
+// takes over one reference on `buf`
+static Node* new_leaf(ktc_buf buf, const Shape& shape, int dev) {
+    Node* n = new Node();
+    ++g_live_nodes;
+    n->kind = K_LEAF; n->shape = shape; n->buf = buf; n->dev = dev;
+    n->leaves.push_back(buf);
+    return n;
+}
+
+static Node* new_const(float v) {
+    Shape s; s.nd = 1; s.d[0] = 1;
+    return new_node(K_CONST, s, 0, nullptr, nullptr, &v, 1);
+}
+
+static Node* strip(Node* n) {                             // look through broadcast markers: they change the shape, not the value
+    while (n->kind == K_BCAST && !n->stored()) n = n->args[0];
+    return n;
+}
+
+// ---- cells ----------------------------------------------------------------------------------------
+static Cell* cell_of(uint64_t id) {
+    const uint32_t idx = (uint32_t)(id & 0xffffffffu);
+    if (idx == 0 || idx > g_cells.size()) return nullptr;
+    Cell* c = &g_cells[idx - 1];
+    return (c->live && c->gen == (uint32_t)(id >> 32)) ? c : nullptr;
+}
+static uint64_t cell_id(const Cell* c) { return ((uint64_t)c->gen << 32) | (uint64_t)((c - g_cells.data()) + 1); }
+
+static uint64_t new_cell(Node* node /* one reference is taken over */) {
+    uint32_t idx;
+    if (!g_free_cells.empty()) { idx = g_free_cells.back(); g_free_cells.pop_back(); }
+    else { g_cells.emplace_back(); idx = (uint32_t)g_cells.size() - 1; }
+    Cell& c = g_cells[idx];
+    c.live = true; c.node = node;
+    return ((uint64_t)c.gen << 32) | (uint64_t)(idx + 1);
+}
+
+static bool waiting(const Node* n) {                      // a live cell still waits for exactly this value
+    const Cell* c = cell_of(n->owner);
+    return c && c->node == n && !n->stored();
+}
+
+static void register_cell(uint64_t id, Node* node) {
+    node->owner = id;
+    for (ktc_buf h : node->leaves) {
+        auto& refs = g_deps[h];
+        refs.push_back(id);
+        const size_t k = refs.size();
+        if (k > 64 && (k & (k - 1)) == 0)                 // at powers of two: drop the dead ones
+            refs.erase(std::remove_if(refs.begin(), refs.end(), [](uint64_t r) { return cell_of(r) == nullptr; }), refs.end());
+    }
+    if (g_deps.size() > g_deps_purge_at) {
+        for (auto it = g_deps.begin(); it != g_deps.end();) {
+            auto& refs = it->second;
+            refs.erase(std::remove_if(refs.begin(), refs.end(), [](uint64_t r) { return cell_of(r) == nullptr; }), refs.end());
+            if (refs.empty()) it = g_deps.erase(it); else ++it;
+        }
+        g_deps_purge_at = std::max<size_t>(1024, 2 * g_deps.size());
+    }
+}
+
+static uint64_t pending_cell(Kind kind, const Shape& shape, int op, Node* a0, Node* a1, const float* imm, int nimm) {
+    Node* n = new_node(kind, shape, op, a0, a1, imm, nimm);
+    const uint64_t id = new_cell(node_ref(n));
+    register_cell(id, n);
+    return id;
+}
+
+// The value of `node` now lives in `buf` (one reference is taken over): forget how it was computed, and make
+// everything that is computed from it depend on the new buffer.
+static void set_stored(Node* node, ktc_buf buf) {
+    node->buf = buf;
+    std::vector<Node*> dead;
+    drop_args(node, dead);
+    for (Node* d : dead) { ++d->refs; node_unref(d); }
+    const uint32_t ep = ++g_epoch;
+    std::vector<Node*> stack(node->parents.begin(), node->parents.end());
+    while (!stack.empty()) {
+        Node* a = stack.back(); stack.pop_back();
+        if (a->epoch == ep) continue;
+        a->epoch = ep;
+        add_leaf(a->leaves, buf);
+        if (cell_of(a->owner)) g_deps[buf].push_back(a->owner);
+        stack.insert(stack.end(), a->parents.begin(), a->parents.end());
+    }
+}
+
+// ---- shape algebra ----------------------------------------------------------------------------------
+// right-aligned broadcast shape (ShapeFunctions.kt:168-185); false on a non-singleton mismatch
+static bool common_shape(const Shape& a, const Shape& b, Shape* out) {
+    out->nd = std::max(a.nd, b.nd);
+    for (int i = 0; i < out->nd; ++i) {
+        const int ia = i - (out->nd - a.nd), ib = i - (out->nd - b.nd);
+        const int64_t da = ia >= 0 ? a.d[ia] : 1, db = ib >= 0 ? b.d[ib] : 1;
+        if (da != db && da != 1 && db != 1) return false;
+        out->d[i] = da == 1 ? db : da;
+    }
+    return true;
+}
+
+// ---- programs ---------------------------------------------------------------------------------------
+static bool has_pending_sum(Node* const* roots, int n) {
+    const uint32_t ep = ++g_epoch;
+    std::vector<Node*> stack;
+    for (int i = 0; i < n; ++i) if (roots[i] && roots[i]->has_sum) stack.push_back(roots[i]);
+    while (!stack.empty()) {
+        Node* x = stack.back(); stack.pop_back();
+        if (x->epoch == ep || x->stored()) continue;
+        x->epoch = ep;
+        if (x->kind == K_REDUCE) return true;
+        for (int i = 0; i < x->nargs; ++i) if (x->args[i]->has_sum) stack.push_back(x->args[i]);
+    }
+    return false;
+}
+
+// Children-first order of the unstored DAG under `roots` (broadcast markers looked through) and the number of
+// uses of every node (one per consumer, one per root); positions and use counts are left in the nodes.
+static void toposort(const std::vector<Node*>& roots, std::vector<Node*>& order) {
+    const uint32_t ep = ++g_epoch;
+    struct Item { Node* n; bool done; };
+    std::vector<Item> stack;
+    for (size_t i = roots.size(); i-- > 0;) stack.push_back({strip(roots[i]), false});
+    while (!stack.empty()) {
+        Item it = stack.back(); stack.pop_back();
+        if (it.done) { it.n->pos = (int)order.size(); order.push_back(it.n); continue; }
+        if (it.n->epoch == ep) { ++it.n->uses; continue; }
+        it.n->epoch = ep; it.n->uses = 1; it.n->reg = -1; it.n->chosen = false;
+        stack.push_back({it.n, true});
+        if (!it.n->stored())
+            for (int i = it.n->nargs; i-- > 0;) stack.push_back({strip(it.n->args[i]), false});
+    }
+}
+
+static const int kHeavy[6] = {10, 10, 12, 16, 2, 1};      // rough issue cost of one element: exp log tanh sigmoid reciprocal neg
+static int weight(const Node* n) {
+    if (n->kind == K_UN) return (n->op >= 0 && n->op < 6) ? kHeavy[n->op] : 1;
+    if (n->kind == K_BIN) return n->op == KTC_POW ? 30 : n->op == KTC_DIV ? 3 : 1;
+    return (n->kind == K_LEAF || n->kind == K_CONST || n->kind == K_BCAST) ? 0 : 1;
+}
+
+static void emit(Program& p, int op, int d = 0, int a = 0, int b = 0, int k = 0) {
+    if ((int)p.code.size() >= KTC_EXPR_MAX_INSTR) { p.ok = false; return; }
+    p.code.push_back((uint32_t)op | ((uint32_t)d << 8) | ((uint32_t)a << 12) | ((uint32_t)b << 16) | ((uint32_t)k << 20));
+}
+static int imm_index(Program& p, const float* v, int n, int src) {
+    if ((int)p.imm.size() + n > KTC_EXPR_MAX_IMM) { p.ok = false; return 0; }
+    const int k = (int)p.imm.size();
+    for (int j = 0; j < n; ++j) { p.imm.push_back(v[j]); p.imm_src.push_back({src, j}); }
+    return k;
+}
+static bool pad_shape(const Shape& s, int nd, Shape* out) {
+    if (s.nd > nd) return false;
+    out->nd = nd;
+    for (int i = 0; i < nd - s.nd; ++i) out->d[i] = 1;
+    for (int i = 0; i < s.nd; ++i) out->d[nd - s.nd + i] = s.d[i];
+    return true;
+}
+static int leaf_index(Program& p, ktc_buf h, const Shape& s, int src) {
+    Shape padded;
+    if (!pad_shape(s, p.shape.nd, &padded)) { p.ok = false; return 0; }
+    for (size_t i = 0; i < p.leaves.size(); ++i)
+        if (p.leaves[i].first == h && p.leaves[i].second == padded) return (int)i;
+    if ((int)p.leaves.size() >= KTC_EXPR_MAX_LEAVES) { p.ok = false; return 0; }
+    p.leaves.push_back({h, padded});
+    p.leaf_src.push_back(src);
+    return (int)p.leaves.size() - 1;
+}
+static int alloc_reg(Program& p) {
+    if (p.free_regs.empty()) { p.ok = false; return 0; }
+    const int r = p.free_regs.back(); p.free_regs.pop_back();
+    return r;
+}
+
+static const int kBinX[5] = {KTC_X_ADD, KTC_X_SUB, KTC_X_MUL, KTC_X_DIV, KTC_X_POW};
+static const int kUnX[6] = {KTC_X_EXP, KTC_X_LOG, KTC_X_TANH, KTC_X_SIGMOID, KTC_X_RCP, KTC_X_NEG};
+static const int kCmpX[4] = {KTC_X_CMP_LT, KTC_X_CMP_LTE, KTC_X_CMP_GT, KTC_X_CMP_GTE};
+
+// The uncached compilation: side-output choice, register allocation, emission.
+static void compile_uncached(Program& prog, std::vector<Node*>& store_nodes, const std::vector<Node*>& accs,
+                             const std::vector<Node*>& sinks, const std::vector<Node*>& order, int recompute_limit, int store_cost) {
+    const int64_t full_volume = prog.shape.volume();
+    // Side outputs.  Recomputing a short chain from an operand that is read anyway costs no memory traffic, so
+    // cheap values are recomputed (a bounded number of times); a value behind a transcendental is stored the
+    // first time -- the kernel that computes it is issue-bound and the store rides along.  Chosen bottom-up (a
+    // chosen value makes what is built on it cheap), then pruned top-down: nothing reaches below a stored value.
+    if (recompute_limit > 0 || store_cost > 0) {
+        for (Node* n : order) {
+            if (n->stored() || n->kind == K_CONST || n->kind == K_LEAF) { n->cost = 0; continue; }
+            int c = weight(n);
+            for (int i = 0; i < n->nargs; ++i) c += strip(n->args[i])->cost;
+            const bool requested = std::find(store_nodes.begin(), store_nodes.end(), n) != store_nodes.end();
+            if (waiting(n) && n->shape.volume() == full_volume && !requested &&
+                ((recompute_limit > 0 && n->evals >= recompute_limit) || (store_cost > 0 && c >= store_cost))) {
+                n->chosen = true;
+                c = 0;
+            }
+            n->cost = c;
+        }
+        const uint32_t ep = ++g_epoch;
+        std::vector<Node*> stack(sinks.begin(), sinks.end());
+        while (!stack.empty()) {
+            Node* n = strip(stack.back()); stack.pop_back();
+            if (n->epoch == ep || n->stored()) continue;
+            n->epoch = ep;
+            if (n->chosen && (int)store_nodes.size() < KTC_EXPR_MAX_STORES) { store_nodes.push_back(n); ++n->uses; continue; }
+            for (int i = 0; i < n->nargs; ++i) stack.push_back(n->args[i]);
+        }
+    }
+    auto release_use = [&](Node* n) { if (--n->uses == 0) prog.free_regs.push_back(n->reg); };
+    for (Node* n : order) {
+        int d;
+        if (n->stored()) {
+            d = alloc_reg(prog);
+            emit(prog, KTC_X_LOAD, d, 0, 0, leaf_index(prog, n->buf, n->shape, n->pos));
+        } else if (n->kind == K_CONST) {
+            d = alloc_reg(prog);
+            emit(prog, KTC_X_CONST, d, 0, 0, imm_index(prog, n->imm, 1, n->pos));
+        } else {
+            int srcs[2] = {0, 0};
+            Node* kids[2] = {nullptr, nullptr};
+            for (int i = 0; i < n->nargs; ++i) { kids[i] = strip(n->args[i]); srcs[i] = kids[i]->reg; }
+            for (int i = 0; i < n->nargs; ++i) release_use(kids[i]);
+            d = alloc_reg(prog);                          // may reuse a source register: the kernel reads before it writes
+            switch (n->kind) {
+            case K_BIN: emit(prog, kBinX[n->op], d, srcs[0], srcs[1]); break;
+            case K_UN: emit(prog, kUnX[n->op], d, srcs[0]); break;
+            case K_SQUARE: emit(prog, KTC_X_SQUARE, d, srcs[0]); break;
+            case K_CLAMP: emit(prog, KTC_X_CLAMP, d, srcs[0], 0, imm_index(prog, n->imm, 2, n->pos)); break;
+            case K_CMP: emit(prog, kCmpX[n->op], d, srcs[0], 0, imm_index(prog, n->imm, 1, n->pos)); break;
+            default: prog.ok = false; break;
+            }
+        }
+        if (!prog.ok) return;
+        n->reg = d;
+        for (size_t k = 0; k < store_nodes.size(); ++k)
+            if (store_nodes[k] == n) { emit(prog, KTC_X_STORE, 0, d, 0, (int)k); release_use(n); }
+        for (size_t j = 0; j < accs.size(); ++j)
+            if (accs[j] == n) { emit(prog, KTC_X_ACC, 0, d, 0, (int)j); release_use(n); }
+        if (!prog.ok) return;
+    }
+}
+
+static void key_put(std::string& k, int64_t v) { k.append(reinterpret_cast<const char*>(&v), sizeof(v)); }
+
+// Linearise the DAG under `stores` + `accs` into a register program over the iteration space `shape`.
+// accs: the summed node of a single-sink program, or one node per sink of a multi-sink program (the ACC of
+// entry j carries sink index j).  store_nodes returns the nodes written by STORE, in store-index order; the
+// first n_requested of them are the requested ones.  prog.ok == false: not fusable.
+// The program depends on the structure of the DAG (operations, sharing, which values are in memory and which
+// leaves are the same buffer) and on the per-node facts the side-output rule looks at -- not on buffer handles or
+// constants.  Graphs are rebuilt with fresh nodes every step, so the compiled form is cached by that structure
+// and re-bound to the current nodes: immediates, leaf handles and store nodes are looked up by position.
+static void compile_program(Program& prog, const Shape& shape, const std::vector<Node*>& stores_in, const std::vector<Node*>& accs_in,
+                            bool multi, int recompute_limit, int store_cost, std::vector<Node*>& store_nodes, int* n_requested) {
+    prog.shape = shape;
+    std::vector<Node*> accs, sinks;
+    for (Node* n : stores_in) sinks.push_back(strip(n));
+    for (Node* a : accs_in) { accs.push_back(strip(a)); sinks.push_back(accs.back()); }
+    toposort(sinks, prog.order);
+    const std::vector<Node*>& order = prog.order;
+    const int64_t full_volume = shape.volume();
+    std::string key;
+    key.reserve(64 + order.size() * 48);
+    key_put(key, shape.nd);
+    for (int i = 0; i < shape.nd; ++i) key_put(key, shape.d[i]);
+    key_put(key, (int64_t)stores_in.size());
+    for (Node* n : stores_in) key_put(key, strip(n)->pos);
+    key_put(key, (int64_t)accs.size());
+    for (Node* a : accs) key_put(key, a->pos);
+    key_put(key, multi ? 1 : 0); key_put(key, recompute_limit); key_put(key, store_cost);
+    std::vector<std::pair<std::pair<ktc_buf, Shape>, int>> first_leaf;       // (buffer, right-aligned shape) -> first position
+    for (Node* n : order) {
+        if (n->stored()) {
+            Shape padded;
+            if (!pad_shape(n->shape, shape.nd, &padded)) { prog.ok = false; return; }
+            int first = n->pos;
+            for (auto& f : first_leaf) if (f.first.first == n->buf && f.first.second == padded) { first = f.second; break; }
+            if (first == n->pos) first_leaf.push_back({{n->buf, padded}, n->pos});
+            key_put(key, -1); key_put(key, n->shape.nd);
+            for (int i = 0; i < n->shape.nd; ++i) key_put(key, n->shape.d[i]);
+            key_put(key, first);
+        } else if (n->kind == K_CONST) {
+            key_put(key, -2);
+        } else {
+            key_put(key, n->kind); key_put(key, n->op); key_put(key, n->nimm); key_put(key, n->nargs);
+            for (int i = 0; i < n->nargs; ++i) key_put(key, strip(n->args[i])->pos);
+            key_put(key, (waiting(n) && n->shape.volume() == full_volume) ? 1 : 0);
+            key_put(key, (recompute_limit > 0 && n->evals >= recompute_limit) ? 1 : 0);
+        }
+    }
+    auto hit = g_cache.find(key);
+    if (hit != g_cache.end()) {
+        ++st_cache_hits;
+        const Cached& c = hit->second;
+        if (!c.fusable) { prog.ok = false; return; }
+        prog.code = c.code;
+        for (auto& s : c.imm_src) prog.imm.push_back(order[s.first]->imm[s.second]);
+        for (auto& l : c.leaf_plan) prog.leaves.push_back({order[l.first]->buf, l.second});
+        store_nodes.clear();
+        for (int p : c.store_plan) store_nodes.push_back(order[p]);
+        *n_requested = c.n_requested;
+        return;
+    }
+    ++st_compiles;
+    for (int r = KTC_EXPR_REGS - 1; r >= 0; --r) prog.free_regs.push_back(r);
+    store_nodes.clear();
+    for (Node* n : stores_in) store_nodes.push_back(strip(n));
+    *n_requested = (int)store_nodes.size();
+    compile_uncached(prog, store_nodes, accs, sinks, order, recompute_limit, store_cost);
+    if (g_cache.size() < kCacheMax) {
+        Cached c;
+        c.fusable = prog.ok;
+        if (prog.ok) {
+            c.code = prog.code; c.imm_src = prog.imm_src; c.n_requested = *n_requested;
+            for (size_t i = 0; i < prog.leaves.size(); ++i) c.leaf_plan.push_back({prog.leaf_src[i], prog.leaves[i].second});
+            for (Node* n : store_nodes) c.store_plan.push_back(n->pos);
+        }
+        g_cache.emplace(std::move(key), std::move(c));
+    }
+}
+
+// views the iteration space [A, ...] as [A, rest]: possible when every operand is either full or broadcast
+// over the trailing dimensions
+static bool as_rows(Program& prog, const Shape& shape) {
+    int64_t rest = 1;
+    for (int i = 1; i < shape.nd; ++i) rest *= shape.d[i];
+    for (auto& l : prog.leaves) {
+        const Shape& s = l.second;
+        bool full = true, ones = true;
+        for (int i = 1; i < shape.nd; ++i) { full = full && s.d[i] == shape.d[i]; ones = ones && s.d[i] == 1; }
+        Shape r; r.nd = 2; r.d[0] = s.d[0];
+        if (full) r.d[1] = rest; else if (ones) r.d[1] = 1; else return false;
+        l.second = r;
+    }
+    prog.shape.nd = 2; prog.shape.d[0] = shape.d[0]; prog.shape.d[1] = rest;
+    return true;
+}
+
+static void pack_leaves(const Program& prog, std::vector<ktc_buf>& hs, std::vector<int64_t>& shapes) {
+    for (auto& l : prog.leaves) {
+        hs.push_back(l.first);
+        for (int i = 0; i < prog.shape.nd; ++i) shapes.push_back(l.second.d[i]);
+    }
+    if (hs.empty()) { hs.push_back(0); shapes.push_back(0); }
+}
+
+static int run_pending();
+static int force(Node* node, ktc_buf* h, Shape* shape);
+static int eager_into(Node* node, const Shape& shape, ktc_buf out);
+
+static int alloc_handle(int dev, int64_t n, ktc_buf* h) { return B.alloc(dev < 0 ? 0 : dev, n, h); }
+
+// `handle` (one owned reference) now holds node's value
+static void adopt(Node* node, ktc_buf handle) { set_stored(node, handle); }
+
+// Compile `stores` (+ the summed node `acc`) and run them as one kernel.  handles[i] receives stores[i]; own[i]:
+// the handle is a fresh buffer that node i adopts (its reference passes to the node).  Nodes stored on the side
+// get fresh buffers.  *fused = false: not fusable, nothing was run.
+static int try_fused(const Shape& shape, const std::vector<Node*>& stores, const std::vector<ktc_buf>& handles, const std::vector<bool>& own,
+                     Node* acc, int sink, ktc_buf sink_out, bool mean, bool rows_view, int dev, bool* fused) {
+    *fused = false;
+    if (!g_pending.empty()) {
+        std::vector<Node*> roots(stores);
+        if (acc) roots.push_back(acc);
+        if (has_pending_sum(roots.data(), (int)roots.size())) LZ_TRY(run_pending());
+    }
+    Program prog;
+    std::vector<Node*> store_nodes, accs;
+    if (acc) accs.push_back(acc);
+    int n_req = 0;
+    compile_program(prog, shape, stores, accs, false, opt_recompute_limit, opt_store_cost, store_nodes, &n_req);
+    if (!prog.ok) return KTC_OK;
+    if (rows_view && !as_rows(prog, shape)) return KTC_OK;
+    const int64_t total = shape.volume();
+    std::vector<ktc_buf> all(handles);
+    for (size_t i = n_req; i < store_nodes.size(); ++i) {
+        ktc_buf h = 0;
+        const int s = alloc_handle(dev, total, &h);
+        if (s != KTC_OK) { for (size_t j = handles.size(); j < all.size(); ++j) B.release(all[j]); return s; }
+        all.push_back(h);
+    }
+    std::vector<ktc_buf> lh; std::vector<int64_t> ls;
+    pack_leaves(prog, lh, ls);
+    const ktc_buf none = 0;
+    const float zero = 0.f;
+    const int rc = B.expr_eval(prog.code.data(), (int)prog.code.size(), prog.imm.empty() ? &zero : prog.imm.data(), (int)prog.imm.size(),
+                               prog.shape.d, prog.shape.nd, lh.data(), ls.data(), (int)prog.leaves.size(),
+                               all.empty() ? &none : all.data(), (int)all.size(), sink, sink_out, mean ? 1 : 0);
+    if (rc != KTC_OK) {
+        for (size_t j = handles.size(); j < all.size(); ++j) B.release(all[j]);
+        return rc == KTC_ENOTSUP ? KTC_OK : rc;
+    }
+    ++st_fused;
+    *fused = true;
+    for (Node* n : prog.order) ++n->evals;
+    for (int i = 0; i < n_req; ++i) if (own[i]) adopt(store_nodes[i], handles[i]);
+    for (size_t i = n_req; i < store_nodes.size(); ++i) adopt(store_nodes[i], all[handles.size() + (i - n_req)]);
+    return KTC_OK;
+}
+
+// Make sure the value under `node` (looking through broadcast markers) is in memory; the handle stays valid
+// while the node is alive.
+static int force(Node* node, ktc_buf* h, Shape* shape) {
+    Node* nd = strip(node);
+    if (nd->kind == K_REDUCE && !nd->stored()) {
+        LZ_TRY(run_pending());
+        if (!nd->stored()) return fail(KTC_ESTATE, "a pending sum was not evaluated");
+    }
+    if (!nd->stored()) {
+        ktc_buf fresh = 0;
+        LZ_TRY(alloc_handle(nd->dev, nd->shape.volume(), &fresh));
+        bool fused = false;
+        int s = try_fused(nd->shape, {nd}, {fresh}, {true}, nullptr, KTC_EXPR_STORE_ONLY, 0, false, false, nd->dev, &fused);
+        if (s == KTC_OK && !fused) {
+            ++st_unfused;
+            s = eager_into(nd, nd->shape, fresh);
+            if (s == KTC_OK) adopt(nd, fresh);
+        }
+        if (s != KTC_OK) { if (!nd->stored()) B.release(fresh); return s; }
+    }
+    *h = nd->buf;
+    if (shape) *shape = nd->shape;
+    return KTC_OK;
+}
+
+// Give a pending cell storage.
+static int materialize_cell(Cell* cell) {
+    Node* node = cell->node;
+    if (strip(node) == node) {
+        if (node->stored()) return KTC_OK;
+        ktc_buf h;
+        return force(node, &h, nullptr);
+    }
+    // an alias of / a broadcast over another value: storage of its own
+    node_ref(node);                                       // the cell may be re-pointed while its operands are evaluated
+    ktc_buf h = 0;
+    int s = alloc_handle(node->dev, node->shape.volume(), &h);
+    if (s == KTC_OK) {
+        bool fused = false;
+        s = try_fused(node->shape, {node}, {h}, {false}, nullptr, KTC_EXPR_STORE_ONLY, 0, false, false, node->dev, &fused);
+        if (s == KTC_OK && !fused) { ++st_unfused; s = eager_into(node, node->shape, h); }
+        if (s == KTC_OK) {
+            Node* leaf = new_leaf(h, node->shape, node->dev);
+            leaf->owner = cell_id(cell);
+            Node* old = cell->node;
+            cell->node = node_ref(leaf);
+            node_unref(old);
+        } else {
+            B.release(h);
+        }
+    }
+    node_unref(node);
+    return s;
+}
+
+// Before `handle` is written in place: every pending expression that reads it is evaluated.
+static int flush_dependents(ktc_buf handle) {
+    if (!g_pending.empty()) {
+        bool hit = g_pending_targets.count(handle) != 0;
+        for (size_t i = 0; !hit && i < g_pending.size(); ++i) hit = has_leaf(g_pending[i].node, handle);
+        if (hit) LZ_TRY(run_pending());
+    }
+    auto it = g_deps.find(handle);
+    if (it == g_deps.end()) return KTC_OK;
+    std::vector<uint64_t> refs = std::move(it->second);
+    g_deps.erase(it);
+    for (uint64_t id : refs) {
+        Cell* c = cell_of(id);
+        if (c && c->node && !c->node->stored() && has_leaf(c->node, handle)) LZ_TRY(materialize_cell(c));
+    }
+    return KTC_OK;
+}
+
+// ---- call-by-call evaluation of what the kernel declines -----------------------------------------------
+static int call_op(Node* nd, Node* const* kids, ktc_buf out, int64_t m) {
+    if (nd->kind == K_BIN) {
+        Node *a = kids[0], *b = kids[1];
+        if (a->kind == K_CONST || b->kind == K_CONST) {
+            const bool first = a->kind == K_CONST;
+            ktc_buf h; LZ_TRY(force(first ? b : a, &h, nullptr));
+            return B.scalar(nd->op, out, h, (first ? a : b)->imm[0], m, first ? 1 : 0);
+        }
+        ktc_buf ha, hb; Shape sa, sb;
+        LZ_TRY(force(a, &ha, &sa)); LZ_TRY(force(b, &hb, &sb));
+        if (sa == sb) return B.binary(nd->op, out, ha, hb, m);
+        return B.binary_bcast(nd->op, out, ha, sa.d, sa.nd, hb, sb.d, sb.nd);
+    }
+    ktc_buf h; LZ_TRY(force(kids[0], &h, nullptr));
+    switch (nd->kind) {
+    case K_UN: return B.unary(nd->op, out, h, m);
+    case K_SQUARE: return B.scalar(KTC_POW, out, h, 2.0f, m, 0);
+    case K_CLAMP: return B.clamp(out, h, nd->imm[0], nd->imm[1], m);
+    case K_CMP: return B.compare_scalar(nd->op, out, h, nd->imm[0], m);
+    default: return fail(KTC_ESTATE, "cannot evaluate an expression node of kind %d", (int)nd->kind);
+    }
+}
+
+// One step of the call-by-call evaluation: the operands of `node` are forced into memory (each as a fused
+// program where possible), then the library call for `node` itself runs at the operation's natural shape --
+// the common shape of its operands with broadcast markers looked through -- and the result is spread to
+// `shape` if that is larger.
+static int eager_into(Node* node, const Shape& shape, ktc_buf out) {
+    Node* nd = strip(node);
+    const int64_t n = shape.volume();
+    auto spread = [&](ktc_buf h, const Shape& shp) -> int {
+        if (shp.volume() == n) return B.d2d(out, 0, h, 0, n);
+        return B.broadcast_to(out, shape.d, shape.nd, h, shp.d, shp.nd);
+    };
+    if (nd->kind == K_REDUCE && !nd->stored()) { ktc_buf h; LZ_TRY(force(nd, &h, nullptr)); }
+    if (nd->stored()) return spread(nd->buf, nd->shape);
+    node_ref(nd);
+    Node* kids[2] = {nullptr, nullptr};
+    Shape natural; bool have = false;
+    for (int i = 0; i < nd->nargs; ++i) {
+        kids[i] = strip(nd->args[i]);
+        node_ref(kids[i]);
+        if (kids[i]->kind == K_CONST) continue;
+        if (!have) { natural = kids[i]->shape; have = true; }
+        else if (natural != kids[i]->shape) { Shape c; common_shape(natural, kids[i]->shape, &c); natural = c; }
+    }
+    const int nk = nd->nargs;
+    const int64_t m = natural.volume();
+    int s;
+    if (m == n) {
+        s = call_op(nd, kids, out, m);
+    } else {
+        ktc_buf tmp = 0;
+        s = alloc_handle(nd->dev, m, &tmp);
+        if (s == KTC_OK) {
+            s = call_op(nd, kids, tmp, m);
+            if (s == KTC_OK) s = spread(tmp, natural);
+            B.release(tmp);
+        }
+    }
+    for (int i = 0; i < nk; ++i) node_unref(kids[i]);
+    node_unref(nd);
+    return s;
+}
+
+// ---- pending sums ---------------------------------------------------------------------------------------
+static int try_fused_sums(const Shape& shape, const std::vector<Node*>& nodes, bool* fused) {
+    *fused = false;
+    std::vector<Node*> exprs; std::vector<int> kinds, means;
+    bool any_rows = false;
+    for (Node* nd : nodes) { exprs.push_back(nd->args[0]); kinds.push_back(nd->op); means.push_back(nd->imm[0] != 0.f ? 1 : 0); any_rows = any_rows || nd->op == KTC_EXPR_SUM_ROWS; }
+    Program prog;
+    std::vector<Node*> store_nodes; int n_req = 0;
+    // every consumer known so far sits in this pass: nothing is stored on the side for its cost alone
+    compile_program(prog, shape, {}, exprs, true, opt_recompute_limit, 0, store_nodes, &n_req);
+    if (!prog.ok) return KTC_OK;
+    if (any_rows && !as_rows(prog, shape)) return KTC_OK;
+    const int dev = nodes[0]->dev;
+    std::vector<ktc_buf> outs, extra;
+    auto drop = [&]() { for (ktc_buf h : outs) B.release(h); for (ktc_buf h : extra) B.release(h); };
+    for (Node* nd : nodes) { ktc_buf h = 0; const int s = alloc_handle(dev, nd->shape.volume(), &h); if (s != KTC_OK) { drop(); return s; } outs.push_back(h); }
+    for (size_t i = 0; i < store_nodes.size(); ++i) { ktc_buf h = 0; const int s = alloc_handle(dev, shape.volume(), &h); if (s != KTC_OK) { drop(); return s; } extra.push_back(h); }
+    std::vector<ktc_buf> lh; std::vector<int64_t> ls;
+    pack_leaves(prog, lh, ls);
+    const ktc_buf none = 0; const float zero = 0.f;
+    const int rc = B.expr_eval_multi(prog.code.data(), (int)prog.code.size(), prog.imm.empty() ? &zero : prog.imm.data(), (int)prog.imm.size(),
+                                     prog.shape.d, prog.shape.nd, lh.data(), ls.data(), (int)prog.leaves.size(),
+                                     extra.empty() ? &none : extra.data(), (int)extra.size(), kinds.data(), outs.data(), means.data(), (int)nodes.size());
+    if (rc != KTC_OK) { drop(); return rc == KTC_ENOTSUP ? KTC_OK : rc; }
+    ++st_fused; ++st_multi;
+    *fused = true;
+    for (Node* n : prog.order) ++n->evals;
+    for (size_t i = 0; i < store_nodes.size(); ++i) adopt(store_nodes[i], extra[i]);
+    for (size_t i = 0; i < nodes.size(); ++i) adopt(nodes[i], outs[i]);
+    return KTC_OK;
+}
+
+// A single pending sum: fused with its expression, else the expression is evaluated and reduced by the
+// library's reduction call.
+static int run_one_sum(Node* nd) {
+    Node* expr = node_ref(nd->args[0]);
+    const Shape shape = expr->shape;
+    const bool mean = nd->imm[0] != 0.f;
+    ktc_buf out = 0;
+    int s = alloc_handle(nd->dev, nd->shape.volume(), &out);
+    if (s != KTC_OK) { node_unref(expr); return s; }
+    bool ok = false;
+    s = try_fused(shape, {}, {}, {}, expr, nd->op, out, mean, nd->op == KTC_EXPR_SUM_ROWS, nd->dev, &ok);
+    if (s == KTC_OK && !ok) {
+        ++st_unfused;
+        ktc_buf h; Shape shp;
+        s = force(expr, &h, &shp);
+        const int64_t n = shape.volume();
+        ktc_buf tmp = 0;
+        if (s == KTC_OK && shp.volume() != n) {           // a broadcast marker over a smaller value
+            s = alloc_handle(nd->dev, n, &tmp);
+            if (s == KTC_OK) { h = tmp; s = eager_into(expr, shape, tmp); }
+        }
+        if (s == KTC_OK) {
+            if (nd->op == KTC_EXPR_SUM_ALL) s = B.reduce_all(mean ? KTC_MEAN : KTC_SUM, out, h, n);
+            else if (nd->op == KTC_EXPR_SUM_LAST) s = B.reduce_axis(KTC_SUM, out, h, n / shape.d[shape.nd - 1], shape.d[shape.nd - 1], 1);
+            else s = B.reduce_axis(KTC_SUM, out, h, 1, shape.d[0], n / shape.d[0]);
+        }
+        if (tmp) B.release(tmp);
+    }
+    node_unref(expr);
+    if (s != KTC_OK) { B.release(out); return s; }
+    adopt(nd, out);
+    return KTC_OK;
+}
+
+// Evaluate every pending sum that is still wanted, then apply the pending updates in the order they were
+// requested.  Sums over the same iteration space run as one multi-sink pass (up to KTC_EXPR_MAX_SINKS per
+// pass); a sum whose expression contains another pending sum waits for it.
+static int run_pending() {
+    std::vector<Pending> entries;
+    entries.swap(g_pending);
+    g_pending_targets.clear();
+    struct Todo { Node* nd; std::vector<ktc_buf> targets; std::vector<uint64_t> seq; };
+    std::vector<Todo> todo;
+    for (Pending& e : entries) {
+        if (!e.strong) node_ref(e.node);                  // keep every sum alive until this call is over
+        if (!e.node->stored()) todo.push_back({e.node, e.targets, e.seq});
+    }
+    int status = KTC_OK;
+    std::vector<Node*> waiting_nodes;
+    for (auto& t : todo) waiting_nodes.push_back(t.nd);
+    while (status == KTC_OK && !waiting_nodes.empty()) {
+        std::vector<Node*> ready, rest;
+        for (Node* nd : waiting_nodes) { Node* e = nd->args[0]; (has_pending_sum(&e, 1) ? rest : ready).push_back(nd); }
+        if (ready.empty()) { status = fail(KTC_ESTATE, "pending sums depend on one another"); break; }
+        waiting_nodes.swap(rest);
+        // one pass per iteration space; leading-axis sums view the space as [A, rest], last-axis sums need its
+        // innermost dimension, so the two kinds do not share a pass (full sums join either)
+        std::vector<std::pair<Shape, std::vector<Node*>>> by_shape;
+        for (Node* nd : ready) {
+            const Shape& s = nd->args[0]->shape;
+            auto it = std::find_if(by_shape.begin(), by_shape.end(), [&](const std::pair<Shape, std::vector<Node*>>& p) { return p.first == s; });
+            if (it == by_shape.end()) { by_shape.push_back({s, {}}); it = by_shape.end() - 1; }
+            it->second.push_back(nd);
+        }
+        std::vector<std::pair<Shape, std::vector<Node*>>> groups;
+        for (auto& bs : by_shape) {
+            std::vector<Node*> last, rows, full;
+            for (Node* nd : bs.second) (nd->op == KTC_EXPR_SUM_LAST ? last : nd->op == KTC_EXPR_SUM_ROWS ? rows : full).push_back(nd);
+            if (!rows.empty() || last.empty()) { rows.insert(rows.end(), full.begin(), full.end()); groups.push_back({bs.first, rows}); full.clear(); }
+            if (!last.empty()) { last.insert(last.end(), full.begin(), full.end()); groups.push_back({bs.first, last}); }
+        }
+        for (auto& g : groups) {
+            for (size_t i = 0; status == KTC_OK && i < g.second.size(); i += KTC_EXPR_MAX_SINKS) {
+                std::vector<Node*> chunk(g.second.begin() + i, g.second.begin() + std::min(g.second.size(), i + KTC_EXPR_MAX_SINKS));
+                bool fused = false;
+                if (chunk.size() > 1) status = try_fused_sums(g.first, chunk, &fused);
+                for (size_t j = 0; status == KTC_OK && !fused && j < chunk.size(); ++j) status = run_one_sum(chunk[j]);
+            }
+        }
+    }
+    if (status == KTC_OK) {
+        struct Up { uint64_t seq; ktc_buf target; Node* nd; };
+        std::vector<Up> ups;
+        for (auto& t : todo) for (size_t i = 0; i < t.targets.size(); ++i) ups.push_back({t.seq[i], t.targets[i], t.nd});
+        std::sort(ups.begin(), ups.end(), [](const Up& a, const Up& b) { return a.seq < b.seq; });
+        for (auto& u : ups) {
+            status = B.binary_inplace(KTC_PLUS, u.target, u.nd->buf, u.nd->shape.volume());
+            if (status != KTC_OK) break;
+        }
+    }
+    for (Pending& e : entries) {
+        for (ktc_buf h : e.targets) B.release(h);
+        node_unref(e.node);
+    }
+    return status;
+}
+
+// Remember `buffer handle += node` (node: a pending sum).  The node is kept alive from here on.
+static bool add_pending_update(Node* node, ktc_buf handle) {
+    for (Pending& e : g_pending) {
+        if (e.node != node) continue;
+        if (B.retain(handle) != KTC_OK) return false;
+        if (!e.strong) { e.strong = true; node_ref(node); }
+        e.targets.push_back(handle);
+        e.seq.push_back(++g_update_seq);
+        ++g_pending_targets[handle];
+        return true;
+    }
+    return false;
+}
+
+static uint64_t defer_sum(Node* expr, int kind, bool mean, const Shape& res_shape) {
+    const float m = mean ? 1.f : 0.f;
+    Node* n = new_node(K_REDUCE, res_shape, kind, expr, nullptr, &m, 1);
+    const uint64_t id = new_cell(node_ref(n));
+    register_cell(id, n);
+    g_pending.push_back({n, false, {}, {}});
+    return id;
+}
+
+// ---- operands -------------------------------------------------------------------------------------------
+// the node under a cell as an operand of a new expression
+static int operand(uint64_t id, Node** out) {
+    Cell* c = cell_of(id);
+    if (!c || !c->node) return fail(KTC_ESTATE, "stale or unknown expression cell");
+    Node* n = c->node;
+    if (n->stored() && !g_pending_targets.empty() && g_pending_targets.count(n->buf)) {
+        LZ_TRY(run_pending());                            // a `+= pending sum` update of this buffer is due
+        c = cell_of(id);
+        n = c->node;
+    }
+    *out = n;
+    return KTC_OK;
+}
+
+// target = f(target, ...) in place.  state: 0 the target's buffer was written (or will be, by a recorded
+// update: 2); 1 the cell is pending now (a caller that held the buffer drops its reference).
+static int assign(uint64_t target_id, Kind kind, int op, Node* a0, Node* a1, const float* imm, int nimm, int* state) {
+    Cell* cell = cell_of(target_id);
+    Node* own = cell->node;
+    Node* node = new_node(kind, own->shape, op, a0, a1, imm, nimm);
+    node_ref(node);
+    auto done = [&](int s, int st) { if (state) *state = st; node_unref(node); return s; };
+    if (!own->stored()) {                                 // a pending target takes the new value
+        cell->node = node_ref(node);
+        register_cell(target_id, node);
+        node_unref(own);
+        return done(KTC_OK, 1);
+    }
+    if (strip(own) != own) return done(fail(KTC_ESTATE, "in-place call on a broadcast marker"), 0);
+    const ktc_buf h = own->buf;
+    const int64_t n = own->shape.volume();
+    node_ref(own);
+    auto finish = [&](int s, int st) { node_unref(own); return done(s, st); };
+    int s = flush_dependents(h);
+    if (s != KTC_OK) return finish(s, 0);
+    Node* other = kind == K_BIN ? strip(a1) : nullptr;
+    if (node->has_sum && !g_pending.empty()) {
+        if (other && op == KTC_PLUS && other->kind == K_REDUCE && !other->stored() && other->shape.volume() == n && strip(a0)->stored()
+            && add_pending_update(other, h))
+            return finish(KTC_OK, 2);                     // target += pending sum: applied when the sums run
+        s = run_pending();
+        if (s != KTC_OK) return finish(s, 0);
+    }
+    if (other && (other->kind == K_CONST || (other->stored() && other->shape.volume() == n))) {
+        // nothing to fuse: the operand is already in memory (a gradient accumulated into a Variable, ...)
+        if (other->kind == K_CONST) return finish(B.scalar_inplace(op, h, other->imm[0], n), 0);
+        return finish(B.binary_inplace(op, h, other->buf, n), 0);
+    }
+    cell = cell_of(target_id);
+    if (opt_defer_inplace && cell->node == own && (a0 == own || a1 == own)) {
+        // Nobody else holds the buffer (the caller's reference and this cell's node): instead of a pass that
+        // rewrites the buffer now, the cell becomes pending -- its node reads the old buffer as an operand -- so that
+        // the in-place calls that follow join one program.  A buffer with another holder (a view, a shallow copy, a
+        // pending expression that still reads it) is written in place as before.
+        int cnt = 0;
+        s = B.refcount(h, &cnt);
+        if (s != KTC_OK) return finish(s, 0);
+        if (cnt == 2) {
+            cell->node = node_ref(node);
+            register_cell(target_id, node);
+            node_unref(own);                              // the cell's reference; `node` keeps the leaf and its buffer
+            return finish(KTC_OK, 1);
+        }
+    }
+    bool fused = false;
+    s = try_fused(own->shape, {node}, {h}, {false}, nullptr, KTC_EXPR_STORE_ONLY, 0, false, false, own->dev, &fused);
+    if (s != KTC_OK || fused) return finish(s, 0);
+    ++st_unfused;
+    if (kind == K_SQUARE) return finish(B.scalar_inplace(KTC_POW, h, 2.0f, n), 0);
+    if (kind != K_BIN) return finish(fail(KTC_ESTATE, "in-place call of kind %d", (int)kind), 0);
+    if (other->kind == K_CONST) return finish(B.scalar_inplace(op, h, other->imm[0], n), 0);
+    ktc_buf hb; Shape shp;
+    s = force(other, &hb, &shp);
+    if (s != KTC_OK) return finish(s, 0);
+    if (shp.volume() != n) {                              // a broadcast marker over a smaller value
+        ktc_buf tmp = 0;
+        s = alloc_handle(own->dev, n, &tmp);
+        if (s == KTC_OK) { s = eager_into(a1, own->shape, tmp); if (s == KTC_OK) s = B.binary_inplace(op, h, tmp, n); B.release(tmp); }
+        return finish(s, 0);
+    }
+    return finish(B.binary_inplace(op, h, hb, n), 0);
+}
+
+}  // namespace lz
+}  // namespace ktc
+
+// ---- the C ABI ------------------------------------------------------------------------------------------
+using namespace ktc::lz;
+#define LZ_LOCK std::lock_guard<std::mutex> lock_(g_mu)
+
+extern "C" {
+
+#ifdef KTC_LAZY_STANDALONE
+KTC_API int ktc_lazy_test_set_backend(void* const* table, int n) {
+    if (n != kBackendEntries) return KTC_EINVAL;
+    memcpy(&B, table, sizeof(B));
+    return KTC_OK;
+}
+KTC_API const char* ktc_last_error(void) { return g_err; }
+#endif
+
+KTC_API int ktc_lazy_leaf(ktc_buf buf, const int64_t* shape, int ndim, ktc_lazy_cell* out) {
+    LZ_LOCK;
+    if (!out || ndim < 0 || ndim > MAXD) return fail(KTC_EINVAL, "ktc_lazy_leaf: bad arguments");
+    int dev = 0; int64_t n = 0;
+    LZ_TRY(B.buf_info(buf, &dev, &n, nullptr));
+    const Shape s = make_shape(shape, ndim);
+    if (s.volume() > n) return fail(KTC_EINVAL, "ktc_lazy_leaf: shape holds %lld elements, the buffer %lld", (long long)s.volume(), (long long)n);
+    LZ_TRY(B.retain(buf));
+    Node* leaf = new_leaf(buf, s, dev);
+    *out = new_cell(node_ref(leaf));
+    leaf->owner = *out;
+    return KTC_OK;
+}
+
+KTC_API int ktc_lazy_free(ktc_lazy_cell cell) {
+    LZ_LOCK;
+    Cell* c = cell_of(cell);
+    if (!c) return fail(KTC_ESTATE, "ktc_lazy_free: stale or unknown cell");
+    Node* n = c->node;
+    c->node = nullptr; c->live = false; ++c->gen;
+    g_free_cells.push_back((uint32_t)(c - g_cells.data()));
+    node_unref(n);
+    return KTC_OK;
+}
+
+KTC_API int ktc_lazy_unary(int op, ktc_lazy_cell a, ktc_lazy_cell* out) {
+    LZ_LOCK;
+    if (op < KTC_EXP || op > KTC_NEG) return fail(KTC_ENOTSUP, "ktc_lazy_unary: op %d is not an expression instruction", op);
+    Node* na; LZ_TRY(operand(a, &na));
+    *out = pending_cell(K_UN, na->shape, op, na, nullptr, nullptr, 0);
+    return KTC_OK;
+}
+
+KTC_API int ktc_lazy_binary(int op, ktc_lazy_cell a, ktc_lazy_cell b, ktc_lazy_cell* out) {
+    LZ_LOCK;
+    if (op < KTC_PLUS || op > KTC_POW) return fail(KTC_EINVAL, "ktc_lazy_binary: unknown op %d", op);
+    Node *na, *nb;
+    LZ_TRY(operand(a, &na)); LZ_TRY(operand(b, &nb)); LZ_TRY(operand(a, &na));
+    Shape common;
+    if (!common_shape(na->shape, nb->shape, &common)) return fail(KTC_EINVAL, "ktc_lazy_binary: shapes do not broadcast");
+    *out = pending_cell(K_BIN, common, op, na, nb, nullptr, 0);
+    return KTC_OK;
+}
+
+static int scalar_node(int op, Node* me, float s, int scalar_first, Kind* kind, Node** a0, Node** a1) {
+    if (op == KTC_POW && !scalar_first && s == 2.0f) { *kind = K_SQUARE; *a0 = me; *a1 = nullptr; return 0; }
+    Node* c = new_const(s);
+    *kind = K_BIN;
+    *a0 = scalar_first ? c : me; *a1 = scalar_first ? me : c;
+    return 1;                                             // a constant node was created (one floating reference to drop)
+}
+
+KTC_API int ktc_lazy_scalar(int op, ktc_lazy_cell a, float s, int scalar_first, ktc_lazy_cell* out) {
+    LZ_LOCK;
+    if (op < KTC_PLUS || op > KTC_POW) return fail(KTC_EINVAL, "ktc_lazy_scalar: unknown op %d", op);
+    Node* na; LZ_TRY(operand(a, &na));
+    if (op == KTC_POW && !scalar_first && s == 1.0f) {    // x pow 1 is x: a deep copy that is not made yet
+        *out = pending_cell(K_BCAST, na->shape, 0, na, nullptr, nullptr, 0);
+        return KTC_OK;
+    }
+    Kind kind; Node *a0, *a1;
+    const int made = scalar_node(op, na, s, scalar_first, &kind, &a0, &a1);
+    Node* c = made ? (scalar_first ? a0 : a1) : nullptr;
+    if (c) node_ref(c);
+    *out = pending_cell(kind, na->shape, kind == K_SQUARE ? 0 : op, a0, a1, nullptr, 0);
+    if (c) node_unref(c);
+    return KTC_OK;
+}
+
+KTC_API int ktc_lazy_clamp(ktc_lazy_cell a, float lo, float hi, ktc_lazy_cell* out) {
+    LZ_LOCK;
+    Node* na; LZ_TRY(operand(a, &na));
+    const float imm[2] = {lo, hi};
+    *out = pending_cell(K_CLAMP, na->shape, 0, na, nullptr, imm, 2);
+    return KTC_OK;
+}
+
+KTC_API int ktc_lazy_compare_scalar(int op, ktc_lazy_cell a, float value, ktc_lazy_cell* out) {
+    LZ_LOCK;
+    if (op < KTC_LT || op > KTC_GTE) return fail(KTC_ENOTSUP, "ktc_lazy_compare_scalar: op %d is not an expression instruction", op);
+    Node* na; LZ_TRY(operand(a, &na));
+    *out = pending_cell(K_CMP, na->shape, op, na, nullptr, &value, 1);
+    return KTC_OK;
+}
+
+KTC_API int ktc_lazy_broadcast_to(ktc_lazy_cell a, const int64_t* shape, int ndim, ktc_lazy_cell* out) {
+    LZ_LOCK;
+    if (ndim < 0 || ndim > MAXD) return fail(KTC_EINVAL, "ktc_lazy_broadcast_to: bad rank");
+    Node* na; LZ_TRY(operand(a, &na));
+    const Shape s = make_shape(shape, ndim);
+    Shape common;
+    if (!common_shape(na->shape, s, &common) || common != s) return fail(KTC_EINVAL, "ktc_lazy_broadcast_to: shape cannot be broadcast to the target");
+    *out = pending_cell(K_BCAST, s, 0, na, nullptr, nullptr, 0);
+    return KTC_OK;
+}
+
+KTC_API int ktc_lazy_assign_binary(int op, ktc_lazy_cell target, ktc_lazy_cell other, int* state) {
+    LZ_LOCK;
+    if (op < KTC_PLUS || op > KTC_POW) return fail(KTC_EINVAL, "ktc_lazy_assign_binary: unknown op %d", op);
+    Node *nt, *no;
+    LZ_TRY(operand(target, &nt)); LZ_TRY(operand(other, &no)); LZ_TRY(operand(target, &nt));
+    if (nt->shape != no->shape) return fail(KTC_EINVAL, "Shapes does not match for inplace operation on tensors");
+    node_ref(no);
+    const int s = assign(target, K_BIN, op, nt, no, nullptr, 0, state);
+    node_unref(no);
+    return s;
+}
+
+KTC_API int ktc_lazy_assign_scalar(int op, ktc_lazy_cell target, float s, int* state) {
+    LZ_LOCK;
+    if (op < KTC_PLUS || op > KTC_POW) return fail(KTC_EINVAL, "ktc_lazy_assign_scalar: unknown op %d", op);
+    Node* nt; LZ_TRY(operand(target, &nt));
+    Kind kind; Node *a0, *a1;
+    const int made = scalar_node(op, nt, s, 0, &kind, &a0, &a1);
+    if (made) node_ref(a1);
+    const int st = assign(target, kind, kind == K_SQUARE ? 0 : op, a0, a1, nullptr, 0, state);
+    if (made) node_unref(a1);
+    return st;
+}
+
+// kind: KTC_EXPR_SUM_ALL (sum() / mean()), KTC_EXPR_SUM_ROWS (sum over axis 0 of [A, ...]), KTC_EXPR_SUM_LAST
+// (sum over the innermost axis); res_shape is the shape of the result.
+KTC_API int ktc_lazy_sum(ktc_lazy_cell a, int kind, int mean, const int64_t* res_shape, int res_ndim, ktc_lazy_cell* out) {
+    LZ_LOCK;
+    if (kind != KTC_EXPR_SUM_ALL && kind != KTC_EXPR_SUM_ROWS && kind != KTC_EXPR_SUM_LAST) return fail(KTC_EINVAL, "ktc_lazy_sum: unknown kind %d", kind);
+    if (res_ndim < 0 || res_ndim > MAXD) return fail(KTC_EINVAL, "ktc_lazy_sum: bad rank");
+    Node* na; LZ_TRY(operand(a, &na));
+    const Shape rs = make_shape(res_shape, res_ndim);
+    const Shape shape = na->shape;
+    if (shape.nd < 1 || (kind != KTC_EXPR_SUM_ALL && shape.nd < 2)) return fail(KTC_EINVAL, "ktc_lazy_sum: rank %d has no such axis", shape.nd);
+    const int64_t n = shape.volume();
+    const int64_t want = kind == KTC_EXPR_SUM_ALL ? 1 : kind == KTC_EXPR_SUM_ROWS ? n / std::max<int64_t>(1, shape.d[0]) : n / std::max<int64_t>(1, shape.d[shape.nd - 1]);
+    if (rs.volume() != want) return fail(KTC_EINVAL, "ktc_lazy_sum: result shape holds %lld elements, the sum %lld", (long long)rs.volume(), (long long)want);
+    Node* expr = strip(na);
+    const bool pending_expr = !expr->stored() && expr->kind != K_REDUCE;
+    if (opt_defer_sums && pending_expr) { *out = defer_sum(na, kind, mean != 0, rs); return KTC_OK; }
+    // the sum runs now: fused with the pending expression where possible, else over the evaluated operand
+    node_ref(na);
+    ktc_buf res = 0;
+    int s = alloc_handle(na->dev, rs.volume(), &res);
+    bool fused = false;
+    if (s == KTC_OK && pending_expr)
+        s = try_fused(shape, {}, {}, {}, na, kind, res, mean != 0, kind == KTC_EXPR_SUM_ROWS, na->dev, &fused);
+    if (s == KTC_OK && !fused) {
+        ktc_buf h; Shape shp;
+        s = force(na, &h, &shp);
+        ktc_buf tmp = 0;
+        if (s == KTC_OK && shp.volume() != n) { s = alloc_handle(na->dev, n, &tmp); if (s == KTC_OK) { h = tmp; s = eager_into(na, shape, tmp); } }
+        if (s == KTC_OK) {
+            if (kind == KTC_EXPR_SUM_ALL) s = B.reduce_all(mean ? KTC_MEAN : KTC_SUM, res, h, n);
+            else if (kind == KTC_EXPR_SUM_LAST) s = B.reduce_axis(KTC_SUM, res, h, n / shape.d[shape.nd - 1], shape.d[shape.nd - 1], 1);
+            else s = B.reduce_axis(KTC_SUM, res, h, 1, shape.d[0], n / shape.d[0]);
+        }
+        if (tmp) B.release(tmp);
+    }
+    node_unref(na);
+    if (s != KTC_OK) { if (res) B.release(res); return s; }
+    Node* leaf = new_leaf(res, rs, na->dev);
+    *out = new_cell(node_ref(leaf));
+    leaf->owner = *out;
+    return KTC_OK;
+}
+
+// The buffer that holds the cell's value; a pending value is computed first.  One reference on the buffer is
+// added for the caller (to be dropped with ktc_release).
+KTC_API int ktc_lazy_buffer(ktc_lazy_cell cell, ktc_buf* out) {
+    LZ_LOCK;
+    Cell* c = cell_of(cell);
+    if (!c || !c->node) return fail(KTC_ESTATE, "ktc_lazy_buffer: stale or unknown cell");
+    if (!c->node->stored()) {
+        LZ_TRY(materialize_cell(c));
+        c = cell_of(cell);
+    } else if (!g_pending_targets.empty() && g_pending_targets.count(c->node->buf)) {
+        LZ_TRY(run_pending());
+        c = cell_of(cell);
+    }
+    if (!c->node->stored()) return fail(KTC_ESTATE, "a pending value did not receive its storage");
+    LZ_TRY(B.retain(c->node->buf));
+    *out = c->node->buf;
+    return KTC_OK;
+}
+
+// pending: 1 while the cell's value is not in memory; is_sum: 1 while it is a sum that has not run
+KTC_API int ktc_lazy_info(ktc_lazy_cell cell, int* pending, int* is_sum, int64_t* shape, int* ndim) {
+    LZ_LOCK;
+    Cell* c = cell_of(cell);
+    if (!c || !c->node) return fail(KTC_ESTATE, "ktc_lazy_info: stale or unknown cell");
+    if (pending) *pending = c->node->stored() ? 0 : 1;
+    if (is_sum) *is_sum = (!c->node->stored() && strip(c->node)->kind == K_REDUCE && !strip(c->node)->stored()) ? 1 : 0;
+    if (ndim) *ndim = c->node->shape.nd;
+    if (shape) for (int i = 0; i < c->node->shape.nd; ++i) shape[i] = c->node->shape.d[i];
+    return KTC_OK;
+}
+
+// To be called before `buf` is written by any call that is not recorded here: pending expressions that read
+// it -- and pending `+= sum` updates of it -- run first.
+KTC_API int ktc_lazy_flush(ktc_buf buf) {
+    LZ_LOCK;
+    return flush_dependents(buf);
+}
+
+KTC_API int ktc_lazy_run_pending(void) {
+    LZ_LOCK;
+    if (g_pending.empty()) return KTC_OK;
+    return run_pending();
+}
+
+// recompute_limit, store_cost, defer_sums, defer_inplace
+KTC_API int ktc_lazy_option(const char* name, int value) {
+    LZ_LOCK;
+    if (!name) return fail(KTC_EINVAL, "ktc_lazy_option: no name");
+    if (!strcmp(name, "recompute_limit")) opt_recompute_limit = value;
+    else if (!strcmp(name, "store_cost")) opt_store_cost = value;
+    else if (!strcmp(name, "defer_sums")) opt_defer_sums = value;
+    else if (!strcmp(name, "defer_inplace")) opt_defer_inplace = value;
+    else return fail(KTC_EINVAL, "ktc_lazy_option: unknown option %s", name);
+    return KTC_OK;
+}
+
+// out8: programs run, expressions that fell back to separate calls, passes with several sums, sums pending now,
+// program-cache hits, programs compiled, live nodes, live cells
+KTC_API int ktc_lazy_stats(int64_t* out8) {
+    LZ_LOCK;
+    if (!out8) return fail(KTC_EINVAL, "ktc_lazy_stats: no output");
+    out8[0] = st_fused; out8[1] = st_unfused; out8[2] = st_multi; out8[3] = (int64_t)g_pending.size();
+    out8[4] = st_cache_hits; out8[5] = st_compiles; out8[6] = g_live_nodes;
+    out8[7] = (int64_t)g_cells.size() - (int64_t)g_free_cells.size();
+    return KTC_OK;
+}
+
+}  // extern "C"

@@ -27,24 +27,34 @@ from . import shape_functions as SF
 
 
 class _Cell:
-    """Storage slot of one or more tensors: a buffer handle (one owned reference), or a pending
-    expression, or both (the node then is the cached leaf for the buffer).  Shallow copies of a
-    deferred tensor share the cell, so that they end up sharing storage exactly as in the
-    reference; every other tensor has a cell of its own."""
+    """Storage slot of one or more tensors: a buffer handle (one owned reference), or a cell of the
+    library's expression recorder whose value is still pending, or both (the recorder cell then stands
+    for the buffer when the tensor is an operand of a recorded call).  Shallow copies of a deferred
+    tensor share the cell, so that they end up sharing storage exactly as in the reference; every other
+    tensor has a cell of its own."""
 
-    __slots__ = ("store", "node", "share", "__weakref__")
+    __slots__ = ("store", "lz", "lz_shape", "share", "rec", "__weakref__")
 
-    def __init__(self, store, node):
-        self.store, self.node, self.share = store, node, 1
+    def __init__(self, store, lz=None, lz_shape=None, rec=None):
+        self.store, self.lz, self.lz_shape, self.share, self.rec = store, lz, lz_shape, 1, rec
+
+    def __del__(self):
+        # a tensor that was never released (an output its Function kept) still gives back its recorder cell, and
+        # with it the operands its pending value holds, when the host object goes away
+        if self.lz is not None and self.rec is not None:
+            try:
+                self.rec.free(self.lz)
+            except Exception:
+                pass
 
 
 class CUDARawTensor:
     __slots__ = ("shape", "_cell", "ops", "refCount", "mustSurviveGC", "_released", "__weakref__")
 
-    def __init__(self, shape: Sequence[int], store: Optional[int], ops: "CUDATensorOperations", node=None, cell=None):
+    def __init__(self, shape: Sequence[int], store: Optional[int], ops: "CUDATensorOperations", lz=None, cell=None):
         self.shape: List[int] = [int(d) for d in shape]
         if cell is None:
-            cell = _Cell(store, node)               # store: ktc_buf handle (one reference); None while deferred
+            cell = _Cell(store, lz, list(self.shape) if lz is not None else None, ops._recorder)   # store: ktc_buf handle (one reference); None while deferred
         else:
             cell.share += 1
         self._cell = cell
@@ -62,13 +72,12 @@ class CUDARawTensor:
     def _store(self, h) -> None:
         self._cell.store = h
 
-    @property
-    def _node(self):
-        return self._cell.node
-
-    @_node.setter
-    def _node(self, n) -> None:
-        self._cell.node = n
+    def _drop_recorded(self) -> None:
+        """Forget the recorder cell (the tensor's value is about to be replaced by something the recorder does not see)."""
+        cell = self._cell
+        if cell.lz is not None:
+            self.ops._recorder.free(cell.lz)
+            cell.lz = cell.lz_shape = None
 
     # ---- bookkeeping -------------------------------------------------------
     @property
@@ -81,7 +90,8 @@ class CUDARawTensor:
 
     @property
     def isDeferred(self) -> bool:
-        return self._store is None and self._node is not None
+        cell = self._cell
+        return cell.store is None and cell.lz is not None and self.ops._recorder.is_pending(cell.lz)
 
     @property
     def storeReference(self) -> int:
@@ -91,11 +101,14 @@ class CUDARawTensor:
     def _buf(self) -> int:
         if self._released:
             raise RuntimeError("Raw tensor already released")   # OCLMemoryObject.kt:167-170
-        if self._store is None:
-            self.ops._materialize(self)
-        elif self.ops._pending_targets and self._store in self.ops._pending_targets:
+        cell = self._cell
+        if cell.store is None:
+            if cell.lz is None:
+                raise RuntimeError("Raw tensor has no storage")
+            cell.store = self.ops._recorder.buffer(cell.lz)     # evaluates the pending expression; one reference for this cell
+        elif self.ops._pending_targets and cell.store in self.ops._pending_targets:
             self.ops._run_pending()                             # a `+= pending sum` update of this buffer is due
-        return self._store
+        return cell.store
 
     def incrementRef(self) -> None:
         self.refCount += 1
@@ -113,7 +126,9 @@ class CUDARawTensor:
             if cell.share <= 0:
                 if cell.store is not None:
                     L.check(self.ops.lib.ktc_release(cell.store))
-                cell.node = None
+                if cell.lz is not None:
+                    self.ops._recorder.free(cell.lz)
+                    cell.lz = None
             self._released = True
             return True
         return False
@@ -121,17 +136,33 @@ class CUDARawTensor:
     def _new(self, shape: Sequence[int]) -> "CUDARawTensor":
         return self.ops.createRaw(list(shape))
 
-    def _as_node(self):
-        """This tensor as an operand of a deferred expression."""
+    def _lz(self) -> int:
+        """This tensor as an operand of a recorded call: its recorder cell (a stored tensor gets one over its buffer)."""
         if self._released:
             raise RuntimeError("Raw tensor already released")
-        if self._store is None:
-            return self._node
-        if self.ops._pending_targets and self._store in self.ops._pending_targets:
+        cell = self._cell
+        if cell.store is None:
+            return cell.lz
+        if self.ops._pending_targets and cell.store in self.ops._pending_targets:
             self.ops._run_pending()
-        if self._node is None or not self._node.stored() or self._node.buf.handle != self._store or self._node.shape != self.shape:
-            self._node = lazy.leaf(self.ops.lib, self._store, self.shape)
-        return self._node
+        if cell.lz is None or cell.lz_shape != self.shape:
+            if cell.lz is not None:
+                self.ops._recorder.free(cell.lz)
+            cell.lz, cell.lz_shape = self.ops._recorder.leaf(cell.store, self.shape), list(self.shape)
+        return cell.lz
+
+    def _recorded(self, shape, lz: int) -> "CUDARawTensor":
+        return CUDARawTensor(shape, None, self.ops, lz=lz)
+
+    def _after_assign(self, state: int) -> None:
+        """What an in-place call through the recorder left behind (ktc_lazy_assign_*)."""
+        cell = self._cell
+        if state == lazy.STATE_PENDING:
+            if cell.store is not None:                          # the cell's value is pending now; its old buffer belongs to the recorder
+                L.check(self.ops.lib.ktc_release(cell.store))
+                cell.store = None
+        elif state == lazy.STATE_UPDATE_RECORDED:
+            self.ops._pending_targets.add(cell.store)
 
     def _before_inplace_write(self) -> None:
         """Deferred tensors that read this buffer are evaluated before it changes."""
@@ -174,7 +205,7 @@ class CUDARawTensor:
         broadcast operand."""
         if self.ops.lazy:
             common = self.shape if self.shape == other.shape else SF.infer_implicit_broadcast_shape(self.shape, other.shape)
-            return self.ops._deferred("bin", common, op, (self._as_node(), other._as_node()))
+            return self._recorded(common, self.ops._recorder.binary(op, self._lz(), other._lz()))
         if self.shape == other.shape:
             res = self._new(self.shape)
             L.check(self.ops.lib.ktc_binary(op, res._buf(), self._buf(), other._buf(), self.size))
@@ -192,39 +223,28 @@ class CUDARawTensor:
             raise ValueError("Shapes does not match for inplace operation on tensors with shapes: "
                              f"{self.shape} and {other.shape}.")
         if self.ops.lazy:
-            self.ops._deferred_assign(self, "bin", op, (self._as_node(), other._as_node()))
+            self._after_assign(self.ops._recorder.assign_binary(op, self._lz(), other._lz()))
             return
         self._before_inplace_write()
         L.check(self.ops.lib.ktc_binary_inplace(op, self._buf(), other._buf(), self.size))
 
-    def _scalar_node(self, op: int, s: float, scalar_first: bool):
-        me = self._as_node()
-        if op == L.POW and not scalar_first and float(s) == 2.0:
-            return "square", 0, (me,)
-        args = (lazy.const(s), me) if scalar_first else (me, lazy.const(s))
-        return "bin", op, args
-
     def _scalar(self, op: int, s: float, scalar_first: bool = False) -> "CUDARawTensor":
         if self.ops.lazy:
-            if op == L.POW and not scalar_first and float(s) == 1.0:
-                return self.ops._deferred_alias(self)
-            kind, o, args = self._scalar_node(op, s, scalar_first)
-            return self.ops._deferred(kind, self.shape, o, args)
+            return self._recorded(self.shape, self.ops._recorder.scalar(op, self._lz(), s, scalar_first))
         res = self._new(self.shape)
         L.check(self.ops.lib.ktc_scalar(op, res._buf(), self._buf(), float(s), self.size, 1 if scalar_first else 0))
         return res
 
     def _scalar_assign(self, op: int, s: float) -> None:
         if self.ops.lazy:
-            kind, o, args = self._scalar_node(op, s, False)
-            self.ops._deferred_assign(self, kind, o, args)
+            self._after_assign(self.ops._recorder.assign_scalar(op, self._lz(), s))
             return
         self._before_inplace_write()
         L.check(self.ops.lib.ktc_scalar_inplace(op, self._buf(), float(s), self.size))
 
     def _unary(self, op: int) -> "CUDARawTensor":
         if self.ops.lazy and op <= L.NEG:                       # the ops the fused expression kernels implement
-            return self.ops._deferred("un", self.shape, op, (self._as_node(),))
+            return self._recorded(self.shape, self.ops._recorder.unary(op, self._lz()))
         res = self._new(self.shape)
         L.check(self.ops.lib.ktc_unary(op, res._buf(), self._buf(), self.size))
         return res
@@ -328,14 +348,14 @@ class CUDARawTensor:
 
     def clamp(self, min: float, max: float):
         if self.ops.lazy:
-            return self.ops._deferred("clamp", self.shape, 0, (self._as_node(),), imm=(float(min), float(max)))
+            return self._recorded(self.shape, self.ops._recorder.clamp(self._lz(), min, max))
         res = self._new(self.shape)
         L.check(self.ops.lib.ktc_clamp(res._buf(), self._buf(), float(min), float(max), self.size))
         return res
 
     def _compare(self, op: int, value: float):
         if self.ops.lazy:
-            return self.ops._deferred("cmp", self.shape, op, (self._as_node(),), imm=(float(value),))
+            return self._recorded(self.shape, self.ops._recorder.compare_scalar(op, self._lz(), value))
         res = self._new(self.shape)
         L.check(self.ops.lib.ktc_compare_scalar(op, res._buf(), self._buf(), float(value), self.size))
         return res
@@ -390,7 +410,7 @@ class CUDARawTensor:
             return self
         SF.infer_explicit_broadcast_shape(self.shape, shape)
         if self.ops.lazy:
-            return self.ops._deferred("bcast", shape, 0, (self._as_node(),))
+            return self._recorded(shape, self.ops._recorder.broadcast_to(self._lz(), shape))
         res = self._new(shape)
         so, no = L.shape_array(shape)
         sa, na = L.shape_array(self.shape)
@@ -405,8 +425,8 @@ class CUDARawTensor:
                 return CUDARawTensor(self.shape, None, self.ops, cell=self._cell)
             L.check(self.ops.lib.ktc_retain(self._buf()))
             return CUDARawTensor(self.shape, self._store, self.ops)
-        if self.isDeferred:
-            return self.ops._deferred_alias(self)               # nodes are immutable values: a deep copy can share one
+        if self.isDeferred:                                     # pending values are immutable: a deep copy can share one
+            return self._recorded(self.shape, self.ops._recorder.broadcast_to(self._lz(), self.shape))
         res = self._new(self.shape)
         L.check(self.ops.lib.ktc_d2d(res._buf(), 0, self._buf(), 0, self.size))
         return res
@@ -421,6 +441,7 @@ class CUDARawTensor:
         """reshape (ART:79-84): a deep copy with the new shape."""
         new_shape = SF.reshape(self.shape, shape)
         res = self.copy()
+        res._buf()                                              # a pending expression is tied to its shape
         res.shape = new_shape
         return res
 
@@ -450,7 +471,7 @@ class CUDARawTensor:
 
     def inplaceFill(self, value: float) -> None:
         if self.isDeferred:                                     # the pending value is overwritten: just take storage
-            self._node = None
+            self._drop_recorded()
             h = C.c_uint64(0)
             L.check(self.ops.lib.ktc_alloc(self.ops.device, self.size, C.byref(h)))
             self._store = h.value
@@ -465,13 +486,12 @@ class CUDARawTensor:
         res_shape = SF.aggregate_over(self.shape, a, True)
         outer, length, inner = SF.collapse_axis(self.shape, a)
         res = None
-        if self.isDeferred and op == L.SUM and a == 0 and len(self.shape) >= 2 and self._node.kind != "reduce":
+        if self.isDeferred and op == L.SUM and a == 0 and len(self.shape) >= 2:
             final = list(res_shape) if keep_dimensions else list(res_shape[1:])
-            res = self.ops._sum_leading_axis(self, final)       # fused with the pending expression when possible
-        elif self.isDeferred and op == L.SUM and a == len(self.shape) - 1 and len(self.shape) >= 2 and self.shape[a] > 1 \
-                and self._node.kind != "reduce" and self.ops.deferSums:
+            res = self._recorded(final, self.ops._recorder.sum(self._lz(), L.EXPR_SUM_ROWS, False, final))    # fused with the pending expression when possible
+        elif self.isDeferred and op == L.SUM and a == len(self.shape) - 1 and len(self.shape) >= 2 and self.shape[a] > 1 and self.ops.deferSums:
             final = list(res_shape) if keep_dimensions else list(res_shape[:-1])
-            res = self.ops._defer_sum(self, L.EXPR_SUM_LAST, False, final)      # row sums: a pending sum over the last axis
+            res = self._recorded(final, self.ops._recorder.sum(self._lz(), L.EXPR_SUM_LAST, False, final))    # row sums: a pending sum over the last axis
         if res is None:
             res = self._new(res_shape)
             L.check(self.ops.lib.ktc_reduce_axis(op, res._buf(), self._buf(), outer, length, inner))
@@ -484,9 +504,7 @@ class CUDARawTensor:
     def sum(self, axis: Optional[int] = None, keepDimensions: bool = False):
         if axis is None:
             if self.isDeferred:
-                res = self.ops._sum_all(self, mean=False)
-                if res is not None:
-                    return res
+                return self._recorded([1], self.ops._recorder.sum(self._lz(), L.EXPR_SUM_ALL, False, [1]))
             res = self._new([1])                     # sum() -> shape [1] (JVMRawTensor.kt:146-148)
             L.check(self.ops.lib.ktc_reduce_all(L.SUM, res._buf(), self._buf(), self.size))
             return res
@@ -495,9 +513,7 @@ class CUDARawTensor:
     def mean(self, axis: Optional[int] = None, keepDimensions: bool = False):
         if axis is None:
             if self.isDeferred:
-                res = self.ops._sum_all(self, mean=True)
-                if res is not None:
-                    return res
+                return self._recorded([1], self.ops._recorder.sum(self._lz(), L.EXPR_SUM_ALL, True, [1]))
             res = self._new([1])                     # mean() -> shape [1] (JVMRawTensor.kt:150-152)
             L.check(self.ops.lib.ktc_reduce_all(L.MEAN, res._buf(), self._buf(), self.size))
             return res
@@ -640,10 +656,6 @@ class CUDARawTensor:
         a = SF.normalize_axis(self.shape, axis)
         if len(index.shape) != len(self.shape):
             raise ValueError(f"Gather expects the index to have the tensor's dimensions, got {index.shape} for {self.shape}")
-        if self.isDeferred and self.ops.lazy:
-            res = self.ops._gather_deferred(self, a, index)     # few picks from a pending expression: gather its operands instead
-            if res is not None:
-                return res
         res = self._new(index.shape)
         pi, n = L.shape_array(self.shape)
         px, _ = L.shape_array(index.shape)
@@ -714,7 +726,8 @@ class CUDARawTensor:
             L.check(self.ops.lib.ktc_fill(h.value, keep, n_new - keep, 0.0))
         self._before_inplace_write()
         L.check(self.ops.lib.ktc_release(old))
-        self._store, self._node = h.value, None
+        self._drop_recorded()
+        self._store = h.value
         self.shape = new_shape
 
     def __repr__(self) -> str:

@@ -1,17 +1,22 @@
 """A host stand-in for libkten_cuda.so, for CPU tests of the host logic only.
 
-The deferred-expression layer (kten_b200.lazy, raw_tensor._Cell, tensor_operations) is pure
-host code: which calls it makes, in which order, with which buffers, decides whether aliases,
-in-place writes and side outputs keep the semantics of the eager backend.  This module
-implements the few C-ABI entry points that logic drives -- buffers, copies, the elementwise
-calls, the full reduction and ktc_expr_eval (a numpy interpreter of the program encoding) --
-with the CPU oracle's arithmetic, so that the same script can be run call by call and deferred
-on a machine without a GPU and the two results compared.  It is test infrastructure: nothing in
-the product imports it, and it says nothing about the CUDA kernels.
+The deferred-expression layer is host code: which calls it makes, in which order, with which
+buffers, decides whether aliases, in-place writes and side outputs keep the semantics of the eager
+backend.  Its core -- the recorder behind `ktc_lazy_*` (kten_b200/csrc/ktc_lazy.cpp) -- is plain C++
+that reaches the rest of the library through a table of C-ABI entry points, so it is compiled here
+on its own (g++, no CUDA) and the table is filled with this module's implementations: buffers,
+copies, the elementwise calls, the reductions and ktc_expr_eval (a numpy interpreter of the program
+encoding), all with the CPU oracle's arithmetic.  The same script can then be run call by call and
+deferred on a machine without a GPU and the two results compared.  It is test infrastructure:
+nothing in the product imports it, and it says nothing about the CUDA kernels.
 """
 from __future__ import annotations
 
 import ctypes as C
+import os
+import shutil
+import subprocess
+import tempfile
 
 import numpy as np
 
@@ -20,6 +25,70 @@ from kten_b200.tensor_operations import CUDATensorOperations
 from oracle import oracle as O
 
 BIN = {L.PLUS: O.PLUS, L.MINUS: O.MINUS, L.TIMES: O.TIMES, L.DIV: O.DIV, L.POW: O.POW}
+
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+RECORDER_SRC = os.path.join(HERE, "..", "kten_b200", "csrc", "ktc_lazy.cpp")
+RECORDER_SO = os.path.join(HERE, "host_lazy", "libktc_lazy_host.so")
+
+u64, i64, i32, f32 = C.c_uint64, C.c_int64, C.c_int, C.c_float
+P = C.POINTER
+# the recorder's backend table, in the order of `struct Backend` (ktc_lazy.cpp): name, C signature
+BACKEND = [
+    ("ktc_alloc", (i32, i32, i64, P(u64))),
+    ("ktc_retain", (i32, u64)),
+    ("ktc_release", (i32, u64)),
+    ("ktc_refcount", (i32, u64, P(i32))),
+    ("ktc_buf_info", (i32, u64, P(i32), P(i64), P(C.c_void_p))),
+    ("ktc_d2d", (i32, u64, i64, u64, i64, i64)),
+    ("ktc_binary", (i32, i32, u64, u64, u64, i64)),
+    ("ktc_binary_bcast", (i32, i32, u64, u64, P(i64), i32, u64, P(i64), i32)),
+    ("ktc_binary_inplace", (i32, i32, u64, u64, i64)),
+    ("ktc_scalar", (i32, i32, u64, u64, f32, i64, i32)),
+    ("ktc_scalar_inplace", (i32, i32, u64, f32, i64)),
+    ("ktc_unary", (i32, i32, u64, u64, i64)),
+    ("ktc_clamp", (i32, u64, u64, f32, f32, i64)),
+    ("ktc_compare_scalar", (i32, i32, u64, u64, f32, i64)),
+    ("ktc_broadcast_to", (i32, u64, P(i64), i32, u64, P(i64), i32)),
+    ("ktc_reduce_axis", (i32, i32, u64, u64, i64, i64, i64)),
+    ("ktc_reduce_all", (i32, i32, u64, u64, i64)),
+    ("ktc_expr_eval", (i32, P(C.c_uint32), i32, P(f32), i32, P(i64), i32, P(u64), P(i64), i32, P(u64), i32, i32, u64, i32)),
+    ("ktc_expr_eval_multi", (i32, P(C.c_uint32), i32, P(f32), i32, P(i64), i32, P(u64), P(i64), i32, P(u64), i32, P(i32), P(u64), P(i32), i32)),
+]
+RECORDER_CALLS = {
+    "ktc_lazy_leaf": (i32, [u64, P(i64), i32, P(u64)]), "ktc_lazy_free": (i32, [u64]),
+    "ktc_lazy_unary": (i32, [i32, u64, P(u64)]), "ktc_lazy_binary": (i32, [i32, u64, u64, P(u64)]),
+    "ktc_lazy_scalar": (i32, [i32, u64, f32, i32, P(u64)]), "ktc_lazy_clamp": (i32, [u64, f32, f32, P(u64)]),
+    "ktc_lazy_compare_scalar": (i32, [i32, u64, f32, P(u64)]), "ktc_lazy_broadcast_to": (i32, [u64, P(i64), i32, P(u64)]),
+    "ktc_lazy_assign_binary": (i32, [i32, u64, u64, P(i32)]), "ktc_lazy_assign_scalar": (i32, [i32, u64, f32, P(i32)]),
+    "ktc_lazy_sum": (i32, [u64, i32, i32, P(i64), i32, P(u64)]), "ktc_lazy_buffer": (i32, [u64, P(u64)]),
+    "ktc_lazy_info": (i32, [u64, P(i32), P(i32), P(i64), P(i32)]), "ktc_lazy_flush": (i32, [u64]),
+    "ktc_lazy_run_pending": (i32, []), "ktc_lazy_option": (i32, [C.c_char_p, i32]), "ktc_lazy_stats": (i32, [P(i64)]),
+}
+
+
+def build_recorder() -> str:
+    """g++ build of the recorder alone (no CUDA); returns the path of the shared object."""
+    if not os.path.exists(RECORDER_SO) or os.path.getmtime(RECORDER_SO) < os.path.getmtime(RECORDER_SRC):
+        os.makedirs(os.path.dirname(RECORDER_SO), exist_ok=True)
+        subprocess.run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-DKTC_LAZY_STANDALONE", "-o", RECORDER_SO, RECORDER_SRC], check=True)
+    return RECORDER_SO
+
+
+class _Out:
+    """What the stand-in's methods expect of a ctypes.byref argument, over a pointer handed in by C."""
+
+    def __init__(self, ptr):
+        self._obj = self
+        self._ptr = ptr
+
+    @property
+    def value(self):
+        return self._ptr[0]
+
+    @value.setter
+    def value(self, v):
+        self._ptr[0] = v
 
 
 def _ints(ptr, n):
@@ -34,7 +103,45 @@ class FakeLib:
         self.expr_calls = 0
         self.multi_calls = 0
         self.calls = []         # names of compute calls, in order
+        self.programs = []      # every program handed to ktc_expr_eval / ktc_expr_eval_multi, as the recorder built it
         self.error = b""
+        self._attach_recorder()
+
+    # ---- the expression recorder, compiled alone, with this object as the library it drives ----------
+    def _attach_recorder(self):
+        # the recorder keeps one state per loaded object: every stand-in loads a copy of its own
+        fd, path = tempfile.mkstemp(suffix=".so", prefix="ktc_lazy_host_")
+        os.close(fd)
+        shutil.copyfile(build_recorder(), path)
+        self._recorder = C.CDLL(path)
+        os.unlink(path)
+        self._callbacks = []
+        table = (C.c_void_p * len(BACKEND))()
+        for i, (name, sig) in enumerate(BACKEND):
+            cb = C.CFUNCTYPE(*sig)(self._adapter(name))
+            self._callbacks.append(cb)
+            table[i] = C.cast(cb, C.c_void_p).value
+        self._recorder.ktc_lazy_test_set_backend.argtypes = [C.POINTER(C.c_void_p), i32]
+        assert self._recorder.ktc_lazy_test_set_backend(table, len(BACKEND)) == 0
+        for name, (res, args) in RECORDER_CALLS.items():
+            fn = getattr(self._recorder, name)
+            fn.restype, fn.argtypes = res, args
+            setattr(self, name, fn)
+
+    def _adapter(self, name):
+        method = getattr(self, name)
+        if name == "ktc_alloc":
+            return lambda dev, n, out: method(dev, n, _Out(out))
+        if name == "ktc_refcount":
+            return lambda h, out: method(h, _Out(out))
+        return method
+
+    def ktc_buf_info(self, h, dev, n, ptr):
+        if dev:
+            dev[0] = 0
+        if n:
+            n[0] = self._get(h).size
+        return 0
 
     # ---- buffers -----------------------------------------------------------------------------
     def _get(self, h):
@@ -207,6 +314,10 @@ class FakeLib:
         self.expr_calls += 1
         self._note("expr_eval")
         total = int(np.prod(shp))
+        self.programs.append({"code": [int(code[i]) for i in range(n_code)], "imm": [float(imm[i]) for i in range(n_imm)], "shape": shp,
+                              "leaves": [int(leaves[i]) for i in range(n_leaves)],
+                              "leaf_shapes": [_ints(lshapes, (i + 1) * ndim)[i * ndim:] for i in range(n_leaves)],
+                              "n_stores": int(n_stores), "sink": int(sink), "sinks": sinks})
         regs = [None] * L.EXPR_REGS
         acc = None
         accs = {}
@@ -253,7 +364,7 @@ class FakeLib:
 
 
 def make_ops() -> CUDATensorOperations:
-    """A CUDATensorOperations whose library is the stand-in above (no device, no shared object)."""
+    """A CUDATensorOperations whose library is the stand-in above (no device, no CUDA library)."""
     import threading
     ops = object.__new__(CUDATensorOperations)
     ops.lib = FakeLib()
@@ -261,10 +372,5 @@ def make_ops() -> CUDATensorOperations:
     ops.platformKey = "CUDA - host stand-in"
     ops._tls = threading.local()
     ops.epsilon = 1e-7
-    ops.lazy = False
-    ops._deps, ops._deps_purge_at = {}, 1024
-    ops.recomputeLimit, ops.storeCost = 2, 8
-    ops.deferSums, ops._pending, ops._pending_targets, ops.multiSinkEvaluations = True, [], {}, 0
-    ops.deferInplace = True
-    ops.fusedEvaluations = ops.unfusedEvaluations = 0
+    ops._init_deferred()
     return ops

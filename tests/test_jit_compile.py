@@ -5,9 +5,10 @@ import ctypes as C
 
 import pytest
 
+import numpy as np
+
 from kten_b200 import _lib as L
-from kten_b200 import lazy as Z
-from tests.test_lazy_host import FakeLib
+from tests import fake_lib
 
 
 def ins(op, d=0, a=0, b=0, k=0):
@@ -51,55 +52,66 @@ def test_ill_formed_program_is_rejected():
     assert lib.ktc_test_expr_compile(bad, 1, 0, None, None, 0, L.EXPR_STORE_ONLY, None, None) == L.KTC_EINVAL
 
 
+def recorded_step(one_pass: bool):
+    """The sharded benchmark step -- loss = sum(sigmoid(x*w + b) pow 2), backward for w and b -- issued through
+    the autograd caller over the stand-in library with everything deferred; returns the programs the recorder
+    handed to ktc_expr_eval."""
+    ops = fake_lib.make_ops()
+    ops.lazy, ops.deferSums = True, one_pass
+    rng = np.random.default_rng(3)
+    shape = [32, 64]
+    from kten_b200.sharded import ShardedSigmoidGraph
+    x = ops.createRaw(shape, rng.uniform(-1, 1, shape).astype(np.float32))
+    w = ops.createRaw([1, 64], rng.normal(0, 0.02, [1, 64]).astype(np.float32))
+    b = ops.createRaw([64], np.zeros(64, np.float32))
+    graph = ShardedSigmoidGraph(ops, x, w, b)
+    with ops.garbageCollector():
+        for r in graph.step():
+            r.toArray()
+        graph.release_step()
+    return ops.lib.programs
+
+
+def flags(prog):
+    inner = [1 if sh[-1] != 1 else 0 for sh in prog["leaf_shapes"]]
+    fixed = [1 if sh[0] == 1 else 0 for sh in prog["leaf_shapes"]]
+    return inner, fixed
+
+
 def test_program_from_the_expression_compiler_compiles():
-    """The sharded benchmark step's backward formula, as the deferred layer emits it."""
-    lib = FakeLib()
-    shape = [4096, 1024]
-    x, w, b, g = Z.leaf(lib, 1, shape), Z.leaf(lib, 2, [1, 1024]), Z.leaf(lib, 3, [1024]), Z.leaf(lib, 4, [1])
-    bin_ = lambda op, p, q: Z.Node("bin", shape, op, (p, q))
-    s = Z.Node("un", shape, L.SIGMOID, (bin_(L.PLUS, bin_(L.TIMES, x, w), b),))
-    gp = bin_(L.TIMES, bin_(L.TIMES, Z.Node("bcast", shape, 0, (g,)), Z.const(2.0)), s)       # PowConstant backward
-    t = bin_(L.PLUS, Z.Node("un", shape, L.NEG, (s,)), Z.const(1.0))                            # Sigmoid backward
-    dz = bin_(L.TIMES, bin_(L.TIMES, t, s), gp)
-    prog, _, _ = Z.compile_program(shape, [], bin_(L.TIMES, dz, x), 0)
-    inner = [1 if sh[-1] != 1 else 0 for _, sh in prog.leaves]
-    fixed = [1 if sh[0] == 1 else 0 for _, sh in prog.leaves]
-    nbytes, ms = compile_only(prog.code, inner, fixed, 0, L.EXPR_SUM_ROWS)
+    """The step's backward formula with its leading-axis sum, as the recorder emits it (one sum per pass)."""
+    progs = [p for p in recorded_step(one_pass=False) if p["sink"] == L.EXPR_SUM_ROWS]
+    assert progs
+    prog = max(progs, key=lambda p: len(p["code"]))
+    inner, fixed = flags(prog)
+    nbytes, ms = compile_only(prog["code"], inner, fixed, 0, L.EXPR_SUM_ROWS)
     assert ms < 20000
 
 
 def test_multi_sink_program_compiles():
-    """Loss, weight gradient and bias gradient of the sharded step as ONE program with three sinks
-    (SUM_ALL mean, SUM_ROWS, SUM_ROWS), as the deferred layer emits it once sums are deferred too."""
-    lib = FakeLib()
-    shape = [4096, 1024]
-    x, w, b, y, g = (Z.leaf(lib, 1, shape), Z.leaf(lib, 2, [1, 1024]), Z.leaf(lib, 3, [1024]), Z.leaf(lib, 5, shape), Z.leaf(lib, 4, [1]))
-    bin_ = lambda op, p, q: Z.Node("bin", shape, op, (p, q))
-    s = Z.Node("un", shape, L.SIGMOID, (bin_(L.PLUS, bin_(L.TIMES, x, w), b),))
-    d = bin_(L.MINUS, s, y)
-    loss = Z.Node("square", shape, 0, (d,))
-    gp = bin_(L.TIMES, bin_(L.TIMES, Z.Node("bcast", shape, 0, (g,)), Z.const(2.0)), d)
-    t = bin_(L.PLUS, Z.Node("un", shape, L.NEG, (s,)), Z.const(1.0))
-    dz = bin_(L.TIMES, bin_(L.TIMES, t, s), gp)
-    prog, _, _ = Z.compile_program(shape, [], [loss, bin_(L.TIMES, dz, x), dz], 0)
-    accs = [(c >> 20) for c in prog.code if (c & 0xff) == L.X_ACC]
+    """Loss, weight gradient and bias gradient of the step as ONE program with three sinks (SUM_ALL, SUM_ROWS,
+    SUM_ROWS), as the recorder emits it once sums are deferred too."""
+    progs = [p for p in recorded_step(one_pass=True) if p["sinks"] and len(p["sinks"]) == 3]
+    assert len(progs) == 1
+    prog = progs[0]
+    accs = [(c >> 20) for c in prog["code"] if (c & 0xff) == L.X_ACC]
     assert sorted(accs) == [0, 1, 2]
-    inner = [1 if sh[-1] != 1 else 0 for _, sh in prog.leaves]
-    fixed = [1 if sh[0] == 1 else 0 for _, sh in prog.leaves]
+    assert sorted(k for k, _, _ in prog["sinks"]) == [L.EXPR_SUM_ALL, L.EXPR_SUM_ROWS, L.EXPR_SUM_ROWS]
+    inner, fixed = flags(prog)
     lib_ = L.load()
-    code = (C.c_uint32 * len(prog.code))(*prog.code)
+    code = (C.c_uint32 * len(prog["code"]))(*prog["code"])
     n = len(inner)
     nbytes, ms = C.c_int64(0), C.c_double(0)
-    kinds = (C.c_int * 3)(L.EXPR_SUM_ALL, L.EXPR_SUM_ROWS, L.EXPR_SUM_ROWS)
+    kinds = (C.c_int * 3)(*[k for k, _, _ in prog["sinks"]])
     for rank3 in (0, 1):
-        rc = lib_.ktc_test_expr_compile_multi(code, len(prog.code), n, (C.c_int * n)(*inner), (C.c_int * n)(*fixed), rank3, kinds, 3,
+        rc = lib_.ktc_test_expr_compile_multi(code, len(prog["code"]), n, (C.c_int * n)(*inner), (C.c_int * n)(*fixed), rank3, kinds, 3,
                                               C.byref(nbytes), C.byref(ms))
         if rc == L.KTC_ENOTSUP:
             pytest.skip("NVRTC is not installed here: " + lib_.ktc_last_error().decode())
         assert rc == L.KTC_OK, lib_.ktc_last_error().decode()[:4000]
         assert nbytes.value > 1000
     bad = (C.c_int * 1)(L.EXPR_STORE_ONLY)
-    assert lib_.ktc_test_expr_compile_multi(code, len(prog.code), n, (C.c_int * n)(*inner), (C.c_int * n)(*fixed), 0, bad, 1, None, None) == L.KTC_EINVAL
+    assert lib_.ktc_test_expr_compile_multi(code, len(prog["code"]), n, (C.c_int * n)(*inner), (C.c_int * n)(*fixed), 0, bad, 1, None, None) == L.KTC_EINVAL
 
 
 def test_last_axis_sum_sink_compiles():

@@ -319,3 +319,20 @@ def test_inplace_chain_on_a_buffer_nobody_else_holds_waits():
     calls = stats[1][2]
     # deferred: acc and g in one program each when they are read (g's is a side output or a second program), held at once
     assert calls.count("expr_eval") <= 3 and calls.count("binary") == 0 and calls.count("scalar") == 0
+
+
+def test_updates_of_one_buffer_apply_in_the_order_they_were_written():
+    """`t += s2; t += s1` with s1 created first: float addition does not commute with rounding, so the pending
+    updates must be applied in the order of the calls, not in the order the sums came into being."""
+    def script(o):
+        a = o.createRaw([4, 8], np.full(32, 1.0 / 32, np.float32))
+        b = o.createRaw([4, 8], np.full(32, -1e8 / 32, np.float32))
+        t = o.createRaw([1], np.array([1e8], np.float32))
+        s1 = a.times(1.0).sum()              # 1.0, created first
+        s2 = b.times(1.0).sum()              # -1e8
+        t.plusAssign(s2)
+        t.plusAssign(s1)                     # (1e8 - 1e8) + 1 = 1; the other order gives (1e8 + 1) - 1e8 = 0
+        return [t]
+    eager, lazy, stats = both(script)
+    assert eager[0][0] == 1.0 and same_bits(eager[0], lazy[0])
+    assert stats[1][1] == 1                  # both sums in one pass
