@@ -258,6 +258,19 @@ KTC_API int ktc_expr_eval_multi(const uint32_t* code, int n_code, const float* i
                                 const ktc_buf* stores, int n_stores,
                                 const int* sink_kinds, const ktc_buf* sink_outs, const int* means, int n_sinks);
 
+/* ktc_expr_eval_multi with the rest of a training step folded into its second pass (one kernel combines the partial
+ * sums of all sinks): add_to[j] != 0 adds sink j's result into that tensor as well -- target = target + result, the
+ * float addition of Variable.backwardWithGrad's plusAssign (Variable.kt:44-46) -- and comm != 0 sums the n_x tensors
+ * x_bufs (x_counts floats each; typically the sink outputs and the tensors added to) over the ranks of a peer-memory
+ * communicator, in place, when the last block of that kernel has finished: the exchange of ktc_p2p_allreduce_sum,
+ * without a launch of its own.  add_to may be null; comm 0 ignores x_*. */
+KTC_API int ktc_expr_eval_multi_fused(const uint32_t* code, int n_code, const float* imm, int n_imm,
+                                      const int64_t* shape, int ndim,
+                                      const ktc_buf* leaves, const int64_t* leaf_shapes, int n_leaves,
+                                      const ktc_buf* stores, int n_stores,
+                                      const int* sink_kinds, const ktc_buf* sink_outs, const int* means, int n_sinks,
+                                      const ktc_buf* add_to, uint64_t comm, const ktc_buf* x_bufs, const int64_t* x_counts, int n_x);
+
 /* For iteration spaces of at least `expr_jit_min_elems` elements (tunable, default 2^20; tunable
  * `expr_jit` = 0 turns it off) ktc_expr_eval does not interpret the program: it generates CUDA
  * source for it -- straight-line code over hardware registers built from the library's own
@@ -309,9 +322,15 @@ KTC_API int ktc_expr_jit_log(char* buf, int len);
  *                            pending expressions that read it are evaluated first.
  *   ktc_lazy_free            drops the cell (values other expressions still need stay alive).
  *   ktc_lazy_option          recompute_limit (2), store_cost (8), defer_sums (1), defer_inplace (1).
- *   ktc_lazy_stats           out8: programs run, expressions run as separate calls, passes with several
+ *   ktc_lazy_allreduce       sums the values of up to 8 cells over the ranks of a peer-memory communicator, in
+ *                            place (ktc_p2p_allreduce_sum on their buffers, after whatever is pending).  When
+ *                            all the pending work is one pass with several sums whose updates it applies --
+ *                            loss, gradients and their accumulation in a training step -- the exchange runs
+ *                            inside that pass's second-pass kernel (ktc_expr_eval_multi_fused).
+ *   ktc_lazy_stats           out10: programs run, expressions run as separate calls, passes with several
  *                            sums, sums pending now, program-cache hits, programs compiled, live nodes,
- *                            live cells.
+ *                            live cells, `+= sum` updates applied by a second-pass kernel, all-reduces
+ *                            performed by a second-pass kernel.
  * All calls are serialised by one lock; cells of different devices must not meet in one expression. */
 typedef uint64_t ktc_lazy_cell;
 KTC_API int ktc_lazy_leaf(ktc_buf buf, const int64_t* shape, int ndim, ktc_lazy_cell* out);
@@ -330,7 +349,8 @@ KTC_API int ktc_lazy_info(ktc_lazy_cell cell, int* pending, int* is_sum, int64_t
 KTC_API int ktc_lazy_flush(ktc_buf buf);
 KTC_API int ktc_lazy_run_pending(void);
 KTC_API int ktc_lazy_option(const char* name, int value);
-KTC_API int ktc_lazy_stats(int64_t* out8);
+KTC_API int ktc_lazy_allreduce(uint64_t comm, const ktc_lazy_cell* cells, int n);
+KTC_API int ktc_lazy_stats(int64_t* out10);
 
 /* ---- slices, permutes, gather / scatter -----------------------------------------
  * ktc_copy_strided:  dst[dst_offset + i.dst_strides] = src[src_offset + i.src_strides] for every i in the

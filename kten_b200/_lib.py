@@ -107,6 +107,9 @@ _PROTOTYPES = {
     "ktc_lazy_run_pending": (i32, []),
     "ktc_lazy_option": (i32, [C.c_char_p, i32]),
     "ktc_lazy_stats": (i32, [p_i64]),
+    "ktc_lazy_allreduce": (i32, [u64, p_u64, i32]),
+    "ktc_expr_eval_multi_fused": (i32, [C.POINTER(C.c_uint32), i32, p_f32, i32, p_i64, i32, p_u64, p_i64, i32, p_u64, i32, C.POINTER(C.c_int), p_u64, C.POINTER(C.c_int), i32,
+                                        p_u64, u64, p_u64, p_i64, i32]),
     "ktc_sum_to_shape": (i32, [u64, p_i64, i32, u64, p_i64, i32]),
     "ktc_scatter_axis": (i32, [u64, u64, u64, i64, i64, i64]),
     "ktc_comm_unique_id": (i32, [C.c_char_p]),

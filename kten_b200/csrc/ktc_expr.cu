@@ -28,6 +28,7 @@
 #include "ktc_accum.cuh"
 #include "ktc_expr_args.h"
 #include "ktc_jit.hpp"
+#include "ktc_p2p.cuh"
 
 namespace ktc {
 
@@ -164,6 +165,92 @@ __global__ void __launch_bounds__(256) k_expr(const __grid_constant__ ExprArgs p
     }
 }
 
+// ---- second pass of a pass with several sums: ONE kernel for all of them ---------------------------------------
+// Every sink's partials are combined exactly as its own second-pass kernel combines them (k_combine_warp: one warp per
+// output, lanes stride over the segments, xor-shuffle tree; k_combine_thread: one thread per output, segments in order;
+// a full sum: one block, threads stride over the partials, shuffles, then the warp leaders in order), so SUM_ROWS and
+// SUM_LAST results keep the bits of the single-sink calls.  On top of that the kernel can
+//   * add a result into another tensor in the same step (add_to: the gradient accumulated into a Variable,
+//     Variable.kt:44-46 -- target = target + (float)sum, the very float addition the separate in-place call performs);
+//   * sum tensors over the ranks when the last block has finished (x: the peer-memory exchange of ktc_p2p.cuh, run by
+//     whichever block takes the last ticket of a device counter -- no block waits for another block).
+// so that a training step's loss, gradients, accumulation and all-reduce are the producing pass plus this kernel.
+struct CombineArgs {
+    int n_sinks;
+    int mode[kExprMaxSinks];               // 0 one warp per output, 1 one thread per output, 2 one block for a single output
+    const double* part[kExprMaxSinks];
+    float* out[kExprMaxSinks];
+    float* add_to[kExprMaxSinks];          // nullptr: none
+    int64_t n_out[kExprMaxSinks];
+    int S[kExprMaxSinks];                  // partials per output
+    double divisor[kExprMaxSinks];         // > 0: mean
+    int block_end[kExprMaxSinks];          // sink j owns blocks [block_end[j-1], block_end[j])
+    int exchange;                          // != 0: x is valid
+    P2pArgs x;
+};
+__device__ unsigned int g_combine_tickets;  // blocks of the running k_combine_multi that have finished (back to 0 when the last one leaves)
+
+__device__ __forceinline__ void combine_put(const CombineArgs& a, int j, int64_t o, double sum) {
+    const float v = (float)(a.divisor[j] > 0.0 ? sum / a.divisor[j] : sum);
+    a.out[j][o] = v;
+    if (a.add_to[j]) a.add_to[j][o] = __fadd_rn(a.add_to[j][o], v);
+}
+
+__global__ void __launch_bounds__(256) k_combine_multi(const __grid_constant__ CombineArgs a) {
+    __shared__ double sm[8];
+    __shared__ int last_block, timed_out;
+    int j = 0;
+    while (j + 1 < a.n_sinks && (int)blockIdx.x >= a.block_end[j]) ++j;
+    const int block = (int)blockIdx.x - (j ? a.block_end[j - 1] : 0);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const double* part = a.part[j];
+    const int64_t n_out = a.n_out[j];
+    const int S = a.S[j];
+    if (a.mode[j] == 0) {
+        const int64_t o = ((int64_t)block * 256 + tid) >> 5;
+        if (o < n_out) {
+            double acc = 0.0;
+            for (int s = lane; s < S; s += 32) acc += part[(int64_t)s * n_out + o];
+            #pragma unroll
+            for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+            if (lane == 0) combine_put(a, j, o, acc);
+        }
+    } else if (a.mode[j] == 1) {
+        const int64_t o = (int64_t)block * 256 + tid;
+        if (o < n_out) {
+            double acc = 0.0;
+            for (int s = 0; s < S; ++s) acc += part[(int64_t)s * n_out + o];
+            combine_put(a, j, o, acc);
+        }
+    } else {
+        double acc = 0.0;
+        for (int s = tid; s < S; s += 256) acc += part[s];
+        #pragma unroll
+        for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+        if (lane == 0) sm[warp] = acc;
+        __syncthreads();
+        if (tid == 0) {
+            double t = sm[0];
+            #pragma unroll
+            for (int w = 1; w < 8; ++w) t += sm[w];
+            combine_put(a, j, 0, t);
+        }
+    }
+    if (!a.exchange) return;
+    // the block that takes the last ticket sees every other block's results (fence, then the ticket) and exchanges them
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned int ticket = atomicAdd(&g_combine_tickets, 1u);
+        last_block = ticket == gridDim.x - 1;
+        if (last_block) g_combine_tickets = 0;
+    }
+    __syncthreads();
+    if (!last_block) return;
+    __threadfence();
+    p2p_exchange_block(a.x, &timed_out);
+}
+
 static inline int finish_launch_expr(const char* what) {
     count_launch(1);
     cudaError_t e = cudaGetLastError();
@@ -197,7 +284,8 @@ static int expr_eval(const uint32_t* code, int n_code, const float* imm, int n_i
                      const ktc_buf* leaves, const int64_t* leaf_shapes, int n_leaves,
                      const ktc_buf* stores, int n_stores,
                      int sink, ktc_buf sink_out, int mean,
-                     const int* sink_kinds, const ktc_buf* sink_outs, const int* means, int n_sinks) {
+                     const int* sink_kinds, const ktc_buf* sink_outs, const int* means, int n_sinks,
+                     const ktc_buf* add_to = nullptr, ktc_p2p comm = 0, const ktc_buf* x_bufs = nullptr, const int64_t* x_counts = nullptr, int n_x = 0) {
     if (!code || n_code < 1 || n_code > kExprMaxInstr) return fail(KTC_EINVAL, "ktc_expr_eval: program of %d instructions (1..%d allowed)", n_code, kExprMaxInstr);
     if (n_imm < 0 || n_imm > kExprMaxImm || (n_imm > 0 && !imm)) return fail(KTC_EINVAL, "ktc_expr_eval: %d immediates (at most %d)", n_imm, kExprMaxImm);
     if (n_leaves < 0 || n_leaves > kExprMaxLeaves || n_stores < 0 || n_stores > kExprMaxStores)
@@ -300,6 +388,13 @@ static int expr_eval(const uint32_t* code, int n_code, const float* imm, int n_i
     a.col_tiles = (D[2] / 4 + 31) / 32;
     int64_t seg_rows = tune("expr_item_kb", 32) * 1024 / 512;      // rows of 128 columns per warp
     if (seg_rows < 8) seg_rows = 8;
+    // A shard of a strongly scaled step is small: with 32 KB items its grid is one wave and a bit (512 CTAs for 2^25
+    // elements on 148 SMs x 3 resident CTAs, the second wave a quarter full: 86 us where 61 us would do).  Items shrink
+    // (down to 8 rows) until the grid holds a few waves.
+    if (d) {
+        const int64_t want = (int64_t)d->sm_count * 3 * tune("expr_min_waves", 4);
+        while (seg_rows > 8 && ((rows + seg_rows - 1) / seg_rows + 7) / 8 * a.col_tiles < want) seg_rows /= 2;
+    }
     if (seg_rows > rows) seg_rows = rows;
     a.seg_rows = seg_rows;
     int64_t Sg = (rows + seg_rows - 1) / seg_rows;
@@ -344,22 +439,33 @@ static int expr_eval(const uint32_t* code, int n_code, const float* imm, int n_i
             a.mpart[j] = base;
             base += part_size(sink_kinds[j]);
         }
-        KTC_TRY(launch_expr(d, a, n_leaves, sink, grid, total));
+        // everything that can fail is checked before the first launch
+        CombineArgs c{};
+        c.n_sinks = n_sinks;
+        int blocks = 0;
         for (int j = 0; j < n_sinks; ++j) {
-            if (sink_kinds[j] == KTC_EXPR_SUM_ALL) {
-                if (means[j]) k_combine_block<1, SumAcc><<<1, 512, 0, d->stream>>>(a.mpart[j], mout[j].ptr, nullptr, 1, (int)grid, total);
-                else          k_combine_block<0, SumAcc><<<1, 512, 0, d->stream>>>(a.mpart[j], mout[j].ptr, nullptr, 1, (int)grid, total);
-            } else if (sink_kinds[j] == KTC_EXPR_SUM_LAST) {
-                // partial[column tile][row]: one thread per row adds the tiles in order
-                k_combine_thread<0, SumAcc><<<(int)((rows + 255) / 256), 256, 0, d->stream>>>(a.mpart[j], mout[j].ptr, nullptr, rows, (int)a.col_tiles, D[2]);
-            } else if (groups >= 64 || D[2] < 4096) {
-                const int64_t blocks = (D[2] * 32 + 255) / 256;
-                k_combine_warp<0, SumAcc><<<(int)blocks, 256, 0, d->stream>>>(a.mpart[j], mout[j].ptr, nullptr, D[2], (int)groups, rows);
-            } else {
-                k_combine_thread<0, SumAcc><<<(int)((D[2] + 255) / 256), 256, 0, d->stream>>>(a.mpart[j], mout[j].ptr, nullptr, D[2], (int)groups, rows);
+            c.part[j] = a.mpart[j]; c.out[j] = mout[j].ptr; c.divisor[j] = means[j] ? (double)total : 0.0;
+            if (sink_kinds[j] == KTC_EXPR_SUM_ALL) { c.mode[j] = 2; c.n_out[j] = 1; c.S[j] = (int)grid; blocks += 1; }
+            else if (sink_kinds[j] == KTC_EXPR_SUM_LAST) { c.mode[j] = 1; c.n_out[j] = rows; c.S[j] = (int)a.col_tiles; blocks += (int)((rows + 255) / 256); }
+            else if (groups >= 64 || D[2] < 4096) { c.mode[j] = 0; c.n_out[j] = D[2]; c.S[j] = (int)groups; blocks += (int)((D[2] * 32 + 255) / 256); }
+            else { c.mode[j] = 1; c.n_out[j] = D[2]; c.S[j] = (int)groups; blocks += (int)((D[2] + 255) / 256); }
+            c.block_end[j] = blocks;
+            if (add_to && add_to[j]) {
+                Buf t; KTC_TRY(resolve(add_to[j], &t)); KTC_TRY(adopt(t));
+                if (t.n < c.n_out[j]) return fail(KTC_EINVAL, "ktc_expr_eval_multi_fused: the tensor sink %d is added to holds %lld floats, %lld needed", j, (long long)t.n, (long long)c.n_out[j]);
+                if (t.ptr == mout[j].ptr) return fail(KTC_EINVAL, "ktc_expr_eval_multi_fused: sink %d is added to its own output", j);
+                c.add_to[j] = t.ptr;
             }
-            KTC_TRY(finish_launch_expr("expr(combine)"));
         }
+        if (comm) {
+            Device* xd = nullptr;
+            KTC_TRY(p2p_prepare(comm, x_bufs, x_counts, n_x, &c.x, &xd));
+            if (xd != d) return fail(KTC_EINVAL, "ktc_expr_eval_multi_fused: the communicator lives on another device");
+            c.exchange = 1;
+        }
+        KTC_TRY(launch_expr(d, a, n_leaves, sink, grid, total));
+        k_combine_multi<<<blocks, 256, 0, d->stream>>>(c);
+        KTC_TRY(finish_launch_expr("expr(combine)"));
         return KTC_OK;
     }
     a.divisor = mean ? (double)total : 0.0;
@@ -398,6 +504,17 @@ extern "C" int ktc_expr_eval(const uint32_t* code, int n_code, const float* imm,
         return expr_eval(code, n_code, imm, n_imm, shape, ndim, leaves, leaf_shapes, n_leaves, stores, n_stores, KTC_EXPR_MULTI, 0, 0, &kind, &sink_out, &mean, 1);
     }
     return expr_eval(code, n_code, imm, n_imm, shape, ndim, leaves, leaf_shapes, n_leaves, stores, n_stores, sink, sink_out, mean, nullptr, nullptr, nullptr, 0);
+}
+
+extern "C" int ktc_expr_eval_multi_fused(const uint32_t* code, int n_code, const float* imm, int n_imm,
+                                         const int64_t* shape, int ndim,
+                                         const ktc_buf* leaves, const int64_t* leaf_shapes, int n_leaves,
+                                         const ktc_buf* stores, int n_stores,
+                                         const int* sink_kinds, const ktc_buf* sink_outs, const int* means, int n_sinks,
+                                         const ktc_buf* add_to, ktc_p2p comm, const ktc_buf* x_bufs, const int64_t* x_counts, int n_x) {
+    if (comm && (!x_bufs || !x_counts || n_x < 1)) return fail(KTC_EINVAL, "ktc_expr_eval_multi_fused: a communicator without tensors to exchange");
+    return expr_eval(code, n_code, imm, n_imm, shape, ndim, leaves, leaf_shapes, n_leaves, stores, n_stores, KTC_EXPR_MULTI, 0, 0, sink_kinds, sink_outs, means, n_sinks,
+                     add_to, comm, x_bufs, x_counts, n_x);
 }
 
 extern "C" int ktc_expr_eval_multi(const uint32_t* code, int n_code, const float* imm, int n_imm,

@@ -73,8 +73,10 @@ struct Backend {
     int (*reduce_all)(int, ktc_buf, ktc_buf, int64_t);
     int (*expr_eval)(const uint32_t*, int, const float*, int, const int64_t*, int, const ktc_buf*, const int64_t*, int,
                      const ktc_buf*, int, int, ktc_buf, int);
-    int (*expr_eval_multi)(const uint32_t*, int, const float*, int, const int64_t*, int, const ktc_buf*, const int64_t*, int,
-                           const ktc_buf*, int, const int*, const ktc_buf*, const int*, int);
+    int (*expr_eval_multi_fused)(const uint32_t*, int, const float*, int, const int64_t*, int, const ktc_buf*, const int64_t*, int,
+                                 const ktc_buf*, int, const int*, const ktc_buf*, const int*, int,
+                                 const ktc_buf*, uint64_t, const ktc_buf*, const int64_t*, int);
+    int (*p2p_allreduce_sum)(uint64_t, const ktc_buf*, const int64_t*, int);
 };
 constexpr int kBackendEntries = sizeof(Backend) / sizeof(void*);
 
@@ -85,7 +87,7 @@ static void set_error_v(const char* fmt, va_list ap) { vsnprintf(g_err, sizeof(g
 #else
 static Backend B = {ktc_alloc, ktc_retain, ktc_release, ktc_refcount, ktc_buf_info, ktc_d2d, ktc_binary, ktc_binary_bcast,
                     ktc_binary_inplace, ktc_scalar, ktc_scalar_inplace, ktc_unary, ktc_clamp, ktc_compare_scalar, ktc_broadcast_to,
-                    ktc_reduce_axis, ktc_reduce_all, ktc_expr_eval, ktc_expr_eval_multi};
+                    ktc_reduce_axis, ktc_reduce_all, ktc_expr_eval, ktc_expr_eval_multi_fused, ktc_p2p_allreduce_sum};
 static void set_error_v(const char* fmt, va_list ap) { char b[512]; vsnprintf(b, sizeof(b), fmt, ap); ::ktc::set_error("%s", b); }
 #endif
 
@@ -181,7 +183,7 @@ static constexpr size_t kCacheMax = 4096;
 static uint32_t g_epoch = 0;
 static int64_t g_live_nodes = 0;
 static int opt_recompute_limit = 2, opt_store_cost = 8, opt_defer_sums = 1, opt_defer_inplace = 1;
-static int64_t st_fused = 0, st_unfused = 0, st_multi = 0, st_cache_hits = 0, st_compiles = 0;
+static int64_t st_fused = 0, st_unfused = 0, st_multi = 0, st_cache_hits = 0, st_compiles = 0, st_fused_updates = 0, st_fused_exchanges = 0;
 
 // ---- nodes ----------------------------------------------------------------------------------------
 static void node_unref(Node* n);
@@ -596,7 +598,7 @@ static void pack_leaves(const Program& prog, std::vector<ktc_buf>& hs, std::vect
     if (hs.empty()) { hs.push_back(0); shapes.push_back(0); }
 }
 
-static int run_pending();
+static int run_pending(struct Exchange* x = nullptr);
 static int force(Node* node, ktc_buf* h, Shape* shape);
 static int eager_into(Node* node, const Shape& shape, ktc_buf out);
 
@@ -790,7 +792,17 @@ static int eager_into(Node* node, const Shape& shape, ktc_buf out) {
 }
 
 // ---- pending sums ---------------------------------------------------------------------------------------
-static int try_fused_sums(const Shape& shape, const std::vector<Node*>& nodes, bool* fused) {
+// An all-reduce asked for while sums are pending (ktc_lazy_allreduce): when the sums turn out to be ONE pass whose
+// second-pass kernel also applies every pending update, that kernel performs the exchange too.
+struct Exchange {
+    uint64_t comm = 0;
+    std::vector<Node*> nodes;               // the values to sum over the ranks: stored nodes, or pending sums of the pass
+    bool done = false;
+};
+struct Update { uint64_t seq; ktc_buf target; Node* nd; };
+
+// add_to[i]: the buffer node i's sum is also added to (0: none).  x: the exchange to fold in, or null.
+static int try_fused_sums(const Shape& shape, const std::vector<Node*>& nodes, const std::vector<ktc_buf>& add_to, Exchange* x, bool* fused) {
     *fused = false;
     std::vector<Node*> exprs; std::vector<int> kinds, means;
     bool any_rows = false;
@@ -809,11 +821,22 @@ static int try_fused_sums(const Shape& shape, const std::vector<Node*>& nodes, b
     std::vector<ktc_buf> lh; std::vector<int64_t> ls;
     pack_leaves(prog, lh, ls);
     const ktc_buf none = 0; const float zero = 0.f;
-    const int rc = B.expr_eval_multi(prog.code.data(), (int)prog.code.size(), prog.imm.empty() ? &zero : prog.imm.data(), (int)prog.imm.size(),
-                                     prog.shape.d, prog.shape.nd, lh.data(), ls.data(), (int)prog.leaves.size(),
-                                     extra.empty() ? &none : extra.data(), (int)extra.size(), kinds.data(), outs.data(), means.data(), (int)nodes.size());
+    std::vector<ktc_buf> xb; std::vector<int64_t> xc;
+    if (x) {
+        for (Node* n : x->nodes) {
+            ktc_buf h = n->buf;
+            for (size_t i = 0; !h && i < nodes.size(); ++i) if (nodes[i] == n) h = outs[i];
+            if (!h) { x = nullptr; break; }               // not a value of this pass: the exchange runs on its own afterwards
+            xb.push_back(h); xc.push_back(n->shape.volume());
+        }
+    }
+    const int rc = B.expr_eval_multi_fused(prog.code.data(), (int)prog.code.size(), prog.imm.empty() ? &zero : prog.imm.data(), (int)prog.imm.size(),
+                                           prog.shape.d, prog.shape.nd, lh.data(), ls.data(), (int)prog.leaves.size(),
+                                           extra.empty() ? &none : extra.data(), (int)extra.size(), kinds.data(), outs.data(), means.data(), (int)nodes.size(),
+                                           add_to.data(), x ? x->comm : 0, x ? xb.data() : nullptr, x ? xc.data() : nullptr, x ? (int)xb.size() : 0);
     if (rc != KTC_OK) { drop(); return rc == KTC_ENOTSUP ? KTC_OK : rc; }
     ++st_fused; ++st_multi;
+    if (x) { x->done = true; ++st_fused_exchanges; }
     *fused = true;
     for (Node* n : prog.order) ++n->evals;
     for (size_t i = 0; i < store_nodes.size(); ++i) adopt(store_nodes[i], extra[i]);
@@ -858,19 +881,32 @@ static int run_one_sum(Node* nd) {
 // Evaluate every pending sum that is still wanted, then apply the pending updates in the order they were
 // requested.  Sums over the same iteration space run as one multi-sink pass (up to KTC_EXPR_MAX_SINKS per
 // pass); a sum whose expression contains another pending sum waits for it.
-static int run_pending() {
+static int run_pending(Exchange* x) {
     std::vector<Pending> entries;
     entries.swap(g_pending);
-    g_pending_targets.clear();
-    struct Todo { Node* nd; std::vector<ktc_buf> targets; std::vector<uint64_t> seq; };
-    std::vector<Todo> todo;
+    std::unordered_map<ktc_buf, int> target_count;
+    target_count.swap(g_pending_targets);
+    struct Todo { Node* nd; };
+    std::vector<Node*> todo;
+    std::vector<Update> ups;
     for (Pending& e : entries) {
         if (!e.strong) node_ref(e.node);                  // keep every sum alive until this call is over
-        if (!e.node->stored()) todo.push_back({e.node, e.targets, e.seq});
+        if (!e.node->stored()) todo.push_back(e.node);
+        for (size_t i = 0; i < e.targets.size(); ++i) ups.push_back({e.seq[i], e.targets[i], e.node});
     }
+    std::sort(ups.begin(), ups.end(), [](const Update& a, const Update& b) { return a.seq < b.seq; });
+    // an update is folded into the second pass of its sum when it is the only update of its buffer and the only one
+    // hanging on its sum (then its place in the order of the calls cannot matter), and the sum is not read by the pass
+    auto foldable = [&](const Update& u) {
+        if (target_count[u.target] != 1) return false;
+        int n = 0;
+        for (const Update& v : ups) n += v.nd == u.nd;
+        return n == 1 && !u.nd->stored() && u.nd->op != KTC_EXPR_SUM_LAST;
+    };
+    std::vector<char> folded(ups.size(), 0);
     int status = KTC_OK;
-    std::vector<Node*> waiting_nodes;
-    for (auto& t : todo) waiting_nodes.push_back(t.nd);
+    std::vector<Node*> waiting_nodes(todo);
+    int passes = 0;
     while (status == KTC_OK && !waiting_nodes.empty()) {
         std::vector<Node*> ready, rest;
         for (Node* nd : waiting_nodes) { Node* e = nd->args[0]; (has_pending_sum(&e, 1) ? rest : ready).push_back(nd); }
@@ -896,20 +932,27 @@ static int run_pending() {
             for (size_t i = 0; status == KTC_OK && i < g.second.size(); i += KTC_EXPR_MAX_SINKS) {
                 std::vector<Node*> chunk(g.second.begin() + i, g.second.begin() + std::min(g.second.size(), i + KTC_EXPR_MAX_SINKS));
                 bool fused = false;
-                if (chunk.size() > 1) status = try_fused_sums(g.first, chunk, &fused);
+                ++passes;
+                if (chunk.size() > 1) {
+                    std::vector<ktc_buf> add_to(chunk.size(), 0);
+                    std::vector<size_t> which(chunk.size(), 0);
+                    size_t n_fold = 0;
+                    for (size_t k = 0; k < ups.size(); ++k)
+                        for (size_t c = 0; c < chunk.size(); ++c)
+                            if (ups[k].nd == chunk[c] && foldable(ups[k])) { add_to[c] = ups[k].target; which[c] = k; ++n_fold; }
+                    // the exchange joins only when this is the whole of the pending work: one pass, every update in it
+                    const bool whole = passes == 1 && waiting_nodes.empty() && groups.size() == 1 && g.second.size() == chunk.size() && n_fold == ups.size();
+                    status = try_fused_sums(g.first, chunk, add_to, (x && whole) ? x : nullptr, &fused);
+                    if (status == KTC_OK && fused)
+                        for (size_t c = 0; c < chunk.size(); ++c) if (add_to[c]) { folded[which[c]] = 1; ++st_fused_updates; }
+                }
                 for (size_t j = 0; status == KTC_OK && !fused && j < chunk.size(); ++j) status = run_one_sum(chunk[j]);
             }
         }
     }
-    if (status == KTC_OK) {
-        struct Up { uint64_t seq; ktc_buf target; Node* nd; };
-        std::vector<Up> ups;
-        for (auto& t : todo) for (size_t i = 0; i < t.targets.size(); ++i) ups.push_back({t.seq[i], t.targets[i], t.nd});
-        std::sort(ups.begin(), ups.end(), [](const Up& a, const Up& b) { return a.seq < b.seq; });
-        for (auto& u : ups) {
-            status = B.binary_inplace(KTC_PLUS, u.target, u.nd->buf, u.nd->shape.volume());
-            if (status != KTC_OK) break;
-        }
+    for (size_t k = 0; status == KTC_OK && k < ups.size(); ++k) {
+        if (folded[k]) continue;
+        status = B.binary_inplace(KTC_PLUS, ups[k].target, ups[k].nd->buf, ups[k].nd->shape.volume());
     }
     for (Pending& e : entries) {
         for (ktc_buf h : e.targets) B.release(h);
@@ -1250,6 +1293,37 @@ KTC_API int ktc_lazy_run_pending(void) {
     return run_pending();
 }
 
+// Sum the values of `cells` over the ranks of a peer-memory communicator, in place (ktc_p2p_allreduce_sum on their
+// buffers).  Pending values are computed first; when all the pending work is one pass with several sums -- the loss
+// and the gradients of a training step -- the exchange runs inside that pass's second-pass kernel.
+KTC_API int ktc_lazy_allreduce(uint64_t comm, const ktc_lazy_cell* cells, int n) {
+    LZ_LOCK;
+    if (!cells || n < 1 || n > 8) return fail(KTC_EINVAL, "ktc_lazy_allreduce: 1..8 cells per call");
+    Exchange x;
+    x.comm = comm;
+    for (int i = 0; i < n; ++i) {
+        Cell* c = cell_of(cells[i]);
+        if (!c || !c->node) return fail(KTC_ESTATE, "ktc_lazy_allreduce: stale or unknown cell");
+        Node* nd = strip(c->node);
+        if (!nd->stored() && nd->kind != K_REDUCE) { ktc_buf h; LZ_TRY(force(nd, &h, nullptr)); }      // an elementwise value: computed now
+        x.nodes.push_back(node_ref(nd));
+    }
+    int s = KTC_OK;
+    if (!g_pending.empty()) s = run_pending(&x);
+    if (s == KTC_OK && !x.done) {
+        std::vector<ktc_buf> bufs; std::vector<int64_t> counts;
+        for (Node* nd : x.nodes) {
+            ktc_buf h = 0;
+            s = force(nd, &h, nullptr);
+            if (s != KTC_OK) break;
+            bufs.push_back(h); counts.push_back(nd->shape.volume());
+        }
+        if (s == KTC_OK) s = B.p2p_allreduce_sum(comm, bufs.data(), counts.data(), n);
+    }
+    for (Node* nd : x.nodes) node_unref(nd);
+    return s;
+}
+
 // recompute_limit, store_cost, defer_sums, defer_inplace
 KTC_API int ktc_lazy_option(const char* name, int value) {
     LZ_LOCK;
@@ -1262,14 +1336,16 @@ KTC_API int ktc_lazy_option(const char* name, int value) {
     return KTC_OK;
 }
 
-// out8: programs run, expressions that fell back to separate calls, passes with several sums, sums pending now,
-// program-cache hits, programs compiled, live nodes, live cells
-KTC_API int ktc_lazy_stats(int64_t* out8) {
+// out10: programs run, expressions that fell back to separate calls, passes with several sums, sums pending now,
+// program-cache hits, programs compiled, live nodes, live cells, `+= sum` updates applied by a second-pass kernel,
+// all-reduces performed by a second-pass kernel
+KTC_API int ktc_lazy_stats(int64_t* out10) {
     LZ_LOCK;
-    if (!out8) return fail(KTC_EINVAL, "ktc_lazy_stats: no output");
-    out8[0] = st_fused; out8[1] = st_unfused; out8[2] = st_multi; out8[3] = (int64_t)g_pending.size();
-    out8[4] = st_cache_hits; out8[5] = st_compiles; out8[6] = g_live_nodes;
-    out8[7] = (int64_t)g_cells.size() - (int64_t)g_free_cells.size();
+    if (!out10) return fail(KTC_EINVAL, "ktc_lazy_stats: no output");
+    out10[0] = st_fused; out10[1] = st_unfused; out10[2] = st_multi; out10[3] = (int64_t)g_pending.size();
+    out10[4] = st_cache_hits; out10[5] = st_compiles; out10[6] = g_live_nodes;
+    out10[7] = (int64_t)g_cells.size() - (int64_t)g_free_cells.size();
+    out10[8] = st_fused_updates; out10[9] = st_fused_exchanges;
     return KTC_OK;
 }
 

@@ -17,7 +17,7 @@
 // call so that a rank that runs ahead cannot overwrite values a slower rank is still reading: a
 // rank can only be one call ahead, because finishing a call needs every peer's flag for it.
 // Only ordinary loads and stores on mapped peer memory are used; no collective library is involved.
-#include "ktc_internal.hpp"
+#include "ktc_p2p.cuh"
 
 #include <cstring>
 
@@ -25,82 +25,13 @@ using namespace ktc;
 
 namespace {
 
-constexpr int kMaxWorld = KTC_P2P_MAX_RANKS;
-constexpr int kMaxFloats = KTC_P2P_MAX_FLOATS;
-constexpr int kMaxBufs = KTC_P2P_MAX_TENSORS;
-
-struct Mailbox {
-    unsigned int flags[2][kMaxWorld];        // flags[set][r]: the last call for which rank r's values are complete
-    unsigned int status;                     // 1: a wait ran out (sticky until read by the host)
-    unsigned int pad[31];
-    float slots[2][kMaxWorld][kMaxFloats];
-};
-
-struct P2pArgs {
-    Mailbox* mine;
-    Mailbox* peer[kMaxWorld];
-    int world, rank;
-    unsigned int epoch;
-    int n_bufs;
-    float* buf[kMaxBufs];
-    int count[kMaxBufs];
-    long long limit_ns;
-};
-
-__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
-    unsigned int v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
+constexpr int kMaxWorld = kP2pMaxWorld;
+constexpr int kMaxBufs = kP2pMaxBufs;
+constexpr int kMaxFloats = kP2pMaxFloats;
 
 __global__ void __launch_bounds__(1024) k_p2p_allreduce(const __grid_constant__ P2pArgs a) {
     __shared__ int timed_out;
-    const int tid = threadIdx.x;
-    const int set = a.epoch & 1;
-    if (tid == 0) timed_out = 0;
-    // 1. publish
-    int off = 0;
-    for (int b = 0; b < a.n_bufs; ++b) {
-        for (int j = tid; j < a.count[b]; j += 1024) {
-            const float v = a.buf[b][j];
-            for (int p = 0; p < a.world; ++p) a.peer[p]->slots[set][a.rank][off + j] = v;
-        }
-        off += a.count[b];
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (tid < a.world) st_release_sys(&a.peer[tid]->flags[set][a.rank], a.epoch);
-    // 2. bounded wait for every rank's flag in this rank's mailbox
-    if (tid < a.world) {
-        unsigned long long t0, t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-        bool ok = false;
-        for (int iter = 0; iter < (1 << 26); ++iter) {
-            if (ld_acquire_sys(&a.mine->flags[set][tid]) == a.epoch) { ok = true; break; }
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-            if ((long long)(t - t0) > a.limit_ns) break;
-            __nanosleep(64);
-        }
-        if (!ok) timed_out = 1;
-    }
-    __syncthreads();
-    if (timed_out) {
-        if (tid == 0) a.mine->status = 1;
-        return;
-    }
-    // 3. combine in rank order
-    off = 0;
-    for (int b = 0; b < a.n_bufs; ++b) {
-        for (int j = tid; j < a.count[b]; j += 1024) {
-            float s = __ldcg(&a.mine->slots[set][0][off + j]);
-            for (int r = 1; r < a.world; ++r) s = __fadd_rn(s, __ldcg(&a.mine->slots[set][r][off + j]));
-            a.buf[b][j] = s;
-        }
-        off += a.count[b];
-    }
+    p2p_exchange_block(a, &timed_out);
 }
 
 struct P2pRec {
@@ -122,6 +53,39 @@ int lookup(ktc_p2p h, P2pRec* out, const char* who) {
 }
 
 }  // namespace
+
+namespace ktc {
+
+int p2p_prepare(ktc_p2p p, const ktc_buf* bufs, const int64_t* counts, int n_bufs, P2pArgs* out, Device** dev) {
+    if (!bufs || !counts || n_bufs < 1 || n_bufs > kMaxBufs) return fail(KTC_EINVAL, "ktc_p2p_allreduce_sum: 1..%d tensors per call", kMaxBufs);
+    P2pRec r; KTC_TRY(lookup(p, &r, "ktc_p2p_allreduce_sum"));
+    if (!r.connected) return fail(KTC_ESTATE, "ktc_p2p_allreduce_sum: not connected");
+    Device* d = device(r.dev); if (!d) return KTC_ESTATE;
+    KTC_TRY(use_device(d));
+    P2pArgs a{};
+    int64_t total = 0;
+    for (int i = 0; i < n_bufs; ++i) {
+        Buf b; KTC_TRY(resolve(bufs[i], &b));
+        if (b.dev != r.dev) return fail(KTC_EINVAL, "ktc_p2p_allreduce_sum: tensor %d on device %d, communicator on %d", i, b.dev, r.dev);
+        if (counts[i] < 0 || counts[i] > b.n) return fail(KTC_EINVAL, "ktc_p2p_allreduce_sum: tensor %d holds %lld floats, %lld given", i, (long long)b.n, (long long)counts[i]);
+        a.buf[i] = b.ptr; a.count[i] = (int)counts[i];
+        total += counts[i];
+    }
+    if (total > kMaxFloats) return fail(KTC_EINVAL, "ktc_p2p_allreduce_sum: %lld floats per call (at most %d)", (long long)total, kMaxFloats);
+    unsigned int epoch;
+    {
+        std::lock_guard<std::mutex> lk(g_p2p_mu);
+        epoch = ++g_p2p[p - 1].epoch;
+    }
+    a.mine = r.mine;
+    for (int q = 0; q < r.world; ++q) a.peer[q] = r.peer[q];
+    a.world = r.world; a.rank = r.rank; a.epoch = epoch; a.n_bufs = n_bufs;
+    a.limit_ns = (long long)tune("p2p_wait_ms", 10000) * 1000000LL;
+    *out = a; *dev = d;
+    return KTC_OK;
+}
+
+}  // namespace ktc
 
 extern "C" {
 
@@ -184,30 +148,9 @@ int ktc_test_p2p_connect_self(ktc_p2p p) {
 }
 
 int ktc_p2p_allreduce_sum(ktc_p2p p, const ktc_buf* bufs, const int64_t* counts, int n_bufs) {
-    if (!bufs || !counts || n_bufs < 1 || n_bufs > kMaxBufs) return fail(KTC_EINVAL, "ktc_p2p_allreduce_sum: 1..%d tensors per call", kMaxBufs);
-    P2pRec r; KTC_TRY(lookup(p, &r, "ktc_p2p_allreduce_sum"));
-    if (!r.connected) return fail(KTC_ESTATE, "ktc_p2p_allreduce_sum: not connected");
-    Device* d = device(r.dev); if (!d) return KTC_ESTATE;
-    KTC_TRY(use_device(d));
     P2pArgs a{};
-    int64_t total = 0;
-    for (int i = 0; i < n_bufs; ++i) {
-        Buf b; KTC_TRY(resolve(bufs[i], &b));
-        if (b.dev != r.dev) return fail(KTC_EINVAL, "ktc_p2p_allreduce_sum: tensor %d on device %d, communicator on %d", i, b.dev, r.dev);
-        if (counts[i] < 0 || counts[i] > b.n) return fail(KTC_EINVAL, "ktc_p2p_allreduce_sum: tensor %d holds %lld floats, %lld given", i, (long long)b.n, (long long)counts[i]);
-        a.buf[i] = b.ptr; a.count[i] = (int)counts[i];
-        total += counts[i];
-    }
-    if (total > kMaxFloats) return fail(KTC_EINVAL, "ktc_p2p_allreduce_sum: %lld floats per call (at most %d)", (long long)total, kMaxFloats);
-    unsigned int epoch;
-    {
-        std::lock_guard<std::mutex> lk(g_p2p_mu);
-        epoch = ++g_p2p[p - 1].epoch;
-    }
-    a.mine = r.mine;
-    for (int q = 0; q < r.world; ++q) a.peer[q] = r.peer[q];
-    a.world = r.world; a.rank = r.rank; a.epoch = epoch; a.n_bufs = n_bufs;
-    a.limit_ns = (long long)tune("p2p_wait_ms", 10000) * 1000000LL;
+    Device* d = nullptr;
+    KTC_TRY(p2p_prepare(p, bufs, counts, n_bufs, &a, &d));
     k_p2p_allreduce<<<1, 1024, 0, d->stream>>>(a);
     count_launch(1);
     cudaError_t e = cudaGetLastError();

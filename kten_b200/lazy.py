@@ -28,7 +28,7 @@ from . import _lib as L
 
 STATE_WRITTEN, STATE_PENDING, STATE_UPDATE_RECORDED = 0, 1, 2
 OPTIONS = ("recompute_limit", "store_cost", "defer_sums", "defer_inplace")
-STATS = ("fused", "unfused", "multi_sink", "pending_sums", "cache_hits", "compiled", "live_nodes", "live_cells")
+STATS = ("fused", "unfused", "multi_sink", "pending_sums", "cache_hits", "compiled", "live_nodes", "live_cells", "folded_updates", "folded_exchanges")
 
 
 class Recorder:
@@ -99,10 +99,16 @@ class Recorder:
     def run_pending(self) -> None:
         L.check(self.lib.ktc_lazy_run_pending())
 
+    def allreduce(self, comm: int, cells: Sequence[int]) -> None:
+        """Sum the cells' values over the ranks of a peer-memory communicator, in place; pending work runs first
+        and takes the exchange into its second-pass kernel where it can."""
+        arr = (C.c_uint64 * len(cells))(*cells)
+        L.check(self.lib.ktc_lazy_allreduce(comm, arr, len(cells)))
+
     def option(self, name: str, value: int) -> None:
         L.check(self.lib.ktc_lazy_option(name.encode(), int(value)))
 
     def stats(self) -> dict:
-        out = (C.c_int64 * 8)()
+        out = (C.c_int64 * 10)()
         L.check(self.lib.ktc_lazy_stats(out))
         return dict(zip(STATS, (int(v) for v in out)))

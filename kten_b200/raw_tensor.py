@@ -136,14 +136,16 @@ class CUDARawTensor:
     def _new(self, shape: Sequence[int]) -> "CUDARawTensor":
         return self.ops.createRaw(list(shape))
 
-    def _lz(self) -> int:
-        """This tensor as an operand of a recorded call: its recorder cell (a stored tensor gets one over its buffer)."""
+    def _lz(self, apply_updates: bool = True) -> int:
+        """This tensor as an operand of a recorded call: its recorder cell (a stored tensor gets one over its buffer).
+        apply_updates = False leaves a recorded `+= pending sum` update of the buffer pending (the caller hands the
+        cell to a recorder call that deals with it)."""
         if self._released:
             raise RuntimeError("Raw tensor already released")
         cell = self._cell
         if cell.store is None:
             return cell.lz
-        if self.ops._pending_targets and cell.store in self.ops._pending_targets:
+        if apply_updates and self.ops._pending_targets and cell.store in self.ops._pending_targets:
             self.ops._run_pending()
         if cell.lz is None or cell.lz_shape != self.shape:
             if cell.lz is not None:

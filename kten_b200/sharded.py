@@ -87,6 +87,11 @@ class PeerMemoryCollective:
 
     def allreduce_sum(self, raws: Sequence) -> None:
         L = self._L
+        if len(raws) <= L.P2P_MAX_TENSORS and all(hasattr(r, "_lz") for r in raws) and getattr(self.ops, "_recorder", None) is not None:
+            # through the expression recorder: what is still pending is computed first, and where that is one pass with
+            # several sums the exchange runs inside its second-pass kernel
+            self.ops._recorder.allreduce(self.comm, [r._lz(apply_updates=False) for r in raws])
+            return
         for i in range(0, len(raws), L.P2P_MAX_TENSORS):
             group = raws[i:i + L.P2P_MAX_TENSORS]
             bufs = (C.c_uint64 * len(group))(*[r.storeReference for r in group])

@@ -53,7 +53,9 @@ BACKEND = [
     ("ktc_reduce_axis", (i32, i32, u64, u64, i64, i64, i64)),
     ("ktc_reduce_all", (i32, i32, u64, u64, i64)),
     ("ktc_expr_eval", (i32, P(C.c_uint32), i32, P(f32), i32, P(i64), i32, P(u64), P(i64), i32, P(u64), i32, i32, u64, i32)),
-    ("ktc_expr_eval_multi", (i32, P(C.c_uint32), i32, P(f32), i32, P(i64), i32, P(u64), P(i64), i32, P(u64), i32, P(i32), P(u64), P(i32), i32)),
+    ("ktc_expr_eval_multi_fused", (i32, P(C.c_uint32), i32, P(f32), i32, P(i64), i32, P(u64), P(i64), i32, P(u64), i32, P(i32), P(u64), P(i32), i32,
+                                   P(u64), u64, P(u64), P(i64), i32)),
+    ("ktc_p2p_allreduce_sum", (i32, u64, P(u64), P(i64), i32)),
 ]
 RECORDER_CALLS = {
     "ktc_lazy_leaf": (i32, [u64, P(i64), i32, P(u64)]), "ktc_lazy_free": (i32, [u64]),
@@ -64,6 +66,7 @@ RECORDER_CALLS = {
     "ktc_lazy_sum": (i32, [u64, i32, i32, P(i64), i32, P(u64)]), "ktc_lazy_buffer": (i32, [u64, P(u64)]),
     "ktc_lazy_info": (i32, [u64, P(i32), P(i32), P(i64), P(i32)]), "ktc_lazy_flush": (i32, [u64]),
     "ktc_lazy_run_pending": (i32, []), "ktc_lazy_option": (i32, [C.c_char_p, i32]), "ktc_lazy_stats": (i32, [P(i64)]),
+    "ktc_lazy_allreduce": (i32, [u64, P(u64), i32]),
 }
 
 
@@ -298,6 +301,31 @@ class FakeLib:
         source = self._get(src)[:outer * inner].reshape(outer, inner)
         o, i = np.meshgrid(np.arange(outer), np.arange(inner), indexing="ij")
         tgt[o, idx, i] = source
+        return 0
+
+    # ---- a world of one: the exchange leaves the tensors as they are, and is counted -------------------
+    def ktc_p2p_allreduce_sum(self, comm, bufs, counts, n):
+        self._note("p2p_allreduce")
+        for i in range(n):
+            self._get(bufs[i])
+        return 0
+
+    def ktc_expr_eval_multi_fused(self, code, n_code, imm, n_imm, shape, ndim, leaves, lshapes, n_leaves, stores, n_stores, kinds, outs, means, n_sinks,
+                                  add_to, comm, x_bufs, x_counts, n_x):
+        rc = self.ktc_expr_eval_multi(code, n_code, imm, n_imm, shape, ndim, leaves, lshapes, n_leaves, stores, n_stores, kinds, outs, means, n_sinks)
+        if rc != 0:
+            return rc
+        shp = _ints(shape, ndim)
+        total = int(np.prod(shp))
+        folded = 0
+        for j in range(n_sinks):
+            if add_to and add_to[j]:
+                n = 1 if kinds[j] == L.EXPR_SUM_ALL else shp[-1] if kinds[j] == L.EXPR_SUM_ROWS else total // shp[-1]
+                t = self._get(add_to[j])
+                t[:n] = (t[:n] + self._get(outs[j])[:n]).astype(np.float32)
+                folded += 1
+        self.programs[-1]["folded_updates"] = folded
+        self.programs[-1]["exchange"] = [int(x_bufs[i]) for i in range(n_x)] if comm else None
         return 0
 
     # ---- the fused expression call: the program encoding interpreted with the oracle's arithmetic ----

@@ -147,8 +147,9 @@ def test_programs_the_kernel_declines_are_split():
 
 def test_sharded_graph_step_deferred_equals_call_by_call():
     """The config-5 autograd step through the stand-in: same loss and gradients in both execution modes; the deferred
-    mode runs ONE pass with three sinks (loss, both broadcast gradients) plus the two in-place gradient accumulations
-    instead of two dozen calls -- three single-sink passes with ops.deferSums off --, nothing left allocated."""
+    mode runs ONE pass with three sinks (loss, both broadcast gradients) whose second pass also performs the two
+    in-place gradient accumulations, instead of two dozen calls -- three single-sink passes with ops.deferSums
+    off --, nothing left allocated."""
     from kten_b200.sharded import ShardedSigmoidGraph
     rows, cols = 32, 16
     x, w, b = D.uniform(rows * cols, 0, -1.0, 1.0), D.normal(cols, 0, 0.0, 0.5, stream=1), D.uniform(cols, 0, -0.1, 0.1, stream=2)
@@ -164,17 +165,17 @@ def test_sharded_graph_step_deferred_equals_call_by_call():
                 loss, gw, gb = g.step()
                 vals = (loss.toArray().copy(), gw.toArray().copy(), gb.toArray().copy())
                 g.release_step()
-            res.append((vals, ops.lib.calls[n0:], ops.lib.multi_calls))
+            res.append((vals, ops.lib.calls[n0:], ops.lib.multi_calls, ops.lib.programs[-1].get("folded_updates") if ops.lib.programs else None))
             for v in (g.x, g.w, g.b):
                 v.getRawValue().release()
             g.w.gradient.release(); g.b.gradient.release()
         gc.collect()
         assert ops.lib.live_buffers() == 0
-    (ve, ce, _), (vl, cl, multi), (vs, cs, multi_off) = res
+    (ve, ce, _, _), (vl, cl, multi, folded), (vs, cs, multi_off, _) = res[0], res[1], res[2]
     for a, c, d in zip(ve, vl, vs):
         assert np.allclose(a, c, rtol=1e-6, atol=1e-6) and np.allclose(a, d, rtol=1e-6, atol=1e-6)
     assert ce.count("expr_eval") == 0 and cs.count("expr_eval") == 3 and multi_off == 0 and len(cs) < len(ce) / 2
-    assert cl.count("expr_eval") == 1 and multi == 2 and cl.count("binary") == 2, cl      # one pass per step, two steps
+    assert cl == ["expr_eval"] and multi == 2 and folded == 2, cl      # one pass per step (two steps), both `+=` inside it
 
 
 def test_pending_sums_keep_the_semantics_of_sums_that_run_at_once():
@@ -336,3 +337,43 @@ def test_updates_of_one_buffer_apply_in_the_order_they_were_written():
     eager, lazy, stats = both(script)
     assert eager[0][0] == 1.0 and same_bits(eager[0], lazy[0])
     assert stats[1][1] == 1                  # both sums in one pass
+
+
+def test_allreduce_through_the_recorder_joins_the_pass_when_it_can():
+    """ktc_lazy_allreduce on (loss, grad w, grad b): with everything deferred the step is one pass whose second pass
+    applies both updates and performs the exchange (no call of the collective's own); call by call, or with sums that
+    run where they are written, the values are computed first and the collective is called on their buffers."""
+    from kten_b200.sharded import ShardedSigmoidGraph
+
+    class RecorderCollective:                      # what PeerMemoryCollective.allreduce_sum does, without a communicator to create
+        def __init__(self, ops):
+            self.ops = ops
+
+        def allreduce_sum(self, raws):
+            self.ops._recorder.allreduce(7, [r._lz(apply_updates=False) for r in raws])
+
+    rows, cols = 32, 16
+    x, w, b = D.uniform(rows * cols, 0, -1.0, 1.0), D.normal(cols, 0, 0.0, 0.5, stream=1), D.uniform(cols, 0, -0.1, 0.1, stream=2)
+    vals = {}
+    for mode in ("eager", "deferred", "sums at once"):
+        ops = make_ops()
+        ops.lazy = mode != "eager"
+        ops.deferSums = mode == "deferred"
+        with ops.garbageCollector():
+            g = ShardedSigmoidGraph(ops, ops.createRaw([rows, cols], x), ops.createRaw([1, cols], w), ops.createRaw([cols], b), RecorderCollective(ops))
+            for _ in range(2):
+                n0 = len(ops.lib.calls)
+                loss, gw, gb = g.step()
+                calls = ops.lib.calls[n0:]
+                vals[mode] = (loss.toArray().copy(), gw.toArray().copy(), gb.toArray().copy())
+                g.release_step()
+            if mode == "deferred":
+                last = ops.lib.programs[-1]
+                assert calls == ["expr_eval"] and last["folded_updates"] == 2
+                assert last["exchange"] == [loss.storeReference, gw.storeReference, gb.storeReference]
+                assert ops._recorder.stats()["folded_exchanges"] == 2
+            else:
+                assert calls[-1] == "p2p_allreduce" and calls.count("p2p_allreduce") == 1
+                assert ops._recorder.stats()["folded_exchanges"] == 0
+    for a, c, d in zip(vals["eager"], vals["deferred"], vals["sums at once"]):
+        assert np.allclose(a, c, rtol=1e-6, atol=1e-6) and np.allclose(a, d, rtol=1e-6, atol=1e-6)
