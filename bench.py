@@ -142,8 +142,9 @@ class ClockSampler:
 def cpu_sample_pass(sample_log2: int, tuned: bool = False):
     """One pass of the sweep on a 2^sample_log2-element sample with the CPU oracle:
     broadcast operands materialised, out-of-place maps single-threaded, in-place ops and
-    axis aggregation on all host threads (what kten-jvm does).  Returns (seconds, algorithmic
-    bytes of the sample, per-op seconds)."""
+    axis aggregation on all host threads (what kten-jvm does).  `tuned`: every map on all
+    host threads and no materialised broadcast operands -- the host's upper bound with the
+    same arithmetic.  Returns (seconds, algorithmic bytes of the sample, per-op seconds)."""
     from kten_b200 import datagen as D
     from oracle import oracle as O
     n = 1 << sample_log2
@@ -166,11 +167,11 @@ def cpu_sample_pass(sample_log2: int, tuned: bool = False):
             else:
                 O.unary({"exp": O.EXP, "log": O.LOG, "tanh": O.TANH, "sigmoid": O.SIGMOID}[op], a, tuned=tuned)
         elif name == "c3.a*b":
-            t3, _ = O.binary(O.TIMES, a3, [rows3, 1024, 256], b3, [1, 1024, 1])
+            t3, _ = O.binary(O.TIMES, a3, [rows3, 1024, 256], b3, [1, 1024, 1], tuned=tuned)
         elif name == "c3.(a*b)+c":
-            O.binary(O.PLUS, t3, [rows3, 1024, 256], c3, [rows3, 1, 256])
+            O.binary(O.PLUS, t3, [rows3, 1024, 256], c3, [rows3, 1, 256], tuned=tuned)
         elif name == "c3.a/b":
-            O.binary(O.DIV, a3, [rows3, 1024, 256], b3, [1, 1024, 1])
+            O.binary(O.DIV, a3, [rows3, 1024, 256], b3, [1, 1024, 1], tuned=tuned)
         elif name.startswith("c4.last."):
             O.aggregate({"sum": O.SUM, "mean": O.MEAN, "max": O.MAX, "argmax": O.ARGMAX}[name[8:]], x4, rows4, 4096, 1, mode=0)
         elif name.startswith("c4.mid."):
@@ -386,7 +387,7 @@ class GpuSweep:
         return float(ms.value)
 
 
-def run_sharded_graph(ops, lib, L, D, rank, world, collective, steps, warmup, dist):
+def run_sharded_graph(ops, lib, L, D, rank, world, collective, steps, warmup, dist, gpu_index=0):
     """The sharded autograd configuration: x[262144,1024] ~ U(-1,1) split by rows over the ranks
     (strong scaling: the global tensor is fixed), w[1,1024] ~ N(0,0.02), b[1024] = 0;
     loss = sum(sigmoid(x*w + b) pow 2), backward for w and b, partials all-reduced."""
@@ -483,16 +484,22 @@ def run_sharded_graph(ops, lib, L, D, rank, world, collective, steps, warmup, di
 
     eager = timed(False)
     single = timed(True, defer_sums=False)
+    sampler = ClockSampler(gpu_index)                       # clocks of this block's own window: the two deferred runs
+    sampler.start()
+    time.sleep(0.3)
+    t_window0 = time.time()
     fused = timed(True)
     try:
         native_fused = timed_native(True)
+        clocks = sampler.stop(t_window0, time.time())
         native_eager = timed_native(False)
     except Exception as exc:                                # the Python host's figures stand on their own
+        clocks = sampler.stop(t_window0, time.time())
         native_fused = native_eager = {"unavailable": str(exc)}
     for r in (x, w, b):
         r.release()
     res = {"workload": "x[262144,1024] row-sharded, loss = sum(sigmoid(x*w+b) pow 2), backward + all-reduce of (loss, gw, gb)",
-           "scaling": "strong", "rows_per_gpu": count}
+           "scaling": "strong", "rows_per_gpu": count, "n_gpus": world, "steps": steps}
     # the same raw-tensor call sequence of kten's autograd in the backend's two execution modes; the headline
     # figures are those of the faster one (the deferred mode is bound by this Python host side once a rank's
     # shard takes less device time than building and compiling the step's expressions)
@@ -511,6 +518,18 @@ def run_sharded_graph(ops, lib, L, D, rank, world, collective, steps, warmup, di
                                                  "grad_w_abs_sum", "grad_b_abs_sum")})
         res["execution"] = "deferred elementwise calls and sums, one pass with three sinks per step, issued by the compiled host (libkten_host.so)"
         res["host_us_per_step"] = native_fused["host_us_per_step"]
+    # roofline of the step: a rank has to read its shard of x once (the fused lower bound of the configuration); the
+    # time is the max over ranks.  The kernel is bound by instruction issue, not by HBM -- sigmoid's exp costs about 40
+    # issue slots per element, a double operation taking two -- which is what this fraction shows.
+    peak, peak_src = measured_peak()
+    shard_bytes = float(count * cols * 4)
+    achieved = shard_bytes / res["ms_per_step"] / 1e6
+    res["gelem_per_s_per_gpu"] = res["gelem_per_s"] / world
+    res["roofline"] = {"bound": "hbm", "kernel": "ktc_jit_kernel (one pass with three sinks) + k_combine_multi", "achieved": achieved, "peak": peak,
+                       "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src, "algorithmic_bytes_per_step_per_gpu": shard_bytes,
+                       "hbm_floor_ms": shard_bytes / peak / 1e6, "traffic": None,
+                       "note": "strong scaling: efficiency at N GPUs = ms_per_step(N=1) / (N * ms_per_step(N)), both from this block"}
+    res["clocks"] = clocks
     return res
 
 
@@ -546,6 +565,16 @@ def run_other_ops(ops, lib, L, D, steps):
         ("sqrt", 2 * G, lambda: x.sqrt()),
         ("sin", 2 * G, lambda: x.sin()),
         ("eq (tensor, tensor)", 3 * G, lambda: x.eq(idx)),
+        # tensor (op) scalar and the in-place forms (JVMRawTensor.kt:112-136): 8 B / element, and 12 B / element for a += b
+        ("times (tensor, scalar)", 2 * G, lambda: x.times(1.5)),
+        ("pow (scalar, tensor)", 2 * G, lambda: ops.pow(1.5, x)),
+        ("timesAssign (scalar), in place", 2 * G, lambda: acc.timesAssign(0.999)),
+        ("plusAssign (tensor), in place", 3 * G, lambda: acc.plusAssign(xr)),
+        # the broadcast-gradient sum-to-shape (mayUnexpand, Utils.kt:14-41) in one call: the config-5 shapes, and the
+        # two-axis shape of the plumbing graph scaled up ([32,64,128] -> [64,1] there)
+        ("sumToShape [262144,1024] -> [1,1024]", G + 4096, lambda: xr.sumToShape([1, 1024])),
+        ("sumToShape [262144,1024] -> [1024]", G + 4096, lambda: xr.sumToShape([1024])),
+        ("sumToShape [1024,1024,256] -> [1024,1]", G + 4096, lambda: xm.sumToShape([1024, 1])),
     ]
     reps = max(2, min(steps, 10))
     for name, nbytes, fn in cases:
@@ -744,7 +773,7 @@ def run_gpu_arm(args):
         for r in [sweep.a2, sweep.b2, sweep.a3, sweep.t3, sweep.x4] + getattr(sweep, "outs", [sweep.out]):
             r.release()                               # hand the sweep's buffers back to the pool first
         L.check(lib.ktc_pool_trim(local))
-        sharded = run_sharded_graph(sweep.ops, lib, L, D, rank, world, collective, max(2, min(args.steps, 5)), args.warmup, dist)
+        sharded = run_sharded_graph(sweep.ops, lib, L, D, rank, world, collective, max(args.steps, 20), args.warmup, dist, local)
         sharded["collective"] = collective_name
 
     other_ops = None
@@ -782,7 +811,7 @@ def run_gpu_arm(args):
     fam_ms = sum(p["ms"] for p, _ in fam_ops) / len(fam_ops)
     achieved = fam_bytes / fam_ms / 1e6
     kernel_names = {"map2": "k_map2_vec", "map1": "k_map1_vec", "bcast": "k_bcast3", "reduce_rows": "k_rows_warp", "reduce_cols": "k_cols_warp"}
-    traffic = load_traffic(kernel_names[top_family])
+    traffic, traffic_detail = load_traffic(kernel_names[top_family])
 
     line = {
         "metric": "HBM GB/s (algorithmic bytes / time), broadcast elementwise + axis reduce sweep",
@@ -802,7 +831,7 @@ def run_gpu_arm(args):
                         "uploads, kernels and downloads of neighbouring pieces overlap); bound by the device-to-host link"},
         "roofline": {"bound": "hbm", "kernel": kernel_names[top_family], "ops": [p["name"] for p, _ in fam_ops],
                      "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
-                     "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "traffic": traffic,
+                     "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "traffic": traffic, "traffic_detail": traffic_detail,
                      "algorithmic_bytes_per_launch": fam_bytes, "ms_per_launch": fam_ms,
                      "share_of_step": fam_time[top_family] / sum(fam_time.values())},
         "per_op": [{"name": p["name"], "ms": round(p["ms"], 4), "gbs": round(p["gbs"], 1), "frac_measured": round(p["gbs"] / peak, 3),
@@ -821,11 +850,15 @@ def run_gpu_arm(args):
     if rank == 0:
         if args.cpu_baseline:
             secs, nbytes, _ = cpu_sample_pass(args.cpu_sample_log2)
+            tuned_secs, tuned_bytes, _ = cpu_sample_pass(args.cpu_sample_log2, tuned=True)
             from oracle import oracle as O
             line["cpu_baseline"] = {"value": nbytes / secs / 1e9, "unit": "GB/s", "cores": O.num_threads(), "kind": "port",
                                     "sample": f"the same sweep on 2^{args.cpu_sample_log2}-element operands ({secs:.1f} s), CPU oracle in "
                                               "kten-jvm's structure (broadcast operands materialised, out-of-place maps single-threaded, "
-                                              "in-place ops and axis aggregation on all host threads)"}
+                                              "in-place ops and axis aggregation on all host threads)",
+                                    "tuned": {"value": tuned_bytes / tuned_secs / 1e9, "unit": "GB/s", "cores": O.num_threads(),
+                                              "sample": f"same sample ({tuned_secs:.1f} s), every elementwise map on all host threads: the "
+                                                        "upper bound of what the host can do with the same algorithm"}}
         sys.stdout.flush()
         os.write(json_fd, (json.dumps(line) + "\n").encode())
     if dist is not None:
@@ -981,23 +1014,33 @@ def run_single_case(args):
     return 0
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures summarised under
-# profiles/ (k_map2_vec__contiguous_binary.md, k_map1_vec__contiguous_unary.md, k_bcast3__broadcast_binary.md,
-# k_rows_warp__last_axis_and_full_reductions.md, k_cols_warp__middle_axis_reductions.md).  The captures ran
-# on 2^26-element operands (the full-size launch is too large to replay ~40 times); traffic grows in
-# proportion to the elements processed, so it is scaled x4 to the 2^28-element launch timed here.
+# dram__bytes_read.sum and dram__bytes_write.sum of one launch of each kernel family, from ncu captures of 2^26-element
+# cases (a full-size launch is too large to replay for ~40 passes).  Traffic grows in proportion to the elements
+# processed, so the figures are scaled x4 to the 2^28-element launch timed here.  Reads equal the operands exactly
+# once.  The write counter stops at the end of the kernel while tens of MB of dirty lines are still in the 126 MB L2,
+# so writes read low at the capture size, and the scaled total lands below the algorithmic bytes for kernels that
+# write full-size results; the detail says so.
 NCU_TRAFFIC_AT_2_26 = {
-    "k_map2_vec": 536.9e6 + 221.9e6,      # c2.plus
-    "k_map1_vec": 268.5e6 + 213.9e6,      # c2.exp
-    "k_bcast3": 268.5e6 + 212.8e6,        # c3.a*b
-    "k_rows_warp": 268.5e6 + 3.5e6,       # c4.last.sum
-    "k_cols_warp": 268.4e6 + 3.3e6,       # c4.mid.sum
+    "k_map2_vec": (536.9e6, 221.9e6, "c2.plus"),
+    "k_map1_vec": (268.5e6, 213.9e6, "c2.exp"),
+    "k_bcast3": (268.5e6, 212.8e6, "c3.a*b"),
+    "k_rows_warp": (268.5e6, 3.5e6, "c4.last.sum"),
+    "k_cols_warp": (268.4e6, 3.3e6, "c4.mid.sum"),
 }
 
 
 def load_traffic(kernel: str):
-    v = NCU_TRAFFIC_AT_2_26.get(kernel)
-    return None if v is None else v * (N28 / (1 << 26))
+    """(traffic scaled to the full-size launch, what it is made of) or (None, None)."""
+    rec = NCU_TRAFFIC_AT_2_26.get(kernel)
+    if rec is None:
+        return None, None
+    scale = N28 / (1 << 26)
+    read, write, case = rec
+    return (read + write) * scale, {"dram_read_bytes": read * scale, "dram_write_bytes": write * scale, "measured_at_elements": 1 << 26,
+                                    "scaled_by": scale, "case": case,
+                                    "note": "ncu dram__bytes_read/write of one launch on 2^26-element operands, scaled by elements; reads = every "
+                                            "operand exactly once; writes are under-counted at the capture size (dirty lines still in L2 when the "
+                                            "kernel ends), so the total can read below the algorithmic bytes"}
 
 
 def main():
@@ -1012,7 +1055,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="kten_b200", choices=["kten_b200", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=2)
-    ap.add_argument("--cpu-sample-log2", type=int, default=None, help="log2 of the CPU sample size (default 25 for cpu_baseline, 24 for --impl reference)")
+    ap.add_argument("--cpu-sample-log2", type=int, default=None, help="log2 of the CPU sample size per operand (default 26, for cpu_baseline and for --impl reference alike)")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     ap.add_argument("--collective", choices=("p2p", "nccl"), default="p2p",
                     help="N > 1: sum of the partials across ranks by one kernel over peer memory (default) or through NCCL")
@@ -1024,7 +1067,7 @@ def main():
     ap.add_argument("--reps", type=int, default=3)
     args = ap.parse_args()
     if args.cpu_sample_log2 is None:
-        args.cpu_sample_log2 = 24 if args.impl == "reference" else 25
+        args.cpu_sample_log2 = 26                   # the reference arm and the in-line baseline time the same sample
     if args.impl == "reference":
         return run_reference_arm(args)
     if args.case:

@@ -197,8 +197,10 @@ KTC_API int ktc_sum_to_shape(ktc_buf out, const int64_t* old_shape, int old_ndim
  * receives one float); the per-CTA partials live in a fixed
  * KTC_NOALLOC_SCRATCH_BYTES array inside the library image on every GPU that
  * loads it.  n may not exceed KTC_NOALLOC_MAX_ELEMS (KTC_EINVAL otherwise).
- * All calls on a device share that array: they are issued on the device's one
- * compute stream and must not be made to overlap on the GPU.  The first call
+ * All calls on a device share that array.  A call is two launches on the
+ * device's one compute stream, issued under a per-device lock, so calls from
+ * several host threads of this process do not interleave; anything else that
+ * could make two calls overlap on the GPU is the caller's to prevent.  The first call
  * on a device resolves the array's device address; make it before any stream
  * capture begins. */
 #define KTC_NOALLOC_SCRATCH_BYTES 16384

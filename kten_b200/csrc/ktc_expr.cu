@@ -90,8 +90,9 @@ __global__ void __launch_bounds__(256) k_expr(const __grid_constant__ ExprArgs p
                 switch (op) {
                 case KTC_X_LOAD: {
                     const float* base = p.leaf[k] + i0 * p.ls0[k] + i1 * p.ls1[k];
-                    if (p.ls2[k]) v = __ldg(reinterpret_cast<const float4*>(base + col));
-                    else v = f4(__ldg(base));
+                    // plain (coherent) loads: an in-place program stores into the buffer one of its leaves reads
+                    if (p.ls2[k]) v = __ldcs(reinterpret_cast<const float4*>(base + col));
+                    else v = f4(*base);
                     break;
                 }
                 case KTC_X_CONST: v = f4(p.imm[k]); break;

@@ -397,16 +397,6 @@ __global__ void __launch_bounds__(256) k_ia_apply(T* __restrict__ target, const 
     target[t] = acc;
 }
 
-// reads the device error word (set by a kernel that met an invalid index), clears it, waits
-int take_index_error(Device* d, const char* what, int64_t axis_len, int axis) {
-    int h = 0;
-    KTC_CUDA(cudaMemcpyAsync(&h, d->err_flag, sizeof(int), cudaMemcpyDeviceToHost, d->stream));
-    KTC_CUDA(cudaMemsetAsync(d->err_flag, 0, sizeof(int), d->stream));
-    KTC_CUDA(cudaStreamSynchronize(d->stream));
-    if (h != 0) return fail(KTC_EINVAL, "%s got invalid index, index value is out of bounds 0 and %lld at axis: %d", what, (long long)axis_len, axis);
-    return KTC_OK;
-}
-
 int64_t grid_of(int64_t items, int per_block) { return (items + per_block - 1) / per_block; }
 
 }  // namespace
@@ -513,7 +503,7 @@ int launch_gather_axis(Device* d, float* out, const float* in, const int64_t* in
         const size_t smem = (size_t)in_shape[axis] * sizeof(float);
         if (smem > 48 * 1024)                                       // per device: cheap enough to repeat
             KTC_CUDA(cudaFuncSetAttribute(k_gather_lastaxis_smem, cudaFuncAttributeMaxDynamicSharedMemorySize, 40960 * (int)sizeof(float)));
-        k_gather_lastaxis_smem<<<(int)outer, 512, smem, d->stream>>>(out, in, index, (int)in_shape[axis], (int)index_shape[axis], d->err_flag);
+        k_gather_lastaxis_smem<<<(int)outer, 512, smem, d->stream>>>(out, in, index, (int)in_shape[axis], (int)index_shape[axis], d->idx_err);
         KTC_TRY(finish("gather_lastaxis_smem"));
         return take_index_error(d, "Gather", a.t_axis_len, axis);
     }
@@ -522,15 +512,15 @@ int launch_gather_axis(Device* d, float* out, const float* in, const int64_t* in
         if (grid > 0x7fffffffLL) return fail(KTC_ENOTSUP, "tensor too large for one launch");
         if (a.total < (1LL << 31) && in_total < (1LL << 31))
             k_gather_axis3<uint32_t><<<(int)grid, 256, 0, d->stream>>>(out, in, index, (uint32_t)in_shape[axis], (uint32_t)index_shape[axis],
-                                                                        (uint32_t)inner, (uint32_t)total4, d->err_flag);
+                                                                        (uint32_t)inner, (uint32_t)total4, d->idx_err);
         else
-            k_gather_axis3<int64_t><<<(int)grid, 256, 0, d->stream>>>(out, in, index, in_shape[axis], index_shape[axis], inner, total4, d->err_flag);
+            k_gather_axis3<int64_t><<<(int)grid, 256, 0, d->stream>>>(out, in, index, in_shape[axis], index_shape[axis], inner, total4, d->idx_err);
         KTC_TRY(finish("gather_axis3"));
         return take_index_error(d, "Gather", a.t_axis_len, axis);
     }
     const int64_t grid = grid_of(a.total, 256);
     if (grid > 0x7fffffffLL) return fail(KTC_ENOTSUP, "tensor too large for one launch");
-    k_gather_axis<<<(int)grid, 256, 0, d->stream>>>(out, in, index, a, d->err_flag);
+    k_gather_axis<<<(int)grid, 256, 0, d->stream>>>(out, in, index, a, d->idx_err);
     KTC_TRY(finish("gather_axis"));
     return take_index_error(d, "Gather", a.t_axis_len, axis);
 }
@@ -547,9 +537,9 @@ int launch_scatter_axis_nd(Device* d, int mode, float* target, const int64_t* ta
     if (a.total == 0 || index_shape[axis] == 0) return KTC_OK;
     const int64_t grid = grid_of(a.total, 128);
     if (grid > 0x7fffffffLL) return fail(KTC_ENOTSUP, "tensor too large for one launch");
-    if (mode == KTC_SCATTER_SET) k_scatter_axis_nd<0><<<(int)grid, 128, 0, d->stream>>>(target, index, src, a, constant, d->err_flag);
-    else if (mode == KTC_SCATTER_ADD) k_scatter_axis_nd<1><<<(int)grid, 128, 0, d->stream>>>(target, index, src, a, constant, d->err_flag);
-    else k_scatter_axis_nd<2><<<(int)grid, 128, 0, d->stream>>>(target, index, nullptr, a, constant, d->err_flag);
+    if (mode == KTC_SCATTER_SET) k_scatter_axis_nd<0><<<(int)grid, 128, 0, d->stream>>>(target, index, src, a, constant, d->idx_err);
+    else if (mode == KTC_SCATTER_ADD) k_scatter_axis_nd<1><<<(int)grid, 128, 0, d->stream>>>(target, index, src, a, constant, d->idx_err);
+    else k_scatter_axis_nd<2><<<(int)grid, 128, 0, d->stream>>>(target, index, nullptr, a, constant, d->idx_err);
     KTC_TRY(finish("scatter_axis_nd"));
     return take_index_error(d, "Scatter", a.t_axis_len, axis);
 }
@@ -563,14 +553,14 @@ int launch_index_select(Device* d, float* out, const float* in, const float* ind
         const int64_t total4 = total / 4, g4 = grid_of(total4, 1024);
         if (total < (1LL << 31) && outer * A * inner < (1LL << 31))
             k_index_select_vec<uint32_t><<<(int)g4, 256, 0, d->stream>>>(reinterpret_cast<float4*>(out), reinterpret_cast<const float4*>(in), index,
-                                                                         (uint32_t)A, (uint32_t)n_idx, (uint32_t)(inner / 4), (uint32_t)total4, d->err_flag);
+                                                                         (uint32_t)A, (uint32_t)n_idx, (uint32_t)(inner / 4), (uint32_t)total4, d->idx_err);
         else
             k_index_select_vec<int64_t><<<(int)g4, 256, 0, d->stream>>>(reinterpret_cast<float4*>(out), reinterpret_cast<const float4*>(in), index,
-                                                                        A, n_idx, inner / 4, total4, d->err_flag);
+                                                                        A, n_idx, inner / 4, total4, d->idx_err);
         KTC_TRY(finish("index_select(vec)"));
         return take_index_error(d, "Index select", A, -1);
     }
-    k_index_select<<<(int)grid, 256, 0, d->stream>>>(out, in, index, outer, A, n_idx, inner, d->err_flag);
+    k_index_select<<<(int)grid, 256, 0, d->stream>>>(out, in, index, outer, A, n_idx, inner, d->idx_err);
     KTC_TRY(finish("index_select"));
     return take_index_error(d, "Index select", A, -1);
 }
@@ -618,7 +608,7 @@ int launch_index_add(Device* d, float* target, const float* index, const float* 
     }
     const int64_t grid = grid_of(cols, 128);
     if (grid > 0x7fffffffLL) return fail(KTC_ENOTSUP, "tensor too large for one launch");
-    k_index_add<<<(int)grid, 128, 0, d->stream>>>(target, index, src, alpha, outer, A, n_idx, inner, d->err_flag);
+    k_index_add<<<(int)grid, 128, 0, d->stream>>>(target, index, src, alpha, outer, A, n_idx, inner, d->idx_err);
     KTC_TRY(finish("index_add"));
     return take_index_error(d, "Index Add", A, -1);
 }

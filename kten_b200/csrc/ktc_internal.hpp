@@ -43,8 +43,11 @@ struct Device {
     int64_t n_alloc_calls = 0, n_pool_hits = 0;
     // misc device-side scratch owned by the runtime
     void* l2_flush = nullptr; size_t l2_flush_bytes = 0;
-    int* err_flag = nullptr;          // device int, set by kernels that validate indices
+    int* err_flag = nullptr;          // device int: status slot of kernels that report at once (NaN search, bounded wait)
     int* wait_flag = nullptr;         // device int nothing ever sets (bounded-wait test hook)
+    int* idx_err = nullptr;           // device int, set by kernels that meet an invalid index (gather / scatter / index ops)
+    bool idx_pending = false;         // an index check is outstanding: read at the next call that waits for the stream
+    char idx_what[96] = {0};          // the last call that may have set it, for the message
 };
 
 struct BufRec {
@@ -73,7 +76,9 @@ int pool_alloc(Device* d, int64_t n_floats, float** ptr, size_t* rounded);
 void pool_free(Device* d, void* ptr, size_t rounded);
 int check_cuda(cudaError_t e, const char* what);
 void count_launch(int n = 1);
-int tune(const char* key, int dflt);     // integer tunables (env KTC_<KEY> or ktc_tune_set)
+int tune(const char* key, int dflt);     // integer tunables (env KTC_<KEY> or ktc_tune_set); `key` must be a string literal
+int take_index_error(Device* d, const char* what, int64_t axis_len, int axis);   // after a kernel that validates indices
+int check_deferred_index_error(Device* d);                                       // after the stream has been waited for
 
 #define KTC_CUDA(call) do { int _s = ::ktc::check_cuda((call), #call); if (_s != KTC_OK) return _s; } while (0)
 #define KTC_TRY(call) do { int _s = (call); if (_s != KTC_OK) return _s; } while (0)

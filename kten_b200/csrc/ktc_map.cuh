@@ -29,7 +29,7 @@ template <class F> __device__ __forceinline__ float4 apply2(const F& f, float4 a
 constexpr int kMapThreads = 256;
 
 template <int U, class F>
-__global__ void __launch_bounds__(kMapThreads) k_map1_vec(const float4* __restrict__ a, float4* __restrict__ out, int64_t n4, F f) {
+__global__ void __launch_bounds__(kMapThreads) k_map1_vec(const float4* a, float4* out, int64_t n4, F f) {     // out may be a (in-place forms): no __restrict__
     const int64_t base = (int64_t)blockIdx.x * (kMapThreads * U) + threadIdx.x;
     const float4* pa = a + base;
     float4* po = out + base;
@@ -50,8 +50,7 @@ template <class F> struct MapMinBlocks { static constexpr int value = 1; };
 template <> struct MapMinBlocks<BinOp<KTC_POW>> { static constexpr int value = 4; };
 
 template <int U, class F>
-__global__ void __launch_bounds__(kMapThreads, MapMinBlocks<F>::value) k_map2_vec(const float4* __restrict__ a, const float4* __restrict__ b,
-                                                          float4* __restrict__ out, int64_t n4, F f) {
+__global__ void __launch_bounds__(kMapThreads, MapMinBlocks<F>::value) k_map2_vec(const float4* a, const float4* b, float4* out, int64_t n4, F f) {     // out may be a
     const int64_t base = (int64_t)blockIdx.x * (kMapThreads * U) + threadIdx.x;
     const float4* pa = a + base;
     const float4* pb = b + base;
@@ -67,13 +66,14 @@ __global__ void __launch_bounds__(kMapThreads, MapMinBlocks<F>::value) k_map2_ve
     }
 }
 
+// the in-place forms call these with out == a: no __restrict__, no read-only loads
 template <class F>
-__global__ void k_map1_scalar(const float* __restrict__ a, float* __restrict__ out, int64_t n, F f) {
+__global__ void k_map1_scalar(const float* a, float* out, int64_t n, F f) {
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
         out[i] = f(a[i]);
 }
 template <class F>
-__global__ void k_map2_scalar(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out, int64_t n, F f) {
+__global__ void k_map2_scalar(const float* a, const float* b, float* out, int64_t n, F f) {
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
         out[i] = f(a[i], b[i]);
 }

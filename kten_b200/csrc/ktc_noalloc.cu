@@ -22,9 +22,12 @@
 //  * The scratch array is shared by every call on a device and keeps whatever
 //    the previous call left there.  Each call overwrites exactly the slots it
 //    later reads, so nothing has to be cleared -- but two calls that overlap on
-//    the same GPU (different host threads driving different streams) would
-//    race on it.  The library issues the call on the device's one compute
-//    stream, which serialises them; callers must not defeat that.
+//    the same GPU would race on it.  A call is two launches on the device's
+//    one compute stream; a per-device lock is held across the pair, so calls
+//    from several host threads cannot interleave their launches (partial A,
+//    partial B, final A would add B's partials).  Work that reaches the GPU
+//    by other routes -- another process, another library's stream -- is not
+//    covered: such callers serialise their calls themselves.
 //  * The first call on a device looks up the device address of the array
 //    (cudaGetSymbolAddress).  Make that first call before starting any stream
 //    capture.
@@ -107,6 +110,7 @@ __global__ void __launch_bounds__(kNoallocThreads) k_noalloc_final(const double*
 
 // device address of the scratch array, looked up once per device
 static std::mutex g_sym_mu;
+static std::mutex g_call_mu[64];           // held across the two launches of a call
 static double* g_sym_ptr[64] = {nullptr};
 
 static int scratch_for(Device* d, double** out) {
@@ -155,6 +159,7 @@ extern "C" int ktc_reduce_all_noalloc(int op, ktc_buf out, ktc_buf in, int64_t n
     if (blocks < 1) blocks = 1;
     if (blocks > kNoallocMaxPartials) return fail(KTC_EINVAL, "ktc_reduce_all_noalloc: internal segment count exceeds the scratch array");
     const int vec_ok = aligned16(bi.ptr) ? 1 : 0;
+    std::lock_guard<std::mutex> pair_lock(g_call_mu[d->id]);           // the two launches enter the stream back to back
     k_noalloc_partial<<<(int)blocks, kNoallocThreads, 0, d->stream>>>(bi.ptr, n, seg, partials, vec_ok);
     k_noalloc_final<<<1, kNoallocThreads, 0, d->stream>>>(partials, (int)blocks, bo.ptr, op == KTC_MEAN ? 1 : 0, (double)n);
     count_launch(2);

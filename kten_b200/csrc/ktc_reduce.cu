@@ -413,16 +413,9 @@ int launch_scatter_axis(Device* d, float* target, const float* index, const floa
     if (n == 0) return KTC_OK;
     int64_t blocks = (n + 255) / 256; const int64_t cap = (int64_t)d->sm_count * 16;
     if (blocks > cap) blocks = cap;
-    k_scatter_axis<<<(int)blocks, 256, 0, d->stream>>>(target, index, src, outer, A, inner, d->err_flag);
+    k_scatter_axis<<<(int)blocks, 256, 0, d->stream>>>(target, index, src, outer, A, inner, d->idx_err);
     KTC_TRY(finish_launch("scatter_axis"));
-    int h = 0;
-    KTC_CUDA(cudaMemcpyAsync(&h, d->err_flag, sizeof(int), cudaMemcpyDeviceToHost, d->stream));
-    KTC_CUDA(cudaStreamSynchronize(d->stream));
-    if (h != 0) {
-        KTC_CUDA(cudaMemsetAsync(d->err_flag, 0, sizeof(int), d->stream));
-        return fail(KTC_EINVAL, "Scatter got invalid index, an index value is out of bounds 0 and %lld", (long long)A);
-    }
-    return KTC_OK;
+    return take_index_error(d, "Scatter", A, 1);       // read where the host next waits for the stream (or at once: index_check_sync)
 }
 
 }  // namespace ktc

@@ -45,19 +45,65 @@ int check_cuda(cudaError_t e, const char* what) {
 
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
+// Tunables are read on every launch.  Keys are string literals, so a small table keyed by the literal's address
+// answers without a lock or a string; it is rebuilt after ktc_tune_set (a version number says so).
+namespace {
+struct TuneSlot { std::atomic<const char*> key{nullptr}; std::atomic<int> value{0}; std::atomic<uint32_t> version{0}; };
+TuneSlot g_tune_fast[64];
+std::atomic<uint32_t> g_tune_version{1};
+}
+
 int tune(const char* key, int dflt) {
+    const uint32_t ver = g_tune_version.load(std::memory_order_acquire);
+    const size_t h = (reinterpret_cast<uintptr_t>(key) >> 3) & 63;
+    TuneSlot& slot = g_tune_fast[h];
+    if (slot.version.load(std::memory_order_acquire) == ver) {                   // read, then make sure nobody rewrote the slot meanwhile
+        const char* k = slot.key.load(std::memory_order_acquire);
+        const int v = slot.value.load(std::memory_order_acquire);
+        if (k == key && slot.version.load(std::memory_order_acquire) == ver) return v;
+    }
+    int val;
     {
         std::lock_guard<std::mutex> lk(g_tune_mu);
         auto it = g_tune.find(key);
-        if (it != g_tune.end()) return it->second;
+        if (it != g_tune.end()) {
+            val = it->second;
+        } else {
+            std::string env = std::string("KTC_") + key;
+            for (auto& c : env) c = (char)toupper((unsigned char)c);
+            const char* v = getenv(env.c_str());
+            val = v ? atoi(v) : dflt;
+            g_tune[key] = val;
+        }
+        slot.version.store(0, std::memory_order_release);      // readers skip the slot while it changes
+        slot.value.store(val, std::memory_order_relaxed);
+        slot.key.store(key, std::memory_order_release);
+        slot.version.store(ver, std::memory_order_release);
     }
-    std::string env = std::string("KTC_") + key;
-    for (auto& c : env) c = (char)toupper((unsigned char)c);
-    const char* v = getenv(env.c_str());
-    int val = v ? atoi(v) : dflt;
-    std::lock_guard<std::mutex> lk(g_tune_mu);
-    g_tune[key] = val;
     return val;
+}
+
+// The index checks of gather / scatter / index-select / index-add kernels (they record an invalid index in a device
+// word and skip the access) are read where the host waits for the stream anyway: ktc_sync and blocking copies.  With the
+// tunable `index_check_sync` = 1 every such call waits and reports at once, as the reference throws at the call
+// (JVMRawTensor.kt:334-353).
+int take_index_error(Device* d, const char* what, int64_t axis_len, int axis) {
+    snprintf(d->idx_what, sizeof(d->idx_what), "%s (axis %d of extent %lld)", what, axis, (long long)axis_len);
+    d->idx_pending = true;
+    if (!tune("index_check_sync", 0)) return KTC_OK;
+    KTC_CUDA(cudaStreamSynchronize(d->stream));
+    return check_deferred_index_error(d);
+}
+
+int check_deferred_index_error(Device* d) {
+    if (!d->idx_pending) return KTC_OK;
+    d->idx_pending = false;
+    int h = 0;
+    KTC_CUDA(cudaMemcpy(&h, d->idx_err, sizeof(int), cudaMemcpyDeviceToHost));
+    if (h == 0) return KTC_OK;
+    KTC_CUDA(cudaMemset(d->idx_err, 0, sizeof(int)));
+    return fail(KTC_EINVAL, "%s got invalid index, index value is out of bounds (the access was skipped; with index_check_sync = 0 the call that "
+                            "reports this is the first one that waits for the device after it)", d->idx_what);
 }
 
 Device* device(int dev) {
@@ -77,9 +123,10 @@ int use_device(Device* d) {
             for (int i = 0; i < Device::kEventRing; ++i) KTC_CUDA(cudaEventCreateWithFlags(&d->ring[i], cudaEventDisableTiming));
             KTC_CUDA(cudaEventCreate(&d->ev_start));
             KTC_CUDA(cudaEventCreate(&d->ev_stop));
-            KTC_CUDA(cudaMalloc(&d->err_flag, 2 * sizeof(int)));
-            KTC_CUDA(cudaMemset(d->err_flag, 0, 2 * sizeof(int)));
+            KTC_CUDA(cudaMalloc(&d->err_flag, 3 * sizeof(int)));
+            KTC_CUDA(cudaMemset(d->err_flag, 0, 3 * sizeof(int)));
             d->wait_flag = d->err_flag + 1;
+            d->idx_err = d->err_flag + 2;
             d->ready = true;
         }
     }
@@ -304,7 +351,9 @@ int ktc_pool_stats(int dev, int64_t* live, int64_t* cached, int64_t* n_alloc, in
 int ktc_pool_trim(int dev) {
     Device* d = device(dev); if (!d) return KTC_ESTATE;
     KTC_TRY(use_device(d));
-    KTC_CUDA(cudaStreamSynchronize(d->stream));   // cached blocks may still be read by queued work
+    KTC_CUDA(cudaStreamSynchronize(d->stream));   // cached blocks may still be read by queued work ...
+    KTC_CUDA(cudaStreamSynchronize(d->stream_up));     // ... and by overlapped copies on the two copy streams
+    KTC_CUDA(cudaStreamSynchronize(d->stream_down));
     std::lock_guard<std::mutex> lk(d->pool_mu);
     trim_locked(d);
     return KTC_OK;
@@ -394,7 +443,7 @@ int ktc_d2h(float* dst, ktc_buf src, int64_t src_off, int64_t n, int mode) {
     Device* d = device(b.dev); if (!d) return KTC_ESTATE; KTC_TRY(use_device(d));
     if (mode >= KTC_COPY_OVERLAP) return overlapped_copy(d, d->stream_down, dst, b.ptr + src_off, (size_t)n * 4, cudaMemcpyDeviceToHost, mode == KTC_COPY_OVERLAP);
     KTC_CUDA(cudaMemcpyAsync(dst, b.ptr + src_off, (size_t)n * 4, cudaMemcpyDeviceToHost, d->stream));
-    if (mode == KTC_COPY_SYNC) KTC_CUDA(cudaStreamSynchronize(d->stream));
+    if (mode == KTC_COPY_SYNC) { KTC_CUDA(cudaStreamSynchronize(d->stream)); return check_deferred_index_error(d); }
     return KTC_OK;
 }
 
@@ -420,7 +469,7 @@ int ktc_sync(int dev) {
     KTC_CUDA(cudaStreamSynchronize(d->stream));
     KTC_CUDA(cudaStreamSynchronize(d->stream_up));
     KTC_CUDA(cudaStreamSynchronize(d->stream_down));
-    return KTC_OK;
+    return check_deferred_index_error(d);
 }
 
 int ktc_copy_fence(int dev) {
@@ -470,6 +519,7 @@ int ktc_tune_set(const char* key, int value) {
     if (!key) return fail(KTC_EINVAL, "ktc_tune_set: key is null");
     std::lock_guard<std::mutex> lk(g_tune_mu);
     g_tune[key] = value;
+    g_tune_version.fetch_add(1, std::memory_order_acq_rel);        // the per-literal table is stale now
     return KTC_OK;
 }
 

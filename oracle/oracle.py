@@ -116,14 +116,16 @@ def broadcast_to(a, shape_a: Sequence[int], target: Sequence[int]) -> np.ndarray
     return out
 
 
-def binary(op: int, a, shape_a, b, shape_b):
-    """elementwiseOpOnTensors: returns (flat result, common shape)."""
+def binary(op: int, a, shape_a, b, shape_b, tuned: bool = False):
+    """elementwiseOpOnTensors: returns (flat result, common shape).  `tuned`: the same values without the
+    reference's materialised broadcast operands and on all host threads (host upper bound only)."""
     a, b = _flat(a), _flat(b)
     cs = common_shape(shape_a, shape_b)
     out = np.empty(volume(cs), dtype=np.float32)
     sa, na = _s(shape_a)
     sb, nb = _s(shape_b)
-    _ok(lib().kto_binary_bcast(op, _f(a), sa, na, _f(b), sb, nb, _f(out)), "binary")
+    fn = lib().kto_binary_bcast_tuned if tuned else lib().kto_binary_bcast
+    _ok(fn(op, _f(a), sa, na, _f(b), sb, nb, _f(out)), "binary")
     return out, cs
 
 

@@ -32,3 +32,14 @@ def gc_scope(cuda_ops):
     (backend/kten-opencl/src/test/.../OpenCLTensorTests.kt:37-46)."""
     with cuda_ops.garbageCollector() as scope:
         yield scope
+
+
+@pytest.fixture()
+def index_checks_at_call(cuda_ops):
+    """The reference throws on an invalid index at the call (JVMRawTensor.kt:334-353); the library reads its index
+    checks where the host next waits for the device unless `index_check_sync` is set.  Tests that expect the exception at
+    the call switch it on."""
+    from kten_b200 import _lib as L
+    L.check(cuda_ops.lib.ktc_tune_set(b"index_check_sync", 1))
+    yield
+    L.check(cuda_ops.lib.ktc_tune_set(b"index_check_sync", 0))

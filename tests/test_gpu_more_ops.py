@@ -171,7 +171,7 @@ def index_tensor(ops_list, shape, extent, seed):
     return [o.createRaw(shape, idx) for o in ops_list]
 
 
-def test_gather_scatter_index_ops(cuda_ops, gc_scope):
+def test_gather_scatter_index_ops(cuda_ops, gc_scope, index_checks_at_call):
     both = (cuda_ops, ORACLE)
     shape = [6, 9, 10]
     g, o = pair(both, shape, 71)
@@ -211,7 +211,7 @@ def test_gather_scatter_index_ops(cuda_ops, gc_scope):
 
 
 @pytest.mark.parametrize("shape,idx_cols", [([37, 2048], 2048), ([5, 1027], 3001), ([3, 4, 4096], 512), ([2, 40960], 8)])
-def test_gather_along_the_last_axis_with_long_rows(cuda_ops, gc_scope, shape, idx_cols):
+def test_gather_along_the_last_axis_with_long_rows(cuda_ops, gc_scope, shape, idx_cols, index_checks_at_call):
     """Rows of 4 KB and more are staged in shared memory by one CTA each; same results as the generic kernel."""
     both = (cuda_ops, ORACLE)
     g, o = pair(both, shape, 111)
@@ -230,7 +230,7 @@ def test_gather_along_the_last_axis_with_long_rows(cuda_ops, gc_scope, shape, id
 
 
 @pytest.mark.parametrize("n_idx,rows,inner,outer", [(5000, 300, 16, 3), (5000, 300, 5, 1), (3000, 4000, 8, 2), (2000, 3, 64, 1), (70, 70, 4, 1)])
-def test_index_add_many_indices_keeps_the_sequential_order(cuda_ops, gc_scope, n_idx, rows, inner, outer):
+def test_index_add_many_indices_keeps_the_sequential_order(cuda_ops, gc_scope, n_idx, rows, inner, outer, index_checks_at_call):
     """Many (repeated) indices: the grouped kernels must add in index-position order, bit for bit like the
     reference's sequential loop; (2000, 3, ...) has lists beyond the grouping limit and takes the per-column walk."""
     both = (cuda_ops, ORACLE)
@@ -285,3 +285,18 @@ def test_softmax_cross_entropy_matches_oracle(cuda_ops, gc_scope, deferred, rows
     want_loss, want_grad, _, _ = softmax_cross_entropy_property(ORACLE, rows=rows)
     assert abs(float(loss[0]) - float(want_loss[0])) <= 2e-6
     assert float(np.abs(grad.astype(np.float64) - want_grad.astype(np.float64)).max()) <= 1e-8
+
+
+def test_index_checks_are_read_where_the_host_waits(cuda_ops, gc_scope):
+    """Without `index_check_sync` a gather with an invalid index does not stall the host: the kernel skips the access and
+    records it, the call returns, and the next call that waits for the device (a blocking read, ktc_sync) reports it --
+    once -- after which the device works as before."""
+    x = cuda_ops.createRaw([4, 8], np.arange(32, dtype=np.float32))
+    bad = cuda_ops.createRaw([4, 2], np.array([0, 1, 2, 8, 4, 5, 6, 7], dtype=np.float32))
+    res = x.gather(1, bad)                                         # returns: nothing waited
+    with pytest.raises(ValueError, match="invalid index"):
+        cuda_ops.synchronize()
+    cuda_ops.synchronize()                                         # reported once
+    assert res.toArray().shape == (4, 2)                           # what the faulty call wrote is unspecified, reading it is safe
+    good = cuda_ops.createRaw([4, 2], np.array([0, 1, 2, 3, 4, 5, 6, 7], dtype=np.float32))
+    assert x.gather(1, good).toArray().reshape(-1).tolist() == [0, 1, 10, 11, 20, 21, 30, 31]

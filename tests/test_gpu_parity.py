@@ -326,7 +326,7 @@ def test_may_unexpand_chain_equals_fused(cuda_ops, gc_scope):
     assert chain.shape == fused.shape == old and same_bits(chain.toArray(), fused.toArray())
 
 
-def test_scatter_axis_rejects_bad_index(cuda_ops, gc_scope):
+def test_scatter_axis_rejects_bad_index(cuda_ops, gc_scope, index_checks_at_call):
     t = cuda_ops.createRawFill([2, 3], 0.0)
     src = cuda_ops.createRaw([2, 1], [5.0, 6.0])
     t.inplaceScatter(1, cuda_ops.createRaw([2, 1], [2.0, 0.0]), src)
