@@ -35,6 +35,41 @@ class CUDATensorOperations(override val platformKey: String, val device: Int) : 
 
     private val collector = ThreadLocal<MutableList<CUDARawTensor>?>()
 
+    /**
+     * Deferred mode: elementwise calls and sums on raw tensors are recorded by the library's expression recorder
+     * (ktc_lazy_*) instead of running at once; the recorder fuses them into one kernel per iteration space when a
+     * value is needed.  Results equal the call-by-call results bit for bit (sums: up to summation order).
+     */
+    var lazy = false
+    var deferSums = true
+        set(value) { field = value; setRecorderOption("defer_sums", if (value) 1 else 0) }
+
+    /** buffers with a recorded `+= pending sum` update; may hold stale entries (the recorder runs updates on its own too) */
+    internal val pendingTargets = HashSet<Long>()
+
+    internal fun runPending() {
+        pendingTargets.clear()
+        check(KtcNative.lazyRunPending.invokeExact() as Int)
+    }
+
+    /** before `handle` is written by a call the recorder does not see */
+    internal fun flush(handle: Long) {
+        pendingTargets.remove(handle)
+        check(KtcNative.lazyFlush.invokeExact(handle) as Int)
+    }
+
+    fun setRecorderOption(name: String, value: Int) = Arena.ofConfined().use { arena ->
+        check(KtcNative.lazyOption.invokeExact(arena.allocateFrom(name), value) as Int)
+    }
+
+    /** Sum raw tensors over the ranks of a peer-memory communicator, in place; pending work runs first and takes the exchange along. */
+    fun allreduceSum(comm: Long, tensors: List<CUDARawTensor>) = Arena.ofConfined().use { arena ->
+        val cells = arena.allocate(JAVA_LONG, tensors.size.toLong())
+        tensors.forEachIndexed { i, t -> cells.setAtIndex(JAVA_LONG, i.toLong(), t.cell(applyUpdates = false)) }
+        check(KtcNative.lazyAllreduce.invokeExact(comm, cells, tensors.size) as Int)
+        pendingTargets.clear()
+    }
+
     internal fun instanceCreated(raw: CUDARawTensor) {
         collector.get()?.add(raw)
     }
@@ -69,7 +104,7 @@ class CUDATensorOperations(override val platformKey: String, val device: Int) : 
         if (data.isEmpty()) return
         Arena.ofConfined().use { arena ->
             val host = arena.allocateFrom(JAVA_FLOAT, *data)
-            check(KtcNative.h2d.invokeExact(raw.storeReference.handle, 0L, host, data.size.toLong(), 1) as Int)
+            check(KtcNative.h2d.invokeExact(raw.bufferForWrite(), 0L, host, data.size.toLong(), 1) as Int)
         }
     }
 

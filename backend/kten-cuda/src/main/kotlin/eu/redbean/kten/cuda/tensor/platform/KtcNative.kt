@@ -85,6 +85,29 @@ internal object KtcNative {
         ADDRESS, JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_INT)
     val exprEvalMulti = handle("ktc_expr_eval_multi", JAVA_INT, ADDRESS, JAVA_INT, ADDRESS, JAVA_INT, ADDRESS, JAVA_INT, ADDRESS, ADDRESS, JAVA_INT,
         ADDRESS, JAVA_INT, ADDRESS, ADDRESS, ADDRESS, JAVA_INT)
+    val exprEvalMultiFused = handle("ktc_expr_eval_multi_fused", JAVA_INT, ADDRESS, JAVA_INT, ADDRESS, JAVA_INT, ADDRESS, JAVA_INT, ADDRESS, ADDRESS, JAVA_INT,
+        ADDRESS, JAVA_INT, ADDRESS, ADDRESS, ADDRESS, JAVA_INT, ADDRESS, JAVA_LONG, ADDRESS, ADDRESS, JAVA_INT)
+    // the deferred-expression recorder: elementwise calls and sums are recorded below the C ABI and run fused when a value is needed
+    const val EXPR_SUM_ALL = 1; const val EXPR_SUM_ROWS = 2; const val EXPR_SUM_LAST = 4
+    const val ASSIGN_WRITTEN = 0; const val ASSIGN_PENDING = 1; const val ASSIGN_UPDATE_RECORDED = 2
+    val lazyLeaf = handle("ktc_lazy_leaf", JAVA_INT, JAVA_LONG, ADDRESS, JAVA_INT, ADDRESS)
+    val lazyFree = handle("ktc_lazy_free", JAVA_INT, JAVA_LONG)
+    val lazyUnary = handle("ktc_lazy_unary", JAVA_INT, JAVA_INT, JAVA_LONG, ADDRESS)
+    val lazyBinary = handle("ktc_lazy_binary", JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_LONG, ADDRESS)
+    val lazyScalar = handle("ktc_lazy_scalar", JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_FLOAT, JAVA_INT, ADDRESS)
+    val lazyClamp = handle("ktc_lazy_clamp", JAVA_INT, JAVA_LONG, JAVA_FLOAT, JAVA_FLOAT, ADDRESS)
+    val lazyCompareScalar = handle("ktc_lazy_compare_scalar", JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_FLOAT, ADDRESS)
+    val lazyBroadcastTo = handle("ktc_lazy_broadcast_to", JAVA_INT, JAVA_LONG, ADDRESS, JAVA_INT, ADDRESS)
+    val lazyAssignBinary = handle("ktc_lazy_assign_binary", JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_LONG, ADDRESS)
+    val lazyAssignScalar = handle("ktc_lazy_assign_scalar", JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_FLOAT, ADDRESS)
+    val lazySum = handle("ktc_lazy_sum", JAVA_INT, JAVA_LONG, JAVA_INT, JAVA_INT, ADDRESS, JAVA_INT, ADDRESS)
+    val lazyBuffer = handle("ktc_lazy_buffer", JAVA_INT, JAVA_LONG, ADDRESS)
+    val lazyInfo = handle("ktc_lazy_info", JAVA_INT, JAVA_LONG, ADDRESS, ADDRESS, ADDRESS, ADDRESS)
+    val lazyFlush = handle("ktc_lazy_flush", JAVA_INT, JAVA_LONG)
+    val lazyRunPending = handle("ktc_lazy_run_pending", JAVA_INT)
+    val lazyAllreduce = handle("ktc_lazy_allreduce", JAVA_INT, JAVA_LONG, ADDRESS, JAVA_INT)
+    val lazyOption = handle("ktc_lazy_option", JAVA_INT, ADDRESS, JAVA_INT)
+    val lazyStats = handle("ktc_lazy_stats", JAVA_INT, ADDRESS)
     val refcount = handle("ktc_refcount", JAVA_INT, JAVA_LONG, ADDRESS)
     val indexAdd = handle("ktc_index_add", JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_FLOAT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG)
 
@@ -98,6 +121,13 @@ internal object KtcNative {
             -3 -> throw OutOfMemoryError(message)
             else -> throw RuntimeException("kten-cuda [$status]: $message")
         }
+    }
+
+    /** Calls a recorder entry point whose last argument is the result cell and returns that cell. */
+    fun cell(call: (MemorySegment) -> Int): Long = Arena.ofConfined().use { arena ->
+        val out = arena.allocate(JAVA_LONG)
+        check(call(out))
+        out.get(JAVA_LONG, 0)
     }
 
     fun shape(arena: Arena, shape: List<Int>): MemorySegment {

@@ -22,13 +22,23 @@ import java.lang.foreign.MemorySegment
 import java.lang.foreign.ValueLayout.JAVA_FLOAT
 import java.lang.foreign.ValueLayout.JAVA_INT
 
-/** Device storage: one reference-counted buffer handle of libkten_cuda.so. */
-class CUDABuffer(val handle: Long, val size: Int)
+/**
+ * Storage slot of one or more raw tensors: a reference-counted buffer handle of libkten_cuda.so (one owned reference),
+ * or a cell of the library's expression recorder whose value is still pending, or both (the recorder cell then stands
+ * for the buffer when the tensor is an operand of a recorded call).  Shallow copies of a pending tensor share the slot,
+ * so that they end up sharing storage exactly as in the other backends; every other tensor has a slot of its own.
+ */
+class CUDABuffer(var handle: Long, val size: Int) {
+    var lz = 0L                          // recorder cell, 0: none
+    var lzShape: List<Int>? = null
+    var share = 1
+}
 
 /**
  * RawTensor of the kten-cuda backend: shape on the JVM heap, data in HBM.  Every operation of the
- * float32 hot path is one call through the C ABI; operations outside that path are not provided by
- * the native library yet and throw UnsupportedOperationException.
+ * float32 hot path is one call through the C ABI -- run at once, or, with `ops.lazy`, recorded by the
+ * library's expression recorder and run fused when a value is needed; operations outside that path are not
+ * provided by the native library yet and throw UnsupportedOperationException.
  */
 class CUDARawTensor(
     shape: List<Int>,
@@ -44,11 +54,71 @@ class CUDARawTensor(
         ops.instanceCreated(this)
     }
 
+    /** The buffer handle; a pending value is computed first, a recorded `+= pending sum` update of the buffer applied. */
     private val handle: Long
         get() {
             if (released) throw IllegalStateException("Raw tensor already released")
-            return storeReference.handle
+            val slot = storeReference
+            if (slot.handle == 0L) {
+                slot.handle = KtcNative.cell { out -> KtcNative.lazyBuffer.invokeExact(slot.lz, out) as Int }     // one reference for this slot
+            } else if (ops.pendingTargets.isNotEmpty() && slot.handle in ops.pendingTargets) ops.runPending()
+            return slot.handle
         }
+
+    /** The handle of a buffer that is about to be written by a call the recorder does not see. */
+    internal fun bufferForWrite(): Long {
+        val h = handle
+        ops.flush(h)
+        return h
+    }
+
+    /** This tensor as an operand of a recorded call: its recorder cell (a stored tensor gets one over its buffer). */
+    internal fun cell(applyUpdates: Boolean = true): Long {
+        if (released) throw IllegalStateException("Raw tensor already released")
+        val slot = storeReference
+        if (slot.handle == 0L) return slot.lz
+        if (applyUpdates && ops.pendingTargets.isNotEmpty() && slot.handle in ops.pendingTargets) ops.runPending()
+        if (slot.lz == 0L || slot.lzShape != shape) {
+            if (slot.lz != 0L) check(KtcNative.lazyFree.invokeExact(slot.lz) as Int)
+            slot.lz = Arena.ofConfined().use { arena ->
+                KtcNative.cell { out -> KtcNative.lazyLeaf.invokeExact(slot.handle, KtcNative.shape(arena, shape), shape.size, out) as Int }
+            }
+            slot.lzShape = shape
+        }
+        return slot.lz
+    }
+
+    private val isDeferred: Boolean
+        get() {
+            val slot = storeReference
+            if (slot.handle != 0L || slot.lz == 0L) return false
+            return Arena.ofConfined().use { arena ->
+                val pending = arena.allocate(JAVA_INT)
+                check(KtcNative.lazyInfo.invokeExact(slot.lz, pending, MemorySegment.NULL, MemorySegment.NULL, MemorySegment.NULL) as Int)
+                pending.get(JAVA_INT, 0) != 0
+            }
+        }
+
+    private fun recorded(shape: List<Int>, cell: Long): CUDARawTensor =
+        CUDARawTensor(shape, CUDABuffer(0L, shape.toStoreSize()).also { it.lz = cell; it.lzShape = shape }, ops)
+
+    /** What an in-place call through the recorder left behind (ktc_lazy_assign_*). */
+    private fun afterAssign(state: Int) {
+        val slot = storeReference
+        when (state) {
+            KtcNative.ASSIGN_PENDING -> if (slot.handle != 0L) {       // the value is pending now; the old buffer belongs to the recorder
+                check(KtcNative.release.invokeExact(slot.handle) as Int)
+                slot.handle = 0L
+            }
+            KtcNative.ASSIGN_UPDATE_RECORDED -> ops.pendingTargets.add(slot.handle)
+        }
+    }
+
+    private fun assignState(call: (MemorySegment) -> Int): Int = Arena.ofConfined().use { arena ->
+        val state = arena.allocate(JAVA_INT)
+        check(call(state))
+        state.get(JAVA_INT, 0)
+    }
 
     private val volume: Long get() = shape.toStoreSize().toLong()
 
@@ -56,7 +126,11 @@ class CUDARawTensor(
         if (released) return false
         if (!mustSurviveGC) refCount--
         if (refCount <= 0) {
-            check(KtcNative.release.invokeExact(storeReference.handle) as Int)
+            val slot = storeReference
+            if (--slot.share <= 0) {
+                if (slot.handle != 0L) check(KtcNative.release.invokeExact(slot.handle) as Int)
+                if (slot.lz != 0L) { check(KtcNative.lazyFree.invokeExact(slot.lz) as Int); slot.lz = 0L }
+            }
             released = true
             return true
         }
@@ -66,6 +140,10 @@ class CUDARawTensor(
     // ---- elementwise -------------------------------------------------------------------------------
     private fun binary(op: Int, other: AbstractRawTensor<CUDABuffer>): CUDARawTensor {
         other as CUDARawTensor
+        if (ops.lazy) {
+            val common = if (shape == other.shape) shape else calculateCommonShapeWith(other)
+            return recorded(common, KtcNative.cell { out -> KtcNative.lazyBinary.invokeExact(op, cell(), other.cell(), out) as Int })
+        }
         if (shape == other.shape) {
             val res = ops.createRaw(shape)
             check(KtcNative.binary.invokeExact(op, res.handle, handle, other.handle, volume) as Int)
@@ -82,25 +160,40 @@ class CUDARawTensor(
     private fun binaryAssign(op: Int, other: AbstractRawTensor<CUDABuffer>) {
         if (shape != other.shape)
             throw IllegalArgumentException("Shapes does not match for inplace operation on tensors with shapes: $shape and ${other.shape}.")
-        check(KtcNative.binaryInplace.invokeExact(op, handle, (other as CUDARawTensor).handle, volume) as Int)
+        other as CUDARawTensor
+        if (ops.lazy) {
+            afterAssign(assignState { state -> KtcNative.lazyAssignBinary.invokeExact(op, cell(), other.cell(), state) as Int })
+            return
+        }
+        check(KtcNative.binaryInplace.invokeExact(op, bufferForWrite(), other.handle, volume) as Int)
     }
 
     internal fun scalar(op: Int, constant: Float, scalarFirst: Boolean = false): CUDARawTensor {
+        if (ops.lazy)
+            return recorded(shape, KtcNative.cell { out -> KtcNative.lazyScalar.invokeExact(op, cell(), constant, if (scalarFirst) 1 else 0, out) as Int })
         val res = ops.createRaw(shape)
         check(KtcNative.scalar.invokeExact(op, res.handle, handle, constant, volume, if (scalarFirst) 1 else 0) as Int)
         return res
     }
 
-    private fun scalarAssign(op: Int, constant: Float) =
-        check(KtcNative.scalarInplace.invokeExact(op, handle, constant, volume) as Int)
+    private fun scalarAssign(op: Int, constant: Float) {
+        if (ops.lazy) {
+            afterAssign(assignState { state -> KtcNative.lazyAssignScalar.invokeExact(op, cell(), constant, state) as Int })
+            return
+        }
+        check(KtcNative.scalarInplace.invokeExact(op, bufferForWrite(), constant, volume) as Int)
+    }
 
     private fun unary(op: Int): CUDARawTensor {
+        if (ops.lazy && op <= KtcNative.NEG)                     // the maps the fused expression kernels implement
+            return recorded(shape, KtcNative.cell { out -> KtcNative.lazyUnary.invokeExact(op, cell(), out) as Int })
         val res = ops.createRaw(shape)
         check(KtcNative.unary.invokeExact(op, res.handle, handle, volume) as Int)
         return res
     }
 
     private fun compare(op: Int, value: Float): CUDARawTensor {
+        if (ops.lazy) return recorded(shape, KtcNative.cell { out -> KtcNative.lazyCompareScalar.invokeExact(op, cell(), value, out) as Int })
         val res = ops.createRaw(shape)
         check(KtcNative.compareScalar.invokeExact(op, res.handle, handle, value, volume) as Int)
         return res
@@ -129,6 +222,7 @@ class CUDARawTensor(
     override fun sigmoid() = unary(KtcNative.SIGMOID)
 
     override fun clamp(min: Float, max: Float): CUDARawTensor {
+        if (ops.lazy) return recorded(shape, KtcNative.cell { out -> KtcNative.lazyClamp.invokeExact(cell(), min, max, out) as Int })
         val res = ops.createRaw(shape)
         check(KtcNative.clamp.invokeExact(res.handle, handle, min, max, volume) as Int)
         return res
@@ -151,17 +245,30 @@ class CUDARawTensor(
             AggregatingOperation.ARG_MAX -> KtcNative.ARGMAX
             AggregatingOperation.ARG_MIN -> KtcNative.ARGMIN
         }
+        // sums of a pending value over the leading or the innermost axis join its expression (resShape keeps the axis as 1)
+        if (op == KtcNative.SUM && shape.size >= 2 && isDeferred) {
+            val kind = if (axis == 0) KtcNative.EXPR_SUM_ROWS else if (axis == shape.size - 1 && shape[axis] > 1 && ops.deferSums) KtcNative.EXPR_SUM_LAST else 0
+            if (kind != 0) return recordedSum(kind, false, resShape)
+        }
         val res = ops.createRaw(resShape)
         check(KtcNative.reduceAxis.invokeExact(op, res.handle, handle, outer, shape[axis].toLong(), inner) as Int)
         return res
     }
 
-    override fun sum(): CUDARawTensor = ops.createRaw(listOf(1)).also {
-        check(KtcNative.reduceAll.invokeExact(KtcNative.SUM, it.handle, handle, volume) as Int)
+    private fun recordedSum(kind: Int, mean: Boolean, resShape: List<Int>): CUDARawTensor = Arena.ofConfined().use { arena ->
+        recorded(resShape, KtcNative.cell { out ->
+            KtcNative.lazySum.invokeExact(cell(), kind, if (mean) 1 else 0, KtcNative.shape(arena, resShape), resShape.size, out) as Int
+        })
     }
 
-    override fun mean(): CUDARawTensor = ops.createRaw(listOf(1)).also {
-        check(KtcNative.reduceAll.invokeExact(KtcNative.MEAN, it.handle, handle, volume) as Int)
+    override fun sum(): CUDARawTensor {
+        if (isDeferred) return recordedSum(KtcNative.EXPR_SUM_ALL, false, listOf(1))
+        return ops.createRaw(listOf(1)).also { check(KtcNative.reduceAll.invokeExact(KtcNative.SUM, it.handle, handle, volume) as Int) }
+    }
+
+    override fun mean(): CUDARawTensor {
+        if (isDeferred) return recordedSum(KtcNative.EXPR_SUM_ALL, true, listOf(1))
+        return ops.createRaw(listOf(1)).also { check(KtcNative.reduceAll.invokeExact(KtcNative.MEAN, it.handle, handle, volume) as Int) }
     }
 
     // one index per position along the axis over the whole target (Max / Min backward): fully parallel kernel;
@@ -172,7 +279,7 @@ class CUDARawTensor(
         if (index.shape[a] == 1 && index.shape == src.shape && offAxis(index.shape) == offAxis(shape)) {
             val outer = shape.take(a).toStoreSize().toLong()
             val inner = shape.drop(a + 1).toStoreSize().toLong()
-            check(KtcNative.scatterAxis.invokeExact(handle, (index as CUDARawTensor).handle, (src as CUDARawTensor).handle,
+            check(KtcNative.scatterAxis.invokeExact(bufferForWrite(), (index as CUDARawTensor).handle, (src as CUDARawTensor).handle,
                                                     outer, shape[a].toLong(), inner) as Int)
         } else scatterNd(KtcNative.SCATTER_SET, a, index as CUDARawTensor, src as CUDARawTensor, 0f)
     }
@@ -185,7 +292,7 @@ class CUDARawTensor(
 
     private fun scatterNd(mode: Int, axis: Int, index: CUDARawTensor, src: CUDARawTensor?, constant: Float) {
         Arena.ofConfined().use { arena ->
-            check(KtcNative.scatterAxisNd.invokeExact(mode, handle, KtcNative.shape(arena, shape), index.handle, KtcNative.shape(arena, index.shape),
+            check(KtcNative.scatterAxisNd.invokeExact(mode, bufferForWrite(), KtcNative.shape(arena, shape), index.handle, KtcNative.shape(arena, index.shape),
                                                       src?.handle ?: 0L, if (src == null) MemorySegment.NULL else KtcNative.shape(arena, src.shape),
                                                       shape.size, axis, constant) as Int)
         }
@@ -195,6 +302,9 @@ class CUDARawTensor(
     override fun broadcastTo(shape: List<Int>): CUDARawTensor {
         if (this.shape == shape) return this
         this.shape.inferExplicitBroadcastShape(shape)
+        if (ops.lazy) return Arena.ofConfined().use { arena ->
+            recorded(shape, KtcNative.cell { out -> KtcNative.lazyBroadcastTo.invokeExact(cell(), KtcNative.shape(arena, shape), shape.size, out) as Int })
+        }
         val res = ops.createRaw(shape)
         Arena.ofConfined().use { arena ->
             check(KtcNative.broadcastTo.invokeExact(res.handle, KtcNative.shape(arena, shape), shape.size,
@@ -205,8 +315,15 @@ class CUDARawTensor(
 
     override fun copy(shallow: Boolean): CUDARawTensor {
         if (shallow) {
+            if (isDeferred) {                                    // aliases share the pending value, later its storage
+                storeReference.share++
+                return CUDARawTensor(shape, storeReference, ops)
+            }
             check(KtcNative.retain.invokeExact(handle) as Int)
-            return CUDARawTensor(shape, storeReference, ops)
+            return CUDARawTensor(shape, CUDABuffer(storeReference.handle, storeReference.size), ops)
+        }
+        if (isDeferred) return Arena.ofConfined().use { arena ->   // pending values are immutable: a deep copy can share one
+            recorded(shape, KtcNative.cell { out -> KtcNative.lazyBroadcastTo.invokeExact(cell(), KtcNative.shape(arena, shape), shape.size, out) as Int })
         }
         val res = ops.createRaw(shape)
         check(KtcNative.d2d.invokeExact(res.handle, 0L, handle, 0L, volume) as Int)
@@ -215,7 +332,7 @@ class CUDARawTensor(
 
     override fun view(shape: List<Int>): CUDARawTensor {
         check(KtcNative.retain.invokeExact(handle) as Int)
-        return CUDARawTensor(this.shape.reshape(shape), storeReference, ops)
+        return CUDARawTensor(this.shape.reshape(shape), CUDABuffer(storeReference.handle, storeReference.size), ops)
     }
 
     override fun getSingleValue(indexes: List<Int>): Float {
@@ -236,7 +353,14 @@ class CUDARawTensor(
         }
     }
 
-    override fun inplaceFill(value: Float) = check(KtcNative.fill.invokeExact(handle, 0L, volume, value) as Int)
+    override fun inplaceFill(value: Float) {
+        val slot = storeReference
+        if (slot.handle == 0L) {                                 // a pending value is overwritten: just take storage
+            if (slot.lz != 0L) { check(KtcNative.lazyFree.invokeExact(slot.lz) as Int); slot.lz = 0L }
+            slot.handle = KtcNative.cell { out -> KtcNative.alloc.invokeExact(ops.device, volume, out) as Int }
+        }
+        check(KtcNative.fill.invokeExact(bufferForWrite(), 0L, volume, value) as Int)
+    }
 
     override fun containsNan(): Boolean = Arena.ofConfined().use { arena ->
         val res = arena.allocate(JAVA_INT)
@@ -333,9 +457,10 @@ class CUDARawTensor(
         if (value != null) {
             if (value.volume != boxShape.toStoreSize().toLong())
                 throw IllegalArgumentException("Cannot set tensor with shape: ${value.shape} to tensor with shape: $shape at index: $indexForMessage")
+            ops.flush(handle)
             copyBox(this, offset, st, value, 0L, strides(boxShape), boxShape)
         } else Arena.ofConfined().use { arena ->
-            check(KtcNative.fillStrided.invokeExact(handle, offset, KtcNative.shape(arena, st), KtcNative.shape(arena, boxShape), boxShape.size, constant) as Int)
+            check(KtcNative.fillStrided.invokeExact(bufferForWrite(), offset, KtcNative.shape(arena, st), KtcNative.shape(arena, boxShape), boxShape.size, constant) as Int)
         }
     }
 
@@ -384,7 +509,7 @@ class CUDARawTensor(
 
     override fun indexAdd(axis: Int, index: AbstractRawTensor<CUDABuffer>, src: AbstractRawTensor<CUDABuffer>, alpha: Float) {
         val a = shape.indexAddCheckShapesNormAxis(axis, index.shape, src.shape)
-        check(KtcNative.indexAdd.invokeExact(handle, (index as CUDARawTensor).handle, (src as CUDARawTensor).handle, alpha,
+        check(KtcNative.indexAdd.invokeExact(bufferForWrite(), (index as CUDARawTensor).handle, (src as CUDARawTensor).handle, alpha,
                                              shape.take(a).toStoreSize().toLong(), shape[a].toLong(), index.shape[0].toLong(),
                                              shape.drop(a + 1).toStoreSize().toLong()) as Int)
     }

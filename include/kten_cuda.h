@@ -188,6 +188,16 @@ KTC_API int ktc_reduce_all(int op, ktc_buf out, ktc_buf in, int64_t n);
 KTC_API int ktc_sum_to_shape(ktc_buf out, const int64_t* old_shape, int old_ndim,
                              ktc_buf in, const int64_t* in_shape, int in_ndim);
 
+/* The forward of SoftmaxCrossEntropy (kten-api/.../functions/nn/SoftmaxCrossEntropy.kt:40-59) in one pass over the
+ * logits [rows, cols]: row maximum, exp of the shifted row, its sum, the quotients -- written to `softmax`, the tensor
+ * the function saves for backward --, their sum, and -log(clamp(softmax[target] / that sum, lo, hi)) per row into
+ * `nll` [rows]; the mean over the rows is ktc_reduce_all(KTC_MEAN) on nll.  Every operation is the reference's, in its
+ * order, and the two row sums accumulate exactly as ktc_reduce_axis does, so both outputs carry the bits of the
+ * eleven separate calls.  targets [rows]: class indices as floats (truncated like Float.toInt); an index outside
+ * [0, cols) is recorded like an invalid gather index and gives a NaN row.  KTC_ENOTSUP (cols > 2048 or <= 64, cols not
+ * a multiple of 4, unaligned rows): issue the separate calls. */
+KTC_API int ktc_softmax_xent_forward(ktc_buf softmax, ktc_buf nll, ktc_buf logits, ktc_buf targets, int64_t rows, int64_t cols, float lo, float hi);
+
 /* Full sum / mean that obtains no memory, for callers that must not allocate
  * while they run: loops whose free device memory is already committed to
  * another allocator, latency-bound sections that cannot take the device-wide
@@ -230,7 +240,9 @@ KTC_API int ktc_reduce_all_noalloc(int op, ktc_buf out, ktc_buf in, int64_t n);
 #define KTC_EXPR_MAX_SINKS 4
 enum { KTC_X_LOAD = 1, KTC_X_CONST, KTC_X_ADD, KTC_X_SUB, KTC_X_MUL, KTC_X_DIV, KTC_X_POW, KTC_X_NEG, KTC_X_RCP,
        KTC_X_SQUARE, KTC_X_EXP, KTC_X_LOG, KTC_X_TANH, KTC_X_SIGMOID, KTC_X_CLAMP, KTC_X_CMP_LT, KTC_X_CMP_LTE,
-       KTC_X_CMP_GT, KTC_X_CMP_GTE, KTC_X_STORE, KTC_X_ACC };
+       KTC_X_CMP_GT, KTC_X_CMP_GTE, KTC_X_STORE, KTC_X_ACC,
+       KTC_X_SCATC };   /* d = (column == (int)b) ? imm[k] : a -- inplaceScatter(-1, index, constant) with one index per row (JVM:317-332):
+                           b is the row's index broadcast over the columns; an index outside the row is recorded, nothing is written */
 enum { KTC_EXPR_STORE_ONLY = 0, KTC_EXPR_SUM_ALL = 1, KTC_EXPR_SUM_ROWS = 2, KTC_EXPR_MULTI = 3, KTC_EXPR_SUM_LAST = 4 };
 KTC_API int ktc_expr_eval(const uint32_t* code, int n_code, const float* imm, int n_imm,
                           const int64_t* shape, int ndim,
@@ -261,17 +273,18 @@ KTC_API int ktc_expr_eval_multi(const uint32_t* code, int n_code, const float* i
                                 const int* sink_kinds, const ktc_buf* sink_outs, const int* means, int n_sinks);
 
 /* ktc_expr_eval_multi with the rest of a training step folded into its second pass (one kernel combines the partial
- * sums of all sinks): add_to[j] != 0 adds sink j's result into that tensor as well -- target = target + result, the
- * float addition of Variable.backwardWithGrad's plusAssign (Variable.kt:44-46) -- and comm != 0 sums the n_x tensors
+ * sums of all sinks): add_to[j] != 0 adds sink j's result into that tensor as well -- add_mode[j] = 1: target = target +
+ * result, the float addition of Variable.backwardWithGrad's plusAssign (Variable.kt:44-46); add_mode[j] = 2: target =
+ * 0f + result, the same call on a gradient that was just zeroed (its old contents are not read) -- and comm != 0 sums the n_x tensors
  * x_bufs (x_counts floats each; typically the sink outputs and the tensors added to) over the ranks of a peer-memory
  * communicator, in place, when the last block of that kernel has finished: the exchange of ktc_p2p_allreduce_sum,
- * without a launch of its own.  add_to may be null; comm 0 ignores x_*. */
+ * without a launch of its own.  add_to / add_mode may be null; comm 0 ignores x_*. */
 KTC_API int ktc_expr_eval_multi_fused(const uint32_t* code, int n_code, const float* imm, int n_imm,
                                       const int64_t* shape, int ndim,
                                       const ktc_buf* leaves, const int64_t* leaf_shapes, int n_leaves,
                                       const ktc_buf* stores, int n_stores,
                                       const int* sink_kinds, const ktc_buf* sink_outs, const int* means, int n_sinks,
-                                      const ktc_buf* add_to, uint64_t comm, const ktc_buf* x_bufs, const int64_t* x_counts, int n_x);
+                                      const ktc_buf* add_to, const int* add_mode, uint64_t comm, const ktc_buf* x_bufs, const int64_t* x_counts, int n_x);
 
 /* For iteration spaces of at least `expr_jit_min_elems` elements (tunable, default 2^20; tunable
  * `expr_jit` = 0 turns it off) ktc_expr_eval does not interpret the program: it generates CUDA
@@ -314,6 +327,16 @@ KTC_API int ktc_expr_jit_log(char* buf, int len);
  *                            ktc_lazy_flush and every recorder call that reads the buffer apply it first).
  *                            The caller is expected to hold exactly one reference of its own on a stored
  *                            target's buffer; the recorder reads "nobody else holds it" off the count.
+ *                            3: the call was `zeroed pending cell += pending sum`: the cell owns a new buffer that
+ *                            receives 0f + sum when the pending sums run (fetch it with ktc_lazy_buffer when needed).
+ *   ktc_lazy_full            a cell whose pending value is `value` everywhere (createRawFill, zerosLike): no buffer, no fill kernel
+ *                            until somebody needs one; constants fold into the programs that use them.
+ *   ktc_lazy_assign_fill     inplaceFill on a cell: a pending cell, or a stored one whose buffer nobody else holds, becomes
+ *                            that pending constant (*state = 1); another stored cell is filled at once (*state = 0).
+ *   ktc_lazy_assign_scatter_const   inplaceScatter(-1, index, constant) with one index per row (the `-1 at the target`
+ *                            of SoftmaxCrossEntropy.doBackward, SoftmaxCrossEntropy.kt:61-67), recorded as an expression
+ *                            instruction; index: a cell of the target's shape with last extent 1.  KTC_ENOTSUP for other
+ *                            index shapes: use ktc_scatter_axis_nd on the buffers.
  *   ktc_lazy_sum             sum() / mean() (KTC_EXPR_SUM_ALL), sum over axis 0 (KTC_EXPR_SUM_ROWS) or over
  *                            the innermost axis (KTC_EXPR_SUM_LAST) of a cell; with option defer_sums the
  *                            sum of a pending cell is pending too, and pending sums over one iteration
@@ -345,6 +368,9 @@ KTC_API int ktc_lazy_compare_scalar(int op, ktc_lazy_cell a, float value, ktc_la
 KTC_API int ktc_lazy_broadcast_to(ktc_lazy_cell a, const int64_t* shape, int ndim, ktc_lazy_cell* out);
 KTC_API int ktc_lazy_assign_binary(int op, ktc_lazy_cell target, ktc_lazy_cell other, int* state);
 KTC_API int ktc_lazy_assign_scalar(int op, ktc_lazy_cell target, float s, int* state);
+KTC_API int ktc_lazy_full(int dev, const int64_t* shape, int ndim, float value, ktc_lazy_cell* out);
+KTC_API int ktc_lazy_assign_fill(ktc_lazy_cell target, float value, int* state);
+KTC_API int ktc_lazy_assign_scatter_const(ktc_lazy_cell target, ktc_lazy_cell index, float value, int* state);
 KTC_API int ktc_lazy_sum(ktc_lazy_cell a, int kind, int mean, const int64_t* res_shape, int res_ndim, ktc_lazy_cell* out);
 KTC_API int ktc_lazy_buffer(ktc_lazy_cell cell, ktc_buf* out);
 KTC_API int ktc_lazy_info(ktc_lazy_cell cell, int* pending, int* is_sum, int64_t* shape, int* ndim);

@@ -1282,6 +1282,17 @@ class SoftmaxCrossEntropy(UnaryTensorFunction):    # functions/nn/SoftmaxCrossEn
     def doForward(self, x):
         ops, eps = self.ops, self.ops.epsilon
         idx = self.targets._forwarded()
+        fused = getattr(x, "softmaxCrossEntropyForward", None)
+        if fused is not None:
+            # a backend may offer the whole forward as one call with the results of the sequence below (the CUDA backend:
+            # one pass over the logits); kten-api would test for the capability the same way
+            res = fused(idx, eps, _f32(1.0 - _f32(eps)))
+            if res is not None:
+                softmax, nll = res
+                self.saveForBackward(softmax)
+                self.output = nll.mean()
+                ops.release(nll)
+                return
         max_val = x.max(-1, keepDimensions=True)
         shifted = x.minus(max_val)
         exp_val = shifted.exp()

@@ -137,6 +137,7 @@ public:
         Cell& c = *cell;
         if (state == 1) { if (c.store) { check(ktc_release(c.store)); c.store = 0; } }
         else if (state == 2) ops->pending_targets.push_back(c.store);
+        // state 3: the recorder gave the pending cell a buffer that receives 0f + sum; nothing to do here
     }
     void before_inplace_write() { if (cell->store) check(ktc_lazy_flush(cell->store)); }
 
@@ -203,6 +204,12 @@ public:
         return res;
     }
     void inplaceFill(float v) {
+        if (ops->lazy && (cell->store || cell->lz)) {              // recorded: a pending constant where nobody else holds the buffer
+            int st = 0;
+            check(ktc_lazy_assign_fill(lz(), v, &st));
+            after_assign(st);
+            return;
+        }
         if (isDeferred() || !cell->store) {                     // the pending value is overwritten: just take storage
             if (cell->lz) { ktc_lazy_free(cell->lz); cell->lz = 0; }
             check(ktc_alloc(ops->device, size(), &cell->store));
@@ -252,7 +259,14 @@ RawP Ops::create(const Shape& shape) {
     check(ktc_alloc(device, volume(shape), &c->store));
     return Raw::make(this, shape, c);
 }
-RawP Ops::create_fill(const Shape& shape, float v) { RawP r = create(shape); r->inplaceFill(v); return r; }
+RawP Ops::create_fill(const Shape& shape, float v) {
+    if (lazy) {                                                 // a pending constant: no buffer, no fill kernel
+        ktc_lazy_cell out;
+        check(ktc_lazy_full(device, shape.data(), (int)shape.size(), v, &out));
+        return Raw::recorded(this, shape, out);
+    }
+    RawP r = create(shape); r->inplaceFill(v); return r;
+}
 
 // Broadcast-gradient sum-to-shape (Utils.kt:14-41): leading axes are summed away, then every remaining axis whose
 // extent differs is summed with the dimension kept; intermediates are released.

@@ -113,6 +113,14 @@ __global__ void __launch_bounds__(256) k_expr(const __grid_constant__ ExprArgs p
                 case KTC_X_CMP_LTE: { const float t = p.imm[k]; v = KTC_EACH(x.x <= t ? 1.f : 0.f, x.y <= t ? 1.f : 0.f, x.z <= t ? 1.f : 0.f, x.w <= t ? 1.f : 0.f); break; }
                 case KTC_X_CMP_GT: { const float t = p.imm[k]; v = KTC_EACH(x.x > t ? 1.f : 0.f, x.y > t ? 1.f : 0.f, x.z > t ? 1.f : 0.f, x.w > t ? 1.f : 0.f); break; }
                 case KTC_X_CMP_GTE: { const float t = p.imm[k]; v = KTC_EACH(x.x >= t ? 1.f : 0.f, x.y >= t ? 1.f : 0.f, x.z >= t ? 1.f : 0.f, x.w >= t ? 1.f : 0.f); break; }
+                case KTC_X_SCATC: {
+                    const int t = (int)y.x;                        // Float.toInt(): truncation; y holds the row's index in every column
+                    if ((unsigned)t >= (unsigned)p.D2) *p.err = 1;
+                    const float c = p.imm[k];
+                    const int c0 = (int)col;
+                    v = make_float4(c0 == t ? c : x.x, c0 + 1 == t ? c : x.y, c0 + 2 == t ? c : x.z, c0 + 3 == t ? c : x.w);
+                    break;
+                }
                 case KTC_X_STORE:
                     __stcs(reinterpret_cast<float4*>(p.store[k] + r * p.D2 + col), x);
                     continue;
@@ -182,6 +190,7 @@ struct CombineArgs {
     const double* part[kExprMaxSinks];
     float* out[kExprMaxSinks];
     float* add_to[kExprMaxSinks];          // nullptr: none
+    int add_mode[kExprMaxSinks];           // 1: target += result; 2: target = 0f + result (a gradient that was just zeroed)
     int64_t n_out[kExprMaxSinks];
     int S[kExprMaxSinks];                  // partials per output
     double divisor[kExprMaxSinks];         // > 0: mean
@@ -194,7 +203,7 @@ __device__ unsigned int g_combine_tickets;  // blocks of the running k_combine_m
 __device__ __forceinline__ void combine_put(const CombineArgs& a, int j, int64_t o, double sum) {
     const float v = (float)(a.divisor[j] > 0.0 ? sum / a.divisor[j] : sum);
     a.out[j][o] = v;
-    if (a.add_to[j]) a.add_to[j][o] = __fadd_rn(a.add_to[j][o], v);
+    if (a.add_to[j]) a.add_to[j][o] = __fadd_rn(a.add_mode[j] == 2 ? 0.f : a.add_to[j][o], v);
 }
 
 __global__ void __launch_bounds__(256) k_combine_multi(const __grid_constant__ CombineArgs a) {
@@ -280,13 +289,13 @@ using namespace ktc;
 
 // sink == KTC_EXPR_MULTI: n_sinks sums described by sink_kinds / sink_outs / means; otherwise the single
 // sink (sink, sink_out, mean).
-static int expr_eval(const uint32_t* code, int n_code, const float* imm, int n_imm,
+static int expr_eval_impl(Device** scatc_dev, const uint32_t* code, int n_code, const float* imm, int n_imm,
                      const int64_t* shape, int ndim,
                      const ktc_buf* leaves, const int64_t* leaf_shapes, int n_leaves,
                      const ktc_buf* stores, int n_stores,
                      int sink, ktc_buf sink_out, int mean,
                      const int* sink_kinds, const ktc_buf* sink_outs, const int* means, int n_sinks,
-                     const ktc_buf* add_to = nullptr, ktc_p2p comm = 0, const ktc_buf* x_bufs = nullptr, const int64_t* x_counts = nullptr, int n_x = 0) {
+                     const ktc_buf* add_to, const int* add_mode, ktc_p2p comm, const ktc_buf* x_bufs, const int64_t* x_counts, int n_x) {
     if (!code || n_code < 1 || n_code > kExprMaxInstr) return fail(KTC_EINVAL, "ktc_expr_eval: program of %d instructions (1..%d allowed)", n_code, kExprMaxInstr);
     if (n_imm < 0 || n_imm > kExprMaxImm || (n_imm > 0 && !imm)) return fail(KTC_EINVAL, "ktc_expr_eval: %d immediates (at most %d)", n_imm, kExprMaxImm);
     if (n_leaves < 0 || n_leaves > kExprMaxLeaves || n_stores < 0 || n_stores > kExprMaxStores)
@@ -360,16 +369,17 @@ static int expr_eval(const uint32_t* code, int n_code, const float* imm, int n_i
 
     // validate the program: register and operand indices, opcodes
     a.n_code = n_code;
-    bool has_acc = false;
+    bool has_acc = false, has_scatc = false;
     bool fed[kExprMaxSinks] = {false};
     for (int i = 0; i < n_code; ++i) {
         const uint32_t ins = code[i];
         const int op = ins & 0xff, dreg = (ins >> 8) & 0xf, ra = (ins >> 12) & 0xf, rb = (ins >> 16) & 0xf, k = ins >> 20;
-        if (op < KTC_X_LOAD || op > KTC_X_ACC) return fail(KTC_EINVAL, "ktc_expr_eval: unknown opcode %d at %d", op, i);
+        if (op < KTC_X_LOAD || op > KTC_X_SCATC) return fail(KTC_EINVAL, "ktc_expr_eval: unknown opcode %d at %d", op, i);
         if (dreg >= kExprRegs || ra >= kExprRegs || rb >= kExprRegs) return fail(KTC_EINVAL, "ktc_expr_eval: register index out of range at %d", i);
         if (op == KTC_X_LOAD && k >= n_leaves) return fail(KTC_EINVAL, "ktc_expr_eval: LOAD of leaf %d (have %d)", k, n_leaves);
         if (op == KTC_X_STORE && k >= n_stores) return fail(KTC_EINVAL, "ktc_expr_eval: STORE to target %d (have %d)", k, n_stores);
-        if ((op == KTC_X_CONST || (op >= KTC_X_CMP_LT && op <= KTC_X_CMP_GTE)) && k >= n_imm) return fail(KTC_EINVAL, "ktc_expr_eval: immediate %d (have %d)", k, n_imm);
+        if (op == KTC_X_SCATC) has_scatc = true;
+        if ((op == KTC_X_CONST || op == KTC_X_SCATC || (op >= KTC_X_CMP_LT && op <= KTC_X_CMP_GTE)) && k >= n_imm) return fail(KTC_EINVAL, "ktc_expr_eval: immediate %d (have %d)", k, n_imm);
         if (op == KTC_X_CLAMP && k + 1 >= n_imm) return fail(KTC_EINVAL, "ktc_expr_eval: clamp immediates %d,%d (have %d)", k, k + 1, n_imm);
         if (op == KTC_X_ACC) {
             if (sink == KTC_EXPR_STORE_ONLY) return fail(KTC_EINVAL, "ktc_expr_eval: ACC without a summing sink");
@@ -417,6 +427,9 @@ static int expr_eval(const uint32_t* code, int n_code, const float* imm, int n_i
     }
     if (!d) return fail(KTC_EINVAL, "ktc_expr_eval: no buffers given");
     a.S = (int)Sg;
+    a.err = d->idx_err;
+    if (has_scatc && a.D2 != shape[ndim - 1]) return fail(KTC_ENOTSUP, "ktc_expr_eval: a scatter along the last axis needs that axis uncollapsed");
+    if (has_scatc && scatc_dev) *scatc_dev = d;           // the caller reads the index check after the launches
 
     if (sink == KTC_EXPR_STORE_ONLY) {
         const int64_t grid = (Sg * a.col_tiles + 7) / 8;
@@ -456,6 +469,8 @@ static int expr_eval(const uint32_t* code, int n_code, const float* imm, int n_i
                 if (t.n < c.n_out[j]) return fail(KTC_EINVAL, "ktc_expr_eval_multi_fused: the tensor sink %d is added to holds %lld floats, %lld needed", j, (long long)t.n, (long long)c.n_out[j]);
                 if (t.ptr == mout[j].ptr) return fail(KTC_EINVAL, "ktc_expr_eval_multi_fused: sink %d is added to its own output", j);
                 c.add_to[j] = t.ptr;
+                c.add_mode[j] = add_mode ? add_mode[j] : 1;
+                if (c.add_mode[j] != 1 && c.add_mode[j] != 2) return fail(KTC_EINVAL, "ktc_expr_eval_multi_fused: add_mode %d of sink %d (1: add, 2: add to zero)", c.add_mode[j], j);
             }
         }
         if (comm) {
@@ -494,6 +509,21 @@ static int expr_eval(const uint32_t* code, int n_code, const float* imm, int n_i
     return finish_launch_expr("expr(combine)");
 }
 
+static int expr_eval(const uint32_t* code, int n_code, const float* imm, int n_imm,
+                     const int64_t* shape, int ndim,
+                     const ktc_buf* leaves, const int64_t* leaf_shapes, int n_leaves,
+                     const ktc_buf* stores, int n_stores,
+                     int sink, ktc_buf sink_out, int mean,
+                     const int* sink_kinds, const ktc_buf* sink_outs, const int* means, int n_sinks,
+                     const ktc_buf* add_to = nullptr, const int* add_mode = nullptr, ktc_p2p comm = 0, const ktc_buf* x_bufs = nullptr,
+                     const int64_t* x_counts = nullptr, int n_x = 0) {
+    Device* scatc_dev = nullptr;
+    KTC_TRY(expr_eval_impl(&scatc_dev, code, n_code, imm, n_imm, shape, ndim, leaves, leaf_shapes, n_leaves, stores, n_stores, sink, sink_out, mean,
+                           sink_kinds, sink_outs, means, n_sinks, add_to, add_mode, comm, x_bufs, x_counts, n_x));
+    if (scatc_dev) return take_index_error(scatc_dev, "Scatter", shape[ndim - 1], ndim - 1);      // a recorded inplaceScatter ran inside the program
+    return KTC_OK;
+}
+
 extern "C" int ktc_expr_eval(const uint32_t* code, int n_code, const float* imm, int n_imm,
                              const int64_t* shape, int ndim,
                              const ktc_buf* leaves, const int64_t* leaf_shapes, int n_leaves,
@@ -512,10 +542,10 @@ extern "C" int ktc_expr_eval_multi_fused(const uint32_t* code, int n_code, const
                                          const ktc_buf* leaves, const int64_t* leaf_shapes, int n_leaves,
                                          const ktc_buf* stores, int n_stores,
                                          const int* sink_kinds, const ktc_buf* sink_outs, const int* means, int n_sinks,
-                                         const ktc_buf* add_to, ktc_p2p comm, const ktc_buf* x_bufs, const int64_t* x_counts, int n_x) {
+                                         const ktc_buf* add_to, const int* add_mode, ktc_p2p comm, const ktc_buf* x_bufs, const int64_t* x_counts, int n_x) {
     if (comm && (!x_bufs || !x_counts || n_x < 1)) return fail(KTC_EINVAL, "ktc_expr_eval_multi_fused: a communicator without tensors to exchange");
     return expr_eval(code, n_code, imm, n_imm, shape, ndim, leaves, leaf_shapes, n_leaves, stores, n_stores, KTC_EXPR_MULTI, 0, 0, sink_kinds, sink_outs, means, n_sinks,
-                     add_to, comm, x_bufs, x_counts, n_x);
+                     add_to, add_mode, comm, x_bufs, x_counts, n_x);
 }
 
 extern "C" int ktc_expr_eval_multi(const uint32_t* code, int n_code, const float* imm, int n_imm,

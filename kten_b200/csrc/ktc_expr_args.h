@@ -35,6 +35,7 @@ struct ExprArgs {
     int n_sinks;
     int sink_kind[kExprMaxSinks];          // KTC_EXPR_SUM_ALL or KTC_EXPR_SUM_ROWS
     double* mpart[kExprMaxSinks];          // partial sums of each sink
+    int* err;                              // device word set when a SCATC instruction meets an index outside its row
 };
 
 }  // namespace ktc

@@ -47,7 +47,7 @@ struct Device {
     int* wait_flag = nullptr;         // device int nothing ever sets (bounded-wait test hook)
     int* idx_err = nullptr;           // device int, set by kernels that meet an invalid index (gather / scatter / index ops)
     bool idx_pending = false;         // an index check is outstanding: read at the next call that waits for the stream
-    char idx_what[96] = {0};          // the last call that may have set it, for the message
+    char idx_what[160] = {0};         // the message of the last call that may have set it
 };
 
 struct BufRec {

@@ -35,6 +35,7 @@
 // own entry points, so that it can be compiled alone (KTC_LAZY_STANDALONE) and driven by a
 // stand-in library on a machine without a GPU.
 #include <algorithm>
+#include <cmath>
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
@@ -60,6 +61,7 @@ struct Backend {
     int (*refcount)(ktc_buf, int*);
     int (*buf_info)(ktc_buf, int*, int64_t*, void**);
     int (*d2d)(ktc_buf, int64_t, ktc_buf, int64_t, int64_t);
+    int (*fill)(ktc_buf, int64_t, int64_t, float);
     int (*binary)(int, ktc_buf, ktc_buf, ktc_buf, int64_t);
     int (*binary_bcast)(int, ktc_buf, ktc_buf, const int64_t*, int, ktc_buf, const int64_t*, int);
     int (*binary_inplace)(int, ktc_buf, ktc_buf, int64_t);
@@ -75,7 +77,7 @@ struct Backend {
                      const ktc_buf*, int, int, ktc_buf, int);
     int (*expr_eval_multi_fused)(const uint32_t*, int, const float*, int, const int64_t*, int, const ktc_buf*, const int64_t*, int,
                                  const ktc_buf*, int, const int*, const ktc_buf*, const int*, int,
-                                 const ktc_buf*, uint64_t, const ktc_buf*, const int64_t*, int);
+                                 const ktc_buf*, const int*, uint64_t, const ktc_buf*, const int64_t*, int);
     int (*p2p_allreduce_sum)(uint64_t, const ktc_buf*, const int64_t*, int);
 };
 constexpr int kBackendEntries = sizeof(Backend) / sizeof(void*);
@@ -85,7 +87,7 @@ static Backend B = {};
 static thread_local char g_err[512];
 static void set_error_v(const char* fmt, va_list ap) { vsnprintf(g_err, sizeof(g_err), fmt, ap); }
 #else
-static Backend B = {ktc_alloc, ktc_retain, ktc_release, ktc_refcount, ktc_buf_info, ktc_d2d, ktc_binary, ktc_binary_bcast,
+static Backend B = {ktc_alloc, ktc_retain, ktc_release, ktc_refcount, ktc_buf_info, ktc_d2d, ktc_fill, ktc_binary, ktc_binary_bcast,
                     ktc_binary_inplace, ktc_scalar, ktc_scalar_inplace, ktc_unary, ktc_clamp, ktc_compare_scalar, ktc_broadcast_to,
                     ktc_reduce_axis, ktc_reduce_all, ktc_expr_eval, ktc_expr_eval_multi_fused, ktc_p2p_allreduce_sum};
 static void set_error_v(const char* fmt, va_list ap) { char b[512]; vsnprintf(b, sizeof(b), fmt, ap); ::ktc::set_error("%s", b); }
@@ -98,7 +100,7 @@ static int fail(int code, const char* fmt, ...) {
 #define LZ_TRY(call) do { int s_ = (call); if (s_ != KTC_OK) return s_; } while (0)
 
 constexpr int MAXD = KTC_MAX_DIMS;
-enum Kind : uint8_t { K_LEAF = 0, K_CONST, K_UN, K_BIN, K_CLAMP, K_CMP, K_SQUARE, K_BCAST, K_REDUCE };
+enum Kind : uint8_t { K_LEAF = 0, K_CONST, K_UN, K_BIN, K_CLAMP, K_CMP, K_SQUARE, K_BCAST, K_REDUCE, K_SCATC };
 
 struct Shape {
     int nd = 0;
@@ -109,6 +111,8 @@ struct Shape {
 };
 static Shape make_shape(const int64_t* s, int nd) { Shape r; r.nd = nd; for (int i = 0; i < nd; ++i) r.d[i] = s[i]; return r; }
 
+// K_SCATC: args[0] with `imm[0]` written at column (int)args[1] of every row -- inplaceScatter(-1, index, constant) with
+// one index per row (JVMRawTensor.kt:317-332).
 // A value.  `buf` is set once the value is in memory (the node then acts as a leaf and forgets how it was
 // computed).  A K_REDUCE node is a sum that has not run yet: args[0] is the summed expression, op the sink
 // kind, imm[0] != 0 a mean; it is never part of a program -- whoever needs its value runs the pending sums.
@@ -146,6 +150,7 @@ struct Pending {
     bool strong;
     std::vector<ktc_buf> targets;           // buffers to which this sum is added when it has run (one reference each)
     std::vector<uint64_t> seq;              // request order of those updates
+    std::vector<char> from_zero;            // the target was zeroed just before: it receives 0f + sum, its contents are not read
 };
 
 struct Cached {
@@ -481,6 +486,7 @@ static void compile_uncached(Program& prog, std::vector<Node*>& store_nodes, con
             case K_SQUARE: emit(prog, KTC_X_SQUARE, d, srcs[0]); break;
             case K_CLAMP: emit(prog, KTC_X_CLAMP, d, srcs[0], 0, imm_index(prog, n->imm, 2, n->pos)); break;
             case K_CMP: emit(prog, kCmpX[n->op], d, srcs[0], 0, imm_index(prog, n->imm, 1, n->pos)); break;
+            case K_SCATC: emit(prog, KTC_X_SCATC, d, srcs[0], srcs[1], imm_index(prog, n->imm, 1, n->pos)); break;
             default: prog.ok = false; break;
             }
         }
@@ -762,6 +768,7 @@ static int eager_into(Node* node, const Shape& shape, ktc_buf out) {
     };
     if (nd->kind == K_REDUCE && !nd->stored()) { ktc_buf h; LZ_TRY(force(nd, &h, nullptr)); }
     if (nd->stored()) return spread(nd->buf, nd->shape);
+    if (nd->kind == K_CONST) return B.fill(out, 0, n, nd->imm[0]);
     node_ref(nd);
     Node* kids[2] = {nullptr, nullptr};
     Shape natural; bool have = false;
@@ -799,10 +806,11 @@ struct Exchange {
     std::vector<Node*> nodes;               // the values to sum over the ranks: stored nodes, or pending sums of the pass
     bool done = false;
 };
-struct Update { uint64_t seq; ktc_buf target; Node* nd; };
+struct Update { uint64_t seq; ktc_buf target; Node* nd; bool from_zero; };
 
 // add_to[i]: the buffer node i's sum is also added to (0: none).  x: the exchange to fold in, or null.
-static int try_fused_sums(const Shape& shape, const std::vector<Node*>& nodes, const std::vector<ktc_buf>& add_to, Exchange* x, bool* fused) {
+static int try_fused_sums(const Shape& shape, const std::vector<Node*>& nodes, const std::vector<ktc_buf>& add_to, const std::vector<int>& add_mode,
+                          Exchange* x, bool* fused) {
     *fused = false;
     std::vector<Node*> exprs; std::vector<int> kinds, means;
     bool any_rows = false;
@@ -833,7 +841,7 @@ static int try_fused_sums(const Shape& shape, const std::vector<Node*>& nodes, c
     const int rc = B.expr_eval_multi_fused(prog.code.data(), (int)prog.code.size(), prog.imm.empty() ? &zero : prog.imm.data(), (int)prog.imm.size(),
                                            prog.shape.d, prog.shape.nd, lh.data(), ls.data(), (int)prog.leaves.size(),
                                            extra.empty() ? &none : extra.data(), (int)extra.size(), kinds.data(), outs.data(), means.data(), (int)nodes.size(),
-                                           add_to.data(), x ? x->comm : 0, x ? xb.data() : nullptr, x ? xc.data() : nullptr, x ? (int)xb.size() : 0);
+                                           add_to.data(), add_mode.data(), x ? x->comm : 0, x ? xb.data() : nullptr, x ? xc.data() : nullptr, x ? (int)xb.size() : 0);
     if (rc != KTC_OK) { drop(); return rc == KTC_ENOTSUP ? KTC_OK : rc; }
     ++st_fused; ++st_multi;
     if (x) { x->done = true; ++st_fused_exchanges; }
@@ -892,7 +900,7 @@ static int run_pending(Exchange* x) {
     for (Pending& e : entries) {
         if (!e.strong) node_ref(e.node);                  // keep every sum alive until this call is over
         if (!e.node->stored()) todo.push_back(e.node);
-        for (size_t i = 0; i < e.targets.size(); ++i) ups.push_back({e.seq[i], e.targets[i], e.node});
+        for (size_t i = 0; i < e.targets.size(); ++i) ups.push_back({e.seq[i], e.targets[i], e.node, e.from_zero[i] != 0});
     }
     std::sort(ups.begin(), ups.end(), [](const Update& a, const Update& b) { return a.seq < b.seq; });
     // an update is folded into the second pass of its sum when it is the only update of its buffer and the only one
@@ -935,14 +943,15 @@ static int run_pending(Exchange* x) {
                 ++passes;
                 if (chunk.size() > 1) {
                     std::vector<ktc_buf> add_to(chunk.size(), 0);
+                    std::vector<int> add_mode(chunk.size(), 0);
                     std::vector<size_t> which(chunk.size(), 0);
                     size_t n_fold = 0;
                     for (size_t k = 0; k < ups.size(); ++k)
                         for (size_t c = 0; c < chunk.size(); ++c)
-                            if (ups[k].nd == chunk[c] && foldable(ups[k])) { add_to[c] = ups[k].target; which[c] = k; ++n_fold; }
+                            if (ups[k].nd == chunk[c] && foldable(ups[k])) { add_to[c] = ups[k].target; add_mode[c] = ups[k].from_zero ? 2 : 1; which[c] = k; ++n_fold; }
                     // the exchange joins only when this is the whole of the pending work: one pass, every update in it
                     const bool whole = passes == 1 && waiting_nodes.empty() && groups.size() == 1 && g.second.size() == chunk.size() && n_fold == ups.size();
-                    status = try_fused_sums(g.first, chunk, add_to, (x && whole) ? x : nullptr, &fused);
+                    status = try_fused_sums(g.first, chunk, add_to, add_mode, (x && whole) ? x : nullptr, &fused);
                     if (status == KTC_OK && fused)
                         for (size_t c = 0; c < chunk.size(); ++c) if (add_to[c]) { folded[which[c]] = 1; ++st_fused_updates; }
                 }
@@ -952,7 +961,9 @@ static int run_pending(Exchange* x) {
     }
     for (size_t k = 0; status == KTC_OK && k < ups.size(); ++k) {
         if (folded[k]) continue;
-        status = B.binary_inplace(KTC_PLUS, ups[k].target, ups[k].nd->buf, ups[k].nd->shape.volume());
+        const int64_t n = ups[k].nd->shape.volume();
+        if (ups[k].from_zero) status = B.fill(ups[k].target, 0, n, 0.f);
+        if (status == KTC_OK) status = B.binary_inplace(KTC_PLUS, ups[k].target, ups[k].nd->buf, n);
     }
     for (Pending& e : entries) {
         for (ktc_buf h : e.targets) B.release(h);
@@ -962,13 +973,14 @@ static int run_pending(Exchange* x) {
 }
 
 // Remember `buffer handle += node` (node: a pending sum).  The node is kept alive from here on.
-static bool add_pending_update(Node* node, ktc_buf handle) {
+static bool add_pending_update(Node* node, ktc_buf handle, bool from_zero = false) {
     for (Pending& e : g_pending) {
         if (e.node != node) continue;
         if (B.retain(handle) != KTC_OK) return false;
         if (!e.strong) { e.strong = true; node_ref(node); }
         e.targets.push_back(handle);
         e.seq.push_back(++g_update_seq);
+        e.from_zero.push_back(from_zero ? 1 : 0);
         ++g_pending_targets[handle];
         return true;
     }
@@ -980,7 +992,7 @@ static uint64_t defer_sum(Node* expr, int kind, bool mean, const Shape& res_shap
     Node* n = new_node(K_REDUCE, res_shape, kind, expr, nullptr, &m, 1);
     const uint64_t id = new_cell(node_ref(n));
     register_cell(id, n);
-    g_pending.push_back({n, false, {}, {}});
+    g_pending.push_back({n, false, {}, {}, {}});
     return id;
 }
 
@@ -1007,6 +1019,26 @@ static int assign(uint64_t target_id, Kind kind, int op, Node* a0, Node* a1, con
     Node* node = new_node(kind, own->shape, op, a0, a1, imm, nimm);
     node_ref(node);
     auto done = [&](int s, int st) { if (state) *state = st; node_unref(node); return s; };
+    if (!own->stored() && kind == K_BIN && op == KTC_PLUS && !g_pending.empty()) {
+        // zeroed pending target += pending sum (a gradient cleared with zeroGrad, then accumulated into): the cell gets a
+        // buffer of its own that receives 0f + sum when the sums run -- in the second pass of their kernel where possible
+        Node* zero = strip(own);
+        Node* other = strip(a1);
+        if (zero->kind == K_CONST && zero->imm[0] == 0.f && !std::signbit(zero->imm[0]) && a0 == own && other->kind == K_REDUCE && !other->stored()
+            && other->shape.volume() == own->shape.volume()) {
+            ktc_buf h = 0;
+            const int s = alloc_handle(other->dev, own->shape.volume(), &h);
+            if (s != KTC_OK) return done(s, 0);
+            if (add_pending_update(other, h, true)) {
+                Node* leaf = new_leaf(h, own->shape, other->dev);
+                leaf->owner = target_id;
+                cell->node = node_ref(leaf);
+                node_unref(own);
+                return done(KTC_OK, 3);
+            }
+            B.release(h);
+        }
+    }
     if (!own->stored()) {                                 // a pending target takes the new value
         cell->node = node_ref(node);
         register_cell(target_id, node);
@@ -1054,6 +1086,7 @@ static int assign(uint64_t target_id, Kind kind, int op, Node* a0, Node* a1, con
     if (s != KTC_OK || fused) return finish(s, 0);
     ++st_unfused;
     if (kind == K_SQUARE) return finish(B.scalar_inplace(KTC_POW, h, 2.0f, n), 0);
+    if (kind == K_SCATC) return finish(fail(KTC_ENOTSUP, "this scatter is not fusable here: use ktc_scatter_axis_nd on the buffers"), 0);
     if (kind != K_BIN) return finish(fail(KTC_ESTATE, "in-place call of kind %d", (int)kind), 0);
     if (other->kind == K_CONST) return finish(B.scalar_inplace(op, h, other->imm[0], n), 0);
     ktc_buf hb; Shape shp;
@@ -1204,6 +1237,68 @@ KTC_API int ktc_lazy_assign_scalar(int op, ktc_lazy_cell target, float s, int* s
     const int st = assign(target, kind, kind == K_SQUARE ? 0 : op, a0, a1, nullptr, 0, state);
     if (made) node_unref(a1);
     return st;
+}
+
+// a pending constant of the given shape
+static Node* constant_node(const Shape& s, float value, int dev) {
+    Node* c = new_const(value);
+    node_ref(c);
+    Node* b = new_node(K_BCAST, s, 0, c, nullptr, nullptr, 0);
+    b->dev = dev;
+    node_unref(c);
+    return b;
+}
+
+KTC_API int ktc_lazy_full(int dev, const int64_t* shape, int ndim, float value, ktc_lazy_cell* out) {
+    LZ_LOCK;
+    if (!out || ndim < 0 || ndim > MAXD) return fail(KTC_EINVAL, "ktc_lazy_full: bad arguments");
+    Node* n = constant_node(make_shape(shape, ndim), value, dev);
+    *out = new_cell(node_ref(n));
+    register_cell(*out, n);
+    return KTC_OK;
+}
+
+KTC_API int ktc_lazy_assign_fill(ktc_lazy_cell target, float value, int* state) {
+    LZ_LOCK;
+    Cell* cell = cell_of(target);
+    if (!cell || !cell->node) return fail(KTC_ESTATE, "ktc_lazy_assign_fill: stale or unknown cell");
+    Node* own = cell->node;
+    if (own->stored()) {
+        const ktc_buf h = own->buf;
+        node_ref(own);
+        int s = flush_dependents(h);                      // pending readers of the old contents, pending updates of it
+        cell = cell_of(target);
+        int cnt = 0;
+        if (s == KTC_OK) s = B.refcount(h, &cnt);
+        if (s != KTC_OK || !(opt_defer_inplace && cell->node == own && cnt == 2)) {
+            if (s == KTC_OK) s = B.fill(h, 0, own->shape.volume(), value);
+            node_unref(own);
+            if (state) *state = 0;
+            return s;
+        }
+        node_unref(own);
+    }
+    Node* n = constant_node(own->shape, value, own->dev);
+    cell->node = node_ref(n);
+    register_cell(target, n);
+    node_unref(own);
+    if (state) *state = 1;
+    return KTC_OK;
+}
+
+KTC_API int ktc_lazy_assign_scatter_const(ktc_lazy_cell target, ktc_lazy_cell index, float value, int* state) {
+    LZ_LOCK;
+    Node *nt, *ni;
+    LZ_TRY(operand(target, &nt)); LZ_TRY(operand(index, &ni)); LZ_TRY(operand(target, &nt));
+    const Shape &st = nt->shape, &si = ni->shape;
+    bool ok = st.nd >= 1 && si.nd == st.nd && si.d[si.nd - 1] == 1 && st.d[st.nd - 1] > 1;
+    for (int i = 0; ok && i + 1 < st.nd; ++i) ok = si.d[i] == st.d[i];
+    if (!ok) return fail(KTC_ENOTSUP, "ktc_lazy_assign_scatter_const: the index must have the target's shape with a last extent of 1");
+    if (!strip(ni)->stored()) { ktc_buf h; LZ_TRY(force(ni, &h, nullptr)); LZ_TRY(operand(target, &nt)); }
+    node_ref(ni);
+    const int s = assign(target, K_SCATC, 0, nt, ni, &value, 1, state);
+    node_unref(ni);
+    return s;
 }
 
 // kind: KTC_EXPR_SUM_ALL (sum() / mean()), KTC_EXPR_SUM_ROWS (sum over axis 0 of [A, ...]), KTC_EXPR_SUM_LAST

@@ -88,7 +88,7 @@ int tune(const char* key, int dflt) {
 // tunable `index_check_sync` = 1 every such call waits and reports at once, as the reference throws at the call
 // (JVMRawTensor.kt:334-353).
 int take_index_error(Device* d, const char* what, int64_t axis_len, int axis) {
-    snprintf(d->idx_what, sizeof(d->idx_what), "%s (axis %d of extent %lld)", what, axis, (long long)axis_len);
+    snprintf(d->idx_what, sizeof(d->idx_what), "%s got invalid index, index value is out of bounds 0 and %lld at axis: %d", what, (long long)axis_len, axis);
     d->idx_pending = true;
     if (!tune("index_check_sync", 0)) return KTC_OK;
     KTC_CUDA(cudaStreamSynchronize(d->stream));
@@ -102,8 +102,8 @@ int check_deferred_index_error(Device* d) {
     KTC_CUDA(cudaMemcpy(&h, d->idx_err, sizeof(int), cudaMemcpyDeviceToHost));
     if (h == 0) return KTC_OK;
     KTC_CUDA(cudaMemset(d->idx_err, 0, sizeof(int)));
-    return fail(KTC_EINVAL, "%s got invalid index, index value is out of bounds (the access was skipped; with index_check_sync = 0 the call that "
-                            "reports this is the first one that waits for the device after it)", d->idx_what);
+    return fail(KTC_EINVAL, "%s (the access was skipped; unless index_check_sync is set, the call that reports this is the first one that "
+                            "waits for the device after the faulty call)", d->idx_what);
 }
 
 Device* device(int dev) {

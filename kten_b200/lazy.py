@@ -26,7 +26,7 @@ from typing import Sequence
 
 from . import _lib as L
 
-STATE_WRITTEN, STATE_PENDING, STATE_UPDATE_RECORDED = 0, 1, 2
+STATE_WRITTEN, STATE_PENDING, STATE_UPDATE_RECORDED, STATE_UPDATE_OF_ZEROED = 0, 1, 2, 3
 OPTIONS = ("recompute_limit", "store_cost", "defer_sums", "defer_inplace")
 STATS = ("fused", "unfused", "multi_sink", "pending_sums", "cache_hits", "compiled", "live_nodes", "live_cells", "folded_updates", "folded_exchanges")
 
@@ -76,6 +76,25 @@ class Recorder:
     def assign_scalar(self, op: int, target: int, s: float) -> int:
         state = C.c_int(0)
         L.check(self.lib.ktc_lazy_assign_scalar(op, target, float(s), C.byref(state)))
+        return state.value
+
+    def full(self, device: int, shape: Sequence[int], value: float) -> int:
+        """A cell whose pending value is `value` everywhere (createRawFill, zerosLike): no buffer until one is needed."""
+        arr, nd = L.shape_array(shape)
+        return self._cell(self.lib.ktc_lazy_full, device, arr, nd, float(value))
+
+    def assign_fill(self, target: int, value: float) -> int:
+        state = C.c_int(0)
+        L.check(self.lib.ktc_lazy_assign_fill(target, float(value), C.byref(state)))
+        return state.value
+
+    def assign_scatter_const(self, target: int, index: int, value: float):
+        """inplaceScatter(-1, index, constant) with one index per row, recorded; None: not recordable here."""
+        state = C.c_int(0)
+        rc = self.lib.ktc_lazy_assign_scatter_const(target, index, float(value), C.byref(state))
+        if rc == L.KTC_ENOTSUP:
+            return None
+        L.check(rc)
         return state.value
 
     def sum(self, a: int, kind: int, mean: bool, res_shape: Sequence[int]) -> int:

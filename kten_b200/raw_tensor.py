@@ -165,6 +165,7 @@ class CUDARawTensor:
                 cell.store = None
         elif state == lazy.STATE_UPDATE_RECORDED:
             self.ops._pending_targets.add(cell.store)
+        # STATE_UPDATE_OF_ZEROED: the recorder gave the (pending) cell a buffer that receives 0 + sum; nothing to do here
 
     def _before_inplace_write(self) -> None:
         """Deferred tensors that read this buffer are evaluated before it changes."""
@@ -472,6 +473,11 @@ class CUDARawTensor:
         return res
 
     def inplaceFill(self, value: float) -> None:
+        if self.ops.lazy and (self._cell.store is not None or self._cell.lz is not None):
+            # recorded: a pending tensor, or a stored one whose buffer nobody else holds, becomes a pending constant
+            # (zeroGrad before a backward pass costs no kernel and no traffic); others are filled at once
+            self._after_assign(self.ops._recorder.assign_fill(self._lz(), value))
+            return
         if self.isDeferred:                                     # the pending value is overwritten: just take storage
             self._drop_recorded()
             h = C.c_uint64(0)
@@ -547,6 +553,22 @@ class CUDARawTensor:
             val.shape, idx.shape = list(s), list(s)
         return val, idx
 
+    def softmaxCrossEntropyForward(self, targets: "CUDARawTensor", lo: float, hi: float):
+        """The forward of SoftmaxCrossEntropy (functions/nn/SoftmaxCrossEntropy.kt:40-59) on logits [rows, cols] in one
+        pass: returns (softmax [rows, cols] -- the tensor the function saves for backward --, nll [rows]) with the bits of
+        the eleven separate calls, or None where the one-pass kernel does not apply (the caller issues the calls)."""
+        entry = getattr(self.ops.lib, "ktc_softmax_xent_forward", None)
+        if entry is None or len(self.shape) != 2 or targets.size != self.shape[0]:
+            return None
+        rows, cols = self.shape
+        softmax, nll = self._new([rows, cols]), self._new([rows])
+        rc = entry(softmax._buf(), nll._buf(), self._buf(), targets._buf(), rows, cols, float(lo), float(hi))
+        if rc == L.KTC_ENOTSUP:
+            softmax.release(); nll.release()
+            return None
+        L.check(rc)
+        return softmax, nll
+
     def sumToShape(self, old_shape: Sequence[int]) -> "CUDARawTensor":
         """mayUnexpand in one call (autograd/functions/Utils.kt:14-41)."""
         old_shape = [int(d) for d in old_shape]
@@ -561,6 +583,13 @@ class CUDARawTensor:
         along `axis` over the whole target -- the Max/Min backward (AggregatingFunctions.kt:68-79) -- takes a
         fully parallel kernel; every other form the general one."""
         if not isinstance(src, CUDARawTensor):
+            a = SF.normalize_axis(self.shape, axis)
+            if self.ops.lazy and a == len(self.shape) - 1 and list(index.shape) == self.shape[:-1] + [1] and self.shape[-1] > 1:
+                # one index per row along the last axis (the `-1 at the target` of SoftmaxCrossEntropy.doBackward): recorded
+                state = self.ops._recorder.assign_scatter_const(self._lz(), index._lz(), float(src))
+                if state is not None:
+                    self._after_assign(state)
+                    return
             self._scatter_nd(L.SCATTER_CONST, axis, index, float(src))
             return
         a = SF.normalize_axis(self.shape, axis)

@@ -159,6 +159,9 @@ class CUDATensorOperations:
         return raw
 
     def createRawFill(self, shape: Sequence[int], constant: float) -> CUDARawTensor:
+        if self.lazy:                       # a pending constant: no buffer and no fill until somebody needs one
+            shape = [int(d) for d in shape]
+            return CUDARawTensor(shape, None, self, lz=self._recorder.full(self.device, shape, constant))
         raw = self.createRaw(shape)
         raw.inplaceFill(constant)
         return raw

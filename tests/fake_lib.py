@@ -41,6 +41,7 @@ BACKEND = [
     ("ktc_refcount", (i32, u64, P(i32))),
     ("ktc_buf_info", (i32, u64, P(i32), P(i64), P(C.c_void_p))),
     ("ktc_d2d", (i32, u64, i64, u64, i64, i64)),
+    ("ktc_fill", (i32, u64, i64, i64, f32)),
     ("ktc_binary", (i32, i32, u64, u64, u64, i64)),
     ("ktc_binary_bcast", (i32, i32, u64, u64, P(i64), i32, u64, P(i64), i32)),
     ("ktc_binary_inplace", (i32, i32, u64, u64, i64)),
@@ -54,7 +55,7 @@ BACKEND = [
     ("ktc_reduce_all", (i32, i32, u64, u64, i64)),
     ("ktc_expr_eval", (i32, P(C.c_uint32), i32, P(f32), i32, P(i64), i32, P(u64), P(i64), i32, P(u64), i32, i32, u64, i32)),
     ("ktc_expr_eval_multi_fused", (i32, P(C.c_uint32), i32, P(f32), i32, P(i64), i32, P(u64), P(i64), i32, P(u64), i32, P(i32), P(u64), P(i32), i32,
-                                   P(u64), u64, P(u64), P(i64), i32)),
+                                   P(u64), P(i32), u64, P(u64), P(i64), i32)),
     ("ktc_p2p_allreduce_sum", (i32, u64, P(u64), P(i64), i32)),
 ]
 RECORDER_CALLS = {
@@ -67,6 +68,8 @@ RECORDER_CALLS = {
     "ktc_lazy_info": (i32, [u64, P(i32), P(i32), P(i64), P(i32)]), "ktc_lazy_flush": (i32, [u64]),
     "ktc_lazy_run_pending": (i32, []), "ktc_lazy_option": (i32, [C.c_char_p, i32]), "ktc_lazy_stats": (i32, [P(i64)]),
     "ktc_lazy_allreduce": (i32, [u64, P(u64), i32]),
+    "ktc_lazy_full": (i32, [i32, P(i64), i32, f32, P(u64)]), "ktc_lazy_assign_fill": (i32, [u64, f32, P(i32)]),
+    "ktc_lazy_assign_scatter_const": (i32, [u64, u64, f32, P(i32)]),
 }
 
 
@@ -311,7 +314,7 @@ class FakeLib:
         return 0
 
     def ktc_expr_eval_multi_fused(self, code, n_code, imm, n_imm, shape, ndim, leaves, lshapes, n_leaves, stores, n_stores, kinds, outs, means, n_sinks,
-                                  add_to, comm, x_bufs, x_counts, n_x):
+                                  add_to, add_mode, comm, x_bufs, x_counts, n_x):
         rc = self.ktc_expr_eval_multi(code, n_code, imm, n_imm, shape, ndim, leaves, lshapes, n_leaves, stores, n_stores, kinds, outs, means, n_sinks)
         if rc != 0:
             return rc
@@ -322,7 +325,8 @@ class FakeLib:
             if add_to and add_to[j]:
                 n = 1 if kinds[j] == L.EXPR_SUM_ALL else shp[-1] if kinds[j] == L.EXPR_SUM_ROWS else total // shp[-1]
                 t = self._get(add_to[j])
-                t[:n] = (t[:n] + self._get(outs[j])[:n]).astype(np.float32)
+                old = np.zeros(n, np.float32) if add_mode and add_mode[j] == 2 else t[:n]
+                t[:n] = (old + self._get(outs[j])[:n]).astype(np.float32)
                 folded += 1
         self.programs[-1]["folded_updates"] = folded
         self.programs[-1]["exchange"] = [int(x_bufs[i]) for i in range(n_x)] if comm else None
@@ -371,6 +375,9 @@ class FakeLib:
                 regs[d] = O.clamp(regs[a], imm[k], imm[k + 1])
             elif L.X_CMP_LT <= op <= L.X_CMP_GTE:
                 regs[d] = O.compare(op - L.X_CMP_LT, regs[a], float(imm[k]))
+            elif op == L.X_SCATC:
+                cols = np.broadcast_to(np.arange(shp[-1]), shp).reshape(-1)
+                regs[d] = np.where(cols == regs[b].astype(np.int64), np.float32(imm[k]), regs[a]).astype(np.float32)
             elif op == L.X_STORE:
                 self._get(stores[k])[:total] = regs[a]
             elif op == L.X_ACC:

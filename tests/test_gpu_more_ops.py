@@ -300,3 +300,43 @@ def test_index_checks_are_read_where_the_host_waits(cuda_ops, gc_scope):
     assert res.toArray().shape == (4, 2)                           # what the faulty call wrote is unspecified, reading it is safe
     good = cuda_ops.createRaw([4, 2], np.array([0, 1, 2, 3, 4, 5, 6, 7], dtype=np.float32))
     assert x.gather(1, good).toArray().reshape(-1).tolist() == [0, 1, 10, 11, 20, 21, 30, 31]
+
+
+@pytest.mark.parametrize("rows,cols", [(300, 2048), (64, 1000), (33, 128), (5, 68), (257, 1364)])
+def test_one_pass_softmax_forward_has_the_bits_of_the_call_sequence(cuda_ops, gc_scope, rows, cols):
+    """ktc_softmax_xent_forward against the eleven raw-tensor calls of SoftmaxCrossEntropy.doForward
+    (SoftmaxCrossEntropy.kt:40-59) issued one by one on the same library: the saved softmax and the per-row negative
+    log-likelihood are bit-identical (the kernel rounds where the calls round and sums rows as ktc_reduce_axis does);
+    shapes the kernel declines fall back to the calls; a target outside the row is reported, not read."""
+    eps = cuda_ops.epsilon
+    hi = float(np.float32(1.0) - np.float32(eps))
+    x = D.uniform(rows * cols, 201, -6.0, 6.0)
+    x[::9973] = 45.0                                                   # a few rows with one dominant logit: softmax entries that underflow, clamped likelihoods
+    t = np.floor(D.uniform(rows, 202, 0.0, cols - 0.01)).astype(np.float32)
+    logits, targets = cuda_ops.createRaw([rows, cols], x), cuda_ops.createRaw([rows], t)
+    res = logits.softmaxCrossEntropyForward(targets, eps, hi)
+    assert res is not None
+    softmax, nll = res
+    idx = targets.view([rows, 1])
+    max_val = logits.max(-1, keepDimensions=True)
+    exp_val = logits.minus(max_val).exp()
+    sm = exp_val.div(exp_val.sum(-1, keepDimensions=True))
+    norm = sm.div(sm.sum(-1, keepDimensions=True))
+    want_nll = norm.clamp(eps, hi).log().gather(-1, idx).unaryMinus()
+    assert same_bits(softmax.toArray(), sm.toArray())
+    assert same_bits(nll.toArray().reshape(-1), want_nll.toArray().reshape(-1))
+    assert len(np.unique(nll.toArray())) > rows // 2
+    assert same_bits(nll.mean().toArray(), want_nll.mean().toArray())
+
+
+def test_one_pass_softmax_forward_declines_and_checks(cuda_ops, gc_scope, index_checks_at_call):
+    eps = cuda_ops.epsilon
+    hi = float(np.float32(1.0) - np.float32(eps))
+    for rows, cols in ((4, 2052), (4, 4096), (4, 30), (4, 66)):           # too long, too short for the warp kernel, not a multiple of 4
+        logits = cuda_ops.createRaw([rows, cols], D.uniform(rows * cols, 203, -1.0, 1.0))
+        assert logits.softmaxCrossEntropyForward(cuda_ops.createRawFill([rows], 0.0), eps, hi) is None
+    logits = cuda_ops.createRaw([4, 128], D.uniform(512, 204, -1.0, 1.0))
+    with pytest.raises(ValueError, match="invalid index"):
+        logits.softmaxCrossEntropyForward(cuda_ops.createRaw([4], np.array([0, 128, 5, 7], dtype=np.float32)), eps, hi)
+    ok = logits.softmaxCrossEntropyForward(cuda_ops.createRaw([4], np.array([0, 127, 5, 7], dtype=np.float32)), eps, hi)
+    assert ok is not None and np.isfinite(ok[1].toArray()).all()

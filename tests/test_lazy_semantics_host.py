@@ -174,7 +174,9 @@ def test_sharded_graph_step_deferred_equals_call_by_call():
     (ve, ce, _, _), (vl, cl, multi, folded), (vs, cs, multi_off, _) = res[0], res[1], res[2]
     for a, c, d in zip(ve, vl, vs):
         assert np.allclose(a, c, rtol=1e-6, atol=1e-6) and np.allclose(a, d, rtol=1e-6, atol=1e-6)
-    assert ce.count("expr_eval") == 0 and cs.count("expr_eval") == 3 and multi_off == 0 and len(cs) < len(ce) / 2
+    # sums that run where they are written: three passes with one sum each, and the two accumulations into the zeroed
+    # (pending-constant) gradients as two small programs
+    assert ce.count("expr_eval") == 0 and cs == ["expr_eval"] * 5 and multi_off == 0
     assert cl == ["expr_eval"] and multi == 2 and folded == 2, cl      # one pass per step (two steps), both `+=` inside it
 
 
