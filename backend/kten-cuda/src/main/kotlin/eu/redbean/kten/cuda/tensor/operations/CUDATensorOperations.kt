@@ -98,7 +98,14 @@ class CUDATensorOperations(override val platformKey: String, val device: Int) : 
         return raw
     }
 
-    override fun createRawFill(shape: List<Int>, constant: Float): CUDARawTensor = createRaw(shape).also { it.inplaceFill(constant) }
+    override fun createRawFill(shape: List<Int>, constant: Float): CUDARawTensor {
+        if (!lazy) return createRaw(shape).also { it.inplaceFill(constant) }
+        // a pending constant: no buffer and no fill until somebody needs one
+        val cell = Arena.ofConfined().use { arena ->
+            KtcNative.cell { out -> KtcNative.lazyFull.invokeExact(device, KtcNative.shape(arena, shape), shape.size, constant, out) as Int }
+        }
+        return CUDARawTensor(shape, CUDABuffer(0L, shape.toStoreSize()).also { it.lz = cell; it.lzShape = shape }, this)
+    }
 
     internal fun upload(raw: CUDARawTensor, data: FloatArray) {
         if (data.isEmpty()) return

@@ -86,10 +86,13 @@ internal object KtcNative {
     val exprEvalMulti = handle("ktc_expr_eval_multi", JAVA_INT, ADDRESS, JAVA_INT, ADDRESS, JAVA_INT, ADDRESS, JAVA_INT, ADDRESS, ADDRESS, JAVA_INT,
         ADDRESS, JAVA_INT, ADDRESS, ADDRESS, ADDRESS, JAVA_INT)
     val exprEvalMultiFused = handle("ktc_expr_eval_multi_fused", JAVA_INT, ADDRESS, JAVA_INT, ADDRESS, JAVA_INT, ADDRESS, JAVA_INT, ADDRESS, ADDRESS, JAVA_INT,
-        ADDRESS, JAVA_INT, ADDRESS, ADDRESS, ADDRESS, JAVA_INT, ADDRESS, JAVA_LONG, ADDRESS, ADDRESS, JAVA_INT)
+        ADDRESS, JAVA_INT, ADDRESS, ADDRESS, ADDRESS, JAVA_INT, ADDRESS, ADDRESS, JAVA_LONG, ADDRESS, ADDRESS, JAVA_INT)
+    // SoftmaxCrossEntropy.doForward in one pass: (softmax, nll, logits, targets, rows, cols, lo, hi); KTC_ENOTSUP (-4): issue the calls instead
+    val softmaxXentForward = handle("ktc_softmax_xent_forward", JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_FLOAT, JAVA_FLOAT)
+    const val ENOTSUP = -4
     // the deferred-expression recorder: elementwise calls and sums are recorded below the C ABI and run fused when a value is needed
     const val EXPR_SUM_ALL = 1; const val EXPR_SUM_ROWS = 2; const val EXPR_SUM_LAST = 4
-    const val ASSIGN_WRITTEN = 0; const val ASSIGN_PENDING = 1; const val ASSIGN_UPDATE_RECORDED = 2
+    const val ASSIGN_WRITTEN = 0; const val ASSIGN_PENDING = 1; const val ASSIGN_UPDATE_RECORDED = 2; const val ASSIGN_UPDATE_OF_ZEROED = 3
     val lazyLeaf = handle("ktc_lazy_leaf", JAVA_INT, JAVA_LONG, ADDRESS, JAVA_INT, ADDRESS)
     val lazyFree = handle("ktc_lazy_free", JAVA_INT, JAVA_LONG)
     val lazyUnary = handle("ktc_lazy_unary", JAVA_INT, JAVA_INT, JAVA_LONG, ADDRESS)
@@ -100,6 +103,9 @@ internal object KtcNative {
     val lazyBroadcastTo = handle("ktc_lazy_broadcast_to", JAVA_INT, JAVA_LONG, ADDRESS, JAVA_INT, ADDRESS)
     val lazyAssignBinary = handle("ktc_lazy_assign_binary", JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_LONG, ADDRESS)
     val lazyAssignScalar = handle("ktc_lazy_assign_scalar", JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_FLOAT, ADDRESS)
+    val lazyFull = handle("ktc_lazy_full", JAVA_INT, JAVA_INT, ADDRESS, JAVA_INT, JAVA_FLOAT, ADDRESS)
+    val lazyAssignFill = handle("ktc_lazy_assign_fill", JAVA_INT, JAVA_LONG, JAVA_FLOAT, ADDRESS)
+    val lazyAssignScatterConst = handle("ktc_lazy_assign_scatter_const", JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_FLOAT, ADDRESS)
     val lazySum = handle("ktc_lazy_sum", JAVA_INT, JAVA_LONG, JAVA_INT, JAVA_INT, ADDRESS, JAVA_INT, ADDRESS)
     val lazyBuffer = handle("ktc_lazy_buffer", JAVA_INT, JAVA_LONG, ADDRESS)
     val lazyInfo = handle("ktc_lazy_info", JAVA_INT, JAVA_LONG, ADDRESS, ADDRESS, ADDRESS, ADDRESS)

@@ -99,7 +99,23 @@ class CUDARawTensor(
             }
         }
 
-    private fun recorded(shape: List<Int>, cell: Long): CUDARawTensor =
+    /**
+     * SoftmaxCrossEntropy.doForward (SoftmaxCrossEntropy.kt:40-59) in one pass over the logits: the saved softmax and the
+     * per-row negative log-likelihood with the bits of the call sequence; null when rows of this length are not handled,
+     * and the caller issues the calls as written.
+     */
+    fun softmaxCrossEntropyForward(targets: CUDARawTensor, lo: Float, hi: Float): Pair<CUDARawTensor, CUDARawTensor>? {
+        if (shape.size != 2) return null
+        val softmax = ops.createRaw(shape)
+        val nll = ops.createRaw(listOf(shape[0], 1))
+        val status = KtcNative.softmaxXentForward.invokeExact(softmax.handle, nll.handle, handle, targets.handle,
+                                                              shape[0].toLong(), shape[1].toLong(), lo, hi) as Int
+        if (status == KtcNative.ENOTSUP) { ops.release(softmax, nll); return null }
+        check(status)
+        return softmax to nll
+    }
+
+    internal fun recorded(shape: List<Int>, cell: Long): CUDARawTensor =
         CUDARawTensor(shape, CUDABuffer(0L, shape.toStoreSize()).also { it.lz = cell; it.lzShape = shape }, ops)
 
     /** What an in-place call through the recorder left behind (ktc_lazy_assign_*). */
@@ -111,6 +127,7 @@ class CUDARawTensor(
                 slot.handle = 0L
             }
             KtcNative.ASSIGN_UPDATE_RECORDED -> ops.pendingTargets.add(slot.handle)
+            // ASSIGN_UPDATE_OF_ZEROED: the recorder gave the (pending, all-zero) cell a buffer that receives 0f + sum; nothing to do here
         }
     }
 
@@ -287,8 +304,20 @@ class CUDARawTensor(
     override fun inplaceScatterAdd(axis: Int, index: AbstractRawTensor<CUDABuffer>, src: AbstractRawTensor<CUDABuffer>) =
         scatterNd(KtcNative.SCATTER_ADD, shape.normalizedAxisScatter(axis, index.shape, src.shape), index as CUDARawTensor, src as CUDARawTensor, 0f)
 
-    override fun inplaceScatter(axis: Int, index: AbstractRawTensor<CUDABuffer>, src: Float) =
-        scatterNd(KtcNative.SCATTER_CONST, shape.normalizeAxis(axis), index as CUDARawTensor, null, src)
+    override fun inplaceScatter(axis: Int, index: AbstractRawTensor<CUDABuffer>, src: Float) {
+        val a = shape.normalizeAxis(axis)
+        if (ops.lazy && a == shape.size - 1 && shape[a] > 1 && index.shape == shape.dropLast(1) + 1) {
+            // one index per row along the last axis (the -1 at the target of SoftmaxCrossEntropy.doBackward): an expression instruction
+            var state = -1
+            val status = Arena.ofConfined().use { arena ->
+                val out = arena.allocate(JAVA_INT)
+                (KtcNative.lazyAssignScatterConst.invokeExact(cell(), (index as CUDARawTensor).cell(), src, out) as Int).also { state = out.get(JAVA_INT, 0) }
+            }
+            if (status == 0) { afterAssign(state); return }
+            if (status != KtcNative.ENOTSUP) check(status)
+        }
+        scatterNd(KtcNative.SCATTER_CONST, a, index as CUDARawTensor, null, src)
+    }
 
     private fun scatterNd(mode: Int, axis: Int, index: CUDARawTensor, src: CUDARawTensor?, constant: Float) {
         Arena.ofConfined().use { arena ->
@@ -355,6 +384,12 @@ class CUDARawTensor(
 
     override fun inplaceFill(value: Float) {
         val slot = storeReference
+        if (ops.lazy && (slot.handle != 0L || slot.lz != 0L)) {
+            // recorded: a pending tensor, or a stored one whose buffer nobody else holds, becomes a pending constant
+            // (zeroing a gradient before a backward pass costs no kernel and no traffic); others are filled at once
+            afterAssign(assignState { state -> KtcNative.lazyAssignFill.invokeExact(cell(), value, state) as Int })
+            return
+        }
         if (slot.handle == 0L) {                                 // a pending value is overwritten: just take storage
             if (slot.lz != 0L) { check(KtcNative.lazyFree.invokeExact(slot.lz) as Int); slot.lz = 0L }
             slot.handle = KtcNative.cell { out -> KtcNative.alloc.invokeExact(ops.device, volume, out) as Int }

@@ -826,6 +826,7 @@ def run_gpu_arm(args):
         "gpu_launches": int(launches),
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d // e2e_steps, "d2h_bytes_per_step": d2h // e2e_steps,
                 "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps, "wall_ms_per_step": 1e3 * e2e_wall / e2e_steps,
+                "h2d_gbs_per_gpu": h2d / (e2e_ms * 1e6), "d2h_gbs_per_gpu": d2h / (e2e_ms * 1e6),      # both directions run for the whole step
                 "note": "pinned host operands: every distinct input of the step is uploaded once (ktc_h2d), every op's result is "
                         "downloaded (ktc_d2h), as a pipeline of 16 MiB pieces (KTC_COPY_OVERLAP_UNFENCED, one fence per step: "
                         "uploads, kernels and downloads of neighbouring pieces overlap); bound by the device-to-host link"},
@@ -883,6 +884,26 @@ def run_single_case(args):
     n = 1 << args.log2n
     scale = n / N28
     name = args.case
+    if name == "c5.graph_native":
+        # the same step issued by the compiled host (libkten_host.so): deferred, one pass with three sinks
+        from kten_b200.native_host import NativeShardedStep
+        cols = 1024
+        rows = max(1, n // cols)
+        x = ops.createRaw([rows, cols], D.uniform(rows * cols, 0, -1.0, 1.0))
+        w = ops.createRaw([1, cols], D.normal(cols, 0, 0.0, 0.02, stream=1))
+        b = ops.createRawFill([cols], 0.0)
+        host = NativeShardedStep(ops, x, w, b, lazy=True)
+        host.run(3)
+        ops.synchronize()
+        l0 = lib.ktc_launch_count()
+        L.check(lib.ktc_timer_start(0))
+        host.run(args.reps)
+        ms = C.c_float(0)
+        L.check(lib.ktc_timer_stop(0, C.byref(ms)))
+        print(json.dumps({"case": name, "elements": rows * cols, "ms": ms.value / args.reps,
+                          "launches_per_step": (lib.ktc_launch_count() - l0) / args.reps}))
+        host.close()
+        return 0
     if name in ("c5.graph_eager", "c5.graph_deferred", "c5.graph_deferred_one_sum"):
         # the sharded-graph step on one device with n = rows * 1024 elements of x
         from kten_b200.sharded import ShardedSigmoidGraph

@@ -141,6 +141,18 @@ __device__ __forceinline__ float4 load_operand(const float* sm, const float* til
     return make_float4(0.f, 0.f, 0.f, 0.f);
 }
 
+// x / b for a divisor shared by a whole row: kd_div_by_reciprocal (ktc_fastmath_d.h), its window tested once per float4
+__device__ __noinline__ float4 div_ieee4(float4 x, float b) {
+    return make_float4(__fdiv_rn(x.x, b), __fdiv_rn(x.y, b), __fdiv_rn(x.z, b), __fdiv_rn(x.w, b));
+}
+__device__ __forceinline__ float4 div_by_row(float4 x, float b, float r) {
+    const uint32_t in_window = kd_div_window(x.x) & kd_div_window(x.y) & kd_div_window(x.z) & kd_div_window(x.w);
+    if (in_window == 0u || r == 0.f) return div_ieee4(x, b);
+    return make_float4(kd_div_by_reciprocal(x.x, b, r), kd_div_by_reciprocal(x.y, b, r), kd_div_by_reciprocal(x.z, b, r), kd_div_by_reciprocal(x.w, b, r));
+}
+template <class F> struct IsDiv { static constexpr bool value = false; };
+template <> struct IsDiv<BinOp<KTC_DIV>> { static constexpr bool value = true; };
+
 // A thread owns one column group (4 floats) and the rows ty, ty + TYC, ... of the tile,
 // at most U of them per batch (U = 8: a tile of 8192 floats is one batch; U = 4 for the
 // arithmetic-heavy functors, whose unrolled code would otherwise not fit the instruction cache).  The loads of the
@@ -151,9 +163,11 @@ __global__ void __launch_bounds__(256) k_bcast3(BcastArgs p, F f) {
     extern __shared__ __align__(16) float smem[];
     constexpr bool STAGE_A = (MODE_A == AM_SMEMROW || MODE_A == AM_ROWSCALAR);
     constexpr bool STAGE_B = (MODE_B == AM_SMEMROW || MODE_B == AM_ROWSCALAR);
+    constexpr bool DIV_ROW = IsDiv<F>::value && MODE_B == AM_ROWSCALAR;      // one divisor per row: divide by its reciprocal
     const int sm_stride = max(p.cols_per_tile, (p.rows_per_tile + 3) & ~3);
     float* sm_a = smem;
     float* sm_b = smem + (STAGE_A ? sm_stride : 0);
+    float* sm_r = sm_b + sm_stride;                                            // the rows' reciprocals (DIV_ROW)
     const int tx = threadIdx.x & (p.txc - 1), ty = threadIdx.x >> p.txc_log2;
     const int tyc = blockDim.x >> p.txc_log2;
 
@@ -192,6 +206,7 @@ __global__ void __launch_bounds__(256) k_bcast3(BcastArgs p, F f) {
                         __syncthreads();                 // readers of the previous tile are done
                         if (STAGE_A) stage_operand<MODE_A>(sm_a, p.a + i0 * p.as0, p.as1, r0, c0, rows, cols4);
                         if (STAGE_B) stage_operand<MODE_B>(sm_b, p.b + i0 * p.bs0, p.bs1, r0, c0, rows, cols4);
+                        if (DIV_ROW) for (int rr = threadIdx.x; rr < rows; rr += blockDim.x) sm_r[rr] = kd_row_reciprocal(sm_b[rr]);   // its own value
                         __syncthreads();
                     }
                     staged = true;
@@ -203,7 +218,9 @@ __global__ void __launch_bounds__(256) k_bcast3(BcastArgs p, F f) {
                     if (col_ok && row < rows) {
                         if (MODE_A != AM_DIRECT) va[u] = load_operand<MODE_A>(sm_a, abase, p.as1, row, col, 0);
                         if (MODE_B != AM_DIRECT) vb[u] = load_operand<MODE_B>(sm_b, bbase, p.bs1, row, col, 0);
-                        st_stream(reinterpret_cast<float4*>(obase + (int64_t)row * p.D2 + col), apply2(f, va[u], vb[u]));
+                        float4* dst = reinterpret_cast<float4*>(obase + (int64_t)row * p.D2 + col);
+                        if (DIV_ROW) st_stream(dst, div_by_row(va[u], vb[u].x, sm_r[row]));
+                        else st_stream(dst, apply2(f, va[u], vb[u]));
                     }
                 }
             }
@@ -241,7 +258,10 @@ template <> struct BatchRows<BinOp<KTC_POW>> { static constexpr int value = 4; }
 
 template <int MA, int MB, class F>
 static void launch_bcast3_modes(Device* d, const BcastArgs& p, int grid, size_t smem, F f) {
-    k_bcast3<MA, MB, BatchRows<F>::value, F><<<grid, 256, smem, d->stream>>>(p, f);
+    if (IsDiv<F>::value && MB == AM_ROWSCALAR && tune("bcast_div_batch", 8) == 8)       // three instructions per quotient: the full batch fits
+        k_bcast3<MA, MB, (IsDiv<F>::value && MB == AM_ROWSCALAR) ? 8 : BatchRows<F>::value, F><<<grid, 256, smem, d->stream>>>(p, f);
+    else
+        k_bcast3<MA, MB, BatchRows<F>::value, F><<<grid, 256, smem, d->stream>>>(p, f);
 }
 
 template <class F>
@@ -312,8 +332,8 @@ static int run_bcast(Device* d, float* out, const int64_t* oshape, int ndim, con
         const int64_t cap = bps > 0 ? (int64_t)d->sm_count * bps : 0x7fffffffLL;
         const int grid = (int)(n_tiles < cap ? n_tiles : cap);
         const int sm_stride = p.cols_per_tile > ((p.rows_per_tile + 3) & ~3) ? p.cols_per_tile : ((p.rows_per_tile + 3) & ~3);
-        const size_t smem = sizeof(float) * (size_t)sm_stride *
-            ((ma == AM_SMEMROW || ma == AM_ROWSCALAR ? 1 : 0) + (mb == AM_SMEMROW || mb == AM_ROWSCALAR ? 1 : 0));
+        const size_t smem = sizeof(float) * (size_t)sm_stride *              // a row-scalar b also gets room for the rows' reciprocals
+            ((ma == AM_SMEMROW || ma == AM_ROWSCALAR ? 1 : 0) + (mb == AM_SMEMROW ? 1 : mb == AM_ROWSCALAR ? 2 : 0));
         return run_bcast3(d, ma, mb, p, grid, smem, f);
     }
 

@@ -53,6 +53,27 @@ KD_TABLE KD_ALIGN(128) double kd_exp2_tab[16] = {
     0x1.ea4afa2a490dap+0    /* 1.9152065613971474 */
 };
 
+// 2^(j/64), j = 0..63: four cache lines.  exp and sigmoid reduce to |z| <= ln2/128 with it, where a degree-4
+// polynomial truncates below 2^-44.5; pow keeps the 16-entry table (its logarithm tables already occupy the L1 pipe).
+KD_TABLE KD_ALIGN(128) double kd_exp2_tab64[64] = {
+    0x1.0000000000000p+0, 0x1.02c9a3e778061p+0, 0x1.059b0d3158574p+0, 0x1.0874518759bc8p+0,
+    0x1.0b5586cf9890fp+0, 0x1.0e3ec32d3d1a2p+0, 0x1.11301d0125b51p+0, 0x1.1429aaea92de0p+0,
+    0x1.172b83c7d517bp+0, 0x1.1a35beb6fcb75p+0, 0x1.1d4873168b9aap+0, 0x1.2063b88628cd6p+0,
+    0x1.2387a6e756238p+0, 0x1.26b4565e27cddp+0, 0x1.29e9df51fdee1p+0, 0x1.2d285a6e4030bp+0,
+    0x1.306fe0a31b715p+0, 0x1.33c08b26416ffp+0, 0x1.371a7373aa9cbp+0, 0x1.3a7db34e59ff7p+0,
+    0x1.3dea64c123422p+0, 0x1.4160a21f72e2ap+0, 0x1.44e086061892dp+0, 0x1.486a2b5c13cd0p+0,
+    0x1.4bfdad5362a27p+0, 0x1.4f9b2769d2ca7p+0, 0x1.5342b569d4f82p+0, 0x1.56f4736b527dap+0,
+    0x1.5ab07dd485429p+0, 0x1.5e76f15ad2148p+0, 0x1.6247eb03a5585p+0, 0x1.6623882552225p+0,
+    0x1.6a09e667f3bcdp+0, 0x1.6dfb23c651a2fp+0, 0x1.71f75e8ec5f74p+0, 0x1.75feb564267c9p+0,
+    0x1.7a11473eb0187p+0, 0x1.7e2f336cf4e62p+0, 0x1.82589994cce13p+0, 0x1.868d99b4492edp+0,
+    0x1.8ace5422aa0dbp+0, 0x1.8f1ae99157736p+0, 0x1.93737b0cdc5e5p+0, 0x1.97d829fde4e50p+0,
+    0x1.9c49182a3f090p+0, 0x1.a0c667b5de565p+0, 0x1.a5503b23e255dp+0, 0x1.a9e6b5579fdbfp+0,
+    0x1.ae89f995ad3adp+0, 0x1.b33a2b84f15fbp+0, 0x1.b7f76f2fb5e47p+0, 0x1.bcc1e904bc1d2p+0,
+    0x1.c199bdd85529cp+0, 0x1.c67f12e57d14bp+0, 0x1.cb720dcef9069p+0, 0x1.d072d4a07897cp+0,
+    0x1.d5818dcfba487p+0, 0x1.da9e603db3285p+0, 0x1.dfc97337b9b5fp+0, 0x1.e502ee78b3ff6p+0,
+    0x1.ea4afa2a490dap+0, 0x1.efa1bee615a27p+0, 0x1.f50765b6e4540p+0, 0x1.fa7c1819e90d8p+0
+};
+
 // For the 32 equal slices (in bit-pattern space) of [sqrt(1/2), sqrt(2)): inv = 1/centre rounded to 13
 // significant bits -- stored as the high word of the double, whose low word is zero -- and -log2(inv).
 // mantissa * inv - 1 is exact in double and below 2^-6 in magnitude; the slice holding 1.0 has inv = 1 and
@@ -97,12 +118,14 @@ KD_TABLE KD_ALIGN(128) double kd_log2_lc[32] = {
 #define KD_C_P2       14   /* (ln 2)^2 / 2 */
 #define KD_C_P1       15   /* ln 2 */
 #define KD_C_MAGIC    16   /* 2^52 + 2^51: adding it leaves the nearest integer in the low word */
-#define KD_C_COUNT    17
+#define KD_C_64_LN2   17   /* 64 / ln 2 */
+#define KD_C_LN2_64   18   /* -(ln 2) / 64 */
+#define KD_C_COUNT    19
 #define KD_CONST_VALUES { \
     23.083120654223414, -0.043321698784996581, 8.3333333333333332e-3, 4.1666666666666664e-2, 1.6666666666666666e-1, \
     -2.404491734814939e-1, 2.8853900817779266e-1, -3.6067376022224085e-1, 4.808983469629878e-1, -7.213475204444817e-1, \
     1.4426950408889634, 1.3333558146428443e-3, 9.618129107628477e-3, 5.550410866482158e-2, 2.4022650695910072e-1, \
-    6.9314718055994531e-1, 6755399441055744.0 }
+    6.9314718055994531e-1, 6755399441055744.0, 92.332482616893656, -0.010830424696249145 }
 #if defined(__CUDACC__)
 static __constant__ double kd_consts[KD_C_COUNT] = KD_CONST_VALUES;
 #else
@@ -117,6 +140,7 @@ static const double kd_consts[KD_C_COUNT] = KD_CONST_VALUES;
 #define KD_F2I(x) __float_as_int(x)
 #define KD_I2F(x) __int_as_float(x)
 #define KD_EXP2_TAB(j) __ldg(&kd_exp2_tab[j])
+#define KD_EXP2_TAB64(j) __ldg(&kd_exp2_tab64[j])
 #else
 KD_FN int32_t kd_lo32(double d) { int64_t i; memcpy(&i, &d, 8); return (int32_t)(uint32_t)(uint64_t)i; }
 KD_FN int32_t kd_hi32(double d) { int64_t i; memcpy(&i, &d, 8); return (int32_t)((uint64_t)i >> 32); }
@@ -129,6 +153,7 @@ KD_FN float kd_i2f(int32_t i) { float f; memcpy(&f, &i, 4); return f; }
 #define KD_F2I(x) kd_f2i(x)
 #define KD_I2F(x) kd_i2f(x)
 #define KD_EXP2_TAB(j) (kd_exp2_tab[j])
+#define KD_EXP2_TAB64(j) (kd_exp2_tab64[j])
 #endif
 
 // 2^(k/16) * (1 + c1 z + c2 z^2 + ... + c5 z^5) for a reduced argument: the table value's exponent field
@@ -138,8 +163,24 @@ KD_FN double kd_scaled_tab(int32_t k) {
     return KD_MAKE(KD_HI32(t) + ((k >> 4) << 20), KD_LO32(t));
 }
 
-// exp(t) for |t| <= 700, relative error below 2^-42 (truncation 2^-42.7 at the edge of the reduced range)
+// exp(t) for |t| <= 700: t = k ln2/64 + z, |z| <= ln2/128, exp(t) = 2^(k/64) (1 + z + z^2/2 + z^3/6 + z^4/24); the
+// truncation is below 2^-44.5 relative at the edge of the reduced range (2^-47 on average), rounding adds about 2^-52
+#ifndef KD_EXP_WIDE_TABLE
+#define KD_EXP_WIDE_TABLE 1
+#endif
 KD_FN double kd_exp(double t) {
+#if KD_EXP_WIDE_TABLE
+    const double v = fma(t, KD_K(KD_C_64_LN2), KD_K(KD_C_MAGIC));
+    const double kd = v - KD_K(KD_C_MAGIC);                            // nearest integer to t * 64 / ln2
+    const double z = fma(kd, KD_K(KD_C_LN2_64), t);                    // t - k * ln2/64
+    double p = fma(z, KD_K(KD_C_E4), KD_K(KD_C_E3));
+    p = fma(p, z, 0.5);
+    p = fma(p, z, 1.0);
+    p = fma(p, z, 1.0);
+    const int32_t k = KD_LO32(v);
+    const double s = KD_EXP2_TAB64(k & 63);
+    return KD_MAKE(KD_HI32(s) + ((k >> 6) << 20), KD_LO32(s)) * p;
+#else
     const double v = fma(t, KD_K(KD_C_16_LN2), KD_K(KD_C_MAGIC));
     const double kd = v - KD_K(KD_C_MAGIC);                            // nearest integer to t * 16 / ln2
     const double z = fma(kd, KD_K(KD_C_LN2_16), t);                    // t - k * ln2/16, |z| <= ln2/32
@@ -149,6 +190,7 @@ KD_FN double kd_exp(double t) {
     p = fma(p, z, 1.0);
     p = fma(p, z, 1.0);
     return kd_scaled_tab(KD_LO32(v)) * p;
+#endif
 }
 
 // Math.max / Math.min-style clamps that keep a NaN argument
@@ -181,6 +223,23 @@ KD_FN float kd_rcp_ieee(float d) {
 #else
     return 1.0f / d;
 #endif
+}
+
+// x / b for a divisor that many dividends share (the b[1,J,1] operand of a broadcast division).  IEEE division costs
+// about ten instructions per element; with r = RN(1/b) computed once, q = RN(x r), e = x - q b (exact in one fma) and
+// RN(q + e r) is the correctly rounded quotient -- Markstein's theorem for a correctly rounded reciprocal, checked on the
+// host for every mantissa of x against thousands of divisors -- in three instructions.  It holds while nothing over- or
+// underflows: divisors in [2^-60, 2^60] (kd_row_reciprocal returns 0 for the others) and dividends in [2^-63, 2^64), i.e.
+// an exponent field in [64, 192): adding 64 to the field sets its top bit exactly then (a zero dividend would lose its
+// sign in the fast form; NaN and infinity are out of the window too).  Everything else takes the IEEE division.
+KD_FN float kd_row_reciprocal(float b) {
+    const float ab = b < 0.0f ? -b : b;
+    return (ab >= 0x1p-60f && ab <= 0x1p60f) ? kd_rcp_ieee(b) : 0.0f;
+}
+KD_FN uint32_t kd_div_window(float x) { return ((uint32_t)KD_F2I(x) + 0x20000000u) & 0x40000000u; }
+KD_FN float kd_div_by_reciprocal(float x, float b, float r) {
+    const float q = x * r;
+    return fmaf(fmaf(-q, b, x), r, q);
 }
 
 // kten-jvm's sigmoid: e = (float)Math.exp((double)(-1f * x)); 1f / (1f + e)   (JVMRawTensor.kt:399).
@@ -237,16 +296,31 @@ KD_FN float kd_pow(float x, float y, bool* ok) {
     const int32_t ix = KD_F2I(x);
     const double p = kd_log2(ix) * (double)y;
     *ok = ((uint32_t)(ix - 0x00800000) < 0x7f000000u) && ((uint32_t)(KD_HI32(p) & 0x7fffffff) < 0x40640000u);
+#ifndef KD_POW_WIDE_TABLE
+#define KD_POW_WIDE_TABLE 0
+#endif
+#if KD_POW_WIDE_TABLE
+    const double v = fma(p, 64.0, KD_K(KD_C_MAGIC));
+    const double kd = v - KD_K(KD_C_MAGIC);
+    const double z = fma(kd, -0.015625, p);                           // p - k/64 exactly, |z| <= 1/128
+    double s = fma(z, KD_K(KD_C_P4), KD_K(KD_C_P3));                   // 2^z = 1 + z ln2 + (z ln2)^2 / 2 + ...
+    s = fma(s, z, KD_K(KD_C_P2));
+    s = fma(s, z, KD_K(KD_C_P1));
+    s = fma(s, z, 1.0);
+    const int32_t k = KD_LO32(v);
+    const double t = KD_EXP2_TAB64(k & 63);
+    return (float)(KD_MAKE(KD_HI32(t) + ((k >> 6) << 20), KD_LO32(t)) * s);
+#else
     const double v = fma(p, 16.0, KD_K(KD_C_MAGIC));
     const double kd = v - KD_K(KD_C_MAGIC);
     const double z = fma(kd, -0.0625, p);                             // p - k/16 exactly, |z| <= 1/32
     double s = fma(z, KD_K(KD_C_P5), KD_K(KD_C_P4));                   // 2^z = 1 + z ln2 + (z ln2)^2 / 2 + ...
     s = fma(s, z, KD_K(KD_C_P3));
-
     s = fma(s, z, KD_K(KD_C_P2));
     s = fma(s, z, KD_K(KD_C_P1));
     s = fma(s, z, 1.0);
     return (float)(kd_scaled_tab(KD_LO32(v)) * s);
+#endif
 }
 
 }  // namespace ktc

@@ -150,8 +150,14 @@ __global__ void __launch_bounds__(256) k_rows_warp(const float* __restrict__ in,
 // MODE 0: final values (S == 1).  MODE 1: one Partial per segment.  MODE 2 (S % 8 == 0):
 // the eight warps of a CTA take eight consecutive segments of the same column tile and
 // leave ONE Partial per column, combined in warp order, at part[(seg / 8) * n_out + o].
+// The kernel is bound by the number of loads in flight, i.e. by resident warps: the sum's double accumulators put it at 53
+// registers, one short of five CTAs per SM (the maximum takes 48 and runs 13 % faster); asking for five costs three
+// spilled loop-invariant values.
+template <class Acc> struct ColsMinBlocks { static constexpr int value = 1; };
+template <> struct ColsMinBlocks<SumAcc> { static constexpr int value = 5; };
+
 template <int VEC, int OUT_KIND, int MODE, class Acc>
-__global__ void __launch_bounds__(256) k_cols_warp(const float* __restrict__ in, float* __restrict__ out, float* __restrict__ out_idx,
+__global__ void __launch_bounds__(256, ColsMinBlocks<Acc>::value) k_cols_warp(const float* __restrict__ in, float* __restrict__ out, float* __restrict__ out_idx,
                                                    typename Acc::Partial* __restrict__ part,
                                                    int64_t outer, int64_t A, int64_t inner, int S, int64_t seg_len,
                                                    int64_t col_tiles, int TX) {

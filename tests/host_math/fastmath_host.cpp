@@ -51,4 +51,49 @@ int64_t kfh_sweep(int fn, uint32_t stride, int64_t* counts) {
     return worst;
 }
 
+// x / b through the reciprocal of a shared divisor (kd_div_by_reciprocal) against the IEEE quotient.
+// mode 0: for `n` divisors (the first 64 with the mantissas nearest to all-ones and to 1.0, the rest seeded) every one of
+// the 2^23 dividend mantissas, which covers the divisor completely: the algorithm is invariant under scaling by powers
+// of two inside its window.  mode 1: n seeded pairs whose exponents span the whole window of both operands, signs mixed.
+// Returns the number of quotients that differ in any bit.
+int64_t kfh_div(int mode, int64_t n) {
+    int64_t bad = 0;
+    if (mode == 0) {
+        #pragma omp parallel for schedule(dynamic) reduction(+:bad)
+        for (int64_t k = 0; k < n; ++k) {
+            uint64_t s = 4242 + (uint64_t)k * 0x9E3779B97F4A7C15ull;
+            s ^= s >> 29; s *= 0xBF58476D1CE4E5B9ull; s ^= s >> 32;
+            uint32_t m = (uint32_t)(s & 0x7fffff);
+            if (k < 32) m = 0x7fffff - (uint32_t)k; else if (k < 64) m = (uint32_t)(k - 32);
+            const uint32_t bb = m | (127u << 23);
+            float b; std::memcpy(&b, &bb, 4);
+            const float r = ktc::kd_row_reciprocal(b);
+            for (uint32_t xm = 0; xm < (1u << 23); ++xm) {
+                const uint32_t xb = xm | (127u << 23);
+                float x; std::memcpy(&x, &xb, 4);
+                const float got = ktc::kd_div_by_reciprocal(x, b, r), want = x / b;
+                if (std::memcmp(&got, &want, 4) != 0) ++bad;
+            }
+        }
+    } else {
+        #pragma omp parallel for schedule(static) reduction(+:bad)
+        for (int64_t i = 0; i < n; ++i) {
+            uint64_t z = 77 + (uint64_t)i * 0x9E3779B97F4A7C15ull;
+            z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull; z = (z ^ (z >> 27)) * 0x94D049BB133111EBull; z ^= z >> 31;
+            uint64_t w = z * 0xD6E8FEB86659FD93ull; w ^= w >> 32;
+            const uint32_t xb = (uint32_t)(z & 0x807fffffu) | ((uint32_t)(64 + (z >> 40) % 128) << 23);     // the whole dividend window
+            const uint32_t bb = (uint32_t)(w & 0x807fffffu) | ((uint32_t)(67 + (w >> 40) % 120) << 23);     // 2^-60 .. 2^60 (exclusive)
+            float x, b; std::memcpy(&x, &xb, 4); std::memcpy(&b, &bb, 4);
+            const float r = ktc::kd_row_reciprocal(b);
+            if (r == 0.0f || ktc::kd_div_window(x) == 0u) { ++bad; continue; }     // both are inside by construction
+            const float got = ktc::kd_div_by_reciprocal(x, b, r), want = x / b;
+            if (std::memcmp(&got, &want, 4) != 0) ++bad;
+        }
+    }
+    return bad;
+}
+
+// 1 where the fast form may be used for this pair (what the kernel tests), else 0
+int kfh_div_accepts(float x, float b) { return (ktc::kd_row_reciprocal(b) != 0.0f && ktc::kd_div_window(x) != 0u) ? 1 : 0; }
+
 }  // extern "C"

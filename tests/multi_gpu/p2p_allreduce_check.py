@@ -4,8 +4,10 @@
         tests/multi_gpu/p2p_allreduce_check.py
 
 Checks the peer-memory all-reduce (ktc_p2p_allreduce_sum) against the rank-ordered float sum computed on
-the host and against NCCL within the reduction tolerance, over many calls and sizes, and times both.
-NVLS is not needed and is switched off for the NCCL leg."""
+the host and against NCCL within the reduction tolerance, over many calls and sizes, and times both; then
+the exchange folded into the second-pass kernel of a deferred training step (ktc_lazy_allreduce) against the
+rank-ordered host sum of the ranks' local results, bit for bit.  NVLS is not needed and is switched off for
+the NCCL leg.  tests/test_gpu_multi.py runs this file when the box has at least two GPUs."""
 import ctypes as C
 import json
 import os
@@ -72,6 +74,36 @@ def main() -> int:
                 print(f"rank {rank}: rep {rep} differs from NCCL", file=sys.stderr)
         for t in mine + again:
             t.release()
+
+    # the exchange inside the producing kernel: one deferred step of the sharded graph per rank
+    from kten_b200.sharded import ShardedSigmoidGraph
+    rows, cols = 4096, 1024
+    xs = D.normal(rows * cols, 31, 0.0, 1.0, stream=rank)
+    w, b = D.uniform(cols, 32, -0.5, 0.5), D.uniform(cols, 33, -0.5, 0.5)
+    ops.lazy = True
+    before = ops._recorder.stats()["folded_exchanges"]
+    local = ShardedSigmoidGraph(ops, ops.createRaw([rows, cols], xs), ops.createRaw([1, cols], w), ops.createRaw([cols], b))
+    mine = [t.toArray().reshape(-1).copy() for t in local.step()]                      # this rank's loss, gw, gb
+    local.release_step()
+    everyone = [None] * world
+    dist.all_gather_object(everyone, mine)
+    fused = ShardedSigmoidGraph(ops, ops.createRaw([rows, cols], xs), ops.createRaw([1, cols], w), ops.createRaw([cols], b), collective=p2p)
+    for step in range(3):                                                               # the first step compiles, the others hit the cache
+        got = [t.toArray().reshape(-1) for t in fused.step()]
+        p2p.check()
+        fused.release_step()
+        for i in range(3):
+            want = everyone[0][i].copy()
+            for r in range(1, world):
+                want = (want + everyone[r][i]).astype(np.float32)
+            if not np.array_equal(got[i].view(np.uint32), want.view(np.uint32)):
+                ok = False
+                print(f"rank {rank}: fused exchange, step {step}, tensor {i} differs from the rank-ordered sum", file=sys.stderr)
+    folded = ops._recorder.stats()["folded_exchanges"] - before
+    if folded != 3:
+        ok = False
+        print(f"rank {rank}: {folded} of 3 exchanges ran inside the second-pass kernel", file=sys.stderr)
+    ops.lazy = False
 
     # timing: loss [1] + gw [1, 1024] + gb [1024], as in the sharded graph
     ts = [ops.createRaw([n], D.uniform(n, 7, -1.0, 1.0, stream=rank)) for n in (1, 1024, 1024)]

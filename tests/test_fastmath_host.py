@@ -28,6 +28,10 @@ def host_math_library():
     lib = C.CDLL(SO)
     lib.kfh_sweep.restype = C.c_int64
     lib.kfh_sweep.argtypes = [C.c_int, C.c_uint32, C.POINTER(C.c_int64)]
+    lib.kfh_div.restype = C.c_int64
+    lib.kfh_div.argtypes = [C.c_int, C.c_int64]
+    lib.kfh_div_accepts.restype = C.c_int
+    lib.kfh_div_accepts.argtypes = [C.c_float, C.c_float]
     return lib
 
 
@@ -114,3 +118,28 @@ def test_special_arguments_of_exp_and_sigmoid(fm):
         assert np.array_equal(np.isnan(got), np.isnan(want)), fn
         keep = ~np.isnan(want)
         assert np.array_equal(got[keep].view(np.uint32), want[keep].view(np.uint32)), (fn, got, want)
+
+
+def test_division_by_a_shared_divisor_is_the_ieee_quotient(fm):
+    """q = x r, then q + (x - q b) r with r = RN(1 / b): the quotient of the broadcast division kernel.  Every
+    dividend mantissa against 1024 divisors (those nearest to all-ones and to 1.0 among them), and 2^28 seeded
+    pairs over the whole exponent window: not one bit differs from x / b."""
+    assert fm.kfh_div(0, 1024) == 0
+    assert fm.kfh_div(1, 1 << 28) == 0
+
+
+def test_division_by_a_shared_divisor_declines_what_it_cannot_do(fm):
+    inf, nan = float("inf"), float("nan")
+    for x, b in ((0.0, 2.0), (-0.0, 2.0), (inf, 2.0), (nan, 2.0), (1e-30, 2.0), (1e30, 2.0), (1e-45, 3.0),
+                 (1.0, 0.0), (1.0, inf), (1.0, nan), (1.0, 1e-30), (1.0, 1e30), (1.0, 1e-45), (3e38, 3.0)):
+        assert fm.kfh_div_accepts(x, b) == 0, (x, b)
+    for x, b in ((1.0, 3.0), (-7.5, 1e-18), (1.1e-19, -1e18), (1.8e19, 9e17)):
+        assert fm.kfh_div_accepts(x, b) == 1, (x, b)
+
+
+def test_tables_of_the_header_are_what_the_generator_prints():
+    pytest.importorskip("mpmath")
+    import sys
+    gen = os.path.join(HERE, "..", "kten_b200", "csrc", "gen_fastmath_d_tables.py")
+    r = subprocess.run([sys.executable, gen, "--check"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr

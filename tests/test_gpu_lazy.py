@@ -6,6 +6,8 @@ deep copies are independent) must hold whether or not a tensor has storage yet."
 import ctypes as C
 
 import numpy as np
+
+from oracle import oracle as O
 import pytest
 
 from kten_b200 import _lib as L
@@ -94,6 +96,19 @@ def test_chains_equal_call_by_call(lazy_ops, shapes):
     eager, lazy = both(lazy_ops, chain)
     for e, l in zip(eager, lazy):
         assert same_bits(e, l)
+    # and directly against the oracle: the exact operations reproduce it bit for bit; exp, sigmoid and pow differ from
+    # the narrowed double libm in fewer than one element per million, so chains of those agree in (nearly) every
+    # element; log and tanh are within 1 and 2 ulp (w, x)
+    want = [r.toArray() for r in chain(O.OracleTensorOperations())]
+    for name, l, o in zip("uvwxyz", lazy, want):
+        assert l.shape == o.shape, name
+        differing = int(np.count_nonzero(l.view(np.uint32) != o.view(np.uint32)))
+        if name in "uvyz":
+            assert differing <= max(1, l.size // 1000), (name, differing, l.size)
+        if name != "y":                                            # y is a comparison: 0 or 1
+            assert np.allclose(l, o, rtol=4e-6, atol=4e-6), name
+        if name in "uz":                                           # only exact operations
+            assert differing == 0, name
 
 
 def test_fused_path_is_the_one_that_runs(lazy_ops):

@@ -181,6 +181,42 @@ def test_broadcast_pow_and_tile_settings(cuda_ops, gc_scope):
         lib.ktc_tune_set(b"bcast_force_generic", 0)
 
 
+def test_broadcast_division_by_row_scalars(cuda_ops, gc_scope):
+    """a[I, J, K] / b[1, J, 1] divides by the rows' reciprocals where that is the IEEE quotient and by IEEE division
+    elsewhere: dividends and divisors of every kind (zeros of both signs, subnormals, huge, tiny, infinite, NaN,
+    negative), each divisor meeting each dividend, both batch sizes of the kernel, also as the scalar-first form
+    b / a, which must keep the ordinary path."""
+    lib = cuda_ops.lib
+    sv = special_values()
+    extra = np.array([1e-19, -1e-19, 1.0842e-19, 1.8e19, -1.8e19, 9.2e18, 2.0 ** -63, 2.0 ** 64, 2.0 ** 63.5, 2.0 ** -64,
+                      1e-30, 1e30, 3.0, 1.0 / 3.0, 0.99999994, 5e-39], dtype=np.float32)
+    vals = np.concatenate([sv, extra, D.normal(80, 5, 0.0, 1.0)])                    # 128 values
+    J, K = vals.size, 64
+    divisors = np.concatenate([sv, extra, np.array([2.0 ** -60, 2.0 ** 60, 2.0 ** -61, 2.0 ** 61, -(2.0 ** 60)], dtype=np.float32),
+                               D.uniform(J - sv.size - extra.size - 5, 6, 0.5, 2.0)]).astype(np.float32)
+    a = np.empty((3, J, K), dtype=np.float32)
+    for i in range(3):
+        for j in range(J):
+            a[i, j] = np.roll(vals, i * 7 + j)[:K]                                   # every divisor meets many kinds of dividends
+    a[1, :, :vals.size // 2] = vals[None, ::2]
+    a = a.reshape(-1)
+    ra, rb = cuda_ops.createRaw([3, J, K], a), cuda_ops.createRaw([1, J, 1], divisors)
+    want = O.binary(O.DIV, a, [3, J, K], divisors, [1, J, 1])[0]
+    want_rev = O.binary(O.DIV, divisors, [1, J, 1], a, [3, J, K])[0]
+    try:
+        for batch in (8, 4):
+            lib.ktc_tune_set(b"bcast_div_batch", batch)
+            assert same_bits(ra.div(rb).toArray(), want), batch
+            assert same_bits(rb.div(ra).toArray(), want_rev), batch
+    finally:
+        lib.ktc_tune_set(b"bcast_div_batch", 8)
+    big = D.normal(64 * 1024 * 256, 9, 0.0, 1.0)
+    big[::1000] = 0.0
+    bdiv = D.uniform(1024, 10, 0.5, 2.0)
+    got = cuda_ops.createRaw([64, 1024, 256], big).div(cuda_ops.createRaw([1, 1024, 1], bdiv)).toArray()
+    assert same_bits(got, O.binary(O.DIV, big, [64, 1024, 256], bdiv, [1, 1024, 1])[0])
+
+
 def test_broadcast_shape_mismatch_is_rejected(cuda_ops, gc_scope):
     a, b = cuda_ops.createRaw([2, 3]), cuda_ops.createRaw([4, 3])
     with pytest.raises(ValueError, match="non-singleton"):
