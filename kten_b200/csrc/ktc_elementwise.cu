@@ -159,7 +159,7 @@ template <> struct IsDiv<BinOp<KTC_DIV>> { static constexpr bool value = true; }
 // full-size (DIRECT) operands are issued first, then the broadcast operand is staged in
 // shared memory, so the staging latency overlaps the main stream instead of preceding it.
 template <int MODE_A, int MODE_B, int U, class F>
-__global__ void __launch_bounds__(256) k_bcast3(BcastArgs p, F f) {
+__global__ void __launch_bounds__(256, IsDiv<F>::value ? 3 : 1) k_bcast3(BcastArgs p, F f) {
     extern __shared__ __align__(16) float smem[];
     constexpr bool STAGE_A = (MODE_A == AM_SMEMROW || MODE_A == AM_ROWSCALAR);
     constexpr bool STAGE_B = (MODE_B == AM_SMEMROW || MODE_B == AM_ROWSCALAR);

@@ -9,12 +9,14 @@
 // costs 4-5x the HBM time of the kernel; float-float arithmetic reaches the correctly rounded
 // float only with ~50 instructions per element and a rounding test.  B200 issues a double fma
 // at half the float rate, so a table-driven reduction plus a degree-5 polynomial in double
-// (8 double operations for exp, 19 for pow) gives a value within 2^-42 of the true one -- the
-// narrowing then returns the correctly rounded float except for about one argument in 2^17 --
-// at roughly half the instruction count of the float-float versions.
+// (9 double operations for exp, 18 for pow) gives a value within 2^-42 of the true one (2^-45
+// on average) -- the narrowing then returns the float the double libm's result narrows to
+// except for fewer than one argument in a million (measured on the host, bit for bit) -- at
+// roughly two thirds of the issue slots of the float-float versions.
 //
-// Tables are tiny on purpose: the 16 doubles of 2^(j/16) are one 128-byte line, so a warp's
-// lookups are served in one pass of the L1 pipeline.
+// Tables are small on purpose: the 16 doubles of 2^(j/16) are one 128-byte line, so a warp's
+// lookups are served in one pass of the L1 pipeline; the 64-entry table is used only where one
+// double operation less is worth three more passes.
 #pragma once
 
 #include <stdint.h>
@@ -53,8 +55,8 @@ KD_TABLE KD_ALIGN(128) double kd_exp2_tab[16] = {
     0x1.ea4afa2a490dap+0    /* 1.9152065613971474 */
 };
 
-// 2^(j/64), j = 0..63: four cache lines.  exp and sigmoid reduce to |z| <= ln2/128 with it, where a degree-4
-// polynomial truncates below 2^-44.5; pow keeps the 16-entry table (its logarithm tables already occupy the L1 pipe).
+// 2^(j/64), j = 0..63: four cache lines.  sigmoid reduces to |z| <= ln2/128 with it, where a degree-4 polynomial
+// truncates below 2^-44.5 (kd_exp_wide); exp and pow keep the 16-entry table.
 KD_TABLE KD_ALIGN(128) double kd_exp2_tab64[64] = {
     0x1.0000000000000p+0, 0x1.02c9a3e778061p+0, 0x1.059b0d3158574p+0, 0x1.0874518759bc8p+0,
     0x1.0b5586cf9890fp+0, 0x1.0e3ec32d3d1a2p+0, 0x1.11301d0125b51p+0, 0x1.1429aaea92de0p+0,
@@ -163,13 +165,25 @@ KD_FN double kd_scaled_tab(int32_t k) {
     return KD_MAKE(KD_HI32(t) + ((k >> 4) << 20), KD_LO32(t));
 }
 
-// exp(t) for |t| <= 700: t = k ln2/64 + z, |z| <= ln2/128, exp(t) = 2^(k/64) (1 + z + z^2/2 + z^3/6 + z^4/24); the
-// truncation is below 2^-44.5 relative at the edge of the reduced range (2^-47 on average), rounding adds about 2^-52
-#ifndef KD_EXP_WIDE_TABLE
-#define KD_EXP_WIDE_TABLE 1
-#endif
+// exp(t) for |t| <= 700 with the 16-entry table: t = k ln2/16 + z, |z| <= ln2/32, degree 5; relative error below
+// 2^-42 (truncation 2^-42.7 at the edge of the reduced range, 2^-45 on average).  The plain exp kernel is bound by
+// memory, and the one cache line of this table leaves the L1 pipe to the data stream.
 KD_FN double kd_exp(double t) {
-#if KD_EXP_WIDE_TABLE
+    const double v = fma(t, KD_K(KD_C_16_LN2), KD_K(KD_C_MAGIC));
+    const double kd = v - KD_K(KD_C_MAGIC);                            // nearest integer to t * 16 / ln2
+    const double z = fma(kd, KD_K(KD_C_LN2_16), t);                    // t - k * ln2/16
+    double p = fma(z, KD_K(KD_C_E5), KD_K(KD_C_E4));
+    p = fma(p, z, KD_K(KD_C_E3));
+    p = fma(p, z, 0.5);
+    p = fma(p, z, 1.0);
+    p = fma(p, z, 1.0);
+    return kd_scaled_tab(KD_LO32(v)) * p;
+}
+
+// The same with the 64-entry table: |z| <= ln2/128, degree 4, truncation below 2^-44.5 at the edge.  One double
+// operation fewer for three more cache lines per warp lookup: the choice where instruction issue is the bound
+// (sigmoid, and the fused training-step kernels built on it: measured 2 % faster, plain exp 3 % slower).
+KD_FN double kd_exp_wide(double t) {
     const double v = fma(t, KD_K(KD_C_64_LN2), KD_K(KD_C_MAGIC));
     const double kd = v - KD_K(KD_C_MAGIC);                            // nearest integer to t * 64 / ln2
     const double z = fma(kd, KD_K(KD_C_LN2_64), t);                    // t - k * ln2/64
@@ -180,17 +194,6 @@ KD_FN double kd_exp(double t) {
     const int32_t k = KD_LO32(v);
     const double s = KD_EXP2_TAB64(k & 63);
     return KD_MAKE(KD_HI32(s) + ((k >> 6) << 20), KD_LO32(s)) * p;
-#else
-    const double v = fma(t, KD_K(KD_C_16_LN2), KD_K(KD_C_MAGIC));
-    const double kd = v - KD_K(KD_C_MAGIC);                            // nearest integer to t * 16 / ln2
-    const double z = fma(kd, KD_K(KD_C_LN2_16), t);                    // t - k * ln2/16, |z| <= ln2/32
-    double p = fma(z, KD_K(KD_C_E5), KD_K(KD_C_E4));
-    p = fma(p, z, KD_K(KD_C_E3));
-    p = fma(p, z, 0.5);
-    p = fma(p, z, 1.0);
-    p = fma(p, z, 1.0);
-    return kd_scaled_tab(KD_LO32(v)) * p;
-#endif
 }
 
 // Math.max / Math.min-style clamps that keep a NaN argument
@@ -249,7 +252,7 @@ KD_FN float kd_div_by_reciprocal(float x, float b, float r) {
 // below KD_RCP_FAST_LIMIT and the IEEE reciprocal otherwise -- the same bits either way where both apply.
 KD_FN float kd_sigmoid_den(float x) {
     const float xc = kd_max_nan(kd_min_nan(x, 30.0f), -89.0f);
-    const float e = (float)kd_exp(-(double)xc);
+    const float e = (float)kd_exp_wide(-(double)xc);
     return 1.0f + e;
 }
 KD_FN float kd_sigmoid(float x) {
@@ -296,21 +299,6 @@ KD_FN float kd_pow(float x, float y, bool* ok) {
     const int32_t ix = KD_F2I(x);
     const double p = kd_log2(ix) * (double)y;
     *ok = ((uint32_t)(ix - 0x00800000) < 0x7f000000u) && ((uint32_t)(KD_HI32(p) & 0x7fffffff) < 0x40640000u);
-#ifndef KD_POW_WIDE_TABLE
-#define KD_POW_WIDE_TABLE 0
-#endif
-#if KD_POW_WIDE_TABLE
-    const double v = fma(p, 64.0, KD_K(KD_C_MAGIC));
-    const double kd = v - KD_K(KD_C_MAGIC);
-    const double z = fma(kd, -0.015625, p);                           // p - k/64 exactly, |z| <= 1/128
-    double s = fma(z, KD_K(KD_C_P4), KD_K(KD_C_P3));                   // 2^z = 1 + z ln2 + (z ln2)^2 / 2 + ...
-    s = fma(s, z, KD_K(KD_C_P2));
-    s = fma(s, z, KD_K(KD_C_P1));
-    s = fma(s, z, 1.0);
-    const int32_t k = KD_LO32(v);
-    const double t = KD_EXP2_TAB64(k & 63);
-    return (float)(KD_MAKE(KD_HI32(t) + ((k >> 6) << 20), KD_LO32(t)) * s);
-#else
     const double v = fma(p, 16.0, KD_K(KD_C_MAGIC));
     const double kd = v - KD_K(KD_C_MAGIC);
     const double z = fma(kd, -0.0625, p);                             // p - k/16 exactly, |z| <= 1/32
@@ -320,7 +308,6 @@ KD_FN float kd_pow(float x, float y, bool* ok) {
     s = fma(s, z, KD_K(KD_C_P1));
     s = fma(s, z, 1.0);
     return (float)(kd_scaled_tab(KD_LO32(v)) * s);
-#endif
 }
 
 }  // namespace ktc

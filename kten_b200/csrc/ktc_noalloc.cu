@@ -142,7 +142,7 @@ extern "C" int ktc_reduce_all_noalloc(int op, ktc_buf out, ktc_buf in, int64_t n
     if (bo.dev != bi.dev) return fail(KTC_EINVAL, "ktc_reduce_all_noalloc: buffers live on devices %d and %d", bo.dev, bi.dev);
     if (bi.n < n) return fail(KTC_EINVAL, "ktc_reduce_all_noalloc: in holds %lld floats, %lld needed", (long long)bi.n, (long long)n);
     if (bo.n < 1) return fail(KTC_EINVAL, "ktc_reduce_all_noalloc: out holds no float");
-    if (bo.ptr == bi.ptr) return fail(KTC_EINVAL, "ktc_reduce_all_noalloc: out aliases in");
+    if (bo.ptr >= bi.ptr && bo.ptr < bi.ptr + n) return fail(KTC_EINVAL, "ktc_reduce_all_noalloc: out lies inside the elements of in that are read");
     Device* d = device(bi.dev); if (!d) return KTC_ESTATE;
     if (!d->ready) return fail(KTC_ESTATE, "ktc_reduce_all_noalloc: device %d has no compute stream yet", d->id);
     KTC_CUDA(cudaSetDevice(d->id));

@@ -150,14 +150,16 @@ __global__ void __launch_bounds__(256) k_rows_warp(const float* __restrict__ in,
 // MODE 0: final values (S == 1).  MODE 1: one Partial per segment.  MODE 2 (S % 8 == 0):
 // the eight warps of a CTA take eight consecutive segments of the same column tile and
 // leave ONE Partial per column, combined in warp order, at part[(seg / 8) * n_out + o].
-// The kernel is bound by the number of loads in flight, i.e. by resident warps: the sum's double accumulators put it at 53
-// registers, one short of five CTAs per SM (the maximum takes 48 and runs 13 % faster); asking for five costs three
-// spilled loop-invariant values.
-template <class Acc> struct ColsMinBlocks { static constexpr int value = 1; };
-template <> struct ColsMinBlocks<SumAcc> { static constexpr int value = 5; };
+// The kernel is bound by the number of loads in flight.  Measured on the middle-axis sum of [512, 4096, 128]: one batch
+// of 8 float4 per lane at five CTAs per SM (48 registers) 6200 GB/s; two batches in flight per lane -- the next one
+// requested before the current one is added -- at two CTAs per SM (120 registers) 6840 GB/s, level with the maximum,
+// whose begin / end are empty so that the compiler overlaps its batches by itself.  Few warps with many requests each
+// beat many warps with few.
+template <class Acc> struct ColsPipelined { static constexpr bool value = false; };
+template <> struct ColsPipelined<SumAcc> { static constexpr bool value = true; };
 
-template <int VEC, int OUT_KIND, int MODE, class Acc>
-__global__ void __launch_bounds__(256, ColsMinBlocks<Acc>::value) k_cols_warp(const float* __restrict__ in, float* __restrict__ out, float* __restrict__ out_idx,
+template <int VEC, int OUT_KIND, int MODE, class Acc, int PIPE = 0>
+__global__ void __launch_bounds__(256, PIPE == 0 ? 1 : 2) k_cols_warp(const float* __restrict__ in, float* __restrict__ out, float* __restrict__ out_idx,
                                                    typename Acc::Partial* __restrict__ part,
                                                    int64_t outer, int64_t A, int64_t inner, int S, int64_t seg_len,
                                                    int64_t col_tiles, int TX) {
@@ -190,7 +192,71 @@ __global__ void __launch_bounds__(256, ColsMinBlocks<Acc>::value) k_cols_warp(co
         const int64_t step = (int64_t)TYW * inner;            // floats between this lane's consecutive rows
         int64_t j = j0 + tyw;
         const float* pj = p + j * inner;
-        if (VEC == 4) {
+        if (VEC == 4 && PIPE != 0) {
+            // Two batches of U loads in flight per lane: the next batch is requested before the current one is added, so a
+            // warp keeps 16 float4 outstanding without waiting in between.  Same order of additions as below for full
+            // groups: float runs of 4 batches (32 values), folded into the doubles.
+            const int64_t bstep = (int64_t)TYW * U;
+            const int64_t nb = (j + (int64_t)TYW * (U - 1) < j1) ? (j1 - 1 - j - (int64_t)TYW * (U - 1)) / bstep + 1 : 0;
+            float4 va[U], vb[U];
+            const float* q = pj;                               // the next row to request: one running address, no table of offsets
+            if (nb > 0) {
+                #pragma unroll
+                for (int u = 0; u < U; ++u, q += step) va[u] = __ldcs(reinterpret_cast<const float4*>(q));
+            }
+            int64_t b = 0;
+            for (; b + 1 < nb; b += 2) {
+                #pragma unroll
+                for (int u = 0; u < U; ++u, q += step) vb[u] = __ldcs(reinterpret_cast<const float4*>(q));
+                if ((b & 3) == 0) {
+                    #pragma unroll
+                    for (int k = 0; k < VEC; ++k) acc[k].begin();
+                }
+                #pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int jj = (int)(j + (int64_t)u * TYW);
+                    acc[0].add(va[u].x, jj); acc[1 % VEC].add(va[u].y, jj); acc[2 % VEC].add(va[u].z, jj); acc[3 % VEC].add(va[u].w, jj);
+                }
+                if (b + 2 < nb) {
+                    #pragma unroll
+                    for (int u = 0; u < U; ++u, q += step) va[u] = __ldcs(reinterpret_cast<const float4*>(q));
+                }
+                #pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int jj = (int)(j + bstep + (int64_t)u * TYW);
+                    acc[0].add(vb[u].x, jj); acc[1 % VEC].add(vb[u].y, jj); acc[2 % VEC].add(vb[u].z, jj); acc[3 % VEC].add(vb[u].w, jj);
+                }
+                if ((b & 3) == 2) {
+                    #pragma unroll
+                    for (int k = 0; k < VEC; ++k) acc[k].end();
+                }
+                j += 2 * bstep;
+            }
+            if (b < nb) {                                      // an odd batch is left in va
+                if ((b & 3) == 0) {
+                    #pragma unroll
+                    for (int k = 0; k < VEC; ++k) acc[k].begin();
+                }
+                #pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int jj = (int)(j + (int64_t)u * TYW);
+                    acc[0].add(va[u].x, jj); acc[1 % VEC].add(va[u].y, jj); acc[2 % VEC].add(va[u].z, jj); acc[3 % VEC].add(va[u].w, jj);
+                }
+                j += bstep;
+            }
+            pj = q;                                            // q has passed exactly the nb full batches
+            // the open run, if any, takes the remaining rows too
+            if (nb == 0 || (nb & 3) == 0) {
+                #pragma unroll
+                for (int k = 0; k < VEC; ++k) acc[k].begin();
+            }
+            for (; j < j1; j += TYW, pj += step) {
+                const float4 v = __ldcs(reinterpret_cast<const float4*>(pj));
+                acc[0].add(v.x, (int)j); acc[1 % VEC].add(v.y, (int)j); acc[2 % VEC].add(v.z, (int)j); acc[3 % VEC].add(v.w, (int)j);
+            }
+            #pragma unroll
+            for (int k = 0; k < VEC; ++k) acc[k].end();
+        } else if (VEC == 4) {
             // four batches per fold into the double accumulators (32 values per float run)
             for (; j + (int64_t)TYW * (4 * U - 1) < j1;) {
                 #pragma unroll
@@ -362,9 +428,13 @@ static int run_reduce(Device* d, float* out, float* out_idx, const float* in, in
     } else {
         const int mode = p.S == 1 ? 0 : (p.S_out == p.S ? 1 : 2);
 #define KTC_CW(V, M) k_cols_warp<V, OUT_KIND, M, Acc><<<grid, 256, 0, d->stream>>>(in, out, out_idx, part, outer, A, inner, p.S, p.seg_len, p.col_tiles, p.tx)
-        if (p.vec == 4) { if (mode == 0) KTC_CW(4, 0); else if (mode == 1) KTC_CW(4, 1); else KTC_CW(4, 2); }
+#define KTC_CWP(M, P) k_cols_warp<4, OUT_KIND, M, Acc, P><<<grid, 256, 0, d->stream>>>(in, out, out_idx, part, outer, A, inner, p.S, p.seg_len, p.col_tiles, p.tx)
+        constexpr int kPipe = ColsPipelined<Acc>::value ? 1 : 0;
+        if (p.vec == 4 && kPipe == 1 && tune("cols_sum_pipe", 1) == 1) { if (mode == 0) KTC_CWP(0, kPipe); else if (mode == 1) KTC_CWP(1, kPipe); else KTC_CWP(2, kPipe); }
+        else if (p.vec == 4) { if (mode == 0) KTC_CW(4, 0); else if (mode == 1) KTC_CW(4, 1); else KTC_CW(4, 2); }
         else            { if (mode == 0) KTC_CW(1, 0); else if (mode == 1) KTC_CW(1, 1); else KTC_CW(1, 2); }
 #undef KTC_CW
+#undef KTC_CWP
     }
     KTC_TRY(finish_launch(p.kind == 1 ? "rows_warp" : "cols_warp"));
     if (p.S > 1) {

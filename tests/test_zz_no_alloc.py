@@ -83,6 +83,11 @@ def test_noalloc_rejects_what_it_was_not_built_for():
         assert lib.ktc_reduce_all_noalloc(L.SUM, h_out, h_in, 17) == L.KTC_EINVAL        # more than the buffer holds
         assert lib.ktc_reduce_all_noalloc(L.MAX, h_out, h_in, 16) == L.KTC_EINVAL
         assert lib.ktc_reduce_all_noalloc(L.SUM, h_in, h_in, 16) == L.KTC_EINVAL          # out aliases in
+        inside = C.c_uint64(0)
+        L.check(lib.ktc_view(h_in, 5, 1, C.byref(inside)))                                # a view inside the input
+        assert lib.ktc_reduce_all_noalloc(L.SUM, inside.value, h_in, 16) == L.KTC_EINVAL
+        L.check(lib.ktc_reduce_all_noalloc(L.SUM, inside.value, h_in, 5))                  # behind the elements that are read: fine
+        lib.ktc_release(inside.value)
         _upload(lib, h_in, np.arange(16, dtype=np.float32))
         L.check(lib.ktc_reduce_all_noalloc(L.MEAN, h_out, h_in, 16))
         assert _read1(lib, h_out) == np.float32(7.5)
