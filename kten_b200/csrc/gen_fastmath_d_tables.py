@@ -1,7 +1,9 @@
 """Prints the constant tables of ktc_fastmath_d.h (run: python gen_fastmath_d_tables.py [--check]).
 
-kd_exp2_tab[j]     = 2^(j/16) rounded to double, j = 0..15          (pow)
-kd_exp2_tab64[j]   = 2^(j/64) rounded to double, j = 0..63          (exp, sigmoid)
+kd_exp2_tab[j]     = 2^(j/16) rounded to double, high word lowered by j << 16, j = 0..15   (exp, pow)
+kd_exp2_tab64[j]   = 2^(j/64) rounded to double, high word lowered by j << 14, j = 0..63   (sigmoid)
+                     (the bias lets the code add k << 16 resp. k << 14 to the high word: the table index in the
+                     low bits of k cancels against it and k's upper part lands in the exponent field)
 kd_log2_inv_hi[j]  = high word of inv_j, kd_log2_lc[j] = -log2(inv_j) for the 32 equal slices (in bit-pattern
                      space) of [sqrt(1/2), sqrt(2)): inv_j is 1/centre rounded to 13 significant bits, so that
                      its low word is zero and the product of a float mantissa with it is exact in double; the
@@ -34,9 +36,14 @@ def hi_word(d):
     return struct.unpack("<q", struct.pack("<d", d))[0] >> 32
 
 
+def biased(d, bias):
+    bits = struct.unpack("<q", struct.pack("<d", d))[0] - (bias << 32)
+    return struct.unpack("<d", struct.pack("<q", bits))[0]
+
+
 def tables():
-    exp16 = [float(mpf(2) ** (mpf(j) / 16)) for j in range(16)]
-    exp64 = [float(mpf(2) ** (mpf(j) / 64)) for j in range(64)]
+    exp16 = [biased(float(mpf(2) ** (mpf(j) / 16)), j << 16) for j in range(16)]
+    exp64 = [biased(float(mpf(2) ** (mpf(j) / 64)), j << 14) for j in range(64)]
     inv_hi, lc, worst = [], [], mpf(0)
     for j in range(32):
         b0, b1 = LO + (j << 18), LO + ((j + 1) << 18) - 1

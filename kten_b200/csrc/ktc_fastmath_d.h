@@ -35,45 +35,35 @@
 
 namespace ktc {
 
-// 2^(j/16), j = 0..15 (gen_fastmath_d_tables.py)
+// 2^(j/16), j = 0..15, with the high word lowered by j << 16 (gen_fastmath_d_tables.py): adding k << 16 to the high
+// word of entry k & 15 gives 2^(k/16) -- the index bits of k cancel against the bias and k >> 4 lands in the exponent
+// field -- with one integer multiply-add instead of a mask, a shift and an add.
 KD_TABLE KD_ALIGN(128) double kd_exp2_tab[16] = {
-    0x1.0000000000000p+0,   /* 1.0 */
-    0x1.0b5586cf9890fp+0,   /* 1.0442737824274138 */
-    0x1.172b83c7d517bp+0,   /* 1.0905077326652577 */
-    0x1.2387a6e756238p+0,   /* 1.1387886347566916 */
-    0x1.306fe0a31b715p+0,   /* 1.189207115002721 */
-    0x1.3dea64c123422p+0,   /* 1.241857812073484 */
-    0x1.4bfdad5362a27p+0,   /* 1.2968395546510096 */
-    0x1.5ab07dd485429p+0,   /* 1.3542555469368927 */
-    0x1.6a09e667f3bcdp+0,   /* 1.4142135623730951 */
-    0x1.7a11473eb0187p+0,   /* 1.4768261459394993 */
-    0x1.8ace5422aa0dbp+0,   /* 1.5422108254079407 */
-    0x1.9c49182a3f090p+0,   /* 1.6104903319492543 */
-    0x1.ae89f995ad3adp+0,   /* 1.681792830507429 */
-    0x1.c199bdd85529cp+0,   /* 1.7562521603732995 */
-    0x1.d5818dcfba487p+0,   /* 1.8340080864093424 */
-    0x1.ea4afa2a490dap+0    /* 1.9152065613971474 */
+    0x1.0000000000000p+0, 0x1.fb5586cf9890fp-1, 0x1.f72b83c7d517bp-1, 0x1.f387a6e756238p-1,
+    0x1.f06fe0a31b715p-1, 0x1.edea64c123422p-1, 0x1.ebfdad5362a27p-1, 0x1.eab07dd485429p-1,
+    0x1.ea09e667f3bcdp-1, 0x1.ea11473eb0187p-1, 0x1.eace5422aa0dbp-1, 0x1.ec49182a3f090p-1,
+    0x1.ee89f995ad3adp-1, 0x1.f199bdd85529cp-1, 0x1.f5818dcfba487p-1, 0x1.fa4afa2a490dap-1
 };
 
-// 2^(j/64), j = 0..63: four cache lines.  sigmoid reduces to |z| <= ln2/128 with it, where a degree-4 polynomial
+// 2^(j/64), j = 0..63, high word lowered by j << 14: four cache lines.  sigmoid reduces to |z| <= ln2/128 with it, where a degree-4 polynomial
 // truncates below 2^-44.5 (kd_exp_wide); exp and pow keep the 16-entry table.
 KD_TABLE KD_ALIGN(128) double kd_exp2_tab64[64] = {
-    0x1.0000000000000p+0, 0x1.02c9a3e778061p+0, 0x1.059b0d3158574p+0, 0x1.0874518759bc8p+0,
-    0x1.0b5586cf9890fp+0, 0x1.0e3ec32d3d1a2p+0, 0x1.11301d0125b51p+0, 0x1.1429aaea92de0p+0,
-    0x1.172b83c7d517bp+0, 0x1.1a35beb6fcb75p+0, 0x1.1d4873168b9aap+0, 0x1.2063b88628cd6p+0,
-    0x1.2387a6e756238p+0, 0x1.26b4565e27cddp+0, 0x1.29e9df51fdee1p+0, 0x1.2d285a6e4030bp+0,
-    0x1.306fe0a31b715p+0, 0x1.33c08b26416ffp+0, 0x1.371a7373aa9cbp+0, 0x1.3a7db34e59ff7p+0,
-    0x1.3dea64c123422p+0, 0x1.4160a21f72e2ap+0, 0x1.44e086061892dp+0, 0x1.486a2b5c13cd0p+0,
-    0x1.4bfdad5362a27p+0, 0x1.4f9b2769d2ca7p+0, 0x1.5342b569d4f82p+0, 0x1.56f4736b527dap+0,
-    0x1.5ab07dd485429p+0, 0x1.5e76f15ad2148p+0, 0x1.6247eb03a5585p+0, 0x1.6623882552225p+0,
-    0x1.6a09e667f3bcdp+0, 0x1.6dfb23c651a2fp+0, 0x1.71f75e8ec5f74p+0, 0x1.75feb564267c9p+0,
-    0x1.7a11473eb0187p+0, 0x1.7e2f336cf4e62p+0, 0x1.82589994cce13p+0, 0x1.868d99b4492edp+0,
-    0x1.8ace5422aa0dbp+0, 0x1.8f1ae99157736p+0, 0x1.93737b0cdc5e5p+0, 0x1.97d829fde4e50p+0,
-    0x1.9c49182a3f090p+0, 0x1.a0c667b5de565p+0, 0x1.a5503b23e255dp+0, 0x1.a9e6b5579fdbfp+0,
-    0x1.ae89f995ad3adp+0, 0x1.b33a2b84f15fbp+0, 0x1.b7f76f2fb5e47p+0, 0x1.bcc1e904bc1d2p+0,
-    0x1.c199bdd85529cp+0, 0x1.c67f12e57d14bp+0, 0x1.cb720dcef9069p+0, 0x1.d072d4a07897cp+0,
-    0x1.d5818dcfba487p+0, 0x1.da9e603db3285p+0, 0x1.dfc97337b9b5fp+0, 0x1.e502ee78b3ff6p+0,
-    0x1.ea4afa2a490dap+0, 0x1.efa1bee615a27p+0, 0x1.f50765b6e4540p+0, 0x1.fa7c1819e90d8p+0
+    0x1.0000000000000p+0, 0x1.fec9a3e778061p-1, 0x1.fd9b0d3158574p-1, 0x1.fc74518759bc8p-1,
+    0x1.fb5586cf9890fp-1, 0x1.fa3ec32d3d1a2p-1, 0x1.f9301d0125b51p-1, 0x1.f829aaea92de0p-1,
+    0x1.f72b83c7d517bp-1, 0x1.f635beb6fcb75p-1, 0x1.f54873168b9aap-1, 0x1.f463b88628cd6p-1,
+    0x1.f387a6e756238p-1, 0x1.f2b4565e27cddp-1, 0x1.f1e9df51fdee1p-1, 0x1.f1285a6e4030bp-1,
+    0x1.f06fe0a31b715p-1, 0x1.efc08b26416ffp-1, 0x1.ef1a7373aa9cbp-1, 0x1.ee7db34e59ff7p-1,
+    0x1.edea64c123422p-1, 0x1.ed60a21f72e2ap-1, 0x1.ece086061892dp-1, 0x1.ec6a2b5c13cd0p-1,
+    0x1.ebfdad5362a27p-1, 0x1.eb9b2769d2ca7p-1, 0x1.eb42b569d4f82p-1, 0x1.eaf4736b527dap-1,
+    0x1.eab07dd485429p-1, 0x1.ea76f15ad2148p-1, 0x1.ea47eb03a5585p-1, 0x1.ea23882552225p-1,
+    0x1.ea09e667f3bcdp-1, 0x1.e9fb23c651a2fp-1, 0x1.e9f75e8ec5f74p-1, 0x1.e9feb564267c9p-1,
+    0x1.ea11473eb0187p-1, 0x1.ea2f336cf4e62p-1, 0x1.ea589994cce13p-1, 0x1.ea8d99b4492edp-1,
+    0x1.eace5422aa0dbp-1, 0x1.eb1ae99157736p-1, 0x1.eb737b0cdc5e5p-1, 0x1.ebd829fde4e50p-1,
+    0x1.ec49182a3f090p-1, 0x1.ecc667b5de565p-1, 0x1.ed503b23e255dp-1, 0x1.ede6b5579fdbfp-1,
+    0x1.ee89f995ad3adp-1, 0x1.ef3a2b84f15fbp-1, 0x1.eff76f2fb5e47p-1, 0x1.f0c1e904bc1d2p-1,
+    0x1.f199bdd85529cp-1, 0x1.f27f12e57d14bp-1, 0x1.f3720dcef9069p-1, 0x1.f472d4a07897cp-1,
+    0x1.f5818dcfba487p-1, 0x1.f69e603db3285p-1, 0x1.f7c97337b9b5fp-1, 0x1.f902ee78b3ff6p-1,
+    0x1.fa4afa2a490dap-1, 0x1.fba1bee615a27p-1, 0x1.fd0765b6e4540p-1, 0x1.fe7c1819e90d8p-1
 };
 
 // For the 32 equal slices (in bit-pattern space) of [sqrt(1/2), sqrt(2)): inv = 1/centre rounded to 13
@@ -158,11 +148,10 @@ KD_FN float kd_i2f(int32_t i) { float f; memcpy(&f, &i, 4); return f; }
 #define KD_EXP2_TAB64(j) (kd_exp2_tab64[j])
 #endif
 
-// 2^(k/16) * (1 + c1 z + c2 z^2 + ... + c5 z^5) for a reduced argument: the table value's exponent field
-// takes k >> 4 directly (the result stays far inside the double range for |k| < 2^14).
+// 2^(k/16) for |k| < 2^14 (the result stays far inside the double range): see the bias of kd_exp2_tab.
 KD_FN double kd_scaled_tab(int32_t k) {
     const double t = KD_EXP2_TAB(k & 15);
-    return KD_MAKE(KD_HI32(t) + ((k >> 4) << 20), KD_LO32(t));
+    return KD_MAKE((int32_t)((uint32_t)KD_HI32(t) + ((uint32_t)k << 16)), KD_LO32(t));
 }
 
 // exp(t) for |t| <= 700 with the 16-entry table: t = k ln2/16 + z, |z| <= ln2/32, degree 5; relative error below
@@ -193,7 +182,7 @@ KD_FN double kd_exp_wide(double t) {
     p = fma(p, z, 1.0);
     const int32_t k = KD_LO32(v);
     const double s = KD_EXP2_TAB64(k & 63);
-    return KD_MAKE(KD_HI32(s) + ((k >> 6) << 20), KD_LO32(s)) * p;
+    return KD_MAKE((int32_t)((uint32_t)KD_HI32(s) + ((uint32_t)k << 14)), KD_LO32(s)) * p;
 }
 
 // Math.max / Math.min-style clamps that keep a NaN argument

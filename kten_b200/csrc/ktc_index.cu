@@ -40,13 +40,15 @@ inline int finish(const char* what) {
 }
 
 // T = float or float4; FILL: no source; I = type of the linear index that is decomposed (32-bit when the
-// box is small enough).  A thread moves four items, 256 apart, and issues its four loads before the stores.
-template <class T, bool FILL, class I>
+// box is small enough).  A thread moves U items, 256 apart, and issues all its loads before the first store (eight
+// float4 in flight per thread: what the streaming kernels of this library need to reach the HBM rate); every element is
+// touched once, hence the streaming hints.
+template <class T, bool FILL, class I, int U>
 __global__ void __launch_bounds__(256) k_copy_nd(T* __restrict__ dst, const T* __restrict__ src, const __grid_constant__ NdArgs a, T v) {
-    const int64_t base = (int64_t)blockIdx.x * 1024 + threadIdx.x;
-    int64_t doff[4], soff[4];
+    const int64_t base = (int64_t)blockIdx.x * (256 * U) + threadIdx.x;
+    int64_t doff[U], soff[U];
     #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < U; ++u) {
         const int64_t i = base + u * 256;
         I rem = (I)(i < a.total ? i : 0);
         int64_t dd = 0, ss = 0;
@@ -61,11 +63,11 @@ __global__ void __launch_bounds__(256) k_copy_nd(T* __restrict__ dst, const T* _
         doff[u] = dd + (int64_t)rem * a.dstr[0];
         soff[u] = FILL ? 0 : ss + (int64_t)rem * a.sstr[0];
     }
-    T val[4];
+    T val[U];
     #pragma unroll
-    for (int u = 0; u < 4; ++u) val[u] = FILL ? v : ((base + u * 256 < a.total) ? src[soff[u]] : v);
+    for (int u = 0; u < U; ++u) val[u] = FILL ? v : ((base + u * 256 < a.total) ? __ldcs(src + soff[u]) : v);
     #pragma unroll
-    for (int u = 0; u < 4; ++u) if (base + u * 256 < a.total) dst[doff[u]] = val[u];
+    for (int u = 0; u < U; ++u) if (base + u * 256 < a.total) __stcs(dst + doff[u], val[u]);
 }
 
 // src is contiguous along dimension P, dst along dimension Q (P != Q): tiles of 64 x 64 over (P, Q); a thread
@@ -449,26 +451,26 @@ int launch_copy_nd(Device* d, float* dst, const int64_t* dstr, const float* src,
         a.shape[m - 1] /= 4;
         for (int i = 0; i < m - 1; ++i) { a.dstr[i] /= 4; a.sstr[i] /= 4; }
         a.total = total / 4;
-        const int64_t grid = grid_of(a.total, 1024);
+        const int64_t grid = grid_of(a.total, 2048);             // 256 threads x 8 items
         if (grid > 0x7fffffffLL) return fail(KTC_ENOTSUP, "tensor too large for one launch");
         const float4 v4 = make_float4(value, value, value, value);
         float4* d4 = reinterpret_cast<float4*>(dst);
         const float4* s4 = reinterpret_cast<const float4*>(src);
         const bool small = a.total < (1LL << 31);
-        if (fill) { if (small) k_copy_nd<float4, true, uint32_t><<<(int)grid, 256, 0, d->stream>>>(d4, nullptr, a, v4);
-                    else k_copy_nd<float4, true, int64_t><<<(int)grid, 256, 0, d->stream>>>(d4, nullptr, a, v4); }
-        else      { if (small) k_copy_nd<float4, false, uint32_t><<<(int)grid, 256, 0, d->stream>>>(d4, s4, a, v4);
-                    else k_copy_nd<float4, false, int64_t><<<(int)grid, 256, 0, d->stream>>>(d4, s4, a, v4); }
+        if (fill) { if (small) k_copy_nd<float4, true, uint32_t, 8><<<(int)grid, 256, 0, d->stream>>>(d4, nullptr, a, v4);
+                    else k_copy_nd<float4, true, int64_t, 8><<<(int)grid, 256, 0, d->stream>>>(d4, nullptr, a, v4); }
+        else      { if (small) k_copy_nd<float4, false, uint32_t, 8><<<(int)grid, 256, 0, d->stream>>>(d4, s4, a, v4);
+                    else k_copy_nd<float4, false, int64_t, 8><<<(int)grid, 256, 0, d->stream>>>(d4, s4, a, v4); }
         return finish("copy_nd(vec)");
     }
     a.total = total;
     const int64_t grid = grid_of(total, 1024);
     if (grid > 0x7fffffffLL) return fail(KTC_ENOTSUP, "tensor too large for one launch");
     const bool small = total < (1LL << 31);
-    if (fill) { if (small) k_copy_nd<float, true, uint32_t><<<(int)grid, 256, 0, d->stream>>>(dst, nullptr, a, value);
-                else k_copy_nd<float, true, int64_t><<<(int)grid, 256, 0, d->stream>>>(dst, nullptr, a, value); }
-    else      { if (small) k_copy_nd<float, false, uint32_t><<<(int)grid, 256, 0, d->stream>>>(dst, src, a, value);
-                else k_copy_nd<float, false, int64_t><<<(int)grid, 256, 0, d->stream>>>(dst, src, a, value); }
+    if (fill) { if (small) k_copy_nd<float, true, uint32_t, 4><<<(int)grid, 256, 0, d->stream>>>(dst, nullptr, a, value);
+                else k_copy_nd<float, true, int64_t, 4><<<(int)grid, 256, 0, d->stream>>>(dst, nullptr, a, value); }
+    else      { if (small) k_copy_nd<float, false, uint32_t, 4><<<(int)grid, 256, 0, d->stream>>>(dst, src, a, value);
+                else k_copy_nd<float, false, int64_t, 4><<<(int)grid, 256, 0, d->stream>>>(dst, src, a, value); }
     return finish("copy_nd");
 }
 
