@@ -249,12 +249,22 @@ KD_FN float kd_sigmoid(float x) {
     return (d < KD_RCP_FAST_LIMIT) ? kd_rcp_fast(d) : kd_rcp_ieee(d);
 }
 
+// The same value for |x| <= KD_SIGMOID_PLAIN_RANGE (and NaN for NaN) without the two clamps and without the test of
+// the denominator: exp(80) < 4e37.  The vector forms test the range once per four elements.
+#define KD_SIGMOID_PLAIN_RANGE 80.0f
+KD_FN float kd_sigmoid_in_range(float x) {
+    return kd_rcp_fast(1.0f + (float)kd_exp_wide(-(double)x));
+}
+
 // float exp with Math.exp's narrowing: the argument is clamped to [-104, 89] (exp(-104) narrows to 0,
 // exp(89) to +infinity, as the unclamped values do)
 KD_FN float kd_expf(float x) {
     const float xc = kd_max_nan(kd_min_nan(x, 89.0f), -104.0f);
     return (float)kd_exp((double)xc);
 }
+// the same value for |x| <= 104 (and NaN for NaN) without the clamps; the vector forms test the range once per four elements
+#define KD_EXP_PLAIN_RANGE 104.0f
+KD_FN float kd_expf_in_range(float x) { return (float)kd_exp((double)x); }
 
 // log2 of the float with bit pattern ix (a positive normal float), relative error below 2^-38
 KD_FN double kd_log2(int32_t ix) {

@@ -90,19 +90,24 @@ struct Identity { __device__ __forceinline__ float operator()(float a) const { r
 // Same values as the scalar functors; the rare slow paths (IEEE reciprocal for a subnormal sigmoid, the
 // library pow) are tested once per float4 instead of once per element, which keeps the common path free of
 // branches and reconvergence points.
-__device__ __forceinline__ float4 apply1(const UnOp<KTC_EXP>&, float4 a) {
+static __device__ __noinline__ float4 exp4_any(float4 a) {
     return make_float4(kd_expf(a.x), kd_expf(a.y), kd_expf(a.z), kd_expf(a.w));
 }
+__device__ __forceinline__ float4 apply1(const UnOp<KTC_EXP>&, float4 a) {
+    const float m = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w)));
+    if (m <= KD_EXP_PLAIN_RANGE)                       // no clamp needed (a NaN passes and comes out as NaN)
+        return make_float4(kd_expf_in_range(a.x), kd_expf_in_range(a.y), kd_expf_in_range(a.z), kd_expf_in_range(a.w));
+    return exp4_any(a);
+}
+static __device__ __noinline__ float4 sigmoid4_any(float4 a) {
+    return make_float4(kd_sigmoid(a.x), kd_sigmoid(a.y), kd_sigmoid(a.z), kd_sigmoid(a.w));
+}
 __device__ __forceinline__ float4 apply1(const UnOp<KTC_SIGMOID>&, float4 a) {
-    const float d0 = kd_sigmoid_den(a.x), d1 = kd_sigmoid_den(a.y), d2 = kd_sigmoid_den(a.z), d3 = kd_sigmoid_den(a.w);
-    float4 o = make_float4(kd_rcp_fast(d0), kd_rcp_fast(d1), kd_rcp_fast(d2), kd_rcp_fast(d3));
-    if (!(fmaxf(fmaxf(d0, d1), fmaxf(d2, d3)) < KD_RCP_FAST_LIMIT)) {          // huge, infinite or all-NaN denominators
-        if (!(d0 < KD_RCP_FAST_LIMIT)) o.x = kd_rcp_ieee(d0);
-        if (!(d1 < KD_RCP_FAST_LIMIT)) o.y = kd_rcp_ieee(d1);
-        if (!(d2 < KD_RCP_FAST_LIMIT)) o.z = kd_rcp_ieee(d2);
-        if (!(d3 < KD_RCP_FAST_LIMIT)) o.w = kd_rcp_ieee(d3);
-    }
-    return o;
+    // arguments within +-80 (a NaN passes: it comes out as NaN either way) need neither clamp nor denominator test
+    const float m = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w)));
+    if (m <= KD_SIGMOID_PLAIN_RANGE)
+        return make_float4(kd_sigmoid_in_range(a.x), kd_sigmoid_in_range(a.y), kd_sigmoid_in_range(a.z), kd_sigmoid_in_range(a.w));
+    return sigmoid4_any(a);
 }
 __device__ __forceinline__ float4 pow4(float4 a, float4 b) {
     bool k0, k1, k2, k3;

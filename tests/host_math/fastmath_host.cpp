@@ -28,7 +28,7 @@ void kfh_pow(const float* x, const float* y, float* out, unsigned char* ok, int6
 }
 
 // Every `stride`-th float bit pattern (all of them: both signs, subnormals, infinities, NaNs) through
-// exp (fn = 0) or sigmoid (fn = 1), against the double libm narrowed as kten-jvm narrows it
+// exp (fn = 0) or sigmoid (fn = 1; fn = 2: its form for |x| <= 80 against the full form; fn = 3: likewise exp for |x| <= 104), against the double libm narrowed as kten-jvm narrows it
 // (JVMRawTensor.kt:395, 399).  counts[k] = inputs at ulp distance k (3 = ">= 3"); a NaN on one side only
 // counts as ">= 3".  Returns the largest distance.
 int64_t kfh_sweep(int fn, uint32_t stride, int64_t* counts) {
@@ -40,6 +40,14 @@ int64_t kfh_sweep(int fn, uint32_t stride, int64_t* counts) {
         float x; std::memcpy(&x, &b, 4);
         float got, want;
         if (fn == 0) { got = ktc::kd_expf(x); want = (float)std::exp((double)x); }
+        else if (fn == 3) {                          // exp without clamps against the full form, inside its range (NaN included)
+            if (x == x && !(std::fabs(x) <= KD_EXP_PLAIN_RANGE)) continue;
+            got = ktc::kd_expf_in_range(x); want = ktc::kd_expf(x);
+        }
+        else if (fn == 2) {                          // the form without clamps against the full one, inside its range (NaN included)
+            if (x == x && !(std::fabs(x) <= KD_SIGMOID_PLAIN_RANGE)) continue;
+            got = ktc::kd_sigmoid_in_range(x); want = ktc::kd_sigmoid(x);
+        }
         else { got = ktc::kd_sigmoid(x); const float e = (float)std::exp((double)(-1.0f * x)); want = 1.0f / (1.0f + e); }
         int64_t d;
         if (want != want || got != got) d = (want != want && got != got) ? 0 : 99;

@@ -75,6 +75,15 @@ def test_sigmoid_every_eleventh_float(fm):
     assert counts[1] + counts[2] <= n // 1_000_000 and counts[3] == 0
 
 
+def test_forms_without_clamps_are_the_same_functions_inside_their_range(fm):
+    """The vector kernels skip the clamps and the denominator test when all four arguments lie within +-80 (or are NaN):
+    every 7th float of that range gives the bits of the full form."""
+    for fn in (2, 3):                                   # sigmoid within +-80, exp within +-104
+        counts = (C.c_int64 * 4)()
+        worst = fm.kfh_sweep(fn, 7, counts)
+        assert worst == 0 and counts[0] > 200_000_000 and counts[1] + counts[2] + counts[3] == 0
+
+
 @pytest.mark.parametrize("domain", ["config2", "wide", "large_exponent", "huge_base", "near_one", "subnormal_result"])
 def test_pow(fm, domain):
     rng = np.random.default_rng(len(domain) * 131)
