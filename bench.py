@@ -414,6 +414,7 @@ def run_sharded_graph(ops, lib, L, D, rank, world, collective, steps, warmup, di
         both gradients come out of one pass."""
         ops.lazy, ops.deferSums = deferred, defer_sums
         passes0 = ops.multiSinkEvaluations
+        rec0 = ops._recorder.stats()
         ms = C.c_float(0)
         for _ in range(max(warmup, 3)):
             one_step()
@@ -426,6 +427,7 @@ def run_sharded_graph(ops, lib, L, D, rank, world, collective, steps, warmup, di
             one_step()
         L.check(lib.ktc_timer_stop(ops.device, C.byref(ms)))
         launches = lib.ktc_launch_count() - launches0
+        rec1 = ops._recorder.stats()
         ops.lazy, ops.deferSums = False, True
         # the loss tensor of the last step was released with its graph; gw / gb are the Variables' gradients
         gw, gb = graph.w.gradient.toArray().reshape(-1), graph.b.gradient.toArray()
@@ -438,6 +440,8 @@ def run_sharded_graph(ops, lib, L, D, rank, world, collective, steps, warmup, di
         return {"ms_per_step": t / steps, "gelem_per_s": rows * cols / (t / steps) / 1e6,
                 "kernel_launches_per_step": launches / steps,
                 "multi_sink_passes_per_step": (ops.multiSinkEvaluations - passes0) / (steps + max(warmup, 3)),
+                "updates_in_second_pass_per_step": (rec1["folded_updates"] - rec0["folded_updates"]) / (steps + max(warmup, 3)),
+                "exchanges_in_second_pass_per_step": (rec1["folded_exchanges"] - rec0["folded_exchanges"]) / (steps + max(warmup, 3)),
                 "grad_w_abs_sum": float(np.abs(gw).sum()), "grad_b_abs_sum": float(np.abs(gb).sum())}
 
     def timed_native(deferred):
@@ -480,6 +484,8 @@ def run_sharded_graph(ops, lib, L, D, rank, world, collective, steps, warmup, di
                 "kernel_launches_per_step": launches / steps,
                 "multi_sink_passes_per_step": (stats1["multi_sink"] - stats0["multi_sink"]) / steps,
                 "programs_compiled_in_timed_region": stats1["compiled"] - stats0["compiled"],
+                "updates_in_second_pass_per_step": (stats1["folded_updates"] - stats0["folded_updates"]) / steps,
+                "exchanges_in_second_pass_per_step": (stats1["folded_exchanges"] - stats0["folded_exchanges"]) / steps,
                 "grad_w_abs_sum": float(np.abs(gw).sum()), "grad_b_abs_sum": float(np.abs(gb).sum())}
 
     eager = timed(False)

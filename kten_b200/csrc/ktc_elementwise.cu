@@ -141,15 +141,6 @@ __device__ __forceinline__ float4 load_operand(const float* sm, const float* til
     return make_float4(0.f, 0.f, 0.f, 0.f);
 }
 
-// x / b for a divisor shared by a whole row: kd_div_by_reciprocal (ktc_fastmath_d.h), its window tested once per float4
-__device__ __noinline__ float4 div_ieee4(float4 x, float b) {
-    return make_float4(__fdiv_rn(x.x, b), __fdiv_rn(x.y, b), __fdiv_rn(x.z, b), __fdiv_rn(x.w, b));
-}
-__device__ __forceinline__ float4 div_by_row(float4 x, float b, float r) {
-    const uint32_t in_window = kd_div_window(x.x) & kd_div_window(x.y) & kd_div_window(x.z) & kd_div_window(x.w);
-    if (in_window == 0u || r == 0.f) return div_ieee4(x, b);
-    return make_float4(kd_div_by_reciprocal(x.x, b, r), kd_div_by_reciprocal(x.y, b, r), kd_div_by_reciprocal(x.z, b, r), kd_div_by_reciprocal(x.w, b, r));
-}
 template <class F> struct IsDiv { static constexpr bool value = false; };
 template <> struct IsDiv<BinOp<KTC_DIV>> { static constexpr bool value = true; };
 
@@ -159,7 +150,7 @@ template <> struct IsDiv<BinOp<KTC_DIV>> { static constexpr bool value = true; }
 // full-size (DIRECT) operands are issued first, then the broadcast operand is staged in
 // shared memory, so the staging latency overlaps the main stream instead of preceding it.
 template <int MODE_A, int MODE_B, int U, class F>
-__global__ void __launch_bounds__(256, IsDiv<F>::value ? 3 : 1) k_bcast3(BcastArgs p, F f) {
+__global__ void __launch_bounds__(256, 3) k_bcast3(BcastArgs p, F f) {
     extern __shared__ __align__(16) float smem[];
     constexpr bool STAGE_A = (MODE_A == AM_SMEMROW || MODE_A == AM_ROWSCALAR);
     constexpr bool STAGE_B = (MODE_B == AM_SMEMROW || MODE_B == AM_ROWSCALAR);

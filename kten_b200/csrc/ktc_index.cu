@@ -40,9 +40,8 @@ inline int finish(const char* what) {
 }
 
 // T = float or float4; FILL: no source; I = type of the linear index that is decomposed (32-bit when the
-// box is small enough).  A thread moves U items, 256 apart, and issues all its loads before the first store (eight
-// float4 in flight per thread: what the streaming kernels of this library need to reach the HBM rate); every element is
-// touched once, hence the streaming hints.
+// box is small enough).  A thread moves U items, 256 apart, and issues all its loads before the first store; every
+// element is touched once, hence the streaming hints.
 template <class T, bool FILL, class I, int U>
 __global__ void __launch_bounds__(256) k_copy_nd(T* __restrict__ dst, const T* __restrict__ src, const __grid_constant__ NdArgs a, T v) {
     const int64_t base = (int64_t)blockIdx.x * (256 * U) + threadIdx.x;
@@ -451,16 +450,18 @@ int launch_copy_nd(Device* d, float* dst, const int64_t* dstr, const float* src,
         a.shape[m - 1] /= 4;
         for (int i = 0; i < m - 1; ++i) { a.dstr[i] /= 4; a.sstr[i] /= 4; }
         a.total = total / 4;
-        const int64_t grid = grid_of(a.total, 2048);             // 256 threads x 8 items
+        const bool u8 = tune("copy_unroll", 4) == 8;              // items per thread: 8 gains nothing on rows of 8 K floats and loses 12 % on 1 K rows
+        const int64_t grid = grid_of(a.total, u8 ? 2048 : 1024);
         if (grid > 0x7fffffffLL) return fail(KTC_ENOTSUP, "tensor too large for one launch");
         const float4 v4 = make_float4(value, value, value, value);
         float4* d4 = reinterpret_cast<float4*>(dst);
         const float4* s4 = reinterpret_cast<const float4*>(src);
         const bool small = a.total < (1LL << 31);
-        if (fill) { if (small) k_copy_nd<float4, true, uint32_t, 8><<<(int)grid, 256, 0, d->stream>>>(d4, nullptr, a, v4);
-                    else k_copy_nd<float4, true, int64_t, 8><<<(int)grid, 256, 0, d->stream>>>(d4, nullptr, a, v4); }
-        else      { if (small) k_copy_nd<float4, false, uint32_t, 8><<<(int)grid, 256, 0, d->stream>>>(d4, s4, a, v4);
-                    else k_copy_nd<float4, false, int64_t, 8><<<(int)grid, 256, 0, d->stream>>>(d4, s4, a, v4); }
+#define KTC_CP(FILL, I) do { if (u8) k_copy_nd<float4, FILL, I, 8><<<(int)grid, 256, 0, d->stream>>>(d4, FILL ? nullptr : s4, a, v4); \
+                             else k_copy_nd<float4, FILL, I, 4><<<(int)grid, 256, 0, d->stream>>>(d4, FILL ? nullptr : s4, a, v4); } while (0)
+        if (fill) { if (small) KTC_CP(true, uint32_t); else KTC_CP(true, int64_t); }
+        else      { if (small) KTC_CP(false, uint32_t); else KTC_CP(false, int64_t); }
+#undef KTC_CP
         return finish("copy_nd(vec)");
     }
     a.total = total;

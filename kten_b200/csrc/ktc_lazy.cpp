@@ -1067,14 +1067,14 @@ static int assign(uint64_t target_id, Kind kind, int op, Node* a0, Node* a1, con
     }
     cell = cell_of(target_id);
     if (opt_defer_inplace && cell->node == own && (a0 == own || a1 == own)) {
-        // Nobody else holds the buffer (the caller's reference and this cell's node): instead of a pass that
+        // Nobody else holds the buffer (this cell's node, and the caller's reference if it ever asked for it): instead of a pass that
         // rewrites the buffer now, the cell becomes pending -- its node reads the old buffer as an operand -- so that
         // the in-place calls that follow join one program.  A buffer with another holder (a view, a shallow copy, a
         // pending expression that still reads it) is written in place as before.
         int cnt = 0;
         s = B.refcount(h, &cnt);
         if (s != KTC_OK) return finish(s, 0);
-        if (cnt == 2) {
+        if (cnt == 2 || cnt == 1) {
             cell->node = node_ref(node);
             register_cell(target_id, node);
             node_unref(own);                              // the cell's reference; `node` keeps the leaf and its buffer
@@ -1270,7 +1270,8 @@ KTC_API int ktc_lazy_assign_fill(ktc_lazy_cell target, float value, int* state) 
         cell = cell_of(target);
         int cnt = 0;
         if (s == KTC_OK) s = B.refcount(h, &cnt);
-        if (s != KTC_OK || !(opt_defer_inplace && cell->node == own && cnt == 2)) {
+        // the holders of a buffer nobody else uses: this cell's node, and the caller's tensor if it ever asked for the buffer
+        if (s != KTC_OK || !(opt_defer_inplace && cell->node == own && (cnt == 2 || cnt == 1))) {
             if (s == KTC_OK) s = B.fill(h, 0, own->shape.volume(), value);
             node_unref(own);
             if (state) *state = 0;

@@ -125,6 +125,17 @@ __device__ __forceinline__ float4 apply2(const BinOp<KTC_POW>&, float4 a, float4
 __device__ __forceinline__ float4 apply1(const ScalarRight<KTC_POW>& f, float4 a) { return pow4(a, make_float4(f.s, f.s, f.s, f.s)); }
 __device__ __forceinline__ float4 apply1(const ScalarLeft<KTC_POW>& f, float4 a) { return pow4(make_float4(f.s, f.s, f.s, f.s), a); }
 
+// x / b for a divisor shared by many dividends (a row scalar of a broadcast division, the row sum of a softmax), with
+// r = kd_row_reciprocal(b): kd_div_by_reciprocal where its window holds -- tested once per float4 -- and IEEE division elsewhere
+static __device__ __noinline__ float4 div_ieee4(float4 x, float b) {
+    return make_float4(__fdiv_rn(x.x, b), __fdiv_rn(x.y, b), __fdiv_rn(x.z, b), __fdiv_rn(x.w, b));
+}
+__device__ __forceinline__ float4 div_by_row(float4 x, float b, float r) {
+    const uint32_t in_window = kd_div_window(x.x) & kd_div_window(x.y) & kd_div_window(x.z) & kd_div_window(x.w);
+    if (in_window == 0u || r == 0.f) return div_ieee4(x, b);
+    return make_float4(kd_div_by_reciprocal(x.x, b, r), kd_div_by_reciprocal(x.y, b, r), kd_div_by_reciprocal(x.z, b, r), kd_div_by_reciprocal(x.w, b, r));
+}
+
 struct ClampOp { float lo, hi; __device__ __forceinline__ float operator()(float x) const { return jmin(jmax(x, lo), hi); } };
 
 template <int OP> struct CompareOp {

@@ -10,7 +10,8 @@
 //   S   = sum_j e_j                         accumulated exactly as ktc_reduce_axis(SUM) accumulates a row of this
 //                                           length: per lane float runs of 8 vectors folded into a double, lanes
 //                                           combined by a xor-shuffle tree in double, one rounding to float
-//   p_j = e_j / S                           IEEE division; written out: the tensor saved for backward
+//   p_j = e_j / S                           the IEEE quotient (through the row's reciprocal where that gives it); written out:
+//                                           the tensor saved for backward
 //   S2  = sum_j p_j                         same accumulation
 //   nll = -log(clamp(p_t / S2, lo, hi))     only at the target column t of the row -- the reference computes the
 //                                           second normalisation, the clamp and the log for every column and then
@@ -76,11 +77,12 @@ __global__ void __launch_bounds__(256) k_softmax_xent_forward(const float* __res
         }
     }
     const float S = sx_row_sum(v, n_l);
+    const float rS = kd_row_reciprocal(S);                         // the IEEE quotients through the row's reciprocal (ktc_math.cuh)
     float4* ps = reinterpret_cast<float4*>(softmax + row * cols);
     #pragma unroll
     for (int u = 0; u < kSxMaxVec; ++u) {
         if (u < n_l) {
-            v[u] = make_float4(__fdiv_rn(v[u].x, S), __fdiv_rn(v[u].y, S), __fdiv_rn(v[u].z, S), __fdiv_rn(v[u].w, S));
+            v[u] = div_by_row(v[u], S, rS);
             __stcs(ps + lane + 32 * u, v[u]);
         }
     }

@@ -82,14 +82,20 @@ def main() -> int:
     w, b = D.uniform(cols, 32, -0.5, 0.5), D.uniform(cols, 33, -0.5, 0.5)
     ops.lazy = True
     before = ops._recorder.stats()["folded_exchanges"]
-    local = ShardedSigmoidGraph(ops, ops.createRaw([rows, cols], xs), ops.createRaw([1, cols], w), ops.createRaw([cols], b))
-    mine = [t.toArray().reshape(-1).copy() for t in local.step()]                      # this rank's loss, gw, gb
-    local.release_step()
+    alone = ShardedSigmoidGraph(ops, ops.createRaw([rows, cols], xs), ops.createRaw([1, cols], w), ops.createRaw([cols], b))
+    mine = [t.toArray().reshape(-1).copy() for t in alone.step()]                      # this rank's loss, gw, gb
+    alone.release_step()
     everyone = [None] * world
     dist.all_gather_object(everyone, mine)
     fused = ShardedSigmoidGraph(ops, ops.createRaw([rows, cols], xs), ops.createRaw([1, cols], w), ops.createRaw([cols], b), collective=p2p)
     for step in range(3):                                                               # the first step compiles, the others hit the cache
-        got = [t.toArray().reshape(-1) for t in fused.step()]
+        launches0 = lib.ktc_launch_count()
+        out = fused.step()
+        launches = lib.ktc_launch_count() - launches0
+        if step > 0 and launches != 2:                                                  # the pass and its second pass, nothing else
+            ok = False
+            print(f"rank {rank}: fused exchange, step {step}: {launches} launches", file=sys.stderr)
+        got = [t.toArray().reshape(-1) for t in out]
         p2p.check()
         fused.release_step()
         for i in range(3):

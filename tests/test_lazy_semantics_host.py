@@ -356,6 +356,17 @@ def test_allreduce_through_the_recorder_joins_the_pass_when_it_can():
 
     rows, cols = 32, 16
     x, w, b = D.uniform(rows * cols, 0, -1.0, 1.0), D.normal(cols, 0, 0.0, 0.5, stream=1), D.uniform(cols, 0, -0.1, 0.1, stream=2)
+    # steps whose results nobody reads in between (a training loop on several ranks): the gradient buffers are held by
+    # the recorder alone, zeroGrad still becomes a pending constant, and every step is the one call
+    ops = make_ops()
+    ops.lazy = True
+    with ops.garbageCollector():
+        g = ShardedSigmoidGraph(ops, ops.createRaw([rows, cols], x), ops.createRaw([1, cols], w), ops.createRaw([cols], b), RecorderCollective(ops))
+        for step in range(3):
+            n0 = len(ops.lib.calls)
+            g.step()
+            assert ops.lib.calls[n0:] == ["expr_eval"], (step, ops.lib.calls[n0:])
+            g.release_step()
     vals = {}
     for mode in ("eager", "deferred", "sums at once"):
         ops = make_ops()
