@@ -49,6 +49,8 @@ __device__ __forceinline__ float sx_row_sum(const float4 (&v)[kSxMaxVec], int n_
     return (float)acc.acc;
 }
 
+// NV > 0: every lane owns exactly NV vectors (cols == 128 NV) and the guards below fold away; NV == 0: any row length
+template <int NV>
 __global__ void __launch_bounds__(256) k_softmax_xent_forward(const float* __restrict__ logits, const float* __restrict__ targets,
                                                               float* __restrict__ softmax, float* __restrict__ nll,
                                                               int64_t rows, int cols, float lo, float hi, int* err) {
@@ -56,7 +58,7 @@ __global__ void __launch_bounds__(256) k_softmax_xent_forward(const float* __res
     const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (row >= rows) return;                                       // whole warps leave together
     const int q1 = cols >> 2;
-    const int n_l = q1 > lane ? (q1 - lane + 31) >> 5 : 0;        // vectors of this lane
+    const int n_l = NV > 0 ? NV : (q1 > lane ? (q1 - lane + 31) >> 5 : 0);        // vectors of this lane
     const float4* px = reinterpret_cast<const float4*>(logits + row * cols);
     float4 v[kSxMaxVec];
     #pragma unroll
@@ -116,7 +118,9 @@ int launch_softmax_xent_forward(Device* d, float* softmax, float* nll, const flo
     if (rows == 0) return KTC_OK;
     const int64_t grid = (rows + 7) / 8;
     if (grid > 0x7fffffffLL) return fail(KTC_ENOTSUP, "tensor too large for one launch");
-    k_softmax_xent_forward<<<(int)grid, 256, 0, d->stream>>>(logits, targets, softmax, nll, rows, (int)cols, lo, hi, d->idx_err);
+#define KTC_SX(NV) k_softmax_xent_forward<NV><<<(int)grid, 256, 0, d->stream>>>(logits, targets, softmax, nll, rows, (int)cols, lo, hi, d->idx_err)
+    if (cols == 2048) KTC_SX(16); else if (cols == 1024) KTC_SX(8); else if (cols == 512) KTC_SX(4); else KTC_SX(0);
+#undef KTC_SX
     count_launch(1);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(KTC_ECUDA, "launch of softmax_xent_forward failed: %s", cudaGetErrorString(e));
