@@ -631,6 +631,48 @@ def run_other_ops(ops, lib, L, D, steps):
     logits.getRawValue().release()
     targets.getRawValue().release()
     x.release()
+
+    # batch normalisation of [256, 64, 128, 128] along axis 1 (training: statistics, running averages, scale and shift) and
+    # its backward, and nearest-neighbour upsampling by 2 with its gradient: compositions of recorded raw-tensor calls
+    # (kten_b200/nn.py).  Bytes: what must cross HBM when every pass reads its operands once -- forward x three times + out,
+    # backward x and gradOut twice + gradIn -- i.e. the passes the reference itself makes.
+    shape, C = [256, 64, 128, 128], 64
+    n = 256 * 64 * 128 * 128
+    bx = ops.createRaw(shape, D.normal(n, 21, 0.0, 1.0))
+    bgo = ops.createRaw(shape, D.normal(n, 22, 0.0, 1.0))
+    gam, bet = ops.createRaw([C], D.uniform(C, 23, 0.5, 1.5)), ops.createRaw([C], D.uniform(C, 24, -0.5, 0.5))
+    rmean, rvar = ops.createRawFill([C], 0.0), ops.createRawFill([C], 1.0)
+    bn = ops.batchNorm(1, 0.1, 1e-3, True)
+
+    def bn_step():
+        o, m, sd = bn.calculateOutput(bx, rmean, rvar, gam, bet)
+        gi, gg, gb = bn.calculateGrads(bx, rmean, rvar, m, sd, gam, bgo, True, True, True)
+        for t in (o, gi, gg, gb):
+            t.storeReference
+
+    up = ops.upsample("NEAREST", 2)
+    ux = ops.createRaw([256, 64, 64, 64], D.normal(n // 4, 25, 0.0, 1.0))
+
+    def up_step():
+        o = up.upsample(ux)
+        up.calculateGrad(o, [256, 64, 64, 64]).storeReference
+
+    for name, fn, nbytes in (("batchNorm [256,64,128,128] axis 1, training forward + backward", bn_step, 9 * 4.0 * n),
+                             ("upsample2d nearest x2 of [256,64,64,64] + gradient", up_step, (0.25 + 1 + 1 + 0.25) * 4.0 * n)):
+        for _ in range(3):
+            with ops.garbageCollector():
+                fn()
+        ops.synchronize()
+        l0 = lib.ktc_launch_count()
+        L.check(lib.ktc_timer_start(ops.device))
+        for _ in range(reps):
+            with ops.garbageCollector():
+                fn()
+        L.check(lib.ktc_timer_stop(ops.device, C.byref(ms)))
+        per = ms.value / reps
+        out.append({"name": name, "ms": round(per, 4), "gbs": round(nbytes / per / 1e6, 1), "launches": (lib.ktc_launch_count() - l0) / reps})
+    for t in (bx, bgo, gam, bet, rmean, rvar, ux):
+        t.release()
     return out
 
 
@@ -966,6 +1008,45 @@ def run_single_case(args):
         per = ms.value / args.reps
         print(json.dumps({"case": name, "elements": rows * cols, "ms": per, "gbs": 2 * 4.0 * rows * cols / per / 1e6,
                           "launches_per_step": (lib.ktc_launch_count() - l0) / args.reps}))
+        return 0
+    if name in ("x.batchnorm", "x.upsample"):
+        # batch norm (training forward + backward) of [n / 2^20, 64, 128, 128] along axis 1; upsampling by 2 with its gradient
+        imgs = max(1, n >> 20)
+        if name == "x.batchnorm":
+            shape = [imgs, 64, 128, 128]
+            vol = imgs << 20
+            bx, bgo = ops.createRaw(shape, D.normal(vol, 21, 0.0, 1.0)), ops.createRaw(shape, D.normal(vol, 22, 0.0, 1.0))
+            gam, bet = ops.createRaw([64], D.uniform(64, 23, 0.5, 1.5)), ops.createRaw([64], D.uniform(64, 24, -0.5, 0.5))
+            rmean, rvar = ops.createRawFill([64], 0.0), ops.createRawFill([64], 1.0)
+            bn = ops.batchNorm(1, 0.1, 1e-3, True)
+
+            def fn():
+                o, m, sd = bn.calculateOutput(bx, rmean, rvar, gam, bet)
+                for t in (o,) + bn.calculateGrads(bx, rmean, rvar, m, sd, gam, bgo, True, True, True):
+                    t.storeReference
+            nbytes = 9 * 4.0 * vol
+        else:
+            shape = [imgs, 64, 64, 64]
+            vol = imgs << 18
+            ux = ops.createRaw(shape, D.normal(vol, 25, 0.0, 1.0))
+            up = ops.upsample("NEAREST", 2)
+
+            def fn():
+                up.calculateGrad(up.upsample(ux), shape).storeReference
+            nbytes = 10 * 4.0 * vol
+        for _ in range(3):
+            with ops.garbageCollector():
+                fn()
+        ops.synchronize()
+        l0 = lib.ktc_launch_count()
+        L.check(lib.ktc_timer_start(0))
+        for _ in range(args.reps):
+            with ops.garbageCollector():
+                fn()
+        ms = C.c_float(0)
+        L.check(lib.ktc_timer_stop(0, C.byref(ms)))
+        per = ms.value / args.reps
+        print(json.dumps({"case": name, "elements": vol, "ms": per, "gbs": nbytes / per / 1e6, "launches_per_step": (lib.ktc_launch_count() - l0) / args.reps}))
         return 0
     if name.startswith("x."):
         # data-movement ops beside the sweep, on a [rows, 4096] tensor of n elements

@@ -227,6 +227,25 @@ class Tensor:
         res = SoftmaxCrossEntropy(self.ops)(self, targets)
         return res if self.requiresGrad else res.noGrad()
 
+    def batchNorm(self, axis: int, runningMean: Optional["Tensor"], runningVar: Optional["Tensor"], training: bool = False,
+                  momentum: float = 0.99, epsilon: float = 1e-3, gamma: Optional["Tensor"] = None, beta: Optional["Tensor"] = None):
+        """Tensor.batchNorm (functions/nn/TensorExtensions.kt:234-245)."""
+        res = BatchNormalizationFunction(axis, momentum, epsilon, training, self.ops)(self, runningMean, runningVar, gamma, beta)
+        return res if self.requiresGrad else res.noGrad()
+
+    def upsample2d(self, scale: int, upsampleType: str = "NEAREST"):
+        """Tensor.upsample2d (functions/nn/TensorExtensions.kt:247-250)."""
+        res = Upsample2DFunction(upsampleType, scale, self.ops)(self)
+        return res if self.requiresGrad else res.noGrad()
+
+    def meanVariance(self, axis: int, keepDimensions: bool = False, unbiased: bool = True):
+        """AGTensor.meanVariance (AGTensor.kt:454-461): the mean keeps the axis, as there."""
+        tensor = self.inplaceSafe()
+        mean = tensor.mean(axis, True)
+        elements = tensor.shape[SF.normalize_axis(tensor.shape, axis)] - (1 if unbiased else 0)
+        centred = tensor - mean
+        return mean, (centred ** 2.0).sum(axis, keepDimensions) / float(elements)
+
     def expand(self, *shape):
         if len(shape) == 1 and isinstance(shape[0], (list, tuple)):
             shape = shape[0]
@@ -289,6 +308,16 @@ class NoGradVariable(Tensor):
         if len(shape) == 1 and isinstance(shape[0], (list, tuple)):
             shape = shape[0]
         return NoGradVariable(self.ops, self.raw.broadcastTo(list(shape)))
+
+    def reshape(self, *shape):                     # NoGradVariable.kt:174
+        if len(shape) == 1 and isinstance(shape[0], (list, tuple)):
+            shape = shape[0]
+        return NoGradVariable(self.ops, self.raw.reshape(list(shape)))
+
+    def view(self, *shape):                        # NoGradVariable.kt:176
+        if len(shape) == 1 and isinstance(shape[0], (list, tuple)):
+            shape = shape[0]
+        return NoGradVariable(self.ops, self.raw.view(list(shape)))
 
 
 class Variable(Tensor):
@@ -1314,6 +1343,100 @@ class SoftmaxCrossEntropy(UnaryTensorFunction):    # functions/nn/SoftmaxCrossEn
         grad_in.plusAssign(self.valuesSaved[0])
         grad_in.divAssign(float(self.rows))
         return [grad_in]
+
+
+class BatchNormalizationFunction(Function):         # functions/nn/BatchNormalizationFunction.kt:12-157
+    """Batch normalisation along `axis` through the backend's BatchNormOperation; the running statistics are
+    variables without gradients that the forward pass updates in place."""
+
+    def __init__(self, axis, momentum, epsilon, training, ops):
+        super().__init__(ops)
+        self.axis, self.momentum, self.epsilon, self.training = axis, momentum, epsilon, training
+
+    def __call__(self, input: Tensor, runningMean, runningVar, gamma, beta):
+        self.input = input.inplaceSafe()
+        if runningMean is not None and runningVar is None:
+            raise ValueError("Running mean and running var must be both set to non-null or both has to be null")
+        if runningMean is None and runningVar is None and not self.training:
+            raise ValueError("Running mean and running var must be non-null for inference mode")
+        if runningMean is not None and (not isinstance(runningMean, NoGradVariable) or not isinstance(runningVar, NoGradVariable)):
+            raise ValueError("Running mean and running var parameters for batch normalization must be variables requiring no gradients")
+        self.runningMean, self.runningVar = runningMean, runningVar
+        self.gamma = gamma.inplaceSafe() if gamma is not None else None
+        self.beta = beta.inplaceSafe() if beta is not None else None
+        norm_axis = SF.normalize_axis(input.shape, self.axis)
+        self.keepOutput = True
+        size = self.input.shape[norm_axis]
+        if runningMean is not None:
+            if len(runningMean.shape) != 1 or len(runningVar.shape) != 1 or runningMean.shape[0] != size or runningVar.shape[0] != size:
+                raise ValueError(f"Running mean and running var parameters for batch normalization all must have shape: [{size}], "
+                                 f"but got tensors with shapes: running mean: {runningMean.shape} running var: {runningVar.shape} ")
+        for t in (self.gamma, self.beta):
+            if t is not None and (len(t.shape) != 1 or t.shape[0] != size):
+                raise ValueError(f"Gamma and beta parameters for batch normalization all must have shape: [{size}]")
+        self.op = self.ops.batchNorm(norm_axis, self.momentum, self.epsilon, self.training)
+        self.cachedShape = list(input.shape)
+        return self
+
+    def getInputsAsList(self):
+        return [t for t in (self.input, self.gamma, self.beta) if t is not None]
+
+    def internalForward(self) -> None:
+        super().internalForward()
+        if self.hasValue():
+            return
+        fns = [t for t in (self.input, self.runningMean, self.runningVar, self.gamma, self.beta) if isinstance(t, Function)]
+        for f in fns:
+            f.internalForward()
+        if not self.hasValue():
+            raw = lambda t: None if t is None else t.getRawValue()
+            out, mean, std = self.op.calculateOutput(raw(self.input), raw(self.runningMean), raw(self.runningVar), raw(self.gamma), raw(self.beta))
+            saved = [raw(self.input), mean, std]
+            if self.runningMean is not None:
+                saved += [raw(self.runningMean), raw(self.runningVar)]
+            if self.gamma is not None:
+                saved.append(raw(self.gamma))
+            self.saveForBackward(*saved)
+            self.output = out
+        for f in fns:
+            f.mayFreeOutput()
+
+    def doBackward(self, gradient):
+        saved = self.valuesSaved
+        x, mean, std = saved[0], saved[1], saved[2]
+        running = saved[3:5] if self.runningMean is not None else [None, None]
+        gamma = saved[-1] if self.gamma is not None else None
+        if list(gradient.shape) != list(x.shape):
+            raise RuntimeError(f"Gradient shape mismatch, output grad shape: {gradient.shape} input shape: {x.shape}")
+        gi, gg, gb = self.op.calculateGrads(x, running[0], running[1], mean, std, gamma, gradient, self.input.requiresGrad,
+                                            bool(self.gamma is not None and self.gamma.requiresGrad),
+                                            bool(self.beta is not None and self.beta.requiresGrad))
+        grads = [gi]
+        if self.gamma is not None:
+            grads.append(gg)
+        if self.beta is not None:
+            grads.append(gb)
+        return grads
+
+
+class Upsample2DFunction(UnaryTensorFunction):       # functions/nn/Upsample2DFunction.kt:9-35
+    modifiesShape = True
+
+    def __init__(self, upsampleType, scale, ops):
+        super().__init__(ops)
+        self.op = ops.upsample(upsampleType, scale)
+
+    def __call__(self, tensor: Tensor):
+        self.inputShape = list(tensor.shape)
+        self.op.checkDimensions(self.inputShape) if hasattr(self.op, "checkDimensions") else self.op._check(self.inputShape)
+        self.cachedShape = self.op.calculateOutputShape(self.inputShape)
+        return super().__call__(tensor)
+
+    def doForward(self, x):
+        self.output = self.op.upsample(x)
+
+    def doBackward(self, gradient):
+        return [self.op.calculateGrad(gradient, self.inputShape)]
 
 
 def oneHot(ops, targets: Tensor, classes: int) -> Tensor:

@@ -1,0 +1,199 @@
+"""The nn operations of the TensorOperations SPI that are reductions and broadcast maps: batch normalisation
+and nearest-neighbour upsampling (TensorOperations.kt:127-131; kten-jvm: JVMBatchNorm.kt, JVMUpsample2DNearest.kt).
+
+Neither needs a kernel of its own.  Viewed as [outer, C * inner] -- `axis` of extent C in the middle -- the sums a
+batch norm takes per channel are leading-axis sums of an elementwise expression followed by a small sum over
+`inner`, and its output is a broadcast map with row vectors of C * inner floats.  With the calls below recorded
+(ops.lazy) a training forward is three passes over the input (mean; centred squares; normalise -- the reference makes
+the same three) and the backward two (both sums in ONE pass with two sinks; the gradient), each a generated kernel that
+reads its operands once; run call by call they are the library's ordinary kernels.  Every per-element operation is
+the reference's float operation in the reference's order, so given the same per-channel statistics the outputs are
+bit-identical; the statistics themselves are sums (double accumulation, compared within the reduction tolerance).
+
+Upsampling is a broadcast copy ([R, 1, W, 1] -> [R, s, W, s]) and its gradient a sum back to the small shape."""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+from . import shape_functions as SF
+
+
+def _volume(shape: Sequence[int]) -> int:
+    n = 1
+    for d in shape:
+        n *= int(d)
+    return n
+
+
+class _Recorded:
+    """Runs the body with the calls recorded where the backend can (so that they fuse), and hands back stored
+    tensors when the caller itself runs call by call."""
+
+    def __init__(self, ops):
+        self.ops, self.was = ops, getattr(ops, "lazy", False)
+
+    def __enter__(self):
+        if hasattr(self.ops, "lazy"):
+            self.ops.lazy = True
+        return self
+
+    def __exit__(self, *exc):
+        if hasattr(self.ops, "lazy"):
+            self.ops.lazy = self.was
+        return False
+
+    def settle(self, *raws):
+        if not self.was:
+            for r in raws:
+                if r is not None and hasattr(r, "_buf"):
+                    r._buf()
+
+
+class CUDABatchNorm:
+    """BatchNormOperation over raw tensors of the CUDA backend (interface: BatchNormOperation.kt:5-44)."""
+
+    def __init__(self, axis: int, momentum: float, epsilon: float, training: bool, ops):
+        self.axis, self.momentum, self.epsilon, self.training, self.ops = int(axis), float(momentum), float(epsilon), bool(training), ops
+
+    # ---- helpers ---------------------------------------------------------------------------------------------
+    def _split(self, shape):
+        a = self.axis
+        return _volume(shape[:a]), int(shape[a]), _volume(shape[a + 1:])
+
+    @staticmethod
+    def _row(t, C, inner):
+        """A [C] tensor as the row vector [1, C * inner] that broadcasts against [outer, C * inner]."""
+        if inner == 1:
+            return t.view([1, C])
+        return t.view([C, 1]).broadcastTo([C, inner]).view([1, C * inner])
+
+    @staticmethod
+    def _channel_sums(t2d, C, inner):
+        """Sum of a [outer, C * inner] tensor per channel: over the leading axis, then over `inner`."""
+        s = t2d.sum(0)
+        return s if inner == 1 else s.view([C, inner]).sum(1)
+
+    # ---- forward ---------------------------------------------------------------------------------------------
+    def calculateOutput(self, input, runningMean, runningVar, gamma, beta):
+        outer, C, inner = self._split(input.shape)
+        n = outer * inner
+        with _Recorded(self.ops) as rec:
+            x = input.view([outer, C * inner])
+            if self.training:
+                mean = self._channel_sums(x, C, inner).div(float(n))                    # sum / elementSize (JVMBatchNorm.kt:54)
+                mean_row = self._row(mean, C, inner)
+                d = x.minus(mean_row)
+                ssq = self._channel_sums(d.times(d), C, inner)                          # :57-61
+                var = ssq.div(float(n)).plus(self.epsilon)
+                if self.epsilon == 0.0:
+                    # the sum is zero and so is epsilon: 0f instead of 1f / 0f.  Where the sum is zero the root is taken of 1
+                    # and the result multiplied by 0; elsewhere the two masks add 0f and multiply by 1f, which change nothing
+                    stdev = var.plus(ssq.lte(0.0)).sqrt().reciprocal().times(ssq.gt(0.0))
+                else:
+                    stdev = var.sqrt().reciprocal()                                     # 1f / sqrt(sum / n + epsilon), :63-65
+                if runningMean is not None and runningVar is not None:                  # :69-73
+                    keep = _f32(_f32(1.0) - _f32(self.momentum))                        # (1f - momentum), a float subtraction
+                    runningMean.timesAssign(keep)
+                    runningMean.plusAssign(mean.times(self.momentum))
+                    runningVar.timesAssign(keep)
+                    runningVar.plusAssign(ssq.div(float(n - 1)).times(self.momentum))
+            else:
+                mean = runningMean
+                stdev = runningVar.plus(self.epsilon).sqrt().reciprocal()               # :75-76
+                mean_row = self._row(mean, C, inner)
+            y = x.minus(mean_row).times(self._row(stdev, C, inner))                     # (x - mean) * stdev * g + b, :82-84
+            if gamma is not None:
+                y = y.times(self._row(gamma, C, inner))
+            y = y.plus(self._row(beta, C, inner)) if beta is not None else y.plus(0.0)
+            out = y.view(list(input.shape))
+            if not self.training:                                                       # the reference leaves both untouched (zeros) here
+                mean, stdev = self.ops.createRawFill([C], 0.0), self.ops.createRawFill([C], 0.0)
+            rec.settle(out, mean, stdev, runningMean, runningVar)
+        return out, mean, stdev
+
+    # ---- backward --------------------------------------------------------------------------------------------
+    def calculateGrads(self, input, runningMean, runningVar, currentMean, currentStd, gamma, gradOut,
+                       inRequiresGrad: bool, gammaRequiresGrad: bool, betaRequiresGrad: bool):
+        if not (inRequiresGrad or gammaRequiresGrad or betaRequiresGrad):
+            return None, None, None
+        outer, C, inner = self._split(input.shape)
+        n = outer * inner
+        with _Recorded(self.ops) as rec:
+            x, go = input.view([outer, C * inner]), gradOut.view([outer, C * inner])
+            if self.training:
+                mean, stdev = currentMean, currentStd
+            else:
+                mean = runningMean
+                stdev = runningVar.plus(self.epsilon).rsqrt()                           # (1.0 / sqrt(double)).toFloat(), :117
+            mean_row = self._row(mean, C, inner)
+            d = x.minus(mean_row)
+            # both sums are pending until the first is needed: one pass over x and gradOut with two sinks
+            s_go = go.sum(0)
+            s_dot = d.times(go).sum(0)
+            total = s_go if inner == 1 else s_go.view([C, inner]).sum(1)                # :120-123
+            dot = s_dot if inner == 1 else s_dot.view([C, inner]).sum(1)                # :125-128
+            grad_in = grad_gamma = grad_beta = None
+            if inRequiresGrad:
+                std_row = self._row(stdev, C, inner)
+                if self.training:                                                       # :131-138
+                    dps = dot.times(stdev).times(stdev).div(float(n))
+                    gmean = total.div(float(n))
+                    t = go.minus(self._row(gmean, C, inner)).minus(d.times(self._row(dps, C, inner))).times(std_row)
+                else:                                                                   # :139-143
+                    t = go.times(std_row)
+                if gamma is not None:
+                    t = t.times(self._row(gamma, C, inner))
+                grad_in = t.view(list(input.shape))
+            if gammaRequiresGrad:
+                grad_gamma = dot.times(stdev)                                           # :147-149
+            if betaRequiresGrad:
+                grad_beta = total                                                       # :151-153
+            rec.settle(grad_in, grad_gamma, grad_beta)
+        return grad_in, grad_gamma, grad_beta
+
+
+def _f32(v: float) -> float:
+    import numpy as np
+    return float(np.float32(v))
+
+
+class CUDAUpsample2DNearest:
+    """Upsample2DOperation (Upsample2DOperation.kt:5-44; kten-jvm: JVMUpsample2DNearest.kt:14-77)."""
+
+    def __init__(self, scale: int, ops):
+        self.scale, self.ops = int(scale), ops
+
+    @staticmethod
+    def checkDimensions(shape) -> None:
+        if len(shape) not in (3, 4):
+            raise ValueError(f"2D Upsampling can only be applied to tensors with 3 or 4 dimensions, but got tensor with shape: {list(shape)}")
+
+    def calculateOutputShape(self, shape) -> List[int]:
+        return list(shape[:-2]) + [shape[-2] * self.scale, shape[-1] * self.scale]
+
+    def checkGradOutShape(self, grad_shape, input_shape) -> None:
+        s = self.scale
+        if len(input_shape) != len(grad_shape):
+            raise ValueError(f"2D Upsample got gradient with different dimensions ({len(grad_shape)}) as the input tensor dimensions ({len(input_shape)})")
+        if grad_shape[-2] % s != 0 or grad_shape[-1] % s != 0:
+            raise ValueError(f"2D Upsample output gradients shape must be divisible by scale: {s} in the last two dimensions,"
+                             f"but got gradient tensor with shape: {list(grad_shape)}")
+        if grad_shape[-2] // s != input_shape[-2] or grad_shape[-1] // s != input_shape[-1] or list(grad_shape[:-2]) != list(input_shape[:-2]):
+            raise ValueError(f"2D Upsample output gradients shape: {list(grad_shape)} does not align with input tensor shape: {list(input_shape)} "
+                             f"with scale: {s}")
+
+    def upsample(self, input):
+        self.checkDimensions(input.shape)
+        s = self.scale
+        rows, W = _volume(input.shape[:-1]), int(input.shape[-1])
+        with _Recorded(self.ops) as rec:
+            out = input.view([rows, 1, W, 1]).broadcastTo([rows, s, W, s]).view(self.calculateOutputShape(input.shape))
+            rec.settle(out)
+        return out
+
+    def calculateGrad(self, gradOut, inputShape):
+        self.checkDimensions(gradOut.shape)
+        self.checkGradOutShape(gradOut.shape, inputShape)
+        s = self.scale
+        rows, W = _volume(inputShape[:-1]), int(inputShape[-1])
+        return gradOut.view([rows, s, W, s]).sumToShape([rows, 1, W, 1]).view(list(inputShape))

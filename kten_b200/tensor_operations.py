@@ -169,6 +169,17 @@ class CUDATensorOperations:
     def zerosLike(self, raw: CUDARawTensor) -> CUDARawTensor:
         return self.createRawFill(raw.shape, 0.0)
 
+    # ---- nn operations built on the path's kernels (TensorOperations.kt:127-131) ------------------------------
+    def batchNorm(self, axis: int, momentum: float, epsilon: float, training: bool):
+        from .nn import CUDABatchNorm
+        return CUDABatchNorm(axis, momentum, epsilon, training, self)
+
+    def upsample(self, upsampleType: str, scale: int):
+        from .nn import CUDAUpsample2DNearest
+        if upsampleType != "NEAREST":                      # UpsampleType has this one member
+            raise ValueError(f"unknown upsample type {upsampleType}")
+        return CUDAUpsample2DNearest(scale, self)
+
     def zeroOut(self, raw: CUDARawTensor) -> None:
         raw.inplaceFill(0.0)
 

@@ -572,6 +572,14 @@ class OracleTensorOperations:
     def pow(self, constant, raw):
         return OracleRawTensor(raw.shape, scalar(POW, raw.data, float(constant), scalar_first=True), self)
 
+    def batchNorm(self, axis, momentum, epsilon, training):
+        return OracleBatchNorm(axis, momentum, epsilon, training, self)
+
+    def upsample(self, upsampleType, scale):
+        if upsampleType != "NEAREST":
+            raise ValueError(f"unknown upsample type {upsampleType}")
+        return OracleUpsample2DNearest(scale, self)
+
     def concat(self, axis, inputs):
         """AbstractJVMTensorOperations.kt:106-120: every input is set into its range of the result."""
         SF = _SF()
@@ -587,3 +595,132 @@ class OracleTensorOperations:
             res.set(ranges, t)
             last += t.shape[a]
         return res
+
+
+# ---- nn operations that are reductions and broadcast maps (JVMBatchNorm.kt, JVMUpsample2DNearest.kt) ----------------
+def _seq_sum(values: np.ndarray, mode: int) -> np.float32:
+    """Sum in the order given: float32 sequential (mode 0, what the JVM loop does) or exact (mode 1: double)."""
+    if values.size == 0:
+        return np.float32(0.0)
+    if mode == 0:
+        return np.add.accumulate(values.astype(np.float32), dtype=np.float32)[-1]
+    return np.float32(values.astype(np.float64).sum())
+
+
+class OracleBatchNorm:
+    """JVMBatchNorm.kt:9-167 restated: per index of `axis`, mean and inverse standard deviation over all other
+    positions (two passes, float arithmetic per element), running statistics, scale and shift; the gradients of
+    :88-165.  Sums follow the oracle's accumulation mode."""
+
+    def __init__(self, axis, momentum, epsilon, training, ops):
+        self.axis, self.training, self.ops = axis, training, ops
+        self.momentum, self.epsilon = np.float32(momentum), np.float32(epsilon)
+
+    def _split(self, shape):
+        a = self.axis
+        return volume(shape[:a]), shape[a], volume(shape[a + 1:])
+
+    def calculateOutput(self, input, runningMean, runningVar, gamma, beta):
+        outer, C, inner = self._split(input.shape)
+        x = input.data.reshape(outer, C, inner)
+        out = np.empty_like(x)
+        cur_mean, cur_std = np.zeros(C, np.float32), np.zeros(C, np.float32)
+        n = outer * inner
+        one = np.float32(1.0)
+        for c in range(C):
+            xc = x[:, c, :].reshape(-1)                       # applyForAxis visits the positions in this order (:17-30)
+            if self.training:
+                mean = np.float32(_seq_sum(xc, self.ops.mode) / np.float32(n))
+                cur_mean[c] = mean
+                d = (xc - mean).astype(np.float32)
+                ssq = _seq_sum((d * d).astype(np.float32), self.ops.mode)
+                stdev = np.float32(0.0)
+                if ssq != 0.0 or self.epsilon != 0.0:
+                    stdev = np.float32(one / np.float32(np.sqrt(np.float32(np.float32(ssq / np.float32(n)) + self.epsilon))))
+                cur_std[c] = stdev
+                if runningMean is not None and runningVar is not None:
+                    runningMean.data[c] = np.float32(self.momentum * mean) + np.float32(np.float32(one - self.momentum) * runningMean.data[c])
+                    unbiased = np.float32(ssq / np.float32(n - 1))
+                    runningVar.data[c] = np.float32(self.momentum * unbiased) + np.float32(np.float32(one - self.momentum) * runningVar.data[c])
+            else:
+                mean = runningMean.data[c]
+                stdev = np.float32(one / np.float32(np.sqrt(np.float32(runningVar.data[c] + self.epsilon))))
+            g = gamma.data[c] if gamma is not None else one
+            b = beta.data[c] if beta is not None else np.float32(0.0)
+            y = ((x[:, c, :] - mean).astype(np.float32) * stdev).astype(np.float32)
+            out[:, c, :] = ((y * g).astype(np.float32) + b).astype(np.float32)
+        mk = lambda v: OracleRawTensor([C], v, self.ops)
+        return OracleRawTensor(list(input.shape), out.reshape(-1), self.ops), mk(cur_mean), mk(cur_std)
+
+    def calculateGrads(self, input, runningMean, runningVar, currentMean, currentStd, gamma, gradOut, inRequiresGrad, gammaRequiresGrad, betaRequiresGrad):
+        if not (inRequiresGrad or gammaRequiresGrad or betaRequiresGrad):
+            return None, None, None
+        outer, C, inner = self._split(input.shape)
+        x = input.data.reshape(outer, C, inner)
+        go = gradOut.data.reshape(outer, C, inner)
+        n = outer * inner
+        grad_in = np.empty_like(x) if inRequiresGrad else None
+        grad_gamma = np.zeros(C, np.float32) if gammaRequiresGrad else None
+        grad_beta = np.zeros(C, np.float32) if betaRequiresGrad else None
+        for c in range(C):
+            g = gamma.data[c] if gamma is not None else np.float32(1.0)
+            if self.training:
+                mean, stdev = currentMean.data[c], currentStd.data[c]
+            else:
+                mean = runningMean.data[c]
+                stdev = np.float32(1.0 / np.sqrt(np.float64(np.float32(runningVar.data[c] + self.epsilon))))
+            xc, gc = x[:, c, :].reshape(-1), go[:, c, :].reshape(-1)
+            total = _seq_sum(gc, self.ops.mode)
+            dot = _seq_sum(((xc - mean).astype(np.float32) * gc).astype(np.float32), self.ops.mode)
+            if grad_in is not None:
+                if self.training:
+                    dps = np.float32(np.float32(np.float32(dot * stdev) * stdev) / np.float32(n))
+                    gm = np.float32(total / np.float32(n))
+                    base = ((x[:, c, :] - mean).astype(np.float32) * dps).astype(np.float32)
+                    t = ((go[:, c, :] - gm).astype(np.float32) - base).astype(np.float32)
+                    grad_in[:, c, :] = ((t * stdev).astype(np.float32) * g).astype(np.float32)
+                else:
+                    grad_in[:, c, :] = ((go[:, c, :] * stdev).astype(np.float32) * g).astype(np.float32)
+            if grad_gamma is not None:
+                grad_gamma[c] = np.float32(dot * stdev)
+            if grad_beta is not None:
+                grad_beta[c] = total
+        wrap = lambda v, shape: None if v is None else OracleRawTensor(shape, v.reshape(-1), self.ops)
+        return wrap(grad_in, list(input.shape)), wrap(grad_gamma, [C]), wrap(grad_beta, [C])
+
+
+class OracleUpsample2DNearest:
+    """JVMUpsample2DNearest.kt:9-79: every input pixel repeated scale x scale times; the gradient of an input pixel is
+    the sum of its block, added in the loop order of :61-68."""
+
+    def __init__(self, scale, ops):
+        self.scale, self.ops = int(scale), ops
+
+    @staticmethod
+    def _check(shape):
+        if len(shape) not in (3, 4):
+            raise ValueError(f"2D Upsampling can only be applied to tensors with 3 or 4 dimensions, but got tensor with shape: {list(shape)}")
+
+    def calculateOutputShape(self, shape):
+        return list(shape[:-2]) + [shape[-2] * self.scale, shape[-1] * self.scale]
+
+    def upsample(self, input):
+        self._check(input.shape)
+        s = self.scale
+        x = input.data.reshape([-1] + list(input.shape[-2:]))
+        out = np.repeat(np.repeat(x, s, axis=1), s, axis=2)
+        return OracleRawTensor(self.calculateOutputShape(input.shape), np.ascontiguousarray(out).reshape(-1), self.ops)
+
+    def calculateGrad(self, gradOut, inputShape):
+        self._check(gradOut.shape)
+        s = self.scale
+        if len(inputShape) != len(gradOut.shape) or gradOut.shape[-2] % s or gradOut.shape[-1] % s \
+                or [gradOut.shape[-2] // s, gradOut.shape[-1] // s] != list(inputShape[-2:]) or list(gradOut.shape[:-2]) != list(inputShape[:-2]):
+            raise ValueError(f"2D Upsample output gradients shape: {list(gradOut.shape)} does not align with input tensor shape: {list(inputShape)} with scale: {s}")
+        H, W = inputShape[-2], inputShape[-1]
+        g = gradOut.data.reshape(-1, H, s, W, s)
+        acc = np.zeros((g.shape[0], H, W), np.float32 if self.ops.mode == 0 else np.float64)
+        for y in range(s):                                  # the column offset is the outer loop (:61-66)
+            for xo in range(s):
+                acc = (acc + g[:, :, xo, :, y]).astype(acc.dtype)
+        return OracleRawTensor(list(inputShape), acc.astype(np.float32).reshape(-1), self.ops)

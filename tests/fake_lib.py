@@ -268,6 +268,13 @@ class FakeLib:
         self._get(out)[:outer * inner] = O.aggregate(op, self._get(a)[:outer * length * inner].copy(), outer, length, inner)
         return 0
 
+    def ktc_sum_to_shape(self, out, out_shape, out_ndim, a, in_shape, in_ndim):
+        self._note("sum_to_shape")
+        ins, outs = _ints(in_shape, in_ndim), _ints(out_shape, out_ndim)
+        n_in, n_out = int(np.prod(ins)), int(np.prod(outs))
+        self._get(out)[:n_out] = O.sum_to_shape(self._get(a)[:n_in].copy(), ins, outs)
+        return 0
+
     def ktc_gather_axis(self, out, inp, in_shape, index, index_shape, ndim, axis):
         self._note("gather")
         ins, ixs = _ints(in_shape, ndim), _ints(index_shape, ndim)

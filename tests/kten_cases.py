@@ -236,3 +236,92 @@ def softmax_cross_entropy_property(ops, rows=256, classes=2048, seed=77, tol=1e-
     assert g1.shape == g2.shape == (rows, classes)
     assert float(np.abs(g1.astype(np.float64) - g2.astype(np.float64)).max()) <= tol
     return got, g1, x, t
+
+
+def _close(a, b, tol):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    assert a.shape == b.shape, (a.shape, b.shape)
+    assert float(np.abs(a - b).max(initial=0.0)) <= tol, float(np.abs(a - b).max())
+
+
+def batch_norm_training_property(ops, with_affine=True, seed=5, tol=1e-4):
+    """should_calculate_batch_norm_for_specified_axis_in_train_mode and ..._in_training_mode_without_gamma_and_beta
+    (kten-testing/.../TensorTestsBase.kt:2015-2064, 2099-2131): batchNorm along axis 1 of a [10, 3, 4, 5] tensor against
+    the same normalisation spelled with mean / variance tensors -- output (the reference allows 0.02 / 0.01 here: the
+    spelled form divides by the unbiased variance), running statistics, and the gradients of input, gamma and beta.
+    The reference draws its tensors from an unseeded generator; here they are seeded.  Returns the arrays."""
+    rng = np.random.default_rng(seed)
+    rnd = lambda *shape: rng.uniform(0.0, 1.0, shape).astype(np.float32)
+    axis, momentum, epsilon = 1, 0.1, 1e-3
+    tensor = AG.tensorOf(ops, rnd(10, 3, 4, 5), requiresGrad=True)
+    gamma = AG.tensorOf(ops, rnd(1, 3, 1, 1), requiresGrad=True) if with_affine else None
+    beta = AG.tensorOf(ops, rnd(1, 3, 1, 1), requiresGrad=True) if with_affine else None
+    running_mean_base, running_var_base = AG.tensorOf(ops, rnd(1, 3, 1, 1)), AG.tensorOf(ops, rnd(1, 3, 1, 1))
+
+    t = tensor.permute(1, 0, 2, 3).view(3, -1)
+    m, v = t.meanVariance(1)
+    mean, variance = m.view(1, 3, 1, 1), v.view(1, 3, 1, 1)
+    running_mean = (mean.noGrad() * momentum) + running_mean_base * (1.0 - momentum)
+    running_var = (variance.noGrad() * momentum) + running_var_base * (1.0 - momentum)
+    result = (tensor - mean) / (variance + epsilon).sqrt()
+    if with_affine:
+        result = result * gamma + beta
+    result.sum().backward()
+    want = {"out": result.toArray(), "gx": tensor.grad().toArray(), "rm": running_mean.toArray().reshape(3), "rv": running_var.toArray().reshape(3)}
+    if with_affine:
+        want["gg"], want["gb"] = gamma.grad().toArray(), beta.grad().toArray()
+    for var in (tensor, gamma, beta):
+        if var is not None:
+            var.zeroGrad()
+
+    running_mean2, running_var2 = running_mean_base.reshape(3), running_var_base.reshape(3)
+    result2 = tensor.batchNorm(axis, running_mean2, running_var2, True, momentum, epsilon,
+                               gamma.view(3) if with_affine else None, beta.view(3) if with_affine else None)
+    result2.sum().backward()
+    got = {"out": result2.toArray(), "gx": tensor.grad().toArray(), "rm": running_mean2.toArray(), "rv": running_var2.toArray()}
+    if with_affine:
+        got["gg"], got["gb"] = gamma.grad().toArray(), beta.grad().toArray()
+    _close(got["out"], want["out"], 0.02 if with_affine else 0.01)
+    for k in ("rm", "rv", "gx") + (("gg", "gb") if with_affine else ()):
+        _close(got[k], want[k], tol)
+    return got
+
+
+def batch_norm_inference_property(ops, with_affine=True, seed=6, tol=1e-6):
+    """should_calculate_batch_norm_for_specified_axis_in_inference_mode and ..._without_gamma_and_beta
+    (TensorTestsBase.kt:2066-2090, 2133-2150): axis 2 of [10, 3, 4, 5], running statistics given."""
+    rng = np.random.default_rng(seed)
+    rnd = lambda *shape: rng.uniform(0.0, 1.0, shape).astype(np.float32)
+    tensor = AG.tensorOf(ops, rnd(10, 3, 4, 5))
+    gamma = AG.tensorOf(ops, rnd(1, 1, 4, 1)) if with_affine else None
+    beta = AG.tensorOf(ops, rnd(1, 1, 4, 1)) if with_affine else None
+    running_mean, running_var = AG.tensorOf(ops, rnd(1, 1, 4, 1)), AG.tensorOf(ops, rnd(1, 1, 4, 1))
+    result = (tensor - running_mean) / (running_var + 1e-3).sqrt()
+    if with_affine:
+        result = result * gamma + beta
+    result2 = tensor.batchNorm(2, running_mean.reshape(4), running_var.reshape(4), False, 0.1, 1e-3,
+                               gamma.view(4) if with_affine else None, beta.view(4) if with_affine else None)
+    got, want = result2.toArray(), result.toArray()
+    _close(got, want, tol)
+    return got
+
+
+def upsample_nearest_property(ops, seed=7, tol=4e-6):        # block sums reach 24: two float roundings against one are 2 ulp = 3.8e-6
+    """should_calculate_upsample_nearest_with_grads (TensorTestsBase.kt:2152-2180): upsample2d of [5, 3, 4, 5] by 3
+    against view / expand / view, values and the gradients of sum(exp(.))."""
+    rng = np.random.default_rng(seed)
+    x = rng.uniform(0.0, 1.0, (5, 3, 4, 5)).astype(np.float32)
+    scale = 3
+    tensor = AG.tensorOf(ops, x, requiresGrad=True)
+    spelled = tensor.view(5, 3, 4, 1, 5, 1).expand(5, 3, 4, scale, 5, scale).view(5, 3, scale * 4, scale * 5)
+    want_out = spelled.noGrad().toArray()
+    spelled.exp().sum().backward()
+    want_grad = tensor.grad().toArray()
+    tensor.zeroGrad()
+    ups = tensor.upsample2d(scale)
+    got_out = ups.noGrad().toArray()
+    ups.exp().sum().backward()
+    got_grad = tensor.grad().toArray()
+    assert np.array_equal(got_out, want_out)
+    _close(got_grad, want_grad, tol)
+    return got_out, got_grad
