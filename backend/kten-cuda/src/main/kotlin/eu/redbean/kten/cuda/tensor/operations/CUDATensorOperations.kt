@@ -17,6 +17,8 @@ import eu.redbean.kten.api.tensor.operations.nn.UpsampleType
 import eu.redbean.kten.api.tensor.serialization.CommonSerializableTensorDescriptor
 import eu.redbean.kten.api.tensor.serialization.SerializableTensorData
 import eu.redbean.kten.api.tensor.store.AbstractRawTensor
+import eu.redbean.kten.cuda.tensor.operations.nn.CUDABatchNorm
+import eu.redbean.kten.cuda.tensor.operations.nn.CUDAUpsample2DNearest
 import eu.redbean.kten.cuda.tensor.platform.KtcNative
 import eu.redbean.kten.cuda.tensor.platform.KtcNative.check
 import eu.redbean.kten.cuda.tensor.store.CUDABuffer
@@ -187,6 +189,10 @@ class CUDATensorOperations(override val platformKey: String, val device: Int) : 
                                                 outputPadding: List<Int>): ConvolutionOperation<CUDARawTensor> = unsupported("volumetricConvolutionTranspose")
     override fun spatialPooling(kernel: List<Int>, padding: List<Int>, stride: List<Int>, dilation: List<Int>,
                                 options: PoolingOptions): PoolingOperation<CUDARawTensor> = unsupported("spatialPooling")
-    override fun batchNorm(axis: Int, momentum: Float, epsilon: Float, training: Boolean): BatchNormOperation<CUDARawTensor> = unsupported("batchNorm")
-    override fun upsample(upsampleType: UpsampleType, scale: Int): Upsample2DOperation<CUDARawTensor> = unsupported("upsample")
+    // reductions and broadcast maps: built from raw-tensor calls on the path's kernels (operations/nn/CUDANnOperations.kt)
+    override fun batchNorm(axis: Int, momentum: Float, epsilon: Float, training: Boolean): BatchNormOperation<CUDARawTensor> =
+        CUDABatchNorm(axis, momentum, epsilon, training, this)
+    override fun upsample(upsampleType: UpsampleType, scale: Int): Upsample2DOperation<CUDARawTensor> = when (upsampleType) {
+        UpsampleType.NEAREST -> CUDAUpsample2DNearest(scale, this)
+    }
 }

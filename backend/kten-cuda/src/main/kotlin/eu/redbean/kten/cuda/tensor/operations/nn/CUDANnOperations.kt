@@ -1,0 +1,136 @@
+package eu.redbean.kten.cuda.tensor.operations.nn
+
+import eu.redbean.kten.api.autograd.utils.toStoreSize
+import eu.redbean.kten.api.tensor.operations.nn.BatchNormOperation
+import eu.redbean.kten.api.tensor.operations.nn.Upsample2DOperation
+import eu.redbean.kten.cuda.tensor.operations.CUDATensorOperations
+import eu.redbean.kten.cuda.tensor.store.CUDARawTensor
+
+/**
+ * Batch normalisation and nearest-neighbour upsampling as compositions of raw-tensor calls (the mirror of
+ * kten_b200/nn.py).  Neither needs a kernel of its own: viewed as [outer, C * inner] the per-channel sums of a batch
+ * norm are leading-axis sums of an elementwise expression followed by a small sum over `inner`, its output a
+ * broadcast map with row vectors of C * inner floats.  The calls are recorded (ops.lazy) while an operation runs, so a
+ * training forward is three passes over the input and the backward two; every per-element operation is kten-jvm's
+ * float operation in kten-jvm's order (JVMBatchNorm.kt:32-165).  Not compiled: no JDK on this box.
+ */
+private inline fun <T> CUDATensorOperations.recorded(body: () -> T): T {
+    val was = lazy
+    lazy = true
+    try {
+        return body()
+    } finally {
+        lazy = was
+    }
+}
+
+class CUDABatchNorm(
+    val axis: Int,
+    val momentum: Float,
+    val epsilon: Float,
+    val training: Boolean,
+    val ops: CUDATensorOperations
+) : BatchNormOperation<CUDARawTensor> {
+
+    private fun split(shape: List<Int>) = Triple(shape.take(axis).toStoreSize(), shape[axis], shape.drop(axis + 1).toStoreSize())
+
+    /** A [C] tensor as the row vector [1, C * inner] that broadcasts against [outer, C * inner]. */
+    private fun row(t: CUDARawTensor, c: Int, inner: Int): CUDARawTensor =
+        if (inner == 1) t.view(listOf(1, c)) else t.view(listOf(c, 1)).broadcastTo(listOf(c, inner)).view(listOf(1, c * inner))
+
+    private fun channelSums(t: CUDARawTensor, c: Int, inner: Int): CUDARawTensor {
+        val s = t.sum(0, false) as CUDARawTensor
+        return if (inner == 1) s else s.view(listOf(c, inner)).sum(1, false) as CUDARawTensor
+    }
+
+    override fun calculateOutput(
+        input: CUDARawTensor, runningMean: CUDARawTensor?, runningVar: CUDARawTensor?, gamma: CUDARawTensor?, beta: CUDARawTensor?
+    ): BatchNormOperation.BatchNormOutputs<CUDARawTensor> = ops.recorded {
+        val (outer, c, inner) = split(input.shape)
+        val n = outer * inner
+        val x = input.view(listOf(outer, c * inner))
+        var mean: CUDARawTensor
+        var stdev: CUDARawTensor
+        if (training) {
+            mean = channelSums(x, c, inner).div(n.toFloat()) as CUDARawTensor
+            val d = x.minus(row(mean, c, inner)) as CUDARawTensor
+            val ssq = channelSums(d.times(d) as CUDARawTensor, c, inner)
+            val variance = ssq.div(n.toFloat()).plus(epsilon) as CUDARawTensor
+            stdev = if (epsilon == 0f)          // sum == 0 and epsilon == 0: 0f instead of 1f / 0f (JVMBatchNorm.kt:63-65)
+                (variance.plus(ssq.lte(0f)).sqrt().reciprocal() as CUDARawTensor).times(ssq.gt(0f)) as CUDARawTensor
+            else variance.sqrt().reciprocal() as CUDARawTensor
+            if (runningMean != null && runningVar != null) {
+                val keep = 1f - momentum
+                runningMean.timesAssign(keep)
+                runningMean.plusAssign(mean.times(momentum))
+                runningVar.timesAssign(keep)
+                runningVar.plusAssign(ssq.div((n - 1).toFloat()).times(momentum))
+            }
+        } else {
+            mean = runningMean!!
+            stdev = runningVar!!.plus(epsilon).sqrt().reciprocal() as CUDARawTensor
+        }
+        var y = x.minus(row(mean, c, inner)).times(row(stdev, c, inner)) as CUDARawTensor
+        if (gamma != null) y = y.times(row(gamma, c, inner)) as CUDARawTensor
+        y = (if (beta != null) y.plus(row(beta, c, inner)) else y.plus(0f)) as CUDARawTensor
+        if (!training) {                        // kten-jvm leaves both untouched (zeros) in inference mode
+            mean = ops.createRawFill(listOf(c), 0f)
+            stdev = ops.createRawFill(listOf(c), 0f)
+        }
+        BatchNormOperation.BatchNormOutputs(y.view(input.shape), mean, stdev)
+    }
+
+    override fun calculateGrads(
+        input: CUDARawTensor, runningMean: CUDARawTensor?, runningVar: CUDARawTensor?, currentMean: CUDARawTensor, currentStd: CUDARawTensor,
+        gamma: CUDARawTensor?, gradOut: CUDARawTensor, inRequiresGrad: Boolean, gammaRequiresGrad: Boolean, betaRequiresGrad: Boolean
+    ): BatchNormOperation.BatchNormGrads<CUDARawTensor> {
+        if (!inRequiresGrad && !gammaRequiresGrad && !betaRequiresGrad) return BatchNormOperation.BatchNormGrads(null, null, null)
+        return ops.recorded {
+            val (outer, c, inner) = split(input.shape)
+            val n = outer * inner
+            val x = input.view(listOf(outer, c * inner))
+            val go = gradOut.view(listOf(outer, c * inner))
+            val mean = if (training) currentMean else runningMean!!
+            val stdev = if (training) currentStd else runningVar!!.plus(epsilon).rsqrt() as CUDARawTensor
+            val d = x.minus(row(mean, c, inner)) as CUDARawTensor
+            // both sums stay pending until the first is needed: one pass over x and gradOut with two sinks
+            val sGo = go.sum(0, false) as CUDARawTensor
+            val sDot = d.times(go).sum(0, false) as CUDARawTensor
+            val total = if (inner == 1) sGo else sGo.view(listOf(c, inner)).sum(1, false) as CUDARawTensor
+            val dot = if (inner == 1) sDot else sDot.view(listOf(c, inner)).sum(1, false) as CUDARawTensor
+            var gradIn: CUDARawTensor? = null
+            if (inRequiresGrad) {
+                val stdRow = row(stdev, c, inner)
+                var t = if (training) {
+                    val dps = dot.times(stdev).times(stdev).div(n.toFloat()) as CUDARawTensor
+                    val gradMean = total.div(n.toFloat()) as CUDARawTensor
+                    go.minus(row(gradMean, c, inner)).minus(d.times(row(dps, c, inner))).times(stdRow) as CUDARawTensor
+                } else go.times(stdRow) as CUDARawTensor
+                if (gamma != null) t = t.times(row(gamma, c, inner)) as CUDARawTensor
+                gradIn = t.view(input.shape)
+            }
+            BatchNormOperation.BatchNormGrads(gradIn, if (gammaRequiresGrad) dot.times(stdev) as CUDARawTensor else null, if (betaRequiresGrad) total else null)
+        }
+    }
+}
+
+class CUDAUpsample2DNearest(override val scale: Int, val ops: CUDATensorOperations) : Upsample2DOperation<CUDARawTensor> {
+
+    override fun upsample(input: CUDARawTensor): CUDARawTensor {
+        checkDimensions(input.shape)
+        val rows = input.shape.dropLast(1).toStoreSize()
+        val w = input.shape.last()
+        return ops.recorded {
+            input.view(listOf(rows, 1, w, 1)).broadcastTo(listOf(rows, scale, w, scale)).view(calculateOutputShape(input.shape))
+        }
+    }
+
+    override fun calculateGrad(gradOut: CUDARawTensor, inputShape: List<Int>): CUDARawTensor {
+        checkDimensions(gradOut.shape)
+        checkGradOutShape(gradOut.shape, inputShape)
+        val rows = inputShape.dropLast(1).toStoreSize()
+        val w = inputShape.last()
+        val blocks = gradOut.view(listOf(rows, scale, w, scale))
+        return (blocks.sum(3, true).sum(1, true) as CUDARawTensor).view(inputShape)
+    }
+}
