@@ -4,6 +4,8 @@ import eu.redbean.kten.api.autograd.utils.toStoreSize
 import eu.redbean.kten.api.tensor.operations.nn.BatchNormOperation
 import eu.redbean.kten.api.tensor.operations.nn.Upsample2DOperation
 import eu.redbean.kten.cuda.tensor.operations.CUDATensorOperations
+import eu.redbean.kten.cuda.tensor.platform.KtcNative
+import eu.redbean.kten.cuda.tensor.platform.KtcNative.check
 import eu.redbean.kten.cuda.tensor.store.CUDARawTensor
 
 /**
@@ -93,8 +95,9 @@ class CUDABatchNorm(
             val mean = if (training) currentMean else runningMean!!
             val stdev = if (training) currentStd else runningVar!!.plus(epsilon).rsqrt() as CUDARawTensor
             val d = x.minus(row(mean, c, inner)) as CUDARawTensor
-            // both sums stay pending until the first is needed: one pass over x and gradOut with two sinks
-            val sGo = go.sum(0, false) as CUDARawTensor
+            // both sums stay pending until the first is needed: one pass over x and gradOut with two sinks (a sum of a stored
+            // tensor would run at once, so gradOut enters as the expression gradOut * 1f, which is gradOut bit for bit)
+            val sGo = go.times(1f).sum(0, false) as CUDARawTensor
             val sDot = d.times(go).sum(0, false) as CUDARawTensor
             val total = if (inner == 1) sGo else sGo.view(listOf(c, inner)).sum(1, false) as CUDARawTensor
             val dot = if (inner == 1) sDot else sDot.view(listOf(c, inner)).sum(1, false) as CUDARawTensor
@@ -118,19 +121,18 @@ class CUDAUpsample2DNearest(override val scale: Int, val ops: CUDATensorOperatio
 
     override fun upsample(input: CUDARawTensor): CUDARawTensor {
         checkDimensions(input.shape)
-        val rows = input.shape.dropLast(1).toStoreSize()
-        val w = input.shape.last()
-        return ops.recorded {
-            input.view(listOf(rows, 1, w, 1)).broadcastTo(listOf(rows, scale, w, scale)).view(calculateOutputShape(input.shape))
-        }
+        val rows = input.shape.dropLast(1).toStoreSize().toLong()
+        val out = ops.createRaw(calculateOutputShape(input.shape))
+        check(KtcNative.upsample2dNearest.invokeExact(out.handle, input.handle, rows, input.shape.last().toLong(), scale) as Int)
+        return out
     }
 
     override fun calculateGrad(gradOut: CUDARawTensor, inputShape: List<Int>): CUDARawTensor {
         checkDimensions(gradOut.shape)
         checkGradOutShape(gradOut.shape, inputShape)
-        val rows = inputShape.dropLast(1).toStoreSize()
-        val w = inputShape.last()
-        val blocks = gradOut.view(listOf(rows, scale, w, scale))
-        return (blocks.sum(3, true).sum(1, true) as CUDARawTensor).view(inputShape)
+        val rows = inputShape.dropLast(1).toStoreSize().toLong()
+        val gradIn = ops.createRaw(inputShape)
+        check(KtcNative.upsample2dNearestGrad.invokeExact(gradIn.handle, gradOut.handle, rows, inputShape.last().toLong(), scale) as Int)
+        return gradIn
     }
 }

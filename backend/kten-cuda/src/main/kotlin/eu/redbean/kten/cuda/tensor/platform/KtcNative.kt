@@ -89,6 +89,9 @@ internal object KtcNative {
         ADDRESS, JAVA_INT, ADDRESS, ADDRESS, ADDRESS, JAVA_INT, ADDRESS, ADDRESS, JAVA_LONG, ADDRESS, ADDRESS, JAVA_INT)
     // SoftmaxCrossEntropy.doForward in one pass: (softmax, nll, logits, targets, rows, cols, lo, hi); KTC_ENOTSUP (-4): issue the calls instead
     val softmaxXentForward = handle("ktc_softmax_xent_forward", JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_FLOAT, JAVA_FLOAT)
+    // nearest-neighbour upsampling and its gradient: (out, in, P, W, scale) with P = the product of all dimensions but the last
+    val upsample2dNearest = handle("ktc_upsample2d_nearest", JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_INT)
+    val upsample2dNearestGrad = handle("ktc_upsample2d_nearest_grad", JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_INT)
     const val ENOTSUP = -4
     // the deferred-expression recorder: elementwise calls and sums are recorded below the C ABI and run fused when a value is needed
     const val EXPR_SUM_ALL = 1; const val EXPR_SUM_ROWS = 2; const val EXPR_SUM_LAST = 4

@@ -55,7 +55,7 @@ class CUDARawTensor(
     }
 
     /** The buffer handle; a pending value is computed first, a recorded `+= pending sum` update of the buffer applied. */
-    private val handle: Long
+    internal val handle: Long
         get() {
             if (released) throw IllegalStateException("Raw tensor already released")
             val slot = storeReference

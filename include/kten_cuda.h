@@ -198,6 +198,14 @@ KTC_API int ktc_sum_to_shape(ktc_buf out, const int64_t* old_shape, int old_ndim
  * a multiple of 4, unaligned rows): issue the separate calls. */
 KTC_API int ktc_softmax_xent_forward(ktc_buf softmax, ktc_buf nll, ktc_buf logits, ktc_buf targets, int64_t rows, int64_t cols, float lo, float hi);
 
+/* Nearest-neighbour upsampling of the last two dimensions by `scale` and its gradient (TensorOperations.upsample,
+ * TensorOperations.kt:131; Upsample2DOperation.kt:5-44; kten-jvm: JVMUpsample2DNearest.kt:14-77).  P is the product of
+ * all dimensions but the last (N * C * H): in [P, W] -> out [P, scale, W * scale]; grad_out [P, scale, W * scale] ->
+ * grad_in [P, W], every position the sum of its scale x scale block (double accumulation in the reference's loop
+ * order, one rounding). */
+KTC_API int ktc_upsample2d_nearest(ktc_buf out, ktc_buf in, int64_t P, int64_t W, int scale);
+KTC_API int ktc_upsample2d_nearest_grad(ktc_buf grad_in, ktc_buf grad_out, int64_t P, int64_t W, int scale);
+
 /* Full sum / mean that obtains no memory, for callers that must not allocate
  * while they run: loops whose free device memory is already committed to
  * another allocator, latency-bound sections that cannot take the device-wide
@@ -234,7 +242,7 @@ KTC_API int ktc_reduce_all_noalloc(int op, ktc_buf out, ktc_buf in, int64_t n);
  * multiple of 4, unaligned rows): issue the separate calls instead. */
 #define KTC_EXPR_MAX_INSTR 32
 #define KTC_EXPR_MAX_IMM 16
-#define KTC_EXPR_MAX_LEAVES 6
+#define KTC_EXPR_MAX_LEAVES 8
 #define KTC_EXPR_MAX_STORES 3
 #define KTC_EXPR_REGS 8
 #define KTC_EXPR_MAX_SINKS 4

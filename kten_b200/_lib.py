@@ -30,7 +30,7 @@ P2P_HANDLE_BYTES, P2P_MAX_RANKS, P2P_MAX_FLOATS, P2P_MAX_TENSORS = 64, 16, 16384
 (X_LOAD, X_CONST, X_ADD, X_SUB, X_MUL, X_DIV, X_POW, X_NEG, X_RCP, X_SQUARE, X_EXP, X_LOG, X_TANH, X_SIGMOID, X_CLAMP,
  X_CMP_LT, X_CMP_LTE, X_CMP_GT, X_CMP_GTE, X_STORE, X_ACC, X_SCATC) = range(1, 23)
 EXPR_STORE_ONLY, EXPR_SUM_ALL, EXPR_SUM_ROWS, EXPR_MULTI, EXPR_SUM_LAST = 0, 1, 2, 3, 4
-EXPR_MAX_INSTR, EXPR_MAX_IMM, EXPR_MAX_LEAVES, EXPR_MAX_STORES, EXPR_REGS, EXPR_MAX_SINKS = 32, 16, 6, 3, 8, 4
+EXPR_MAX_INSTR, EXPR_MAX_IMM, EXPR_MAX_LEAVES, EXPR_MAX_STORES, EXPR_REGS, EXPR_MAX_SINKS = 32, 16, 8, 3, 8, 4
 NOALLOC_SCRATCH_BYTES = 16384
 NOALLOC_MAX_ELEMS = 1 << 30
 
@@ -114,6 +114,8 @@ _PROTOTYPES = {
     "ktc_lazy_assign_fill": (i32, [u64, f32, p_i32]),
     "ktc_lazy_assign_scatter_const": (i32, [u64, u64, f32, p_i32]),
     "ktc_softmax_xent_forward": (i32, [u64, u64, u64, u64, i64, i64, f32, f32]),
+    "ktc_upsample2d_nearest": (i32, [u64, u64, i64, i64, i32]),
+    "ktc_upsample2d_nearest_grad": (i32, [u64, u64, i64, i64, i32]),
     "ktc_sum_to_shape": (i32, [u64, p_i64, i32, u64, p_i64, i32]),
     "ktc_scatter_axis": (i32, [u64, u64, u64, i64, i64, i64]),
     "ktc_comm_unique_id": (i32, [C.c_char_p]),

@@ -10,7 +10,9 @@ reads its operands once; run call by call they are the library's ordinary kernel
 the reference's float operation in the reference's order, so given the same per-channel statistics the outputs are
 bit-identical; the statistics themselves are sums (double accumulation, compared within the reduction tolerance).
 
-Upsampling is a broadcast copy ([R, 1, W, 1] -> [R, s, W, s]) and its gradient a sum back to the small shape."""
+Upsampling is a broadcast copy ([R, 1, W, 1] -> [R, s, W, s]) and its gradient a sum back to the small shape; with an
+innermost extent of s (2, 3 ...) the general broadcast and reduction kernels fall to their element-wise forms, so the
+library has two small kernels for it (ktc_nn.cu) and the composition remains as the form a backend without them uses."""
 from __future__ import annotations
 
 from typing import List, Optional, Sequence
@@ -127,8 +129,9 @@ class CUDABatchNorm:
                 stdev = runningVar.plus(self.epsilon).rsqrt()                           # (1.0 / sqrt(double)).toFloat(), :117
             mean_row = self._row(mean, C, inner)
             d = x.minus(mean_row)
-            # both sums are pending until the first is needed: one pass over x and gradOut with two sinks
-            s_go = go.sum(0)
+            # both sums are pending until the first is needed: one pass over x and gradOut with two sinks (a sum of a stored
+            # tensor would run at once, so gradOut enters as the expression gradOut * 1f, which is gradOut bit for bit)
+            s_go = go.times(1.0).sum(0)
             s_dot = d.times(go).sum(0)
             total = s_go if inner == 1 else s_go.view([C, inner]).sum(1)                # :120-123
             dot = s_dot if inner == 1 else s_dot.view([C, inner]).sum(1)                # :125-128
@@ -186,7 +189,13 @@ class CUDAUpsample2DNearest:
         self.checkDimensions(input.shape)
         s = self.scale
         rows, W = _volume(input.shape[:-1]), int(input.shape[-1])
-        with _Recorded(self.ops) as rec:
+        entry = getattr(self.ops.lib, "ktc_upsample2d_nearest", None)
+        if entry is not None:                                      # the library's kernel
+            from . import _lib as L
+            out = self.ops.createRaw(self.calculateOutputShape(input.shape))
+            L.check(entry(out._buf(), input._buf(), rows, W, s))
+            return out
+        with _Recorded(self.ops) as rec:                           # a broadcast copy [rows, 1, W, 1] -> [rows, s, W, s]
             out = input.view([rows, 1, W, 1]).broadcastTo([rows, s, W, s]).view(self.calculateOutputShape(input.shape))
             rec.settle(out)
         return out
@@ -196,4 +205,10 @@ class CUDAUpsample2DNearest:
         self.checkGradOutShape(gradOut.shape, inputShape)
         s = self.scale
         rows, W = _volume(inputShape[:-1]), int(inputShape[-1])
+        entry = getattr(self.ops.lib, "ktc_upsample2d_nearest_grad", None)
+        if entry is not None:
+            from . import _lib as L
+            res = self.ops.createRaw(list(inputShape))
+            L.check(entry(res._buf(), gradOut._buf(), rows, W, s))
+            return res
         return gradOut.view([rows, s, W, s]).sumToShape([rows, 1, W, 1]).view(list(inputShape))

@@ -68,8 +68,8 @@ def test_registers_are_reused_and_limits_fall_back_to_separate_calls():
         cur, want = cur.plus(0.5), (want + np.float32(0.5)).astype(np.float32)
     assert np.array_equal(cur.toArray(), want)
     many, wantm = x, X.copy()
-    others = [rnd([16], 20 + h) for h in range(7)]
-    for o in others:                                                                # 8 distinct leaves > 6
+    others = [rnd([16], 20 + h) for h in range(9)]
+    for o in others:                                                                # 10 distinct leaves > 8
         many, wantm = many.times(ops.createRaw([16], o)), (wantm * o).astype(np.float32)
     before = ops.unfusedEvaluations
     assert np.array_equal(many.toArray(), wantm) and ops.unfusedEvaluations > before
