@@ -521,6 +521,7 @@ def run_sharded_graph(ops, lib, L, D, rank, world, collective, steps, warmup, di
     res["compiled_host"] = {"deferred": native_fused, "call_by_call": native_eager}
     if "ms_per_step" in native_fused and native_fused["ms_per_step"] < res["ms_per_step"]:
         res.update({k: native_fused[k] for k in ("ms_per_step", "gelem_per_s", "kernel_launches_per_step", "multi_sink_passes_per_step",
+                                                 "updates_in_second_pass_per_step", "exchanges_in_second_pass_per_step",
                                                  "grad_w_abs_sum", "grad_b_abs_sum")})
         res["execution"] = "deferred elementwise calls and sums, one pass with three sinks per step, issued by the compiled host (libkten_host.so)"
         res["host_us_per_step"] = native_fused["host_us_per_step"]

@@ -407,6 +407,12 @@ static int expr_eval_impl(Device** scatc_dev, const uint32_t* code, int n_code, 
         while (seg_rows > 8 && ((rows + seg_rows - 1) / seg_rows + 7) / 8 * a.col_tiles < want) seg_rows /= 2;
     }
     if (seg_rows > rows) seg_rows = rows;
+    if ((multi || sink != KTC_EXPR_STORE_ONLY) && rows >= 64) {
+        // a summing CTA folds eight segments: spread the rows evenly over whole groups of eight, so that a short row space
+        // (256 rows of a batch-norm statistic: four segments of 64) does not leave half of every CTA's warps without work
+        const int64_t groups8 = (rows + 8 * seg_rows - 1) / (8 * seg_rows);
+        seg_rows = (rows + 8 * groups8 - 1) / (8 * groups8);
+    }
     a.seg_rows = seg_rows;
     int64_t Sg = (rows + seg_rows - 1) / seg_rows;
 

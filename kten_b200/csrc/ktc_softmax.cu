@@ -50,8 +50,9 @@ __device__ __forceinline__ float sx_row_sum(const float4 (&v)[kSxMaxVec], int n_
 }
 
 // NV > 0: every lane owns exactly NV vectors (cols == 128 NV) and the guards below fold away; NV == 0: any row length
-template <int NV>
-__global__ void __launch_bounds__(256) k_softmax_xent_forward(const float* __restrict__ logits, const float* __restrict__ targets,
+// MINB: resident CTAs per SM the register allocation must allow (the row of 2048 columns alone is 64 registers per lane)
+template <int NV, int MINB>
+__global__ void __launch_bounds__(256, MINB) k_softmax_xent_forward(const float* __restrict__ logits, const float* __restrict__ targets,
                                                               float* __restrict__ softmax, float* __restrict__ nll,
                                                               int64_t rows, int cols, float lo, float hi, int* err) {
     const int lane = threadIdx.x & 31;
@@ -118,8 +119,9 @@ int launch_softmax_xent_forward(Device* d, float* softmax, float* nll, const flo
     if (rows == 0) return KTC_OK;
     const int64_t grid = (rows + 7) / 8;
     if (grid > 0x7fffffffLL) return fail(KTC_ENOTSUP, "tensor too large for one launch");
-#define KTC_SX(NV) k_softmax_xent_forward<NV><<<(int)grid, 256, 0, d->stream>>>(logits, targets, softmax, nll, rows, (int)cols, lo, hi, d->idx_err)
-    if (cols == 2048) KTC_SX(16); else if (cols == 1024) KTC_SX(8); else if (cols == 512) KTC_SX(4); else KTC_SX(0);
+#define KTC_SX(NV, MINB) k_softmax_xent_forward<NV, MINB><<<(int)grid, 256, 0, d->stream>>>(logits, targets, softmax, nll, rows, (int)cols, lo, hi, d->idx_err)
+    if (cols == 2048) { if (tune("softmax_min_blocks", 2) == 3) KTC_SX(16, 3); else KTC_SX(16, 2); }
+    else if (cols == 1024) KTC_SX(8, 3); else if (cols == 512) KTC_SX(4, 4); else KTC_SX(0, 2);
 #undef KTC_SX
     count_launch(1);
     cudaError_t e = cudaGetLastError();
