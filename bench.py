@@ -540,6 +540,38 @@ def run_sharded_graph(ops, lib, L, D, rank, world, collective, steps, warmup, di
     return res
 
 
+def release_loss(loss):
+    """Drops what a finished SoftmaxCrossEntropy step still holds -- the retained [1] output of the root and the
+    unsqueezed targets -- so that a loop of steps returns every buffer to the pool (on the JVM the tensors' owner does
+    this; left alone each step would take two small device allocations)."""
+    loss.keepOutput, loss.freeOutput = False, True
+    loss.releaseUnusedInGraph()
+    loss.targets.getRawValue().release()
+
+
+def timed_in_batches(ops, lib, L, fn, reps, batches=5):
+    """ms per call of `fn` (run inside a collector scope), timed in `batches` batches of `reps` calls with device events:
+    returns (fastest batch, median batch, launches per call).  These steps are issued by the Python host, whose time per
+    step (0.2-0.5 ms) is of the order of the device time: a batch in which the host is disturbed measures the host, so
+    the fastest batch is the device figure and the median is printed beside it."""
+    ms = C.c_float(0)
+    per = []
+    l0 = lib.ktc_launch_count()
+    m0 = ops.getMetrics()
+    for _ in range(batches):
+        ops.synchronize()
+        L.check(lib.ktc_timer_start(ops.device))
+        for _ in range(reps):
+            with ops.garbageCollector():
+                fn()
+        L.check(lib.ktc_timer_stop(ops.device, C.byref(ms)))
+        per.append(ms.value / reps)
+    per.sort()
+    m1 = ops.getMetrics()
+    timed_in_batches.last_device_mallocs = (m1["allocCalls"] - m1["poolHits"]) - (m0["allocCalls"] - m0["poolHits"])
+    return per[0], per[len(per) // 2], (lib.ktc_launch_count() - l0) / (reps * batches)
+
+
 def run_other_ops(ops, lib, L, D, steps):
     """The raw-tensor ops beside the sweep (slices, permutes, gather / scatter, the remaining maps), timed the same
     way on 2^28-element tensors: GB/s of algorithmic bytes (inputs read once + output written once)."""
@@ -609,6 +641,7 @@ def run_other_ops(ops, lib, L, D, steps):
         loss = logits.softmaxCrossEntropy(targets)
         loss.backward()
         logits.gradient.storeReference
+        release_loss(loss)
 
     for mode, label in ((False, "call by call"), (True, "deferred")):
         ops.lazy = mode
@@ -616,18 +649,11 @@ def run_other_ops(ops, lib, L, D, steps):
             for _ in range(4):                              # the buffer pool settles over the first steps
                 with ops.garbageCollector():
                     xent()
-            ops.synchronize()
-            l0 = lib.ktc_launch_count()
-            L.check(lib.ktc_timer_start(ops.device))
-            for _ in range(reps):
-                with ops.garbageCollector():
-                    xent()
-            L.check(lib.ktc_timer_stop(ops.device, C.byref(ms)))
+            per, med, launches = timed_in_batches(ops, lib, L, xent, max(2, reps // 2))
         finally:
             ops.lazy = False
-        per = ms.value / reps
-        out.append({"name": f"softmaxCrossEntropy [131072,2048] forward + backward, {label}", "ms": round(per, 4), "gbs": round(2 * G / per / 1e6, 1),
-                    "launches": (lib.ktc_launch_count() - l0) / reps})
+        out.append({"name": f"softmaxCrossEntropy [131072,2048] forward + backward, {label}", "ms": round(per, 4), "ms_median_batch": round(med, 4),
+                    "gbs": round(2 * G / per / 1e6, 1), "launches": launches})
     logits.gradient.release()
     logits.getRawValue().release()
     targets.getRawValue().release()
@@ -663,15 +689,8 @@ def run_other_ops(ops, lib, L, D, steps):
         for _ in range(3):
             with ops.garbageCollector():
                 fn()
-        ops.synchronize()
-        l0 = lib.ktc_launch_count()
-        L.check(lib.ktc_timer_start(ops.device))
-        for _ in range(reps):
-            with ops.garbageCollector():
-                fn()
-        L.check(lib.ktc_timer_stop(ops.device, C.byref(ms)))
-        per = ms.value / reps
-        out.append({"name": name, "ms": round(per, 4), "gbs": round(nbytes / per / 1e6, 1), "launches": (lib.ktc_launch_count() - l0) / reps})
+        per, med, launches = timed_in_batches(ops, lib, L, fn, max(2, reps // 2))
+        out.append({"name": name, "ms": round(per, 4), "ms_median_batch": round(med, 4), "gbs": round(nbytes / per / 1e6, 1), "launches": launches})
     for t in (bx, bgo, gam, bet, rmean, rvar, ux):
         t.release()
     return out
@@ -991,24 +1010,22 @@ def run_single_case(args):
         targets = AG.NoGradVariable(ops, ops.createRaw([rows], np.floor(D.uniform(rows, 15, 0.0, cols - 0.01)).astype(np.float32)))
         ops.lazy = name.endswith("deferred")
 
+        def xent_unscoped():
+            logits.zeroGrad()
+            loss = logits.softmaxCrossEntropy(targets)
+            loss.backward()
+            logits.gradient.storeReference
+            release_loss(loss)
+
         def xent():
             with ops.garbageCollector():
-                logits.zeroGrad()
-                logits.softmaxCrossEntropy(targets).backward()
-                logits.gradient.storeReference
+                xent_unscoped()
 
         for _ in range(4):                                  # the buffer pool settles over the first steps
             xent()
-        ops.synchronize()
-        l0 = lib.ktc_launch_count()
-        L.check(lib.ktc_timer_start(0))
-        for _ in range(args.reps):
-            xent()
-        ms = C.c_float(0)
-        L.check(lib.ktc_timer_stop(0, C.byref(ms)))
-        per = ms.value / args.reps
-        print(json.dumps({"case": name, "elements": rows * cols, "ms": per, "gbs": 2 * 4.0 * rows * cols / per / 1e6,
-                          "launches_per_step": (lib.ktc_launch_count() - l0) / args.reps}))
+        per, med, launches = timed_in_batches(ops, lib, L, xent_unscoped, args.reps)
+        print(json.dumps({"case": name, "elements": rows * cols, "ms": per, "ms_median_batch": med, "gbs": 2 * 4.0 * rows * cols / per / 1e6,
+                          "launches_per_step": launches, "device_mallocs_in_timed_region": timed_in_batches.last_device_mallocs}))
         return 0
     if name in ("x.batchnorm", "x.upsample"):
         # batch norm (training forward + backward) of [n / 2^20, 64, 128, 128] along axis 1; upsampling by 2 with its gradient
@@ -1038,16 +1055,8 @@ def run_single_case(args):
         for _ in range(3):
             with ops.garbageCollector():
                 fn()
-        ops.synchronize()
-        l0 = lib.ktc_launch_count()
-        L.check(lib.ktc_timer_start(0))
-        for _ in range(args.reps):
-            with ops.garbageCollector():
-                fn()
-        ms = C.c_float(0)
-        L.check(lib.ktc_timer_stop(0, C.byref(ms)))
-        per = ms.value / args.reps
-        print(json.dumps({"case": name, "elements": vol, "ms": per, "gbs": nbytes / per / 1e6, "launches_per_step": (lib.ktc_launch_count() - l0) / args.reps}))
+        per, med, launches = timed_in_batches(ops, lib, L, fn, args.reps)
+        print(json.dumps({"case": name, "elements": vol, "ms": per, "ms_median_batch": med, "gbs": nbytes / per / 1e6, "launches_per_step": launches}))
         return 0
     if name.startswith("x."):
         # data-movement ops beside the sweep, on a [rows, 4096] tensor of n elements
