@@ -663,12 +663,12 @@ def run_other_ops(ops, lib, L, D, steps):
     # its backward, and nearest-neighbour upsampling by 2 with its gradient: compositions of recorded raw-tensor calls
     # (kten_b200/nn.py).  Bytes: what must cross HBM when every pass reads its operands once -- forward x three times + out,
     # backward x and gradOut twice + gradIn -- i.e. the passes the reference itself makes.
-    shape, C = [256, 64, 128, 128], 64
+    shape, channels = [256, 64, 128, 128], 64
     n = 256 * 64 * 128 * 128
     bx = ops.createRaw(shape, D.normal(n, 21, 0.0, 1.0))
     bgo = ops.createRaw(shape, D.normal(n, 22, 0.0, 1.0))
-    gam, bet = ops.createRaw([C], D.uniform(C, 23, 0.5, 1.5)), ops.createRaw([C], D.uniform(C, 24, -0.5, 0.5))
-    rmean, rvar = ops.createRawFill([C], 0.0), ops.createRawFill([C], 1.0)
+    gam, bet = ops.createRaw([channels], D.uniform(channels, 23, 0.5, 1.5)), ops.createRaw([channels], D.uniform(channels, 24, -0.5, 0.5))
+    rmean, rvar = ops.createRawFill([channels], 0.0), ops.createRawFill([channels], 1.0)
     bn = ops.batchNorm(1, 0.1, 1e-3, True)
 
     def bn_step():
