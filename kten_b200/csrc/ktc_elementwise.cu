@@ -162,14 +162,17 @@ __global__ void __launch_bounds__(256, 3) k_bcast3(BcastArgs p, F f) {
     const int tx = threadIdx.x & (p.txc - 1), ty = threadIdx.x >> p.txc_log2;
     const int tyc = blockDim.x >> p.txc_log2;
 
-    const int64_t tiles_per_i0 = p.tiles_d1 * p.tiles_d2;
-    const int64_t n_tiles = p.D0 * tiles_per_i0;
+    // tile counts fit 32 bits (the host falls back to the generic kernel otherwise): no 64-bit division on this path
+    const uint32_t tiles_d2 = (uint32_t)p.tiles_d2;
+    const uint32_t tiles_per_i0 = (uint32_t)p.tiles_d1 * tiles_d2;
+    const uint32_t n_tiles = (uint32_t)p.D0 * tiles_per_i0;
 
-    for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
-        const int64_t i0 = t / tiles_per_i0;
-        const int64_t rem = t - i0 * tiles_per_i0;
-        const int64_t td1 = rem / p.tiles_d2, td2 = rem - td1 * p.tiles_d2;
-        const int64_t r0 = td1 * p.rows_per_tile, c0 = td2 * (int64_t)p.cols_per_tile;
+    for (uint32_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+        const uint32_t i0u = t / tiles_per_i0;
+        const uint32_t rem = t - i0u * tiles_per_i0;
+        const uint32_t td1 = rem / tiles_d2, td2 = rem - td1 * tiles_d2;
+        const int64_t i0 = i0u;
+        const int64_t r0 = (int64_t)td1 * p.rows_per_tile, c0 = (int64_t)td2 * p.cols_per_tile;
         const int rows = (int)min((int64_t)p.rows_per_tile, p.D1 - r0);
         const int cols4 = (int)(min((int64_t)p.cols_per_tile, p.D2 - c0) >> 2);
         const float* abase = (MODE_A == AM_DIRECT) ? p.a + i0 * p.as0 + r0 * p.as1 + c0 : nullptr;
@@ -318,6 +321,10 @@ static int run_bcast(Device* d, float* out, const int64_t* oshape, int ndim, con
         const int cw4 = p.cols_per_tile >> 2;
         p.txc = 1; p.txc_log2 = 0;
         while (p.txc < 256 && p.txc < cw4) { p.txc <<= 1; ++p.txc_log2; }
+        const int64_t n_tiles = D[0] * p.tiles_d1 * p.tiles_d2;
+        if (n_tiles >= 0x7fffffffLL) tiled = false;                  // the kernel decomposes the tile index with 32-bit arithmetic
+    }
+    if (tiled) {
         const int64_t n_tiles = D[0] * p.tiles_d1 * p.tiles_d2;
         const int bps = tune("bcast_blocks_per_sm", 0);             // <= 0: one tile per CTA, tiles in address order
         const int64_t cap = bps > 0 ? (int64_t)d->sm_count * bps : 0x7fffffffLL;
