@@ -93,6 +93,7 @@ class CUDABatchNorm(
             val x = input.view(listOf(outer, c * inner))
             val go = gradOut.view(listOf(outer, c * inner))
             val mean = if (training) currentMean else runningMean!!
+            // kten-jvm takes the inference-mode deviation in double (JVMBatchNorm.kt:117); rsqrt is 1f / sqrt(float): at most one ulp apart
             val stdev = if (training) currentStd else runningVar!!.plus(epsilon).rsqrt() as CUDARawTensor
             val d = x.minus(row(mean, c, inner)) as CUDARawTensor
             // both sums stay pending until the first is needed: one pass over x and gradOut with two sinks (a sum of a stored

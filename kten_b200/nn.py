@@ -126,7 +126,9 @@ class CUDABatchNorm:
                 mean, stdev = currentMean, currentStd
             else:
                 mean = runningMean
-                stdev = runningVar.plus(self.epsilon).rsqrt()                           # (1.0 / sqrt(double)).toFloat(), :117
+                # kten-jvm takes this one in double, (1.0 / sqrt((rv + eps).toDouble())).toFloat() (:117); rsqrt is 1f / sqrt(float):
+                # two float roundings instead of one, at most one ulp apart in the inverse deviation
+                stdev = runningVar.plus(self.epsilon).rsqrt()
             mean_row = self._row(mean, C, inner)
             d = x.minus(mean_row)
             # both sums are pending until the first is needed: one pass over x and gradOut with two sinks (a sum of a stored
