@@ -202,7 +202,7 @@ class CUDARawTensor(
     }
 
     private fun unary(op: Int): CUDARawTensor {
-        if (ops.lazy && op <= KtcNative.NEG)                     // the maps the fused expression kernels implement
+        if (ops.lazy && (op <= KtcNative.NEG || op == KtcNative.SQRT || op == KtcNative.RSQRT || op == KtcNative.ABS))   // the maps that are expression instructions
             return recorded(shape, KtcNative.cell { out -> KtcNative.lazyUnary.invokeExact(op, cell(), out) as Int })
         val res = ops.createRaw(shape)
         check(KtcNative.unary.invokeExact(op, res.handle, handle, volume) as Int)

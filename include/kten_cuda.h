@@ -249,8 +249,9 @@ KTC_API int ktc_reduce_all_noalloc(int op, ktc_buf out, ktc_buf in, int64_t n);
 enum { KTC_X_LOAD = 1, KTC_X_CONST, KTC_X_ADD, KTC_X_SUB, KTC_X_MUL, KTC_X_DIV, KTC_X_POW, KTC_X_NEG, KTC_X_RCP,
        KTC_X_SQUARE, KTC_X_EXP, KTC_X_LOG, KTC_X_TANH, KTC_X_SIGMOID, KTC_X_CLAMP, KTC_X_CMP_LT, KTC_X_CMP_LTE,
        KTC_X_CMP_GT, KTC_X_CMP_GTE, KTC_X_STORE, KTC_X_ACC,
-       KTC_X_SCATC };   /* d = (column == (int)b) ? imm[k] : a -- inplaceScatter(-1, index, constant) with one index per row (JVM:317-332):
+       KTC_X_SCATC,     /* d = (column == (int)b) ? imm[k] : a -- inplaceScatter(-1, index, constant) with one index per row (JVM:317-332):
                            b is the row's index broadcast over the columns; an index outside the row is recorded, nothing is written */
+       KTC_X_SQRT, KTC_X_RSQRT, KTC_X_ABS };   /* sqrt (JVM:413), 1f / sqrt (JVM:435), abs (JVM:405): the chains of optimisers and normalisations */
 enum { KTC_EXPR_STORE_ONLY = 0, KTC_EXPR_SUM_ALL = 1, KTC_EXPR_SUM_ROWS = 2, KTC_EXPR_MULTI = 3, KTC_EXPR_SUM_LAST = 4 };
 KTC_API int ktc_expr_eval(const uint32_t* code, int n_code, const float* imm, int n_imm,
                           const int64_t* shape, int ndim,

@@ -20,6 +20,7 @@ PLUS, MINUS, TIMES, DIV, POW = range(5)
 EXP, LOG, TANH, SIGMOID, RECIPROCAL, NEG = range(6)
 SUM, MEAN, MAX, MIN, ARGMAX, ARGMIN = range(6)
 (SINH, COSH, ABS, SIGN, SQRT, SIN, COS, TAN, ASIN, ACOS, ATAN, FLOOR, CEIL, ROUND, TRUNC, RSQRT) = range(6, 22)
+RECORDABLE_UNARY = frozenset(range(0, 6)) | {SQRT, RSQRT, ABS}      # the unary operations that are expression instructions
 LT, LTE, GT, GTE, EQ, NEQ = range(6)
 SCATTER_SET, SCATTER_ADD, SCATTER_CONST = 0, 1, 2
 MAX_DIMS = 10
@@ -28,7 +29,7 @@ COMM_ID_BYTES = 128
 P2P_HANDLE_BYTES, P2P_MAX_RANKS, P2P_MAX_FLOATS, P2P_MAX_TENSORS = 64, 16, 16384, 8
 # fused expression programs (ktc_expr_eval)
 (X_LOAD, X_CONST, X_ADD, X_SUB, X_MUL, X_DIV, X_POW, X_NEG, X_RCP, X_SQUARE, X_EXP, X_LOG, X_TANH, X_SIGMOID, X_CLAMP,
- X_CMP_LT, X_CMP_LTE, X_CMP_GT, X_CMP_GTE, X_STORE, X_ACC, X_SCATC) = range(1, 23)
+ X_CMP_LT, X_CMP_LTE, X_CMP_GT, X_CMP_GTE, X_STORE, X_ACC, X_SCATC, X_SQRT, X_RSQRT, X_ABS) = range(1, 26)
 EXPR_STORE_ONLY, EXPR_SUM_ALL, EXPR_SUM_ROWS, EXPR_MULTI, EXPR_SUM_LAST = 0, 1, 2, 3, 4
 EXPR_MAX_INSTR, EXPR_MAX_IMM, EXPR_MAX_LEAVES, EXPR_MAX_STORES, EXPR_REGS, EXPR_MAX_SINKS = 32, 16, 8, 3, 8, 4
 NOALLOC_SCRATCH_BYTES = 16384

@@ -113,6 +113,9 @@ __global__ void __launch_bounds__(256) k_expr(const __grid_constant__ ExprArgs p
                 case KTC_X_CMP_LTE: { const float t = p.imm[k]; v = KTC_EACH(x.x <= t ? 1.f : 0.f, x.y <= t ? 1.f : 0.f, x.z <= t ? 1.f : 0.f, x.w <= t ? 1.f : 0.f); break; }
                 case KTC_X_CMP_GT: { const float t = p.imm[k]; v = KTC_EACH(x.x > t ? 1.f : 0.f, x.y > t ? 1.f : 0.f, x.z > t ? 1.f : 0.f, x.w > t ? 1.f : 0.f); break; }
                 case KTC_X_CMP_GTE: { const float t = p.imm[k]; v = KTC_EACH(x.x >= t ? 1.f : 0.f, x.y >= t ? 1.f : 0.f, x.z >= t ? 1.f : 0.f, x.w >= t ? 1.f : 0.f); break; }
+                case KTC_X_SQRT: v = KTC_EACH(__fsqrt_rn(x.x), __fsqrt_rn(x.y), __fsqrt_rn(x.z), __fsqrt_rn(x.w)); break;
+                case KTC_X_RSQRT: v = KTC_EACH(__fdiv_rn(1.0f, __fsqrt_rn(x.x)), __fdiv_rn(1.0f, __fsqrt_rn(x.y)), __fdiv_rn(1.0f, __fsqrt_rn(x.z)), __fdiv_rn(1.0f, __fsqrt_rn(x.w))); break;
+                case KTC_X_ABS: v = KTC_EACH(fabsf(x.x), fabsf(x.y), fabsf(x.z), fabsf(x.w)); break;
                 case KTC_X_SCATC: {
                     const int t = (int)y.x;                        // Float.toInt(): truncation; y holds the row's index in every column
                     if ((unsigned)t >= (unsigned)p.D2) *p.err = 1;
@@ -374,7 +377,7 @@ static int expr_eval_impl(Device** scatc_dev, const uint32_t* code, int n_code, 
     for (int i = 0; i < n_code; ++i) {
         const uint32_t ins = code[i];
         const int op = ins & 0xff, dreg = (ins >> 8) & 0xf, ra = (ins >> 12) & 0xf, rb = (ins >> 16) & 0xf, k = ins >> 20;
-        if (op < KTC_X_LOAD || op > KTC_X_SCATC) return fail(KTC_EINVAL, "ktc_expr_eval: unknown opcode %d at %d", op, i);
+        if (op < KTC_X_LOAD || op > KTC_X_ABS) return fail(KTC_EINVAL, "ktc_expr_eval: unknown opcode %d at %d", op, i);
         if (dreg >= kExprRegs || ra >= kExprRegs || rb >= kExprRegs) return fail(KTC_EINVAL, "ktc_expr_eval: register index out of range at %d", i);
         if (op == KTC_X_LOAD && k >= n_leaves) return fail(KTC_EINVAL, "ktc_expr_eval: LOAD of leaf %d (have %d)", k, n_leaves);
         if (op == KTC_X_STORE && k >= n_stores) return fail(KTC_EINVAL, "ktc_expr_eval: STORE to target %d (have %d)", k, n_stores);

@@ -392,7 +392,7 @@ static void toposort(const std::vector<Node*>& roots, std::vector<Node*>& order)
 
 static const int kHeavy[6] = {10, 10, 12, 16, 2, 1};      // rough issue cost of one element: exp log tanh sigmoid reciprocal neg
 static int weight(const Node* n) {
-    if (n->kind == K_UN) return (n->op >= 0 && n->op < 6) ? kHeavy[n->op] : 1;
+    if (n->kind == K_UN) return (n->op >= 0 && n->op < 6) ? kHeavy[n->op] : (n->op == KTC_SQRT ? 3 : n->op == KTC_RSQRT ? 5 : 1);
     if (n->kind == K_BIN) return n->op == KTC_POW ? 30 : n->op == KTC_DIV ? 3 : 1;
     return (n->kind == K_LEAF || n->kind == K_CONST || n->kind == K_BCAST) ? 0 : 1;
 }
@@ -432,6 +432,9 @@ static int alloc_reg(Program& p) {
 
 static const int kBinX[5] = {KTC_X_ADD, KTC_X_SUB, KTC_X_MUL, KTC_X_DIV, KTC_X_POW};
 static const int kUnX[6] = {KTC_X_EXP, KTC_X_LOG, KTC_X_TANH, KTC_X_SIGMOID, KTC_X_RCP, KTC_X_NEG};
+// the unary operations that are expression instructions: exp .. neg, and sqrt, 1 / sqrt, abs
+static bool unary_recordable(int op) { return (op >= KTC_EXP && op <= KTC_NEG) || op == KTC_SQRT || op == KTC_RSQRT || op == KTC_ABS; }
+static int unary_x(int op) { return op <= KTC_NEG ? kUnX[op] : op == KTC_SQRT ? KTC_X_SQRT : op == KTC_RSQRT ? KTC_X_RSQRT : KTC_X_ABS; }
 static const int kCmpX[4] = {KTC_X_CMP_LT, KTC_X_CMP_LTE, KTC_X_CMP_GT, KTC_X_CMP_GTE};
 
 // The uncached compilation: side-output choice, register allocation, emission.
@@ -482,7 +485,7 @@ static void compile_uncached(Program& prog, std::vector<Node*>& store_nodes, con
             d = alloc_reg(prog);                          // may reuse a source register: the kernel reads before it writes
             switch (n->kind) {
             case K_BIN: emit(prog, kBinX[n->op], d, srcs[0], srcs[1]); break;
-            case K_UN: emit(prog, kUnX[n->op], d, srcs[0]); break;
+            case K_UN: emit(prog, unary_x(n->op), d, srcs[0]); break;
             case K_SQUARE: emit(prog, KTC_X_SQUARE, d, srcs[0]); break;
             case K_CLAMP: emit(prog, KTC_X_CLAMP, d, srcs[0], 0, imm_index(prog, n->imm, 2, n->pos)); break;
             case K_CMP: emit(prog, kCmpX[n->op], d, srcs[0], 0, imm_index(prog, n->imm, 1, n->pos)); break;
@@ -1146,7 +1149,7 @@ KTC_API int ktc_lazy_free(ktc_lazy_cell cell) {
 
 KTC_API int ktc_lazy_unary(int op, ktc_lazy_cell a, ktc_lazy_cell* out) {
     LZ_LOCK;
-    if (op < KTC_EXP || op > KTC_NEG) return fail(KTC_ENOTSUP, "ktc_lazy_unary: op %d is not an expression instruction", op);
+    if (!unary_recordable(op)) return fail(KTC_ENOTSUP, "ktc_lazy_unary: op %d is not an expression instruction", op);
     Node* na; LZ_TRY(operand(a, &na));
     *out = pending_cell(K_UN, na->shape, op, na, nullptr, nullptr, 0);
     return KTC_OK;

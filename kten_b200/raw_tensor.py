@@ -246,7 +246,7 @@ class CUDARawTensor:
         L.check(self.ops.lib.ktc_scalar_inplace(op, self._buf(), float(s), self.size))
 
     def _unary(self, op: int) -> "CUDARawTensor":
-        if self.ops.lazy and op <= L.NEG:                       # the ops the fused expression kernels implement
+        if self.ops.lazy and op in L.RECORDABLE_UNARY:          # the ops the fused expression kernels implement
             return self._recorded(self.shape, self.ops._recorder.unary(op, self._lz()))
         res = self._new(self.shape)
         L.check(self.ops.lib.ktc_unary(op, res._buf(), self._buf(), self.size))

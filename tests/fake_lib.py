@@ -373,8 +373,9 @@ class FakeLib:
             elif op in (L.X_ADD, L.X_SUB, L.X_MUL, L.X_DIV, L.X_POW):
                 o = {L.X_ADD: O.PLUS, L.X_SUB: O.MINUS, L.X_MUL: O.TIMES, L.X_DIV: O.DIV, L.X_POW: O.POW}[op]
                 regs[d] = O.binary_same(o, regs[a], regs[b])
-            elif op in (L.X_NEG, L.X_RCP, L.X_EXP, L.X_LOG, L.X_TANH, L.X_SIGMOID):
-                o = {L.X_NEG: O.NEG, L.X_RCP: O.RECIPROCAL, L.X_EXP: O.EXP, L.X_LOG: O.LOG, L.X_TANH: O.TANH, L.X_SIGMOID: O.SIGMOID}[op]
+            elif op in (L.X_NEG, L.X_RCP, L.X_EXP, L.X_LOG, L.X_TANH, L.X_SIGMOID, L.X_SQRT, L.X_RSQRT, L.X_ABS):
+                o = {L.X_NEG: O.NEG, L.X_RCP: O.RECIPROCAL, L.X_EXP: O.EXP, L.X_LOG: O.LOG, L.X_TANH: O.TANH, L.X_SIGMOID: O.SIGMOID,
+                     L.X_SQRT: O.SQRT, L.X_RSQRT: O.RSQRT, L.X_ABS: O.ABS}[op]
                 regs[d] = O.unary(o, regs[a])
             elif op == L.X_SQUARE:
                 regs[d] = O.binary_same(O.TIMES, regs[a], regs[a])

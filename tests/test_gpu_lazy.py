@@ -91,7 +91,8 @@ def test_chains_equal_call_by_call(lazy_ops, shapes):
         x = v.times(w).plus(u.exp().reciprocal()).unaryMinus()
         y = ta.pow(tc).minus(ops.pow(1.5, tb)).lt(0.75)
         z = ta.pow(1.0).plus(3.0)
-        return [u, v, w, x, y, z]
+        q = tb.abs().plus(1.0).rsqrt().times(tc.sqrt()).plus(ta)      # abs, 1 / sqrt and sqrt are expression instructions too
+        return [u, v, w, x, y, z, q]
 
     eager, lazy = both(lazy_ops, chain)
     for e, l in zip(eager, lazy):
@@ -100,14 +101,14 @@ def test_chains_equal_call_by_call(lazy_ops, shapes):
     # the narrowed double libm in fewer than one element per million, so chains of those agree in (nearly) every
     # element; log and tanh are within 1 and 2 ulp (w, x)
     want = [r.toArray() for r in chain(O.OracleTensorOperations())]
-    for name, l, o in zip("uvwxyz", lazy, want):
+    for name, l, o in zip("uvwxyzq", lazy, want):
         assert l.shape == o.shape, name
         differing = int(np.count_nonzero(l.view(np.uint32) != o.view(np.uint32)))
-        if name in "uvyz":
+        if name in "uvyzq":
             assert differing <= max(1, l.size // 1000), (name, differing, l.size)
         if name != "y":                                            # y is a comparison: 0 or 1
             assert np.allclose(l, o, rtol=4e-6, atol=4e-6), name
-        if name in "uz":                                           # only exact operations
+        if name in "uzq":                                          # only exact operations
             assert differing == 0, name
 
 

@@ -34,7 +34,8 @@ def test_every_opcode_compiles_for_every_sink():
             ins(L.X_ADD, 4, 0, 1), ins(L.X_SUB, 4, 4, 2), ins(L.X_MUL, 4, 4, 3), ins(L.X_DIV, 4, 4, 1), ins(L.X_POW, 5, 0, 4),
             ins(L.X_NEG, 5, 5), ins(L.X_RCP, 5, 5), ins(L.X_SQUARE, 5, 5), ins(L.X_EXP, 6, 5), ins(L.X_LOG, 6, 6),
             ins(L.X_TANH, 6, 6), ins(L.X_SIGMOID, 6, 6), ins(L.X_CLAMP, 6, 6, k=1), ins(L.X_CMP_LT, 7, 6, k=3),
-            ins(L.X_CMP_LTE, 7, 7, k=3), ins(L.X_CMP_GT, 7, 7, k=3), ins(L.X_CMP_GTE, 7, 7, k=3), ins(L.X_MUL, 7, 7, 6)]
+            ins(L.X_CMP_LTE, 7, 7, k=3), ins(L.X_CMP_GT, 7, 7, k=3), ins(L.X_CMP_GTE, 7, 7, k=3), ins(L.X_MUL, 7, 7, 6),
+            ins(L.X_ABS, 6, 6), ins(L.X_SQRT, 6, 6), ins(L.X_RSQRT, 6, 6), ins(L.X_ADD, 7, 7, 6)]
     for sink, tail in ((L.EXPR_STORE_ONLY, [ins(L.X_STORE, a=7, k=0), ins(L.X_STORE, a=4, k=1)]),
                        (L.EXPR_SUM_ALL, [ins(L.X_STORE, a=4, k=0), ins(L.X_ACC, a=7)]),
                        (L.EXPR_SUM_ROWS, [ins(L.X_ACC, a=7)])):

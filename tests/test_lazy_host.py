@@ -161,3 +161,18 @@ def test_program_cache_tells_one_buffer_read_twice_from_two_buffers():
     assert st["compiled"] == 2 and st["cache_hits"] == 0
     third = x.plus(b).times(c).toArray()                                           # the same structure again: re-bound, not recompiled
     assert np.array_equal(third, second) and ops._recorder.stats()["cache_hits"] == 1
+
+
+def test_sqrt_rsqrt_and_abs_are_expression_instructions():
+    """The step of an optimiser, m / (sqrt(v) + eps), and a normalisation, x * rsqrt(abs(x) + 1), stay one program each
+    and give the bits of the separate calls."""
+    M, V = rnd([8, 16], 70), np.abs(rnd([8, 16], 71)) + np.float32(0.01)
+    ops, (m, v) = ops_with(M, V)
+    upd = m.div(v.sqrt().plus(1e-8))
+    norm = m.times(m.abs().plus(1.0).rsqrt())
+    want_upd = (M / (np.sqrt(V, dtype=np.float32) + np.float32(1e-8))).astype(np.float32)
+    want_norm = (M * (np.float32(1.0) / np.sqrt(np.abs(M) + np.float32(1.0), dtype=np.float32))).astype(np.float32)
+    n0 = ops.lib.expr_calls
+    assert np.array_equal(upd.toArray(), want_upd) and np.array_equal(norm.toArray(), want_norm)
+    assert ops.lib.expr_calls == n0 + 2 and ops.unfusedEvaluations == 0
+    assert L.X_SQRT in opcodes(ops.lib.programs[-2]) and {L.X_ABS, L.X_RSQRT} <= set(opcodes(ops.lib.programs[-1]))
