@@ -222,6 +222,64 @@ __global__ void __launch_bounds__(256, 3) k_bcast3(BcastArgs p, F f) {
     }
 }
 
+// The same tile when every tile of the launch is whole and exactly one batch (32 rows x 256 columns, 64 x 4 threads, 8 rows
+// each: the geometry of any tensor whose extents are multiples of the tile): per-thread base pointers and strides are
+// formed once and the body is straight-line -- about a third of the instructions of the guarded form, which matters when
+// the clock drops under a power cap and a streaming kernel becomes bound by instruction issue.
+template <int MODE_A, int MODE_B, int U, class F>
+__global__ void __launch_bounds__(256, 3) k_bcast3_full(BcastArgs p, F f) {
+    extern __shared__ __align__(16) float smem[];
+    constexpr bool STAGE_A = (MODE_A == AM_SMEMROW || MODE_A == AM_ROWSCALAR);
+    constexpr bool STAGE_B = (MODE_B == AM_SMEMROW || MODE_B == AM_ROWSCALAR);
+    constexpr bool DIV_ROW = IsDiv<F>::value && MODE_B == AM_ROWSCALAR;
+    const int sm_stride = max(p.cols_per_tile, (p.rows_per_tile + 3) & ~3);
+    float* sm_a = smem;
+    float* sm_b = smem + (STAGE_A ? sm_stride : 0);
+    float* sm_r = sm_b + sm_stride;
+    const int tx = threadIdx.x & (p.txc - 1), ty = threadIdx.x >> p.txc_log2;
+    const int tyc = blockDim.x >> p.txc_log2;
+    const uint32_t tiles_d2 = (uint32_t)p.tiles_d2;
+    const uint32_t tiles_per_i0 = (uint32_t)p.tiles_d1 * tiles_d2;
+    const uint32_t t = blockIdx.x;                                     // one tile per CTA
+    const uint32_t i0u = t / tiles_per_i0;
+    const uint32_t rem = t - i0u * tiles_per_i0;
+    const uint32_t td1 = rem / tiles_d2, td2 = rem - td1 * tiles_d2;
+    const int64_t i0 = i0u;
+    const int64_t r0 = (int64_t)td1 * p.rows_per_tile, c0 = (int64_t)td2 * p.cols_per_tile;
+    const int cols4 = p.cols_per_tile >> 2;
+    const bool active = tx < cols4;
+    const int col = tx << 2;
+    const float* pa = (MODE_A == AM_DIRECT) ? p.a + i0 * p.as0 + (r0 + ty) * p.as1 + c0 + col : nullptr;
+    const float* pb = (MODE_B == AM_DIRECT) ? p.b + i0 * p.bs0 + (r0 + ty) * p.bs1 + c0 + col : nullptr;
+    float* po = p.out + (i0 * p.D1 + r0 + ty) * p.D2 + c0 + col;
+    const int64_t sa = (int64_t)tyc * p.as1, sb = (int64_t)tyc * p.bs1, so = (int64_t)tyc * p.D2;
+    float4 va[U], vb[U];
+    if (active) {
+        #pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (MODE_A == AM_DIRECT) { const float4* q = reinterpret_cast<const float4*>(pa + u * sa); va[u] = p.a_stream ? __ldcs(q) : __ldg(q); }
+            if (MODE_B == AM_DIRECT) { const float4* q = reinterpret_cast<const float4*>(pb + u * sb); vb[u] = p.b_stream ? __ldcs(q) : __ldg(q); }
+        }
+    }
+    if (STAGE_A || STAGE_B) {
+        if (STAGE_A) stage_operand<MODE_A>(sm_a, p.a + i0 * p.as0, p.as1, r0, c0, p.rows_per_tile, cols4);
+        if (STAGE_B) stage_operand<MODE_B>(sm_b, p.b + i0 * p.bs0, p.bs1, r0, c0, p.rows_per_tile, cols4);
+        if (DIV_ROW) for (int rr = threadIdx.x; rr < p.rows_per_tile; rr += blockDim.x) sm_r[rr] = kd_row_reciprocal(sm_b[rr]);
+        __syncthreads();
+    }
+    if (active) {
+        #pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int row = ty + u * tyc;
+            if (MODE_A != AM_DIRECT) va[u] = load_operand<MODE_A>(sm_a, nullptr, p.as1, row, col, 0);
+            if (MODE_B != AM_DIRECT) vb[u] = load_operand<MODE_B>(sm_b, nullptr, p.bs1, row, col, 0);
+            float4* dst = reinterpret_cast<float4*>(po + u * so);
+            if (DIV_ROW) st_stream(dst, div_by_row(va[u], vb[u].x, sm_r[row]));
+            else st_stream(dst, apply2(f, va[u], vb[u]));
+        }
+    }
+}
+
 // Fallback for anything the tiled kernel does not take (more than three
 // collapsed dimensions, an inner extent that is not a multiple of 4, unaligned
 // bases): one element per thread-iteration, index decomposed per element.
@@ -252,8 +310,17 @@ template <> struct BatchRows<BinOp<KTC_POW>> { static constexpr int value = 4; }
 
 template <int MA, int MB, class F>
 static void launch_bcast3_modes(Device* d, const BcastArgs& p, int grid, size_t smem, F f) {
-    if (IsDiv<F>::value && MB == AM_ROWSCALAR && tune("bcast_div_batch", 8) == 8)       // three instructions per quotient: the full batch fits
-        k_bcast3<MA, MB, (IsDiv<F>::value && MB == AM_ROWSCALAR) ? 8 : BatchRows<F>::value, F><<<grid, 256, smem, d->stream>>>(p, f);
+    constexpr bool kDivRow = IsDiv<F>::value && MB == AM_ROWSCALAR;
+    constexpr int kU = kDivRow ? 8 : BatchRows<F>::value;                // three instructions per quotient: the full batch fits
+    const int tyc = 256 >> p.txc_log2;
+    const int64_t n_tiles = p.D0 * p.tiles_d1 * p.tiles_d2;
+    // every tile whole, one batch per tile, one tile per CTA: the straight-line kernel
+    const bool full = p.D1 % p.rows_per_tile == 0 && p.D2 % p.cols_per_tile == 0 && p.txc * 4 >= p.cols_per_tile
+                      && tyc * kU == p.rows_per_tile && grid == n_tiles && tune("bcast_full_tiles", 1) != 0
+                      && !(kDivRow && tune("bcast_div_batch", 8) != 8);
+    if (full) { k_bcast3_full<MA, MB, kU, F><<<grid, 256, smem, d->stream>>>(p, f); return; }
+    if (kDivRow && tune("bcast_div_batch", 8) == 8)
+        k_bcast3<MA, MB, kU, F><<<grid, 256, smem, d->stream>>>(p, f);
     else
         k_bcast3<MA, MB, BatchRows<F>::value, F><<<grid, 256, smem, d->stream>>>(p, f);
 }
