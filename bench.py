@@ -640,7 +640,8 @@ def run_other_ops(ops, lib, L, D, steps):
         logits.zeroGrad()
         loss = logits.softmaxCrossEntropy(targets)
         loss.backward()
-        logits.gradient.storeReference
+        logits.gradient.storeReference                      # gradient and loss in memory: nothing of the step is left pending
+        loss.getRawValue().storeReference
         release_loss(loss)
 
     for mode, label in ((False, "call by call"), (True, "deferred")):
@@ -1014,7 +1015,8 @@ def run_single_case(args):
             logits.zeroGrad()
             loss = logits.softmaxCrossEntropy(targets)
             loss.backward()
-            logits.gradient.storeReference
+            logits.gradient.storeReference                  # gradient and loss in memory: nothing of the step is left pending
+            loss.getRawValue().storeReference
             release_loss(loss)
 
         def xent():

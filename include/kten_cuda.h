@@ -198,6 +198,21 @@ KTC_API int ktc_sum_to_shape(ktc_buf out, const int64_t* old_shape, int old_ndim
  * a multiple of 4, unaligned rows): issue the separate calls. */
 KTC_API int ktc_softmax_xent_forward(ktc_buf softmax, ktc_buf nll, ktc_buf logits, ktc_buf targets, int64_t rows, int64_t cols, float lo, float hi);
 
+/* The same forward with an elementwise program (the encoding of ktc_expr_eval) as its epilogue: leaf `soft_leaf` of the
+ * program is the row's softmax while it is still in registers.  A consumer of the saved tensor -- the function's backward,
+ * (softmax with -1 at the target) / rows, SoftmaxCrossEntropy.kt:61-67, and the accumulation into the Variable's gradient,
+ * Variable.kt:44-46 -- then runs in the pass that reads the logits, and `softmax` may be 0: the saved tensor is not written.
+ * The other leaves are [rows | 1, cols | 1] tensors (leaf_shapes: two extents per leaf; the entry of soft_leaf is ignored),
+ * STORE k writes stores[k], [rows, cols]; ACC is not allowed.  Each instruction is the reference operation of the
+ * stand-alone call with its own rounding, so nll and the stored tensors carry the bits of ktc_softmax_xent_forward
+ * followed by ktc_expr_eval on the stored softmax.  The kernel is generated at run time; KTC_ENOTSUP (rows the one-pass
+ * kernel does not take, no run-time compiler): run the two separately.  ktc_lazy_softmax_xent_forward records the forward
+ * and makes this call when the recorded consumer is evaluated. */
+KTC_API int ktc_softmax_xent_forward_expr(ktc_buf softmax, ktc_buf nll, ktc_buf logits, ktc_buf targets, int64_t rows, int64_t cols, float lo, float hi,
+                                          const uint32_t* code, int n_code, const float* imm, int n_imm,
+                                          const ktc_buf* leaves, const int64_t* leaf_shapes, int n_leaves, int soft_leaf,
+                                          const ktc_buf* stores, int n_stores);
+
 /* Nearest-neighbour upsampling of the last two dimensions by `scale` and its gradient (TensorOperations.upsample,
  * TensorOperations.kt:131; Upsample2DOperation.kt:5-44; kten-jvm: JVMUpsample2DNearest.kt:14-77).  P is the product of
  * all dimensions but the last (N * C * H): in [P, W] -> out [P, scale, W * scale]; grad_out [P, scale, W * scale] ->
@@ -346,6 +361,13 @@ KTC_API int ktc_expr_jit_log(char* buf, int len);
  *                            of SoftmaxCrossEntropy.doBackward, SoftmaxCrossEntropy.kt:61-67), recorded as an expression
  *                            instruction; index: a cell of the target's shape with last extent 1.  KTC_ENOTSUP for other
  *                            index shapes: use ktc_scatter_axis_nd on the buffers.
+ *   ktc_lazy_softmax_xent_forward   the forward of SoftmaxCrossEntropy (SoftmaxCrossEntropy.kt:40-59), recorded: *softmax
+ *                            is the tensor the function saves for backward, *nll the loss per row; nothing runs until one
+ *                            of them is needed.  An elementwise expression of the softmax's shape recorded meanwhile (the
+ *                            function's backward, the accumulation into the Variable's gradient) is then evaluated inside
+ *                            the forward's kernel (ktc_softmax_xent_forward_expr) and the softmax is written only if a
+ *                            tensor still holds it: logits in, gradient out.  KTC_ENOTSUP for rows the one-pass kernel
+ *                            does not take.
  *   ktc_lazy_sum             sum() / mean() (KTC_EXPR_SUM_ALL), sum over axis 0 (KTC_EXPR_SUM_ROWS) or over
  *                            the innermost axis (KTC_EXPR_SUM_LAST) of a cell; with option defer_sums the
  *                            sum of a pending cell is pending too, and pending sums over one iteration
@@ -380,6 +402,7 @@ KTC_API int ktc_lazy_assign_scalar(int op, ktc_lazy_cell target, float s, int* s
 KTC_API int ktc_lazy_full(int dev, const int64_t* shape, int ndim, float value, ktc_lazy_cell* out);
 KTC_API int ktc_lazy_assign_fill(ktc_lazy_cell target, float value, int* state);
 KTC_API int ktc_lazy_assign_scatter_const(ktc_lazy_cell target, ktc_lazy_cell index, float value, int* state);
+KTC_API int ktc_lazy_softmax_xent_forward(ktc_lazy_cell logits, ktc_lazy_cell targets, float lo, float hi, ktc_lazy_cell* softmax, ktc_lazy_cell* nll);
 KTC_API int ktc_lazy_sum(ktc_lazy_cell a, int kind, int mean, const int64_t* res_shape, int res_ndim, ktc_lazy_cell* out);
 KTC_API int ktc_lazy_buffer(ktc_lazy_cell cell, ktc_buf* out);
 KTC_API int ktc_lazy_info(ktc_lazy_cell cell, int* pending, int* is_sum, int64_t* shape, int* ndim);
@@ -490,6 +513,9 @@ KTC_API int ktc_test_bounded_wait(int dev, int64_t limit_ns, int* status);   /* 
  * KTC_ENOTSUP when NVRTC is not installed. */
 KTC_API int ktc_test_expr_compile(const uint32_t* code, int n_code, int n_leaves, const int* leaf_inner, const int* leaf_fixed,
                                   int rank3, int sink, int64_t* cubin_bytes, double* compile_ms);
+/* The same for the softmax row kernel with an epilogue program (ktc_softmax_xent_forward_expr) on rows of `cols` columns. */
+KTC_API int ktc_test_softmax_expr_compile(const uint32_t* code, int n_code, int n_leaves, const int* leaf_inner, const int* leaf_fixed,
+                                          int soft_leaf, int cols, int64_t* cubin_bytes, double* compile_ms);
 /* The same for a program with several sums (ktc_expr_eval_multi). */
 KTC_API int ktc_test_expr_compile_multi(const uint32_t* code, int n_code, int n_leaves, const int* leaf_inner, const int* leaf_fixed,
                                         int rank3, const int* sink_kinds, int n_sinks, int64_t* cubin_bytes, double* compile_ms);

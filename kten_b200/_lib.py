@@ -114,7 +114,11 @@ _PROTOTYPES = {
     "ktc_lazy_full": (i32, [i32, p_i64, i32, f32, p_u64]),
     "ktc_lazy_assign_fill": (i32, [u64, f32, p_i32]),
     "ktc_lazy_assign_scatter_const": (i32, [u64, u64, f32, p_i32]),
+    "ktc_lazy_softmax_xent_forward": (i32, [u64, u64, f32, f32, p_u64, p_u64]),
     "ktc_softmax_xent_forward": (i32, [u64, u64, u64, u64, i64, i64, f32, f32]),
+    "ktc_softmax_xent_forward_expr": (i32, [u64, u64, u64, u64, i64, i64, f32, f32, C.POINTER(C.c_uint32), i32, C.POINTER(C.c_float), i32,
+                                            C.POINTER(u64), p_i64, i32, i32, C.POINTER(u64), i32]),
+    "ktc_test_softmax_expr_compile": (i32, [C.POINTER(C.c_uint32), i32, i32, C.POINTER(C.c_int), C.POINTER(C.c_int), i32, i32, p_i64, C.POINTER(C.c_double)]),
     "ktc_upsample2d_nearest": (i32, [u64, u64, i64, i64, i32]),
     "ktc_upsample2d_nearest_grad": (i32, [u64, u64, i64, i64, i32]),
     "ktc_sum_to_shape": (i32, [u64, p_i64, i32, u64, p_i64, i32]),

@@ -1320,7 +1320,9 @@ class SoftmaxCrossEntropy(UnaryTensorFunction):    # functions/nn/SoftmaxCrossEn
                 softmax, nll = res
                 self.saveForBackward(softmax)
                 self.output = nll.mean()
-                ops.release(nll)
+                # both are this function's own: the saved reference keeps the softmax until backward has run, and once that is
+                # dropped a backend that defers the forward knows that nobody reads the softmax again (it need not be written)
+                ops.release(nll, softmax)
                 return
         max_val = x.max(-1, keepDimensions=True)
         shifted = x.minus(max_val)

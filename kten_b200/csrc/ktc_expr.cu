@@ -29,6 +29,7 @@
 #include "ktc_expr_args.h"
 #include "ktc_jit.hpp"
 #include "ktc_p2p.cuh"
+#include "ktc_softmax.cuh"
 
 namespace ktc {
 
@@ -563,4 +564,77 @@ extern "C" int ktc_expr_eval_multi(const uint32_t* code, int n_code, const float
                                    const ktc_buf* stores, int n_stores,
                                    const int* sink_kinds, const ktc_buf* sink_outs, const int* means, int n_sinks) {
     return expr_eval(code, n_code, imm, n_imm, shape, ndim, leaves, leaf_shapes, n_leaves, stores, n_stores, KTC_EXPR_MULTI, 0, 0, sink_kinds, sink_outs, means, n_sinks);
+}
+
+// The forward of SoftmaxCrossEntropy (ktc_softmax_xent_forward) with an elementwise program as its epilogue: leaf
+// `soft_leaf` of the program is the row's softmax while it is still in registers, so a consumer of the saved tensor --
+// the function's backward, (softmax with -1 added at the target) / rows, SoftmaxCrossEntropy.kt:61-67 -- runs in the pass
+// that reads the logits, and `softmax` may be 0 (not written).  The other leaves are [rows | 1, cols | 1] tensors
+// (leaf_shapes: two extents per leaf; the entry of soft_leaf is ignored), STORE k writes stores[k], [rows, cols]; no ACC.
+// Every instruction is the reference operation of the stand-alone call, so the stored values are those of the forward
+// followed by the separate program.  KTC_ENOTSUP: rows the one-pass kernel does not take, or no run-time compiler -- run
+// the two separately.
+extern "C" int ktc_softmax_xent_forward_expr(ktc_buf softmax, ktc_buf nll, ktc_buf logits, ktc_buf targets, int64_t rows, int64_t cols, float lo, float hi,
+                                             const uint32_t* code, int n_code, const float* imm, int n_imm,
+                                             const ktc_buf* leaves, const int64_t* leaf_shapes, int n_leaves, int soft_leaf,
+                                             const ktc_buf* stores, int n_stores) {
+    const char* me = "ktc_softmax_xent_forward_expr";
+    if (rows < 0 || cols < 1) return fail(KTC_EINVAL, "%s: bad shape [%lld, %lld]", me, (long long)rows, (long long)cols);
+    if (!code || n_code < 1 || n_code > kExprMaxInstr) return fail(KTC_EINVAL, "%s: program of %d instructions (1..%d allowed)", me, n_code, kExprMaxInstr);
+    if (n_imm < 0 || n_imm > kExprMaxImm || (n_imm > 0 && !imm)) return fail(KTC_EINVAL, "%s: %d immediates (at most %d)", me, n_imm, kExprMaxImm);
+    if (n_leaves < 1 || n_leaves > kExprMaxLeaves || !leaves || !leaf_shapes || soft_leaf < 0 || soft_leaf >= n_leaves || n_stores < 0 || n_stores > kExprMaxStores || (n_stores && !stores))
+        return fail(KTC_EINVAL, "%s: %d leaves (softmax: %d) / %d stores (at most %d / %d)", me, n_leaves, soft_leaf, n_stores, kExprMaxLeaves, kExprMaxStores);
+    Buf bs{}, bn, bl, bt;
+    if (softmax) KTC_TRY(resolve(softmax, &bs));
+    KTC_TRY(resolve(nll, &bn)); KTC_TRY(resolve(logits, &bl)); KTC_TRY(resolve(targets, &bt));
+    if ((softmax && bs.dev != bl.dev) || bn.dev != bl.dev || bt.dev != bl.dev) return fail(KTC_EINVAL, "%s: buffers live on different devices", me);
+    const int64_t total = rows * cols;
+    if (bl.n < total || (softmax && bs.n < total) || bn.n < rows || bt.n < rows) return fail(KTC_EINVAL, "%s: a buffer is too small for [%lld, %lld]", me, (long long)rows, (long long)cols);
+    if (softmax && bs.ptr == bl.ptr) return fail(KTC_EINVAL, "%s: softmax aliases logits", me);
+    if (cols > kSxMaxVec * 128 || cols <= tune("reduce_rows_small_max", 64) || (cols & 3) || !aligned16(bl.ptr) || (softmax && !aligned16(bs.ptr)))
+        return fail(KTC_ENOTSUP, "%s: rows of %lld columns are not handled in one pass", me, (long long)cols);
+    if (rows == 0) return KTC_OK;
+    ExprArgs a{};
+    for (int l = 0; l < n_leaves; ++l) {
+        if (l == soft_leaf) { a.leaf[l] = nullptr; a.ls1[l] = cols; a.ls2[l] = 1; continue; }
+        Buf b; KTC_TRY(resolve(leaves[l], &b));
+        if (b.dev != bl.dev) return fail(KTC_EINVAL, "%s: leaf %d lives on another device", me, l);
+        const int64_t r = leaf_shapes[2 * l], c = leaf_shapes[2 * l + 1];
+        if ((r != rows && r != 1) || (c != cols && c != 1)) return fail(KTC_EINVAL, "%s: leaf %d of shape [%lld, %lld] does not broadcast to [%lld, %lld]", me, l, (long long)r, (long long)c, (long long)rows, (long long)cols);
+        if (b.n < r * c) return fail(KTC_EINVAL, "%s: leaf %d holds %lld floats, %lld needed", me, l, (long long)b.n, (long long)(r * c));
+        a.leaf[l] = b.ptr;
+        a.ls2[l] = c == cols ? 1 : 0;
+        a.ls1[l] = (r == rows && rows != 1) ? c : 0;
+        if (a.ls2[l] && !aligned16(b.ptr)) return fail(KTC_ENOTSUP, "%s: leaf %d rows are not 16-byte aligned", me, l);
+    }
+    for (int k = 0; k < n_stores; ++k) {
+        Buf b; KTC_TRY(resolve(stores[k], &b));
+        if (b.dev != bl.dev) return fail(KTC_EINVAL, "%s: store target %d lives on another device", me, k);
+        if (b.n < total) return fail(KTC_EINVAL, "%s: store target %d holds %lld floats, %lld needed", me, k, (long long)b.n, (long long)total);
+        if (!aligned16(b.ptr)) return fail(KTC_ENOTSUP, "%s: store target is not 16-byte aligned", me);
+        if (b.ptr == bl.ptr || (softmax && b.ptr == bs.ptr)) return fail(KTC_EINVAL, "%s: store target %d aliases the logits or the softmax", me, k);
+        a.store[k] = b.ptr;
+    }
+    a.n_code = n_code;
+    for (int i = 0; i < n_code; ++i) {
+        const uint32_t ins = code[i];
+        const int op = ins & 0xff, dreg = (ins >> 8) & 0xf, ra = (ins >> 12) & 0xf, rb = (ins >> 16) & 0xf, k = ins >> 20;
+        if (op < KTC_X_LOAD || op > KTC_X_ABS || op == KTC_X_ACC) return fail(KTC_EINVAL, "%s: opcode %d at %d", me, op, i);
+        if (dreg >= kExprRegs || ra >= kExprRegs || rb >= kExprRegs) return fail(KTC_EINVAL, "%s: register index out of range at %d", me, i);
+        if (op == KTC_X_LOAD && k >= n_leaves) return fail(KTC_EINVAL, "%s: LOAD of leaf %d (have %d)", me, k, n_leaves);
+        if (op == KTC_X_STORE && k >= n_stores) return fail(KTC_EINVAL, "%s: STORE to target %d (have %d)", me, k, n_stores);
+        if ((op == KTC_X_CONST || op == KTC_X_SCATC || (op >= KTC_X_CMP_LT && op <= KTC_X_CMP_GTE)) && k >= n_imm) return fail(KTC_EINVAL, "%s: immediate %d (have %d)", me, k, n_imm);
+        if (op == KTC_X_CLAMP && k + 1 >= n_imm) return fail(KTC_EINVAL, "%s: clamp immediates %d,%d (have %d)", me, k, k + 1, n_imm);
+        a.code[i] = ins;
+    }
+    for (int i = 0; i < n_imm; ++i) a.imm[i] = imm[i];
+    Device* d = device(bl.dev); if (!d) return KTC_ESTATE;
+    KTC_TRY(use_device(d));
+    a.D0 = 1; a.D1 = rows; a.D2 = cols; a.col_tiles = (cols / 4 + 31) / 32; a.seg_rows = 1; a.S = 0;
+    a.err = d->idx_err;
+    const SxArgs sa{bl.ptr, bt.ptr, bs.ptr, bn.ptr, rows, (int)cols, lo, hi, d->idx_err};
+    const int rc = jit_launch_softmax(d, a, n_leaves, soft_leaf, sa);
+    if (rc == KTC_ENOTSUP) return fail(KTC_ENOTSUP, "%s: no generated kernel for this program (NVRTC unavailable or the compilation failed)", me);
+    KTC_TRY(rc);
+    return take_index_error(d, "SoftmaxCrossEntropy target", cols, 1);
 }

@@ -12,4 +12,9 @@ namespace ktc {
 int jit_launch(Device* d, const ExprArgs& a, int n_leaves, int sink, int64_t grid);
 void jit_count_interpreter_launch();
 
+// The softmax row kernel (ktc_softmax.cuh) generated with a's program as its epilogue: leaf `soft_leaf` of the program
+// is the row's softmax, in registers.  Same return codes.
+struct SxArgs;
+int jit_launch_softmax(Device* d, const ExprArgs& a, int n_leaves, int soft_leaf, const SxArgs& sa);
+
 }  // namespace ktc

@@ -79,6 +79,9 @@ struct Backend {
                                  const ktc_buf*, int, const int*, const ktc_buf*, const int*, int,
                                  const ktc_buf*, const int*, uint64_t, const ktc_buf*, const int64_t*, int);
     int (*p2p_allreduce_sum)(uint64_t, const ktc_buf*, const int64_t*, int);
+    int (*softmax_fwd)(ktc_buf, ktc_buf, ktc_buf, ktc_buf, int64_t, int64_t, float, float);
+    int (*softmax_fwd_expr)(ktc_buf, ktc_buf, ktc_buf, ktc_buf, int64_t, int64_t, float, float, const uint32_t*, int, const float*, int,
+                            const ktc_buf*, const int64_t*, int, int, const ktc_buf*, int);
 };
 constexpr int kBackendEntries = sizeof(Backend) / sizeof(void*);
 
@@ -89,7 +92,8 @@ static void set_error_v(const char* fmt, va_list ap) { vsnprintf(g_err, sizeof(g
 #else
 static Backend B = {ktc_alloc, ktc_retain, ktc_release, ktc_refcount, ktc_buf_info, ktc_d2d, ktc_fill, ktc_binary, ktc_binary_bcast,
                     ktc_binary_inplace, ktc_scalar, ktc_scalar_inplace, ktc_unary, ktc_clamp, ktc_compare_scalar, ktc_broadcast_to,
-                    ktc_reduce_axis, ktc_reduce_all, ktc_expr_eval, ktc_expr_eval_multi_fused, ktc_p2p_allreduce_sum};
+                    ktc_reduce_axis, ktc_reduce_all, ktc_expr_eval, ktc_expr_eval_multi_fused, ktc_p2p_allreduce_sum,
+                    ktc_softmax_xent_forward, ktc_softmax_xent_forward_expr};
 static void set_error_v(const char* fmt, va_list ap) { char b[512]; vsnprintf(b, sizeof(b), fmt, ap); ::ktc::set_error("%s", b); }
 #endif
 
@@ -100,7 +104,7 @@ static int fail(int code, const char* fmt, ...) {
 #define LZ_TRY(call) do { int s_ = (call); if (s_ != KTC_OK) return s_; } while (0)
 
 constexpr int MAXD = KTC_MAX_DIMS;
-enum Kind : uint8_t { K_LEAF = 0, K_CONST, K_UN, K_BIN, K_CLAMP, K_CMP, K_SQUARE, K_BCAST, K_REDUCE, K_SCATC };
+enum Kind : uint8_t { K_LEAF = 0, K_CONST, K_UN, K_BIN, K_CLAMP, K_CMP, K_SQUARE, K_BCAST, K_REDUCE, K_SCATC, K_SOFTMAX, K_NLL };
 
 struct Shape {
     int nd = 0;
@@ -116,6 +120,11 @@ static Shape make_shape(const int64_t* s, int nd) { Shape r; r.nd = nd; for (int
 // A value.  `buf` is set once the value is in memory (the node then acts as a leaf and forgets how it was
 // computed).  A K_REDUCE node is a sum that has not run yet: args[0] is the summed expression, op the sink
 // kind, imm[0] != 0 a mean; it is never part of a program -- whoever needs its value runs the pending sums.
+// K_SOFTMAX / K_NLL: the two results of SoftmaxCrossEntropy's forward that has not run yet (SoftmaxCrossEntropy.kt:40-59):
+// K_SOFTMAX, args {logits, targets} (both in memory), imm {lo, hi}, is the [rows, cols] tensor the function saves for
+// backward; K_NLL, args {the K_SOFTMAX node}, is the [rows] loss per row.  One kernel computes both; when the softmax is
+// read by ONE recorded elementwise expression of its shape (the function's backward), that expression runs inside the same
+// kernel and the softmax is written only if something else still wants it.
 struct Node {
     int refs = 0;
     Kind kind = K_LEAF;
@@ -131,6 +140,7 @@ struct Node {
     uint64_t owner = 0;                     // id of the cell that waits for this value (weak)
     std::vector<Node*> parents;             // nodes built on this one (weak; a dying node unlinks itself)
     bool has_sum = false;                   // a pending sum may sit underneath (never reset: a stale true only costs a look)
+    bool has_row = false;                   // a pending K_SOFTMAX / K_NLL may sit underneath (never reset either)
     std::vector<ktc_buf> leaves;            // buffers this value is read from (sorted, unique)
     // scratch of the walks (valid for one epoch)
     uint32_t epoch = 0;
@@ -186,6 +196,7 @@ static uint64_t g_update_seq = 0;
 static std::unordered_map<std::string, Cached> g_cache;
 static constexpr size_t kCacheMax = 4096;
 static uint32_t g_epoch = 0;
+static std::vector<struct Node*> g_evaluating;                        // values a caller further up the stack is computing right now
 static int64_t g_live_nodes = 0;
 static int opt_recompute_limit = 2, opt_store_cost = 8, opt_defer_sums = 1, opt_defer_inplace = 1;
 static int64_t st_fused = 0, st_unfused = 0, st_multi = 0, st_cache_hits = 0, st_compiles = 0, st_fused_updates = 0, st_fused_exchanges = 0;
@@ -244,12 +255,14 @@ static Node* new_node(Kind kind, const Shape& shape, int op, Node* a0, Node* a1,
     n->kind = kind; n->op = op; n->shape = shape;
     n->nimm = nimm; for (int i = 0; i < nimm; ++i) n->imm[i] = imm[i];
     n->has_sum = kind == K_REDUCE;
+    n->has_row = kind == K_SOFTMAX || kind == K_NLL;
     Node* as[2] = {a0, a1};
     for (int i = 0; i < 2; ++i) {
         Node* a = as[i];
         if (!a) continue;
         n->args[n->nargs++] = node_ref(a);
         if (a->has_sum && !a->stored()) n->has_sum = true;
+        if (a->has_row && !a->stored()) n->has_row = true;
         if (a->dev >= 0) n->dev = a->dev;
         if (a->stored()) add_leaf(n->leaves, a->buf); else merge_leaves(n->leaves, a->leaves);
         if (a->kind != K_CONST) a->parents.push_back(n);
@@ -608,6 +621,10 @@ static void pack_leaves(const Program& prog, std::vector<ktc_buf>& hs, std::vect
 }
 
 static int run_pending(struct Exchange* x = nullptr);
+static int settle_rows(Node* const* roots, int n);
+static int try_fused_softmax(const Shape& shape, const std::vector<Node*>& stores, const std::vector<ktc_buf>& handles, const std::vector<bool>& own,
+                             Node* acc, int sink, int dev, bool* fused);
+static int run_softmax(Node* sm, bool want_softmax);
 static int force(Node* node, ktc_buf* h, Shape* shape);
 static int eager_into(Node* node, const Shape& shape, ktc_buf out);
 
@@ -626,6 +643,23 @@ static int try_fused(const Shape& shape, const std::vector<Node*>& stores, const
         std::vector<Node*> roots(stores);
         if (acc) roots.push_back(acc);
         if (has_pending_sum(roots.data(), (int)roots.size())) LZ_TRY(run_pending());
+    }
+    {
+        bool rows_below = acc && acc->has_row;
+        for (Node* n : stores) rows_below = rows_below || n->has_row;
+        if (rows_below) {
+            // a pending softmax forward underneath: this expression becomes its epilogue, or the forward runs first
+            LZ_TRY(try_fused_softmax(shape, stores, handles, own, acc, sink, dev, fused));
+            if (*fused) return KTC_OK;
+            std::vector<Node*> roots(stores);
+            if (acc) roots.push_back(acc);
+            const size_t mark = g_evaluating.size();
+            g_evaluating.insert(g_evaluating.end(), stores.begin(), stores.end());
+            for (Node* n : stores) g_evaluating.push_back(strip(n));
+            const int rs = settle_rows(roots.data(), (int)roots.size());
+            g_evaluating.resize(mark);
+            LZ_TRY(rs);
+        }
     }
     Program prog;
     std::vector<Node*> store_nodes, accs;
@@ -668,6 +702,10 @@ static int force(Node* node, ktc_buf* h, Shape* shape) {
     if (nd->kind == K_REDUCE && !nd->stored()) {
         LZ_TRY(run_pending());
         if (!nd->stored()) return fail(KTC_ESTATE, "a pending sum was not evaluated");
+    }
+    if ((nd->kind == K_SOFTMAX || nd->kind == K_NLL) && !nd->stored()) {
+        LZ_TRY(run_softmax(nd->kind == K_SOFTMAX ? nd : nd->args[0], nd->kind == K_SOFTMAX));
+        if (!nd->stored()) return fail(KTC_ESTATE, "a pending softmax forward was not evaluated");
     }
     if (!nd->stored()) {
         ktc_buf fresh = 0;
@@ -769,7 +807,7 @@ static int eager_into(Node* node, const Shape& shape, ktc_buf out) {
         if (shp.volume() == n) return B.d2d(out, 0, h, 0, n);
         return B.broadcast_to(out, shape.d, shape.nd, h, shp.d, shp.nd);
     };
-    if (nd->kind == K_REDUCE && !nd->stored()) { ktc_buf h; LZ_TRY(force(nd, &h, nullptr)); }
+    if ((nd->kind == K_REDUCE || nd->kind == K_SOFTMAX || nd->kind == K_NLL) && !nd->stored()) { ktc_buf h; LZ_TRY(force(nd, &h, nullptr)); }
     if (nd->stored()) return spread(nd->buf, nd->shape);
     if (nd->kind == K_CONST) return B.fill(out, 0, n, nd->imm[0]);
     node_ref(nd);
@@ -801,6 +839,180 @@ static int eager_into(Node* node, const Shape& shape, ktc_buf out) {
     return s;
 }
 
+// ---- SoftmaxCrossEntropy's forward as a pending value ---------------------------------------------------
+static Node* nll_of(Node* sm) {
+    for (Node* p : sm->parents) if (p->kind == K_NLL && !p->stored()) return p;
+    return nullptr;
+}
+
+// the pending K_SOFTMAX nodes under `roots`: `direct` are read by the expressions themselves, `via_nll` only through
+// their K_NLL
+static void find_rows(Node* const* roots, int n, std::vector<Node*>& direct, std::vector<Node*>& via_nll) {
+    const uint32_t ep = ++g_epoch;
+    struct Item { Node* n; bool from_nll; };
+    std::vector<Item> stack;
+    for (int i = 0; i < n; ++i) if (roots[i] && roots[i]->has_row) stack.push_back({roots[i], false});
+    while (!stack.empty()) {
+        Item it = stack.back(); stack.pop_back();
+        Node* x = it.n;
+        if (x->stored() || x->kind == K_REDUCE) continue;
+        if (x->kind == K_SOFTMAX) {
+            auto& into = it.from_nll ? via_nll : direct;
+            if (std::find(into.begin(), into.end(), x) == into.end()) into.push_back(x);
+            continue;
+        }
+        if (x->epoch == ep) continue;
+        x->epoch = ep;
+        for (int i = 0; i < x->nargs; ++i) if (x->args[i]->has_row) stack.push_back({x->args[i], x->kind == K_NLL});
+    }
+}
+
+// Runs every pending softmax forward under `roots`, so that what is left is an ordinary expression.
+static int settle_rows(Node* const* roots, int n) {
+    bool any = false;
+    for (int i = 0; i < n; ++i) any = any || (roots[i] && roots[i]->has_row);
+    if (!any) return KTC_OK;
+    std::vector<Node*> direct, via_nll;
+    find_rows(roots, n, direct, via_nll);
+    for (Node* sm : direct) node_ref(sm);
+    for (Node* sm : via_nll) node_ref(sm);
+    int s = KTC_OK;
+    for (Node* sm : direct) if (s == KTC_OK && !sm->stored()) s = run_softmax(sm, true);
+    for (Node* sm : via_nll) if (s == KTC_OK && !sm->stored()) s = run_softmax(sm, false);
+    for (Node* sm : direct) node_unref(sm);
+    for (Node* sm : via_nll) node_unref(sm);
+    return s;
+}
+
+// After a program over `order` has run with the softmax in registers: does anything still need it in memory?  A cell
+// that waits for it, or a reader outside the program.  (A cell that waits for an interior value of the program which the
+// program did not store gets that value, if it ever asks, as any recomputed interior value: from the operands -- here
+// the logits, through the forward once more.)
+static bool softmax_needed_later(Node* sm, const std::vector<Node*>& order, const std::vector<Node*>& store_nodes) {
+    if (waiting(sm)) return true;
+    std::vector<Node*> seen, stack(sm->parents.begin(), sm->parents.end());
+    while (!stack.empty()) {
+        Node* p = stack.back(); stack.pop_back();
+        if (p->kind == K_NLL || p->stored() || std::find(seen.begin(), seen.end(), p) != seen.end()) continue;
+        seen.push_back(p);
+        if (std::find(order.begin(), order.end(), p) == order.end()) return true;
+        if (std::find(store_nodes.begin(), store_nodes.end(), p) != store_nodes.end()) continue;      // in memory from now on
+        stack.insert(stack.end(), p->parents.begin(), p->parents.end());
+    }
+    return false;
+}
+
+static constexpr ktc_buf kSoftmaxInRegisters = ~(ktc_buf)0;      // stands for the softmax's buffer while a program is compiled around it
+static std::vector<Node*> g_rows_busy;                            // K_SOFTMAX nodes whose evaluation is under way
+
+// `stores` as the epilogue of the one pending softmax forward underneath them.  *fused = false: not of that form (or
+// the library declined), nothing was run.
+static int try_fused_softmax(const Shape& shape, const std::vector<Node*>& stores, const std::vector<ktc_buf>& handles, const std::vector<bool>& own,
+                             Node* acc, int sink, int dev, bool* fused) {
+    *fused = false;
+    if (acc || sink != KTC_EXPR_STORE_ONLY || shape.nd != 2 || stores.empty() || !B.softmax_fwd_expr) return KTC_OK;
+    std::vector<Node*> direct, via_nll;
+    find_rows(stores.data(), (int)stores.size(), direct, via_nll);
+    if (direct.size() != 1 || !via_nll.empty()) return KTC_OK;
+    Node* sm = direct[0];
+    if (sm->shape != shape) return KTC_OK;
+    node_ref(sm);
+    Node* nll = nll_of(sm);
+    if (nll) node_ref(nll);
+    auto done = [&](int s) { if (nll) node_unref(nll); node_unref(sm); return s; };
+    const ktc_buf h_logits = sm->args[0]->buf, h_targets = sm->args[1]->buf;
+    const float lo = sm->imm[0], hi = sm->imm[1];
+    Program prog;
+    std::vector<Node*> store_nodes;
+    int n_req = 0;
+    sm->buf = kSoftmaxInRegisters;                         // the program sees the softmax as a value in memory: one of its leaves
+    compile_program(prog, shape, stores, {}, false, opt_recompute_limit, opt_store_cost, store_nodes, &n_req);
+    sm->buf = 0;
+    if (!prog.ok) return done(KTC_OK);
+    int soft_leaf = -1, n_soft = 0;
+    for (size_t i = 0; i < prog.leaves.size(); ++i) if (prog.leaves[i].first == kSoftmaxInRegisters) { soft_leaf = (int)i; ++n_soft; }
+    if (n_soft != 1) return done(KTC_OK);
+    const int64_t rows = shape.d[0], cols = shape.d[1], total = rows * cols;
+    const bool keep = softmax_needed_later(sm, prog.order, store_nodes);
+    std::vector<ktc_buf> fresh;                            // buffers allocated here, released on failure
+    auto fail_with = [&](int s) { for (ktc_buf h : fresh) B.release(h); return done(s); };
+    ktc_buf h_soft = 0, h_nll = 0;
+    int s = KTC_OK;
+    if (keep) { s = alloc_handle(dev, total, &h_soft); if (s != KTC_OK) return fail_with(s); fresh.push_back(h_soft); }
+    s = alloc_handle(dev, rows, &h_nll); if (s != KTC_OK) return fail_with(s); fresh.push_back(h_nll);
+    std::vector<ktc_buf> all(handles);
+    for (size_t i = n_req; i < store_nodes.size(); ++i) {
+        ktc_buf h = 0;
+        s = alloc_handle(dev, total, &h); if (s != KTC_OK) return fail_with(s);
+        fresh.push_back(h); all.push_back(h);
+    }
+    std::vector<ktc_buf> lh; std::vector<int64_t> ls;
+    for (auto& l : prog.leaves) { lh.push_back(l.first == kSoftmaxInRegisters ? 0 : l.first); ls.push_back(l.second.d[0]); ls.push_back(l.second.d[1]); }
+    const float zero = 0.f;
+    const int rc = B.softmax_fwd_expr(h_soft, h_nll, h_logits, h_targets, rows, cols, lo, hi, prog.code.data(), (int)prog.code.size(),
+                                      prog.imm.empty() ? &zero : prog.imm.data(), (int)prog.imm.size(), lh.data(), ls.data(), (int)lh.size(), soft_leaf,
+                                      all.data(), (int)all.size());
+    if (rc != KTC_OK) return fail_with(rc == KTC_ENOTSUP ? KTC_OK : rc);
+    ++st_fused;
+    *fused = true;
+    for (Node* n : prog.order) ++n->evals;
+    for (int i = 0; i < n_req; ++i) if (own[i]) adopt(store_nodes[i], handles[i]);
+    for (size_t i = n_req; i < store_nodes.size(); ++i) adopt(store_nodes[i], all[handles.size() + (i - n_req)]);
+    if (keep) adopt(sm, h_soft);
+    if (nll && !nll->stored()) adopt(nll, h_nll); else B.release(h_nll);
+    return done(KTC_OK);
+}
+
+// The forward on its own: softmax (if anything wants it in memory) and nll.
+static int run_softmax_alone(Node* sm, Node* nll, bool want_softmax) {
+    bool keep = want_softmax || waiting(sm);
+    for (Node* p : sm->parents) keep = keep || p->kind != K_NLL;
+    const int64_t rows = sm->shape.d[0], cols = sm->shape.d[1];
+    ktc_buf h_soft = 0, h_nll = 0;
+    if (keep) LZ_TRY(alloc_handle(sm->dev, rows * cols, &h_soft));
+    int s = alloc_handle(sm->dev, rows, &h_nll);
+    if (s == KTC_OK) s = B.softmax_fwd(h_soft, h_nll, sm->args[0]->buf, sm->args[1]->buf, rows, cols, sm->imm[0], sm->imm[1]);
+    if (s != KTC_OK) { if (h_soft) B.release(h_soft); if (h_nll) B.release(h_nll); return s; }
+    if (nll && !nll->stored()) adopt(nll, h_nll); else B.release(h_nll);
+    if (keep) adopt(sm, h_soft);
+    return KTC_OK;
+}
+
+// Evaluate a pending softmax forward because its softmax (want_softmax) or its nll is needed.  Recorded expressions
+// that read the softmax go first: the one that has its shape takes the forward into its own kernel.
+static int run_softmax(Node* sm, bool want_softmax) {
+    if (sm->stored()) return KTC_OK;
+    node_ref(sm);
+    Node* nll = nll_of(sm);
+    if (nll) node_ref(nll);
+    int s = KTC_OK;
+    const bool busy = std::find(g_rows_busy.begin(), g_rows_busy.end(), sm) != g_rows_busy.end();
+    if (!busy) {
+        g_rows_busy.push_back(sm);
+        // the cells at the top of what has been built on the softmax
+        std::vector<uint64_t> tops;
+        std::vector<Node*> seen, stack(sm->parents.begin(), sm->parents.end());
+        while (!stack.empty()) {
+            Node* p = stack.back(); stack.pop_back();
+            if (p->kind == K_NLL || p->kind == K_REDUCE || p->stored() || std::find(seen.begin(), seen.end(), p) != seen.end()) continue;
+            seen.push_back(p);
+            if (p->parents.empty() && waiting(p) && p->shape == sm->shape && std::find(g_evaluating.begin(), g_evaluating.end(), p) == g_evaluating.end())
+                tops.push_back(p->owner);
+            stack.insert(stack.end(), p->parents.begin(), p->parents.end());
+        }
+        for (uint64_t id : tops) {
+            Cell* c = cell_of(id);
+            if (s == KTC_OK && c && c->node && !c->node->stored() && !sm->stored()) s = materialize_cell(c);
+        }
+        g_rows_busy.erase(std::find(g_rows_busy.begin(), g_rows_busy.end(), sm));
+    }
+    const bool have = want_softmax ? sm->stored() : (sm->stored() || !nll || nll->stored());
+    if (s == KTC_OK && !have) s = run_softmax_alone(sm, nll, want_softmax);
+    if (nll) node_unref(nll);
+    node_unref(sm);
+    return s;
+}
+
 // ---- pending sums ---------------------------------------------------------------------------------------
 // An all-reduce asked for while sums are pending (ktc_lazy_allreduce): when the sums turn out to be ONE pass whose
 // second-pass kernel also applies every pending update, that kernel performs the exchange too.
@@ -818,6 +1030,7 @@ static int try_fused_sums(const Shape& shape, const std::vector<Node*>& nodes, c
     std::vector<Node*> exprs; std::vector<int> kinds, means;
     bool any_rows = false;
     for (Node* nd : nodes) { exprs.push_back(nd->args[0]); kinds.push_back(nd->op); means.push_back(nd->imm[0] != 0.f ? 1 : 0); any_rows = any_rows || nd->op == KTC_EXPR_SUM_ROWS; }
+    LZ_TRY(settle_rows(exprs.data(), (int)exprs.size()));
     Program prog;
     std::vector<Node*> store_nodes; int n_req = 0;
     // every consumer known so far sits in this pass: nothing is stored on the side for its cost alone
@@ -1302,6 +1515,41 @@ KTC_API int ktc_lazy_assign_scatter_const(ktc_lazy_cell target, ktc_lazy_cell in
     node_ref(ni);
     const int s = assign(target, K_SCATC, 0, nt, ni, &value, 1, state);
     node_unref(ni);
+    return s;
+}
+
+// The forward of SoftmaxCrossEntropy (SoftmaxCrossEntropy.kt:40-59) on logits [rows, cols] and targets (rows class indices),
+// recorded: *softmax is the tensor the function saves for backward, *nll the loss per row.  Nothing runs until one of them
+// is needed; an elementwise expression of the softmax's shape recorded meanwhile (the function's backward and what is
+// accumulated from it) is then evaluated inside the forward's kernel, and the softmax itself is written only if a tensor
+// still holds it.  KTC_ENOTSUP: rows the one-pass kernel does not take -- issue the calls.
+KTC_API int ktc_lazy_softmax_xent_forward(ktc_lazy_cell logits, ktc_lazy_cell targets, float lo, float hi, ktc_lazy_cell* softmax, ktc_lazy_cell* nll) {
+    LZ_LOCK;
+    if (!softmax || !nll) return fail(KTC_EINVAL, "ktc_lazy_softmax_xent_forward: null output");
+    if (!B.softmax_fwd) return fail(KTC_ENOTSUP, "ktc_lazy_softmax_xent_forward: the library has no one-pass forward");
+    Node *lg, *tg;
+    LZ_TRY(operand(logits, &lg)); LZ_TRY(operand(targets, &tg)); LZ_TRY(operand(logits, &lg));
+    if (lg->shape.nd != 2) return fail(KTC_EINVAL, "ktc_lazy_softmax_xent_forward: logits of %d dimensions", lg->shape.nd);
+    const int64_t rows = lg->shape.d[0], cols = lg->shape.d[1];
+    if (tg->shape.volume() != rows) return fail(KTC_EINVAL, "ktc_lazy_softmax_xent_forward: %lld targets for %lld rows", (long long)tg->shape.volume(), (long long)rows);
+    if (rows < 1 || cols <= 64 || cols > 2048 || (cols & 3) || strip(lg)->shape.volume() != rows * cols || strip(tg)->shape.volume() != rows)
+        return fail(KTC_ENOTSUP, "ktc_lazy_softmax_xent_forward: [%lld, %lld] logits are not handled in one pass", (long long)rows, (long long)cols);
+    node_ref(lg); node_ref(tg);
+    ktc_buf hl = 0, ht = 0;
+    int s = force(lg, &hl, nullptr);
+    if (s == KTC_OK) s = force(tg, &ht, nullptr);
+    void* ptr = nullptr; int dev = 0; int64_t n = 0;
+    if (s == KTC_OK) s = B.buf_info(hl, &dev, &n, &ptr);
+    if (s == KTC_OK && (reinterpret_cast<uintptr_t>(ptr) & 15)) s = fail(KTC_ENOTSUP, "ktc_lazy_softmax_xent_forward: the logits are not 16-byte aligned");
+    if (s == KTC_OK) {
+        const float imm[2] = {lo, hi};
+        Node* sm = new_node(K_SOFTMAX, strip(lg)->shape, 0, strip(lg), strip(tg), imm, 2);
+        Shape rs; rs.nd = 1; rs.d[0] = rows;
+        Node* nl = new_node(K_NLL, rs, 0, sm, nullptr, nullptr, 0);
+        *softmax = new_cell(node_ref(sm)); register_cell(*softmax, sm);
+        *nll = new_cell(node_ref(nl)); register_cell(*nll, nl);
+    }
+    node_unref(lg); node_unref(tg);
     return s;
 }
 

@@ -97,6 +97,19 @@ class Recorder:
         L.check(rc)
         return state.value
 
+    def softmax_xent_forward(self, logits: int, targets: int, lo: float, hi: float):
+        """The forward of SoftmaxCrossEntropy, recorded: (softmax cell, nll cell), or None where the one-pass kernel does not
+        apply (the caller issues the calls)."""
+        fn = getattr(self.lib, "ktc_lazy_softmax_xent_forward", None)
+        if fn is None:
+            return None
+        softmax, nll = C.c_uint64(0), C.c_uint64(0)
+        rc = fn(logits, targets, float(lo), float(hi), C.byref(softmax), C.byref(nll))
+        if rc == L.KTC_ENOTSUP:
+            return None
+        L.check(rc)
+        return softmax.value, nll.value
+
     def sum(self, a: int, kind: int, mean: bool, res_shape: Sequence[int]) -> int:
         arr, nd = L.shape_array(res_shape)
         return self._cell(self.lib.ktc_lazy_sum, a, kind, 1 if mean else 0, arr, nd)

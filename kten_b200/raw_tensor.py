@@ -561,6 +561,11 @@ class CUDARawTensor:
         if entry is None or len(self.shape) != 2 or targets.size != self.shape[0]:
             return None
         rows, cols = self.shape
+        if self.ops.lazy:
+            # recorded: the kernel runs when the loss or the gradient is needed, and takes the recorded backward with it
+            cells = self.ops._recorder.softmax_xent_forward(self._lz(), targets._lz(), lo, hi)
+            if cells is not None:
+                return self._recorded([rows, cols], cells[0]), self._recorded([rows], cells[1])
         softmax, nll = self._new([rows, cols]), self._new([rows])
         rc = entry(softmax._buf(), nll._buf(), self._buf(), targets._buf(), rows, cols, float(lo), float(hi))
         if rc == L.KTC_ENOTSUP:

@@ -57,6 +57,8 @@ BACKEND = [
     ("ktc_expr_eval_multi_fused", (i32, P(C.c_uint32), i32, P(f32), i32, P(i64), i32, P(u64), P(i64), i32, P(u64), i32, P(i32), P(u64), P(i32), i32,
                                    P(u64), P(i32), u64, P(u64), P(i64), i32)),
     ("ktc_p2p_allreduce_sum", (i32, u64, P(u64), P(i64), i32)),
+    ("ktc_softmax_xent_forward", (i32, u64, u64, u64, u64, i64, i64, f32, f32)),
+    ("ktc_softmax_xent_forward_expr", (i32, u64, u64, u64, u64, i64, i64, f32, f32, P(C.c_uint32), i32, P(f32), i32, P(u64), P(i64), i32, i32, P(u64), i32)),
 ]
 RECORDER_CALLS = {
     "ktc_lazy_leaf": (i32, [u64, P(i64), i32, P(u64)]), "ktc_lazy_free": (i32, [u64]),
@@ -70,6 +72,7 @@ RECORDER_CALLS = {
     "ktc_lazy_allreduce": (i32, [u64, P(u64), i32]),
     "ktc_lazy_full": (i32, [i32, P(i64), i32, f32, P(u64)]), "ktc_lazy_assign_fill": (i32, [u64, f32, P(i32)]),
     "ktc_lazy_assign_scatter_const": (i32, [u64, u64, f32, P(i32)]),
+    "ktc_lazy_softmax_xent_forward": (i32, [u64, u64, f32, f32, P(u64), P(u64)]),
 }
 
 
@@ -319,6 +322,55 @@ class FakeLib:
         for i in range(n):
             self._get(bufs[i])
         return 0
+
+    # ---- SoftmaxCrossEntropy's forward: the call sequence of SoftmaxCrossEntropy.kt:40-59 with the oracle's arithmetic ----
+    def _softmax_rows(self, logits, targets, rows, cols, lo, hi):
+        x = self._get(logits)[:rows * cols].copy()
+        t = self._get(targets)[:rows].astype(np.int64)
+        rep = lambda v: np.repeat(v, cols)
+        shifted = O.binary_same(O.MINUS, x, rep(O.aggregate(L.MAX, x, rows, cols, 1)))
+        e = O.unary(O.EXP, shifted)
+        p = O.binary_same(O.DIV, e, rep(O.aggregate(L.SUM, e, rows, cols, 1)))
+        pn = O.binary_same(O.DIV, p, rep(O.aggregate(L.SUM, p, rows, cols, 1)))
+        logp = O.unary(O.LOG, O.clamp(pn, lo, hi))
+        nll = O.unary(O.NEG, logp.reshape(rows, cols)[np.arange(rows), t].copy())
+        return p, nll
+
+    def ktc_softmax_xent_forward(self, softmax, nll, logits, targets, rows, cols, lo, hi):
+        if cols > 2048 or cols <= 64 or cols % 4:
+            self.error = b"rows not handled in one pass"
+            return L.KTC_ENOTSUP
+        self._note("softmax_xent_forward")
+        p, l = self._softmax_rows(logits, targets, rows, cols, lo, hi)
+        if softmax:
+            self._get(softmax)[:rows * cols] = p
+        self._get(nll)[:rows] = l
+        return 0
+
+    def ktc_softmax_xent_forward_expr(self, softmax, nll, logits, targets, rows, cols, lo, hi, code, n_code, imm, n_imm, leaves, lshapes, n_leaves, soft_leaf,
+                                      stores, n_stores):
+        if cols > 2048 or cols <= 64 or cols % 4 or getattr(self, "no_softmax_epilogue", False):
+            self.error = b"rows not handled in one pass"
+            return L.KTC_ENOTSUP
+        self._note("softmax_xent_forward_expr")
+        self.launches -= 1                                   # one kernel: the program below counts it
+        p, l = self._softmax_rows(logits, targets, rows, cols, lo, hi)
+        if softmax:
+            self._get(softmax)[:rows * cols] = p
+        self._get(nll)[:rows] = l
+        # the program sees the row's softmax as its leaf `soft_leaf`: a scratch buffer here, registers in the kernel
+        ref = _Out([0])
+        self.ktc_alloc(0, rows * cols, ref)
+        tmp = ref.value
+        self._get(tmp)[:] = p
+        hs = (u64 * n_leaves)(*[tmp if i == soft_leaf else int(leaves[i]) for i in range(n_leaves)])
+        shapes = []
+        for i in range(n_leaves):
+            shapes += [rows, cols] if i == soft_leaf else [int(lshapes[2 * i]), int(lshapes[2 * i + 1])]
+        rc = self.ktc_expr_eval(code, n_code, imm, n_imm, (i64 * 2)(rows, cols), 2, hs, (i64 * len(shapes))(*shapes), n_leaves, stores, n_stores,
+                                L.EXPR_STORE_ONLY, 0, 0)
+        self.ktc_release(tmp)
+        return rc
 
     def ktc_expr_eval_multi_fused(self, code, n_code, imm, n_imm, shape, ndim, leaves, lshapes, n_leaves, stores, n_stores, kinds, outs, means, n_sinks,
                                   add_to, add_mode, comm, x_bufs, x_counts, n_x):

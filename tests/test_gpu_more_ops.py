@@ -2,6 +2,8 @@
 maskedFill, containsNan, slices / permutes and gather / scatter / index ops, against the CPU oracle
 (oracle/) on the same seeded inputs, through the C ABI.  Exact for everything that is IEEE or index
 arithmetic; at most 2 ulp for the transcendental maps."""
+import ctypes as C
+
 import numpy as np
 import pytest
 
@@ -340,3 +342,111 @@ def test_one_pass_softmax_forward_declines_and_checks(cuda_ops, gc_scope, index_
         logits.softmaxCrossEntropyForward(cuda_ops.createRaw([4], np.array([0, 128, 5, 7], dtype=np.float32)), eps, hi)
     ok = logits.softmaxCrossEntropyForward(cuda_ops.createRaw([4], np.array([0, 127, 5, 7], dtype=np.float32)), eps, hi)
     assert ok is not None and np.isfinite(ok[1].toArray()).all()
+
+
+@pytest.mark.parametrize("rows,cols", [(1024, 2048), (700, 1024), (515, 512), (333, 640), (64, 68)])
+def test_softmax_backward_inside_the_forward_kernel_has_the_bits_of_the_separate_kernels(cuda_ops, gc_scope, rows, cols):
+    """Deferred, the forward of SoftmaxCrossEntropy waits for its consumer: the function's backward and the accumulation
+    into the Variable's gradient (SoftmaxCrossEntropy.kt:61-67, Variable.kt:44-46) run as the epilogue of the kernel that
+    reads the logits (ktc_softmax_xent_forward_expr, generated at run time) and the saved softmax is never written.  Loss
+    and gradient carry the bits of the call-by-call run, in either order of asking; three launches at most (the kernel and
+    the mean of the rows' losses)."""
+    from kten_b200 import autograd as AG
+    x = D.uniform(rows * cols, 211, -6.0, 6.0)
+    x[::7919] = 45.0
+    t = np.floor(D.uniform(rows, 212, 0.0, cols - 0.01)).astype(np.float32)
+    lib = cuda_ops.lib
+
+    def step(loss_first):
+        logits = AG.Variable(cuda_ops, cuda_ops.createRaw([rows, cols], x))
+        targets = AG.NoGradVariable(cuda_ops, cuda_ops.createRaw([rows], t))
+        l0 = lib.ktc_launch_count()
+        loss = logits.softmaxCrossEntropy(targets)
+        loss.backward()
+        if loss_first:
+            lv = loss.toArray(); gv = logits.grad().toArray()
+        else:
+            gv = logits.grad().toArray(); lv = loss.toArray()
+        return lv, gv, lib.ktc_launch_count() - l0
+
+    le, ge, _ = step(False)
+    stats = (C.c_int64 * 6)()
+    L.check(lib.ktc_expr_stats(stats))
+    if stats[5] == 0:
+        pytest.skip("no run-time compiler on this machine: the forward and its consumer run separately")
+    cuda_ops.lazy = True
+    try:
+        for loss_first in (False, True):
+            ll, gl, launches = step(loss_first)
+            assert same_bits(le, ll) and same_bits(ge, gl)
+            assert launches <= 3, launches
+    finally:
+        cuda_ops.lazy = False
+
+
+def test_softmax_forward_with_an_epilogue_program_through_the_c_abi(cuda_ops, gc_scope, index_checks_at_call):
+    """ktc_softmax_xent_forward_expr against ktc_softmax_xent_forward followed by ktc_expr_eval on the stored softmax: the
+    same nll, softmax and stored results, with and without the softmax written; argument checks; a target outside its row
+    is reported."""
+    rows, cols = 300, 1024
+    lib = cuda_ops.lib
+    x = D.uniform(rows * cols, 221, -4.0, 4.0)
+    t = np.floor(D.uniform(rows, 222, 0.0, cols - 0.01)).astype(np.float32)
+    w = D.uniform(cols, 223, 0.5, 1.5)
+    logits, targets, scale = cuda_ops.createRaw([rows, cols], x), cuda_ops.createRaw([rows, 1], t), cuda_ops.createRaw([1, cols], w)
+    eps = cuda_ops.epsilon
+    hi = float(np.float32(1.0) - np.float32(eps))
+
+    def ins(op, d=0, a=0, b=0, k=0):
+        return op | d << 8 | a << 12 | b << 16 | k << 20
+
+    # out0 = ((0 with -1 at the target) + softmax) / rows ; out1 = out0 * scale[col]      leaves: 0 targets, 1 softmax, 2 scale
+    code = [ins(L.X_CONST, 0, 0, 0, 0), ins(L.X_LOAD, 1, 0, 0, 0), ins(L.X_SCATC, 0, 0, 1, 1), ins(L.X_LOAD, 1, 0, 0, 1), ins(L.X_ADD, 0, 0, 1),
+            ins(L.X_CONST, 1, 0, 0, 2), ins(L.X_DIV, 0, 0, 1), ins(L.X_STORE, 0, 0, 0, 0), ins(L.X_LOAD, 1, 0, 0, 2), ins(L.X_MUL, 2, 0, 1), ins(L.X_STORE, 0, 2, 0, 1)]
+    code_a = (C.c_uint32 * len(code))(*code)
+    imm = (C.c_float * 3)(0.0, -1.0, float(rows))
+    shapes = (C.c_int64 * 6)(rows, 1, rows, cols, 1, cols)
+
+    def run(keep_softmax):
+        sm = cuda_ops.createRaw([rows, cols]) if keep_softmax else None
+        nll, o0, o1 = cuda_ops.createRaw([rows]), cuda_ops.createRaw([rows, cols]), cuda_ops.createRaw([rows, cols])
+        leaves = (C.c_uint64 * 3)(targets.storeReference, 0, scale.storeReference)
+        stores = (C.c_uint64 * 2)(o0.storeReference, o1.storeReference)
+        rc = lib.ktc_softmax_xent_forward_expr(sm.storeReference if sm else 0, nll.storeReference, logits.storeReference, targets.storeReference, rows, cols,
+                                               eps, hi, code_a, len(code), imm, 3, leaves, shapes, 3, 1, stores, 2)
+        return rc, sm, nll, o0, o1
+
+    rc, sm, nll, o0, o1 = run(True)
+    if rc == L.KTC_ENOTSUP:
+        pytest.skip("no run-time compiler on this machine")
+    L.check(rc)
+    want_sm, want_nll = logits.softmaxCrossEntropyForward(targets, eps, hi)
+    w0, w1 = cuda_ops.createRaw([rows, cols]), cuda_ops.createRaw([rows, cols])
+    leaves = (C.c_uint64 * 3)(targets.storeReference, want_sm.storeReference, scale.storeReference)
+    stores = (C.c_uint64 * 2)(w0.storeReference, w1.storeReference)
+    L.check(lib.ktc_expr_eval(code_a, len(code), imm, 3, (C.c_int64 * 2)(rows, cols), 2, leaves, shapes, 3, stores, 2, L.EXPR_STORE_ONLY, 0, 0))
+    assert same_bits(sm.toArray(), want_sm.toArray()) and same_bits(nll.toArray(), want_nll.toArray())
+    assert same_bits(o0.toArray(), w0.toArray()) and same_bits(o1.toArray(), w1.toArray())
+    rc, _, nll2, p0, p1 = run(False)
+    L.check(rc)
+    assert same_bits(nll2.toArray(), want_nll.toArray()) and same_bits(p0.toArray(), w0.toArray()) and same_bits(p1.toArray(), w1.toArray())
+    # argument checks
+    leaves = (C.c_uint64 * 3)(targets.storeReference, 0, scale.storeReference)
+    stores = (C.c_uint64 * 2)(o0.storeReference, o1.storeReference)
+    args = (0, nll.storeReference, logits.storeReference, targets.storeReference, rows, cols, eps, hi)
+    assert lib.ktc_softmax_xent_forward_expr(*args, code_a, len(code), imm, 3, leaves, shapes, 3, 5, stores, 2) == L.KTC_EINVAL          # no such leaf
+    assert lib.ktc_softmax_xent_forward_expr(*args, code_a, len(code), imm, 3, leaves, shapes, 3, 1, stores, 1) == L.KTC_EINVAL          # STORE 1 without a target
+    bad = (C.c_int64 * 6)(rows, 1, rows, cols, 1, cols - 4)
+    assert lib.ktc_softmax_xent_forward_expr(*args, code_a, len(code), imm, 3, leaves, bad, 3, 1, stores, 2) == L.KTC_EINVAL             # leaf does not broadcast
+    acc = (C.c_uint32 * 2)(ins(L.X_LOAD, 0, 0, 0, 1), ins(L.X_ACC, 0, 0))
+    assert lib.ktc_softmax_xent_forward_expr(*args, acc, 2, imm, 3, leaves, shapes, 3, 1, stores, 2) == L.KTC_EINVAL                     # sums are not epilogues
+    short = cuda_ops.createRaw([4, 48], D.uniform(192, 224, -1.0, 1.0))
+    assert lib.ktc_softmax_xent_forward_expr(0, nll.storeReference, short.storeReference, targets.storeReference, 4, 48, eps, hi,
+                                             code_a, len(code), imm, 3, leaves, shapes, 3, 1, stores, 2) == L.KTC_ENOTSUP
+    # a target outside its row: reported at the call (index_checks_at_call), nothing read out of bounds
+    tb = t.copy(); tb[7] = float(cols)
+    bad_targets = cuda_ops.createRaw([rows, 1], tb)
+    leaves = (C.c_uint64 * 3)(bad_targets.storeReference, 0, scale.storeReference)
+    rc = lib.ktc_softmax_xent_forward_expr(0, nll.storeReference, logits.storeReference, bad_targets.storeReference, rows, cols, eps, hi,
+                                           code_a, len(code), imm, 3, leaves, shapes, 3, 1, stores, 2)
+    assert rc != 0

@@ -132,3 +132,26 @@ def test_last_axis_sum_sink_compiles():
                 pytest.skip("NVRTC is not installed here: " + lib.ktc_last_error().decode())
             assert rc == L.KTC_OK, lib.ktc_last_error().decode()[:4000]
             assert nbytes.value > 1000
+
+
+@pytest.mark.parametrize("cols", [2048, 1024, 512, 640])
+def test_softmax_row_kernel_with_an_epilogue_program_compiles(cols):
+    """The generated form of the softmax forward (ktc_softmax_xent_forward_expr): the backward of SoftmaxCrossEntropy as
+    its epilogue -- (0 with -1 at the target + softmax) / rows, then the accumulation into a zeroed gradient -- and a
+    program that touches every other kind of leaf, for each row-length specialisation."""
+    lib = L.load()
+    # leaves: 0 targets [rows, 1], 1 the softmax (registers), 2 a row vector [1, cols], 3 a [rows, cols] tensor, 4 a scalar [1, 1]
+    prog = [ins(L.X_CONST, 0, k=0), ins(L.X_LOAD, 1, k=0), ins(L.X_SCATC, 0, 0, 1, k=1), ins(L.X_LOAD, 1, k=1), ins(L.X_ADD, 0, 0, 1),
+            ins(L.X_CONST, 1, k=2), ins(L.X_DIV, 0, 0, 1), ins(L.X_CONST, 1, k=0), ins(L.X_ADD, 0, 1, 0), ins(L.X_STORE, a=0, k=0),
+            ins(L.X_LOAD, 2, k=2), ins(L.X_MUL, 2, 2, 0), ins(L.X_LOAD, 3, k=3), ins(L.X_SUB, 2, 2, 3), ins(L.X_LOAD, 3, k=4), ins(L.X_MUL, 2, 2, 3),
+            ins(L.X_EXP, 2, 2), ins(L.X_STORE, a=2, k=1)]
+    code = (C.c_uint32 * len(prog))(*prog)
+    inner, fixed = (C.c_int * 5)(0, 1, 1, 1, 0), (C.c_int * 5)(0, 0, 1, 0, 1)
+    nbytes, ms = C.c_int64(0), C.c_double(0)
+    rc = lib.ktc_test_softmax_expr_compile(code, len(prog), 5, inner, fixed, 1, cols, C.byref(nbytes), C.byref(ms))
+    if rc == L.KTC_ENOTSUP:
+        pytest.skip("NVRTC is not installed here: " + lib.ktc_last_error().decode())
+    assert rc == L.KTC_OK, lib.ktc_last_error().decode()[:4000]
+    assert nbytes.value > 1000
+    acc = (C.c_uint32 * 2)(ins(L.X_LOAD, 0, k=1), ins(L.X_ACC, a=0))
+    assert lib.ktc_test_softmax_expr_compile(acc, 2, 5, inner, fixed, 1, cols, None, None) == L.KTC_EINVAL
