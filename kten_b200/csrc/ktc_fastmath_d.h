@@ -234,6 +234,14 @@ KD_FN float kd_div_by_reciprocal(float x, float b, float r) {
     return fmaf(fmaf(-q, b, x), r, q);
 }
 
+// A divisor that is a power of two inside kd_row_reciprocal's range: x / b and x * (1 / b) are then roundings of the same
+// real number (the reciprocal is exact), for every x -- zeros keep their sign, subnormal quotients round alike, infinities
+// and NaN pass -- so one multiplication is the IEEE quotient and no window test is needed.
+KD_FN bool kd_is_pow2_divisor(float b) {
+    const uint32_t bits = (uint32_t)KD_F2I(b) & 0x7fffffffu;
+    return (bits & 0x007fffffu) == 0u && bits >= (67u << 23) && bits <= (187u << 23);      // 2^-60 .. 2^60
+}
+
 // kten-jvm's sigmoid: e = (float)Math.exp((double)(-1f * x)); 1f / (1f + e)   (JVMRawTensor.kt:399).
 // x is clamped to [-89, 30] first: beyond 30 the sum 1f + e is 1f exactly, below -88.73 e is +infinity
 // (exp(89) narrows to infinity as Math.exp's value does), so the clamp does not change any result.

@@ -136,6 +136,19 @@ __device__ __forceinline__ float4 div_by_row(float4 x, float b, float r) {
     return make_float4(kd_div_by_reciprocal(x.x, b, r), kd_div_by_reciprocal(x.y, b, r), kd_div_by_reciprocal(x.z, b, r), kd_div_by_reciprocal(x.w, b, r));
 }
 
+// the same with the window test done by the caller (in_window: every dividend of x is known to lie in kd_div_window's
+// range -- e.g. exp of an argument above -43); both forms give the IEEE quotient wherever they apply
+__device__ __forceinline__ float4 div_by_row_known(float4 x, float b, float r, bool in_window) {
+    if (!in_window || r == 0.f) return div_ieee4(x, b);
+    return make_float4(kd_div_by_reciprocal(x.x, b, r), kd_div_by_reciprocal(x.y, b, r), kd_div_by_reciprocal(x.z, b, r), kd_div_by_reciprocal(x.w, b, r));
+}
+// x / b for a divisor that is the same for a whole kernel (a constant of a recorded expression): r = kd_row_reciprocal(b),
+// pow2 = kd_is_pow2_divisor(b).  A power of two (a batch size, usually) is one multiplication by its exact reciprocal.
+__device__ __forceinline__ float4 div_by_const(float4 x, float b, float r, bool pow2) {
+    if (pow2) return make_float4(__fmul_rn(x.x, r), __fmul_rn(x.y, r), __fmul_rn(x.z, r), __fmul_rn(x.w, r));
+    return div_by_row(x, b, r);
+}
+
 struct ClampOp { float lo, hi; __device__ __forceinline__ float operator()(float x) const { return jmin(jmax(x, lo), hi); } };
 
 template <int OP> struct CompareOp {

@@ -11,7 +11,14 @@ namespace ktc {
 // MINB: resident CTAs per SM the register allocation must allow (the row of 2048 columns alone is 64 registers per lane)
 template <int NV, int MINB>
 __global__ void __launch_bounds__(256, MINB) k_softmax_xent_forward(const __grid_constant__ SxArgs a) {
-    sx_rows<NV>(a, SxNoEpilogue());
+    SxNoEpilogue none;
+    sx_rows<NV>(a, none);
+}
+
+template <int MINB>
+__global__ void __launch_bounds__(256, MINB) k_softmax_xent_forward_pair(const __grid_constant__ SxArgs a) {
+    SxNoEpilogue none;
+    sx_rows_pair(a, none);
 }
 
 int launch_softmax_xent_forward(Device* d, float* softmax, float* nll, const float* logits, const float* targets,
@@ -21,7 +28,13 @@ int launch_softmax_xent_forward(Device* d, float* softmax, float* nll, const flo
     if (grid > 0x7fffffffLL) return fail(KTC_ENOTSUP, "tensor too large for one launch");
     const SxArgs a{logits, targets, softmax, nll, rows, (int)cols, lo, hi, d->idx_err};
 #define KTC_SX(NV, MINB) k_softmax_xent_forward<NV, MINB><<<(int)grid, 256, 0, d->stream>>>(a)
-    if (cols == 2048) { if (tune("softmax_min_blocks", 2) == 3) KTC_SX(16, 3); else KTC_SX(16, 2); }
+    if (cols == 2048 && tune("softmax_pair", 1)) {                 // two warps per row: half the registers, twice the warps in flight
+        const int64_t grid4 = (rows + 3) / 4;
+        if (grid4 > 0x7fffffffLL) return fail(KTC_ENOTSUP, "tensor too large for one launch");
+        if (tune("softmax_pair_min_blocks", 4) == 3) k_softmax_xent_forward_pair<3><<<(int)grid4, 256, 0, d->stream>>>(a);
+        else k_softmax_xent_forward_pair<4><<<(int)grid4, 256, 0, d->stream>>>(a);
+    }
+    else if (cols == 2048) { if (tune("softmax_min_blocks", 2) == 3) KTC_SX(16, 3); else KTC_SX(16, 2); }
     else if (cols == 1024) KTC_SX(8, 3); else if (cols == 512) KTC_SX(4, 4); else KTC_SX(0, 2);
 #undef KTC_SX
     count_launch(1);

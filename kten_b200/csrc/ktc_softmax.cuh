@@ -29,6 +29,7 @@
 namespace ktc {
 
 constexpr int kSxMaxVec = 16;             // float4 per lane: rows of up to 2048 columns
+constexpr float kSxWindowArg = -43.0f;    // exp of anything above is >= 2^-62.1, inside kd_div_window's dividend range [2^-63, 2^64)
 
 struct SxArgs {
     const float* logits; const float* targets;
@@ -61,15 +62,20 @@ __device__ __forceinline__ float sx_row_sum(const float4 (&v)[kSxMaxVec], int n_
     return (float)acc.acc;
 }
 
-struct SxNoEpilogue { __device__ __forceinline__ void operator()(int64_t, int, const float4&) const {} };
+struct SxNoEpilogue {
+    __device__ __forceinline__ void begin(int64_t) {}
+    __device__ __forceinline__ void operator()(int64_t, int, const float4&) const {}
+};
 
 // One warp per row, eight rows per CTA of 256 threads.  NV > 0: every lane owns exactly NV vectors (cols == 128 NV)
-// and the guards below fold away; NV == 0: any row length.  epi(row, column of the vector's first element, p).
+// and the guards below fold away; NV == 0: any row length.  The epilogue: begin(row) once -- whatever it needs per row --,
+// then epi(row, column of the vector's first element, p) for every vector of quotients.
 template <int NV, class Epi>
-__device__ __forceinline__ void sx_rows(const SxArgs& a, const Epi& epi) {
+__device__ __forceinline__ void sx_rows(const SxArgs& a, Epi& epi) {
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (row >= a.rows) return;                                     // whole warps leave together
+    epi.begin(row);
     const int cols = a.cols;
     const int q1 = cols >> 2;
     const int n_l = NV > 0 ? NV : (q1 > lane ? (q1 - lane + 31) >> 5 : 0);        // vectors of this lane
@@ -84,11 +90,14 @@ __device__ __forceinline__ void sx_rows(const SxArgs& a, const Epi& epi) {
     #pragma unroll
     for (int off = 16; off > 0; off >>= 1) mx.shfl_merge(0xffffffffu, off);
     const float m = mx.v;
-    // exp(x - max)
+    // exp(x - max); an argument above kSxWindowArg gives a dividend inside the window of the division by the row's reciprocal
+    // (exp(-43) > 2^-63; a NaN fails the comparison): tested here on the argument, one comparison per element
+    unsigned in_window = 0u;
     #pragma unroll
     for (int u = 0; u < kSxMaxVec; ++u) {
         if (u < n_l) {
             const float4 s = make_float4(__fsub_rn(v[u].x, m), __fsub_rn(v[u].y, m), __fsub_rn(v[u].z, m), __fsub_rn(v[u].w, m));
+            if (s.x >= kSxWindowArg && s.y >= kSxWindowArg && s.z >= kSxWindowArg && s.w >= kSxWindowArg) in_window |= 1u << u;
             v[u] = apply1(UnOp<KTC_EXP>(), s);
         }
     }
@@ -99,7 +108,7 @@ __device__ __forceinline__ void sx_rows(const SxArgs& a, const Epi& epi) {
     #pragma unroll
     for (int u = 0; u < kSxMaxVec; ++u) {
         if (u < n_l) {
-            v[u] = div_by_row(v[u], S, rS);
+            v[u] = div_by_row_known(v[u], S, rS, (in_window >> u) & 1u);
             if (keep) __stcs(ps + lane + 32 * u, v[u]);
             epi(row, (lane + 32 * u) * 4, v[u]);
         }
@@ -126,6 +135,87 @@ __device__ __forceinline__ void sx_rows(const SxArgs& a, const Epi& epi) {
             *a.err = 1;
             a.nll[row] = CUDART_NAN_F;
         }
+    }
+}
+
+// Rows of exactly 2048 columns with TWO warps per row (four rows per CTA of 256 threads): each lane then holds 8 vectors
+// instead of 16, the kernel needs half the registers, and twice as many warps are resident to hide the latency of the
+// loads and of the exp chain.  The bits do not change: warp h of the pair owns the vectors lane + 32 (8 h + u), u < 8 --
+// exactly the h-th float run of the one-warp form -- so a lane's double is (0.0 + run_0) + run_1 as before (the second run
+// arrives through shared memory), and both warps then walk the same xor-shuffle tree; the maximum is associative.
+template <class Epi>
+__device__ __forceinline__ void sx_rows_pair(const SxArgs& a, Epi& epi) {
+    __shared__ float sh_max[8];
+    __shared__ double sh_run[2][8][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, half = warp & 1, pr = warp >> 1;
+    const int64_t row = (int64_t)blockIdx.x * 4 + pr;
+    if (row >= a.rows) return;                                     // both warps of a pair leave together
+    epi.begin(row);
+    constexpr int cols = 2048;
+    const int first = lane + 256 * half;                           // float4 index of this lane's first vector
+    const float4* px = reinterpret_cast<const float4*>(a.logits + row * cols) + first;
+    float4 v[8];
+    #pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = __ldcs(px + 32 * u);
+    auto pair_barrier = [&]() { asm volatile("bar.sync %0, 64;" :: "r"(pr + 1) : "memory"); };
+    ExtAcc<true> mx; mx.init();
+    #pragma unroll
+    for (int u = 0; u < 8; ++u) mx.add4(v[u], 0);
+    #pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mx.shfl_merge(0xffffffffu, off);
+    if (lane == 0) sh_max[warp] = mx.v;
+    pair_barrier();
+    const float m = max_nan(sh_max[2 * pr], sh_max[2 * pr + 1]);
+    unsigned in_window = 0u;
+    #pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const float4 s = make_float4(__fsub_rn(v[u].x, m), __fsub_rn(v[u].y, m), __fsub_rn(v[u].z, m), __fsub_rn(v[u].w, m));
+        if (s.x >= kSxWindowArg && s.y >= kSxWindowArg && s.z >= kSxWindowArg && s.w >= kSxWindowArg) in_window |= 1u << u;
+        v[u] = apply1(UnOp<KTC_EXP>(), s);
+    }
+    // the row sum: this warp's float run, folded with the partner's in the order run_0, run_1
+    auto row_sum = [&](int which) -> float {
+        SumAcc acc; acc.init();
+        acc.begin();
+        #pragma unroll
+        for (int u = 0; u < 8; ++u) acc.add4(v[u], 0);
+        sh_run[which][warp][lane] = (double)acc.run;
+        pair_barrier();
+        acc.acc = 0.0;
+        acc.acc += sh_run[which][2 * pr][lane];
+        acc.acc += sh_run[which][2 * pr + 1][lane];
+        acc.acc += 0.0;                                            // the empty tail run of the one-warp form
+        #pragma unroll
+        for (int off = 16; off > 0; off >>= 1) acc.shfl_merge(0xffffffffu, off);
+        return (float)acc.acc;
+    };
+    const float S = row_sum(0);
+    const float rS = kd_row_reciprocal(S);
+    const bool keep = a.softmax != nullptr;
+    float4* ps = keep ? reinterpret_cast<float4*>(a.softmax + row * cols) + first : nullptr;
+    #pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        v[u] = div_by_row_known(v[u], S, rS, (in_window >> u) & 1u);
+        if (keep) __stcs(ps + 32 * u, v[u]);
+        epi(row, (first + 32 * u) * 4, v[u]);
+    }
+    const float S2 = row_sum(1);
+    const float tf = a.targets[row];
+    const int t = (int)tf;                                          // Float.toInt(): truncation
+    const bool ok = tf == tf && t >= 0 && t < cols;
+    if (ok) {
+        const int q = t >> 2, owner = q & 31, u_all = q >> 5, c = t & 3;
+        if ((u_all >> 3) != half) return;                           // the other warp of the pair holds the target column
+        const int u_t = u_all & 7;
+        float mine = 0.f;
+        #pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (u == u_t) mine = c == 0 ? v[u].x : c == 1 ? v[u].y : c == 2 ? v[u].z : v[u].w;
+        const float picked = __shfl_sync(0xffffffffu, mine, owner);
+        if (lane == 0) a.nll[row] = -log_f(jmin(jmax(__fdiv_rn(picked, S2), a.lo), a.hi));
+    } else if (half == 0 && lane == 0) {
+        *a.err = 1;
+        a.nll[row] = CUDART_NAN_F;
     }
 }
 

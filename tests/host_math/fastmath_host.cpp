@@ -101,6 +101,38 @@ int64_t kfh_div(int mode, int64_t n) {
     return bad;
 }
 
+// Division by a power of two as a multiplication by its reciprocal: every divisor kd_is_pow2_divisor accepts against n seeded
+// dividends over ALL bit patterns (zeros, subnormals, infinities, NaN included) plus the edges; returns the mismatches.
+// NaN results count as equal when both are NaN.
+int64_t kfh_div_pow2(int64_t n) {
+    int64_t bad = 0;
+    for (int e = -62; e <= 62; ++e) {
+        for (int sign = 0; sign < 2; ++sign) {
+            const float b = std::ldexp(sign ? -1.0f : 1.0f, e);
+            const bool ok = ktc::kd_is_pow2_divisor(b);
+            if (ok != (e >= -60 && e <= 60)) { ++bad; continue; }
+            if (!ok) continue;
+            const float r = ktc::kd_row_reciprocal(b);
+            #pragma omp parallel for schedule(static) reduction(+:bad)
+            for (int64_t i = 0; i < n; ++i) {
+                uint64_t z = 99 + (uint64_t)(i + 1) * 0x9E3779B97F4A7C15ull + (uint64_t)(e + 100) * 0xD6E8FEB86659FD93ull;
+                z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull; z = (z ^ (z >> 27)) * 0x94D049BB133111EBull; z ^= z >> 31;
+                uint32_t xb = (uint32_t)z;
+                if (i < 8) { const uint32_t edge[8] = {0u, 0x80000000u, 1u, 0x007fffffu, 0x00800000u, 0x7f7fffffu, 0x7f800000u, 0x7fc00000u}; xb = edge[i]; }
+                float x; std::memcpy(&x, &xb, 4);
+                const float got = x * r, want = x / b;
+                if (got != got && want != want) continue;
+                if (std::memcmp(&got, &want, 4) != 0) ++bad;
+            }
+        }
+    }
+    const float no[6] = {3.0f, 0.75f, 0.0f, 1.5f, 0x1p61f, 0x1p-61f};
+    for (float b : no) if (ktc::kd_is_pow2_divisor(b)) ++bad;
+    float inf = INFINITY, nan = NAN;
+    if (ktc::kd_is_pow2_divisor(inf) || ktc::kd_is_pow2_divisor(nan)) ++bad;
+    return bad;
+}
+
 // 1 where the fast form may be used for this pair (what the kernel tests), else 0
 int kfh_div_accepts(float x, float b) { return (ktc::kd_row_reciprocal(b) != 0.0f && ktc::kd_div_window(x) != 0u) ? 1 : 0; }
 
