@@ -109,6 +109,8 @@ internal object KtcNative {
     val lazyFull = handle("ktc_lazy_full", JAVA_INT, JAVA_INT, ADDRESS, JAVA_INT, JAVA_FLOAT, ADDRESS)
     val lazyAssignFill = handle("ktc_lazy_assign_fill", JAVA_INT, JAVA_LONG, JAVA_FLOAT, ADDRESS)
     val lazyAssignScatterConst = handle("ktc_lazy_assign_scatter_const", JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_FLOAT, ADDRESS)
+    // the forward of SoftmaxCrossEntropy, recorded: (logits cell, targets cell, lo, hi, &softmax cell, &nll cell); ENOTSUP: issue the calls
+    val lazySoftmaxXentForward = handle("ktc_lazy_softmax_xent_forward", JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_FLOAT, JAVA_FLOAT, ADDRESS, ADDRESS)
     val lazySum = handle("ktc_lazy_sum", JAVA_INT, JAVA_LONG, JAVA_INT, JAVA_INT, ADDRESS, JAVA_INT, ADDRESS)
     val lazyBuffer = handle("ktc_lazy_buffer", JAVA_INT, JAVA_LONG, ADDRESS)
     val lazyInfo = handle("ktc_lazy_info", JAVA_INT, JAVA_LONG, ADDRESS, ADDRESS, ADDRESS, ADDRESS)

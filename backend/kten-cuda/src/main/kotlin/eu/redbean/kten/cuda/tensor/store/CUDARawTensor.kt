@@ -21,6 +21,7 @@ import java.lang.foreign.Arena
 import java.lang.foreign.MemorySegment
 import java.lang.foreign.ValueLayout.JAVA_FLOAT
 import java.lang.foreign.ValueLayout.JAVA_INT
+import java.lang.foreign.ValueLayout.JAVA_LONG
 
 /**
  * Storage slot of one or more raw tensors: a reference-counted buffer handle of libkten_cuda.so (one owned reference),
@@ -106,6 +107,16 @@ class CUDARawTensor(
      */
     fun softmaxCrossEntropyForward(targets: CUDARawTensor, lo: Float, hi: Float): Pair<CUDARawTensor, CUDARawTensor>? {
         if (shape.size != 2) return null
+        if (ops.lazy) {
+            // recorded: the kernel runs when the loss or the gradient is needed and takes the recorded backward with it -- the
+            // saved softmax is then written only if a tensor still holds it (ktc_lazy_softmax_xent_forward)
+            val cells = Arena.ofConfined().use { arena ->
+                val sm = arena.allocate(JAVA_LONG); val nl = arena.allocate(JAVA_LONG)
+                val status = KtcNative.lazySoftmaxXentForward.invokeExact(cell(), targets.cell(), lo, hi, sm, nl) as Int
+                if (status == KtcNative.ENOTSUP) null else { check(status); sm.get(JAVA_LONG, 0) to nl.get(JAVA_LONG, 0) }
+            }
+            if (cells != null) return recorded(shape, cells.first) to recorded(listOf(shape[0], 1), cells.second)
+        }
         val softmax = ops.createRaw(shape)
         val nll = ops.createRaw(listOf(shape[0], 1))
         val status = KtcNative.softmaxXentForward.invokeExact(softmax.handle, nll.handle, handle, targets.handle,
