@@ -221,6 +221,21 @@ KTC_API int ktc_softmax_xent_forward_expr(ktc_buf softmax, ktc_buf nll, ktc_buf 
 KTC_API int ktc_upsample2d_nearest(ktc_buf out, ktc_buf in, int64_t P, int64_t W, int scale);
 KTC_API int ktc_upsample2d_nearest_grad(ktc_buf grad_in, ktc_buf grad_out, int64_t P, int64_t W, int scale);
 
+/* Spatial (2-D) pooling and its gradient (TensorOperations.spatialPooling, TensorOperations.kt:127; PoolingOperation.kt:
+ * 5-15; kten-jvm: JVMSpatialMaxPooling.kt:24-69, JVMSpatialAvgPooling.kt:23-88; 1-D pooling is the same with a trailing
+ * extent of 1).  planes = N * C; in and grad_in are [planes, H, W], out / indices / grad_out [planes, OH, OW].
+ * geom: {H, W, OH, OW, kernelH, kernelW, paddingH, paddingW, strideH, strideW, dilationH, dilationW}; the caller computes
+ * OH and OW as the reference does (on floats, ceil or floor, minus a last window that would start in the padding:
+ * JVMSpatialPoolingBase.kt:27-77).  Max: strict `>` from -infinity in window order, so NaN never wins and the first of
+ * equals stays; indices are positions inside the plane (y * W + x) as floats, -1 where no value won.  Average: a float sum
+ * in row-major order divided by the items in the window (include_padding: by the window clipped to the padded extent).
+ * Gradients: every input position adds the contributions of the outputs that reach it, in output order, in float --
+ * the additions the reference's sequential scatter performs, so results are bit-identical and run-to-run stable. */
+KTC_API int ktc_pool2d_max(ktc_buf out, ktc_buf indices, ktc_buf in, int64_t planes, const int* geom);
+KTC_API int ktc_pool2d_max_grad(ktc_buf grad_in, ktc_buf grad_out, ktc_buf indices, int64_t planes, const int* geom);
+KTC_API int ktc_pool2d_avg(ktc_buf out, ktc_buf in, int64_t planes, const int* geom, int include_padding);
+KTC_API int ktc_pool2d_avg_grad(ktc_buf grad_in, ktc_buf grad_out, int64_t planes, const int* geom, int include_padding);
+
 /* Full sum / mean that obtains no memory, for callers that must not allocate
  * while they run: loops whose free device memory is already committed to
  * another allocator, latency-bound sections that cannot take the device-wide

@@ -121,6 +121,10 @@ _PROTOTYPES = {
     "ktc_test_softmax_expr_compile": (i32, [C.POINTER(C.c_uint32), i32, i32, C.POINTER(C.c_int), C.POINTER(C.c_int), i32, i32, p_i64, C.POINTER(C.c_double)]),
     "ktc_upsample2d_nearest": (i32, [u64, u64, i64, i64, i32]),
     "ktc_upsample2d_nearest_grad": (i32, [u64, u64, i64, i64, i32]),
+    "ktc_pool2d_max": (i32, [u64, u64, u64, i64, C.POINTER(C.c_int)]),
+    "ktc_pool2d_max_grad": (i32, [u64, u64, u64, i64, C.POINTER(C.c_int)]),
+    "ktc_pool2d_avg": (i32, [u64, u64, i64, C.POINTER(C.c_int), i32]),
+    "ktc_pool2d_avg_grad": (i32, [u64, u64, i64, C.POINTER(C.c_int), i32]),
     "ktc_sum_to_shape": (i32, [u64, p_i64, i32, u64, p_i64, i32]),
     "ktc_scatter_axis": (i32, [u64, u64, u64, i64, i64, i64]),
     "ktc_comm_unique_id": (i32, [C.c_char_p]),

@@ -238,6 +238,38 @@ class Tensor:
         res = Upsample2DFunction(upsampleType, scale, self.ops)(self)
         return res if self.requiresGrad else res.noGrad()
 
+    def _pooled(self, kernel, stride, padding, dilation, options, one_d: bool):
+        function = Pooling2DOperation(self.ops, list(kernel), list(stride), list(padding), list(dilation), options)
+        if not one_d:
+            return function(self) if self.requiresGrad else function(self).noGrad()
+        if len(self.shape) != 3:
+            raise RuntimeError(f"1D pooling cannot be applied to tensor with shape: {self.shape} "
+                               "only tensors with 3 dimensions allowed (batch x channels x elements)")
+        inp = self.unsqueeze(3)
+        return (function(inp) if self.requiresGrad else function(inp).noGrad()).squeeze(3)
+
+    def maxPooling1d(self, kernel: int, stride: Optional[int] = None, padding: int = 0, dilation: int = 1, useCeil: bool = False):
+        """Tensor.maxPooling1d (functions/nn/TensorExtensions.kt:158-175): 2-D pooling of [N, C, L, 1]."""
+        from .nn import PoolingOptions, PoolingType
+        stride = kernel if stride is None else stride
+        return self._pooled((kernel, 1), (stride, 1), (padding, 0), (dilation, 1), PoolingOptions(PoolingType.MAX, useCeil), True)
+
+    def maxPooling2d(self, kernel, stride=None, padding=(0, 0), dilation=(1, 1), useCeil: bool = False):
+        """Tensor.maxPooling2d (TensorExtensions.kt:177-192)."""
+        from .nn import PoolingOptions, PoolingType
+        return self._pooled(kernel, kernel if stride is None else stride, padding, dilation, PoolingOptions(PoolingType.MAX, useCeil), False)
+
+    def avgPooling1d(self, kernel: int, stride: Optional[int] = None, padding: int = 0, useCeil: bool = False, includePadding: bool = False):
+        """Tensor.avgPooling1d (TensorExtensions.kt:194-215)."""
+        from .nn import PoolingOptions, PoolingType
+        stride = kernel if stride is None else stride
+        return self._pooled((kernel, 1), (stride, 1), (padding, 0), (1, 1), PoolingOptions(PoolingType.AVG, useCeil, includePadding), True)
+
+    def avgPooling2d(self, kernel, stride=None, padding=(0, 0), useCeil: bool = False, includePadding: bool = False):
+        """Tensor.avgPooling2d (TensorExtensions.kt:217-232)."""
+        from .nn import PoolingOptions, PoolingType
+        return self._pooled(kernel, kernel if stride is None else stride, padding, (1, 1), PoolingOptions(PoolingType.AVG, useCeil, includePadding), False)
+
     def meanVariance(self, axis: int, keepDimensions: bool = False, unbiased: bool = True):
         """AGTensor.meanVariance (AGTensor.kt:454-461): the mean keeps the axis, as there."""
         tensor = self.inplaceSafe()
@@ -1439,6 +1471,40 @@ class Upsample2DFunction(UnaryTensorFunction):       # functions/nn/Upsample2DFu
 
     def doBackward(self, gradient):
         return [self.op.calculateGrad(gradient, self.inputShape)]
+
+
+class Pooling2DOperation(UnaryTensorFunction):       # functions/nn/PoolingFunctions.kt:11-88
+    """2-D pooling through the backend's PoolingOperation; the input (and, for max pooling, the winners' positions) are
+    saved for backward."""
+    modifiesShape = True
+
+    def __init__(self, ops, kernelSize, stride, padding, dilation, poolingOptions):
+        super().__init__(ops)
+        self.kernelSize, self.stride, self.padding, self.dilation, self.poolingOptions = kernelSize, stride, padding, dilation, poolingOptions
+
+    def __call__(self, tensor: Tensor):
+        if len(tensor.shape) not in (3, 4):
+            raise ValueError(f"2D pooling requires input tensor with 3 or 4 dimensions, but got tensor with shape: {tensor.shape}")
+        from .nn import pooled_size
+        o = self.poolingOptions
+        hw = [pooled_size(tensor.shape[-2], self.dilation[0], self.kernelSize[0], self.padding[0], self.stride[0], o.useCeil),
+              pooled_size(tensor.shape[-1], self.dilation[1], self.kernelSize[1], self.padding[1], self.stride[1], o.useCeil)]
+        self.cachedShape = list(tensor.shape[:-2]) + hw
+        self.poolingOp = self.ops.spatialPooling(self.kernelSize, self.padding, self.stride, self.dilation, o)
+        return super().__call__(tensor)
+
+    def doForward(self, x):
+        out, indices = self.poolingOp.updateOutput(x)
+        if indices is not None:
+            self.saveForBackward(x, indices)
+        else:
+            self.saveForBackward(x)
+        self.output = out
+
+    def doBackward(self, gradient):
+        x = self.valuesSaved[0]
+        indices = self.valuesSaved[1] if len(self.valuesSaved) == 2 else None
+        return [self.poolingOp.calculateGradInput(x, gradient, indices)]
 
 
 def oneHot(ops, targets: Tensor, classes: int) -> Tensor:

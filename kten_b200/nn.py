@@ -12,7 +12,11 @@ bit-identical; the statistics themselves are sums (double accumulation, compared
 
 Upsampling is a broadcast copy ([R, 1, W, 1] -> [R, s, W, s]) and its gradient a sum back to the small shape; with an
 innermost extent of s (2, 3 ...) the general broadcast and reduction kernels fall to their element-wise forms, so the
-library has two small kernels for it (ktc_nn.cu) and the composition remains as the form a backend without them uses."""
+library has two small kernels for it (ktc_nn.cu) and the composition remains as the form a backend without them uses.
+
+Spatial pooling (TensorOperations.spatialPooling, TensorOperations.kt:127) is a window reduction with kernels of its own
+(ktc_pool.cu); this file holds the host part of kten-jvm's JVMSpatialPoolingBase: the shape checks, the output extents
+computed on floats, the result tensors."""
 from __future__ import annotations
 
 from typing import List, Optional, Sequence
@@ -214,3 +218,87 @@ class CUDAUpsample2DNearest:
             L.check(entry(res._buf(), gradOut._buf(), rows, W, s))
             return res
         return gradOut.view([rows, s, W, s]).sumToShape([rows, 1, W, 1]).view(list(inputShape))
+
+
+class PoolingType:                                      # PoolingOptions.kt:3-5
+    MAX, AVG = "MAX", "AVG"
+
+
+class PoolingOptions:                                   # PoolingOptions.kt:6-10
+    def __init__(self, type: str, useCeil: bool = False, includePadding: bool = False):
+        self.type, self.useCeil, self.includePadding = type, bool(useCeil), bool(includePadding)
+
+
+def pooled_size(extent: int, dilation: int, kernel: int, padding: int, stride: int, use_ceil: bool) -> int:
+    """PoolingOperation.calculateSizeOnFloats (PoolingOperation.kt:10-13) in float arithmetic, then ceil or floor."""
+    import numpy as np
+    f = np.float32
+    v = (f(extent) - (f(dilation) * (f(kernel) - f(1.0)) + f(1.0)) + f(2.0) * f(padding)) / f(stride) + f(1.0)
+    return int(np.ceil(v)) if use_ceil else int(np.floor(v))
+
+
+class CUDASpatialPooling:
+    """PoolingOperation over raw tensors of the CUDA backend (interface: PoolingOperation.kt:5-15; host logic:
+    JVMSpatialPoolingBase.kt:14-137; kernels: ktc_pool.cu).  [N, C, H, W] or [C, H, W] input; max pooling returns the
+    positions of the winners inside their planes as a second tensor, average pooling none."""
+
+    def __init__(self, kernel, padding, stride, dilation, options: PoolingOptions, ops):
+        self.kh, self.kw = int(kernel[0]), int(kernel[1])
+        self.ph, self.pw = int(padding[0]), int(padding[1])
+        self.sh, self.sw = int(stride[0]), int(stride[1])
+        self.is_max = options.type == PoolingType.MAX
+        self.dh, self.dw = (int(dilation[0]), int(dilation[1])) if self.is_max else (1, 1)      # AbstractJVMTensorOperations: AVG ignores it
+        self.useCeil, self.includePadding, self.ops = options.useCeil, options.includePadding, ops
+
+    def _geometry(self, input, gradOut=None, indices=None):
+        if self.kh <= 0 or self.kw <= 0:
+            raise ValueError("Kernel size should be greater than zero")
+        if self.sh <= 0 or self.sw <= 0:
+            raise ValueError("Stride should be greater than zero")
+        if self.dh <= 0 or self.dw <= 0:
+            raise ValueError("Dilation should be greater than zero")
+        if len(input.shape) not in (3, 4):
+            raise ValueError("Input must be 3D or 4D tensor")
+        if self.ph > self.kh // 2 or self.pw > self.kw // 2:
+            raise ValueError("Padding should be smaller than kernel size / 2, "
+                             f"but got kernel: ({self.kh}, {self.kw}) and padding: ({self.ph}, {self.pw})")
+        f = 1 if len(input.shape) == 4 else 0
+        planes_c, H, W = input.shape[f], input.shape[f + 1], input.shape[f + 2]
+        OH = pooled_size(H, self.dh, self.kh, self.ph, self.sh, self.useCeil)
+        OW = pooled_size(W, self.dw, self.kw, self.pw, self.sw, self.useCeil)
+        if self.ph > 0 or self.pw > 0:                      # a last window must start inside the plane or its left padding
+            if (OH - 1) * self.sh >= H + self.ph:
+                OH -= 1
+            if (OW - 1) * self.sw >= W + self.pw:
+                OW -= 1
+        if OH < 1 or OW < 1:
+            raise ValueError(f"Calculated output size: {planes_c} x {OH} x {OW} is too small. Input size: {planes_c} x {H} x {W}")
+        for t, what in ((gradOut, "gradient"), (indices, "indices")):
+            if t is not None and (t.shape[f] != planes_c or t.shape[f + 1] != OH or t.shape[f + 2] != OW):
+                raise ValueError(f"Invalid {what} shape, {what} must have shape with (F x H x W) = {planes_c} x {OH} x {OW}, "
+                                 f"but got {t.shape[f]} x {t.shape[f + 1]} x {t.shape[f + 2]}")
+        planes = planes_c * (input.shape[0] if f else 1)
+        import ctypes as C
+        geom = (C.c_int * 12)(H, W, OH, OW, self.kh, self.kw, self.ph, self.pw, self.sh, self.sw, self.dh, self.dw)
+        return planes, list(input.shape[:f + 1]) + [OH, OW], geom
+
+    def updateOutput(self, input):
+        from . import _lib as L
+        planes, out_shape, geom = self._geometry(input)
+        out = self.ops.createRaw(out_shape)
+        if self.is_max:
+            indices = self.ops.createRaw(out_shape)
+            L.check(self.ops.lib.ktc_pool2d_max(out._buf(), indices._buf(), input._buf(), planes, geom))
+            return out, indices
+        L.check(self.ops.lib.ktc_pool2d_avg(out._buf(), input._buf(), planes, geom, 1 if self.includePadding else 0))
+        return out, None
+
+    def calculateGradInput(self, input, gradOut, indices):
+        from . import _lib as L
+        planes, _, geom = self._geometry(input, gradOut, indices)
+        grad_in = self.ops.createRaw(list(input.shape))
+        if self.is_max:
+            L.check(self.ops.lib.ktc_pool2d_max_grad(grad_in._buf(), gradOut._buf(), indices._buf(), planes, geom))
+        else:
+            L.check(self.ops.lib.ktc_pool2d_avg_grad(grad_in._buf(), gradOut._buf(), planes, geom, 1 if self.includePadding else 0))
+        return grad_in

@@ -180,6 +180,11 @@ class CUDATensorOperations:
             raise ValueError(f"unknown upsample type {upsampleType}")
         return CUDAUpsample2DNearest(scale, self)
 
+    def spatialPooling(self, kernel, padding, stride, dilation, options):
+        """TensorOperations.spatialPooling (TensorOperations.kt:127): options is a PoolingOptions (kten_b200.nn)."""
+        from .nn import CUDASpatialPooling
+        return CUDASpatialPooling(kernel, padding, stride, dilation, options, self)
+
     def zeroOut(self, raw: CUDARawTensor) -> None:
         raw.inplaceFill(0.0)
 

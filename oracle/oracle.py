@@ -580,6 +580,9 @@ class OracleTensorOperations:
             raise ValueError(f"unknown upsample type {upsampleType}")
         return OracleUpsample2DNearest(scale, self)
 
+    def spatialPooling(self, kernel, padding, stride, dilation, options):
+        return OracleSpatialPooling(kernel, padding, stride, dilation, options, self)
+
     def concat(self, axis, inputs):
         """AbstractJVMTensorOperations.kt:106-120: every input is set into its range of the result."""
         SF = _SF()
@@ -724,3 +727,115 @@ class OracleUpsample2DNearest:
             for xo in range(s):
                 acc = (acc + g[:, :, xo, :, y]).astype(acc.dtype)
         return OracleRawTensor(list(inputShape), acc.astype(np.float32).reshape(-1), self.ops)
+
+
+class OracleSpatialPooling:
+    """JVMSpatialPoolingBase.kt:14-137 with JVMSpatialMaxPooling.kt:24-69 and JVMSpatialAvgPooling.kt:23-88: the loops of
+    the reference over one plane, vectorised over the planes (every plane sees the same sequence of float operations
+    as in the reference, so results are bit-identical to it).  `options` has the fields of PoolingOptions.kt:6-10."""
+
+    def __init__(self, kernel, padding, stride, dilation, options, ops):
+        self.kh, self.kw = int(kernel[0]), int(kernel[1])
+        self.ph, self.pw = int(padding[0]), int(padding[1])
+        self.sh, self.sw = int(stride[0]), int(stride[1])
+        self.is_max = options.type == "MAX"
+        self.dh, self.dw = (int(dilation[0]), int(dilation[1])) if self.is_max else (1, 1)
+        self.useCeil, self.includePadding, self.ops = bool(options.useCeil), bool(options.includePadding), ops
+
+    @staticmethod
+    def size_on_floats(extent, dilation, kernel, padding, stride):       # PoolingOperation.kt:10-13
+        f = np.float32
+        return (f(extent) - (f(dilation) * (f(kernel) - f(1.0)) + f(1.0)) + f(2.0) * f(padding)) / f(stride) + f(1.0)
+
+    def _geometry(self, input, gradOut=None, indices=None):
+        if self.kh <= 0 or self.kw <= 0:
+            raise ValueError("Kernel size should be greater than zero")
+        if self.sh <= 0 or self.sw <= 0:
+            raise ValueError("Stride should be greater than zero")
+        if self.dh <= 0 or self.dw <= 0:
+            raise ValueError("Dilation should be greater than zero")
+        if len(input.shape) not in (3, 4):
+            raise ValueError("Input must be 3D or 4D tensor")
+        if self.ph > self.kh // 2 or self.pw > self.kw // 2:
+            raise ValueError(f"Padding should be smaller than kernel size / 2, but got kernel: ({self.kh}, {self.kw}) and padding: ({self.ph}, {self.pw})")
+        f = 1 if len(input.shape) == 4 else 0
+        C_, H, W = input.shape[f], input.shape[f + 1], input.shape[f + 2]
+        rnd = np.ceil if self.useCeil else np.floor
+        OH = int(rnd(self.size_on_floats(H, self.dh, self.kh, self.ph, self.sh)))
+        OW = int(rnd(self.size_on_floats(W, self.dw, self.kw, self.pw, self.sw)))
+        if self.ph > 0 or self.pw > 0:
+            if (OH - 1) * self.sh >= H + self.ph:
+                OH -= 1
+            if (OW - 1) * self.sw >= W + self.pw:
+                OW -= 1
+        if OH < 1 or OW < 1:
+            raise ValueError(f"Calculated output size: {C_} x {OH} x {OW} is too small. Input size: {C_} x {H} x {W}")
+        for t, what in ((gradOut, "gradient"), (indices, "indices")):
+            if t is not None and (t.shape[f] != C_ or t.shape[f + 1] != OH or t.shape[f + 2] != OW):
+                raise ValueError(f"Invalid {what} shape, {what} must have shape with (F x H x W) = {C_} x {OH} x {OW}, "
+                                 f"but got {t.shape[f]} x {t.shape[f + 1]} x {t.shape[f + 2]}")
+        return C_ * (input.shape[0] if f else 1), H, W, OH, OW, list(input.shape[:f + 1]) + [OH, OW]
+
+    def _avg_window(self, i, j, H, W):
+        h0, w0 = i * self.sh - self.ph, j * self.sw - self.pw
+        h1, w1 = min(h0 + self.kh, H + self.ph), min(w0 + self.kw, W + self.pw)
+        pool = (h1 - h0) * (w1 - w0)
+        h0, w0, h1, w1 = max(h0, 0), max(w0, 0), min(h1, H), min(w1, W)
+        return h0, h1, w0, w1, (pool if self.includePadding else (h1 - h0) * (w1 - w0))
+
+    def updateOutput(self, input):
+        P, H, W, OH, OW, out_shape = self._geometry(input)
+        x = input.data.reshape(P, H, W)
+        if self.is_max:
+            best = np.full((P, OH, OW), -np.inf, np.float32)
+            at = np.full((P, OH, OW), -1.0, np.float32)
+            for i in range(OH):
+                for j in range(OW):
+                    h0, w0 = i * self.sh - self.ph, j * self.sw - self.pw
+                    h1, w1 = min(h0 + (self.kh - 1) * self.dh + 1, H), min(w0 + (self.kw - 1) * self.dw + 1, W)
+                    while h0 < 0:
+                        h0 += self.dh
+                    while w0 < 0:
+                        w0 += self.dw
+                    for y in range(h0, h1, self.dh):
+                        for xx in range(w0, w1, self.dw):
+                            v = x[:, y, xx]
+                            win = v > best[:, i, j]                       # strict: NaN never wins, the first of equals stays
+                            best[:, i, j] = np.where(win, v, best[:, i, j])
+                            at[:, i, j] = np.where(win, np.float32(y * W + xx), at[:, i, j])
+            return OracleRawTensor(out_shape, best.reshape(-1), self.ops), OracleRawTensor(out_shape, at.reshape(-1), self.ops)
+        out = np.empty((P, OH, OW), np.float32)
+        with np.errstate(divide="ignore", invalid="ignore"):
+            for i in range(OH):
+                for j in range(OW):
+                    h0, h1, w0, w1, items = self._avg_window(i, j, H, W)
+                    acc = np.zeros(P, np.float32)
+                    for y in range(h0, h1):
+                        for xx in range(w0, w1):
+                            acc = acc + x[:, y, xx]                       # float32 + float32
+                    out[:, i, j] = acc / np.float32(items)
+        return OracleRawTensor(out_shape, out.reshape(-1), self.ops), None
+
+    def calculateGradInput(self, input, gradOut, indices):
+        P, H, W, OH, OW, _ = self._geometry(input, gradOut, indices)
+        g = gradOut.data.reshape(P, OH, OW)
+        gin = np.zeros((P, H * W), np.float32)
+        planes = np.arange(P)
+        if self.is_max:
+            idx = indices.data.reshape(P, OH, OW).astype(np.int64)            # Float.toInt()
+            for i in range(OH):
+                for j in range(OW):
+                    k = idx[:, i, j]
+                    hit = k != -1
+                    gin[planes[hit], k[hit]] = gin[planes[hit], k[hit]] + g[hit, i, j]
+        else:
+            gin3 = gin.reshape(P, H, W)
+            with np.errstate(divide="ignore", invalid="ignore"):
+                for i in range(OH):
+                    for j in range(OW):
+                        h0, h1, w0, w1, items = self._avg_window(i, j, H, W)
+                        c = g[:, i, j] / np.float32(items)
+                        for y in range(h0, h1):
+                            for xx in range(w0, w1):
+                                gin3[:, y, xx] = gin3[:, y, xx] + c
+        return OracleRawTensor(list(input.shape), gin.reshape(-1), self.ops)

@@ -325,3 +325,21 @@ def upsample_nearest_property(ops, seed=7, tol=4e-6):        # block sums reach 
     assert np.array_equal(got_out, want_out)
     _close(got_grad, want_grad, tol)
     return got_out, got_grad
+
+
+def max_pooling_1d_golden(ops):
+    """should_calculate_max_pooling_for_1d_cases (kten-testing/.../nn/PoolingTestsBase.kt:13-42) on the reference's own
+    fixture (tests/golden/maxpool1d_k3_s2_p1_d2_on_2x3x10_ceil.json, made from its XML): result, sum of the result and the
+    input's gradient within the test's 1e-4."""
+    with open(os.path.join(HERE, "golden", "maxpool1d_k3_s2_p1_d2_on_2x3x10_ceil.json")) as fh:
+        case = json.load(fh)
+    t1 = AG.tensorOf(ops, np.array(case["t1"], np.float32), requiresGrad=True)
+    o = case["op"]
+    res = t1.maxPooling1d(kernel=o["kernel"], stride=o["stride"], padding=o["padding"], dilation=o["dilation"], useCeil=o["useCeil"])
+    total = res.sum()
+    total.backward()
+    got = res.toArray(), total.toArray(), t1.grad().toArray()
+    _close(got[0], np.array(case["res"], np.float32), case["tol"])
+    _close(got[1], np.array(case["sumRes"], np.float32), case["tol"])
+    _close(got[2], np.array(case["t1Grad"], np.float32), case["tol"])
+    return got
