@@ -685,8 +685,22 @@ def run_other_ops(ops, lib, L, D, steps):
         o = up.upsample(ux)
         up.calculateGrad(o, [256, 64, 64, 64]).storeReference
 
-    for name, fn, nbytes in (("batchNorm [256,64,128,128] axis 1, training forward + backward", bn_step, 9 * 4.0 * n),
-                             ("upsample2d nearest x2 of [256,64,64,64] + gradient", up_step, (0.25 + 1 + 1 + 0.25) * 4.0 * n)):
+    # spatial pooling of [256, 64, 128, 128] with its gradient (ktc_pool.cu).  Bytes: input read, result (and, for max, the
+    # winners' positions) written; gradOut (and the positions) read, gradIn written
+    from kten_b200.nn import PoolingOptions, PoolingType
+    pools = {"max 2x2 / 2": ops.spatialPooling((2, 2), (0, 0), (2, 2), (1, 1), PoolingOptions(PoolingType.MAX)),
+             "max 3x3 / 2 pad 1": ops.spatialPooling((3, 3), (1, 1), (2, 2), (1, 1), PoolingOptions(PoolingType.MAX)),
+             "avg 2x2 / 2": ops.spatialPooling((2, 2), (0, 0), (2, 2), (1, 1), PoolingOptions(PoolingType.AVG))}
+
+    def pool_step(op):
+        def step():
+            o, idx = op.updateOutput(bx)
+            op.calculateGradInput(bx, o, idx).storeReference
+        return step
+
+    pool_lines = [(f"spatialPooling {k} of [256,64,128,128] + gradient", pool_step(op), (3.0 if k.startswith("max") else 2.5) * 4.0 * n) for k, op in pools.items()]
+    for name, fn, nbytes in [("batchNorm [256,64,128,128] axis 1, training forward + backward", bn_step, 9 * 4.0 * n),
+                             ("upsample2d nearest x2 of [256,64,64,64] + gradient", up_step, (0.25 + 1 + 1 + 0.25) * 4.0 * n)] + pool_lines:
         for _ in range(3):
             with ops.garbageCollector():
                 fn()
@@ -1028,6 +1042,26 @@ def run_single_case(args):
         per, med, launches = timed_in_batches(ops, lib, L, xent_unscoped, args.reps)
         print(json.dumps({"case": name, "elements": rows * cols, "ms": per, "ms_median_batch": med, "gbs": 2 * 4.0 * rows * cols / per / 1e6,
                           "launches_per_step": launches, "device_mallocs_in_timed_region": timed_in_batches.last_device_mallocs}))
+        return 0
+    if name in ("x.maxpool", "x.maxpool3", "x.avgpool"):
+        # spatial pooling of [n / 2^20, 64, 128, 128] with its gradient
+        from kten_b200.nn import PoolingOptions, PoolingType
+        imgs = max(1, n >> 20)
+        shape, vol = [imgs, 64, 128, 128], imgs << 20
+        px = ops.createRaw(shape, D.normal(vol, 21, 0.0, 1.0))
+        op = {"x.maxpool": ops.spatialPooling((2, 2), (0, 0), (2, 2), (1, 1), PoolingOptions(PoolingType.MAX)),
+              "x.maxpool3": ops.spatialPooling((3, 3), (1, 1), (2, 2), (1, 1), PoolingOptions(PoolingType.MAX)),
+              "x.avgpool": ops.spatialPooling((2, 2), (0, 0), (2, 2), (1, 1), PoolingOptions(PoolingType.AVG))}[name]
+
+        def fn():
+            o, idx = op.updateOutput(px)
+            op.calculateGradInput(px, o, idx).storeReference
+        nbytes = (2.5 if name == "x.avgpool" else 3.0) * 4.0 * vol
+        for _ in range(3):
+            with ops.garbageCollector():
+                fn()
+        per, med, launches = timed_in_batches(ops, lib, L, fn, args.reps)
+        print(json.dumps({"case": name, "elements": vol, "ms": per, "ms_median_batch": med, "gbs": nbytes / per / 1e6, "launches_per_step": launches}))
         return 0
     if name in ("x.batchnorm", "x.upsample"):
         # batch norm (training forward + backward) of [n / 2^20, 64, 128, 128] along axis 1; upsampling by 2 with its gradient

@@ -5,7 +5,7 @@
 // A window reduction over [planes, H, W] with planes = N * C: every value is read a few times through L1 / L2 and every
 // result written once, so these are streaming kernels like the axis reductions, and they keep the reference's
 // arithmetic to the bit:
-//   * max forward: one thread per output; the window is walked in the reference's order (rows, then columns, both in
+//   * max forward: one thread per output (a CTA owns four output rows of a plane); the window is walked in the reference's order (rows, then columns, both in
 //     steps of the dilation) with its strict `>` from -infinity, so a NaN never wins, the first of equal values stays,
 //     and a window without a winner gives -infinity and index -1.  The index is the position inside the plane
 //     (y * W + x) as a float, as the reference stores it.
@@ -25,55 +25,76 @@ namespace ktc {
 namespace {
 
 struct PoolGeom { int H, W, OH, OW, kh, kw, ph, pw, sh, sw, dh, dw; };
+struct PoolLaunchArgs { unsigned grid; dim3 block; cudaStream_t stream; const float* p0; float* p1; float* p2; PoolGeom g; int flag; };
 
 __device__ __forceinline__ int ceil_div_pos(int a, int b) { return a <= 0 ? 0 : (a + b - 1) / b; }
 
-__global__ void __launch_bounds__(256) k_pool_max_forward(const float* __restrict__ in, float* __restrict__ out, float* __restrict__ idx,
-                                                          int64_t planes, const PoolGeom g) {
-    const int64_t per = (int64_t)g.OH * g.OW, total = planes * per;
-    for (int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t p = o / per;
-        const int r = (int)(o - p * per), i = r / g.OW, j = r - i * g.OW;
-        int h0 = i * g.sh - g.ph, w0 = j * g.sw - g.pw;
-        const int h1 = min(h0 + (g.kh - 1) * g.dh + 1, g.H), w1 = min(w0 + (g.kw - 1) * g.dw + 1, g.W);
-        while (h0 < 0) h0 += g.dh;
+// Work decomposition shared by the four kernels: a CTA of bx x by = 256 threads (bx: a power of two that covers a row's
+// items -- outputs for the forward kernels, groups of four input positions for the gradients -- up to 64) owns
+// by * kRowsPerThread consecutive rows of one plane; threadIdx.y picks the row, threadIdx.x strides over the row.  The
+// only division by a run-time value per CTA is plane = blockIdx / tiles.
+constexpr int kRowsPerThread = 4;
+struct Tile { int64_t plane; int row0; };
+__device__ __forceinline__ Tile tile_of(int rows_per_plane) {
+    const int per_cta = blockDim.y * kRowsPerThread;
+    const int tiles = (rows_per_plane + per_cta - 1) / per_cta;
+    Tile t;
+    t.plane = blockIdx.x / tiles;
+    t.row0 = (int)(blockIdx.x - t.plane * tiles) * per_cta + threadIdx.y;
+    return t;
+}
+#define KTC_POOL_ROWS(var, limit) for (int var = t.row0, r_ = 0; r_ < kRowsPerThread && var < (limit); ++r_, var += blockDim.y)
+
+__global__ void __launch_bounds__(256) k_pool_max_forward(const float* __restrict__ in, float* __restrict__ out, float* __restrict__ idx, const PoolGeom g) {
+    const Tile t = tile_of(g.OH);
+    const float* plane = in + t.plane * (int64_t)g.H * g.W;
+    KTC_POOL_ROWS(i, g.OH) {
+    int h0 = i * g.sh - g.ph;
+    const int h1 = min(h0 + (g.kh - 1) * g.dh + 1, g.H);
+    while (h0 < 0) h0 += g.dh;
+    const int64_t orow = (t.plane * g.OH + i) * (int64_t)g.OW;
+    for (int j = threadIdx.x; j < g.OW; j += blockDim.x) {
+        int w0 = j * g.sw - g.pw;
+        const int w1 = min(w0 + (g.kw - 1) * g.dw + 1, g.W);
         while (w0 < 0) w0 += g.dw;
-        const float* plane = in + p * (int64_t)g.H * g.W;
-        float best = -CUDART_INF_F, at = -1.0f;
+        float best = -CUDART_INF_F;
+        int at = -1;
         for (int y = h0; y < h1; y += g.dh)
             for (int x = w0; x < w1; x += g.dw) {
                 const float v = __ldg(plane + y * g.W + x);
-                if (v > best) { best = v; at = (float)(y * g.W + x); }
+                if (v > best) { best = v; at = y * g.W + x; }
             }
-        out[o] = best;
-        idx[o] = at;
+        __stcs(out + orow + j, best);
+        __stcs(idx + orow + j, (float)at);
+    }
     }
 }
 
 // the reference's window of output (i, j): [h0, h1) x [w0, w1) inside the plane, and the number of items it divides by
-struct AvgWindow { int h0, h1, w0, w1, items; };
-__device__ __forceinline__ AvgWindow avg_window(const PoolGeom& g, int i, int j, bool include_padding) {
-    AvgWindow a;
-    int h0 = i * g.sh - g.ph, w0 = j * g.sw - g.pw;
-    int h1 = min(h0 + g.kh, g.H + g.ph), w1 = min(w0 + g.kw, g.W + g.pw);
-    const int pool = (h1 - h0) * (w1 - w0);
-    a.h0 = max(h0, 0); a.w0 = max(w0, 0); a.h1 = min(h1, g.H); a.w1 = min(w1, g.W);
-    a.items = include_padding ? pool : (a.h1 - a.h0) * (a.w1 - a.w0);
-    return a;
+struct AvgSpan { int lo, hi, padded; };                      // clipped to the plane; `padded`: its length clipped to the padded extent only
+__device__ __forceinline__ AvgSpan avg_span(int o, int stride, int pad, int kernel, int extent) {
+    const int a = o * stride - pad, b = min(a + kernel, extent + pad);
+    AvgSpan s;
+    s.padded = b - a; s.lo = max(a, 0); s.hi = min(b, extent);
+    return s;
+}
+__device__ __forceinline__ int avg_items(const AvgSpan& h, const AvgSpan& w, bool include_padding) {
+    return include_padding ? h.padded * w.padded : (h.hi - h.lo) * (w.hi - w.lo);
 }
 
-__global__ void __launch_bounds__(256) k_pool_avg_forward(const float* __restrict__ in, float* __restrict__ out, int64_t planes, const PoolGeom g,
-                                                          int include_padding) {
-    const int64_t per = (int64_t)g.OH * g.OW, total = planes * per;
-    for (int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t p = o / per;
-        const int r = (int)(o - p * per), i = r / g.OW, j = r - i * g.OW;
-        const AvgWindow a = avg_window(g, i, j, include_padding != 0);
-        const float* plane = in + p * (int64_t)g.H * g.W;
+__global__ void __launch_bounds__(256) k_pool_avg_forward(const float* __restrict__ in, float* __restrict__ out, const PoolGeom g, int include_padding) {
+    const Tile t = tile_of(g.OH);
+    const float* plane = in + t.plane * (int64_t)g.H * g.W;
+    KTC_POOL_ROWS(i, g.OH) {
+    const AvgSpan h = avg_span(i, g.sh, g.ph, g.kh, g.H);
+    const int64_t orow = (t.plane * g.OH + i) * (int64_t)g.OW;
+    for (int j = threadIdx.x; j < g.OW; j += blockDim.x) {
+        const AvgSpan w = avg_span(j, g.sw, g.pw, g.kw, g.W);
         float sum = 0.f;
-        for (int y = a.h0; y < a.h1; ++y)
-            for (int x = a.w0; x < a.w1; ++x) sum = __fadd_rn(sum, __ldg(plane + y * g.W + x));
-        out[o] = __fdiv_rn(sum, (float)a.items);
+        for (int y = h.lo; y < h.hi; ++y)
+            for (int x = w.lo; x < w.hi; ++x) sum = __fadd_rn(sum, __ldg(plane + y * g.W + x));
+        __stcs(out + orow + j, __fdiv_rn(sum, (float)avg_items(h, w, include_padding != 0)));
+    }
     }
 }
 
@@ -83,46 +104,214 @@ __device__ __forceinline__ void reach(int y, int pad, int span, int stride, int 
     *hi = min((y + pad) / stride, n_out - 1);
 }
 
-__global__ void __launch_bounds__(256) k_pool_max_backward(const float* __restrict__ gout, const float* __restrict__ idx, float* __restrict__ gin,
-                                                           int64_t planes, const PoolGeom g) {
-    const int64_t per = (int64_t)g.H * g.W, total = planes * per;
+// Gradients: a thread owns four neighbouring input positions (y, x0 .. x0 + 3).  It walks the outputs that can reach any
+// of them in (i, j) order once and hands every contribution to the position it belongs to, so each position still sees
+// its own contributions in output order.
+__global__ void __launch_bounds__(256) k_pool_max_backward(const float* __restrict__ gout, const float* __restrict__ idx, float* __restrict__ gin, const PoolGeom g) {
+    const Tile t = tile_of(g.H);
     const int span_h = (g.kh - 1) * g.dh + 1, span_w = (g.kw - 1) * g.dw + 1;
-    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t p = e / per;
-        const int pos = (int)(e - p * per), y = pos / g.W, x = pos - y * g.W;
-        int i0, i1, j0, j1;
-        reach(y, g.ph, span_h, g.sh, g.OH, &i0, &i1);
-        reach(x, g.pw, span_w, g.sw, g.OW, &j0, &j1);
-        const int64_t base = p * (int64_t)g.OH * g.OW;
-        float acc = 0.f;
-        for (int i = i0; i <= i1; ++i)
+    const int64_t obase = t.plane * (int64_t)g.OH * g.OW;
+    const bool vec = (g.W & 3) == 0 && (reinterpret_cast<uintptr_t>(gin) & 15) == 0;
+    KTC_POOL_ROWS(y, g.H) {
+    int i0, i1;
+    reach(y, g.ph, span_h, g.sh, g.OH, &i0, &i1);
+    float* row = gin + (t.plane * g.H + y) * (int64_t)g.W;
+    for (int x0 = threadIdx.x * 4; x0 < g.W; x0 += 4 * blockDim.x) {
+        int j0, j1, unused;
+        reach(x0, g.pw, span_w, g.sw, g.OW, &j0, &unused);
+        reach(min(x0 + 3, g.W - 1), g.pw, span_w, g.sw, g.OW, &unused, &j1);
+        const int pos0 = y * g.W + x0;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int i = i0; i <= i1; ++i) {
+            const int64_t o = obase + (int64_t)i * g.OW;
             for (int j = j0; j <= j1; ++j) {
-                const int64_t o = base + (int64_t)i * g.OW + j;
-                if ((int)__ldg(idx + o) == pos) acc = __fadd_rn(acc, __ldg(gout + o));      // Float.toInt() of the saved index
+                const unsigned k = (unsigned)((int)__ldg(idx + o + j) - pos0);      // Float.toInt() of the saved position
+                if (k < 4u) {
+                    const float v = __ldg(gout + o + j);
+                    #pragma unroll
+                    for (int c = 0; c < 4; ++c) if (k == (unsigned)c) acc[c] = __fadd_rn(acc[c], v);
+                }
             }
-        gin[e] = acc;
+        }
+        if (vec) __stcs(reinterpret_cast<float4*>(row + x0), make_float4(acc[0], acc[1], acc[2], acc[3]));
+        else
+            for (int c = 0; c < 4 && x0 + c < g.W; ++c) row[x0 + c] = acc[c];
+    }
     }
 }
 
-__global__ void __launch_bounds__(256) k_pool_avg_backward(const float* __restrict__ gout, float* __restrict__ gin, int64_t planes, const PoolGeom g,
-                                                           int include_padding) {
-    const int64_t per = (int64_t)g.H * g.W, total = planes * per;
-    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t p = e / per;
-        const int pos = (int)(e - p * per), y = pos / g.W, x = pos - y * g.W;
-        int i0, i1, j0, j1;
-        reach(y, g.ph, g.kh, g.sh, g.OH, &i0, &i1);
-        reach(x, g.pw, g.kw, g.sw, g.OW, &j0, &j1);
-        const int64_t base = p * (int64_t)g.OH * g.OW;
-        float acc = 0.f;
-        for (int i = i0; i <= i1; ++i)
+__global__ void __launch_bounds__(256) k_pool_avg_backward(const float* __restrict__ gout, float* __restrict__ gin, const PoolGeom g, int include_padding) {
+    const Tile t = tile_of(g.H);
+    const int64_t obase = t.plane * (int64_t)g.OH * g.OW;
+    const bool vec = (g.W & 3) == 0 && (reinterpret_cast<uintptr_t>(gin) & 15) == 0;
+    KTC_POOL_ROWS(y, g.H) {
+    int i0, i1;
+    reach(y, g.ph, g.kh, g.sh, g.OH, &i0, &i1);
+    float* row = gin + (t.plane * g.H + y) * (int64_t)g.W;
+    for (int x0 = threadIdx.x * 4; x0 < g.W; x0 += 4 * blockDim.x) {
+        int j0, j1, unused;
+        reach(x0, g.pw, g.kw, g.sw, g.OW, &j0, &unused);
+        reach(min(x0 + 3, g.W - 1), g.pw, g.kw, g.sw, g.OW, &unused, &j1);
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int i = i0; i <= i1; ++i) {
+            const AvgSpan h = avg_span(i, g.sh, g.ph, g.kh, g.H);
+            if (y < h.lo || y >= h.hi) continue;
+            const int64_t o = obase + (int64_t)i * g.OW;
             for (int j = j0; j <= j1; ++j) {
-                const AvgWindow a = avg_window(g, i, j, include_padding != 0);
-                if (y >= a.h0 && y < a.h1 && x >= a.w0 && x < a.w1)
-                    acc = __fadd_rn(acc, __fdiv_rn(__ldg(gout + base + (int64_t)i * g.OW + j), (float)a.items));
+                const AvgSpan w = avg_span(j, g.sw, g.pw, g.kw, g.W);
+                const float c = __fdiv_rn(__ldg(gout + o + j), (float)avg_items(h, w, include_padding != 0));
+                #pragma unroll
+                for (int k = 0; k < 4; ++k) if (x0 + k >= w.lo && x0 + k < w.hi) acc[k] = __fadd_rn(acc[k], c);
             }
-        gin[e] = acc;
+        }
+        if (vec) __stcs(reinterpret_cast<float4*>(row + x0), make_float4(acc[0], acc[1], acc[2], acc[3]));
+        else
+            for (int c = 0; c < 4 && x0 + c < g.W; ++c) row[x0 + c] = acc[c];
     }
+    }
+}
+
+// ---- square windows of 2 or 3 with stride 1 or 2 and no dilation: the same arithmetic with compile-time trip counts ----
+// In the kernels above a window is a run-time loop whose every iteration loads a value and uses it at once: the loads of a
+// thread go out one at a time.  With K and S known the loops unroll, every load of a thread's four rows is issued before
+// the first comparison, and positions outside the plane take a neutral value instead of a branch: -infinity never wins
+// the strict `>`, and +0f added to a sum that started at +0f changes nothing.
+template <int K, int S, bool IS_MAX>
+__global__ void __launch_bounds__(256) k_pool_forward_ks(const float* __restrict__ in, float* __restrict__ out, float* __restrict__ idx, const PoolGeom g,
+                                                         int include_padding) {
+    const Tile t = tile_of(g.OH);
+    const float* plane = in + t.plane * (int64_t)g.H * g.W;
+    for (int j = threadIdx.x; j < g.OW; j += blockDim.x) {
+        const int xa = j * S - g.pw;
+        float v[kRowsPerThread][K][K];
+        #pragma unroll
+        for (int r = 0; r < kRowsPerThread; ++r) {
+            const int i = t.row0 + r * blockDim.y, ya = i * S - g.ph;
+            #pragma unroll
+            for (int a = 0; a < K; ++a) {
+                #pragma unroll
+                for (int b = 0; b < K; ++b) {
+                    const int y = ya + a, x = xa + b;
+                    const bool ok = i < g.OH && y >= 0 && y < g.H && x >= 0 && x < g.W;
+                    v[r][a][b] = ok ? __ldg(plane + y * g.W + x) : (IS_MAX ? -CUDART_INF_F : 0.f);
+                }
+            }
+        }
+        #pragma unroll
+        for (int r = 0; r < kRowsPerThread; ++r) {
+            const int i = t.row0 + r * blockDim.y, ya = i * S - g.ph;
+            if (i >= g.OH) break;
+            const int64_t o = (t.plane * g.OH + i) * (int64_t)g.OW + j;
+            if (IS_MAX) {
+                float best = -CUDART_INF_F;
+                int at = -1;
+                #pragma unroll
+                for (int a = 0; a < K; ++a) {
+                    #pragma unroll
+                    for (int b = 0; b < K; ++b)
+                        if (v[r][a][b] > best) { best = v[r][a][b]; at = (ya + a) * g.W + xa + b; }
+                }
+                __stcs(out + o, best);
+                __stcs(idx + o, (float)at);
+            } else {
+                const AvgSpan h = avg_span(i, S, g.ph, K, g.H), w = avg_span(j, S, g.pw, K, g.W);
+                float sum = 0.f;
+                #pragma unroll
+                for (int a = 0; a < K; ++a) {
+                    #pragma unroll
+                    for (int b = 0; b < K; ++b) sum = __fadd_rn(sum, v[r][a][b]);
+                }
+                __stcs(out + o, __fdiv_rn(sum, (float)avg_items(h, w, include_padding != 0)));
+            }
+        }
+    }
+}
+
+template <int K, int S, bool IS_MAX>
+__global__ void __launch_bounds__(256) k_pool_backward_ks(const float* __restrict__ gout, const float* __restrict__ idx, float* __restrict__ gin, const PoolGeom g,
+                                                          int include_padding) {
+    constexpr int NI = (K + S - 1) / S;                      // outputs that can reach one input row
+    constexpr int NJ = (K + 2) / S + 1;                      // ... four neighbouring input columns
+    const Tile t = tile_of(g.H);
+    const float* gp = gout + t.plane * (int64_t)g.OH * g.OW;      // offsets inside a plane fit 32 bits (read_geometry)
+    const float* ip = idx + t.plane * (int64_t)g.OH * g.OW;
+    float* plane_in = gin + t.plane * (int64_t)g.H * g.W;
+    const bool vec = (g.W & 3) == 0 && (reinterpret_cast<uintptr_t>(gin) & 15) == 0;
+    KTC_POOL_ROWS(y, g.H) {
+        int i0, i1;
+        reach(y, g.ph, K, S, g.OH, &i0, &i1);
+        float* row = plane_in + y * g.W;
+        for (int x0 = threadIdx.x * 4; x0 < g.W; x0 += 4 * blockDim.x) {
+            int j0, j1, unused;
+            reach(x0, g.pw, K, S, g.OW, &j0, &unused);
+            reach(min(x0 + 3, g.W - 1), g.pw, K, S, g.OW, &unused, &j1);
+            float go[NI][NJ], ix[NI][NJ];
+            #pragma unroll
+            for (int a = 0; a < NI; ++a) {
+                #pragma unroll
+                for (int b = 0; b < NJ; ++b) {
+                    const bool ok = i0 + a <= i1 && j0 + b <= j1;
+                    const int o = ok ? (i0 + a) * g.OW + j0 + b : 0;
+                    go[a][b] = __ldg(gp + o);
+                    ix[a][b] = IS_MAX ? __ldg(ip + o) : 0.f;
+                }
+            }
+            // positions are integers below 2^24 kept as floats: comparing the floats is comparing the positions
+            const float p0 = (float)(y * g.W + x0), p1 = p0 + 1.f, p2 = p0 + 2.f, p3 = p0 + 3.f;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            #pragma unroll
+            for (int a = 0; a < NI; ++a) {
+                #pragma unroll
+                for (int b = 0; b < NJ; ++b) {
+                    if (i0 + a > i1 || j0 + b > j1) continue;
+                    if (IS_MAX) {
+                        const float at = ix[a][b];
+                        if (at == p0) acc[0] = __fadd_rn(acc[0], go[a][b]);
+                        if (at == p1) acc[1] = __fadd_rn(acc[1], go[a][b]);
+                        if (at == p2) acc[2] = __fadd_rn(acc[2], go[a][b]);
+                        if (at == p3) acc[3] = __fadd_rn(acc[3], go[a][b]);
+                    } else {
+                        const AvgSpan h = avg_span(i0 + a, S, g.ph, K, g.H), w = avg_span(j0 + b, S, g.pw, K, g.W);
+                        if (y < h.lo || y >= h.hi) continue;
+                        const float c = __fdiv_rn(go[a][b], (float)avg_items(h, w, include_padding != 0));
+                        #pragma unroll
+                        for (int k = 0; k < 4; ++k) if (x0 + k >= w.lo && x0 + k < w.hi) acc[k] = __fadd_rn(acc[k], c);
+                    }
+                }
+            }
+            if (vec) __stcs(reinterpret_cast<float4*>(row + x0), make_float4(acc[0], acc[1], acc[2], acc[3]));
+            else
+                for (int c = 0; c < 4 && x0 + c < g.W; ++c) row[x0 + c] = acc[c];
+        }
+    }
+}
+
+// 0: no specialised kernel for this geometry; else K * 10 + S
+int fast_shape(const PoolGeom& g) {
+    if (g.kh != g.kw || g.sh != g.sw || g.dh != 1 || g.dw != 1 || !tune("pool_fast", 1)) return 0;
+    if ((g.kh == 2 || g.kh == 3) && (g.sh == 1 || g.sh == 2)) return g.kh * 10 + g.sh;
+    return 0;
+}
+
+template <bool IS_MAX>
+bool launch_fast_forward(int shape, const PoolLaunchArgs& a) {
+    switch (shape) {
+    case 22: k_pool_forward_ks<2, 2, IS_MAX><<<a.grid, a.block, 0, a.stream>>>(a.p0, a.p1, a.p2, a.g, a.flag); return true;
+    case 21: k_pool_forward_ks<2, 1, IS_MAX><<<a.grid, a.block, 0, a.stream>>>(a.p0, a.p1, a.p2, a.g, a.flag); return true;
+    case 32: k_pool_forward_ks<3, 2, IS_MAX><<<a.grid, a.block, 0, a.stream>>>(a.p0, a.p1, a.p2, a.g, a.flag); return true;
+    case 31: k_pool_forward_ks<3, 1, IS_MAX><<<a.grid, a.block, 0, a.stream>>>(a.p0, a.p1, a.p2, a.g, a.flag); return true;
+    }
+    return false;
+}
+template <bool IS_MAX>
+bool launch_fast_backward(int shape, const PoolLaunchArgs& a) {
+    switch (shape) {
+    case 22: k_pool_backward_ks<2, 2, IS_MAX><<<a.grid, a.block, 0, a.stream>>>(a.p0, a.p1, a.p2, a.g, a.flag); return true;
+    case 21: k_pool_backward_ks<2, 1, IS_MAX><<<a.grid, a.block, 0, a.stream>>>(a.p0, a.p1, a.p2, a.g, a.flag); return true;
+    case 32: k_pool_backward_ks<3, 2, IS_MAX><<<a.grid, a.block, 0, a.stream>>>(a.p0, a.p1, a.p2, a.g, a.flag); return true;
+    case 31: k_pool_backward_ks<3, 1, IS_MAX><<<a.grid, a.block, 0, a.stream>>>(a.p0, a.p1, a.p2, a.g, a.flag); return true;
+    }
+    return false;
 }
 
 int read_geometry(const char* what, const int* geom, PoolGeom* g) {
@@ -141,11 +330,17 @@ int read_geometry(const char* what, const int* geom, PoolGeom* g) {
     return KTC_OK;
 }
 
-int grid_for(Device* d, int64_t items) {
-    int64_t blocks = (items + 255) / 256;
-    const int64_t cap = (int64_t)d->sm_count * 32;
-    if (blocks > cap) blocks = cap;
-    return (int)(blocks < 1 ? 1 : blocks);
+// CTA shape for rows of `items` items and the grid for planes x rows; grid 0: more than a launch takes
+struct PoolLaunch { dim3 block; int64_t grid; };
+PoolLaunch launch_for(int64_t planes, int rows, int items) {
+    int bx = 8;
+    while (bx < 64 && bx < items) bx <<= 1;
+    PoolLaunch l;
+    l.block = dim3(bx, 256 / bx);
+    const int per_cta = (256 / bx) * kRowsPerThread;
+    const int64_t blocks = planes * ((rows + per_cta - 1) / per_cta);
+    l.grid = blocks > 0x7fffffffLL ? 0 : blocks;
+    return l;
 }
 
 int finish_pool(const char* what) {
@@ -194,7 +389,10 @@ extern "C" int ktc_pool2d_max(ktc_buf out, ktc_buf indices, ktc_buf in, int64_t 
     if (planes == 0) return KTC_OK;
     Device* d = device(bb[0].dev); if (!d) return KTC_ESTATE;
     KTC_TRY(use_device(d));
-    k_pool_max_forward<<<grid_for(d, planes * g.OH * g.OW), 256, 0, d->stream>>>(bb[0].ptr, bs[0].ptr, bs[1].ptr, planes, g);
+    const PoolLaunch pl = launch_for(planes, g.OH, g.OW); const int64_t grid = pl.grid;
+    if (!grid) return fail(KTC_ENOTSUP, "ktc_pool2d_max: tensor too large for one launch");
+    if (!launch_fast_forward<true>(fast_shape(g), PoolLaunchArgs{(unsigned)grid, pl.block, d->stream, bb[0].ptr, bs[0].ptr, bs[1].ptr, g, 0}))
+        k_pool_max_forward<<<(unsigned)grid, pl.block, 0, d->stream>>>(bb[0].ptr, bs[0].ptr, bs[1].ptr, g);
     return finish_pool("pool2d_max");
 }
 
@@ -208,7 +406,10 @@ extern "C" int ktc_pool2d_max_grad(ktc_buf grad_in, ktc_buf grad_out, ktc_buf in
     if (planes == 0) return KTC_OK;
     Device* d = device(bb[0].dev); if (!d) return KTC_ESTATE;
     KTC_TRY(use_device(d));
-    k_pool_max_backward<<<grid_for(d, planes * g.H * g.W), 256, 0, d->stream>>>(bs[0].ptr, bs[1].ptr, bb[0].ptr, planes, g);
+    const PoolLaunch pl = launch_for(planes, g.H, (g.W + 3) / 4); const int64_t grid = pl.grid;
+    if (!grid) return fail(KTC_ENOTSUP, "ktc_pool2d_max_grad: tensor too large for one launch");
+    if (!launch_fast_backward<true>(fast_shape(g), PoolLaunchArgs{(unsigned)grid, pl.block, d->stream, bs[0].ptr, bs[1].ptr, bb[0].ptr, g, 0}))
+        k_pool_max_backward<<<(unsigned)grid, pl.block, 0, d->stream>>>(bs[0].ptr, bs[1].ptr, bb[0].ptr, g);
     return finish_pool("pool2d_max_grad");
 }
 
@@ -223,7 +424,10 @@ extern "C" int ktc_pool2d_avg(ktc_buf out, ktc_buf in, int64_t planes, const int
     if (planes == 0) return KTC_OK;
     Device* d = device(bb[0].dev); if (!d) return KTC_ESTATE;
     KTC_TRY(use_device(d));
-    k_pool_avg_forward<<<grid_for(d, planes * g.OH * g.OW), 256, 0, d->stream>>>(bb[0].ptr, bs[0].ptr, planes, g, include_padding);
+    const PoolLaunch pl = launch_for(planes, g.OH, g.OW); const int64_t grid = pl.grid;
+    if (!grid) return fail(KTC_ENOTSUP, "ktc_pool2d_avg: tensor too large for one launch");
+    if (!launch_fast_forward<false>(fast_shape(g), PoolLaunchArgs{(unsigned)grid, pl.block, d->stream, bb[0].ptr, bs[0].ptr, nullptr, g, include_padding}))
+        k_pool_avg_forward<<<(unsigned)grid, pl.block, 0, d->stream>>>(bb[0].ptr, bs[0].ptr, g, include_padding);
     return finish_pool("pool2d_avg");
 }
 
@@ -236,6 +440,9 @@ extern "C" int ktc_pool2d_avg_grad(ktc_buf grad_in, ktc_buf grad_out, int64_t pl
     if (planes == 0) return KTC_OK;
     Device* d = device(bb[0].dev); if (!d) return KTC_ESTATE;
     KTC_TRY(use_device(d));
-    k_pool_avg_backward<<<grid_for(d, planes * g.H * g.W), 256, 0, d->stream>>>(bs[0].ptr, bb[0].ptr, planes, g, include_padding);
+    const PoolLaunch pl = launch_for(planes, g.H, (g.W + 3) / 4); const int64_t grid = pl.grid;
+    if (!grid) return fail(KTC_ENOTSUP, "ktc_pool2d_avg_grad: tensor too large for one launch");
+    if (!launch_fast_backward<false>(fast_shape(g), PoolLaunchArgs{(unsigned)grid, pl.block, d->stream, bs[0].ptr, nullptr, bb[0].ptr, g, include_padding}))
+        k_pool_avg_backward<<<(unsigned)grid, pl.block, 0, d->stream>>>(bs[0].ptr, bb[0].ptr, g, include_padding);
     return finish_pool("pool2d_avg_grad");
 }
