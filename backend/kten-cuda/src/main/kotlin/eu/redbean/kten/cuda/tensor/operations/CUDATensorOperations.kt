@@ -17,7 +17,9 @@ import eu.redbean.kten.api.tensor.operations.nn.UpsampleType
 import eu.redbean.kten.api.tensor.serialization.CommonSerializableTensorDescriptor
 import eu.redbean.kten.api.tensor.serialization.SerializableTensorData
 import eu.redbean.kten.api.tensor.store.AbstractRawTensor
+import eu.redbean.kten.api.tensor.operations.nn.PoolingType
 import eu.redbean.kten.cuda.tensor.operations.nn.CUDABatchNorm
+import eu.redbean.kten.cuda.tensor.operations.nn.CUDASpatialPooling
 import eu.redbean.kten.cuda.tensor.operations.nn.CUDAUpsample2DNearest
 import eu.redbean.kten.cuda.tensor.platform.KtcNative
 import eu.redbean.kten.cuda.tensor.platform.KtcNative.check
@@ -188,7 +190,8 @@ class CUDATensorOperations(override val platformKey: String, val device: Int) : 
     override fun volumetricConvolutionTranspose(kernel: List<Int>, padding: List<Int>, stride: List<Int>, dilation: List<Int>,
                                                 outputPadding: List<Int>): ConvolutionOperation<CUDARawTensor> = unsupported("volumetricConvolutionTranspose")
     override fun spatialPooling(kernel: List<Int>, padding: List<Int>, stride: List<Int>, dilation: List<Int>,
-                                options: PoolingOptions): PoolingOperation<CUDARawTensor> = unsupported("spatialPooling")
+                                options: PoolingOptions): PoolingOperation<CUDARawTensor> =
+        CUDASpatialPooling(kernel, padding, stride, if (options.type == PoolingType.MAX) dilation else listOf(1, 1), options, this)
     // reductions and broadcast maps: built from raw-tensor calls on the path's kernels (operations/nn/CUDANnOperations.kt)
     override fun batchNorm(axis: Int, momentum: Float, epsilon: Float, training: Boolean): BatchNormOperation<CUDARawTensor> =
         CUDABatchNorm(axis, momentum, epsilon, training, this)

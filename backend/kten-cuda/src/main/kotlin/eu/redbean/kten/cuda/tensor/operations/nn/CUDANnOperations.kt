@@ -137,3 +137,81 @@ class CUDAUpsample2DNearest(override val scale: Int, val ops: CUDATensorOperatio
         return gradIn
     }
 }
+
+/**
+ * Spatial pooling (TensorOperations.spatialPooling; interface: PoolingOperation.kt:5-15): the host part of kten-jvm's
+ * JVMSpatialPoolingBase.kt:14-137 -- shape checks, output extents on floats, result tensors -- over the library's window
+ * kernels (ktc_pool2d_*), which keep kten-jvm's arithmetic and order to the bit.  The mirror of kten_b200/nn.py.
+ * Not compiled: no JDK on this box.
+ */
+class CUDASpatialPooling(
+    kernel: List<Int>, padding: List<Int>, stride: List<Int>, dilation: List<Int>,
+    val options: eu.redbean.kten.api.tensor.operations.nn.PoolingOptions,
+    val ops: CUDATensorOperations
+) : eu.redbean.kten.api.tensor.operations.nn.PoolingOperation<CUDARawTensor> {
+
+    private val kh = kernel[0]; private val kw = kernel[1]
+    private val ph = padding[0]; private val pw = padding[1]
+    private val sh = stride[0]; private val sw = stride[1]
+    private val dh = dilation[0]; private val dw = dilation[1]
+    private val isMax = options.type == eu.redbean.kten.api.tensor.operations.nn.PoolingType.MAX
+
+    private class Geometry(val planes: Long, val outShape: List<Int>, val values: IntArray)
+
+    private fun pooled(extent: Int, dilation: Int, kernel: Int, padding: Int, stride: Int): Int {
+        val v = eu.redbean.kten.api.tensor.operations.nn.PoolingOperation.calculateSizeOnFloats(
+            extent.toFloat(), dilation.toFloat(), kernel.toFloat(), padding.toFloat(), stride.toFloat())
+        return if (options.useCeil) kotlin.math.ceil(v).toInt() else kotlin.math.floor(v).toInt()
+    }
+
+    private fun geometry(input: CUDARawTensor, gradOut: CUDARawTensor?, indices: CUDARawTensor?): Geometry {
+        if (kh <= 0 || kw <= 0) throw IllegalArgumentException("Kernel size should be greater than zero")
+        if (sh <= 0 || sw <= 0) throw IllegalArgumentException("Stride should be greater than zero")
+        if (dh <= 0 || dw <= 0) throw IllegalArgumentException("Dilation should be greater than zero")
+        if (input.dimensions !in listOf(3, 4)) throw IllegalArgumentException("Input must be 3D or 4D tensor")
+        if (ph > kh / 2 || pw > kw / 2)
+            throw IllegalArgumentException("Padding should be smaller than kernel size / 2, but got kernel: ($kh, $kw) and padding: ($ph, $pw)")
+        val f = if (input.dimensions == 4) 1 else 0
+        val c = input.shape[f]; val h = input.shape[f + 1]; val w = input.shape[f + 2]
+        var oh = pooled(h, dh, kh, ph, sh)
+        var ow = pooled(w, dw, kw, pw, sw)
+        if (ph > 0 || pw > 0) {                               // a last window must not start in the right / bottom padding
+            if ((oh - 1) * sh >= h + ph) oh--
+            if ((ow - 1) * sw >= w + pw) ow--
+        }
+        if (oh < 1 || ow < 1)
+            throw IllegalArgumentException("Calculated output size: $c x $oh x $ow is too small. Input size: $c x $h x $w")
+        for ((t, what) in listOf(gradOut to "gradient", indices to "indices")) {
+            if (t != null && (t.shape[f] != c || t.shape[f + 1] != oh || t.shape[f + 2] != ow))
+                throw IllegalArgumentException("Invalid $what shape, $what must have shape with (F x H x W) = $c x $oh x $ow, " +
+                        "but got ${t.shape[f]} x ${t.shape[f + 1]} x ${t.shape[f + 2]}")
+        }
+        val planes = c.toLong() * (if (f == 1) input.shape[0] else 1)
+        return Geometry(planes, input.shape.take(f + 1) + listOf(oh, ow), intArrayOf(h, w, oh, ow, kh, kw, ph, pw, sh, sw, dh, dw))
+    }
+
+    private fun <T> withGeom(g: Geometry, call: (java.lang.foreign.MemorySegment) -> T): T =
+        java.lang.foreign.Arena.ofConfined().use { arena -> call(arena.allocateFrom(java.lang.foreign.ValueLayout.JAVA_INT, *g.values)) }
+
+    override fun updateOutput(input: CUDARawTensor): eu.redbean.kten.api.tensor.operations.nn.PoolingResult<CUDARawTensor> {
+        val g = geometry(input, null, null)
+        val out = ops.createRaw(g.outShape)
+        if (isMax) {
+            val indices = ops.createRaw(g.outShape)
+            withGeom(g) { check(KtcNative.pool2dMax.invokeExact(out.handle, indices.handle, input.handle, g.planes, it) as Int) }
+            return eu.redbean.kten.api.tensor.operations.nn.PoolingResult(out, indices)
+        }
+        withGeom(g) { check(KtcNative.pool2dAvg.invokeExact(out.handle, input.handle, g.planes, it, if (options.includePadding) 1 else 0) as Int) }
+        return eu.redbean.kten.api.tensor.operations.nn.PoolingResult(out, null)
+    }
+
+    override fun calculateGradInput(input: CUDARawTensor, gradOut: CUDARawTensor, indices: CUDARawTensor?): CUDARawTensor {
+        val g = geometry(input, gradOut, indices)
+        val gradIn = ops.createRaw(input.shape)
+        if (isMax)
+            withGeom(g) { check(KtcNative.pool2dMaxGrad.invokeExact(gradIn.handle, gradOut.handle, indices!!.handle, g.planes, it) as Int) }
+        else
+            withGeom(g) { check(KtcNative.pool2dAvgGrad.invokeExact(gradIn.handle, gradOut.handle, g.planes, it, if (options.includePadding) 1 else 0) as Int) }
+        return gradIn
+    }
+}

@@ -92,6 +92,12 @@ internal object KtcNative {
     // nearest-neighbour upsampling and its gradient: (out, in, P, W, scale) with P = the product of all dimensions but the last
     val upsample2dNearest = handle("ktc_upsample2d_nearest", JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_INT)
     val upsample2dNearestGrad = handle("ktc_upsample2d_nearest_grad", JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_INT)
+    // spatial pooling: (out, indices, in, planes, geom), (grad_in, grad_out, indices, planes, geom), (out, in, planes, geom, include_padding),
+    // (grad_in, grad_out, planes, geom, include_padding); geom = {H, W, OH, OW, kH, kW, pH, pW, sH, sW, dH, dW} as twelve ints
+    val pool2dMax = handle("ktc_pool2d_max", JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, ADDRESS)
+    val pool2dMaxGrad = handle("ktc_pool2d_max_grad", JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, ADDRESS)
+    val pool2dAvg = handle("ktc_pool2d_avg", JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, ADDRESS, JAVA_INT)
+    val pool2dAvgGrad = handle("ktc_pool2d_avg_grad", JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, ADDRESS, JAVA_INT)
     const val ENOTSUP = -4
     // the deferred-expression recorder: elementwise calls and sums are recorded below the C ABI and run fused when a value is needed
     const val EXPR_SUM_ALL = 1; const val EXPR_SUM_ROWS = 2; const val EXPR_SUM_LAST = 4
