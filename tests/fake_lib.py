@@ -278,6 +278,45 @@ class FakeLib:
         self._get(out)[:n_out] = O.sum_to_shape(self._get(a)[:n_in].copy(), ins, outs)
         return 0
 
+    # ---- spatial pooling: the oracle's loops behind the library's entry points -------------------------------------------
+    def _pool(self, geom, is_max, include_padding=False):
+        H, W, OH, OW, kh, kw, ph, pw, sh, sw, dh, dw = (int(geom[i]) for i in range(12))
+        opt = type("Options", (), {"type": "MAX" if is_max else "AVG", "useCeil": False, "includePadding": bool(include_padding)})()
+        op = O.OracleSpatialPooling((kh, kw), (ph, pw), (sh, sw), (dh, dw), opt, None)
+        op._geometry = lambda inp, g=None, i=None: (inp.shape[0], H, W, OH, OW, [inp.shape[0], OH, OW])      # the extents are the caller's
+        return op, H, W, OH, OW
+
+    def _plane_tensor(self, h, planes, rows, cols):
+        return O.OracleRawTensor([planes, rows, cols], self._get(h)[:planes * rows * cols].copy(), None)
+
+    def ktc_pool2d_max(self, out, indices, inp, planes, geom):
+        self._note("pool2d_max")
+        op, H, W, OH, OW = self._pool(geom, True)
+        o, i = op.updateOutput(self._plane_tensor(inp, planes, H, W))
+        self._get(out)[:planes * OH * OW], self._get(indices)[:planes * OH * OW] = o.data, i.data
+        return 0
+
+    def ktc_pool2d_max_grad(self, grad_in, grad_out, indices, planes, geom):
+        self._note("pool2d_max_grad")
+        op, H, W, OH, OW = self._pool(geom, True)
+        x = O.OracleRawTensor([planes, H, W], np.zeros(planes * H * W, np.float32), None)
+        g = op.calculateGradInput(x, self._plane_tensor(grad_out, planes, OH, OW), self._plane_tensor(indices, planes, OH, OW))
+        self._get(grad_in)[:planes * H * W] = g.data
+        return 0
+
+    def ktc_pool2d_avg(self, out, inp, planes, geom, include_padding):
+        self._note("pool2d_avg")
+        op, H, W, OH, OW = self._pool(geom, False, include_padding)
+        self._get(out)[:planes * OH * OW] = op.updateOutput(self._plane_tensor(inp, planes, H, W))[0].data
+        return 0
+
+    def ktc_pool2d_avg_grad(self, grad_in, grad_out, planes, geom, include_padding):
+        self._note("pool2d_avg_grad")
+        op, H, W, OH, OW = self._pool(geom, False, include_padding)
+        x = O.OracleRawTensor([planes, H, W], np.zeros(planes * H * W, np.float32), None)
+        self._get(grad_in)[:planes * H * W] = op.calculateGradInput(x, self._plane_tensor(grad_out, planes, OH, OW), None).data
+        return 0
+
     def ktc_gather_axis(self, out, inp, in_shape, index, index_shape, ndim, axis):
         self._note("gather")
         ins, ixs = _ints(in_shape, ndim), _ints(index_shape, ndim)

@@ -7,6 +7,7 @@ import pytest
 from kten_b200 import autograd as AG
 from kten_b200.nn import PoolingOptions, PoolingType, pooled_size
 from oracle import oracle as O
+from tests.fake_lib import make_ops
 from tests.kten_cases import max_pooling_1d_golden
 
 ORACLE = O.OracleTensorOperations()
@@ -114,3 +115,36 @@ def test_output_extents_and_checks():
     t = AG.tensorOf(ORACLE, np.zeros((2, 8), np.float32))
     with pytest.raises(RuntimeError, match="1D pooling cannot be applied"):
         t.maxPooling1d(2)
+
+
+def test_the_backend_host_code_on_the_stand_in_library():
+    """The CUDA backend's own host part (kten_b200/nn.py: checks, output extents, result tensors; the autograd function) over
+    the stand-in library, whose pooling entry points run the oracle's loops on the extents they are given: the reference
+    fixture, both execution modes, and every geometry of the oracle tests against the oracle backend."""
+    for lazy in (False, True):
+        ops = make_ops()
+        ops.lazy = lazy
+        with ops.garbageCollector():
+            got = max_pooling_1d_golden(ops)
+            want = max_pooling_1d_golden(ORACLE)
+            assert all(np.array_equal(a, b) for a, b in zip(got, want))
+    rng = np.random.default_rng(8)
+    x = rng.normal(size=(2, 3, 11, 9)).astype(np.float32)
+    ops = make_ops()
+    with ops.garbageCollector():
+        for k, s, p, d, ceil in CONFIGS:
+            for kind in (PoolingType.MAX, PoolingType.AVG):
+                opt = PoolingOptions(kind, ceil, includePadding=(kind == PoolingType.AVG and ceil))
+                res = []
+                for backend in (ORACLE, ops):
+                    op = backend.spatialPooling(k, p, s, d, opt)
+                    raw = backend.createRaw(list(x.shape), x.reshape(-1))
+                    out, idx = op.updateOutput(raw)
+                    g = backend.createRaw(list(out.shape), np.arange(int(np.prod(out.shape)), dtype=np.float32))
+                    gin = op.calculateGradInput(raw, g, idx)
+                    res.append((list(out.shape), out.toArray(), gin.toArray()))
+                assert res[0][0] == res[1][0] and np.array_equal(res[0][1], res[1][1], equal_nan=True) and np.array_equal(res[0][2], res[1][2], equal_nan=True)
+        with pytest.raises(ValueError, match="Padding should be smaller"):
+            ops.spatialPooling((2, 2), (2, 2), (1, 1), (1, 1), PoolingOptions(PoolingType.MAX)).updateOutput(ops.createRaw([1, 2, 8, 8], np.zeros(128, np.float32)))
+        with pytest.raises(ValueError, match="too small"):
+            ops.spatialPooling((9, 9), (0, 0), (1, 1), (1, 1), PoolingOptions(PoolingType.AVG)).updateOutput(ops.createRaw([1, 2, 8, 8], np.zeros(128, np.float32)))
