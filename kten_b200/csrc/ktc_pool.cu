@@ -179,49 +179,55 @@ __global__ void __launch_bounds__(256) k_pool_avg_backward(const float* __restri
 template <int K, int S, bool IS_MAX>
 __global__ void __launch_bounds__(256) k_pool_forward_ks(const float* __restrict__ in, float* __restrict__ out, float* __restrict__ idx, const PoolGeom g,
                                                          int include_padding) {
+    constexpr int RT = K == 2 ? 4 : 2;                       // rows whose loads are issued together (9 values per row for K = 3)
     const Tile t = tile_of(g.OH);
     const float* plane = in + t.plane * (int64_t)g.H * g.W;
+    float* oplane = out + t.plane * (int64_t)g.OH * g.OW;
+    float* iplane = IS_MAX ? idx + t.plane * (int64_t)g.OH * g.OW : nullptr;
     for (int j = threadIdx.x; j < g.OW; j += blockDim.x) {
         const int xa = j * S - g.pw;
-        float v[kRowsPerThread][K][K];
-        #pragma unroll
-        for (int r = 0; r < kRowsPerThread; ++r) {
-            const int i = t.row0 + r * blockDim.y, ya = i * S - g.ph;
+        #pragma unroll 1
+        for (int rb = 0; rb < kRowsPerThread; rb += RT) {
+            float v[RT][K][K];
             #pragma unroll
-            for (int a = 0; a < K; ++a) {
+            for (int r = 0; r < RT; ++r) {
+                const int i = t.row0 + (rb + r) * blockDim.y, ya = i * S - g.ph;
                 #pragma unroll
-                for (int b = 0; b < K; ++b) {
-                    const int y = ya + a, x = xa + b;
-                    const bool ok = i < g.OH && y >= 0 && y < g.H && x >= 0 && x < g.W;
-                    v[r][a][b] = ok ? __ldg(plane + y * g.W + x) : (IS_MAX ? -CUDART_INF_F : 0.f);
+                for (int a = 0; a < K; ++a) {
+                    #pragma unroll
+                    for (int b = 0; b < K; ++b) {
+                        const int y = ya + a, x = xa + b;
+                        const bool ok = i < g.OH && y >= 0 && y < g.H && x >= 0 && x < g.W;
+                        v[r][a][b] = ok ? __ldg(plane + y * g.W + x) : (IS_MAX ? -CUDART_INF_F : 0.f);
+                    }
                 }
             }
-        }
-        #pragma unroll
-        for (int r = 0; r < kRowsPerThread; ++r) {
-            const int i = t.row0 + r * blockDim.y, ya = i * S - g.ph;
-            if (i >= g.OH) break;
-            const int64_t o = (t.plane * g.OH + i) * (int64_t)g.OW + j;
-            if (IS_MAX) {
-                float best = -CUDART_INF_F;
-                int at = -1;
-                #pragma unroll
-                for (int a = 0; a < K; ++a) {
+            #pragma unroll
+            for (int r = 0; r < RT; ++r) {
+                const int i = t.row0 + (rb + r) * blockDim.y, ya = i * S - g.ph;
+                if (i >= g.OH) break;
+                const int o = i * g.OW + j;
+                if (IS_MAX) {
+                    float best = -CUDART_INF_F;
+                    int at = -1;
                     #pragma unroll
-                    for (int b = 0; b < K; ++b)
-                        if (v[r][a][b] > best) { best = v[r][a][b]; at = (ya + a) * g.W + xa + b; }
-                }
-                __stcs(out + o, best);
-                __stcs(idx + o, (float)at);
-            } else {
-                const AvgSpan h = avg_span(i, S, g.ph, K, g.H), w = avg_span(j, S, g.pw, K, g.W);
-                float sum = 0.f;
-                #pragma unroll
-                for (int a = 0; a < K; ++a) {
+                    for (int a = 0; a < K; ++a) {
+                        #pragma unroll
+                        for (int b = 0; b < K; ++b)
+                            if (v[r][a][b] > best) { best = v[r][a][b]; at = (ya + a) * g.W + xa + b; }
+                    }
+                    __stcs(oplane + o, best);
+                    __stcs(iplane + o, (float)at);
+                } else {
+                    const AvgSpan h = avg_span(i, S, g.ph, K, g.H), w = avg_span(j, S, g.pw, K, g.W);
+                    float sum = 0.f;
                     #pragma unroll
-                    for (int b = 0; b < K; ++b) sum = __fadd_rn(sum, v[r][a][b]);
+                    for (int a = 0; a < K; ++a) {
+                        #pragma unroll
+                        for (int b = 0; b < K; ++b) sum = __fadd_rn(sum, v[r][a][b]);
+                    }
+                    __stcs(oplane + o, __fdiv_rn(sum, (float)avg_items(h, w, include_padding != 0)));
                 }
-                __stcs(out + o, __fdiv_rn(sum, (float)avg_items(h, w, include_padding != 0)));
             }
         }
     }
