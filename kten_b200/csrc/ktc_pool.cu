@@ -78,6 +78,12 @@ __device__ __forceinline__ AvgSpan avg_span(int o, int stride, int pad, int kern
     s.padded = b - a; s.lo = max(a, 0); s.hi = min(b, extent);
     return s;
 }
+// x / items in float: a power of two (the 2 x 2 and 4 x 4 windows) divides exactly as a multiplication by its reciprocal --
+// both are roundings of the same real number, subnormal quotients included
+__device__ __forceinline__ float div_items(float x, int items) {
+    if (items > 0 && (items & (items - 1)) == 0) return __fmul_rn(x, __int_as_float((96 + __clz(items)) << 23));      // 2^-(31 - clz)
+    return __fdiv_rn(x, (float)items);
+}
 __device__ __forceinline__ int avg_items(const AvgSpan& h, const AvgSpan& w, bool include_padding) {
     return include_padding ? h.padded * w.padded : (h.hi - h.lo) * (w.hi - w.lo);
 }
@@ -93,7 +99,7 @@ __global__ void __launch_bounds__(256) k_pool_avg_forward(const float* __restric
         float sum = 0.f;
         for (int y = h.lo; y < h.hi; ++y)
             for (int x = w.lo; x < w.hi; ++x) sum = __fadd_rn(sum, __ldg(plane + y * g.W + x));
-        __stcs(out + orow + j, __fdiv_rn(sum, (float)avg_items(h, w, include_padding != 0)));
+        __stcs(out + orow + j, div_items(sum, avg_items(h, w, include_padding != 0)));
     }
     }
 }
@@ -159,7 +165,7 @@ __global__ void __launch_bounds__(256) k_pool_avg_backward(const float* __restri
             const int64_t o = obase + (int64_t)i * g.OW;
             for (int j = j0; j <= j1; ++j) {
                 const AvgSpan w = avg_span(j, g.sw, g.pw, g.kw, g.W);
-                const float c = __fdiv_rn(__ldg(gout + o + j), (float)avg_items(h, w, include_padding != 0));
+                const float c = div_items(__ldg(gout + o + j), avg_items(h, w, include_padding != 0));
                 #pragma unroll
                 for (int k = 0; k < 4; ++k) if (x0 + k >= w.lo && x0 + k < w.hi) acc[k] = __fadd_rn(acc[k], c);
             }
@@ -226,7 +232,7 @@ __global__ void __launch_bounds__(256) k_pool_forward_ks(const float* __restrict
                         #pragma unroll
                         for (int b = 0; b < K; ++b) sum = __fadd_rn(sum, v[r][a][b]);
                     }
-                    __stcs(oplane + o, __fdiv_rn(sum, (float)avg_items(h, w, include_padding != 0)));
+                    __stcs(oplane + o, div_items(sum, avg_items(h, w, include_padding != 0)));
                 }
             }
         }
@@ -279,7 +285,7 @@ __global__ void __launch_bounds__(256) k_pool_backward_ks(const float* __restric
                     } else {
                         const AvgSpan h = avg_span(i0 + a, S, g.ph, K, g.H), w = avg_span(j0 + b, S, g.pw, K, g.W);
                         if (y < h.lo || y >= h.hi) continue;
-                        const float c = __fdiv_rn(go[a][b], (float)avg_items(h, w, include_padding != 0));
+                        const float c = div_items(go[a][b], avg_items(h, w, include_padding != 0));
                         #pragma unroll
                         for (int k = 0; k < 4; ++k) if (x0 + k >= w.lo && x0 + k < w.hi) acc[k] = __fadd_rn(acc[k], c);
                     }
