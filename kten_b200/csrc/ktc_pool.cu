@@ -249,14 +249,16 @@ __global__ void __launch_bounds__(256) k_pool_backward_ks(const float* __restric
     const float* ip = idx + t.plane * (int64_t)g.OH * g.OW;
     float* plane_in = gin + t.plane * (int64_t)g.H * g.W;
     const bool vec = (g.W & 3) == 0 && (reinterpret_cast<uintptr_t>(gin) & 15) == 0;
-    KTC_POOL_ROWS(y, g.H) {
-        int i0, i1;
-        reach(y, g.ph, K, S, g.OH, &i0, &i1);
-        float* row = plane_in + y * g.W;
-        for (int x0 = threadIdx.x * 4; x0 < g.W; x0 += 4 * blockDim.x) {
-            int j0, j1, unused;
-            reach(x0, g.pw, K, S, g.OW, &j0, &unused);
-            reach(min(x0 + 3, g.W - 1), g.pw, K, S, g.OW, &unused, &j1);
+    for (int x0 = threadIdx.x * 4; x0 < g.W; x0 += 4 * blockDim.x) {
+        int j0, j1, unused;                                  // the same for every row of the thread
+        reach(x0, g.pw, K, S, g.OW, &j0, &unused);
+        reach(min(x0 + 3, g.W - 1), g.pw, K, S, g.OW, &unused, &j1);
+        AvgSpan wsp[NJ];                                     // average: the column spans of the outputs in reach, also the same for every row
+        #pragma unroll
+        for (int b = 0; b < NJ; ++b) wsp[b] = avg_span(j0 + b, S, g.pw, K, g.W);
+        KTC_POOL_ROWS(y, g.H) {
+            int i0, i1;
+            reach(y, g.ph, K, S, g.OH, &i0, &i1);
             float go[NI][NJ], ix[NI][NJ];
             #pragma unroll
             for (int a = 0; a < NI; ++a) {
@@ -265,7 +267,8 @@ __global__ void __launch_bounds__(256) k_pool_backward_ks(const float* __restric
                     const bool ok = i0 + a <= i1 && j0 + b <= j1;
                     const int o = ok ? (i0 + a) * g.OW + j0 + b : 0;
                     go[a][b] = __ldg(gp + o);
-                    ix[a][b] = IS_MAX ? __ldg(ip + o) : 0.f;
+                    // max: an output outside the range takes a position no input has; average: it contributes through `ok` below
+                    ix[a][b] = IS_MAX ? (ok ? __ldg(ip + o) : -2.0f) : (ok ? 1.0f : 0.0f);
                 }
             }
             // positions are integers below 2^24 kept as floats: comparing the floats is comparing the positions
@@ -275,15 +278,16 @@ __global__ void __launch_bounds__(256) k_pool_backward_ks(const float* __restric
             for (int a = 0; a < NI; ++a) {
                 #pragma unroll
                 for (int b = 0; b < NJ; ++b) {
-                    if (i0 + a > i1 || j0 + b > j1) continue;
                     if (IS_MAX) {
-                        const float at = ix[a][b];
+                        const float at = ix[a][b];               // Float.toInt() of the saved position, compared as a float
                         if (at == p0) acc[0] = __fadd_rn(acc[0], go[a][b]);
                         if (at == p1) acc[1] = __fadd_rn(acc[1], go[a][b]);
                         if (at == p2) acc[2] = __fadd_rn(acc[2], go[a][b]);
                         if (at == p3) acc[3] = __fadd_rn(acc[3], go[a][b]);
                     } else {
-                        const AvgSpan h = avg_span(i0 + a, S, g.ph, K, g.H), w = avg_span(j0 + b, S, g.pw, K, g.W);
+                        if (ix[a][b] == 0.0f) continue;
+                        const AvgSpan h = avg_span(i0 + a, S, g.ph, K, g.H);
+                        const AvgSpan& w = wsp[b];
                         if (y < h.lo || y >= h.hi) continue;
                         const float c = div_items(go[a][b], avg_items(h, w, include_padding != 0));
                         #pragma unroll
@@ -291,6 +295,7 @@ __global__ void __launch_bounds__(256) k_pool_backward_ks(const float* __restric
                     }
                 }
             }
+            float* row = plane_in + y * g.W;
             if (vec) __stcs(reinterpret_cast<float4*>(row + x0), make_float4(acc[0], acc[1], acc[2], acc[3]));
             else
                 for (int c = 0; c < 4 && x0 + c < g.W; ++c) row[x0 + c] = acc[c];
