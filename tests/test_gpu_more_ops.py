@@ -452,3 +452,33 @@ def test_softmax_forward_with_an_epilogue_program_through_the_c_abi(cuda_ops, gc
     rc = lib.ktc_softmax_xent_forward_expr(0, nll.storeReference, logits.storeReference, bad_targets.storeReference, rows, cols, eps, hi,
                                            code_a, len(code), imm, 3, leaves, shapes, 3, 1, stores, 2)
     assert rc != 0
+
+
+@pytest.mark.parametrize("rows,cols", [(513, 2048), (300, 1024), (77, 132)])
+def test_recorded_softmax_forward_without_a_consumer(cuda_ops, gc_scope, rows, cols):
+    """Only the loss is asked for (no backward): the recorded forward runs on its own and, nothing holding the softmax,
+    does not write it (ktc_softmax_xent_forward with softmax = 0); held, the softmax is written by the same kernel.  The
+    per-row losses and the softmax carry the bits of the call-by-call run."""
+    eps = cuda_ops.epsilon
+    hi = float(np.float32(1.0) - np.float32(eps))
+    x = D.uniform(rows * cols, 231, -5.0, 5.0)
+    t = np.floor(D.uniform(rows, 232, 0.0, cols - 0.01)).astype(np.float32)
+    logits, targets = cuda_ops.createRaw([rows, cols], x), cuda_ops.createRaw([rows, 1], t)
+    want_sm, want_nll = logits.softmaxCrossEntropyForward(targets, eps, hi)
+    lib = cuda_ops.lib
+    cuda_ops.lazy = True
+    try:
+        sm, nll = logits.softmaxCrossEntropyForward(targets, eps, hi)
+        assert sm.isDeferred and nll.isDeferred
+        sm.release()
+        l0 = lib.ktc_launch_count()
+        got_nll = nll.toArray()
+        assert lib.ktc_launch_count() - l0 == 1
+        sm2, nll2 = logits.softmaxCrossEntropyForward(targets, eps, hi)
+        got_sm = sm2.toArray()                                       # asked for: written, and the nll with it
+        l0 = lib.ktc_launch_count()
+        got_nll2 = nll2.toArray()
+        assert lib.ktc_launch_count() == l0
+    finally:
+        cuda_ops.lazy = False
+    assert same_bits(got_nll, want_nll.toArray()) and same_bits(got_nll2, want_nll.toArray()) and same_bits(got_sm, want_sm.toArray())
