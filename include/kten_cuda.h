@@ -216,8 +216,8 @@ KTC_API int ktc_softmax_xent_forward_expr(ktc_buf softmax, ktc_buf nll, ktc_buf 
 /* Nearest-neighbour upsampling of the last two dimensions by `scale` and its gradient (TensorOperations.upsample,
  * TensorOperations.kt:131; Upsample2DOperation.kt:5-44; kten-jvm: JVMUpsample2DNearest.kt:14-77).  P is the product of
  * all dimensions but the last (N * C * H): in [P, W] -> out [P, scale, W * scale]; grad_out [P, scale, W * scale] ->
- * grad_in [P, W], every position the sum of its scale x scale block (double accumulation in the reference's loop
- * order, one rounding). */
+ * grad_in [P, W], every position the sum of its scale x scale block, added in float from 0f in the reference's loop
+ * order (JVMUpsample2DNearest.kt:61-68): bit-identical to kten-jvm. */
 KTC_API int ktc_upsample2d_nearest(ktc_buf out, ktc_buf in, int64_t P, int64_t W, int scale);
 KTC_API int ktc_upsample2d_nearest_grad(ktc_buf grad_in, ktc_buf grad_out, int64_t P, int64_t W, int scale);
 

@@ -5,9 +5,9 @@
 // every input row becomes s identical output rows in which every value is repeated s times.  Forward: a thread builds
 // one float4 of the expanded row from the (at most four) input values under it and stores it to the s output rows --
 // the input is read once, through L1, and the output, s * s times as large, is written once with 128-bit stores.
-// Gradient: an input position receives the sum of its s x s block, added in the reference's order (column offset in
-// the outer loop, row offset in the inner one, JVMUpsample2DNearest.kt:61-68) in double and rounded once, which is the
-// exact-sum convention of this library's reductions; a thread produces four neighbouring positions from s rows of
+// Gradient: an input position receives the sum of its s x s block, added in float from 0f in the reference's order (column
+// offset in the outer loop, row offset in the inner one, JVMUpsample2DNearest.kt:61-68): the reference's own additions, so
+// the result is bit-identical to kten-jvm's; a thread produces four neighbouring positions from s rows of
 // 4 * s contiguous floats (128-bit loads for scales 2 to 4).  Shapes whose rows do not split into float4 take one-element-per-thread forms of the same loops.
 #include "ktc_internal.hpp"
 
@@ -58,26 +58,26 @@ __global__ void __launch_bounds__(256) k_upsample_nearest_grad(const float* __re
                     v[x][4 * j] = t.x; v[x][4 * j + 1] = t.y; v[x][4 * j + 2] = t.z; v[x][4 * j + 3] = t.w;
                 }
             }
-            double acc[4] = {0.0, 0.0, 0.0, 0.0};
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
             #pragma unroll
             for (int y = 0; y < S; ++y) {                                 // column offset: the reference's outer loop
                 #pragma unroll
                 for (int x = 0; x < S; ++x) {                             // row offset
                     #pragma unroll
-                    for (int k = 0; k < 4; ++k) acc[k] += (double)v[x][k * S + y];
+                    for (int k = 0; k < 4; ++k) acc[k] = __fadd_rn(acc[k], v[x][k * S + y]);
                 }
             }
-            __stcs(reinterpret_cast<float4*>(gin + p * W + w), make_float4((float)acc[0], (float)acc[1], (float)acc[2], (float)acc[3]));
+            __stcs(reinterpret_cast<float4*>(gin + p * W + w), make_float4(acc[0], acc[1], acc[2], acc[3]));
         }
     } else {
         const int64_t total = P * W;
         for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
             const int64_t p = i / W, w = i - p * W;
             const float* base = gout + p * s * OW + w * s;
-            double acc = 0.0;
+            float acc = 0.f;
             for (int y = 0; y < s; ++y)
-                for (int x = 0; x < s; ++x) acc += (double)__ldg(base + x * OW + y);
-            gin[i] = (float)acc;
+                for (int x = 0; x < s; ++x) acc = __fadd_rn(acc, __ldg(base + x * OW + y));
+            gin[i] = acc;
         }
     }
 }

@@ -103,3 +103,7 @@ def test_upsample_matches_the_oracle(ops, shape, scale):
     ga, g0 = up.calculateGrad(ops.createRaw(a.shape, g.reshape(-1)), shape), upo.calculateGrad(ORACLE.createRaw(a.shape, g.reshape(-1)), shape)
     assert ga.shape == g0.shape == shape
     assert np.allclose(ga.toArray().reshape(-1), g0.toArray().reshape(-1), atol=1e-5)
+    # the library's kernel adds the block in kten-jvm's order in float: the bits of the oracle in its kten-jvm-faithful mode
+    faithful = O.OracleTensorOperations(mode=0)
+    gf = faithful.upsample("NEAREST", scale).calculateGrad(faithful.createRaw(a.shape, g.reshape(-1)), shape)
+    assert np.array_equal(ga.toArray().reshape(-1).view(np.uint32), gf.toArray().reshape(-1).view(np.uint32))
