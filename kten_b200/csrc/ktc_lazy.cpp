@@ -28,7 +28,11 @@
 //     buffer nobody else holds makes the cell pending (its node reads the old buffer);
 //   * compiled programs are cached by the structure of the expression DAG and re-bound to the
 //     step's fresh nodes, so a training step that rebuilds the same graph pays for ordering and
-//     register allocation once.
+//     register allocation once;
+//   * the forward of SoftmaxCrossEntropy can be recorded too (ktc_lazy_softmax_xent_forward): its two
+//     results stay pending, and an elementwise expression of the softmax's shape built on it -- the
+//     function's backward -- is evaluated inside the forward's own kernel, which then writes the
+//     softmax only if something else still wants it.
 // Whatever ktc_expr_eval declines (KTC_ENOTSUP) runs as the library's separate calls.
 //
 // The file is plain C++ and reaches the rest of the library only through a table of the C ABI's
