@@ -1019,7 +1019,7 @@ def run_single_case(args):
     if name in ("x.softmax_eager", "x.softmax_deferred"):
         # SoftmaxCrossEntropy forward + backward on [n / 2048, 2048] logits through the autograd caller
         from kten_b200 import autograd as AG
-        cols = 2048
+        cols = args.cols
         rows = max(1, n // cols)
         logits = AG.Variable(ops, ops.createRaw([rows, cols], D.uniform(rows * cols, 11, 0.1, 2.0)))
         targets = AG.NoGradVariable(ops, ops.createRaw([rows], np.floor(D.uniform(rows, 15, 0.0, cols - 0.01)).astype(np.float32)))
@@ -1208,6 +1208,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="kten_b200", choices=["kten_b200", "reference"])
+    ap.add_argument("--cols", type=int, default=2048, help="row length of the x.softmax_* cases (classes)")
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--cpu-sample-log2", type=int, default=None, help="log2 of the CPU sample size per operand (default 26, for cpu_baseline and for --impl reference alike)")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")

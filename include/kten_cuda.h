@@ -194,7 +194,7 @@ KTC_API int ktc_sum_to_shape(ktc_buf out, const int64_t* old_shape, int old_ndim
  * `nll` [rows]; the mean over the rows is ktc_reduce_all(KTC_MEAN) on nll.  Every operation is the reference's, in its
  * order, and the two row sums accumulate exactly as ktc_reduce_axis does, so both outputs carry the bits of the
  * eleven separate calls.  targets [rows]: class indices as floats (truncated like Float.toInt); an index outside
- * [0, cols) is recorded like an invalid gather index and gives a NaN row.  KTC_ENOTSUP (cols > 2048 or <= 64, cols not
+ * [0, cols) is recorded like an invalid gather index and gives a NaN row.  KTC_ENOTSUP (cols > 12288 or <= 64, cols not
  * a multiple of 4, unaligned rows): issue the separate calls. */
 KTC_API int ktc_softmax_xent_forward(ktc_buf softmax, ktc_buf nll, ktc_buf logits, ktc_buf targets, int64_t rows, int64_t cols, float lo, float hi);
 

@@ -591,7 +591,7 @@ extern "C" int ktc_softmax_xent_forward_expr(ktc_buf softmax, ktc_buf nll, ktc_b
     const int64_t total = rows * cols;
     if (bl.n < total || (softmax && bs.n < total) || bn.n < rows || bt.n < rows) return fail(KTC_EINVAL, "%s: a buffer is too small for [%lld, %lld]", me, (long long)rows, (long long)cols);
     if (softmax && bs.ptr == bl.ptr) return fail(KTC_EINVAL, "%s: softmax aliases logits", me);
-    if (cols > kSxMaxVec * 128 || cols <= tune("reduce_rows_small_max", 64) || (cols & 3) || !aligned16(bl.ptr) || (softmax && !aligned16(bs.ptr)))
+    if (!softmax_row_length_ok(cols) || !aligned16(bl.ptr) || (softmax && !aligned16(bs.ptr)))
         return fail(KTC_ENOTSUP, "%s: rows of %lld columns are not handled in one pass", me, (long long)cols);
     if (rows == 0) return KTC_OK;
     ExprArgs a{};

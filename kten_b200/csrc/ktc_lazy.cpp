@@ -1536,7 +1536,7 @@ KTC_API int ktc_lazy_softmax_xent_forward(ktc_lazy_cell logits, ktc_lazy_cell ta
     if (lg->shape.nd != 2) return fail(KTC_EINVAL, "ktc_lazy_softmax_xent_forward: logits of %d dimensions", lg->shape.nd);
     const int64_t rows = lg->shape.d[0], cols = lg->shape.d[1];
     if (tg->shape.volume() != rows) return fail(KTC_EINVAL, "ktc_lazy_softmax_xent_forward: %lld targets for %lld rows", (long long)tg->shape.volume(), (long long)rows);
-    if (rows < 1 || cols <= 64 || cols > 2048 || (cols & 3) || strip(lg)->shape.volume() != rows * cols || strip(tg)->shape.volume() != rows)
+    if (rows < 1 || cols <= 64 || cols > 12288 || (cols & 3) || strip(lg)->shape.volume() != rows * cols || strip(tg)->shape.volume() != rows)
         return fail(KTC_ENOTSUP, "ktc_lazy_softmax_xent_forward: [%lld, %lld] logits are not handled in one pass", (long long)rows, (long long)cols);
     node_ref(lg); node_ref(tg);
     ktc_buf hl = 0, ht = 0;

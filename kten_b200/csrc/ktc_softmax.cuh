@@ -219,4 +219,94 @@ __device__ __forceinline__ void sx_rows_pair(const SxArgs& a, Epi& epi) {
     }
 }
 
+// Rows of more than 2048 columns (up to kSxMaxColsCta): ONE CTA per row, one warp for every 1024 columns (up to twelve),
+// eight vectors per lane.  ktc_reduce_axis(SUM) gives such a row to a single warp (up to 12288 columns with its default
+// segment length): lane l adds its vectors l + 32 u in runs of eight -- float runs, each folded into the lane's double in
+// order, the remainder as a last shorter run -- and the lanes are combined by the xor-shuffle tree.  Here warp w owns
+// u in [8 w, 8 w + 8), i.e. run w of every lane; the run sums go through shared memory and every warp folds all of its
+// lane's runs in order (a run beyond the row is 0f: adding it changes nothing) and then walks the tree: the same
+// operations in the same order, so the same bits.  The maximum is associative.  This is sx_rows_pair for any number of
+// warps, with the CTA's barrier in place of the pair's.
+constexpr int kSxMaxColsCta = 12288;
+constexpr int kSxMaxWarpsCta = kSxMaxColsCta / 1024;
+__host__ __device__ inline int sx_cta_warps(int cols) { return (cols + 1023) / 1024; }
+template <class Epi>
+__device__ __forceinline__ void sx_rows_cta(const SxArgs& a, Epi& epi) {
+    __shared__ float sh_max[kSxMaxWarpsCta];
+    __shared__ float sh_run[2][kSxMaxWarpsCta][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const int64_t row = blockIdx.x;                                 // grid == rows
+    epi.begin(row);
+    const int cols = a.cols;
+    const int q1 = cols >> 2;
+    const int n_row = q1 > lane ? (q1 - lane + 31) >> 5 : 0;        // this lane's vectors in the one-warp form
+    const int n_l = min(max(n_row - 8 * warp, 0), 8);              // ... of which this warp holds [8 warp, 8 warp + n_l)
+    const int first = lane + 256 * warp;                           // float4 index of the first
+    const float4* px = reinterpret_cast<const float4*>(a.logits + row * cols) + first;
+    float4 v[8];
+    #pragma unroll
+    for (int u = 0; u < 8; ++u) if (u < n_l) v[u] = __ldcs(px + 32 * u);
+    ExtAcc<true> mx; mx.init();
+    #pragma unroll
+    for (int u = 0; u < 8; ++u) if (u < n_l) mx.add4(v[u], 0);
+    #pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mx.shfl_merge(0xffffffffu, off);
+    if (lane == 0) sh_max[warp] = mx.v;
+    __syncthreads();
+    float m = sh_max[0];
+    for (int w = 1; w < n_warps; ++w) m = max_nan(m, sh_max[w]);
+    unsigned in_window = 0u;
+    #pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        if (u < n_l) {
+            const float4 s = make_float4(__fsub_rn(v[u].x, m), __fsub_rn(v[u].y, m), __fsub_rn(v[u].z, m), __fsub_rn(v[u].w, m));
+            if (s.x >= kSxWindowArg && s.y >= kSxWindowArg && s.z >= kSxWindowArg && s.w >= kSxWindowArg) in_window |= 1u << u;
+            v[u] = apply1(UnOp<KTC_EXP>(), s);
+        }
+    }
+    auto row_sum = [&](int which) -> float {
+        SumAcc acc; acc.init();
+        acc.begin();
+        #pragma unroll
+        for (int u = 0; u < 8; ++u) if (u < n_l) acc.add4(v[u], 0);
+        sh_run[which][warp][lane] = acc.run;
+        __syncthreads();
+        double d = 0.0;
+        for (int r = 0; r < n_warps; ++r) d += (double)sh_run[which][r][lane];
+        #pragma unroll
+        for (int off = 16; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+        return (float)d;
+    };
+    const float S = row_sum(0);
+    const float rS = kd_row_reciprocal(S);
+    const bool keep = a.softmax != nullptr;
+    float4* ps = keep ? reinterpret_cast<float4*>(a.softmax + row * cols) + first : nullptr;
+    #pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        if (u < n_l) {
+            v[u] = div_by_row_known(v[u], S, rS, (in_window >> u) & 1u);
+            if (keep) __stcs(ps + 32 * u, v[u]);
+            epi(row, (first + 32 * u) * 4, v[u]);
+        }
+    }
+    const float S2 = row_sum(1);
+    const float tf = a.targets[row];
+    const int t = (int)tf;                                          // Float.toInt(): truncation
+    const bool ok = tf == tf && t >= 0 && t < cols;
+    if (ok) {
+        const int q = t >> 2, owner = q & 31, u_all = q >> 5, c = t & 3;
+        if ((u_all >> 3) != warp) return;                           // another warp holds the target column
+        const int u_t = u_all & 7;
+        float mine = 0.f;
+        #pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (u == u_t) mine = c == 0 ? v[u].x : c == 1 ? v[u].y : c == 2 ? v[u].z : v[u].w;
+        const float picked = __shfl_sync(0xffffffffu, mine, owner);
+        if (lane == 0) a.nll[row] = -log_f(jmin(jmax(__fdiv_rn(picked, S2), a.lo), a.hi));
+    } else if (warp == 0 && lane == 0) {
+        *a.err = 1;
+        a.nll[row] = CUDART_NAN_F;
+    }
+}
+
 }  // namespace ktc

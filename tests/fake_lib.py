@@ -376,7 +376,7 @@ class FakeLib:
         return p, nll
 
     def ktc_softmax_xent_forward(self, softmax, nll, logits, targets, rows, cols, lo, hi):
-        if cols > 2048 or cols <= 64 or cols % 4:
+        if cols > 12288 or cols <= 64 or cols % 4:
             self.error = b"rows not handled in one pass"
             return L.KTC_ENOTSUP
         self._note("softmax_xent_forward")
@@ -388,7 +388,7 @@ class FakeLib:
 
     def ktc_softmax_xent_forward_expr(self, softmax, nll, logits, targets, rows, cols, lo, hi, code, n_code, imm, n_imm, leaves, lshapes, n_leaves, soft_leaf,
                                       stores, n_stores):
-        if cols > 2048 or cols <= 64 or cols % 4 or getattr(self, "no_softmax_epilogue", False):
+        if cols > 12288 or cols <= 64 or cols % 4 or getattr(self, "no_softmax_epilogue", False):
             self.error = b"rows not handled in one pass"
             return L.KTC_ENOTSUP
         self._note("softmax_xent_forward_expr")

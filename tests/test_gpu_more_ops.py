@@ -304,7 +304,7 @@ def test_index_checks_are_read_where_the_host_waits(cuda_ops, gc_scope):
     assert x.gather(1, good).toArray().reshape(-1).tolist() == [0, 1, 10, 11, 20, 21, 30, 31]
 
 
-@pytest.mark.parametrize("rows,cols", [(300, 2048), (64, 1000), (33, 128), (5, 68), (257, 1364)])
+@pytest.mark.parametrize("rows,cols", [(300, 2048), (64, 1000), (33, 128), (5, 68), (257, 1364), (70, 2052), (48, 4096), (37, 8192), (21, 12288), (19, 9000), (9, 6148)])
 def test_one_pass_softmax_forward_has_the_bits_of_the_call_sequence(cuda_ops, gc_scope, rows, cols):
     """ktc_softmax_xent_forward against the eleven raw-tensor calls of SoftmaxCrossEntropy.doForward
     (SoftmaxCrossEntropy.kt:40-59) issued one by one on the same library: the saved softmax and the per-row negative
@@ -313,7 +313,7 @@ def test_one_pass_softmax_forward_has_the_bits_of_the_call_sequence(cuda_ops, gc
     eps = cuda_ops.epsilon
     hi = float(np.float32(1.0) - np.float32(eps))
     x = D.uniform(rows * cols, 201, -6.0, 6.0)
-    x[::9973] = 45.0                                                   # a few rows with one dominant logit: softmax entries that underflow, clamped likelihoods
+    x.reshape(rows, cols)[::7, 3] = 45.0                               # every seventh row has one dominant logit: softmax entries that underflow, clamped likelihoods
     t = np.floor(D.uniform(rows, 202, 0.0, cols - 0.01)).astype(np.float32)
     logits, targets = cuda_ops.createRaw([rows, cols], x), cuda_ops.createRaw([rows], t)
     res = logits.softmaxCrossEntropyForward(targets, eps, hi)
@@ -327,14 +327,14 @@ def test_one_pass_softmax_forward_has_the_bits_of_the_call_sequence(cuda_ops, gc
     want_nll = norm.clamp(eps, hi).log().gather(-1, idx).unaryMinus()
     assert same_bits(softmax.toArray(), sm.toArray())
     assert same_bits(nll.toArray().reshape(-1), want_nll.toArray().reshape(-1))
-    assert len(np.unique(nll.toArray())) > rows // 2
+    assert len(np.unique(nll.toArray())) > rows // 4                   # not a constant: long rows clamp many likelihoods at -log(epsilon)
     assert same_bits(nll.mean().toArray(), want_nll.mean().toArray())
 
 
 def test_one_pass_softmax_forward_declines_and_checks(cuda_ops, gc_scope, index_checks_at_call):
     eps = cuda_ops.epsilon
     hi = float(np.float32(1.0) - np.float32(eps))
-    for rows, cols in ((4, 2052), (4, 4096), (4, 30), (4, 66)):           # too long, too short for the warp kernel, not a multiple of 4
+    for rows, cols in ((4, 12292), (4, 16384), (4, 30), (4, 66)):         # too long, too short for the warp kernel, not a multiple of 4
         logits = cuda_ops.createRaw([rows, cols], D.uniform(rows * cols, 203, -1.0, 1.0))
         assert logits.softmaxCrossEntropyForward(cuda_ops.createRawFill([rows], 0.0), eps, hi) is None
     logits = cuda_ops.createRaw([4, 128], D.uniform(512, 204, -1.0, 1.0))
@@ -344,7 +344,7 @@ def test_one_pass_softmax_forward_declines_and_checks(cuda_ops, gc_scope, index_
     assert ok is not None and np.isfinite(ok[1].toArray()).all()
 
 
-@pytest.mark.parametrize("rows,cols", [(1024, 2048), (700, 1024), (515, 512), (333, 640), (64, 68)])
+@pytest.mark.parametrize("rows,cols", [(1024, 2048), (700, 1024), (515, 512), (333, 640), (64, 68), (130, 4096), (65, 12288), (33, 5004)])
 def test_softmax_backward_inside_the_forward_kernel_has_the_bits_of_the_separate_kernels(cuda_ops, gc_scope, rows, cols):
     """Deferred, the forward of SoftmaxCrossEntropy waits for its consumer: the function's backward and the accumulation
     into the Variable's gradient (SoftmaxCrossEntropy.kt:61-67, Variable.kt:44-46) run as the epilogue of the kernel that
@@ -454,7 +454,7 @@ def test_softmax_forward_with_an_epilogue_program_through_the_c_abi(cuda_ops, gc
     assert rc != 0
 
 
-@pytest.mark.parametrize("rows,cols", [(513, 2048), (300, 1024), (77, 132)])
+@pytest.mark.parametrize("rows,cols", [(513, 2048), (300, 1024), (77, 132), (40, 8192)])
 def test_recorded_softmax_forward_without_a_consumer(cuda_ops, gc_scope, rows, cols):
     """Only the loss is asked for (no backward): the recorded forward runs on its own and, nothing holding the softmax,
     does not write it (ktc_softmax_xent_forward with softmax = 0); held, the softmax is written by the same kernel.  The

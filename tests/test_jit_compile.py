@@ -134,7 +134,7 @@ def test_last_axis_sum_sink_compiles():
             assert nbytes.value > 1000
 
 
-@pytest.mark.parametrize("cols", [2048, 1024, 512, 640])
+@pytest.mark.parametrize("cols", [2048, 1024, 512, 640, 4096, 12288])
 def test_softmax_row_kernel_with_an_epilogue_program_compiles(cols):
     """The generated form of the softmax forward (ktc_softmax_xent_forward_expr): the backward of SoftmaxCrossEntropy as
     its epilogue -- (0 with -1 at the target + softmax) / rows, then the accumulation into a zeroed gradient -- and a
