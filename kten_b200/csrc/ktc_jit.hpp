@@ -15,7 +15,8 @@ void jit_count_interpreter_launch();
 // The softmax row kernel (ktc_softmax.cuh) generated with a's program as its epilogue: leaf `soft_leaf` of the program
 // is the row's softmax, in registers.  Same return codes.
 struct SxArgs;
-bool softmax_row_length_ok(int64_t cols);          // ktc_softmax.cu: the row lengths the one-pass kernels take
+bool softmax_row_length_ok(int64_t cols);
+bool softmax_row_takes_cta(int64_t cols);           // ktc_softmax.cu: one CTA per row (sx_rows_cta) instead of one warp          // ktc_softmax.cu: the row lengths the one-pass kernels take
 int jit_launch_softmax(Device* d, const ExprArgs& a, int n_leaves, int soft_leaf, const SxArgs& sa);
 
 }  // namespace ktc

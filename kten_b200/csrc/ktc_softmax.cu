@@ -34,6 +34,14 @@ bool softmax_row_length_ok(int64_t cols) {
     return cols > tune("reduce_rows_small_max", 64) && cols <= kSxMaxColsCta && cols <= seg + seg / 2 && (cols & 3) == 0;
 }
 
+// rows that get one CTA (sx_rows_cta) instead of one warp: beyond what a warp's registers hold, and rows of fewer than 1024
+// columns without a kernel specialised on their length (a CTA of one warp with eight vectors per lane: measured 0.71 ms
+// against 1.04 ms for 2^28 logits in rows of 768, forward + backward; between 1024 and 2048 columns the two are level)
+bool softmax_row_takes_cta(int64_t cols) {
+    if (cols > kSxMaxVec * 128) return true;
+    return cols < 1024 && cols != 512 && tune("softmax_cta_short_rows", 1);
+}
+
 int launch_softmax_xent_forward(Device* d, float* softmax, float* nll, const float* logits, const float* targets,
                                 int64_t rows, int64_t cols, float lo, float hi) {
     if (rows == 0) return KTC_OK;
@@ -41,7 +49,7 @@ int launch_softmax_xent_forward(Device* d, float* softmax, float* nll, const flo
     if (grid > 0x7fffffffLL) return fail(KTC_ENOTSUP, "tensor too large for one launch");
     const SxArgs a{logits, targets, softmax, nll, rows, (int)cols, lo, hi, d->idx_err};
 #define KTC_SX(NV, MINB) k_softmax_xent_forward<NV, MINB><<<(int)grid, 256, 0, d->stream>>>(a)
-    if (cols > kSxMaxVec * 128) {                                  // one CTA per row
+    if (softmax_row_takes_cta(cols)) {                             // one CTA per row
         if (rows > 0x7fffffffLL) return fail(KTC_ENOTSUP, "tensor too large for one launch");
         k_softmax_xent_forward_cta<<<(unsigned)rows, 32 * sx_cta_warps((int)cols), 0, d->stream>>>(a);
     }
