@@ -22,9 +22,10 @@ __global__ void __launch_bounds__(256, MINB) k_softmax_xent_forward_pair(const _
     sx_rows_pair(a, none);
 }
 
+template <bool FULL>
 __global__ void __launch_bounds__(32 * kSxMaxWarpsCta, 2) k_softmax_xent_forward_cta(const __grid_constant__ SxArgs a) {
     SxNoEpilogue none;
-    sx_rows_cta(a, none);
+    sx_rows_cta<FULL>(a, none);
 }
 
 // Row lengths the one-pass kernels take: what ktc_reduce_axis(SUM) gives to ONE warp per row (whose accumulation they
@@ -51,7 +52,8 @@ int launch_softmax_xent_forward(Device* d, float* softmax, float* nll, const flo
 #define KTC_SX(NV, MINB) k_softmax_xent_forward<NV, MINB><<<(int)grid, 256, 0, d->stream>>>(a)
     if (softmax_row_takes_cta(cols)) {                             // one CTA per row
         if (rows > 0x7fffffffLL) return fail(KTC_ENOTSUP, "tensor too large for one launch");
-        k_softmax_xent_forward_cta<<<(unsigned)rows, 32 * sx_cta_warps((int)cols), 0, d->stream>>>(a);
+        if (cols % 1024 == 0) k_softmax_xent_forward_cta<true><<<(unsigned)rows, 32 * sx_cta_warps((int)cols), 0, d->stream>>>(a);
+        else k_softmax_xent_forward_cta<false><<<(unsigned)rows, 32 * sx_cta_warps((int)cols), 0, d->stream>>>(a);
     }
     else if (cols == 2048 && tune("softmax_pair", 1)) {                 // two warps per row: half the registers, twice the warps in flight
         const int64_t grid4 = (rows + 3) / 4;

@@ -230,7 +230,8 @@ __device__ __forceinline__ void sx_rows_pair(const SxArgs& a, Epi& epi) {
 constexpr int kSxMaxColsCta = 12288;
 constexpr int kSxMaxWarpsCta = kSxMaxColsCta / 1024;
 __host__ __device__ inline int sx_cta_warps(int cols) { return (cols + 1023) / 1024; }
-template <class Epi>
+// FULL: the row is a multiple of 1024 columns, every lane of every warp owns exactly eight vectors and the guards fold away
+template <bool FULL, class Epi>
 __device__ __forceinline__ void sx_rows_cta(const SxArgs& a, Epi& epi) {
     __shared__ float sh_max[kSxMaxWarpsCta];
     __shared__ float sh_run[2][kSxMaxWarpsCta][32];
@@ -240,7 +241,7 @@ __device__ __forceinline__ void sx_rows_cta(const SxArgs& a, Epi& epi) {
     const int cols = a.cols;
     const int q1 = cols >> 2;
     const int n_row = q1 > lane ? (q1 - lane + 31) >> 5 : 0;        // this lane's vectors in the one-warp form
-    const int n_l = min(max(n_row - 8 * warp, 0), 8);              // ... of which this warp holds [8 warp, 8 warp + n_l)
+    const int n_l = FULL ? 8 : min(max(n_row - 8 * warp, 0), 8);   // ... of which this warp holds [8 warp, 8 warp + n_l)
     const int first = lane + 256 * warp;                           // float4 index of the first
     const float4* px = reinterpret_cast<const float4*>(a.logits + row * cols) + first;
     float4 v[8];
