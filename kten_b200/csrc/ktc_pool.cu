@@ -249,6 +249,21 @@ __global__ void __launch_bounds__(256) k_pool_backward_ks(const float* __restric
     const float* ip = idx + t.plane * (int64_t)g.OH * g.OW;
     float* plane_in = gin + t.plane * (int64_t)g.H * g.W;
     const bool vec = (g.W & 3) == 0 && (reinterpret_cast<uintptr_t>(gin) & 15) == 0;
+    if (!IS_MAX && K == S && g.ph == 0 && g.pw == 0 && g.H == g.OH * K && g.W == g.OW * K && vec) {
+        // average pooling whose windows tile the plane exactly: every position lies in ONE window of K * K items, so its
+        // gradient is 0f + gradOut / (K * K) -- what the general walk below computes, without the walk
+        KTC_POOL_ROWS(y, g.H) {
+            const float* grow = gp + (y / K) * g.OW;
+            float* row = plane_in + y * g.W;
+            for (int x0 = threadIdx.x * 4; x0 < g.W; x0 += 4 * blockDim.x) {
+                float r[4];
+                #pragma unroll
+                for (int c = 0; c < 4; ++c) r[c] = __fadd_rn(0.f, div_items(__ldg(grow + (x0 + c) / K), K * K));
+                __stcs(reinterpret_cast<float4*>(row + x0), make_float4(r[0], r[1], r[2], r[3]));
+            }
+        }
+        return;
+    }
     for (int x0 = threadIdx.x * 4; x0 < g.W; x0 += 4 * blockDim.x) {
         int j0, j1, unused;                                  // the same for every row of the thread
         reach(x0, g.pw, K, S, g.OW, &j0, &unused);
