@@ -170,3 +170,24 @@ def test_an_interior_value_read_later_is_recomputed_from_the_logits():
     (h0, g0, n0, _), (h1, g1, n1, cl) = res
     assert same_bits(h0, h1) and same_bits(g0, g1) and same_bits(n0, n1)
     assert cl.count("softmax_xent_forward_expr") == 2 and "softmax_xent_forward" not in cl, cl
+
+
+def test_gradient_accumulated_over_two_steps():
+    """Two forward + backward passes into the same Variable without clearing or reading its gradient in between: the
+    gradient is then ONE expression over two pending forwards, which is not the form a forward takes into its kernel -- both
+    run on their own and the expression after them, with the bits of the call-by-call run."""
+    x, t = _inputs()
+    res = []
+    for mode in (False, True):
+        ops = make_ops()
+        ops.lazy = mode
+        with ops.garbageCollector():
+            logits = AG.Variable(ops, ops.createRaw([ROWS, COLS], x))
+            targets = AG.NoGradVariable(ops, ops.createRaw([ROWS], t))
+            for _ in range(2):
+                loss = logits.softmaxCrossEntropy(targets)
+                loss.backward()
+            res.append((logits.grad().toArray(), loss.toArray(), list(ops.lib.calls)))
+    (g0, l0, _), (g1, l1, cl) = res
+    assert same_bits(g0, g1) and same_bits(l0, l1)
+    assert cl.count("softmax_xent_forward") + cl.count("softmax_xent_forward_expr") == 2, cl
