@@ -1236,6 +1236,26 @@ static int operand(uint64_t id, Node** out) {
 static int assign(uint64_t target_id, Kind kind, int op, Node* a0, Node* a1, const float* imm, int nimm, int* state) {
     Cell* cell = cell_of(target_id);
     Node* own = cell->node;
+    if (!own->stored() && own->has_row) {
+        // The target is an expression over a pending softmax forward, and so is the operand (a gradient accumulated over two
+        // steps): in one expression neither forward could take its consumer along, so the target is evaluated first -- with
+        // its own forward -- and the new expression starts from the stored result.
+        Node* other = a0 == own ? a1 : a0;
+        if (other && other != own && other->has_row && !other->stored()) {
+            const bool first = a0 == own, second = a1 == own;
+            node_ref(other);
+            const int ms = materialize_cell(cell);
+            cell = cell_of(target_id);
+            if (ms == KTC_OK && cell) {
+                own = cell->node;
+                if (first) a0 = own;
+                if (second) a1 = own;
+            }
+            node_unref(other);                            // still held by the caller's cell
+            if (ms != KTC_OK) return ms;
+            if (!cell) return fail(KTC_ESTATE, "in-place call on a cell that went away");
+        }
+    }
     Node* node = new_node(kind, own->shape, op, a0, a1, imm, nimm);
     node_ref(node);
     auto done = [&](int s, int st) { if (state) *state = st; node_unref(node); return s; };
