@@ -15,8 +15,10 @@ namespace ktc {
 
 namespace {
 
-template <bool VEC>
-__global__ void __launch_bounds__(256) k_upsample_nearest(const float* __restrict__ in, float* __restrict__ out, int64_t P, int64_t W, int s) {
+// S > 0: the scale is S (2, 3 or 4) at compile time, so the divisions below are shifts or multiplications; S == 0: any scale
+template <bool VEC, int S>
+__global__ void __launch_bounds__(256) k_upsample_nearest(const float* __restrict__ in, float* __restrict__ out, int64_t P, int64_t W, int s_arg) {
+    const int s = S > 0 ? S : s_arg;
     const int64_t OW = W * s;
     if (VEC) {
         const int64_t q = OW >> 2;                                       // float4 per expanded row
@@ -119,8 +121,12 @@ extern "C" int ktc_upsample2d_nearest(ktc_buf out, ktc_buf in, int64_t P, int64_
     Device* d = device(bi.dev); if (!d) return KTC_ESTATE;
     KTC_TRY(use_device(d));
     const bool vec = ((W * scale) & 3) == 0 && aligned16(bo.ptr);
-    if (vec) k_upsample_nearest<true><<<grid_of(d, P * (W * scale / 4)), 256, 0, d->stream>>>(bi.ptr, bo.ptr, P, W, scale);
-    else     k_upsample_nearest<false><<<grid_of(d, P * W * scale * scale), 256, 0, d->stream>>>(bi.ptr, bo.ptr, P, W, scale);
+    const int g4 = grid_of(d, P * (W * scale / 4));
+    if (vec && scale == 2)      k_upsample_nearest<true, 2><<<g4, 256, 0, d->stream>>>(bi.ptr, bo.ptr, P, W, scale);
+    else if (vec && scale == 3) k_upsample_nearest<true, 3><<<g4, 256, 0, d->stream>>>(bi.ptr, bo.ptr, P, W, scale);
+    else if (vec && scale == 4) k_upsample_nearest<true, 4><<<g4, 256, 0, d->stream>>>(bi.ptr, bo.ptr, P, W, scale);
+    else if (vec)               k_upsample_nearest<true, 0><<<g4, 256, 0, d->stream>>>(bi.ptr, bo.ptr, P, W, scale);
+    else                        k_upsample_nearest<false, 0><<<grid_of(d, P * W * scale * scale), 256, 0, d->stream>>>(bi.ptr, bo.ptr, P, W, scale);
     return finish("upsample2d_nearest");
 }
 
