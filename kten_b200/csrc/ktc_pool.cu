@@ -192,20 +192,22 @@ __global__ void __launch_bounds__(256) k_pool_forward_ks(const float* __restrict
     float* iplane = IS_MAX ? idx + t.plane * (int64_t)g.OH * g.OW : nullptr;
     for (int j = threadIdx.x; j < g.OW; j += blockDim.x) {
         const int xa = j * S - g.pw;
+        bool xok[K];                                         // a window position is inside the plane if its row and its column are
+        #pragma unroll
+        for (int b = 0; b < K; ++b) xok[b] = (unsigned)(xa + b) < (unsigned)g.W;
         #pragma unroll 1
         for (int rb = 0; rb < kRowsPerThread; rb += RT) {
             float v[RT][K][K];
             #pragma unroll
             for (int r = 0; r < RT; ++r) {
                 const int i = t.row0 + (rb + r) * blockDim.y, ya = i * S - g.ph;
+                const float* corner = plane + ya * g.W + xa;  // may lie outside the plane: only dereferenced where yok && xok
                 #pragma unroll
                 for (int a = 0; a < K; ++a) {
+                    const bool yok = i < g.OH && (unsigned)(ya + a) < (unsigned)g.H;
                     #pragma unroll
-                    for (int b = 0; b < K; ++b) {
-                        const int y = ya + a, x = xa + b;
-                        const bool ok = i < g.OH && y >= 0 && y < g.H && x >= 0 && x < g.W;
-                        v[r][a][b] = ok ? __ldg(plane + y * g.W + x) : (IS_MAX ? -CUDART_INF_F : 0.f);
-                    }
+                    for (int b = 0; b < K; ++b)
+                        v[r][a][b] = (yok && xok[b]) ? __ldg(corner + a * g.W + b) : (IS_MAX ? -CUDART_INF_F : 0.f);
                 }
             }
             #pragma unroll
@@ -277,10 +279,12 @@ __global__ void __launch_bounds__(256) k_pool_backward_ks(const float* __restric
             float go[NI][NJ], ix[NI][NJ];
             #pragma unroll
             for (int a = 0; a < NI; ++a) {
+                const bool rok = i0 + a <= i1;
+                const int orow = (i0 + a) * g.OW + j0;
                 #pragma unroll
                 for (int b = 0; b < NJ; ++b) {
-                    const bool ok = i0 + a <= i1 && j0 + b <= j1;
-                    const int o = ok ? (i0 + a) * g.OW + j0 + b : 0;
+                    const bool ok = rok && j0 + b <= j1;
+                    const int o = ok ? orow + b : 0;
                     go[a][b] = __ldg(gp + o);
                     // max: an output outside the range takes a position no input has; average: it contributes through `ok` below
                     ix[a][b] = IS_MAX ? (ok ? __ldg(ip + o) : -2.0f) : (ok ? 1.0f : 0.0f);
