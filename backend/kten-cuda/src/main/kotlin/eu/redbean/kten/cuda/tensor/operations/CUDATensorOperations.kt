@@ -44,7 +44,7 @@ class CUDATensorOperations(override val platformKey: String, val device: Int) : 
      * (ktc_lazy_*) instead of running at once; the recorder fuses them into one kernel per iteration space when a
      * value is needed.  Results equal the call-by-call results bit for bit (sums: up to summation order).
      */
-    var lazy = false
+    var lazy = System.getenv("KTEN_CUDA_LAZY") == "1"      // the process-wide default (off: every call runs at once, like kten-jvm)
     var deferSums = true
         set(value) { field = value; setRecorderOption("defer_sums", if (value) 1 else 0) }
 

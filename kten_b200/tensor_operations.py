@@ -74,7 +74,8 @@ class CUDATensorOperations:
     # and run fused when a value is needed.  The recorder is one per process; its options are set through
     # these attributes.
     def _init_deferred(self) -> None:
-        self.lazy = False
+        import os
+        self.lazy = os.environ.get("KTEN_CUDA_LAZY", "0") == "1"    # the process-wide default; the attribute can be set at any time
         self._recorder = Z.Recorder(self.lib)
         self._pending_targets = set()       # buffers with a recorded `+= pending sum` update (may hold stale entries)
         self._options = {"recompute_limit": 2, "store_cost": 8, "defer_sums": 1, "defer_inplace": 1}
