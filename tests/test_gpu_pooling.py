@@ -121,3 +121,42 @@ def test_argument_checks(cuda_ops, gc_scope):
     assert lib.ktc_pool2d_avg(out.storeReference, x.storeReference, 3, ok, 0) == L.KTC_EINVAL                                                            # three planes do not fit
     with pytest.raises(ValueError, match="Padding should be smaller"):
         cuda_ops.spatialPooling((2, 2), (2, 2), (1, 1), (1, 1), PoolingOptions(PoolingType.MAX)).updateOutput(x)
+
+
+def test_random_geometries_match_the_oracle(cuda_ops, gc_scope):
+    """Sixty seeded geometries -- kernels 1 to 5, strides 1 to 4, any admissible padding, dilations 1 to 3, both rounding modes,
+    odd plane sizes -- for max and average pooling: results, positions and gradients bit-identical to the oracle (windows
+    other than 2 and 3, strides above 2 and dilations take the kernels with run-time window loops)."""
+    rng = np.random.default_rng(2024)
+    done = 0
+    while done < 60:
+        kh, kw = int(rng.integers(1, 6)), int(rng.integers(1, 6))
+        sh, sw = int(rng.integers(1, 5)), int(rng.integers(1, 5))
+        ph, pw = int(rng.integers(0, kh // 2 + 1)), int(rng.integers(0, kw // 2 + 1))
+        is_max = bool(rng.integers(0, 2))
+        dh, dw = (int(rng.integers(1, 4)), int(rng.integers(1, 4))) if is_max else (1, 1)
+        H, W = int(rng.integers(4, 40)), int(rng.integers(4, 40))
+        shape = [int(rng.integers(1, 4)), int(rng.integers(1, 5)), H, W] if rng.integers(0, 2) else [int(rng.integers(1, 6)), H, W]
+        opt = PoolingOptions(PoolingType.MAX if is_max else PoolingType.AVG, bool(rng.integers(0, 2)), bool(rng.integers(0, 2)))
+        x = rng.normal(size=shape).astype(np.float32)
+        if is_max:
+            x.reshape(-1)[::53] = np.round(x.reshape(-1)[::53])
+        res = []
+        try:
+            for ops in (ORACLE, cuda_ops):
+                op = ops.spatialPooling((kh, kw), (ph, pw), (sh, sw), (dh, dw), opt)
+                raw = ops.createRaw(shape, x.reshape(-1))
+                out, idx = op.updateOutput(raw)
+                g = np.random.default_rng(done).normal(size=out.shape).astype(np.float32)
+                gin = op.calculateGradInput(raw, ops.createRaw(list(out.shape), g.reshape(-1)), idx)
+                res.append((list(out.shape), out.toArray(), gin.toArray()) + ((idx.toArray(),) if idx is not None else ()))
+        except ValueError as exc:                                    # the window does not fit the plane: both backends must say so
+            assert "too small" in str(exc) and not res
+            with pytest.raises(ValueError, match="too small"):
+                cuda_ops.spatialPooling((kh, kw), (ph, pw), (sh, sw), (dh, dw), opt).updateOutput(cuda_ops.createRaw(shape, x.reshape(-1)))
+            continue
+        what = (kh, kw, sh, sw, ph, pw, dh, dw, shape, opt.type, opt.useCeil, opt.includePadding)
+        assert res[0][0] == res[1][0], what
+        for a, b in zip(res[0][1:], res[1][1:]):
+            assert same_bits(a, b), what
+        done += 1
