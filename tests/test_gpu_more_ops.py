@@ -482,3 +482,40 @@ def test_recorded_softmax_forward_without_a_consumer(cuda_ops, gc_scope, rows, c
     finally:
         cuda_ops.lazy = False
     assert same_bits(got_nll, want_nll.toArray()) and same_bits(got_nll2, want_nll.toArray()) and same_bits(got_sm, want_sm.toArray())
+
+
+def test_softmax_over_seeded_row_lengths(cuda_ops, gc_scope):
+    """Twenty-four seeded row lengths between 68 and 12288 columns (multiples of 4: every form of the row kernel -- one
+    warp with guards, specialised on the length, two warps, one CTA with and without guards): the one-pass forward has the
+    bits of the call sequence, and the deferred step (the backward inside the forward's kernel) the gradient of the
+    call-by-call step."""
+    from kten_b200 import autograd as AG
+    rng = np.random.default_rng(77)
+    eps = cuda_ops.epsilon
+    hi = float(np.float32(1.0) - np.float32(eps))
+    lengths = sorted({int(c) * 4 for c in rng.integers(17, 3073, 18)} | {128 * int(k) for k in rng.integers(1, 17, 3)} | {1024 * int(k) for k in rng.integers(1, 13, 3)})
+    for cols in lengths:
+        rows = int(rng.integers(3, 40))
+        x = rng.uniform(-8.0, 8.0, (rows, cols)).astype(np.float32)
+        x[::5, cols // 2] = 50.0                                       # rows with a dominant logit: underflowing quotients, clamped likelihoods
+        t = rng.integers(0, cols, rows).astype(np.float32)
+        logits, targets = cuda_ops.createRaw([rows, cols], x.reshape(-1)), cuda_ops.createRaw([rows], t)
+        softmax, nll = logits.softmaxCrossEntropyForward(targets, eps, hi)
+        max_val = logits.max(-1, keepDimensions=True)
+        exp_val = logits.minus(max_val).exp()
+        sm = exp_val.div(exp_val.sum(-1, keepDimensions=True))
+        norm = sm.div(sm.sum(-1, keepDimensions=True))
+        want_nll = norm.clamp(eps, hi).log().gather(-1, targets.view([rows, 1])).unaryMinus()
+        assert same_bits(softmax.toArray(), sm.toArray()), cols
+        assert same_bits(nll.toArray().reshape(-1), want_nll.toArray().reshape(-1)), cols
+        grads = []
+        for lazy in (False, True):
+            cuda_ops.lazy = lazy
+            try:
+                var = AG.Variable(cuda_ops, cuda_ops.createRaw([rows, cols], x.reshape(-1)))
+                loss = var.softmaxCrossEntropy(AG.NoGradVariable(cuda_ops, cuda_ops.createRaw([rows], t)))
+                loss.backward()
+                grads.append(var.grad().toArray())
+            finally:
+                cuda_ops.lazy = False
+        assert same_bits(grads[0], grads[1]), cols
