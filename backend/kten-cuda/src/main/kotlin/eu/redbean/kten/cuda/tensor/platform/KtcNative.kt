@@ -98,6 +98,8 @@ internal object KtcNative {
     val pool2dMaxGrad = handle("ktc_pool2d_max_grad", JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, ADDRESS)
     val pool2dAvg = handle("ktc_pool2d_avg", JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, ADDRESS, JAVA_INT)
     val pool2dAvgGrad = handle("ktc_pool2d_avg_grad", JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, ADDRESS, JAVA_INT)
+    // instruction codes of ktc_expr_eval programs used by the binding itself (enum in kten_cuda.h: op | dst << 8 | a << 12 | b << 16 | k << 20)
+    const val X_LOAD = 1; const val X_CONST = 2; const val X_ADD = 3; const val X_DIV = 6; const val X_STORE = 20; const val X_SCATC = 22
     const val ENOTSUP = -4
     // the deferred-expression recorder: elementwise calls and sums are recorded below the C ABI and run fused when a value is needed
     const val EXPR_SUM_ALL = 1; const val EXPR_SUM_ROWS = 2; const val EXPR_SUM_LAST = 4

@@ -126,6 +126,33 @@ class CUDARawTensor(
         return softmax to nll
     }
 
+    /**
+     * SoftmaxCrossEntropy.doBackward (SoftmaxCrossEntropy.kt:61-67) on the saved softmax (`this`) as one program of
+     * ktc_expr_eval: zerosLike, -1 scattered at the targets, `+= softmax`, `/= rows` -- the same four operations with
+     * their own roundings, one pass instead of four.  null when the calls are recorded anyway (the recorder fuses them
+     * itself, and with the forward) or the program is declined: the caller issues the calls.
+     */
+    fun softmaxCrossEntropyBackward(targets: CUDARawTensor, rows: Int): CUDARawTensor? {
+        if (ops.lazy || shape.size != 2 || shape[1] % 4 != 0) return null
+        fun ins(op: Int, d: Int = 0, a: Int = 0, b: Int = 0, k: Int = 0) = op or (d shl 8) or (a shl 12) or (b shl 16) or (k shl 20)
+        // leaves: 0 the targets [rows, 1], 1 the softmax; immediates: 0f, -1f, rows
+        val code = intArrayOf(ins(KtcNative.X_CONST, 0, k = 0), ins(KtcNative.X_LOAD, 1, k = 0), ins(KtcNative.X_SCATC, 0, 0, 1, k = 1),
+                              ins(KtcNative.X_LOAD, 1, k = 1), ins(KtcNative.X_ADD, 0, 0, 1), ins(KtcNative.X_CONST, 1, k = 2),
+                              ins(KtcNative.X_DIV, 0, 0, 1), ins(KtcNative.X_STORE, a = 0, k = 0))
+        val grad = ops.createRaw(shape)
+        val status = Arena.ofConfined().use { arena ->
+            KtcNative.exprEval.invokeExact(arena.allocateFrom(JAVA_INT, *code), code.size,
+                arena.allocateFrom(java.lang.foreign.ValueLayout.JAVA_FLOAT, 0f, -1f, rows.toFloat()), 3,
+                arena.allocateFrom(JAVA_LONG, shape[0].toLong(), shape[1].toLong()), 2,
+                arena.allocateFrom(JAVA_LONG, targets.handle, handle),
+                arena.allocateFrom(JAVA_LONG, shape[0].toLong(), 1L, shape[0].toLong(), shape[1].toLong()), 2,
+                arena.allocateFrom(JAVA_LONG, grad.handle), 1, 0 /* KTC_EXPR_STORE_ONLY */, 0L, 0) as Int
+        }
+        if (status == KtcNative.ENOTSUP) { ops.release(grad); return null }
+        check(status)
+        return grad
+    }
+
     internal fun recorded(shape: List<Int>, cell: Long): CUDARawTensor =
         CUDARawTensor(shape, CUDABuffer(0L, shape.toStoreSize()).also { it.lz = cell; it.lzShape = shape }, ops)
 

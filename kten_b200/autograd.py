@@ -1372,6 +1372,12 @@ class SoftmaxCrossEntropy(UnaryTensorFunction):    # functions/nn/SoftmaxCrossEn
         ops.release(max_val, shifted, exp_val, exp_sum, softmax_sum, softmax_norm, clipped, log_softmax, at_targets, nll)
 
     def doBackward(self, g):
+        fused = getattr(self.valuesSaved[0], "softmaxCrossEntropyBackward", None)
+        if fused is not None:
+            # the same capability test as in doForward: the four calls below as one pass, with their roundings
+            res = fused(self.targets._forwarded(), self.rows)
+            if res is not None:
+                return [res]
         grad_in = self.ops.zerosLike(self.valuesSaved[0])
         grad_in.inplaceScatter(-1, self.targets._forwarded(), -1.0)
         grad_in.plusAssign(self.valuesSaved[0])

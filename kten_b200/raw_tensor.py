@@ -574,6 +574,31 @@ class CUDARawTensor:
         L.check(rc)
         return softmax, nll
 
+    def softmaxCrossEntropyBackward(self, targets: "CUDARawTensor", rows: int):
+        """The backward of SoftmaxCrossEntropy (functions/nn/SoftmaxCrossEntropy.kt:61-67) on the saved softmax (`self`):
+        zerosLike, -1 scattered at the targets, `+= softmax`, `/= rows` as ONE program of ktc_expr_eval -- the same four
+        operations with their own roundings, one pass instead of four.  None when the calls are recorded anyway (the
+        recorder fuses them itself, and with the forward) or the program is declined: the caller issues the calls."""
+        if self.ops.lazy or len(self.shape) != 2 or targets.size != self.shape[0] or self.shape[1] % 4:
+            return None
+
+        def ins(op, d=0, a=0, b=0, k=0):
+            return op | d << 8 | a << 12 | b << 16 | k << 20
+
+        # leaves: 0 the targets [rows, 1], 1 the softmax; immediates: 0f, -1f, rows
+        code = [ins(L.X_CONST, 0, k=0), ins(L.X_LOAD, 1, k=0), ins(L.X_SCATC, 0, 0, 1, k=1), ins(L.X_LOAD, 1, k=1), ins(L.X_ADD, 0, 0, 1),
+                ins(L.X_CONST, 1, k=2), ins(L.X_DIV, 0, 0, 1), ins(L.X_STORE, a=0, k=0)]
+        n_rows, cols = self.shape
+        grad = self._new([n_rows, cols])
+        rc = self.ops.lib.ktc_expr_eval((C.c_uint32 * len(code))(*code), len(code), (C.c_float * 3)(0.0, -1.0, float(rows)), 3,
+                                        (C.c_int64 * 2)(n_rows, cols), 2, (C.c_uint64 * 2)(targets._buf(), self._buf()),
+                                        (C.c_int64 * 4)(n_rows, 1, n_rows, cols), 2, (C.c_uint64 * 1)(grad._buf()), 1, L.EXPR_STORE_ONLY, 0, 0)
+        if rc == L.KTC_ENOTSUP:
+            grad.release()
+            return None
+        L.check(rc)
+        return grad
+
     def sumToShape(self, old_shape: Sequence[int]) -> "CUDARawTensor":
         """mayUnexpand in one call (autograd/functions/Utils.kt:14-41)."""
         old_shape = [int(d) for d in old_shape]

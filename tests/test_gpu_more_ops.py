@@ -519,3 +519,28 @@ def test_softmax_over_seeded_row_lengths(cuda_ops, gc_scope):
             finally:
                 cuda_ops.lazy = False
         assert same_bits(grads[0], grads[1]), cols
+
+
+@pytest.mark.parametrize("rows,cols", [(300, 2048), (77, 132), (40, 8192), (9, 68)])
+def test_eager_softmax_backward_in_one_pass_has_the_bits_of_the_four_calls(cuda_ops, gc_scope, rows, cols):
+    """Call by call, the backward of SoftmaxCrossEntropy (SoftmaxCrossEntropy.kt:61-67) runs as one program of
+    ktc_expr_eval: the bits of zerosLike, inplaceScatter(-1), += softmax, /= rows issued one by one."""
+    eps = cuda_ops.epsilon
+    hi = float(np.float32(1.0) - np.float32(eps))
+    x = D.uniform(rows * cols, 241, -5.0, 5.0)
+    t = np.floor(D.uniform(rows, 242, 0.0, cols - 0.01)).astype(np.float32)
+    logits, targets = cuda_ops.createRaw([rows, cols], x), cuda_ops.createRaw([rows, 1], t)
+    softmax, _ = logits.softmaxCrossEntropyForward(targets, eps, hi)
+    l0 = cuda_ops.lib.ktc_launch_count()
+    got = softmax.softmaxCrossEntropyBackward(targets, rows)
+    assert got is not None and cuda_ops.lib.ktc_launch_count() - l0 == 1
+    want = cuda_ops.zerosLike(softmax)
+    want.inplaceScatter(-1, targets, -1.0)
+    want.plusAssign(softmax)
+    want.divAssign(float(rows))
+    assert same_bits(got.toArray(), want.toArray())
+    cuda_ops.lazy = True
+    try:
+        assert softmax.softmaxCrossEntropyBackward(targets, rows) is None        # recorded calls are fused by the recorder
+    finally:
+        cuda_ops.lazy = False
