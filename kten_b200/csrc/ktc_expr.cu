@@ -211,6 +211,9 @@ __device__ __forceinline__ void combine_put(const CombineArgs& a, int j, int64_t
 }
 
 __global__ void __launch_bounds__(256) k_combine_multi(const __grid_constant__ CombineArgs a) {
+    // Launched with programmatic stream serialisation, this kernel's CTAs may be scheduled while the first pass drains; they
+    // wait here until that grid has completed and its partial sums are visible (a no-op after an ordinary launch).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     __shared__ double sm[8];
     __shared__ int last_block, timed_out;
     int j = 0;
@@ -490,7 +493,18 @@ static int expr_eval_impl(Device** scatc_dev, const uint32_t* code, int n_code, 
             c.exchange = 1;
         }
         KTC_TRY(launch_expr(d, a, n_leaves, sink, grid, total));
-        k_combine_multi<<<blocks, 256, 0, d->stream>>>(c);
+        {
+            // the second pass follows the first in the stream, but its launch need not wait for the first to end: it is allowed to
+            // start early and waits for the first pass itself (griddepcontrol.wait at its top), which hides its launch latency
+            cudaLaunchConfig_t cfg{};
+            cfg.gridDim = dim3((unsigned)blocks); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = d->stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr; cfg.numAttrs = tune("expr_overlap_second_pass", 1) ? 1 : 0;
+            const cudaError_t le = cudaLaunchKernelEx(&cfg, k_combine_multi, c);
+            if (le != cudaSuccess) { cudaGetLastError(); k_combine_multi<<<blocks, 256, 0, d->stream>>>(c); }
+        }
         KTC_TRY(finish_launch_expr("expr(combine)"));
         return KTC_OK;
     }
