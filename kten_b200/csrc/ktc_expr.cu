@@ -56,6 +56,7 @@ static __device__ __noinline__ float4 expr_tanh(float4 x) {
 
 template <int SINK>
 __global__ void __launch_bounds__(256) k_expr(const __grid_constant__ ExprArgs p) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");      // launched early (launch_early below): the stream's earlier work is complete from here on
     __shared__ float4 regs[kExprRegs][256];
     __shared__ double sm_part[SINK == KTC_EXPR_SUM_ROWS ? 8 * 32 * 4 : 8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -268,6 +269,23 @@ __global__ void __launch_bounds__(256) k_combine_multi(const __grid_constant__ C
     p2p_exchange_block(a.x, &timed_out);
 }
 
+// Launches a kernel that begins with griddepcontrol.wait so that its CTAs may be scheduled while the kernel before it in the
+// stream drains (programmatic stream serialisation): the stream's order, with the launch latency hidden.
+template <class... Params, class... Args>
+static inline void launch_early(void (*kernel)(Params...), dim3 grid, dim3 block, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = 0; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = tune("expr_overlap_launches", 1) ? 1 : 0;
+    if (cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...) != cudaSuccess && cfg.numAttrs) {
+        cudaGetLastError();                                  // an attribute the driver refuses: the ordinary way
+        cfg.numAttrs = 0;
+        cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+    }
+}
+
 static inline int finish_launch_expr(const char* what) {
     count_launch(1);
     cudaError_t e = cudaGetLastError();
@@ -284,9 +302,9 @@ static int launch_expr(Device* d, const ExprArgs& a, int n_leaves, int sink, int
     }
     if (sink == KTC_EXPR_MULTI) return fail(KTC_ENOTSUP, "ktc_expr_eval_multi: no generated kernel for this program (iteration space below expr_jit_min_elems, or NVRTC unavailable)");
     jit_count_interpreter_launch();
-    if (sink == KTC_EXPR_STORE_ONLY) k_expr<KTC_EXPR_STORE_ONLY><<<(int)grid, 256, 0, d->stream>>>(a);
-    else if (sink == KTC_EXPR_SUM_ALL) k_expr<KTC_EXPR_SUM_ALL><<<(int)grid, 256, 0, d->stream>>>(a);
-    else k_expr<KTC_EXPR_SUM_ROWS><<<(int)grid, 256, 0, d->stream>>>(a);
+    if (sink == KTC_EXPR_STORE_ONLY) launch_early(k_expr<KTC_EXPR_STORE_ONLY>, dim3((unsigned)grid), dim3(256), d->stream, a);
+    else if (sink == KTC_EXPR_SUM_ALL) launch_early(k_expr<KTC_EXPR_SUM_ALL>, dim3((unsigned)grid), dim3(256), d->stream, a);
+    else launch_early(k_expr<KTC_EXPR_SUM_ROWS>, dim3((unsigned)grid), dim3(256), d->stream, a);
     return finish_launch_expr("expr");
 }
 
@@ -493,18 +511,10 @@ static int expr_eval_impl(Device** scatc_dev, const uint32_t* code, int n_code, 
             c.exchange = 1;
         }
         KTC_TRY(launch_expr(d, a, n_leaves, sink, grid, total));
-        {
-            // the second pass follows the first in the stream, but its launch need not wait for the first to end: it is allowed to
-            // start early and waits for the first pass itself (griddepcontrol.wait at its top), which hides its launch latency
-            cudaLaunchConfig_t cfg{};
-            cfg.gridDim = dim3((unsigned)blocks); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = d->stream;
-            cudaLaunchAttribute attr[1];
-            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-            attr[0].val.programmaticStreamSerializationAllowed = 1;
-            cfg.attrs = attr; cfg.numAttrs = tune("expr_overlap_second_pass", 1) ? 1 : 0;
-            const cudaError_t le = cudaLaunchKernelEx(&cfg, k_combine_multi, c);
-            if (le != cudaSuccess) { cudaGetLastError(); k_combine_multi<<<blocks, 256, 0, d->stream>>>(c); }
-        }
+        // the second pass follows the first in the stream, but its launch need not wait for the first to end: it starts early and
+        // waits for the first pass itself (griddepcontrol.wait at its top)
+        if (tune("expr_overlap_second_pass", 1)) launch_early(k_combine_multi, dim3((unsigned)blocks), dim3(256), d->stream, c);
+        else k_combine_multi<<<blocks, 256, 0, d->stream>>>(c);
         KTC_TRY(finish_launch_expr("expr(combine)"));
         return KTC_OK;
     }
